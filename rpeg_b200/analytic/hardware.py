@@ -1,0 +1,99 @@
+"""Alpha-beta hardware description used by the cost and memory models.
+
+The field set and tier selection follow the reference (RPEG/model/hardware.py:18-122): peak FLOP/s,
+HBM capacity and bandwidth, alpha/beta for collectives and point-to-point on three tiers (inside a
+node ``g``, across nodes ``n``, across racks ``r``), GEMM saturation constants, decode bandwidth
+efficiency, non-GEMM per-layer costs and the run-time correction scales.
+
+Two additions describe an NVSwitch machine such as an 8xB200 node:
+  * ``fabric="nvswitch"`` replaces the ring collective formulas inside a node with switch ones
+    (every GPU reaches every peer at full link bandwidth; all-reduce can reduce in the switch);
+  * ``fused_overlap`` in [0, 1] is the measured fraction of a tensor-parallel or data-parallel
+    collective that the fused compute+collective kernels hide behind math.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, fields, replace
+from typing import Iterable, Tuple
+
+from ..core.types import Allocation
+
+
+@dataclass(frozen=True)
+class Hardware:
+    flops_per_gpu: float
+    memory_per_gpu: float
+    memory_bandwidth: float
+    alpha_coll_g: float
+    beta_coll_g: float
+    alpha_coll_n: float
+    beta_coll_n: float
+    alpha_coll_r: float
+    beta_coll_r: float
+    alpha_p2p_g: float
+    beta_p2p_g: float
+    alpha_p2p_n: float
+    beta_p2p_n: float
+    alpha_p2p_r: float
+    beta_p2p_r: float
+    gemm_m_half: float = 5.0
+    gemm_k_half: float = 0.0
+    decode_bw_eff: float = 0.15
+    non_gemm_constant: float = 0.0
+    non_gemm_scaling: float = 0.0
+    non_gemm_batch_cal: float = 64
+    op_generation_scale: float = 1.0
+    op_inference_scale: float = 1.0
+    op_training_scale: float = 1.0
+    activation_comm_overhead_s: float = 0.0
+    weight_comm_scale: float = 1.0
+    reshard_scale: float = 1.0
+    # --- NVSwitch / fused-kernel extensions (defaults keep the reference's ring model exactly)
+    fabric: str = "ring"
+    fused_overlap: float = 0.0
+
+    @staticmethod
+    def _span(allocs: Iterable[Allocation]) -> Tuple[int, int]:
+        allocs = tuple(allocs)
+        racks = max(a.origin[0] + a.extent[0] for a in allocs) - min(a.origin[0] for a in allocs)
+        nodes = max(a.origin[1] + a.extent[1] for a in allocs) - min(a.origin[1] for a in allocs)
+        return racks, nodes
+
+    def tier_name(self, allocs: Iterable[Allocation]) -> str:
+        racks, nodes = self._span(allocs)
+        return "r" if racks > 1 else ("n" if nodes > 1 else "g")
+
+    def tier_coll(self, allocs: Iterable[Allocation]) -> Tuple[float, float]:
+        t = self.tier_name(allocs)
+        return getattr(self, f"alpha_coll_{t}"), getattr(self, f"beta_coll_{t}")
+
+    def tier_p2p(self, allocs: Iterable[Allocation]) -> Tuple[float, float]:
+        t = self.tier_name(allocs)
+        return getattr(self, f"alpha_p2p_{t}"), getattr(self, f"beta_p2p_{t}")
+
+    def tier(self, allocs: Iterable[Allocation]) -> Tuple[float, float]:
+        return self.tier_p2p(allocs)
+
+    def with_updates(self, **kw) -> "Hardware":
+        return replace(self, **kw)
+
+    @classmethod
+    def field_names(cls) -> Tuple[str, ...]:
+        return tuple(f.name for f in fields(cls))
+
+
+def b200_nvswitch(flops: float = 1.37e15, hbm_bw: float = 6.5e12, mem: float = 180e9,
+                  link_bw: float = 770e9, allreduce_busbw: float = 725e9) -> Hardware:
+    """One 8xB200 NVSwitch node: measured sustained bf16 GEMM rate, STREAM-style HBM copy rate,
+    peer copy 770 GB/s per direction, 8-rank all-reduce bus bandwidth 725 GB/s. The inter-node and
+    inter-rack tiers are filled with a 400 Gb/s-per-GPU network so multi-node plans stay priceable."""
+    ib = 1.0 / 50e9
+    return Hardware(
+        flops_per_gpu=flops, memory_per_gpu=mem, memory_bandwidth=hbm_bw,
+        alpha_coll_g=6e-6, beta_coll_g=1.0 / allreduce_busbw,
+        alpha_coll_n=25e-6, beta_coll_n=ib, alpha_coll_r=40e-6, beta_coll_r=2 * ib,
+        alpha_p2p_g=4e-6, beta_p2p_g=1.0 / link_bw,
+        alpha_p2p_n=15e-6, beta_p2p_n=ib, alpha_p2p_r=30e-6, beta_p2p_r=2 * ib,
+        gemm_m_half=96.0, gemm_k_half=0.0, decode_bw_eff=0.6,
+        fabric="nvswitch", fused_overlap=0.0,
+    )

@@ -1,0 +1,314 @@
+// Causal flash attention forward for sm_100a on packed variable-length sequences, head dim 128.
+//
+//   O = softmax(Q K^T * scale + causal) V      per (sequence, head)
+//
+// One CTA = one 128-row query tile of one head. Both GEMMs run on tcgen05 with accumulators in
+// TMEM:
+//   S = Q K^T   : A = Q tile, B = K tile, both K-major in shared memory (two 64-column 128B-swizzle
+//                 atoms each), accumulator S in TMEM (double buffered so S_{j+1} is computed while
+//                 the softmax of S_j runs);
+//   O += P V    : A = P read directly from TMEM (bf16, written over S by the softmax threads),
+//                 B = V tile in shared memory, MN-major (head dim contiguous).
+// Softmax maps one thread to one query row (TMEM lane), so row max / row sum need no shuffles.
+// The running max is only refreshed when it grows by more than 8 (in log2 units); a stale max is
+// exact after the final division by l, and it makes the O rescale (TMEM load, scale, store) rare.
+//
+// Q/K/V are column blocks of one packed [T, ld] bf16 activation (the fused QKV projection output);
+// cu_seqlens[b] is the first row of sequence b. Outputs: O [T, H*128] bf16, LSE [H, T] fp32.
+//
+// Replaces the reference's attention: Megatron core attention with an explicit (1,1,s,s) causal
+// mask (RPEG/runtime/workers/megatron_worker.py:457,691,1618) / F.scaled_dot_product_attention in
+// calibrate.py:230-376.
+#include "common.cuh"
+#include "rpeg_kernels.h"
+
+namespace rpeg {
+
+constexpr int FA_BM = 128;   // query rows per CTA
+constexpr int FA_BN = 128;   // keys per tile
+constexpr int FA_HD = 128;
+constexpr int FA_THREADS = 192;
+constexpr int FA_TILE_BYTES = 128 * 128 * 2;  // 32 KiB: one [128 x 128] bf16 tile (two 16 KiB atoms)
+constexpr int FA_KV_STAGES = 2;
+constexpr int FA_SMEM = FA_TILE_BYTES * (1 + 2 * FA_KV_STAGES) + 1024 + 256;
+constexpr float FA_RESCALE_THRESHOLD = 8.0f;
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const int* __restrict__ cu_seqlens,
+                      __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out, int T, int H, int Hkv,
+                      int q_col0, int k_col0, int v_col0, float scale_log2, int* status) {
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
+  const int seq0 = cu_seqlens[b];
+  const int L = cu_seqlens[b + 1] - seq0;
+  const int q0 = qt * FA_BM;
+  if (q0 >= L) return;
+  const int hk = h / (H / Hkv);
+  const int kv_len = min(L, q0 + FA_BM);
+  const int n_tiles = (kv_len + FA_BN - 1) / FA_BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_sm = smem;
+  uint8_t* k_sm = smem + FA_TILE_BYTES;
+  uint8_t* v_sm = k_sm + FA_KV_STAGES * FA_TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_sm + FA_KV_STAGES * FA_TILE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = k_full + FA_KV_STAGES;
+  uint64_t* v_full = k_empty + FA_KV_STAGES;
+  uint64_t* v_empty = v_full + FA_KV_STAGES;
+  uint64_t* s_full = v_empty + FA_KV_STAGES;  // [2]
+  uint64_t* p_full = s_full + 2;              // [2]
+  uint64_t* pv_done = p_full + 2;             // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < FA_KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4); }
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_qkv);
+      mbar_expect_tx(q_full, FA_TILE_BYTES);
+      tma_load_2d(q_sm, &tmap_qkv, q_full, q_col0 + h * FA_HD, seq0 + q0);
+      tma_load_2d(q_sm + 16384, &tmap_qkv, q_full, q_col0 + h * FA_HD + 64, seq0 + q0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j % FA_KV_STAGES;
+        const uint32_t ph = static_cast<uint32_t>(j / FA_KV_STAGES) & 1u;
+        if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag, status, 500)) break;
+        mbar_expect_tx(&k_full[st], FA_TILE_BYTES);
+        tma_load_2d(k_sm + st * FA_TILE_BYTES, &tmap_qkv, &k_full[st], k_col0 + hk * FA_HD, seq0 + j * FA_BN);
+        tma_load_2d(k_sm + st * FA_TILE_BYTES + 16384, &tmap_qkv, &k_full[st], k_col0 + hk * FA_HD + 64,
+                    seq0 + j * FA_BN);
+        if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag, status, 501)) break;
+        mbar_expect_tx(&v_full[st], FA_TILE_BYTES);
+        tma_load_2d(v_sm + st * FA_TILE_BYTES, &tmap_qkv, &v_full[st], v_col0 + hk * FA_HD, seq0 + j * FA_BN);
+        tma_load_2d(v_sm + st * FA_TILE_BYTES + 16384, &tmap_qkv, &v_full[st], v_col0 + hk * FA_HD + 64,
+                    seq0 + j * FA_BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 128, 0, 1);
+      const uint32_t q_addr = smem_u32(q_sm);
+      auto issue_qk = [&](int j) {
+        const int st = j % FA_KV_STAGES;
+        const uint32_t k_addr = smem_u32(k_sm + st * FA_TILE_BYTES);
+        const uint32_t ts = tmem_base + static_cast<uint32_t>((j & 1) * 128);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = static_cast<uint32_t>((k >> 2) * 16384 + (k & 3) * 32);
+          umma_bf16_ss(ts, make_smem_desc_sw128(q_addr + off, 16, 1024), make_smem_desc_sw128(k_addr + off, 16, 1024),
+                       idesc_qk, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[j & 1]);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, status, 510);
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, status, 511);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_qk(0);
+        for (int j = 0; j < n_tiles; ++j) {
+          const int st = j % FA_KV_STAGES;
+          const uint32_t ph = static_cast<uint32_t>(j / FA_KV_STAGES) & 1u;
+          if (j + 1 < n_tiles) {
+            const int st1 = (j + 1) % FA_KV_STAGES;
+            const uint32_t ph1 = static_cast<uint32_t>((j + 1) / FA_KV_STAGES) & 1u;
+            if (!mbar_wait(&k_full[st1], ph1, abort_flag, status, 512)) break;
+            tc_fence_after_sync();
+            issue_qk(j + 1);
+          }
+          if (!mbar_wait(&p_full[j & 1], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, status, 513)) break;
+          if (!mbar_wait(&v_full[st], ph, abort_flag, status, 514)) break;
+          tc_fence_after_sync();
+          const uint32_t v_addr = smem_u32(v_sm + st * FA_TILE_BYTES);
+          const uint32_t tp = tmem_base + static_cast<uint32_t>((j & 1) * 128);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            // 16 keys per step: 8 packed TMEM columns of P, 16 rows (2 KiB) of the V tile.
+            umma_bf16_ts(tmem_o, tp + k * 8, make_smem_desc_sw128(v_addr + k * 2048, 16384, 1024), idesc_pv,
+                         (j | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&v_empty[st]);
+          umma_commit(pv_done);
+        }
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int qi = q0 + r;  // position inside the sequence
+    const bool row_valid = qi < L;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    // pv_done completes once per KV tile. A parity wait only tells "that phase is over" when the
+    // waiter is at most one phase behind, so every completion is consumed in order: completion
+    // j-2 is already implied by s_full[j] (QK_j is issued after PV_{j-2}) and costs nothing.
+    int pv_seen = 0;
+    auto wait_pv = [&](int upto, int where) -> bool {
+      while (pv_seen <= upto) {
+        if (!__all_sync(0xffffffffu, mbar_wait(pv_done, static_cast<uint32_t>(pv_seen) & 1u, abort_flag, status, where)))
+          return false;
+        ++pv_seen;
+      }
+      return true;
+    };
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const uint32_t ts = tmem_base + lane_base + static_cast<uint32_t>((j & 1) * 128);
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, status, 520))) { ok = false; break; }
+      if (!wait_pv(j - 2, 523)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int k0 = j * FA_BN;
+      const bool need_mask = (k0 + FA_BN - 1 > q0) || (k0 + FA_BN > L);
+      // pass 1: row max
+      float tmax = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kj = k0 + c * 32 + i;
+          const bool valid = !need_mask || (kj <= qi && kj < L);
+          if (valid) tmax = fmaxf(tmax, __uint_as_float(v[i]));
+        }
+      }
+      tmax *= scale_log2;  // scale > 0, so max commutes with the scaling
+      if (!row_valid || tmax == -INFINITY) tmax = (m_ref == -INFINITY) ? 0.f : m_ref;
+      bool need = false;
+      if (j == 0) {
+        m_ref = tmax;
+      } else {
+        need = tmax > m_ref + FA_RESCALE_THRESHOLD;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        if (!wait_pv(j - 1, 521)) { ok = false; break; }
+        tc_fence_after_sync();
+        const float alpha = need ? exp2f(m_ref - tmax) : 1.f;
+        if (need) { m_ref = tmax; l *= alpha; }
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_o + lane_base + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32(tmem_o + lane_base + c * 32, v);
+        }
+        tmem_wait_st();
+      }
+      // pass 2: P = exp2(s*scale - m_ref), packed bf16 written over the S buffer
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(ts + c * 32, v);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int kj = k0 + c * 32 + 2 * i;
+          const bool v0 = row_valid && (!need_mask || (kj <= qi && kj < L));
+          const bool v1 = row_valid && (!need_mask || (kj + 1 <= qi && kj + 1 < L));
+          const float p0 = v0 ? exp2f(__uint_as_float(v[2 * i]) * scale_log2 - m_ref) : 0.f;
+          const float p1 = v1 ? exp2f(__uint_as_float(v[2 * i + 1]) * scale_log2 - m_ref) : 0.f;
+          l += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x16(ts + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[j & 1]);
+    }
+    if (ok && wait_pv(n_tiles - 1, 522)) {
+      tc_fence_after_sync();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = out + (static_cast<size_t>(seq0 + qi) * H + h) * FA_HD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_o + lane_base + c * 32, v);
+        tmem_wait_ld();
+        if (row_valid) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[i * 8 + 0]) * inv_l, __uint_as_float(v[i * 8 + 1]) * inv_l);
+            o.y = pack_bf16x2(__uint_as_float(v[i * 8 + 2]) * inv_l, __uint_as_float(v[i * 8 + 3]) * inv_l);
+            o.z = pack_bf16x2(__uint_as_float(v[i * 8 + 4]) * inv_l, __uint_as_float(v[i * 8 + 5]) * inv_l);
+            o.w = pack_bf16x2(__uint_as_float(v[i * 8 + 6]) * inv_l, __uint_as_float(v[i * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = o;
+          }
+        }
+      }
+      if (row_valid && lse_out != nullptr)
+        lse_out[static_cast<size_t>(h) * T + seq0 + qi] = (m_ref + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+
+}  // namespace rpeg
+
+using namespace rpeg;
+
+extern "C" int rpeg_flash_attn_fwd(const void* qkv, int ld, int q_col0, int k_col0, int v_col0,
+                                   const int* cu_seqlens, int B, int max_seqlen, int T, int H, int Hkv, int hd,
+                                   float scale, void* out, float* lse, int* status, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (hd != FA_HD || H % Hkv != 0) return -2;
+  if ((ld | q_col0 | k_col0 | v_col0) & 7) return -3;
+  if (reinterpret_cast<uintptr_t>(qkv) & 15) return -1;
+  if (B <= 0 || T <= 0 || max_seqlen <= 0) return 0;
+  CUtensorMap tm;
+  const int rc = make_tmap_bf16_2d(&tm, qkv, static_cast<uint64_t>(ld), static_cast<uint64_t>(T),
+                                   static_cast<uint64_t>(ld), 64, 128);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  dim3 grid((max_seqlen + FA_BM - 1) / FA_BM, H, B);
+  flash_attn_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, stream>>>(tm, cu_seqlens, static_cast<__nv_bfloat16*>(out), lse,
+                                                              T, H, Hkv, q_col0, k_col0, v_col0,
+                                                              scale * 1.4426950408889634f, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

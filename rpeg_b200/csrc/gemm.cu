@@ -1,0 +1,351 @@
+// bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM -> epilogue.
+//
+//   C[M,N] = op(A)[M,K] * op(B)[N,K]^T        (fp32 accumulate in TMEM)
+//
+// transA = 0: A is stored [M,K] (K contiguous, "K-major");  1: A is stored [K,M] ("MN-major").
+// transB = 0: B is stored [N,K] (the [out,in] layout of a linear weight); 1: B is stored [K,N].
+// Those four combinations cover forward (x W^T), dgrad (dy W) and wgrad (dy^T x) of a linear layer
+// without materialising a transposed copy: the MN-major cases only change the TMA box and the
+// shared-memory matrix descriptor.
+//
+// Kernel structure (persistent, one CTA per SM, 192 threads):
+//   warp 0      TMA producer: fills a ring of STAGES {A tile, B tile} buffers
+//   warp 1      allocates TMEM, issues tcgen05.mma from one thread, frees TMEM at the end
+//   warps 2..5  epilogue: tcgen05.ld the 128 x BN fp32 accumulator (thread = row), convert, store
+// The accumulator is double buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps
+// the main loop of tile i+1.
+//
+// Replaces the cuBLASLt / TransformerEngine GEMMs the reference reaches through megatron-core
+// (reference: RPEG/runtime/workers/megatron_worker.py:676-715 builds the GPTModel whose
+// linear_qkv / linear_proj / linear_fc1 / linear_fc2 / output_layer run them).
+#include "common.cuh"
+#include "rpeg_kernels.h"
+
+namespace rpeg {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_BUDGET = 227 * 1024 - 2048;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
+  static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+};
+
+enum { EPI_BF16 = 0, EPI_F32 = 1 };
+
+template <int BN, int EPI, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         void* __restrict__ Cout, int M, int N, int K, int ldc, int accumulate, int* status) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_area = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Tile order: groups of 8 M-tiles sweep N together so the A rows stay in L2.
+  constexpr int GROUP_M = 8;
+  auto tile_coords = [&](int t, int& tm, int& tn) {
+    const int per_group = GROUP_M * n_tiles;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(m_tiles - first_m, GROUP_M);
+    const int r = t - g * per_group;
+    tm = first_m + (r % gsize);
+    tn = r / gsize;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, 100)) goto producer_done;
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + c * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    producer_done:;
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1u, abort_flag, status, 200)) goto mma_done;
+        tc_fence_after_sync();
+        const uint32_t tacc = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, 201)) goto mma_done;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // K-major: 16 bf16 along K = 32 bytes inside the swizzle row.
+            // MN-major: 16 K rows of 128 bytes; 64-element MN chunks are one TMA box (8 KiB) apart.
+            const uint64_t da = A_MN ? make_smem_desc_sw128(sa + k * 2048, 64 * BK * 2, 1024)
+                                     : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, 64 * BK * 2, 1024)
+                                     : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_bf16_ss(tacc, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        umma_commit(&tfull_bar[buf]);
+        if (++buf == 2) { buf = 0; acc_phase ^= 1u; }
+      }
+    mma_done:;
+    }
+  } else {
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int buf = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, tm, tn);
+      const int row = tm * BM + quad * 32 + lane;
+      const int n0 = tn * BN;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, status, 300))) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(buf * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          if constexpr (EPI == EPI_BF16) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col0 + v * 8 < N) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                *reinterpret_cast<uint4*>(crow + v * 8) = o;
+              }
+            }
+          } else {
+            float* crow = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              if (col0 + v * 4 < N) {
+                float4 o = make_float4(__uint_as_float(r[v * 4 + 0]), __uint_as_float(r[v * 4 + 1]),
+                                       __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+                if (accumulate) {
+                  const float4 p = *reinterpret_cast<const float4*>(crow + v * 4);
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                *reinterpret_cast<float4*>(crow + v * 4) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      if (++buf == 2) { buf = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // Teardown. After an aborted wait there may be bulk copies in flight into this CTA's shared
+  // memory; give them time to land before the block exits.
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements, 128-byte swizzle.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -10;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+template <int BN, int EPI, bool A_MN, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, int ldc,
+                       int accumulate, int* status, int num_sms, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -20;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, accumulate, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+template <int BN, int EPI>
+static int dispatch_major(int transA, int transB, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M,
+                          int N, int K, int ldc, int accumulate, int* status, int num_sms, cudaStream_t stream) {
+  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, status, num_sms, stream);
+  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, status, num_sms, stream);
+  if constexpr (BN >= 64) {  // an MN-major B tile is built from 64-column TMA boxes
+    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, status, num_sms, stream);
+    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, status, num_sms, stream);
+  }
+  return -30;
+}
+
+static int g_num_sms = 0;
+
+}  // namespace rpeg
+
+using namespace rpeg;
+
+extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                              int ldc, int transA, int transB, int out_fp32, int accumulate, int bn_hint,
+                              int* status, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  // TMA needs 16-byte aligned bases and row pitches; the vector epilogue needs N and ldc % 8 == 0.
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return -1;
+  if ((lda | ldb | ldc) & 7) return -2;
+  if (N & 7) return -3;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  int bn = bn_hint;
+  if (bn == 0) {
+    const int m_tiles = (M + BM - 1) / BM;
+    bn = 256;
+    // Few M tiles (decode, small batches): shrink BN until the grid covers the SMs so the weight
+    // stream is pulled by every SM.
+    while (bn > 32 && m_tiles * ((N + bn - 1) / bn) < g_num_sms) bn >>= 1;
+    if (transB && bn < 64) bn = 64;
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  if (!transA) rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
+  else rc = make_tmap_bf16_2d(&ta, A, M, K, lda, 64, BK);
+  if (rc) return rc;
+  if (!transB) rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
+  else rc = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK);
+  if (rc) return rc - 100;
+#define RPEG_GEMM_CASE(BN_)                                                                                   \
+  case BN_:                                                                                                    \
+    return out_fp32 ? dispatch_major<BN_, EPI_F32>(transA, transB, ta, tb, C, M, N, K, ldc, accumulate, status, \
+                                                   g_num_sms, stream)                                          \
+                    : dispatch_major<BN_, EPI_BF16>(transA, transB, ta, tb, C, M, N, K, ldc, accumulate, status, \
+                                                    g_num_sms, stream);
+  switch (bn) {
+    RPEG_GEMM_CASE(256)
+    RPEG_GEMM_CASE(128)
+    RPEG_GEMM_CASE(64)
+    RPEG_GEMM_CASE(32)
+    default:
+      return -4;
+  }
+#undef RPEG_GEMM_CASE
+}

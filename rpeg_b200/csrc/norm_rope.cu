@@ -1,0 +1,348 @@
+// RMSNorm (+ fused residual add) forward/backward, RoPE (rotate-half, in place) and SwiGLU
+// forward/backward for sm_100a. All are HBM-bound row kernels: 16-byte vector accesses, one warp
+// per token row, fp32 math, bf16 storage.
+//
+// The reference gets these from TransformerEngine / apex / ATen through megatron-core
+// (RPEG/runtime/workers/megatron_worker.py:683 normalization, :686 activation; the rotary
+// embedding is Megatron's) and measures them in calibrate.py:744-895.
+#include "common.cuh"
+#include "rpeg_kernels.h"
+
+namespace rpeg {
+
+constexpr int ROW_WARPS = 4;
+
+// y = (x [+ res]) * rstd * w ; optionally writes h = x + res (the new residual stream).
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
+                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int T, int d, float eps) {
+  const int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const int lane = threadIdx.x & 31;
+  const int nvec = d >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * d);
+  const uint4* rr = res ? reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * d) : nullptr;
+  uint4* hr = h_out ? reinterpret_cast<uint4*>(h_out + static_cast<size_t>(row) * d) : nullptr;
+  float ss = 0.f;
+  for (int i = lane; i < nvec; i += 32) {
+    uint4 v = xr[i];
+    uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+    if (rr) {
+      uint4 r = rr[i];
+      const uint32_t* pr = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 a = unpack_bf16x2(pv[k]), b = unpack_bf16x2(pr[k]);
+        pv[k] = pack_bf16x2(a.x + b.x, a.y + b.y);
+      }
+      if (hr) hr[i] = v;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = unpack_bf16x2(pv[k]);
+      ss += a.x * a.x + a.y * a.y;
+    }
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / static_cast<float>(d) + eps);
+  if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * d);
+  // Second pass re-reads the row (L1/L2 resident) rather than holding d/32 values per lane.
+  const uint4* src = (rr && hr) ? reinterpret_cast<const uint4*>(hr) : xr;
+  for (int i = lane; i < nvec; i += 32) {
+    uint4 v = src[i];
+    uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+    if (rr && !hr) {
+      uint4 r = rr[i];
+      const uint32_t* pr = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 a = unpack_bf16x2(pv[k]), b = unpack_bf16x2(pr[k]);
+        pv[k] = pack_bf16x2(a.x + b.x, a.y + b.y);
+      }
+    }
+    uint4 wv = wr[i];
+    const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv);
+    uint4 o;
+    uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = unpack_bf16x2(pv[k]), b = unpack_bf16x2(pw[k]);
+      po[k] = pack_bf16x2(a.x * rstd * b.x, a.y * rstd * b.y);
+    }
+    yr[i] = o;
+  }
+}
+
+// dx = rstd * (dy*w) - x * rstd^3/d * sum(dy*w*x) [+ dres_in];  dw += sum_rows dy * x * rstd.
+// Each CTA walks `rows_per_cta` rows; lanes keep their dw columns in shared memory and flush with
+// one atomicAdd per column per CTA.
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw, int T, int d, int rows_per_cta) {
+  extern __shared__ float dw_sm[];  // [d]
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dw_sm[i] = 0.f;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = d >> 3;
+  const int row0 = blockIdx.x * rows_per_cta;
+  const int row1 = min(T, row0 + rows_per_cta);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  for (int row = row0 + warp; row < row1; row += ROW_WARPS) {
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * d);
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * d);
+    const float rs = rstd[row];
+    float dot = 0.f;
+    for (int i = lane; i < nvec; i += 32) {
+      uint4 a = dyr[i], b = xr[i], c = wr[i];
+      const uint32_t *pa = reinterpret_cast<const uint32_t*>(&a), *pb = reinterpret_cast<const uint32_t*>(&b),
+                     *pc = reinterpret_cast<const uint32_t*>(&c);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 g = unpack_bf16x2(pa[k]), xv = unpack_bf16x2(pb[k]), wv = unpack_bf16x2(pc[k]);
+        dot += g.x * wv.x * xv.x + g.y * wv.y * xv.y;
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = dot * rs * rs * rs / static_cast<float>(d);
+    const uint4* drr = dres_in ? reinterpret_cast<const uint4*>(dres_in + static_cast<size_t>(row) * d) : nullptr;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * d);
+    for (int i = lane; i < nvec; i += 32) {
+      uint4 a = dyr[i], b = xr[i], c = wr[i];
+      const uint32_t *pa = reinterpret_cast<const uint32_t*>(&a), *pb = reinterpret_cast<const uint32_t*>(&b),
+                     *pc = reinterpret_cast<const uint32_t*>(&c);
+      uint4 r = make_uint4(0, 0, 0, 0);
+      if (drr) r = drr[i];
+      const uint32_t* pr = reinterpret_cast<const uint32_t*>(&r);
+      uint4 o;
+      uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 g = unpack_bf16x2(pa[k]), xv = unpack_bf16x2(pb[k]), wv = unpack_bf16x2(pc[k]);
+        float2 rr = drr ? unpack_bf16x2(pr[k]) : make_float2(0.f, 0.f);
+        const float o0 = rs * g.x * wv.x - xv.x * coef + rr.x;
+        const float o1 = rs * g.y * wv.y - xv.y * coef + rr.y;
+        po[k] = pack_bf16x2(o0, o1);
+        atomicAdd(&dw_sm[i * 8 + 2 * k], g.x * xv.x * rs);
+        atomicAdd(&dw_sm[i * 8 + 2 * k + 1], g.y * xv.y * rs);
+      }
+      dxr[i] = o;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(&dw[i], dw_sm[i]);
+}
+
+// RoPE, rotate-half pairing (i, i + hd/2), applied in place to `nheads` heads of width hd that sit
+// at column offset `col0` of a [T, ld] bf16 buffer. cos/sin tables are fp32 [max_pos, hd/2].
+// sign = +1 forward, -1 backward (the transpose of a rotation is the rotation by -angle).
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ pos,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int T, int ld,
+                            int col0, int nheads, int hd, float sign) {
+  const int half = hd >> 1;
+  const int pairs_per_row = nheads * (half >> 1);  // each thread rotates 2 adjacent pairs
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(T) * pairs_per_row) return;
+  const int t = static_cast<int>(idx / pairs_per_row);
+  const int r = static_cast<int>(idx % pairs_per_row);
+  const int head = r / (half >> 1);
+  const int i = (r % (half >> 1)) * 2;
+  const int p = pos[t];
+  __nv_bfloat16* base = buf + static_cast<size_t>(t) * ld + col0 + head * hd;
+  const float2 c = *reinterpret_cast<const float2*>(cos_t + static_cast<size_t>(p) * half + i);
+  float2 s = *reinterpret_cast<const float2*>(sin_t + static_cast<size_t>(p) * half + i);
+  s.x *= sign;
+  s.y *= sign;
+  uint32_t lo = *reinterpret_cast<uint32_t*>(base + i);
+  uint32_t hi = *reinterpret_cast<uint32_t*>(base + i + half);
+  const float2 a = unpack_bf16x2(lo), b = unpack_bf16x2(hi);
+  lo = pack_bf16x2(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y);
+  hi = pack_bf16x2(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y);
+  *reinterpret_cast<uint32_t*>(base + i) = lo;
+  *reinterpret_cast<uint32_t*>(base + i + half) = hi;
+}
+
+// out[t, j] = silu(gu[t, j]) * gu[t, f + j]
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                  long long T, int f) {
+  const int fv = f >> 3;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * fv) return;
+  const long long t = idx / fv;
+  const int j = static_cast<int>(idx % fv);
+  const uint4 g = reinterpret_cast<const uint4*>(gu + t * 2 * f)[j];
+  const uint4 u = reinterpret_cast<const uint4*>(gu + t * 2 * f + f)[j];
+  const uint32_t *pg = reinterpret_cast<const uint32_t*>(&g), *pu = reinterpret_cast<const uint32_t*>(&u);
+  uint4 o;
+  uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float2 a = unpack_bf16x2(pg[k]), b = unpack_bf16x2(pu[k]);
+    const float s0 = a.x / (1.f + __expf(-a.x)), s1 = a.y / (1.f + __expf(-a.y));
+    po[k] = pack_bf16x2(s0 * b.x, s1 * b.y);
+  }
+  reinterpret_cast<uint4*>(out + t * f)[j] = o;
+}
+
+// dgu[t, j] = dout * u * d silu(g);  dgu[t, f + j] = dout * silu(g)
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dout,
+                                  __nv_bfloat16* __restrict__ dgu, long long T, int f) {
+  const int fv = f >> 3;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * fv) return;
+  const long long t = idx / fv;
+  const int j = static_cast<int>(idx % fv);
+  const uint4 g = reinterpret_cast<const uint4*>(gu + t * 2 * f)[j];
+  const uint4 u = reinterpret_cast<const uint4*>(gu + t * 2 * f + f)[j];
+  const uint4 d = reinterpret_cast<const uint4*>(dout + t * f)[j];
+  const uint32_t *pg = reinterpret_cast<const uint32_t*>(&g), *pu = reinterpret_cast<const uint32_t*>(&u),
+                 *pd = reinterpret_cast<const uint32_t*>(&d);
+  uint4 og, ou;
+  uint32_t *pog = reinterpret_cast<uint32_t*>(&og), *pou = reinterpret_cast<uint32_t*>(&ou);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float2 a = unpack_bf16x2(pg[k]), b = unpack_bf16x2(pu[k]), c = unpack_bf16x2(pd[k]);
+    const float sg0 = 1.f / (1.f + __expf(-a.x)), sg1 = 1.f / (1.f + __expf(-a.y));
+    const float si0 = a.x * sg0, si1 = a.y * sg1;
+    pog[k] = pack_bf16x2(c.x * b.x * (sg0 + si0 * (1.f - sg0)), c.y * b.y * (sg1 + si1 * (1.f - sg1)));
+    pou[k] = pack_bf16x2(c.x * si0, c.y * si1);
+  }
+  reinterpret_cast<uint4*>(dgu + t * 2 * f)[j] = og;
+  reinterpret_cast<uint4*>(dgu + t * 2 * f + f)[j] = ou;
+}
+
+// out[i] = a[i] + b[i] (bf16), 8 elements per thread.
+__global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                __nv_bfloat16* __restrict__ out, long long nvec) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const uint4 x = reinterpret_cast<const uint4*>(a)[i], y = reinterpret_cast<const uint4*>(b)[i];
+  const uint32_t *px = reinterpret_cast<const uint32_t*>(&x), *py = reinterpret_cast<const uint32_t*>(&y);
+  uint4 o;
+  uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float2 p = unpack_bf16x2(px[k]), q = unpack_bf16x2(py[k]);
+    po[k] = pack_bf16x2(p.x + q.x, p.y + q.y);
+  }
+  reinterpret_cast<uint4*>(out)[i] = o;
+}
+
+// Row gather of an embedding table and its backward scatter-add into an fp32 gradient.
+__global__ void embed_fwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, int T, int d) {
+  const int dv = d >> 3;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(T) * dv) return;
+  const int t = static_cast<int>(idx / dv), j = static_cast<int>(idx % dv);
+  reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * d)[j] =
+      reinterpret_cast<const uint4*>(table + static_cast<size_t>(ids[t]) * d)[j];
+}
+__global__ void embed_bwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+                                 float* __restrict__ dtable, int T, int d) {
+  const int dv = d >> 1;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(T) * dv) return;
+  const int t = static_cast<int>(idx / dv), j = static_cast<int>(idx % dv);
+  const float2 g = unpack_bf16x2(reinterpret_cast<const uint32_t*>(dout + static_cast<size_t>(t) * d)[j]);
+  float* dst = dtable + static_cast<size_t>(ids[t]) * d + 2 * j;
+  atomicAdd(dst, g.x);
+  atomicAdd(dst + 1, g.y);
+}
+
+}  // namespace rpeg
+
+using namespace rpeg;
+#define STREAM(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -21)
+
+extern "C" int rpeg_rmsnorm_fwd(const void* x, const void* res, const void* w, void* h_out, void* y,
+                                float* rstd, int T, int d, float eps, void* stream) {
+  if (d & 7) return -2;
+  if (T <= 0) return 0;
+  rmsnorm_fwd_kernel<<<(T + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, STREAM(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
+      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(h_out), static_cast<__nv_bfloat16*>(y),
+      rstd, T, d, eps);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                                const void* dres_in, void* dx, float* dw, int T, int d, void* stream) {
+  if (d & 7) return -2;
+  if (T <= 0) return 0;
+  if (d * 4 > 200 * 1024) return -3;
+  const int rows_per_cta = 32;
+  auto kern = rmsnorm_bwd_kernel;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    configured = true;
+  }
+  kern<<<(T + rows_per_cta - 1) / rows_per_cta, ROW_WARPS * 32, d * 4, STREAM(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres_in),
+      static_cast<__nv_bfloat16*>(dx), dw, T, d, rows_per_cta);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_rope(void* buf, const int* pos, const float* cos_t, const float* sin_t, int T, int ld,
+                         int col0, int nheads, int hd, int backward, void* stream) {
+  if ((hd & 3) || (ld & 1) || (col0 & 1)) return -2;
+  const long long n = static_cast<long long>(T) * nheads * (hd >> 2);
+  if (n <= 0) return 0;
+  rope_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
+      static_cast<__nv_bfloat16*>(buf), pos, cos_t, sin_t, T, ld, col0, nheads, hd, backward ? -1.f : 1.f);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_swiglu_fwd(const void* gu, void* out, long long T, int f, void* stream) {
+  if (f & 7) return -2;
+  const long long n = T * (f >> 3);
+  if (n <= 0) return 0;
+  swiglu_fwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), T, f);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_swiglu_bwd(const void* gu, const void* dout, void* dgu, long long T, int f, void* stream) {
+  if (f & 7) return -2;
+  const long long n = T * (f >> 3);
+  if (n <= 0) return 0;
+  swiglu_bwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dout),
+      static_cast<__nv_bfloat16*>(dgu), T, f);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_add_bf16(const void* a, const void* b, void* out, long long n, void* stream) {
+  if (n & 7) return -2;
+  const long long nvec = n >> 3;
+  if (nvec <= 0) return 0;
+  add_bf16_kernel<<<static_cast<unsigned>((nvec + 255) / 256), 256, 0, STREAM(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
+      static_cast<__nv_bfloat16*>(out), nvec);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_embed_fwd(const int* ids, const void* table, void* out, int T, int d, void* stream) {
+  if (d & 7) return -2;
+  const long long n = static_cast<long long>(T) * (d >> 3);
+  if (n <= 0) return 0;
+  embed_fwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), T, d);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_embed_bwd(const int* ids, const void* dout, float* dtable, int T, int d, void* stream) {
+  if (d & 1) return -2;
+  const long long n = static_cast<long long>(T) * (d >> 1);
+  if (n <= 0) return 0;
+  embed_bwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(dout), dtable, T, d);
+  return LAUNCH_OK();
+}

@@ -1,0 +1,277 @@
+// Optimizer-side kernels for sm_100a.
+//
+// Single GPU: fused AdamW on fp32 master weights that also emits the bf16 operational copy and
+// applies the gradient-clip coefficient read from device memory (no host round trip).
+//
+// Data parallel (one process per GPU, NVLink peer memory): gradient reduce-scatter, Adam and the
+// parameter all-gather are two kernels that talk to the peers directly:
+//   dp_reduce_norm : the owner of a shard pulls that shard of every peer's fp32 gradient over
+//                    NVLink, sums it, keeps the reduced shard locally and accumulates its squared
+//                    norm (the clip needs the global norm before any weight moves);
+//   dp_adam_push   : AdamW on the owner's fp32 master shard, then the new bf16 weights are stored
+//                    straight into every peer's parameter buffer (the all-gather is the epilogue).
+// Ordering across GPUs uses a flag barrier on a symmetric signal pad with a bounded spin that
+// reports a timeout in a status word instead of hanging.
+//
+// This is the B200 form of the reference's ZeRO path: async reduce_scatter_tensor buckets
+// (RPEG/runtime/workers/megatron_worker.py:1061-1067), FP32MasterAdamW.step
+// (RPEG/runtime/optimizer_sharding.py:270), all_gather_into_tensor of the bf16 shards
+// (megatron_worker.py:1262-1275) and the clip coefficient clamp(clip/(norm+1e-6), max=1)
+// (megatron_worker.py:3231-3338).
+#include "common.cuh"
+#include "rpeg_kernels.h"
+
+namespace rpeg {
+
+__device__ __forceinline__ float clip_coef_from(const float* sumsq, int n_partials, float max_norm) {
+  if (sumsq == nullptr || max_norm <= 0.f) return 1.f;
+  float s = 0.f;
+  for (int i = 0; i < n_partials; ++i) s += sumsq[i];
+  return fminf(max_norm / (sqrtf(s) + 1e-6f), 1.f);
+}
+
+// p32/m/v fp32, grad fp32. w16 receives bf16(p32). step is 1-based.
+__global__ void adamw_kernel(float* __restrict__ p32, float* __restrict__ m, float* __restrict__ v,
+                             const float* __restrict__ grad, __nv_bfloat16* __restrict__ w16, long long n,
+                             float lr, float beta1, float beta2, float eps, float wd, float bc1, float bc2,
+                             float grad_scale, const float* __restrict__ sumsq, int n_partials,
+                             float max_norm) {
+  const float gs = grad_scale * clip_coef_from(sumsq, n_partials, max_norm);
+  const long long nv = n >> 2;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 p = reinterpret_cast<float4*>(p32)[i];
+    float4 mm = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    const float4 g = reinterpret_cast<const float4*>(grad)[i];
+    float* pp = reinterpret_cast<float*>(&p);
+    float* pm = reinterpret_cast<float*>(&mm);
+    float* pv = reinterpret_cast<float*>(&vv);
+    const float* pg = reinterpret_cast<const float*>(&g);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = pg[k] * gs;
+      pm[k] = beta1 * pm[k] + (1.f - beta1) * gk;
+      pv[k] = beta2 * pv[k] + (1.f - beta2) * gk * gk;
+      const float upd = (pm[k] / bc1) / (sqrtf(pv[k] / bc2) + eps);
+      pp[k] = pp[k] * (1.f - lr * wd) - lr * upd;
+    }
+    reinterpret_cast<float4*>(p32)[i] = p;
+    reinterpret_cast<float4*>(m)[i] = mm;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    uint2 o;
+    o.x = pack_bf16x2(pp[0], pp[1]);
+    o.y = pack_bf16x2(pp[2], pp[3]);
+    reinterpret_cast<uint2*>(w16)[i] = o;
+  }
+}
+
+// out[0] += sum x^2 (fp32 input)
+__global__ void sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  const long long nv = n >> 2;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(x)[i];
+    s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) atomicAdd(out, s);
+  }
+}
+
+struct PeerPtrs {
+  void* p[RPEG_MAX_PEERS];
+};
+
+// Flag barrier over a symmetric signal pad. pad layout per rank: uint32 flag[RPEG_MAX_PEERS] at
+// word offset `slot*RPEG_MAX_PEERS`. Rank r stores `epoch` into flag[r] of every peer, then waits
+// until every flag in its own pad reached `epoch`. Optionally publishes one float per rank
+// (payload area, word offset 1024 + slot*RPEG_MAX_PEERS) before the flag, e.g. a partial norm.
+__global__ void flag_barrier_kernel(PeerPtrs pads, int rank, int world, int slot, unsigned epoch,
+                                    const float* __restrict__ payload_in, float* __restrict__ payload_out,
+                                    unsigned long long spin_limit, int* status) {
+  const int t = threadIdx.x;
+  if (t < world) {
+    unsigned* peer = static_cast<unsigned*>(pads.p[t]);
+    if (payload_in != nullptr) {
+      reinterpret_cast<float*>(peer)[1024 + slot * RPEG_MAX_PEERS + rank] = payload_in[0];
+    }
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer + slot * RPEG_MAX_PEERS + rank), "r"(epoch)
+                 : "memory");
+    const unsigned* mine = static_cast<const unsigned*>(pads.p[rank]) + slot * RPEG_MAX_PEERS + t;
+    unsigned seen = 0;
+    unsigned long long spins = 0;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      if (static_cast<int>(seen - epoch) >= 0) break;
+      if (++spins > spin_limit) {
+        record_error(status, RPEG_ERR_FLAG_TIMEOUT, 400 + slot, t);
+        break;
+      }
+      __nanosleep(64);
+    }
+    if (payload_out != nullptr)
+      payload_out[t] = reinterpret_cast<const volatile float*>(pads.p[rank])[1024 + slot * RPEG_MAX_PEERS + t];
+  }
+}
+
+// reduced[i] = scale * sum_p grads[p][shard_off + i], i in [0, shard_n); sumsq[0] += sum reduced^2.
+__global__ void dp_reduce_norm_kernel(PeerPtrs grads, int world, long long shard_off, long long shard_n,
+                                      float scale, float* __restrict__ reduced, float* __restrict__ sumsq) {
+  __shared__ float red[32];
+  float s = 0.f;
+  const long long nv = shard_n >> 2;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < world; ++p) {
+      const float4 g = reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + shard_off)[i];
+      a.x += g.x; a.y += g.y; a.z += g.z; a.w += g.w;
+    }
+    a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+    reinterpret_cast<float4*>(reduced)[i] = a;
+    s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) atomicAdd(sumsq, s);
+  }
+}
+
+// AdamW on the local shard, then the bf16 result goes to every peer's parameter buffer.
+__global__ void dp_adam_push_kernel(float* __restrict__ p32, float* __restrict__ m, float* __restrict__ v,
+                                    const float* __restrict__ reduced, PeerPtrs params, int world,
+                                    long long shard_off, long long shard_n, float lr, float beta1, float beta2,
+                                    float eps, float wd, float bc1, float bc2, const float* __restrict__ sumsq,
+                                    int n_partials, float max_norm) {
+  const float gs = clip_coef_from(sumsq, n_partials, max_norm);
+  const long long nv = shard_n >> 2;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 p = reinterpret_cast<float4*>(p32)[i];
+    float4 mm = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    const float4 g = reinterpret_cast<const float4*>(reduced)[i];
+    float* pp = reinterpret_cast<float*>(&p);
+    float* pm = reinterpret_cast<float*>(&mm);
+    float* pv = reinterpret_cast<float*>(&vv);
+    const float* pg = reinterpret_cast<const float*>(&g);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = pg[k] * gs;
+      pm[k] = beta1 * pm[k] + (1.f - beta1) * gk;
+      pv[k] = beta2 * pv[k] + (1.f - beta2) * gk * gk;
+      const float upd = (pm[k] / bc1) / (sqrtf(pv[k] / bc2) + eps);
+      pp[k] = pp[k] * (1.f - lr * wd) - lr * upd;
+    }
+    reinterpret_cast<float4*>(p32)[i] = p;
+    reinterpret_cast<float4*>(m)[i] = mm;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    uint2 o;
+    o.x = pack_bf16x2(pp[0], pp[1]);
+    o.y = pack_bf16x2(pp[2], pp[3]);
+    for (int q = 0; q < world; ++q)
+      reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(params.p[q]) + shard_off)[i] = o;
+  }
+}
+
+// dst[i] = src[i] for 16-byte vectors; used for peer-memory pulls/pushes of weight shards.
+__global__ void copy16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long nvec) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
+
+}  // namespace rpeg
+
+using namespace rpeg;
+#define STREAM(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -21)
+static inline unsigned sat_grid(long long work_items, int block) {
+  long long g = (work_items + block - 1) / block;
+  const long long cap = 148 * 8;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<unsigned>(g);
+}
+static PeerPtrs make_peers(void* const* ptrs, int world) {
+  PeerPtrs pp;
+  for (int i = 0; i < RPEG_MAX_PEERS; ++i) pp.p[i] = i < world ? ptrs[i] : nullptr;
+  return pp;
+}
+
+extern "C" int rpeg_adamw(float* p32, float* m, float* v, const float* grad, void* w16, long long n, float lr,
+                          float beta1, float beta2, float eps, float wd, int step, float grad_scale,
+                          const float* sumsq, int n_partials, float max_norm, void* stream) {
+  if (n <= 0) return 0;
+  if (n & 3) return -2;
+  const float bc1 = 1.f - powf(beta1, static_cast<float>(step));
+  const float bc2 = 1.f - powf(beta2, static_cast<float>(step));
+  adamw_kernel<<<sat_grid(n >> 2, 256), 256, 0, STREAM(stream)>>>(p32, m, v, grad,
+                                                                static_cast<__nv_bfloat16*>(w16), n, lr, beta1,
+                                                                beta2, eps, wd, bc1, bc2, grad_scale, sumsq,
+                                                                n_partials, max_norm);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_sumsq(const float* x, long long n, float* out, void* stream) {
+  if (n <= 0) return 0;
+  if (n & 3) return -2;
+  sumsq_kernel<<<sat_grid(n >> 2, 256), 256, 0, STREAM(stream)>>>(x, n, out);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_flag_barrier(void* const* pads, int rank, int world, int slot, unsigned epoch,
+                                 const float* payload_in, float* payload_out, unsigned long long spin_limit,
+                                 int* status, void* stream) {
+  if (world < 1 || world > RPEG_MAX_PEERS || slot < 0 || slot >= 64) return -2;
+  flag_barrier_kernel<<<1, 32, 0, STREAM(stream)>>>(make_peers(pads, world), rank, world, slot, epoch,
+                                                   payload_in, payload_out, spin_limit, status);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_dp_reduce_norm(void* const* grads, int world, long long shard_off, long long shard_n,
+                                   float scale, float* reduced, float* sumsq, void* stream) {
+  if (world < 1 || world > RPEG_MAX_PEERS) return -2;
+  if ((shard_off | shard_n) & 3) return -3;
+  if (shard_n <= 0) return 0;
+  dp_reduce_norm_kernel<<<sat_grid(shard_n >> 2, 256), 256, 0, STREAM(stream)>>>(make_peers(grads, world), world,
+                                                                               shard_off, shard_n, scale,
+                                                                               reduced, sumsq);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_dp_adam_push(float* p32, float* m, float* v, const float* reduced, void* const* params,
+                                 int world, long long shard_off, long long shard_n, float lr, float beta1,
+                                 float beta2, float eps, float wd, int step, const float* sumsq, int n_partials,
+                                 float max_norm, void* stream) {
+  if (world < 1 || world > RPEG_MAX_PEERS) return -2;
+  if ((shard_off | shard_n) & 3) return -3;
+  if (shard_n <= 0) return 0;
+  const float bc1 = 1.f - powf(beta1, static_cast<float>(step));
+  const float bc2 = 1.f - powf(beta2, static_cast<float>(step));
+  dp_adam_push_kernel<<<sat_grid(shard_n >> 2, 256), 256, 0, STREAM(stream)>>>(
+      p32, m, v, reduced, make_peers(params, world), world, shard_off, shard_n, lr, beta1, beta2, eps, wd, bc1,
+      bc2, sumsq, n_partials, max_norm);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_copy16(const void* src, void* dst, long long nbytes, void* stream) {
+  if (nbytes <= 0) return 0;
+  if ((nbytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -2;
+  copy16_kernel<<<sat_grid(nbytes >> 4, 256), 256, 0, STREAM(stream)>>>(static_cast<const uint4*>(src),
+                                                                       static_cast<uint4*>(dst), nbytes >> 4);
+  return LAUNCH_OK();
+}

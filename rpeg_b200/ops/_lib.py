@@ -1,0 +1,83 @@
+"""ctypes loader for the in-tree native library ``rpeg_b200/librpeg_kernels.so``.
+
+The library is never optional on a GPU machine: ``lib()`` raises if it is missing or fails to
+load, so no op can silently fall back to eager PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "librpeg_kernels.so"
+_lib = None
+
+P = c_void_p
+I = c_int
+F = c_float
+LL = c_longlong
+
+_SIGNATURES = {
+    "rpeg_gemm_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
+    "rpeg_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "rpeg_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, P],
+    "rpeg_rope": [P, P, P, P, I, I, I, I, I, I, P],
+    "rpeg_swiglu_fwd": [P, P, LL, I, P],
+    "rpeg_swiglu_bwd": [P, P, P, LL, I, P],
+    "rpeg_add_bf16": [P, P, P, LL, P],
+    "rpeg_embed_fwd": [P, P, P, I, I, P],
+    "rpeg_embed_bwd": [P, P, P, I, I, P],
+    "rpeg_token_logprob_fwd": [P, P, P, P, I, I, I, F, P],
+    "rpeg_token_logprob_bwd": [P, P, P, P, I, I, I, F, P],
+    "rpeg_policy_loss": [P, P, P, P, P, P, P, LL, F, F, F, P],
+    "rpeg_masked_rowsum": [P, P, P, I, I, P],
+    "rpeg_dpo_loss": [P, P, P, P, I, F, P],
+    "rpeg_expand_seq_coef": [P, P, P, I, I, P],
+    "rpeg_value_loss": [P, P, P, P, P, LL, F, P],
+    "rpeg_gae": [P, P, P, P, P, P, P, I, I, F, F, F, I, P],
+    "rpeg_group_advantage": [P, P, I, I, P],
+    "rpeg_sample": [P, I, I, I, F, I, c_ulonglong, P, P, P, P],
+    "rpeg_head_gemv": [P, P, P, P, I, I, P],
+    "rpeg_head_gemv_bwd": [P, P, P, P, P, P, I, I, P],
+    "rpeg_adamw": [P, P, P, P, P, LL, F, F, F, F, F, I, F, P, I, F, P],
+    "rpeg_sumsq": [P, LL, P, P],
+    "rpeg_flag_barrier": [P, I, I, I, c_uint, P, P, c_ulonglong, P, P],
+    "rpeg_dp_reduce_norm": [P, I, LL, LL, F, P, P, P],
+    "rpeg_dp_adam_push": [P, P, P, P, P, I, LL, LL, F, F, F, F, F, I, P, I, F, P],
+    "rpeg_copy16": [P, P, LL, P],
+    "rpeg_kv_append": [P, I, I, I, P, P, P, I, P, P, I, I, I, P],
+    "rpeg_paged_decode_attn": [P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, F, P],
+    "rpeg_flash_attn_fwd": [P, I, I, I, I, P, I, I, I, I, I, I, F, P, P, P, P],
+}
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the native library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(
+                f"{_LIB_PATH} is missing: build it with `python -m rpeg_b200.build_ext` "
+                "(the CUDA kernels are mandatory; there is no eager fallback)"
+            )
+        handle = ctypes.CDLL(str(_LIB_PATH))
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(handle, name, None)
+            if fn is None:
+                continue  # symbol added by a newer source than the built library
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        if hasattr(handle, "rpeg_decode_attn_scratch_bytes"):
+            handle.rpeg_decode_attn_scratch_bytes.argtypes = [I, I, I]
+            handle.rpeg_decode_attn_scratch_bytes.restype = c_longlong
+        _lib = handle
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with native error code {rc}")

@@ -1,0 +1,319 @@
+"""Thin tensor-level wrappers over the native sm_100a kernels (no autograd here).
+
+Every wrapper validates shapes/dtypes/contiguity on the host, passes raw device pointers plus the
+current CUDA stream to the C ABI in ``csrc/rpeg_kernels.h`` and raises on a non-zero return code.
+Kernels with bounded waits share one per-device status word; ``check_status()`` reads it (this
+synchronises) and raises ``KernelWaitTimeout`` if any wait ran out.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ._lib import check, lib
+
+KV_PAGE = 64
+MAX_PEERS = 8
+_status: dict[int, torch.Tensor] = {}
+
+
+class KernelWaitTimeout(RuntimeError):
+    """A bounded device-side wait (mbarrier or peer flag) ran out; the kernel returned early."""
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def status_word(device: torch.device | None = None) -> torch.Tensor:
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    if dev not in _status:
+        _status[dev] = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+    return _status[dev]
+
+
+def check_status() -> None:
+    """Read the status word of the current device (synchronises) and raise if a wait timed out."""
+    st = status_word()
+    vals = st.tolist()
+    if vals[0] != 0:
+        st.zero_()
+        raise KernelWaitTimeout(f"device wait timed out: code={vals[0]} where={vals[1]} block={vals[2]} extra={vals[3]}")
+
+
+def _req(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
+    if not t.is_cuda or t.dtype != dtype:
+        raise TypeError(f"{name}: expected a CUDA {dtype} tensor, got {t.dtype} on {t.device}")
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
+         bn: int = 0) -> torch.Tensor:
+    """``C[M,N] = op(a) @ op(b).T`` on tcgen05 tensor cores with fp32 accumulation.
+
+    ``a`` is ``[M,K]`` (or ``[K,M]`` with ``trans_a``); ``b`` is ``[N,K]`` — the ``[out,in]`` layout
+    of a linear weight — or ``[K,N]`` with ``trans_b``. Rows may be strided (last dim contiguous).
+    ``out_dtype=float32, accumulate=True`` adds into ``out`` (used for weight-gradient accumulation).
+    """
+    _req(a, torch.bfloat16, "a")
+    _req(b, torch.bfloat16, "b")
+    if a.dim() != 2 or b.dim() != 2 or a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("gemm operands must be 2-D with a contiguous last dimension")
+    M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if trans_b else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"gemm inner dimensions differ: {K} vs {Kb}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs an `out` tensor")
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    else:
+        out_dtype = out.dtype
+        if out.shape != (M, N) or out.stride(1) != 1:
+            raise ValueError("gemm out has the wrong shape or a strided last dimension")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("gemm output must be bf16 or fp32")
+    if M == 0 or N == 0:
+        return out
+    rc = lib().rpeg_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                              out.stride(0), int(trans_a), int(trans_b), int(out_dtype == torch.float32),
+                              int(accumulate), bn, status_word(a.device).data_ptr(), _stream())
+    check(rc, "rpeg_gemm_bf16")
+    return out
+
+
+# --------------------------------------------------------------------------- norm / rope / swiglu
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
+                want_sum: bool = False):
+    """Returns ``(y, rstd, h)``: ``h = x + residual`` (only when asked for), ``y = rmsnorm(h) * w``."""
+    _req(x, torch.bfloat16, "x")
+    T, d = x.shape
+    y = torch.empty_like(x)
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    h = torch.empty_like(x) if (residual is not None and want_sum) else None
+    check(lib().rpeg_rmsnorm_fwd(x.data_ptr(), _ptr(residual), w.data_ptr(), _ptr(h), y.data_ptr(),
+                                 rstd.data_ptr(), T, d, eps, _stream()), "rpeg_rmsnorm_fwd")
+    return y, rstd, h
+
+
+def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor, dw: torch.Tensor,
+                dres_in: torch.Tensor | None = None) -> torch.Tensor:
+    """``dx`` of ``y = rmsnorm(x) * w`` (+ ``dres_in`` added in); accumulates ``dw`` (fp32) in place."""
+    T, d = x.shape
+    dx = torch.empty_like(x)
+    check(lib().rpeg_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), _ptr(dres_in),
+                                 dx.data_ptr(), dw.data_ptr(), T, d, _stream()), "rpeg_rmsnorm_bwd")
+    return dx
+
+
+def rope_tables(max_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+def rope_(buf: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torch.Tensor, col0: int, nheads: int,
+          head_dim: int, backward: bool = False) -> None:
+    """Rotate ``nheads`` heads starting at column ``col0`` of the 2-D ``buf`` in place."""
+    _req(buf, torch.bfloat16, "buf")
+    check(lib().rpeg_rope(buf.data_ptr(), pos.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), buf.shape[0],
+                          buf.stride(0), col0, nheads, head_dim, int(backward), _stream()), "rpeg_rope")
+
+
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    T, f2 = gu.shape
+    out = torch.empty((T, f2 // 2), dtype=gu.dtype, device=gu.device)
+    check(lib().rpeg_swiglu_fwd(gu.data_ptr(), out.data_ptr(), T, f2 // 2, _stream()), "rpeg_swiglu_fwd")
+    return out
+
+
+def swiglu_bwd(gu: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
+    T, f2 = gu.shape
+    dgu = torch.empty_like(gu)
+    check(lib().rpeg_swiglu_bwd(gu.data_ptr(), dout.data_ptr(), dgu.data_ptr(), T, f2 // 2, _stream()),
+          "rpeg_swiglu_bwd")
+    return dgu
+
+
+def add_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    out = torch.empty_like(a) if out is None else out
+    check(lib().rpeg_add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _stream()), "rpeg_add_bf16")
+    return out
+
+
+def embed_fwd(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    _req(ids, torch.int32, "ids")
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    check(lib().rpeg_embed_fwd(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(), table.shape[1],
+                               _stream()), "rpeg_embed_fwd")
+    return out
+
+
+def embed_bwd(ids: torch.Tensor, dout: torch.Tensor, dtable: torch.Tensor) -> None:
+    check(lib().rpeg_embed_bwd(ids.data_ptr(), dout.data_ptr(), dtable.data_ptr(), ids.numel(), dout.shape[1],
+                               _stream()), "rpeg_embed_bwd")
+
+
+# --------------------------------------------------------------------------- losses
+def token_logprob_fwd(logits: torch.Tensor, targets: torch.Tensor, temperature: float = 1.0):
+    _req(logits, torch.bfloat16, "logits")
+    _req(targets, torch.int32, "targets")
+    T, V = logits.shape
+    logp = torch.empty(T, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(T, dtype=torch.float32, device=logits.device)
+    check(lib().rpeg_token_logprob_fwd(logits.data_ptr(), targets.data_ptr(), logp.data_ptr(), lse.data_ptr(), T, V,
+                                       logits.stride(0), temperature, _stream()), "rpeg_token_logprob_fwd")
+    return logp, lse
+
+
+def token_logprob_bwd_(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, coef: torch.Tensor,
+                       temperature: float = 1.0) -> torch.Tensor:
+    """Overwrite ``logits`` with ``d loss / d logits`` given ``coef = d loss / d logp`` per row."""
+    T, V = logits.shape
+    check(lib().rpeg_token_logprob_bwd(logits.data_ptr(), targets.data_ptr(), lse.data_ptr(), coef.data_ptr(), T, V,
+                                       logits.stride(0), temperature, _stream()), "rpeg_token_logprob_bwd")
+    return logits
+
+
+def policy_loss(lp, old_lp, ref_lp, adv, mask, clip_eps: float, kl_coef: float, inv_denom: float):
+    """Clipped PPO/GRPO loss. Returns ``(coef, acc)``; ``acc = [loss, sum(lp-ref), n_clipped, sum(old-lp)]``."""
+    coef = torch.empty_like(lp)
+    acc = torch.zeros(4, dtype=torch.float32, device=lp.device)
+    check(lib().rpeg_policy_loss(lp.data_ptr(), old_lp.data_ptr(), _ptr(ref_lp), adv.data_ptr(), mask.data_ptr(),
+                                 coef.data_ptr(), acc.data_ptr(), lp.numel(), clip_eps, kl_coef, inv_denom,
+                                 _stream()), "rpeg_policy_loss")
+    return coef, acc
+
+
+def masked_rowsum(x: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    B, T = x.shape
+    out = torch.empty(B, dtype=torch.float32, device=x.device)
+    check(lib().rpeg_masked_rowsum(x.data_ptr(), mask.data_ptr(), out.data_ptr(), B, T, _stream()),
+          "rpeg_masked_rowsum")
+    return out
+
+
+def dpo_loss(pi_seq: torch.Tensor, ref_seq: torch.Tensor, beta: float):
+    """Rows interleaved (chosen, rejected). Returns ``(seq_coef, acc)``; ``acc = [loss, n_correct, margin]``."""
+    P = pi_seq.numel() // 2
+    seq_coef = torch.empty_like(pi_seq)
+    acc = torch.zeros(4, dtype=torch.float32, device=pi_seq.device)
+    check(lib().rpeg_dpo_loss(pi_seq.data_ptr(), ref_seq.data_ptr(), seq_coef.data_ptr(), acc.data_ptr(), P, beta,
+                              _stream()), "rpeg_dpo_loss")
+    return seq_coef, acc
+
+
+def expand_seq_coef(seq_coef: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    B, T = mask.shape
+    coef = torch.empty_like(mask)
+    check(lib().rpeg_expand_seq_coef(seq_coef.data_ptr(), mask.data_ptr(), coef.data_ptr(), B, T, _stream()),
+          "rpeg_expand_seq_coef")
+    return coef
+
+
+def value_loss(v, ret, mask, inv_denom: float):
+    dv = torch.empty_like(v)
+    acc = torch.zeros(4, dtype=torch.float32, device=v.device)
+    check(lib().rpeg_value_loss(v.data_ptr(), ret.data_ptr(), mask.data_ptr(), dv.data_ptr(), acc.data_ptr(),
+                                v.numel(), inv_denom, _stream()), "rpeg_value_loss")
+    return dv, acc
+
+
+def gae(old_lp, ref_lp, values, mask, scores, beta: float, gamma: float, lam: float, whiten: bool):
+    B, T = values.shape
+    adv = torch.empty_like(values)
+    ret = torch.empty_like(values)
+    check(lib().rpeg_gae(old_lp.data_ptr(), _ptr(ref_lp), values.data_ptr(), mask.data_ptr(), scores.data_ptr(),
+                         adv.data_ptr(), ret.data_ptr(), B, T, beta, gamma, lam, int(whiten), _stream()), "rpeg_gae")
+    return adv, ret
+
+
+def group_advantage(rewards: torch.Tensor, group: int) -> torch.Tensor:
+    out = torch.empty_like(rewards)
+    check(lib().rpeg_group_advantage(rewards.data_ptr(), out.data_ptr(), rewards.numel() // group, group, _stream()),
+          "rpeg_group_advantage")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, greedy: bool, seed: int, forced: torch.Tensor | None = None,
+           token_out: torch.Tensor | None = None, logp_out: torch.Tensor | None = None):
+    B, V = logits.shape
+    tok = torch.empty(B, dtype=torch.int32, device=logits.device) if token_out is None else token_out
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device) if logp_out is None else logp_out
+    check(lib().rpeg_sample(logits.data_ptr(), B, V, logits.stride(0), temperature, int(greedy),
+                            seed & 0xFFFFFFFFFFFFFFFF, _ptr(forced), tok.data_ptr(), lp.data_ptr(), _stream()),
+          "rpeg_sample")
+    return tok, lp
+
+
+def head_gemv(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    T, d = h.shape
+    out = torch.empty(T, dtype=torch.float32, device=h.device)
+    check(lib().rpeg_head_gemv(h.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), T, d, _stream()),
+          "rpeg_head_gemv")
+    return out
+
+
+def head_gemv_bwd(h, w, dout, dw: torch.Tensor, db: torch.Tensor | None) -> torch.Tensor:
+    T, d = h.shape
+    dh = torch.empty_like(h)
+    check(lib().rpeg_head_gemv_bwd(h.data_ptr(), w.data_ptr(), dout.data_ptr(), dh.data_ptr(), dw.data_ptr(),
+                                   _ptr(db), T, d, _stream()), "rpeg_head_gemv_bwd")
+    return dh
+
+
+# --------------------------------------------------------------------------- optimizer
+def adamw_(p32, m, v, grad, w16, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, step=1, grad_scale=1.0,
+           sumsq: torch.Tensor | None = None, max_norm: float = 0.0) -> None:
+    n = p32.numel()
+    check(lib().rpeg_adamw(p32.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(), w16.data_ptr(), n, lr,
+                           beta1, beta2, eps, wd, step, grad_scale, _ptr(sumsq),
+                           0 if sumsq is None else sumsq.numel(), max_norm, _stream()), "rpeg_adamw")
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor) -> None:
+    check(lib().rpeg_sumsq(x.data_ptr(), x.numel(), out.data_ptr(), _stream()), "rpeg_sumsq")
+
+
+# --------------------------------------------------------------------------- attention
+def kv_append(qkv, k_col0, v_col0, seq_id, pos, page_table, kcache, vcache, n_kv_heads, head_dim) -> None:
+    check(lib().rpeg_kv_append(qkv.data_ptr(), qkv.stride(0), k_col0, v_col0, seq_id.data_ptr(), pos.data_ptr(),
+                               page_table.data_ptr(), page_table.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+                               qkv.shape[0], n_kv_heads, head_dim, _stream()), "rpeg_kv_append")
+
+
+def decode_scratch_numel(B: int, H: int, nsplit: int) -> int:
+    return int(lib().rpeg_decode_attn_scratch_bytes(B, H, nsplit)) // 4
+
+
+def paged_decode_attn(q, q_col0, kcache, vcache, page_table, seq_lens, n_heads, n_kv_heads, head_dim, scale,
+                      nsplit: int = 1, scratch: torch.Tensor | None = None, out: torch.Tensor | None = None):
+    B = q.shape[0]
+    out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device) if out is None else out
+    if nsplit > 1 and scratch is None:
+        scratch = torch.empty(decode_scratch_numel(B, n_heads, nsplit), dtype=torch.float32, device=q.device)
+    check(lib().rpeg_paged_decode_attn(q.data_ptr(), q.stride(0), q_col0, kcache.data_ptr(), vcache.data_ptr(),
+                                       page_table.data_ptr(), page_table.stride(0), seq_lens.data_ptr(),
+                                       out.data_ptr(), _ptr(scratch), B, n_heads, n_kv_heads, head_dim, nsplit,
+                                       scale, _stream()), "rpeg_paged_decode_attn")
+    return out
+
+
+def flash_attn_fwd(qkv, q_col0, k_col0, v_col0, cu_seqlens, max_seqlen, n_heads, n_kv_heads, head_dim, scale=None):
+    """Causal attention over packed sequences. Returns ``(out [T, H*hd] bf16, lse [H, T] fp32)``."""
+    _req(qkv, torch.bfloat16, "qkv")
+    T = qkv.shape[0]
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    lse = torch.empty((n_heads, T), dtype=torch.float32, device=qkv.device)
+    check(lib().rpeg_flash_attn_fwd(qkv.data_ptr(), qkv.stride(0), q_col0, k_col0, v_col0, cu_seqlens.data_ptr(),
+                                    cu_seqlens.numel() - 1, max_seqlen, T, n_heads, n_kv_heads, head_dim, scale,
+                                    out.data_ptr(), lse.data_ptr(), status_word(qkv.device).data_ptr(), _stream()),
+          "rpeg_flash_attn_fwd")
+    return out, lse

@@ -1,0 +1,346 @@
+"""Numerics of every single-GPU sm_100a kernel against a plain PyTorch fp32 reference."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from rpeg_b200.ops import kernels as K  # noqa: E402
+
+
+def _rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(cuda_device):
+    torch.manual_seed(0)
+    yield
+    K.check_status()
+
+
+GEMM_SHAPES = [
+    (128, 256, 64), (256, 512, 256), (300, 264, 200), (1024, 4096, 4096), (4096, 11008, 4096),
+    (32, 4096, 4096), (8, 32000, 4096), (64, 12288, 4096), (5, 40, 72),
+]
+
+
+@pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_layouts(cuda_device, M, N, K_, trans_a, trans_b):
+    if trans_a and M % 8:
+        pytest.skip("MN-major A needs M % 8 == 0")
+    a = torch.randn((K_, M) if trans_a else (M, K_), device=cuda_device).bfloat16()
+    b = torch.randn((K_, N) if trans_b else (N, K_), device=cuda_device).bfloat16()
+    ref = (a.float().t() if trans_a else a.float()) @ (b.float() if trans_b else b.float().t())
+    out = K.gemm(a, b, trans_a=trans_a, trans_b=trans_b)
+    assert _rel_err(out, ref) < 1e-2
+    out32 = K.gemm(a, b, trans_a=trans_a, trans_b=trans_b, out_dtype=torch.float32)
+    assert _rel_err(out32, ref) < 2e-3
+
+
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+def test_gemm_tile_widths_and_accumulate(cuda_device, bn):
+    M, N, K_ = 384, 768, 520
+    a = torch.randn(M, K_, device=cuda_device).bfloat16()
+    b = torch.randn(N, K_, device=cuda_device).bfloat16()
+    ref = a.float() @ b.float().t()
+    assert _rel_err(K.gemm(a, b, bn=bn), ref) < 1e-2
+    acc = torch.ones(M, N, device=cuda_device)
+    K.gemm(a, b, out=acc, accumulate=True, bn=bn)
+    assert _rel_err(acc, ref + 1.0) < 2e-3
+
+
+def test_gemm_strided_rows(cuda_device):
+    big = torch.randn(256, 3 * 512, device=cuda_device).bfloat16()
+    a = big[:, 512:1024]
+    w = torch.randn(384, 512, device=cuda_device).bfloat16()
+    assert _rel_err(K.gemm(a, w), a.float() @ w.float().t()) < 1e-2
+
+
+@pytest.mark.parametrize("T,d", [(7, 256), (1000, 4096), (33, 5120)])
+def test_rmsnorm_fwd_bwd(cuda_device, T, d):
+    x = torch.randn(T, d, device=cuda_device).bfloat16()
+    res = torch.randn(T, d, device=cuda_device).bfloat16()
+    w = (1 + 0.1 * torch.randn(d, device=cuda_device)).bfloat16()
+    eps = 1e-5
+    y, rstd, h = K.rmsnorm_fwd(x, w, eps, residual=res, want_sum=True)
+    h_ref = (x.float() + res.float()).bfloat16()
+    assert torch.equal(h, h_ref)
+    hf = h_ref.float()
+    rs_ref = torch.rsqrt(hf.pow(2).mean(-1) + eps)
+    assert _rel_err(rstd, rs_ref) < 1e-4
+    assert _rel_err(y, hf * rs_ref[:, None] * w.float()) < 5e-3
+    # backward against autograd on fp32
+    dy = torch.randn(T, d, device=cuda_device).bfloat16()
+    dres = torch.randn(T, d, device=cuda_device).bfloat16()
+    hx = hf.clone().requires_grad_(True)
+    wf = w.float().clone().requires_grad_(True)
+    yy = hx * torch.rsqrt(hx.pow(2).mean(-1, keepdim=True) + eps) * wf
+    yy.backward(dy.float())
+    dw = torch.zeros(d, device=cuda_device)
+    dx = K.rmsnorm_bwd(dy, h_ref, w, rstd, dw, dres_in=dres)
+    assert _rel_err(dx, hx.grad + dres.float()) < 1e-2
+    assert _rel_err(dw, wf.grad) < 1e-2
+
+
+def test_rope_roundtrip_and_reference(cuda_device):
+    T, H, hd = 300, 4, 128
+    buf = torch.randn(T, 3 * H * hd, device=cuda_device).bfloat16()
+    orig = buf.clone()
+    pos = torch.randint(0, 2048, (T,), device=cuda_device, dtype=torch.int32)
+    cos_t, sin_t = K.rope_tables(2048, hd, 10000.0, cuda_device)
+    K.rope_(buf, pos, cos_t, sin_t, H * hd, H, hd)  # rotate the K block only
+    k = orig[:, H * hd:2 * H * hd].float().view(T, H, hd)
+    c = cos_t[pos.long()][:, None, :]
+    s = sin_t[pos.long()][:, None, :]
+    k1, k2 = k[..., :hd // 2], k[..., hd // 2:]
+    ref = torch.cat([k1 * c - k2 * s, k2 * c + k1 * s], -1).view(T, H * hd)
+    assert _rel_err(buf[:, H * hd:2 * H * hd], ref) < 5e-3
+    assert torch.equal(buf[:, :H * hd], orig[:, :H * hd]) and torch.equal(buf[:, 2 * H * hd:], orig[:, 2 * H * hd:])
+    K.rope_(buf, pos, cos_t, sin_t, H * hd, H, hd, backward=True)
+    assert _rel_err(buf, orig) < 1e-2
+
+
+def test_swiglu(cuda_device):
+    T, f = 257, 1408
+    gu = torch.randn(T, 2 * f, device=cuda_device).bfloat16()
+    dout = torch.randn(T, f, device=cuda_device).bfloat16()
+    g = gu[:, :f].float().clone().requires_grad_(True)
+    u = gu[:, f:].float().clone().requires_grad_(True)
+    ref = torch.nn.functional.silu(g) * u
+    ref.backward(dout.float())
+    assert _rel_err(K.swiglu_fwd(gu), ref) < 5e-3
+    dgu = K.swiglu_bwd(gu, dout)
+    assert _rel_err(dgu[:, :f], g.grad) < 1e-2 and _rel_err(dgu[:, f:], u.grad) < 1e-2
+
+
+def test_embedding(cuda_device):
+    V, d, T = 1000, 256, 513
+    table = torch.randn(V, d, device=cuda_device).bfloat16()
+    ids = torch.randint(0, V, (T,), device=cuda_device, dtype=torch.int32)
+    assert torch.equal(K.embed_fwd(ids, table), table[ids.long()])
+    dout = torch.randn(T, d, device=cuda_device).bfloat16()
+    dt = torch.zeros(V, d, device=cuda_device)
+    K.embed_bwd(ids, dout, dt)
+    ref = torch.zeros(V, d, device=cuda_device).index_add_(0, ids.long(), dout.float())
+    assert _rel_err(dt, ref) < 1e-5
+
+
+@pytest.mark.parametrize("V", [32000, 1003])
+def test_token_logprob_fwd_bwd(cuda_device, V):
+    T = 77
+    ld = (V + 7) // 8 * 8
+    store = (3 * torch.randn(T, ld, device=cuda_device)).bfloat16()
+    logits = store[:, :V]
+    tgt = torch.randint(0, V, (T,), device=cuda_device, dtype=torch.int32)
+    lf = logits.float().clone().requires_grad_(True)
+    ref = torch.log_softmax(lf, -1).gather(1, tgt.long()[:, None])[:, 0]
+    logp, lse = K.token_logprob_fwd(logits, tgt)
+    assert torch.allclose(logp, ref, atol=2e-3, rtol=1e-3)
+    coef = torch.randn(T, device=cuda_device)
+    ref.backward(coef)
+    K.token_logprob_bwd_(logits, tgt, lse, coef)
+    assert _rel_err(logits, lf.grad) < 1e-2
+
+
+def test_policy_loss(cuda_device):
+    n = 5000
+    lp = -torch.rand(n, device=cuda_device) * 3
+    old = lp + 0.3 * torch.randn(n, device=cuda_device)
+    refp = lp + 0.1 * torch.randn(n, device=cuda_device)
+    adv = torch.randn(n, device=cuda_device)
+    mask = (torch.rand(n, device=cuda_device) > 0.3).float()
+    eps, klc = 0.2, 0.05
+    denom = mask.sum().item()
+    x = lp.clone().requires_grad_(True)
+    ratio = torch.exp(x - old)
+    pg = -torch.minimum(ratio * adv, torch.clamp(ratio, 1 - eps, 1 + eps) * adv)
+    loss = ((pg + klc * (x - refp)) * mask).sum() / denom
+    loss.backward()
+    coef, acc = K.policy_loss(lp, old, refp, adv, mask, eps, klc, 1.0 / denom)
+    assert abs(acc[0].item() - loss.item()) < 1e-4
+    assert torch.allclose(coef, x.grad, atol=1e-6, rtol=1e-4)
+
+
+def test_dpo_loss(cuda_device):
+    P, T = 16, 40
+    beta = 0.1
+    lp = -torch.rand(2 * P, T, device=cuda_device)
+    mask = (torch.rand(2 * P, T, device=cuda_device) > 0.4).float()
+    ref_seq = -torch.rand(2 * P, device=cuda_device) * 10
+    x = lp.clone().requires_grad_(True)
+    seq = (x * mask).sum(-1)
+    z = beta * ((seq[0::2] - seq[1::2]) - (ref_seq[0::2] - ref_seq[1::2]))
+    loss = -torch.nn.functional.logsigmoid(z).mean()
+    loss.backward()
+    pi_seq = K.masked_rowsum(lp, mask)
+    assert torch.allclose(pi_seq, seq.detach(), atol=1e-4)
+    seq_coef, acc = K.dpo_loss(pi_seq, ref_seq, beta)
+    coef = K.expand_seq_coef(seq_coef, mask)
+    assert abs(acc[0].item() - loss.item()) < 1e-5
+    assert torch.allclose(coef, x.grad, atol=1e-6, rtol=1e-4)
+
+
+def test_value_loss_and_gae(cuda_device):
+    B, T = 9, 50
+    lens = torch.randint(1, T + 1, (B,), device=cuda_device)
+    mask = (torch.arange(T, device=cuda_device)[None, :] < lens[:, None]).float()
+    v = torch.randn(B, T, device=cuda_device)
+    old = -torch.rand(B, T, device=cuda_device)
+    refp = -torch.rand(B, T, device=cuda_device)
+    scores = torch.randn(B, device=cuda_device)
+    beta, gamma, lam = 0.1, 0.99, 0.95
+    adv, ret = K.gae(old, refp, v, mask, scores, beta, gamma, lam, whiten=False)
+    r = -beta * (old - refp) * mask
+    r[torch.arange(B), lens - 1] += scores
+    a_ref = torch.zeros(B, T, device=cuda_device)
+    a_next = torch.zeros(B, device=cuda_device)
+    for t in reversed(range(T)):
+        v_next = v[:, t + 1] * mask[:, t + 1] if t + 1 < T else torch.zeros(B, device=cuda_device)
+        m_next = mask[:, t + 1] if t + 1 < T else torch.zeros(B, device=cuda_device)
+        delta = r[:, t] + gamma * v_next - v[:, t]
+        a_next = delta + gamma * lam * m_next * a_next
+        a_ref[:, t] = a_next * mask[:, t]
+    assert torch.allclose(adv, a_ref, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(ret, (a_ref + v) * mask, atol=1e-4, rtol=1e-4)
+    adv_w, _ = K.gae(old, refp, v, mask, scores, beta, gamma, lam, whiten=True)
+    n = mask.sum()
+    mean = (a_ref * mask).sum() / n
+    var = (((a_ref - mean) * mask) ** 2).sum() / n
+    assert torch.allclose(adv_w, (a_ref - mean) * torch.rsqrt(var + 1e-6) * mask, atol=1e-3, rtol=1e-3)
+    dv, acc = K.value_loss(v, ret, mask, 1.0 / n.item())
+    assert abs(acc[0].item() - (((v - ret) * mask) ** 2).sum().item() / n.item()) < 1e-4
+    assert torch.allclose(dv, 2 * (v - ret) * mask / n, atol=1e-6)
+
+
+def test_group_advantage(cuda_device):
+    r = torch.randn(8 * 4, device=cuda_device)
+    out = K.group_advantage(r, 4)
+    g = r.view(8, 4)
+    ref = (g - g.mean(1, keepdim=True)) / g.std(1, unbiased=False, keepdim=True).clamp_min(1e-6)
+    assert torch.allclose(out.view(8, 4), ref, atol=1e-5)
+
+
+def test_sampler(cuda_device):
+    B, V = 64, 1000
+    logits = (2 * torch.randn(B, V, device=cuda_device)).bfloat16()
+    tok, lp = K.sample(logits, 1.0, True, 1)
+    assert torch.equal(tok.long(), logits.float().argmax(-1))
+    ref_lp = torch.log_softmax(logits.float(), -1)
+    assert torch.allclose(lp, ref_lp.gather(1, tok.long()[:, None])[:, 0], atol=2e-3)
+    # sampled frequencies follow the softmax (one shared distribution, many rows)
+    row = torch.tensor([2.0, 1.0, 0.0, -1.0] + [-20.0] * 12, device=cuda_device).bfloat16()
+    many = row[None, :].expand(20000, 16).contiguous()
+    tok, _ = K.sample(many, 1.0, False, 1234)
+    freq = torch.bincount(tok.long(), minlength=16).float() / 20000
+    assert torch.allclose(freq, torch.softmax(row.float(), -1), atol=0.02)
+    forced = torch.full((B,), -1, device=cuda_device, dtype=torch.int32)
+    forced[3] = 7
+    tok, lp = K.sample(logits, 1.0, False, 5, forced=forced)
+    assert tok[3].item() == 7 and abs(lp[3].item() - ref_lp[3, 7].item()) < 2e-3
+
+
+def test_scalar_head(cuda_device):
+    T, d = 300, 512
+    h = torch.randn(T, d, device=cuda_device).bfloat16()
+    w = (0.05 * torch.randn(d, device=cuda_device)).bfloat16()
+    b = torch.tensor([0.3], device=cuda_device)
+    out = K.head_gemv(h, w, b)
+    assert torch.allclose(out, h.float() @ w.float() + 0.3, atol=1e-3, rtol=1e-3)
+    dout = torch.randn(T, device=cuda_device)
+    dw = torch.zeros(d, device=cuda_device)
+    db = torch.zeros(1, device=cuda_device)
+    dh = K.head_gemv_bwd(h, w, dout, dw, db)
+    assert _rel_err(dh, dout[:, None] * w.float()[None, :]) < 5e-3
+    assert _rel_err(dw, dout @ h.float()) < 1e-4
+    assert abs(db.item() - dout.sum().item()) < 1e-3
+
+
+def test_adamw_matches_torch(cuda_device):
+    n = 4096 * 3
+    p = torch.randn(n, device=cuda_device)
+    g = torch.randn(n, device=cuda_device)
+    ref_p = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref_p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.01)
+    m = torch.zeros(n, device=cuda_device)
+    v = torch.zeros(n, device=cuda_device)
+    w16 = torch.empty(n, device=cuda_device, dtype=torch.bfloat16)
+    for step in range(1, 4):
+        ref_p.grad = g.clone()
+        opt.step()
+        K.adamw_(p, m, v, g, w16, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.01, step=step)
+    assert torch.allclose(p, ref_p.detach(), atol=1e-5, rtol=1e-4)
+    assert torch.equal(w16, p.bfloat16())
+    ss = torch.zeros(1, device=cuda_device)
+    K.sumsq(g, ss)
+    assert abs(ss.item() - g.pow(2).sum().item()) / g.pow(2).sum().item() < 1e-4
+    # clip coefficient read on the device: max_norm / (norm + 1e-6), capped at 1
+    p2, m2, v2 = torch.zeros(n, device=cuda_device), torch.zeros(n, device=cuda_device), torch.zeros(n, device=cuda_device)
+    K.adamw_(p2, m2, v2, g, w16, lr=1.0, beta1=0.0, beta2=0.0, eps=1.0, step=1, sumsq=ss, max_norm=1.0)
+    gc = g * min(1.0, 1.0 / (g.norm().item() + 1e-6))
+    assert torch.allclose(p2, -(gc / (gc.abs() + 1.0)), atol=1e-6)
+
+
+def _paged_cache(cuda_device, lens, Hkv, hd, num_pages):
+    B = len(lens)
+    max_pages = (max(lens) + K.KV_PAGE - 1) // K.KV_PAGE
+    perm = torch.randperm(num_pages)[: B * max_pages].view(B, max_pages)
+    table = perm.to(device=cuda_device, dtype=torch.int32).contiguous()
+    kc = torch.zeros(num_pages, Hkv, K.KV_PAGE, hd, device=cuda_device, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    return table, kc, vc
+
+
+@pytest.mark.parametrize("nsplit", [1, 4])
+@pytest.mark.parametrize("H,Hkv", [(8, 8), (8, 2)])
+def test_kv_append_and_paged_decode(cuda_device, nsplit, H, Hkv):
+    hd = 128
+    lens = [1, 63, 64, 65, 300, 517]
+    B = len(lens)
+    table, kc, vc = _paged_cache(cuda_device, lens, Hkv, hd, 64)
+    T = sum(lens)
+    ld = (H + 2 * Hkv) * hd
+    qkv = torch.randn(T, ld, device=cuda_device).bfloat16()
+    seq_id = torch.cat([torch.full((l,), i) for i, l in enumerate(lens)]).to(cuda_device, torch.int32)
+    pos = torch.cat([torch.arange(l) for l in lens]).to(cuda_device, torch.int32)
+    K.kv_append(qkv, H * hd, (H + Hkv) * hd, seq_id, pos, table, kc, vc, Hkv, hd)
+    q = torch.randn(B, H * hd, device=cuda_device).bfloat16()
+    seq_lens = torch.tensor(lens, device=cuda_device, dtype=torch.int32)
+    out = K.paged_decode_attn(q, 0, kc, vc, table, seq_lens, H, Hkv, hd, 1 / math.sqrt(hd), nsplit=nsplit)
+    off = 0
+    for i, l in enumerate(lens):
+        kk = qkv[off:off + l, H * hd:(H + Hkv) * hd].float().view(l, Hkv, hd)
+        vv = qkv[off:off + l, (H + Hkv) * hd:].float().view(l, Hkv, hd)
+        kk = kk.repeat_interleave(H // Hkv, 1)
+        vv = vv.repeat_interleave(H // Hkv, 1)
+        qq = q[i].float().view(H, hd)
+        p = torch.softmax(torch.einsum("hd,lhd->hl", qq, kk) / math.sqrt(hd), -1)
+        ref = torch.einsum("hl,lhd->hd", p, vv).reshape(-1)
+        assert _rel_err(out[i], ref) < 1e-2, f"sequence {i}"
+        off += l
+
+
+@pytest.mark.parametrize("lens", [[128], [5, 130, 257], [1000, 31, 384]])
+@pytest.mark.parametrize("H,Hkv", [(4, 4), (4, 2)])
+def test_flash_attn_fwd(cuda_device, lens, H, Hkv):
+    hd = 128
+    T = sum(lens)
+    ld = (H + 2 * Hkv) * hd
+    qkv = torch.randn(T, ld, device=cuda_device).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=cuda_device, dtype=torch.int32)
+    out, lse = K.flash_attn_fwd(qkv, 0, H * hd, (H + Hkv) * hd, cu, max(lens), H, Hkv, hd)
+    K.check_status()
+    off = 0
+    for l in lens:
+        q = qkv[off:off + l, :H * hd].float().view(l, H, hd).transpose(0, 1)
+        k = qkv[off:off + l, H * hd:(H + Hkv) * hd].float().view(l, Hkv, hd).transpose(0, 1).repeat_interleave(H // Hkv, 0)
+        v = qkv[off:off + l, (H + Hkv) * hd:].float().view(l, Hkv, hd).transpose(0, 1).repeat_interleave(H // Hkv, 0)
+        s = q @ k.transpose(1, 2) / math.sqrt(hd)
+        s = s.masked_fill(torch.triu(torch.ones(l, l, device=cuda_device, dtype=torch.bool), 1), float("-inf"))
+        ref = (torch.softmax(s, -1) @ v).transpose(0, 1).reshape(l, H * hd)
+        assert _rel_err(out[off:off + l], ref) < 1e-2
+        assert torch.allclose(lse[:, off:off + l], torch.logsumexp(s, -1), atol=2e-2, rtol=1e-3)
+        off += l
