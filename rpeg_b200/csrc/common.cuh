@@ -16,8 +16,9 @@
 #define RPEG_ERR_FLAG_TIMEOUT 2
 #define RPEG_ERR_BAD_ARG 3
 
-#ifndef RPEG_SPIN_LIMIT
-#define RPEG_SPIN_LIMIT (1u << 24)
+// Upper bound of any single device-side wait, in nanoseconds of %globaltimer.
+#ifndef RPEG_WAIT_LIMIT_NS
+#define RPEG_WAIT_LIMIT_NS 2000000000ull
 #endif
 
 namespace rpeg {
@@ -68,11 +69,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait. `abort_flag` is a shared-memory word any role sets when it gives up, so the
 // other roles leave their own waits promptly instead of running into their own limit.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int where) {
-  for (uint32_t spin = 0; spin < RPEG_SPIN_LIMIT; ++spin) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 255u) == 255u && *abort_flag) return false;
+    if ((spin & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > RPEG_WAIT_LIMIT_NS) break;
+    }
   }
   *abort_flag = 1;
   record_error(status, RPEG_ERR_MBAR_TIMEOUT, where, static_cast<int>(parity));

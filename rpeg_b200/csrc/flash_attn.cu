@@ -312,3 +312,331 @@ extern "C" int rpeg_flash_attn_fwd(const void* qkv, int ld, int q_col0, int k_co
                                                               scale * 1.4426950408889634f, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
+
+namespace rpeg {
+
+// =====================================================================================
+// Backward.
+//
+// One CTA owns one 128-key tile of one (sequence, head) and walks the query tiles at or below the
+// diagonal. Everything is computed transposed (key = TMEM lane = thread) so that P^T and dS^T can
+// feed the next MMA straight from TMEM:
+//   S^T  = K Q^T          (A = K smem,  B = Q smem,  both K-major)      -> TMEM cols   0..127
+//   dP^T = V dO^T         (A = V smem,  B = dO smem, both K-major)      -> TMEM cols 128..255
+//   P^T  = exp2(S^T*scale - lse_q)            bf16, over S^T (cols 0..63)
+//   dS^T = P^T * (dP^T - D_q)                 bf16, over dP^T (cols 128..191) and to shared memory
+//   dV  += P^T  dO        (A = P^T TMEM,  B = dO smem read MN-major)    -> TMEM cols 256..383
+//   dK  += dS^T Q         (A = dS^T TMEM, B = Q smem read MN-major)     -> TMEM cols 384..511
+//   dQ_i = dS K           (A = dS^T smem read MN-major, B = K smem read MN-major)
+//                                                                       -> TMEM cols 0..127 (S^T is dead)
+// dQ_i is drained by the same threads (now lane = query row) with fp32 vector atomics into a
+// [T, H*128] fp32 accumulator; dK (scaled) and dV are written once at the end as bf16 into the
+// K and V column blocks of a packed gradient buffer with the same layout as qkv.
+// D_q = rowsum(dO * O) comes from a small pre-pass. Needs H == Hkv.
+constexpr int FB_SMEM = FA_TILE_BYTES * 5 + 1024 + 1024 + 256;
+
+__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                     float* __restrict__ dvec, int T, int H) {
+  // one warp per (token, head): D[h, t] = sum_d dO * O
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (w >= static_cast<long long>(T) * H) return;
+  const int t = static_cast<int>(w / H), h = static_cast<int>(w % H);
+  const int lane = threadIdx.x & 31;
+  const size_t off = (static_cast<size_t>(t) * H + h) * FA_HD + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(o + off), b = *reinterpret_cast<const uint2*>(dout + off);
+  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  s = warp_sum(s);
+  if (lane == 0) dvec[static_cast<size_t>(h) * T + t] = s;
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+                      const int* __restrict__ cu_seqlens, const float* __restrict__ lse,
+                      const float* __restrict__ dvec, float* __restrict__ dq_acc,
+                      __nv_bfloat16* __restrict__ dqkv, int ld_dqkv, int T, int H, int q_col0, int k_col0,
+                      int v_col0, float scale, int* status) {
+  const int b = blockIdx.z, h = blockIdx.y, kt = blockIdx.x;  // early key tiles carry the most work
+  const int seq0 = cu_seqlens[b];
+  const int L = cu_seqlens[b + 1] - seq0;
+  const int k0 = kt * FA_BN;
+  if (k0 >= L) return;
+  const int n_qt = (L + FA_BM - 1) / FA_BM;
+  const int n_iter = n_qt - kt;  // query tiles kt .. n_qt-1
+  const float scale_log2 = scale * 1.4426950408889634f;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* k_sm = smem;
+  uint8_t* v_sm = k_sm + FA_TILE_BYTES;
+  uint8_t* q_sm = v_sm + FA_TILE_BYTES;
+  uint8_t* do_sm = q_sm + FA_TILE_BYTES;
+  uint8_t* ds_sm = do_sm + FA_TILE_BYTES;
+  float* lse_sm = reinterpret_cast<float*>(ds_sm + FA_TILE_BYTES);  // [128]
+  float* d_sm = lse_sm + 128;                                       // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(d_sm + 128);
+  uint64_t* kv_full = bars;         // K and V landed
+  uint64_t* qdo_full = bars + 1;    // Q_i and dO_i landed
+  uint64_t* qdo_empty = bars + 2;   // MMAs reading Q_i / dO_i / dS_i finished
+  uint64_t* s_done = bars + 3;      // S^T and dP^T complete
+  uint64_t* pds_ready = bars + 4;   // P^T and dS^T written (count 4)
+  uint64_t* dq_done = bars + 5;     // dQ_i complete (implies dV, dK of this iteration too)
+  uint64_t* dq_drained = bars + 6;  // dQ_i read out of TMEM (count 4)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1); mbar_init(qdo_full, 1); mbar_init(qdo_empty, 1); mbar_init(s_done, 1);
+    mbar_init(pds_ready, 4); mbar_init(dq_done, 1); mbar_init(dq_drained, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_qkv);
+      tma_prefetch_desc(&tmap_do);
+      mbar_expect_tx(kv_full, 2 * FA_TILE_BYTES);
+      tma_load_2d(k_sm, &tmap_qkv, kv_full, k_col0 + h * FA_HD, seq0 + k0);
+      tma_load_2d(k_sm + 16384, &tmap_qkv, kv_full, k_col0 + h * FA_HD + 64, seq0 + k0);
+      tma_load_2d(v_sm, &tmap_qkv, kv_full, v_col0 + h * FA_HD, seq0 + k0);
+      tma_load_2d(v_sm + 16384, &tmap_qkv, kv_full, v_col0 + h * FA_HD + 64, seq0 + k0);
+      for (int it = 0; it < n_iter; ++it) {
+        const int q0 = (kt + it) * FA_BM;
+        if (!mbar_wait(qdo_empty, (static_cast<uint32_t>(it) & 1u) ^ 1u, abort_flag, status, 600)) break;
+        mbar_expect_tx(qdo_full, 2 * FA_TILE_BYTES);
+        tma_load_2d(q_sm, &tmap_qkv, qdo_full, q_col0 + h * FA_HD, seq0 + q0);
+        tma_load_2d(q_sm + 16384, &tmap_qkv, qdo_full, q_col0 + h * FA_HD + 64, seq0 + q0);
+        tma_load_2d(do_sm, &tmap_do, qdo_full, h * FA_HD, seq0 + q0);
+        tma_load_2d(do_sm + 16384, &tmap_do, qdo_full, h * FA_HD + 64, seq0 + q0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_kk = make_idesc_bf16(128, 128, 0, 0);   // A K-major, B K-major
+      constexpr uint32_t id_kmn = make_idesc_bf16(128, 128, 0, 1);  // A (TMEM or K-major), B MN-major
+      constexpr uint32_t id_mnmn = make_idesc_bf16(128, 128, 1, 1); // both MN-major
+      const uint32_t ka = smem_u32(k_sm), va = smem_u32(v_sm), qa = smem_u32(q_sm), da = smem_u32(do_sm),
+                     dsa = smem_u32(ds_sm);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, status, 610);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint32_t ph = static_cast<uint32_t>(it) & 1u;
+        if (!mbar_wait(qdo_full, ph, abort_flag, status, 611)) break;
+        if (it > 0 && !mbar_wait(dq_drained, ph ^ 1u, abort_flag, status, 612)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = static_cast<uint32_t>((k >> 2) * 16384 + (k & 3) * 32);
+          umma_bf16_ss(t_s, make_smem_desc_sw128(ka + off, 16, 1024), make_smem_desc_sw128(qa + off, 16, 1024), id_kk,
+                       k != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = static_cast<uint32_t>((k >> 2) * 16384 + (k & 3) * 32);
+          umma_bf16_ss(t_dp, make_smem_desc_sw128(va + off, 16, 1024), make_smem_desc_sw128(da + off, 16, 1024), id_kk,
+                       k != 0 ? 1u : 0u);
+        }
+        umma_commit(s_done);
+        if (!mbar_wait(pds_ready, ph, abort_flag, status, 613)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dV += P^T dO : 16 queries per step
+          umma_bf16_ts(t_dv, t_s + k * 8, make_smem_desc_sw128(da + k * 2048, 16384, 1024), id_kmn, (it | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dK += dS^T Q
+          umma_bf16_ts(t_dk, t_dp + k * 8, make_smem_desc_sw128(qa + k * 2048, 16384, 1024), id_kmn, (it | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dQ = dS K : 16 keys per step, both operands MN-major
+          umma_bf16_ss(t_s, make_smem_desc_sw128(dsa + k * 2048, 16384, 1024),
+                       make_smem_desc_sw128(ka + k * 2048, 16384, 1024), id_mnmn, k != 0 ? 1u : 0u);
+        umma_commit(qdo_empty);
+        umma_commit(dq_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // key row inside the tile; later the query row when draining dQ
+    const int kj = k0 + r;
+    const bool key_valid = kj < L;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const int sm_tid = threadIdx.x - 64;  // 0..127
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const uint32_t ph = static_cast<uint32_t>(it) & 1u;
+      const int q0 = (kt + it) * FA_BM;
+      // per-query vectors of this tile (lse in log2 units); +inf lse turns invalid queries into p = 0
+      {
+        const int qi = q0 + sm_tid;
+        const bool qv = qi < L;
+        lse_sm[sm_tid] = qv ? lse[static_cast<size_t>(h) * T + seq0 + qi] * 1.4426950408889634f : INFINITY;
+        d_sm[sm_tid] = qv ? dvec[static_cast<size_t>(h) * T + seq0 + qi] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!__all_sync(0xffffffffu, mbar_wait(s_done, ph, abort_flag, status, 620))) { ok = false; break; }
+      tc_fence_after_sync();
+      const bool diag = (it == 0);
+      uint8_t* ds_row = ds_sm + r * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(t_s + lane_base + c * 32, sv);
+        tmem_ld_32x32(t_dp + lane_base + c * 32, dv);
+        tmem_wait_ld();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float pv[2], gv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int qq = c * 32 + 2 * i + e;  // query index inside the tile
+            const bool valid = key_valid && (!diag || (q0 + qq >= kj));
+            const float p = valid ? exp2f(__uint_as_float(sv[2 * i + e]) * scale_log2 - lse_sm[qq]) : 0.f;
+            pv[e] = p;
+            gv[e] = p * (__uint_as_float(dv[2 * i + e]) - d_sm[qq]);
+          }
+          pp[i] = pack_bf16x2(pv[0], pv[1]);
+          dd[i] = pack_bf16x2(gv[0], gv[1]);
+        }
+        tmem_st_32x16(t_s + lane_base + c * 16, pp);
+        tmem_st_32x16(t_dp + lane_base + c * 16, dd);
+        // dS^T row r, queries [32c, 32c+32): atom c/2, 16-byte chunks (c%2)*4 .. +3, 128B swizzle
+        uint8_t* atom = ds_row + (c >> 1) * 16384;
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const int chunk = (c & 1) * 4 + v4;
+          *reinterpret_cast<uint4*>(atom + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(dd[v4 * 4 + 0], dd[v4 * 4 + 1], dd[v4 * 4 + 2], dd[v4 * 4 + 3]);
+        }
+      }
+      tmem_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_ready);
+      // drain dQ_i: lane = query row
+      if (!__all_sync(0xffffffffu, mbar_wait(dq_done, ph, abort_flag, status, 621))) { ok = false; break; }
+      tc_fence_after_sync();
+      const int qi = q0 + r;
+      float* dq_row = dq_acc + (static_cast<size_t>(seq0 + qi) * H + h) * FA_HD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + lane_base + c * 32, v);
+        tmem_wait_ld();
+        if (qi < L) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 val = make_float4(__uint_as_float(v[4 * i]) * scale, __uint_as_float(v[4 * i + 1]) * scale,
+                                           __uint_as_float(v[4 * i + 2]) * scale, __uint_as_float(v[4 * i + 3]) * scale);
+            atomicAdd(reinterpret_cast<float4*>(dq_row + c * 32 + 4 * i), val);
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_drained);
+    }
+    if (ok) {
+      // dq_done of the last iteration also covers the last dV / dK accumulation
+      tc_fence_after_sync();
+      __nv_bfloat16* dk_row = dqkv + static_cast<size_t>(seq0 + kj) * ld_dqkv + k_col0 + h * FA_HD;
+      __nv_bfloat16* dv_row = dqkv + static_cast<size_t>(seq0 + kj) * ld_dqkv + v_col0 + h * FA_HD;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t v[32];
+        const bool is_k = c >= 4;
+        tmem_ld_32x32((is_k ? t_dk : t_dv) + lane_base + (c & 3) * 32, v);
+        tmem_wait_ld();
+        if (key_valid) {
+          const float sc = is_k ? scale : 1.f;
+          __nv_bfloat16* dst = (is_k ? dk_row : dv_row) + (c & 3) * 32;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[i * 8 + 0]) * sc, __uint_as_float(v[i * 8 + 1]) * sc);
+            o.y = pack_bf16x2(__uint_as_float(v[i * 8 + 2]) * sc, __uint_as_float(v[i * 8 + 3]) * sc);
+            o.z = pack_bf16x2(__uint_as_float(v[i * 8 + 4]) * sc, __uint_as_float(v[i * 8 + 5]) * sc);
+            o.w = pack_bf16x2(__uint_as_float(v[i * 8 + 6]) * sc, __uint_as_float(v[i * 8 + 7]) * sc);
+            *reinterpret_cast<uint4*>(dst + i * 8) = o;
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// dq (bf16, Q column block of dqkv) <- dq_acc (fp32 [T, H*128])
+__global__ void dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv, int ld, int q_col0,
+                                int T, int width) {
+  const int wv = width >> 2;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(T) * wv) return;
+  const int t = static_cast<int>(idx / wv), j = static_cast<int>(idx % wv);
+  const float4 a = reinterpret_cast<const float4*>(dq_acc + static_cast<size_t>(t) * width)[j];
+  uint2 o;
+  o.x = pack_bf16x2(a.x, a.y);
+  o.y = pack_bf16x2(a.z, a.w);
+  *reinterpret_cast<uint2*>(dqkv + static_cast<size_t>(t) * ld + q_col0 + j * 4) = o;
+}
+
+}  // namespace rpeg (reopened below for the launcher)
+
+// qkv/out/lse are the forward's tensors; dout is [T, H*128] bf16. dq_acc is a caller-provided
+// fp32 [T, H*128] scratch that this call zeroes. dqkv ([T, ld_dqkv] bf16) receives dQ, dK, dV in
+// the same column blocks as qkv.
+extern "C" int rpeg_flash_attn_bwd(const void* qkv, int ld, int q_col0, int k_col0, int v_col0, const void* out,
+                                   const void* dout, const float* lse, const int* cu_seqlens, int B,
+                                   int max_seqlen, int T, int H, int Hkv, int hd, float scale, float* dvec,
+                                   float* dq_acc, void* dqkv, int ld_dqkv, int* status, void* stream_v) {
+  using namespace rpeg;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (hd != FA_HD || H != Hkv) return -2;
+  if ((ld | ld_dqkv | q_col0 | k_col0 | v_col0) & 7) return -3;
+  if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(dout)) & 15) return -1;
+  if (B <= 0 || T <= 0 || max_seqlen <= 0) return 0;
+  CUtensorMap tm_qkv, tm_do;
+  int rc = make_tmap_bf16_2d(&tm_qkv, qkv, static_cast<uint64_t>(ld), static_cast<uint64_t>(T), static_cast<uint64_t>(ld), 64, 128);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tm_do, dout, static_cast<uint64_t>(H) * FA_HD, static_cast<uint64_t>(T),
+                         static_cast<uint64_t>(H) * FA_HD, 64, 128);
+  if (rc) return rc - 100;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FB_SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  const long long warps = static_cast<long long>(T) * H;
+  attn_bwd_prep_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), dvec, T, H);
+  if (cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * H * FA_HD * sizeof(float), stream) != cudaSuccess) return -22;
+  dim3 grid((max_seqlen + FA_BN - 1) / FA_BN, H, B);
+  flash_attn_bwd_kernel<<<grid, FA_THREADS, FB_SMEM, stream>>>(tm_qkv, tm_do, cu_seqlens, lse, dvec, dq_acc,
+                                                              static_cast<__nv_bfloat16*>(dqkv), ld_dqkv, T, H, q_col0,
+                                                              k_col0, v_col0, scale, status);
+  const long long n = static_cast<long long>(T) * (H * FA_HD / 4);
+  dq_store_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dqkv),
+                                                                             ld_dqkv, q_col0, T, H * FA_HD);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

@@ -44,7 +44,8 @@ enum { EPI_BF16 = 0, EPI_F32 = 1 };
 template <int BN, int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         void* __restrict__ Cout, int M, int N, int K, int ldc, int accumulate, int* status) {
+                         void* __restrict__ Cout, int M, int N, int K, int ldc, int accumulate, int k_splits,
+                         long long split_stride, int* status) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -63,6 +64,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int n_tiles = (N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + BK - 1) / BK;
+  // Split-K: work item w = tile * k_splits + split; a split covers kb_per consecutive K blocks and
+  // writes its own fp32 partial at Cout + split * split_stride.
+  const int kb_per = (num_kb + k_splits - 1) / k_splits;
+  const int num_items = num_tiles * k_splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -105,11 +110,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
         int tm, tn;
-        tile_coords(t, tm, tn);
+        tile_coords(w / k_splits, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (w % k_splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, 100)) goto producer_done;
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
@@ -140,11 +146,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t phase = 0;
       int buf = 0;
       uint32_t acc_phase = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
         if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1u, abort_flag, status, 200)) goto mma_done;
         tc_fence_after_sync();
         const uint32_t tacc = tmem_base + static_cast<uint32_t>(buf * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (w % k_splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, 201)) goto mma_done;
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
@@ -157,7 +164,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                      : make_smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, 64 * BK * 2, 1024)
                                      : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_bf16_ss(tacc, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss(tacc, da, db, idesc, (kb > kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -171,9 +178,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     int buf = 0;
     uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
       int tm, tn;
-      tile_coords(t, tm, tn);
+      tile_coords(w / k_splits, tm, tn);
+      const long long split_off = static_cast<long long>(w % k_splits) * split_stride;
       const int row = tm * BM + quad * 32 + lane;
       const int n0 = tn * BN;
       if (!__all_sync(0xffffffffu, mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, status, 300))) break;
@@ -200,7 +208,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               }
             }
           } else {
-            float* crow = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * ldc + col0;
+            float* crow = reinterpret_cast<float*>(Cout) + split_off + static_cast<size_t>(row) * ldc + col0;
 #pragma unroll
             for (int v = 0; v < 8; ++v) {
               if (col0 + v * 4 < N) {
@@ -269,7 +277,8 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
 
 template <int BN, int EPI, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, int ldc,
-                       int accumulate, int* status, int num_sms, cudaStream_t stream) {
+                       int accumulate, int k_splits, long long split_stride, int* status, int num_sms,
+                       cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, A_MN, B_MN>;
   static bool configured = false;
@@ -278,20 +287,22 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, in
     if (e != cudaSuccess) return -20;
     configured = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, accumulate, status);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride,
+                                                        status);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 template <int BN, int EPI>
 static int dispatch_major(int transA, int transB, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M,
-                          int N, int K, int ldc, int accumulate, int* status, int num_sms, cudaStream_t stream) {
-  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, status, num_sms, stream);
-  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, status, num_sms, stream);
+                          int N, int K, int ldc, int accumulate, int k_splits, long long split_stride, int* status,
+                          int num_sms, cudaStream_t stream) {
+  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream);
+  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream);
   if constexpr (BN >= 64) {  // an MN-major B tile is built from 64-column TMA boxes
-    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, status, num_sms, stream);
-    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, status, num_sms, stream);
+    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream);
+    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream);
   }
   return -30;
 }
@@ -304,7 +315,7 @@ using namespace rpeg;
 
 extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                               int ldc, int transA, int transB, int out_fp32, int accumulate, int bn_hint,
-                              int* status, void* stream_v) {
+                              float* workspace, long long workspace_elems, int* status, void* stream_v) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row pitches; the vector epilogue needs N and ldc % 8 == 0.
@@ -325,6 +336,30 @@ extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     while (bn > 32 && m_tiles * ((N + bn - 1) / bn) < g_num_sms) bn >>= 1;
     if (transB && bn < 64) bn = 64;
   }
+  // Split-K for skinny problems (decode): when one wave of output tiles leaves most SMs idle, cut
+  // K so every SM streams a slice of the weights; fp32 partials go to `workspace` and a second
+  // kernel sums them into the bf16 output.
+  int k_splits = 1;
+  long long split_stride = 0;
+  void* gemm_out = C;
+  int gemm_ldc = ldc, gemm_fp32 = out_fp32;
+  if (workspace != nullptr && !out_fp32 && !accumulate && M <= 2 * BM) {
+    if (bn_hint == 0) bn = N >= 256 ? 256 : (N >= 128 ? 128 : (N >= 64 ? 64 : 32));
+    const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    const int num_kb = (K + BK - 1) / BK;
+    int want = g_num_sms / tiles;
+    if (want > num_kb / 4) want = num_kb / 4;
+    const long long per_split = static_cast<long long>(M) * N;
+    if (want > 1 && per_split > 0 && workspace_elems / per_split < want) want = static_cast<int>(workspace_elems / per_split);
+    if (want > 1) {
+      const int kb_per = (num_kb + want - 1) / want;
+      k_splits = (num_kb + kb_per - 1) / kb_per;
+      split_stride = per_split;
+      gemm_out = workspace;
+      gemm_ldc = N;
+      gemm_fp32 = 1;
+    }
+  }
   CUtensorMap ta, tb;
   int rc;
   if (!transA) rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
@@ -333,12 +368,13 @@ extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if (!transB) rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
   else rc = make_tmap_bf16_2d(&tb, B, N, K, ldb, 64, BK);
   if (rc) return rc - 100;
-#define RPEG_GEMM_CASE(BN_)                                                                                   \
-  case BN_:                                                                                                    \
-    return out_fp32 ? dispatch_major<BN_, EPI_F32>(transA, transB, ta, tb, C, M, N, K, ldc, accumulate, status, \
-                                                   g_num_sms, stream)                                          \
-                    : dispatch_major<BN_, EPI_BF16>(transA, transB, ta, tb, C, M, N, K, ldc, accumulate, status, \
-                                                    g_num_sms, stream);
+#define RPEG_GEMM_CASE(BN_)                                                                                      \
+  case BN_:                                                                                                       \
+    rc = gemm_fp32 ? dispatch_major<BN_, EPI_F32>(transA, transB, ta, tb, gemm_out, M, N, K, gemm_ldc, accumulate, \
+                                                  k_splits, split_stride, status, g_num_sms, stream)              \
+                   : dispatch_major<BN_, EPI_BF16>(transA, transB, ta, tb, gemm_out, M, N, K, gemm_ldc, accumulate, \
+                                                   k_splits, split_stride, status, g_num_sms, stream);            \
+    break;
   switch (bn) {
     RPEG_GEMM_CASE(256)
     RPEG_GEMM_CASE(128)
@@ -348,4 +384,6 @@ extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int 
       return -4;
   }
 #undef RPEG_GEMM_CASE
+  if (rc == 0 && k_splits > 1) rc = rpeg_splitk_reduce(workspace, C, M, N, ldc, k_splits, stream_v);
+  return rc;
 }

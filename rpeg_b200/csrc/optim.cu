@@ -94,9 +94,10 @@ struct PeerPtrs {
 // word offset `slot*RPEG_MAX_PEERS`. Rank r stores `epoch` into flag[r] of every peer, then waits
 // until every flag in its own pad reached `epoch`. Optionally publishes one float per rank
 // (payload area, word offset 1024 + slot*RPEG_MAX_PEERS) before the flag, e.g. a partial norm.
+// The wait gives up after `timeout_ns` and records RPEG_ERR_FLAG_TIMEOUT in `status`.
 __global__ void flag_barrier_kernel(PeerPtrs pads, int rank, int world, int slot, unsigned epoch,
                                     const float* __restrict__ payload_in, float* __restrict__ payload_out,
-                                    unsigned long long spin_limit, int* status) {
+                                    unsigned long long timeout_ns, int* status) {
   const int t = threadIdx.x;
   if (t < world) {
     unsigned* peer = static_cast<unsigned*>(pads.p[t]);
@@ -108,11 +109,11 @@ __global__ void flag_barrier_kernel(PeerPtrs pads, int rank, int world, int slot
                  : "memory");
     const unsigned* mine = static_cast<const unsigned*>(pads.p[rank]) + slot * RPEG_MAX_PEERS + t;
     unsigned seen = 0;
-    unsigned long long spins = 0;
+    const uint64_t t0 = global_timer_ns();
     for (;;) {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
       if (static_cast<int>(seen - epoch) >= 0) break;
-      if (++spins > spin_limit) {
+      if (global_timer_ns() - t0 > timeout_ns) {
         record_error(status, RPEG_ERR_FLAG_TIMEOUT, 400 + slot, t);
         break;
       }
@@ -234,11 +235,11 @@ extern "C" int rpeg_sumsq(const float* x, long long n, float* out, void* stream)
 }
 
 extern "C" int rpeg_flag_barrier(void* const* pads, int rank, int world, int slot, unsigned epoch,
-                                 const float* payload_in, float* payload_out, unsigned long long spin_limit,
+                                 const float* payload_in, float* payload_out, unsigned long long timeout_ns,
                                  int* status, void* stream) {
   if (world < 1 || world > RPEG_MAX_PEERS || slot < 0 || slot >= 64) return -2;
   flag_barrier_kernel<<<1, 32, 0, STREAM(stream)>>>(make_peers(pads, world), rank, world, slot, epoch,
-                                                   payload_in, payload_out, spin_limit, status);
+                                                   payload_in, payload_out, timeout_ns, status);
   return LAUNCH_OK();
 }
 

@@ -14,7 +14,8 @@ extern "C" {
 
 // ---- gemm.cu
 int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                   int transA, int transB, int out_fp32, int accumulate, int bn_hint, int* status, void* stream);
+                   int transA, int transB, int out_fp32, int accumulate, int bn_hint, float* workspace,
+                   long long workspace_elems, int* status, void* stream);
 
 // ---- norm_rope.cu
 int rpeg_rmsnorm_fwd(const void* x, const void* res, const void* w, void* h_out, void* y, float* rstd, int T,
@@ -59,7 +60,7 @@ int rpeg_adamw(float* p32, float* m, float* v, const float* grad, void* w16, lon
                float max_norm, void* stream);
 int rpeg_sumsq(const float* x, long long n, float* out, void* stream);
 int rpeg_flag_barrier(void* const* pads, int rank, int world, int slot, unsigned epoch, const float* payload_in,
-                      float* payload_out, unsigned long long spin_limit, int* status, void* stream);
+                      float* payload_out, unsigned long long timeout_ns, int* status, void* stream);
 int rpeg_dp_reduce_norm(void* const* grads, int world, long long shard_off, long long shard_n, float scale,
                         float* reduced, float* sumsq, void* stream);
 int rpeg_dp_adam_push(float* p32, float* m, float* v, const float* reduced, void* const* params, int world,
@@ -76,9 +77,24 @@ int rpeg_paged_decode_attn(const void* q, int ldq, int q_col0, const void* kcach
                            const int* page_table, int max_pages, const int* seq_lens, void* out, float* scratch,
                            int B, int H, int Hkv, int hd, int nsplit, float scale, void* stream);
 
+// ---- generate.cu
+int rpeg_decode_prepare(const int* active, const int* gen_count, const int* forced_len, int* forced, int n_slots,
+                        int eos, void* stream);
+int rpeg_decode_advance(const int* sampled, const float* sampled_lp, int* token, int* pos, int* seq_len,
+                        int* active, int* gen_count, int* out_tok, float* out_lp, int n_slots, int max_new,
+                        int eos, int* n_finished, void* stream);
+int rpeg_gather_rows(const void* x, const int* rows, void* out, int n, int d, void* stream);
+int rpeg_scatter_rows(void* x, const int* rows, const void* src, int n, int d, int overwrite, void* stream);
+int rpeg_splitk_reduce(const float* part, void* out, int M, int N, int ldc, int splits, void* stream);
+
 // ---- flash_attn.cu
 int rpeg_flash_attn_fwd(const void* qkv, int ld, int q_col0, int k_col0, int v_col0, const int* cu_seqlens,
                         int B, int max_seqlen, int T, int H, int Hkv, int hd, float scale, void* out, float* lse,
+                        int* status, void* stream);
+
+int rpeg_flash_attn_bwd(const void* qkv, int ld, int q_col0, int k_col0, int v_col0, const void* out,
+                        const void* dout, const float* lse, const int* cu_seqlens, int B, int max_seqlen, int T,
+                        int H, int Hkv, int hd, float scale, float* dvec, float* dq_acc, void* dqkv, int ld_dqkv,
                         int* status, void* stream);
 
 #ifdef __cplusplus

@@ -18,7 +18,7 @@ F = c_float
 LL = c_longlong
 
 _SIGNATURES = {
-    "rpeg_gemm_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P],
+    "rpeg_gemm_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, LL, P, P],
     "rpeg_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
     "rpeg_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, P],
     "rpeg_rope": [P, P, P, P, I, I, I, I, I, I, P],
@@ -47,7 +47,13 @@ _SIGNATURES = {
     "rpeg_copy16": [P, P, LL, P],
     "rpeg_kv_append": [P, I, I, I, P, P, P, I, P, P, I, I, I, P],
     "rpeg_paged_decode_attn": [P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, F, P],
+    "rpeg_decode_prepare": [P, P, P, P, I, I, P],
+    "rpeg_decode_advance": [P, P, P, P, P, P, P, P, P, I, I, I, P, P],
+    "rpeg_gather_rows": [P, P, P, I, I, P],
+    "rpeg_scatter_rows": [P, P, P, I, I, I, P],
+    "rpeg_splitk_reduce": [P, P, I, I, I, I, P],
     "rpeg_flash_attn_fwd": [P, I, I, I, I, P, I, I, I, I, I, I, F, P, P, P, P],
+    "rpeg_flash_attn_bwd": [P, I, I, I, I, P, P, P, P, I, I, I, I, I, I, F, P, P, P, I, P, P],
 }
 
 

@@ -54,12 +54,14 @@ def _req(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
 # --------------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
-         bn: int = 0) -> torch.Tensor:
+         bn: int = 0, workspace: torch.Tensor | None = None) -> torch.Tensor:
     """``C[M,N] = op(a) @ op(b).T`` on tcgen05 tensor cores with fp32 accumulation.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` with ``trans_a``); ``b`` is ``[N,K]`` — the ``[out,in]`` layout
     of a linear weight — or ``[K,N]`` with ``trans_b``. Rows may be strided (last dim contiguous).
     ``out_dtype=float32, accumulate=True`` adds into ``out`` (used for weight-gradient accumulation).
+    ``workspace`` (fp32 scratch) lets skinny problems (M <= 256, e.g. decode) run split-K so every SM
+    streams part of the weight matrix.
     """
     _req(a, torch.bfloat16, "a")
     _req(b, torch.bfloat16, "b")
@@ -83,7 +85,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         return out
     rc = lib().rpeg_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
                               out.stride(0), int(trans_a), int(trans_b), int(out_dtype == torch.float32),
-                              int(accumulate), bn, status_word(a.device).data_ptr(), _stream())
+                              int(accumulate), bn, _ptr(workspace), 0 if workspace is None else workspace.numel(),
+                              status_word(a.device).data_ptr(), _stream())
     check(rc, "rpeg_gemm_bf16")
     return out
 
@@ -317,3 +320,21 @@ def flash_attn_fwd(qkv, q_col0, k_col0, v_col0, cu_seqlens, max_seqlen, n_heads,
                                     out.data_ptr(), lse.data_ptr(), status_word(qkv.device).data_ptr(), _stream()),
           "rpeg_flash_attn_fwd")
     return out, lse
+
+
+def flash_attn_bwd(qkv, q_col0, k_col0, v_col0, out, dout, lse, cu_seqlens, max_seqlen, n_heads, n_kv_heads, head_dim,
+                   scale=None, dqkv: torch.Tensor | None = None) -> torch.Tensor:
+    """Gradient of ``flash_attn_fwd`` w.r.t. the packed qkv buffer (same column blocks). ``dqkv``
+    may be passed in to reuse a buffer; columns outside the three blocks are left untouched."""
+    T = qkv.shape[0]
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    if dqkv is None:
+        dqkv = torch.empty_like(qkv)
+    dvec = torch.empty((n_heads, T), dtype=torch.float32, device=qkv.device)
+    dq_acc = torch.empty((T, n_heads * head_dim), dtype=torch.float32, device=qkv.device)
+    check(lib().rpeg_flash_attn_bwd(qkv.data_ptr(), qkv.stride(0), q_col0, k_col0, v_col0, out.data_ptr(),
+                                    dout.data_ptr(), lse.data_ptr(), cu_seqlens.data_ptr(), cu_seqlens.numel() - 1,
+                                    max_seqlen, T, n_heads, n_kv_heads, head_dim, scale, dvec.data_ptr(),
+                                    dq_acc.data_ptr(), dqkv.data_ptr(), dqkv.stride(0),
+                                    status_word(qkv.device).data_ptr(), _stream()), "rpeg_flash_attn_bwd")
+    return dqkv

@@ -344,3 +344,29 @@ def test_flash_attn_fwd(cuda_device, lens, H, Hkv):
         assert _rel_err(out[off:off + l], ref) < 1e-2
         assert torch.allclose(lse[:, off:off + l], torch.logsumexp(s, -1), atol=2e-2, rtol=1e-3)
         off += l
+
+
+@pytest.mark.parametrize("lens", [[128], [5, 130, 257], [1000, 31, 384]])
+def test_flash_attn_bwd(cuda_device, lens):
+    H, hd = 4, 128
+    T = sum(lens)
+    qkv = torch.randn(T, 3 * H * hd, device=cuda_device).bfloat16()
+    dout = torch.randn(T, H * hd, device=cuda_device).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=cuda_device, dtype=torch.int32)
+    out, lse = K.flash_attn_fwd(qkv, 0, H * hd, 2 * H * hd, cu, max(lens), H, H, hd)
+    dqkv = K.flash_attn_bwd(qkv, 0, H * hd, 2 * H * hd, out, dout, lse, cu, max(lens), H, H, hd)
+    K.check_status()
+    x = qkv.float().clone().requires_grad_(True)
+    off = 0
+    outs = []
+    for l in lens:
+        q = x[off:off + l, :H * hd].view(l, H, hd).transpose(0, 1)
+        k = x[off:off + l, H * hd:2 * H * hd].view(l, H, hd).transpose(0, 1)
+        v = x[off:off + l, 2 * H * hd:].view(l, H, hd).transpose(0, 1)
+        s = q @ k.transpose(1, 2) / math.sqrt(hd)
+        s = s.masked_fill(torch.triu(torch.ones(l, l, device=cuda_device, dtype=torch.bool), 1), float("-inf"))
+        outs.append((torch.softmax(s, -1) @ v).transpose(0, 1).reshape(l, H * hd))
+        off += l
+    torch.cat(outs).backward(dout.float())
+    for name, lo in (("dq", 0), ("dk", H * hd), ("dv", 2 * H * hd)):
+        assert _rel_err(dqkv[:, lo:lo + H * hd], x.grad[:, lo:lo + H * hd]) < 2e-2, name
