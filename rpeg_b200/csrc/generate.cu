@@ -31,8 +31,10 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, const flo
                                       int* __restrict__ token, int* __restrict__ pos, int* __restrict__ seq_len,
                                       int* __restrict__ active, int* __restrict__ gen_count,
                                       int* __restrict__ out_tok, float* __restrict__ out_lp, int n_slots,
-                                      int max_new, int eos, int* __restrict__ n_finished) {
+                                      int max_new, int eos, int* __restrict__ n_finished,
+                                      unsigned long long* __restrict__ step_counter) {
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s == 0 && step_counter != nullptr) step_counter[0] += 1;
   if (s >= n_slots || !active[s]) return;
   const int t = sampled[s];
   const int g = gen_count[s];
@@ -116,10 +118,12 @@ extern "C" int rpeg_decode_prepare(const int* active, const int* gen_count, cons
 
 extern "C" int rpeg_decode_advance(const int* sampled, const float* sampled_lp, int* token, int* pos, int* seq_len,
                                    int* active, int* gen_count, int* out_tok, float* out_lp, int n_slots,
-                                   int max_new, int eos, int* n_finished, void* stream) {
+                                   int max_new, int eos, int* n_finished, unsigned long long* step_counter,
+                                   void* stream) {
   if (n_slots <= 0) return 0;
   decode_advance_kernel<<<(n_slots + 127) / 128, 128, 0, STREAM(stream)>>>(
-      sampled, sampled_lp, token, pos, seq_len, active, gen_count, out_tok, out_lp, n_slots, max_new, eos, n_finished);
+      sampled, sampled_lp, token, pos, seq_len, active, gen_count, out_tok, out_lp, n_slots, max_new, eos, n_finished,
+      step_counter);
   return LAUNCH_OK();
 }
 

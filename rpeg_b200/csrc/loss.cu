@@ -308,11 +308,13 @@ __device__ __forceinline__ float hash_uniform(uint64_t seed, uint32_t row, uint3
 // synthetic workloads) while still reporting that token's log-prob.
 __global__ void __launch_bounds__(LP_THREADS)
 sample_kernel(const __nv_bfloat16* __restrict__ logits, int V, int ld, float inv_temp, int greedy,
-              unsigned long long seed, const int* __restrict__ forced, int* __restrict__ token_out,
-              float* __restrict__ logp_out) {
+              unsigned long long seed, const unsigned long long* __restrict__ seed_offset,
+              const int* __restrict__ forced, int* __restrict__ token_out, float* __restrict__ logp_out) {
   __shared__ float sm_m[32], sm_s[32], sm_best[32];
   __shared__ int sm_idx[32];
   const int row = blockIdx.x;
+  // a device-resident offset (e.g. a step counter) keeps replays of a captured graph from reusing noise
+  if (seed_offset != nullptr) seed += seed_offset[0] * 0xD1B54A32D192ED03ull;
   const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
   float m = -INFINITY, s = 0.f, best = -INFINITY;
   int best_i = 0;
@@ -464,11 +466,11 @@ extern "C" int rpeg_group_advantage(const float* rewards, float* out, int G, int
   return LAUNCH_OK();
 }
 extern "C" int rpeg_sample(const void* logits, int B, int V, int ld, float temperature, int greedy,
-                           unsigned long long seed, const int* forced, int* token_out, float* logp_out,
-                           void* stream) {
+                           unsigned long long seed, const unsigned long long* seed_offset, const int* forced,
+                           int* token_out, float* logp_out, void* stream) {
   if (B <= 0) return 0;
   sample_kernel<<<B, LP_THREADS, 0, STREAM(stream)>>>(static_cast<const __nv_bfloat16*>(logits), V, ld,
-                                                     1.f / temperature, greedy, seed, forced, token_out, logp_out);
+                                                     1.f / temperature, greedy, seed, seed_offset, forced, token_out, logp_out);
   return LAUNCH_OK();
 }
 extern "C" int rpeg_head_gemv(const void* h, const void* w, const float* bias, float* out, int T, int d,

@@ -49,7 +49,8 @@ int rpeg_gae(const float* old_lp, const float* ref_lp, const float* values, cons
              int whiten, void* stream);
 int rpeg_group_advantage(const float* rewards, float* out, int G, int K, void* stream);
 int rpeg_sample(const void* logits, int B, int V, int ld, float temperature, int greedy,
-                unsigned long long seed, const int* forced, int* token_out, float* logp_out, void* stream);
+                unsigned long long seed, const unsigned long long* seed_offset, const int* forced, int* token_out,
+                float* logp_out, void* stream);
 int rpeg_head_gemv(const void* h, const void* w, const float* bias, float* out, int T, int d, void* stream);
 int rpeg_head_gemv_bwd(const void* h, const void* w, const float* dout, void* dh, float* dw, float* db, int T,
                        int d, void* stream);
@@ -77,12 +78,20 @@ int rpeg_paged_decode_attn(const void* q, int ldq, int q_col0, const void* kcach
                            const int* page_table, int max_pages, const int* seq_lens, void* out, float* scratch,
                            int B, int H, int Hkv, int hd, int nsplit, float scale, void* stream);
 
+// ---- symm.cu
+int rpeg_symm_alloc(unsigned long long bytes, void** out);
+int rpeg_symm_free(void* p);
+int rpeg_ipc_export(void* p, void* handle64);
+int rpeg_ipc_open(const void* handle64, void** out);
+int rpeg_ipc_close(void* p);
+int rpeg_memset_async(void* p, int value, unsigned long long bytes, void* stream);
+
 // ---- generate.cu
 int rpeg_decode_prepare(const int* active, const int* gen_count, const int* forced_len, int* forced, int n_slots,
                         int eos, void* stream);
 int rpeg_decode_advance(const int* sampled, const float* sampled_lp, int* token, int* pos, int* seq_len,
                         int* active, int* gen_count, int* out_tok, float* out_lp, int n_slots, int max_new,
-                        int eos, int* n_finished, void* stream);
+                        int eos, int* n_finished, unsigned long long* step_counter, void* stream);
 int rpeg_gather_rows(const void* x, const int* rows, void* out, int n, int d, void* stream);
 int rpeg_scatter_rows(void* x, const int* rows, const void* src, int n, int d, int overwrite, void* stream);
 int rpeg_splitk_reduce(const float* part, void* out, int M, int N, int ldc, int splits, void* stream);

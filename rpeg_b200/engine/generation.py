@@ -1,0 +1,315 @@
+"""Paged-KV autoregressive generation with continuous batching and CUDA-graph decode steps.
+
+Design (B200-first):
+  * KV lives in fixed pages of 64 tokens; a row reserves the pages for its longest possible
+    sequence when it is admitted and gives them back when it finishes, so the page table of a slot
+    never changes while the row runs and finished rows never trigger the compaction copies the
+    reference performs per layer (RPEG/runtime/workers/megatron_worker.py:2585-2598).
+  * One decode step (all layers, LM head, sampling, state advance) is captured once per slot-count
+    bucket as a CUDA graph and replayed; positions, tokens, EOS detection and output recording are
+    advanced on the device, so the host only looks at a finished-row counter every few steps.
+  * When rows finish, queued prompts are prefilled into the free slots (continuous batching); when
+    the queue is empty and few rows remain, live slots are compacted to the front and a smaller
+    bucket graph takes over. Because KV is paged, compaction moves page-table rows, not KV.
+  * Sampling log-probs are recorded as the PPO/GRPO ``old_logps`` (no second forward), as in the
+    reference (megatron_worker.py:2493-2505).
+Semantics kept from the reference's quantile-phase generation (:2370-2628): rows end at EOS or at
+the length cap; outputs are returned per original row index, right padded, with a response mask.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..models.llama import LlamaModel
+from ..ops import _lib
+from ..ops import kernels as K
+
+PAGE = K.KV_PAGE
+
+
+class PagePool:
+    """Host-side free list of KV pages. Page 0 is a scratch page retired slots point at."""
+
+    def __init__(self, num_pages: int):
+        if num_pages < 2:
+            raise ValueError("need at least two KV pages")
+        self.num_pages = num_pages
+        self.free: List[int] = list(range(num_pages - 1, 0, -1))
+
+    def available(self) -> int:
+        return len(self.free)
+
+    def take(self, n: int) -> List[int]:
+        if n > len(self.free):
+            raise RuntimeError(f"KV page pool exhausted: want {n}, have {len(self.free)}")
+        out = self.free[-n:]
+        del self.free[-n:]
+        return out
+
+    def give(self, pages: List[int]) -> None:
+        self.free.extend(pages)
+
+
+@dataclass
+class GenerationResult:
+    tokens: torch.Tensor        # [N, max_new] int32, right padded with pad_id
+    logprobs: torch.Tensor      # [N, max_new] fp32 log-prob of each generated token under the sampling policy
+    lengths: torch.Tensor       # [N] int32 number of generated tokens (EOS included)
+    counters: Dict[str, float] = field(default_factory=dict)
+
+    def response_mask(self) -> torch.Tensor:
+        t = torch.arange(self.tokens.shape[1], device=self.tokens.device)
+        return (t[None, :] < self.lengths[:, None]).float()
+
+
+class Generator:
+    BUCKETS = (256, 128, 64, 32, 16, 8)
+
+    @staticmethod
+    def kv_bytes_for(cfg, slots: int, max_seq_len: int) -> int:
+        """Bytes of KV storage that ``slots`` rows of up to ``max_seq_len`` tokens need (+ scratch page)."""
+        pages = slots * ((max_seq_len + PAGE - 1) // PAGE) + 1
+        return 2 * cfg.n_layers * pages * cfg.n_kv_heads * PAGE * cfg.head_dim * 2
+
+    def __init__(self, model: LlamaModel, *, max_slots: int = 64, max_seq_len: int = 2048, kv_budget_bytes: float = 16e9,
+                 eos_id: int = 2, pad_id: int = 0, sync_interval: int = 8, use_graphs: bool = True,
+                 kv_storage: Optional[torch.Tensor] = None):
+        """``kv_storage``: optional flat bf16 tensor to carve the KV pages from instead of allocating
+        them; lets the cache share memory with buffers that are dead during generation (gradients)."""
+        cfg = model.cfg
+        self.model, self.cfg, self.dev = model, cfg, model.device
+        self.eos_id, self.pad_id = eos_id, pad_id
+        self.sync_interval = max(1, sync_interval)
+        self.use_graphs = use_graphs
+        self.max_seq_len = max_seq_len
+        self.pages_per_row = (max_seq_len + PAGE - 1) // PAGE
+        page_bytes = 2 * cfg.n_layers * cfg.n_kv_heads * PAGE * cfg.head_dim * 2
+        if kv_storage is not None:
+            kv_budget_bytes = kv_storage.numel() * 2
+        num_pages = int(kv_budget_bytes // page_bytes)
+        max_rows = max(1, (num_pages - 1) // self.pages_per_row)
+        self.max_slots = max(b for b in (*self.BUCKETS, 4, 2, 1) if b <= max(1, min(max_slots, max_rows)))
+        num_pages = self.max_slots * self.pages_per_row + 1
+        self.pool = PagePool(num_pages)
+        shape = (num_pages, cfg.n_kv_heads, PAGE, cfg.head_dim)
+        per = math.prod(shape)
+        if kv_storage is None:
+            kv_storage = torch.zeros(2 * cfg.n_layers * per, dtype=torch.bfloat16, device=self.dev)
+        self.kcache = [kv_storage[(2 * l) * per:(2 * l + 1) * per].view(shape) for l in range(cfg.n_layers)]
+        self.vcache = [kv_storage[(2 * l + 1) * per:(2 * l + 2) * per].view(shape) for l in range(cfg.n_layers)]
+        n = self.max_slots
+        i32 = dict(dtype=torch.int32, device=self.dev)
+        self.token = torch.zeros(n, **i32)
+        self.pos = torch.zeros(n, **i32)
+        self.seq_len = torch.zeros(n, **i32)
+        self.active = torch.zeros(n, **i32)
+        self.gen_count = torch.zeros(n, **i32)
+        self.forced_len = torch.zeros(n, **i32)
+        self.forced = torch.full((n,), -1, **i32)
+        self.slot_ids = torch.arange(n, **i32)
+        self.page_table = torch.zeros((n, self.pages_per_row), **i32)
+        self.sampled = torch.zeros(n, **i32)
+        self.sampled_lp = torch.zeros(n, dtype=torch.float32, device=self.dev)
+        self.n_finished = torch.zeros(1, **i32)
+        self.step_counter = torch.zeros(1, dtype=torch.int64, device=self.dev)
+        self.out_tok: Optional[torch.Tensor] = None
+        self.out_lp: Optional[torch.Tensor] = None
+        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self._graph_launches: Dict[tuple, int] = {}
+        self.kv_bytes = 2 * cfg.n_layers * math.prod(shape) * 2
+
+    # ------------------------------------------------------------------ decode step (graph body)
+    def _nsplit(self, b: int) -> int:
+        ctas = b * self.cfg.n_heads
+        return 1 if ctas >= 296 else min(8, (296 + ctas - 1) // ctas)
+
+    def _decode_body(self, b: int, temperature: float, greedy: bool, seed: int) -> None:
+        m = self.model
+        xf = m.decode_step(self.token[:b], self.pos[:b], self.slot_ids[:b], self.seq_len[:b], self.page_table[:b],
+                           self.kcache, self.vcache, nsplit=self._nsplit(b))
+        logits = m.lm_logits(xf, decode=True)
+        K.decode_prepare(self.active[:b], self.gen_count[:b], self.forced_len[:b], self.forced[:b], self.eos_id)
+        K.sample(logits, temperature, greedy, seed, forced=self.forced[:b], token_out=self.sampled[:b],
+                 logp_out=self.sampled_lp[:b], seed_offset=self.step_counter)
+        K.decode_advance(self.sampled[:b], self.sampled_lp[:b], self.token[:b], self.pos[:b], self.seq_len[:b],
+                         self.active[:b], self.gen_count[:b], self.out_tok[:b], self.out_lp[:b], self.eos_id,
+                         self.n_finished, self.step_counter)
+
+    def _step(self, b: int, temperature: float, greedy: bool, seed: int) -> None:
+        if not self.use_graphs:
+            self._decode_body(b, temperature, greedy, seed)
+            return
+        key = (b, self.out_tok.shape[1], float(temperature), bool(greedy), int(seed), self.out_tok.data_ptr())
+        g = self._graphs.get(key)
+        if g is None:
+            # warm up and capture with every slot parked, so neither pass advances real rows
+            saved = (self.active.clone(), self.n_finished.clone(), self.step_counter.clone())
+            self.active.zero_()
+            cur = torch.cuda.current_stream()
+            side = torch.cuda.Stream(device=self.dev)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                self._decode_body(b, temperature, greedy, seed)
+            cur.wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            n0 = _lib.launch_count()
+            with torch.cuda.graph(g):
+                self._decode_body(b, temperature, greedy, seed)
+            self._graph_launches[key] = _lib.launch_count() - n0
+            _lib.add_launches(-self._graph_launches[key])  # capture itself executes nothing
+            self.active.copy_(saved[0])
+            self.n_finished.copy_(saved[1])
+            self.step_counter.copy_(saved[2])
+            self._graphs[key] = g
+        g.replay()
+        _lib.add_launches(self._graph_launches[key])
+
+    # ------------------------------------------------------------------ prefill of admitted rows
+    def _prefill(self, prompts: List[torch.Tensor], slots: List[int], forced: Optional[List[int]], temperature: float,
+                 greedy: bool, seed: int, max_new: int) -> None:
+        cfg, dev = self.cfg, self.dev
+        lens = [int(p.numel()) for p in prompts]
+        sl = torch.tensor(slots, dtype=torch.long, device=dev)
+        tokens = torch.cat(prompts).to(device=dev, dtype=torch.int32)
+        pos = torch.cat([torch.arange(l, dtype=torch.int32) for l in lens]).to(dev)
+        seq_id = torch.cat([torch.full((l,), s, dtype=torch.int32) for l, s in zip(lens, slots)]).to(dev)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+
+        def sink(layer: int, qkv: torch.Tensor) -> None:
+            K.kv_append(qkv, cfg.q_width, cfg.q_width + cfg.kv_width, seq_id, pos, self.page_table, self.kcache[layer],
+                        self.vcache[layer], cfg.n_kv_heads, cfg.head_dim)
+
+        xf, _ = self.model.forward(tokens, pos, cu, max(lens), keep=False, kv_sink=sink)
+        last = (cu[1:] - 1).contiguous()
+        logits = self.model.lm_logits(K.gather_rows(xf, last))
+        lens_t = torch.tensor(lens, dtype=torch.int32, device=dev)
+        f_len = torch.tensor(forced if forced is not None else [0] * len(slots), dtype=torch.int32, device=dev)
+        first_forced = torch.where(f_len == 1, torch.full_like(f_len, self.eos_id), torch.full_like(f_len, -1))
+        tok, lp = K.sample(logits, temperature, greedy, seed ^ 0x5DEECE66D, forced=first_forced, seed_offset=self.step_counter)
+        done = (tok == self.eos_id) | (max_new <= 1)
+        self.out_tok[sl, 0] = tok
+        self.out_lp[sl, 0] = lp
+        self.gen_count[sl] = 1
+        self.forced_len[sl] = f_len
+        self.active[sl] = (~done).int()
+        self.token[sl] = tok
+        self.pos[sl] = lens_t
+        self.seq_len[sl] = torch.where(done, torch.zeros_like(lens_t), lens_t + 1)
+        self.n_finished += done.sum().int()
+
+    # ------------------------------------------------------------------ public entry
+    @torch.no_grad()
+    def generate(self, prompts, max_new: int, *, temperature: float = 1.0, greedy: bool = False, seed: int = 0,
+                 forced_lens=None) -> GenerationResult:
+        """Generate up to ``max_new`` tokens for every prompt (a ``[N, S]`` int tensor or a list of
+        1-D tensors). ``forced_lens[i] > 0`` makes row ``i`` emit EOS as its ``forced_lens[i]``-th
+        token (synthetic length control for benchmarks); natural EOS and the cap apply regardless."""
+        dev = self.dev
+        rows = [p for p in prompts] if not isinstance(prompts, torch.Tensor) else [prompts[i] for i in range(prompts.shape[0])]
+        N = len(rows)
+        longest = max(int(r.numel()) for r in rows)
+        if longest + max_new > self.max_seq_len:
+            raise ValueError(f"prompt ({longest}) + max_new ({max_new}) exceeds max_seq_len ({self.max_seq_len})")
+        forced = None if forced_lens is None else [int(x) for x in forced_lens]
+        n = self.max_slots
+        if self.out_tok is None or self.out_tok.shape[1] != max_new:  # kept across calls so captured graphs stay valid
+            self.out_tok = torch.empty((n, max_new), dtype=torch.int32, device=dev)
+            self.out_lp = torch.empty((n, max_new), dtype=torch.float32, device=dev)
+            self._graphs.clear()
+        self.out_tok.fill_(self.pad_id)
+        self.out_lp.zero_()
+        res_tok = torch.full((N, max_new), self.pad_id, dtype=torch.int32, device=dev)
+        res_lp = torch.zeros((N, max_new), dtype=torch.float32, device=dev)
+        res_len = torch.zeros(N, dtype=torch.int32, device=dev)
+        for t in (self.active, self.seq_len, self.gen_count, self.n_finished, self.page_table, self.forced_len):
+            t.zero_()
+        slot_row = [-1] * n
+        slot_pages: List[List[int]] = [[] for _ in range(n)]
+        queue = list(range(N))
+        retired = 0
+        counters = dict(prefill_calls=0, decode_steps=0, prefill_tokens=0, compactions=0, host_syncs=0)
+        seen_finished = 0
+
+        def retire(slots_done: List[int]) -> None:
+            nonlocal retired
+            if not slots_done:
+                return
+            s_idx = torch.tensor(slots_done, dtype=torch.long, device=dev)
+            r_idx = torch.tensor([slot_row[s] for s in slots_done], dtype=torch.long, device=dev)
+            res_tok[r_idx] = self.out_tok[s_idx]
+            res_lp[r_idx] = self.out_lp[s_idx]
+            res_len[r_idx] = self.gen_count[s_idx]
+            self.out_tok[s_idx] = self.pad_id
+            self.out_lp[s_idx] = 0
+            self.page_table[s_idx] = 0
+            for s in slots_done:
+                self.pool.give(slot_pages[s])
+                slot_pages[s] = []
+                slot_row[s] = -1
+            retired += len(slots_done)
+
+        while retired < N:
+            free = [s for s in range(n) if slot_row[s] < 0]
+            if queue and free:
+                take = min(len(free), len(queue))
+                new_rows, new_slots = queue[:take], free[:take]
+                del queue[:take]
+                table = torch.zeros((take, self.pages_per_row), dtype=torch.int32)
+                for j, (r, s) in enumerate(zip(new_rows, new_slots)):
+                    need = (int(rows[r].numel()) + max_new + PAGE - 1) // PAGE
+                    pages = self.pool.take(need)
+                    slot_pages[s], slot_row[s] = pages, r
+                    table[j, :need] = torch.tensor(pages, dtype=torch.int32)
+                self.page_table[torch.tensor(new_slots, dtype=torch.long, device=dev)] = table.to(dev)
+                self._prefill([rows[r] for r in new_rows], new_slots, None if forced is None else [forced[r] for r in new_rows],
+                              temperature, greedy, seed, max_new)
+                counters["prefill_calls"] += 1
+                counters["prefill_tokens"] += sum(int(rows[r].numel()) for r in new_rows)
+            live = [s for s in range(n) if slot_row[s] >= 0]
+            used = max(live) + 1 if live else 0
+            if not queue and live and len(live) <= self._bucket(used) // 2 and self._bucket(len(live)) < self._bucket(used):
+                self._compact(live, slot_row, slot_pages)
+                counters["compactions"] += 1
+                live = list(range(len(live)))
+                used = len(live)
+            if used:
+                b = self._bucket(used)
+                for _ in range(self.sync_interval):
+                    self._step(b, temperature, greedy, seed)
+                counters["decode_steps"] += self.sync_interval
+            nf = int(self.n_finished.item())
+            counters["host_syncs"] += 1
+            if nf != seen_finished:
+                seen_finished = nf
+                act = self.active.tolist()
+                retire([s for s in range(n) if slot_row[s] >= 0 and not act[s]])
+        counters["kv_bytes"] = float(self.kv_bytes)
+        return GenerationResult(res_tok, res_lp, res_len, counters)
+
+    def _bucket(self, used: int) -> int:
+        for b in sorted((*self.BUCKETS, 4, 2, 1)):
+            if b >= used and b <= self.max_slots:
+                return b
+        return self.max_slots
+
+    def _compact(self, live: List[int], slot_row: List[int], slot_pages: List[List[int]]) -> None:
+        """Move live slots to the front (state and page-table rows only; KV pages stay where they are)."""
+        k = len(live)
+        idx = torch.tensor(live, dtype=torch.long, device=self.dev)
+        for arr in (self.token, self.pos, self.seq_len, self.active, self.gen_count, self.forced_len, self.page_table,
+                    self.out_tok, self.out_lp):
+            moved = arr[idx].clone()
+            arr[:k] = moved
+            if arr is self.out_tok:
+                arr[k:] = self.pad_id
+            elif arr is not self.pos and arr is not self.token:
+                arr[k:] = 0
+        rows = [slot_row[s] for s in live]
+        pages = [slot_pages[s] for s in live]
+        for s in range(len(slot_row)):
+            slot_row[s] = rows[s] if s < k else -1
+            slot_pages[s] = pages[s] if s < k else []

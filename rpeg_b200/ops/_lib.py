@@ -36,7 +36,7 @@ _SIGNATURES = {
     "rpeg_value_loss": [P, P, P, P, P, LL, F, P],
     "rpeg_gae": [P, P, P, P, P, P, P, I, I, F, F, F, I, P],
     "rpeg_group_advantage": [P, P, I, I, P],
-    "rpeg_sample": [P, I, I, I, F, I, c_ulonglong, P, P, P, P],
+    "rpeg_sample": [P, I, I, I, F, I, c_ulonglong, P, P, P, P, P],
     "rpeg_head_gemv": [P, P, P, P, I, I, P],
     "rpeg_head_gemv_bwd": [P, P, P, P, P, P, I, I, P],
     "rpeg_adamw": [P, P, P, P, P, LL, F, F, F, F, F, I, F, P, I, F, P],
@@ -47,8 +47,14 @@ _SIGNATURES = {
     "rpeg_copy16": [P, P, LL, P],
     "rpeg_kv_append": [P, I, I, I, P, P, P, I, P, P, I, I, I, P],
     "rpeg_paged_decode_attn": [P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, F, P],
+    "rpeg_symm_alloc": [c_ulonglong, P],
+    "rpeg_symm_free": [P],
+    "rpeg_ipc_export": [P, P],
+    "rpeg_ipc_open": [P, P],
+    "rpeg_ipc_close": [P],
+    "rpeg_memset_async": [P, I, c_ulonglong, P],
     "rpeg_decode_prepare": [P, P, P, P, I, I, P],
-    "rpeg_decode_advance": [P, P, P, P, P, P, P, P, P, I, I, I, P, P],
+    "rpeg_decode_advance": [P, P, P, P, P, P, P, P, P, I, I, I, P, P, P],
     "rpeg_gather_rows": [P, P, P, I, I, P],
     "rpeg_scatter_rows": [P, P, P, I, I, I, P],
     "rpeg_splitk_reduce": [P, P, I, I, I, I, P],
@@ -84,6 +90,22 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of native kernel launches issued so far by this process (graph replays included:
+    a replay adds the number of launches recorded while that graph was captured)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def check(rc: int, what: str) -> None:
+    global _launches
     if rc != 0:
         raise RuntimeError(f"{what} failed with native error code {rc}")
+    _launches += 1

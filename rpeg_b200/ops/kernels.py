@@ -245,12 +245,16 @@ def group_advantage(rewards: torch.Tensor, group: int) -> torch.Tensor:
 
 
 def sample(logits: torch.Tensor, temperature: float, greedy: bool, seed: int, forced: torch.Tensor | None = None,
-           token_out: torch.Tensor | None = None, logp_out: torch.Tensor | None = None):
+           token_out: torch.Tensor | None = None, logp_out: torch.Tensor | None = None,
+           seed_offset: torch.Tensor | None = None):
+    """Gumbel-max sample (or argmax) per row with its log-prob; ``seed_offset`` is an int64 device
+    scalar mixed into the seed so graph replays draw fresh noise."""
     B, V = logits.shape
     tok = torch.empty(B, dtype=torch.int32, device=logits.device) if token_out is None else token_out
     lp = torch.empty(B, dtype=torch.float32, device=logits.device) if logp_out is None else logp_out
     check(lib().rpeg_sample(logits.data_ptr(), B, V, logits.stride(0), temperature, int(greedy),
-                            seed & 0xFFFFFFFFFFFFFFFF, _ptr(forced), tok.data_ptr(), lp.data_ptr(), _stream()),
+                            seed & 0xFFFFFFFFFFFFFFFF, _ptr(seed_offset), _ptr(forced), tok.data_ptr(), lp.data_ptr(),
+                            _stream()),
           "rpeg_sample")
     return tok, lp
 
@@ -338,3 +342,29 @@ def flash_attn_bwd(qkv, q_col0, k_col0, v_col0, out, dout, lse, cu_seqlens, max_
                                     dq_acc.data_ptr(), dqkv.data_ptr(), dqkv.stride(0),
                                     status_word(qkv.device).data_ptr(), _stream()), "rpeg_flash_attn_bwd")
     return dqkv
+
+
+# --------------------------------------------------------------------------- decode bookkeeping
+def decode_prepare(active, gen_count, forced_len, forced, eos: int) -> None:
+    check(lib().rpeg_decode_prepare(active.data_ptr(), gen_count.data_ptr(), _ptr(forced_len), forced.data_ptr(),
+                                    active.numel(), eos, _stream()), "rpeg_decode_prepare")
+
+
+def decode_advance(sampled, sampled_lp, token, pos, seq_len, active, gen_count, out_tok, out_lp, eos: int,
+                   n_finished, step_counter=None) -> None:
+    check(lib().rpeg_decode_advance(sampled.data_ptr(), sampled_lp.data_ptr(), token.data_ptr(), pos.data_ptr(),
+                                    seq_len.data_ptr(), active.data_ptr(), gen_count.data_ptr(), out_tok.data_ptr(),
+                                    out_lp.data_ptr(), active.numel(), out_tok.shape[1], eos, n_finished.data_ptr(),
+                                    _ptr(step_counter), _stream()), "rpeg_decode_advance")
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    out = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    check(lib().rpeg_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), rows.numel(), x.shape[1], _stream()),
+          "rpeg_gather_rows")
+    return out
+
+
+def scatter_rows_(x: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, overwrite: bool = False) -> None:
+    check(lib().rpeg_scatter_rows(x.data_ptr(), rows.data_ptr(), src.data_ptr(), rows.numel(), x.shape[1],
+                                  int(overwrite), _stream()), "rpeg_scatter_rows")
