@@ -131,6 +131,7 @@ def schedule(executable: ExecutableRPEG, cost_model: NodeCostModel, device_space
     finish = [None] * n
     ready = [False] * n
     parked: Dict[str, int] = {}
+    placed: List[int] = []
     heap: list = []
     tie = 0
 
@@ -196,6 +197,7 @@ def schedule(executable: ExecutableRPEG, cost_model: NodeCostModel, device_space
             for j in pair:
                 ready[j] = False
                 start[j], finish[j] = t_grp, t_fin
+                placed.append(j)
             for j in pair:
                 for d in blocked[j]:
                     avail[d] = t_fin
@@ -204,6 +206,7 @@ def schedule(executable: ExecutableRPEG, cost_model: NodeCostModel, device_space
             continue
         ready[i] = False
         start[i], finish[i] = t_now, t_now + dur[i]
+        placed.append(i)
         for d in blocked[i]:
             avail[d] = finish[i]
         release(i, finish[i])
@@ -211,4 +214,5 @@ def schedule(executable: ExecutableRPEG, cost_model: NodeCostModel, device_space
     if any(s is None for s in start):
         missing = [nodes[i].id for i in range(n) if start[i] is None]
         raise ValueError(f"cycle in executable graph; unscheduled: {missing}")
-    return Trace({v: start[i] for i, v in enumerate(nodes)}, {v: finish[i] for i, v in enumerate(nodes)}, reserved)
+    return Trace({v: start[i] for i, v in enumerate(nodes)}, {v: finish[i] for i, v in enumerate(nodes)}, reserved,
+                 tuple(nodes[i] for i in placed))

@@ -17,6 +17,7 @@ class Trace:
     start: Dict[ExecNode, float]
     finish: Dict[ExecNode, float]
     reserved_allocations: Optional[Dict[ExecNode, Tuple[Allocation, ...]]] = None
+    dispatch_order: Optional[Tuple[ExecNode, ...]] = None   # nodes in the order the scheduler placed them
 
     def makespan(self) -> float:
         return max(self.finish.values())
@@ -66,4 +67,6 @@ class Trace:
 
     def ordered(self):
         """Nodes by (start, finish, id): the dispatch order a runtime should follow."""
+        if self.dispatch_order is not None:
+            return list(self.dispatch_order)
         return sorted(self.start, key=lambda n: (self.start[n], self.finish[n], n.id))
