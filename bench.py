@@ -241,6 +241,7 @@ def main() -> None:
                     "d2h_bytes_per_step": int(trainer.d2h_bytes), "gen_tokens_per_sec": stats_e2e[1] / (ms_e2e / 1e3)},
             "gpu_launches": int(launches), "clocks": clocks,
             "last_step": {k: round(v, 6) for k, v in outs_e2e[-1].items()},
+            "generation_counters": dict(getattr(trainer, "last_counters", {}) or {}),
             "published_other_hw": "reference paper data: 7B PPO on 8xA100-40GB, 1.73 samples/s (different config)",
         }
         print(json.dumps(line))

@@ -44,6 +44,20 @@ class _Base:
         self.weight_version = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self._marks: List = []
+
+    def _mark(self, name: str) -> None:
+        """Record a CUDA event that closes phase ``name``; the phase times are read after the step's sync."""
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._marks.append((name, ev))
+
+    def _phase_ms(self) -> Dict[str, float]:
+        out: Dict[str, float] = {}
+        for (_, a), (name, b) in zip(self._marks, self._marks[1:]):
+            out[f"{name}_ms"] = out.get(f"{name}_ms", 0.0) + a.elapsed_time(b)
+        self._marks = []
+        return out
 
     @property
     def world(self) -> int:
@@ -107,13 +121,16 @@ class GRPOTrainer(_Base):
         B, S = p_dev.shape
         N = B * self.K
         rep = p_dev.repeat_interleave(self.K, dim=0).contiguous()
+        self._mark("begin")
         gen = self.gen.generate(rep, self.max_new, temperature=self.algo.temperature,
                                 seed=self.seed + 100003 * self.iteration, forced_lens=forced_lens)
         resp_lens = gen.lengths.tolist()
+        self._mark("generate")
         ro = A.Rollout(rep, [S] * N, gen.tokens, resp_lens, gen.logprobs, gen.response_mask(),
                        weight_version=self.weight_version)
         if self.algo.kl_coef != 0.0:
             ro.ref_logp = A.sequence_logprobs(self.ref, ro, self.algo)
+        self._mark("reference")
         if rewards is None:
             raise ValueError("GRPOTrainer.step needs per-sample rewards (the reward model's output)")
         self.h2d_bytes += rewards.numel() * rewards.element_size()
@@ -122,11 +139,14 @@ class GRPOTrainer(_Base):
         denom = self._global_sum(ro.n_response_tokens())
         self.actor.zero_grad()
         m = A.policy_train_step(self.actor, ro, self.algo, denom_tokens=denom)
+        self._mark("train")
         self.opt.step()
+        self._mark("optimizer")
         self.weight_version += 1
         self.iteration += 1
         m["grad_norm"] = self.opt.grad_norm()
         out = self._read(m)
+        out.update(self._phase_ms())
         out.update(samples=float(N), gen_tokens=float(sum(resp_lens)), train_tokens=float(sum(ro.total_lens())),
                    wall_s=time.perf_counter() - t0)
         self.last_counters = dict(gen.counters)

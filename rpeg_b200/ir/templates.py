@@ -146,7 +146,7 @@ BUILDERS = {"ppo": build_PPO_RPEG, "grpo": build_GRPO_RPEG, "dpo": build_DPO_RPE
 
 
 def build_rpeg(algorithm: str, suite, workload, tau=None, verbose=False) -> RPEG:
-    try:
-        return BUILDERS[algorithm.lower()](suite, workload, tau, verbose)
-    except KeyError:
-        raise ValueError(f"unknown algorithm {algorithm!r}; expected one of {sorted(BUILDERS)}") from None
+    builder = BUILDERS.get(algorithm.lower())
+    if builder is None:
+        raise ValueError(f"unknown algorithm {algorithm!r}; expected one of {sorted(BUILDERS)}")
+    return builder(suite, workload, tau, verbose)

@@ -1,0 +1,149 @@
+"""Dependency-free drawings: Gantt charts of predicted schedules and runtime traces as SVG, and the
+algorithm / executable graphs as Graphviz dot text. One lane per GPU; operators are coloured by
+model, transfers are hatched grey. Reference: RPEG/utils/visualize.py (dot and Gantt writers) and
+RPEG/runtime/plot_trace.py (runtime trace renderer).
+"""
+from __future__ import annotations
+
+from html import escape
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+from ..core.types import DeviceSpace
+from ..passes.lower import ExecNodeType
+
+MODEL_COLOURS = {"Pi": "#4c78a8", "V": "#f58518", "Ref": "#54a24b", "R": "#b279a2", "AC": "#e45756",
+                 "actor": "#4c78a8", "critic": "#f58518", "reference": "#54a24b", "reward": "#b279a2", "ac_share": "#e45756"}
+ROLE_SHADE = {"GEN": 1.0, "INF": 0.75, "TRAIN": 0.55}
+TRANSFER_COLOUR = "#9d9d9d"
+
+
+def _shade(hex_colour: str, f: float) -> str:
+    r, g, b = (int(hex_colour[i:i + 2], 16) for i in (1, 3, 5))
+    mix = lambda c: int(255 - (255 - c) * f)
+    return f"#{mix(r):02x}{mix(g):02x}{mix(b):02x}"
+
+
+def gantt_svg(bars: Sequence[Tuple[str, float, float, str, str]], lanes: Sequence[str], path: str, *, title: str = "",
+              width: int = 1400, lane_h: int = 18) -> str:
+    """``bars``: (lane, start_s, finish_s, colour, label). Writes the SVG and returns its text."""
+    lane_index = {l: i for i, l in enumerate(lanes)}
+    t_end = max((b[2] for b in bars), default=1.0) or 1.0
+    left, top = 110, 34
+    h = top + lane_h * len(lanes) + 30
+    sx = (width - left - 20) / t_end
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{h}" font-family="monospace" font-size="10">',
+           f'<rect width="{width}" height="{h}" fill="white"/>',
+           f'<text x="{left}" y="16" font-size="13">{escape(title)} (makespan {t_end:.3f} s)</text>']
+    for l, i in lane_index.items():
+        y = top + i * lane_h
+        out.append(f'<text x="4" y="{y + lane_h - 5}">{escape(l)}</text>')
+        out.append(f'<line x1="{left}" y1="{y + lane_h}" x2="{width - 20}" y2="{y + lane_h}" stroke="#eee"/>')
+    for k in range(11):
+        x = left + (width - left - 20) * k / 10
+        out.append(f'<line x1="{x:.1f}" y1="{top}" x2="{x:.1f}" y2="{h - 26}" stroke="#ddd"/>')
+        out.append(f'<text x="{x - 14:.1f}" y="{h - 12}">{t_end * k / 10:.3g}s</text>')
+    for lane, s, f, colour, label in bars:
+        if lane not in lane_index:
+            continue
+        x, w = left + s * sx, max(0.6, (f - s) * sx)
+        y = top + lane_index[lane] * lane_h + 2
+        out.append(f'<rect x="{x:.2f}" y="{y}" width="{w:.2f}" height="{lane_h - 4}" fill="{colour}" stroke="#333" '
+                   f'stroke-width="0.3"><title>{escape(label)} [{s:.4f}, {f:.4f}] s</title></rect>')
+        if w > 7 * len(label) * 0.62:
+            out.append(f'<text x="{x + 2:.2f}" y="{y + lane_h - 8}" fill="white">{escape(label)}</text>')
+    out.append("</svg>")
+    text = "\n".join(out)
+    if path:
+        with open(path, "w") as fh:
+            fh.write(text)
+    return text
+
+
+def _lanes(space: DeviceSpace) -> List[str]:
+    return [f"gpu:{r}:{n}:{g}" for r in range(space.R) for n in range(space.N) for g in range(space.G)]
+
+
+def trace_to_gantt_svg(trace, path: str, space: DeviceSpace, title: str = "predicted schedule") -> str:
+    """Gantt chart of a scheduler ``Trace`` (planner prediction)."""
+    bars = []
+    for node, s in trace.start.items():
+        f = trace.finish[node]
+        if node.kind is ExecNodeType.OP:
+            model = node.model.value if node.model is not None else "Pi"
+            colour = _shade(MODEL_COLOURS.get(model, "#777777"), ROLE_SHADE.get(node.role.value if node.role else "INF", 0.8))
+            allocs = node.allocs
+        else:
+            colour = TRANSFER_COLOUR
+            allocs = trace.reserved_allocations[node] if trace.reserved_allocations is not None else node.allocs[-1:]
+        for a in allocs:
+            for r, n, g in a.coords():
+                bars.append((f"gpu:{r}:{n}:{g}", s, f, colour, node.id))
+    return gantt_svg(bars, _lanes(space), path, title=title)
+
+
+def runtime_trace_to_gantt_svg(events: Iterable[dict], path: str, space: Optional[DeviceSpace] = None,
+                               title: str = "runtime trace") -> str:
+    """Gantt chart of a JSONL runtime trace: pairs start/finish events per node and draws the bar on
+    every ``gpu:*`` resource the start event lists (or on the worker lane if it lists none)."""
+    starts: Dict[str, dict] = {}
+    bars, lanes_seen = [], []
+    t0 = None
+    for e in events:
+        if e.get("event") == "start":
+            starts[e["node_id"]] = e
+            t0 = e["timestamp"] if t0 is None else min(t0, e["timestamp"])
+        elif e.get("event") == "finish" and e.get("node_id") in starts:
+            s = starts.pop(e["node_id"])
+            c = s.get("counters") or {}
+            res = [r for r in c.get("resources", ()) if r.startswith("gpu:")] or [f"worker:{s.get('worker_id')}"]
+            kind = c.get("kind", "OP")
+            colour = TRANSFER_COLOUR if kind != "OP" else _shade(MODEL_COLOURS.get(c.get("model"), "#777777"),
+                                                                 ROLE_SHADE.get(c.get("role"), 0.8))
+            if e.get("status") != "ok":
+                colour = "#d62728"
+            for r in res:
+                if r not in lanes_seen:
+                    lanes_seen.append(r)
+                bars.append((r, s["timestamp"], e["timestamp"], colour, e["node_id"]))
+    t0 = t0 or 0.0
+    bars = [(l, s - t0, f - t0, c, n) for l, s, f, c, n in bars]
+    lanes = _lanes(space) if space is not None else sorted(lanes_seen)
+    lanes = lanes + [l for l in lanes_seen if l not in lanes]
+    return gantt_svg(bars, lanes, path, title=title)
+
+
+def rpeg_to_dot(rpeg, path: Optional[str] = None) -> str:
+    """The algorithm graph: operators as boxes coloured by model, edges labelled with containers."""
+    lines = ["digraph rpeg {", "  rankdir=LR; node [shape=box, style=filled, fontname=monospace];"]
+    for v in rpeg.vertices:
+        colour = MODEL_COLOURS.get(v.kind.model.value, "#cccccc")
+        lines.append(f'  "{v.id}" [label="{v.id}\\n{v.kind.role.value}", fillcolor="{colour}", fontcolor=white];')
+    for e in rpeg.edges:
+        style = "dashed" if e.kind.value != "Act" else "solid"
+        label = getattr(e, "label", None) or ",".join(sorted(c.name for c in getattr(e, "containers", ()) or ()))
+        lines.append(f'  "{e.src.id}" -> "{e.dst.id}" [label="{label}", style={style}];')
+    lines.append("}")
+    text = "\n".join(lines)
+    if path:
+        with open(path, "w") as fh:
+            fh.write(text)
+    return text
+
+
+def exec_to_dot(executable, path: Optional[str] = None) -> str:
+    """The lowered executable graph: operators as boxes, transfers as ellipses."""
+    lines = ["digraph exec {", "  rankdir=LR; node [fontname=monospace, fontsize=9];"]
+    for n in executable.nodes:
+        if n.kind is ExecNodeType.OP:
+            colour = MODEL_COLOURS.get(n.model.value if n.model else "", "#cccccc")
+            lines.append(f'  "{n.id}" [shape=box, style=filled, fillcolor="{colour}", fontcolor=white];')
+        else:
+            lines.append(f'  "{n.id}" [shape=ellipse, label="{n.kind.value}\\n{n.label or ""}"];')
+    for e in executable.edges:
+        lines.append(f'  "{e.src.id}" -> "{e.dst.id}";')
+    lines.append("}")
+    text = "\n".join(lines)
+    if path:
+        with open(path, "w") as fh:
+            fh.write(text)
+    return text
