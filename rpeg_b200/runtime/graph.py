@@ -81,6 +81,18 @@ class RuntimeGraph:
         return RuntimeGraph(nodes, tuple(i for i in self.topological_order if i in keep), self.composite_operators)
 
 
+def suffix_node_ids(graph: "RuntimeGraph", restored_step: int) -> Set[str]:
+    """Nodes that run after the state at the end of logical step ``restored_step`` was restored: every
+    node of a later step, plus the transfers that cross the boundary (a weight publication or an
+    activation hand-over that leaves a covered step and feeds a later one must be sent again)."""
+    keep = {nid for nid, n in graph.nodes.items() if n.logical_step is None or int(n.logical_step) > restored_step}
+    for nid in reversed(graph.topological_order):
+        n = graph.nodes[nid]
+        if nid not in keep and n.kind is not ExecNodeType.OP and any(s in keep for s in n.successors):
+            keep.add(nid)
+    return keep
+
+
 def gpu_keys(alloc: Allocation) -> Tuple[str, ...]:
     return tuple(f"gpu:{r}:{n}:{g}" for r, n, g in alloc.coords())
 

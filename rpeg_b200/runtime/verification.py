@@ -23,7 +23,7 @@ from typing import Any, Dict, Iterable, List, Optional, Sequence
 from ..passes.lower import ExecNodeType
 from .errors import RuntimeExecutionError
 from .executor import TRAINABLE_NAMES, model_name
-from .graph import RuntimeGraph
+from .graph import RuntimeGraph, suffix_node_ids
 from .weight_versions import consumer_weight_version, uses_shadow_copies
 
 LIFECYCLE_NODES = ("runtime.workers.start", "runtime.workers.initialize", "runtime.weights.publish_initial",
@@ -52,13 +52,21 @@ def verify_runtime_trace(compiled, graph: RuntimeGraph, events: Sequence[dict], 
     finishes: Dict[str, dict] = {}
     attempts = {"replay": 0, "recover": 0}
     failed: List[str] = []
+    restored_steps: List[int] = []
     for e in events:
         nid, ev = e.get("node_id"), e.get("event")
         if ev in attempts:
             attempts[ev] += 1
             if ev == "replay":
-                # a replay attempt restarts the bookkeeping of every node that has not finished successfully
+                # a failed attempt leaves starts without finishes behind
                 starts = {k: v for k, v in starts.items() if k in finishes}
+            else:
+                # nodes after the restored step run again in the next attempt: forget their first execution
+                restored = int((e.get("counters") or {}).get("restored_step", 0))
+                for k in suffix_node_ids(graph, restored):
+                    finishes.pop(k, None)
+                    starts.pop(k, None)
+                restored_steps.append(restored)
             continue
         if nid in LIFECYCLE_NODES:
             continue
@@ -157,7 +165,7 @@ def verify_runtime_trace(compiled, graph: RuntimeGraph, events: Sequence[dict], 
     if attempts["recover"] > attempts["replay"]:
         errors.append("more recover events than replay attempts")
     report = {"ok": not errors, "errors": errors, "warnings": warn, "nodes": len(graph.nodes), "verified_nodes": len(t0),
-              "replay_attempts": attempts["replay"], "recoveries": attempts["recover"], "failed_nodes": sorted(set(failed))}
+              "replay_attempts": attempts["replay"], "recoveries": attempts["recover"], "restored_steps": restored_steps, "failed_nodes": sorted(set(failed))}
     if errors and raise_on_error:
         raise RuntimeExecutionError("runtime trace verification failed: " + "; ".join(errors[:8]))
     return report

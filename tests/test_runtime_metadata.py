@@ -203,3 +203,123 @@ def test_executor_respects_resources_and_timeouts(tmp_path):
 
     with pytest.raises(RuntimeExecutionError, match="timeout"):
         execute(compiled, tmp_path, Stuck(compiled), name="stuck.jsonl", node_timeout_s=0.05)
+
+
+# ---------------------------------------------------------------------------------- run CLI, replay, metrics
+def test_run_cli_modes_and_exit_codes(tmp_path, capsys):
+    from rpeg_b200.runtime.run import main as run_main
+    run = spread_job(tmp_path, "grpo", steps=2)
+    assert run_main(["--config", str(run), "--dry-run"]) == 0
+    summary = json.loads(capsys.readouterr().out)
+    assert summary["algorithm"] == "grpo" and summary["runtime_graph"]["node_count"] > 0 and summary["workers"]
+    assert run_main(["--config", str(run), "--execute-graph-metadata"]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["verification"]["ok"] and out["alerts"] == "ok" and out["summary"]["logical_steps"] == 2
+    for f in ("metrics/summary.json", "metrics/metrics.prom", "metrics/alerts.json", "metrics/dashboard.html", "traces/run.jsonl"):
+        assert (tmp_path / f).exists(), f
+    prom = (tmp_path / "metrics/metrics.prom").read_text()
+    assert 'rpeg_runtime_nodes_finished{run_id="grpo-test"}' in prom
+    bad = load_mapping(run)
+    bad["device_space"]["gpus_per_node"] = 4
+    dump_mapping(bad, tmp_path / "bad.yaml")
+    assert run_main(["--config", str(tmp_path / "bad.yaml"), "--dry-run"]) == 2
+    assert "runtime error:" in capsys.readouterr().err
+    from rpeg_b200.runtime.plot_trace import main as plot_main
+    assert plot_main(["--trace", str(tmp_path / "traces/run.jsonl"), "--config", str(run), "--output", str(tmp_path / "g.svg")]) == 0
+    assert (tmp_path / "g.svg").read_text().startswith("<svg")
+
+
+def test_replay_restores_the_interval_checkpoint_and_runs_the_suffix(tmp_path):
+    from rpeg_b200.runtime import checkpoint as ckpt
+    from rpeg_b200.runtime.run import execute_compiled
+    run = spread_job(tmp_path, "grpo", steps=4, checkpoints={"interval_steps": 2},
+                     monitoring={"graph_replay_retries": 1, "test_inject_failure_after_checkpoint_step": 2,
+                                 "test_inject_failure_attempt": 0})
+    compiled = compile_runtime_plan(run)
+    res = execute_compiled(compiled, "metadata")
+    assert res["error"] is None and res["attempts"] == 2
+    rep = res["verification"]
+    assert rep["ok"] and rep["replay_attempts"] == 1 and rep["recoveries"] == 1 and rep["restored_steps"] == [2]
+    events = read_trace(tmp_path / "traces/run.jsonl")
+    rec = next(e for e in events if e["event"] == "recover")
+    assert rec["counters"]["restored_step"] == 2 and rec["counters"]["weight_versions"] == {"actor": 2}
+    # steps 1-2 ran once, steps 3-4 only in the second attempt; versions continue at 3
+    t_pi = [(e["step"], e["counters"]["produced_weight"]["version"]) for e in events
+            if e["event"] == "finish" and e["node_id"].startswith("t_pi@") and e["status"] == "ok"]
+    assert t_pi == [(1, 1), (2, 2), (3, 3), (4, 4)]
+    idx = ckpt.load_index(tmp_path / "checkpoints")
+    assert idx["latest_interval"] == "step_2" and idx["latest_final"] == "final"
+    assert ckpt.read_weight_versions(tmp_path / "checkpoints/final")["latest"] == {"actor": 4}
+    alerts = json.loads((tmp_path / "metrics/alerts.json").read_text())
+    assert alerts["schema_version"] == "rpeg.runtime_alerts.v1" and alerts["status"] == "critical"
+    assert any(a["rule"] == "max_replay_attempts" for a in alerts["alerts"])
+    # without retries the same injection is fatal
+    run2 = spread_job(tmp_path / "b", "grpo", steps=4, checkpoints={"interval_steps": 2},
+                      monitoring={"test_inject_failure_after_checkpoint_step": 2}) if (tmp_path / "b").mkdir() is None else None
+    res2 = execute_compiled(compile_runtime_plan(run2), "metadata")
+    assert res2["error"] and "injected failure" in res2["error"] and not res2["verification"]["ok"]
+
+
+def test_resume_from_checkpoint_runs_only_the_suffix(tmp_path):
+    from rpeg_b200.runtime.run import execute_compiled
+    (tmp_path / "a").mkdir()
+    first = spread_job(tmp_path / "a", "dpo", steps=2, checkpoints={"interval_steps": 1})
+    assert execute_compiled(compile_runtime_plan(first), "metadata")["error"] is None
+    (tmp_path / "b").mkdir()
+    second = spread_job(tmp_path / "b", "dpo", steps=2, checkpoints={"interval_steps": 1, "resume_from": str(tmp_path / "a/checkpoints")})
+    # the newest usable checkpoint of the first run is its final one (step 2): nothing is left to run but lifecycle nodes
+    res = execute_compiled(compile_runtime_plan(second), "metadata")
+    assert res["error"] is None and res["verification"]["ok"] and res["summary"]["nodes_finished"] == 0
+
+
+def test_checkpoint_flat_shards_reslice_across_dp_degrees(tmp_path):
+    import torch
+    from rpeg_b200.runtime import checkpoint as ckpt
+    full = torch.arange(1000, dtype=torch.float32)
+    w = torch.randn(7, 9).bfloat16()
+    for r in range(4):                                       # written by 4 ranks, 250 elements each
+        ckpt.save_flat_shards(tmp_path / "step_1/actor", r, 4, {"adam.m": full[r * 250:(r + 1) * 250], **({"weights": w} if r == 0 else {})},
+                              ranges={"adam.m": (r * 250, (r + 1) * 250, 1000)})
+    ckpt.finalize_worker_meta(tmp_path / "step_1/actor", 4)
+    ckpt.write_weight_versions(tmp_path / "step_1", step=1, latest={"actor": 1}, retained={"actor": [0, 1]}, tau={"actor": 1})
+    ckpt.register_checkpoint(tmp_path, name="step_1", kind="interval", step=1, workers=["actor"])
+    assert ckpt.verify_checkpoint(tmp_path / "step_1", ["actor"])["errors"] == []
+    for lo, hi in ((0, 334), (334, 667), (667, 1000)):       # read back by 3 ranks
+        assert torch.equal(ckpt.load_flat_range(tmp_path / "step_1/actor", "adam.m", lo, hi), full[lo:hi])
+    assert torch.equal(ckpt.load_tensor(tmp_path / "step_1/actor", "weights"), w)
+    assert ckpt.versions_needed_after(5, 2) == [3, 4, 5]
+    # a truncated shard makes the checkpoint unusable
+    f = tmp_path / "step_1/actor/rank2.bin"
+    f.write_bytes(f.read_bytes()[:-8])
+    assert ckpt.latest_usable_checkpoint(tmp_path) is None
+
+
+def test_metrics_alert_rules_and_fingerprints():
+    from rpeg_b200.runtime.metrics import compare_artifact_numeric_fingerprints, evaluate_alerts, prometheus_text, summarize_trace, tensor_fingerprint
+    import torch
+    ev = [
+        {"run_id": "r", "node_id": "g_pi@0", "event": "start", "status": "ok", "timestamp": 10.0, "step": 1,
+         "counters": {"kind": "OP", "role": "GEN", "model": "actor", "resources": ["gpu:0:0:0"]}},
+        {"run_id": "r", "node_id": "g_pi@0", "event": "finish", "status": "ok", "timestamp": 12.0, "step": 1,
+         "counters": {"duration_s": 2.0, "generated_tokens": 4000, "decode_steps": 100, "kv_pages_taken": 10, "kv_pages_returned": 9}},
+        {"run_id": "r", "node_id": "t_pi@0", "event": "start", "status": "ok", "timestamp": 12.0, "step": 1,
+         "counters": {"kind": "OP", "role": "TRAIN", "model": "actor"}},
+        {"run_id": "r", "node_id": "t_pi@0", "event": "finish", "status": "ok", "timestamp": 13.0, "step": 1,
+         "counters": {"duration_s": 1.0, "loss": float("nan"), "grad_norm": 2.5, "train_tokens": 8000,
+                      "produced_weight": {"model": "actor", "version": 1}}},
+    ]
+    s = summarize_trace(ev)
+    assert s["generation_tokens"] == 4000 and s["generation_tokens_per_s_node"] == 2000.0 and s["wall_time_s"] == 3.0
+    assert s["nonfinite_losses"] == 1 and s["latest_grad_norm"] == 2.5 and s["kv_pool_pages_outstanding"] == 1
+    a = evaluate_alerts(s, {"min_generation_tokens_per_s_wall": {"value": 5000, "severity": "warning"}})
+    rules = {x["rule"]: x["severity"] for x in a["alerts"]}
+    assert rules == {"max_nonfinite_losses": "critical", "max_kv_pool_pages_outstanding": "critical",
+                     "min_generation_tokens_per_s_wall": "warning"} and a["status"] == "critical"
+    assert 'rpeg_runtime_weight_versions_produced{run_id="r",key="actor"} 1' in prometheus_text(s)
+    x = torch.randn(100)
+    fa, fb = {"logp": tensor_fingerprint(x)}, {"logp": tensor_fingerprint(x + 1e-9)}
+    assert compare_artifact_numeric_fingerprints(fa, fb)["ok"]
+    assert not compare_artifact_numeric_fingerprints(fa, {"logp": tensor_fingerprint(x + 1e-2)})["ok"]
+    ia = {"tok": tensor_fingerprint(torch.arange(10))}
+    ib = {"tok": tensor_fingerprint(torch.arange(10) + (torch.arange(10) == 3))}
+    assert not compare_artifact_numeric_fingerprints(ia, ib)["ok"]
