@@ -111,6 +111,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="grpo_7b", choices=sorted(CONFIGS))
     ap.add_argument("--gen-slots", type=int, default=0)
+    ap.add_argument("--kv-gb", type=float, default=0.0, help="KV cache budget per GPU in GB (0 = pick by world size)")
     ap.add_argument("--micro-tokens", type=int, default=16384)
     ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"])
     args = ap.parse_args()
@@ -160,9 +161,12 @@ def main() -> None:
     gen_host = torch.Generator().manual_seed(42)
     n_iters = args.warmup + 2 * args.steps
     if spec["algo"] == "grpo":
-        slots = args.gen_slots or min(b_local * Kk, 32 if world == 1 else 64)
+        # KV pages are handed out on demand, so the slot count may exceed what the budget holds at full length.
+        # One rank keeps the whole fp32 Adam state (81 GB for 7B) and has ~56 GB for KV; sharded ranks have more.
+        slots = args.gen_slots or min(b_local * Kk, 96 if world == 1 else 128)
+        kv_gb = args.kv_gb or (56.0 if world == 1 else 90.0)
         trainer = GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp,
-                              gen_slots=slots, kv_budget_bytes=1e12, recompute=recompute, seed=42, eos_id=2)
+                              gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)
         batches = []
         for _ in range(n_iters):
             prompts = torch.randint(3, cfg.vocab, (B, S), generator=gen_host, dtype=torch.int32)
@@ -234,7 +238,7 @@ def main() -> None:
                        "global_batch": B * Kk if spec["algo"] == "grpo" else B, "prompts": B, "samples_per_prompt": Kk,
                        "seq_len": S + T, "prompt_len": S, "max_new_tokens": T, "gen_quantiles": spec["quantiles"],
                        "parallelism": f"dp{world}", "optimizer": "adamw fp32 master, sharded over dp",
-                       "recompute": recompute, "micro_tokens": args.micro_tokens,
+                       "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if spec["algo"] == "grpo" else None,
                        "l2": "working set (13.5 GB of weights per model) far exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": stats_e2e[0] / (ms_e2e / 1e3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "wall_s_per_step": wall_e2e / args.steps, "h2d_bytes_per_step": int(trainer.h2d_bytes),

@@ -6,8 +6,8 @@
 // their pages back to the allocator, so no compaction copy is ever needed.
 //
 // Decode attention is bandwidth bound (one query row per head): each CTA owns (head, sequence,
-// split), its 4 warps stride over 32-key blocks with one key per lane for QK^T and 4 output
-// columns per lane for PV, keeping an online-softmax state per warp that is merged in shared memory.
+// split), its 4 warps stride over 32-key blocks, 16 lanes per key row so every load is a coalesced
+// 256-byte line, keeping an online-softmax state per warp that is merged in shared memory.
 // With nsplit > 1 the partial (m, l, o) of every split goes to a scratch buffer and a second
 // kernel merges them.
 //
@@ -43,79 +43,192 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, 
   reinterpret_cast<uint4*>(vcache + dst)[j] = reinterpret_cast<const uint4*>(row + v_col0 + h * HD)[j];
 }
 
-struct WarpState {
-  float m, l;
-  float acc[4];
-};
+// One launch for what decode does to a fresh qkv row: rotate the query heads in place, rotate the
+// key heads (in place and into the cache) and copy the value heads into the cache. One warp per
+// (token, head) job; jobs [0, H) are query heads, [H, H+Hkv) key heads, [H+Hkv, H+2Hkv) value heads.
+// Rotate-half pairing: lane i rotates pairs (2i, 2i+1) with their partners at +hd/2 (hd = 128).
+__global__ void __launch_bounds__(256)
+rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, int ld, int q_col0, int k_col0, int v_col0,
+                      const int* __restrict__ seq_id, const int* __restrict__ pos,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                      const int* __restrict__ page_table, int max_pages, __nv_bfloat16* __restrict__ kcache,
+                      __nv_bfloat16* __restrict__ vcache, int T, int H, int Hkv) {
+  const int jobs = H + 2 * Hkv;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (wid >= static_cast<long long>(T) * jobs) return;
+  const int lane = threadIdx.x & 31;
+  const int t = static_cast<int>(wid / jobs), job = static_cast<int>(wid % jobs);
+  const int p = pos[t];
+  __nv_bfloat16* row = qkv + static_cast<size_t>(t) * ld;
+  size_t dst = 0;
+  if (job >= H) {
+    const int page = page_table[static_cast<size_t>(seq_id[t]) * max_pages + p / PAGE];
+    const int hk = (job - H) % Hkv;
+    dst = ((static_cast<size_t>(page) * Hkv + hk) * PAGE + (p % PAGE)) * HD;
+  }
+  if (job >= H + Hkv) {                      // value head: plain copy
+    if (lane < 16)
+      reinterpret_cast<uint4*>(vcache + dst)[lane] = reinterpret_cast<const uint4*>(row + v_col0 + (job - H - Hkv) * HD)[lane];
+    return;
+  }
+  __nv_bfloat16* base = row + (job < H ? q_col0 + job * HD : k_col0 + (job - H) * HD);
+  constexpr int half = HD / 2;
+  const int i = lane * 2;
+  const float2 c = *reinterpret_cast<const float2*>(cos_t + static_cast<size_t>(p) * half + i);
+  const float2 s = *reinterpret_cast<const float2*>(sin_t + static_cast<size_t>(p) * half + i);
+  const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(base + i));
+  const float2 b = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(base + i + half));
+  const uint32_t lo = pack_bf16x2(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y);
+  const uint32_t hi = pack_bf16x2(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y);
+  *reinterpret_cast<uint32_t*>(base + i) = lo;
+  *reinterpret_cast<uint32_t*>(base + i + half) = hi;
+  if (job >= H) {
+    *reinterpret_cast<uint32_t*>(kcache + dst + i) = lo;
+    *reinterpret_cast<uint32_t*>(kcache + dst + i + half) = hi;
+  }
+}
+
+// 16 per-lane partial dot products (one per key of a half block) -> the full dot product of key
+// `lane & 15` in every lane of a 16-lane group: at each level half of the values go to the partner.
+__device__ __forceinline__ float transpose_reduce16(float (&v)[16], int lane) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const bool up = lane & 8;
+    const float send = up ? v[i] : v[i + 8];
+    const float keep = up ? v[i + 8] : v[i];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool up = lane & 4;
+    const float send = up ? v[i] : v[i + 4];
+    const float keep = up ? v[i + 4] : v[i];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const bool up = lane & 2;
+    const float send = up ? v[i] : v[i + 2];
+    const float keep = up ? v[i + 2] : v[i];
+    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+  }
+  const bool up = lane & 1;
+  const float send = up ? v[0] : v[1];
+  const float keep = up ? v[1] : v[0];
+  return keep + __shfl_xor_sync(0xffffffffu, send, 1);
+}
+
+__device__ __forceinline__ float dot8(const uint4& kv, const float (&q)[8]) {
+  const float2 a = unpack_bf16x2(kv.x), b = unpack_bf16x2(kv.y), c = unpack_bf16x2(kv.z), d = unpack_bf16x2(kv.w);
+  return a.x * q[0] + a.y * q[1] + b.x * q[2] + b.y * q[3] + c.x * q[4] + c.y * q[5] + d.x * q[6] + d.y * q[7];
+}
+
+__device__ __forceinline__ void axpy8(float (&acc)[8], float p, const uint4& vv) {
+  const float2 a = unpack_bf16x2(vv.x), b = unpack_bf16x2(vv.y), c = unpack_bf16x2(vv.z), d = unpack_bf16x2(vv.w);
+  acc[0] += p * a.x; acc[1] += p * a.y; acc[2] += p * b.x; acc[3] += p * b.y;
+  acc[4] += p * c.x; acc[5] += p * c.y; acc[6] += p * d.x; acc[7] += p * d.y;
+}
 
 // q: [B, ldq] with head h at column q_col0 + h*HD. out: [B, H*HD] bf16.
 // partial (when nsplit > 1): [B, H, nsplit, HD + 2] fp32 = {o[HD], m, l}.
+//
+// Work split inside a warp: the 32 lanes form two groups of 16; a group reads one 256-byte K (or
+// V) row per load instruction, lane c of the group owning the 16-byte chunk c (head dims 8c..8c+7),
+// so every global load is fully coalesced and a lane keeps 8 independent 16-byte loads in flight.
+// Group g takes keys g*16..g*16+15 of a 32-key block; the 16 partial dot products of a lane are
+// summed across the group by a transposing butterfly that leaves the score of key `lane` in lane
+// `lane`, which is the layout the online softmax wants. For PV each lane accumulates its 8 head
+// dims over the group's keys; the two groups are added at the end.
 __global__ void __launch_bounds__(128)
 paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col0,
                          const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
                          const int* __restrict__ page_table, int max_pages, const int* __restrict__ seq_lens,
                          __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int H, int Hkv,
                          int nsplit, float scale_log2) {
-  __shared__ __align__(16) float q_sm[HD];
   __shared__ float red_m[4], red_l[4];
   __shared__ __align__(16) float red_o[4][HD];
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int hk = h / (H / Hkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 4, c = lane & 15;
   const int L = seq_lens[b];
-  // split boundaries in units of 32-key blocks
-  const int nblk = (L + 31) / 32;
+  const int nblk = (L + 31) / 32;                  // 32-key blocks
   const int blk_per_split = (nblk + nsplit - 1) / nsplit;
   const int blk0 = split * blk_per_split;
   const int blk1 = min(nblk, blk0 + blk_per_split);
 
-  if (threadIdx.x < HD)
-    q_sm[threadIdx.x] = __bfloat162float(q[static_cast<size_t>(b) * ldq + q_col0 + h * HD + threadIdx.x]) * scale_log2;
-  __syncthreads();
+  float qr[8];
+  {
+    const uint4 qv = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(b) * ldq + q_col0 + h * HD + c * 8);
+    const float2 a = unpack_bf16x2(qv.x), bb = unpack_bf16x2(qv.y), cc = unpack_bf16x2(qv.z), d = unpack_bf16x2(qv.w);
+    qr[0] = a.x * scale_log2; qr[1] = a.y * scale_log2; qr[2] = bb.x * scale_log2; qr[3] = bb.y * scale_log2;
+    qr[4] = cc.x * scale_log2; qr[5] = cc.y * scale_log2; qr[6] = d.x * scale_log2; qr[7] = d.y * scale_log2;
+  }
 
   float m = -INFINITY, l = 0.f;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
   const int* pt = page_table + static_cast<size_t>(b) * max_pages;
   for (int blk = blk0 + warp; blk < blk1; blk += 4) {
-    const int key = blk * 32 + lane;
     const int page = pt[(blk * 32) / PAGE];
-    const size_t base = ((static_cast<size_t>(page) * Hkv + hk) * PAGE + ((blk * 32) % PAGE)) * HD;
-    float s = -INFINITY;
-    if (key < L) {
-      const uint4* kr = reinterpret_cast<const uint4*>(kcache + base + static_cast<size_t>(lane) * HD);
-      float d = 0.f;
+    // first row of this group's 16 keys, this lane's 16-byte chunk
+    const size_t base = ((static_cast<size_t>(page) * Hkv + hk) * PAGE + ((blk * 32) % PAGE) + grp * 16) * HD + c * 8;
+    const int nk = min(32, L - blk * 32) - grp * 16;   // valid keys of this group (may be <= 0)
+    const uint4* kp = reinterpret_cast<const uint4*>(kcache + base);
+    const uint4* vp = reinterpret_cast<const uint4*>(vcache + base);
+    float part[16];
+    if (nk >= 16) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint4 kv = kr[i];
-        const uint32_t* pk = reinterpret_cast<const uint32_t*>(&kv);
-        const float4 q0 = *reinterpret_cast<const float4*>(&q_sm[i * 8]);
-        const float4 q1 = *reinterpret_cast<const float4*>(&q_sm[i * 8 + 4]);
-        const float2 a = unpack_bf16x2(pk[0]), bb = unpack_bf16x2(pk[1]), c = unpack_bf16x2(pk[2]),
-                     e = unpack_bf16x2(pk[3]);
-        d += a.x * q0.x + a.y * q0.y + bb.x * q0.z + bb.y * q0.w + c.x * q1.x + c.y * q1.y + e.x * q1.z + e.y * q1.w;
+      for (int half = 0; half < 2; ++half) {
+        uint4 kv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) kv[j] = kp[(half * 8 + j) * (HD / 8)];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) part[half * 8 + j] = dot8(kv[j], qr);
       }
-      s = d;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        part[j] = 0.f;
+        if (j < nk) part[j] = dot8(kp[j * (HD / 8)], qr);
+      }
     }
+    float s = transpose_reduce16(part, lane);       // score of key (blk*32 + lane)
+    if (c >= nk) s = -INFINITY;
     const float bm = warp_max(s);
     const float nm = fmaxf(m, bm);
-    const float alpha = exp2f(m - nm);  // m = -inf on the first block gives 0
-    const float p = (key < L) ? exp2f(s - nm) : 0.f;
+    const float alpha = exp2f(m - nm);              // m = -inf on the first block gives 0
+    const float p = (c < nk) ? exp2f(s - nm) : 0.f;
     l = l * alpha + warp_sum(p);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) acc[k] *= alpha;
+    for (int k = 0; k < 8; ++k) acc[k] *= alpha;
     m = nm;
-    const int nk = min(32, L - blk * 32);
-    const __nv_bfloat16* vb = vcache + base + lane * 4;
-    for (int j = 0; j < nk; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, p, j);
-      const uint2 vv = *reinterpret_cast<const uint2*>(vb + static_cast<size_t>(j) * HD);
-      const float2 v0 = unpack_bf16x2(vv.x), v1 = unpack_bf16x2(vv.y);
-      acc[0] += pj * v0.x; acc[1] += pj * v0.y; acc[2] += pj * v1.x; acc[3] += pj * v1.y;
+    if (nk >= 16) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint4 vv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vv[j] = vp[(half * 8 + j) * (HD / 8)];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) axpy8(acc, __shfl_sync(0xffffffffu, p, grp * 16 + half * 8 + j), vv[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, grp * 16 + j);
+        if (j < nk) axpy8(acc, pj, vp[j * (HD / 8)]);
+      }
     }
   }
-  // merge the 4 warps
+  // add the two key groups, then merge the 4 warps
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], 16);
   if (lane == 0) { red_m[warp] = m; red_l[warp] = l; }
-  *reinterpret_cast<float4*>(&red_o[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  if (grp == 0) {
+    *reinterpret_cast<float4*>(&red_o[warp][c * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(&red_o[warp][c * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
   __syncthreads();
   if (threadIdx.x < HD) {
     float gm = fmaxf(fmaxf(red_m[0], red_m[1]), fmaxf(red_m[2], red_m[3]));
@@ -168,6 +281,19 @@ extern "C" int rpeg_kv_append(const void* qkv, int ld, int k_col0, int v_col0, c
   kv_append_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
       static_cast<const __nv_bfloat16*>(qkv), ld, k_col0, v_col0, seq_id, pos, page_table, max_pages,
       static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache), T, Hkv);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_rope_kv_append(void* qkv, int ld, int q_col0, int k_col0, int v_col0, const int* seq_id, const int* pos,
+                                   const float* cos_t, const float* sin_t, const int* page_table, int max_pages,
+                                   void* kcache, void* vcache, int T, int H, int Hkv, int hd, void* stream) {
+  if (hd != HD) return -2;
+  if ((ld | q_col0 | k_col0 | v_col0) & 7) return -3;
+  const long long threads = static_cast<long long>(T) * (H + 2 * Hkv) * 32;
+  if (threads <= 0) return 0;
+  rope_kv_append_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, STREAM(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), ld, q_col0, k_col0, v_col0, seq_id, pos, cos_t, sin_t, page_table, max_pages,
+      static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache), T, H, Hkv);
   return LAUNCH_OK();
 }
 

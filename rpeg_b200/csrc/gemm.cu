@@ -347,10 +347,23 @@ extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int 
     if (bn_hint == 0) bn = N >= 256 ? 256 : (N >= 128 ? 128 : (N >= 64 ? 64 : 32));
     const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
     const int num_kb = (K + BK - 1) / BK;
-    int want = g_num_sms / tiles;
-    if (want > num_kb / 4) want = num_kb / 4;
+    // Pick the split count by a small cost model in units of "K blocks streamed by one CTA":
+    // waves * blocks per item (+2 per wave for pipeline fill and drain) + the fp32 partial traffic
+    // (written by the GEMM, read by the reduction) spread over all SMs.
     const long long per_split = static_cast<long long>(M) * N;
-    if (want > 1 && per_split > 0 && workspace_elems / per_split < want) want = static_cast<int>(workspace_elems / per_split);
+    const double block_bytes = static_cast<double>(g_num_sms) * BK * (bn + BM) * 2.0;
+    int want = 1;
+    double best = 1e30;
+    const int max_s = num_kb / 2 > 32 ? 32 : num_kb / 2;
+    for (int sp = 1; sp <= (max_s < 1 ? 1 : max_s); ++sp) {
+      const int kb_per = (num_kb + sp - 1) / sp;
+      const int real = (num_kb + kb_per - 1) / kb_per;
+      if (real != sp) continue;
+      if (sp > 1 && per_split > 0 && workspace_elems / per_split < sp) break;
+      const int waves = (tiles * sp + g_num_sms - 1) / g_num_sms;
+      const double cost = waves * (kb_per + 2.0) + (sp > 1 ? sp * per_split * 8.0 / block_bytes : 0.0);
+      if (cost < best - 1e-9) { best = cost; want = sp; }
+    }
     if (want > 1) {
       const int kb_per = (num_kb + want - 1) / want;
       k_splits = (num_kb + kb_per - 1) / kb_per;

@@ -137,6 +137,80 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(&dw[i], dw_sm[i]);
 }
 
+// Row-per-CTA variant: 256 threads keep the whole row in registers (NV 16-byte vectors per thread),
+// so x and res are read once and nothing is re-read for the second pass. Used for d <= 8192.
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
+                       __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int d, float eps) {
+  __shared__ float warp_ss[8];
+  const int row = blockIdx.x;
+  const int nvec = d >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * d);
+  const uint4* rr = res ? reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * d) : nullptr;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 v[NV], wv[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * 256;
+    v[k] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < nvec) { v[k] = xr[i]; wv[k] = wr[i]; }
+  }
+  if (rr) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < nvec) {
+        const uint4 r = rr[i];
+        const uint32_t* pr = reinterpret_cast<const uint32_t*>(&r);
+        uint32_t* pv = reinterpret_cast<uint32_t*>(&v[k]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 a = unpack_bf16x2(pv[e]), b = unpack_bf16x2(pr[e]);
+          pv[e] = pack_bf16x2(a.x + b.x, a.y + b.y);
+        }
+        if (h_out) reinterpret_cast<uint4*>(h_out + static_cast<size_t>(row) * d)[i] = v[k];
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const uint32_t* pv = reinterpret_cast<const uint32_t*>(&v[k]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = unpack_bf16x2(pv[e]);
+      ss += a.x * a.x + a.y * a.y;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) warp_ss[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += warp_ss[k];
+  const float rstd = rsqrtf(tot / static_cast<float>(d) + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * d);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < nvec) {
+      const uint32_t* pv = reinterpret_cast<const uint32_t*>(&v[k]);
+      const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv[k]);
+      uint4 o;
+      uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = unpack_bf16x2(pv[e]), b = unpack_bf16x2(pw[e]);
+        po[e] = pack_bf16x2(a.x * rstd * b.x, a.y * rstd * b.y);
+      }
+      yr[i] = o;
+    }
+  }
+}
+
 // RoPE, rotate-half pairing (i, i + hd/2), applied in place to `nheads` heads of width hd that sit
 // at column offset `col0` of a [T, ld] bf16 buffer. cos/sin tables are fp32 [max_pos, hd/2].
 // sign = +1 forward, -1 backward (the transpose of a rotation is the rotation by -angle).
@@ -264,10 +338,17 @@ extern "C" int rpeg_rmsnorm_fwd(const void* x, const void* res, const void* w, v
                                 float* rstd, int T, int d, float eps, void* stream) {
   if (d & 7) return -2;
   if (T <= 0) return 0;
-  rmsnorm_fwd_kernel<<<(T + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, STREAM(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
-      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(h_out), static_cast<__nv_bfloat16*>(y),
-      rstd, T, d, eps);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* rp = static_cast<const __nv_bfloat16*>(res);
+  const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16* hp = static_cast<__nv_bfloat16*>(h_out);
+  __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+  const int nv = ((d >> 3) + 255) / 256;
+  if (nv == 1) rmsnorm_fwd_row_kernel<1><<<T, 256, 0, STREAM(stream)>>>(xp, rp, wp, hp, yp, rstd, d, eps);
+  else if (nv == 2) rmsnorm_fwd_row_kernel<2><<<T, 256, 0, STREAM(stream)>>>(xp, rp, wp, hp, yp, rstd, d, eps);
+  else if (nv <= 4) rmsnorm_fwd_row_kernel<4><<<T, 256, 0, STREAM(stream)>>>(xp, rp, wp, hp, yp, rstd, d, eps);
+  else
+    rmsnorm_fwd_kernel<<<(T + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, STREAM(stream)>>>(xp, rp, wp, hp, yp, rstd, T, d, eps);
   return LAUNCH_OK();
 }
 

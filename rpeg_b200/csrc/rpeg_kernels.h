@@ -73,6 +73,9 @@ int rpeg_copy16(const void* src, void* dst, long long nbytes, void* stream);
 int rpeg_kv_append(const void* qkv, int ld, int k_col0, int v_col0, const int* seq_id, const int* pos,
                    const int* page_table, int max_pages, void* kcache, void* vcache, int T, int Hkv, int hd,
                    void* stream);
+int rpeg_rope_kv_append(void* qkv, int ld, int q_col0, int k_col0, int v_col0, const int* seq_id, const int* pos,
+                        const float* cos_t, const float* sin_t, const int* page_table, int max_pages, void* kcache,
+                        void* vcache, int T, int H, int Hkv, int hd, void* stream);
 long long rpeg_decode_attn_scratch_bytes(int B, int H, int nsplit);
 int rpeg_paged_decode_attn(const void* q, int ldq, int q_col0, const void* kcache, const void* vcache,
                            const int* page_table, int max_pages, const int* seq_lens, void* out, float* scratch,

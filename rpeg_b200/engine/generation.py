@@ -67,7 +67,7 @@ class GenerationResult:
 
 
 class Generator:
-    BUCKETS = (256, 128, 64, 32, 16, 8)
+    BUCKETS = (256, 192, 128, 96, 64, 48, 32, 24, 16, 8)
 
     @staticmethod
     def kv_bytes_for(cfg, slots: int, max_seq_len: int) -> int:
@@ -90,10 +90,12 @@ class Generator:
         page_bytes = 2 * cfg.n_layers * cfg.n_kv_heads * PAGE * cfg.head_dim * 2
         if kv_storage is not None:
             kv_budget_bytes = kv_storage.numel() * 2
-        num_pages = int(kv_budget_bytes // page_bytes)
-        max_rows = max(1, (num_pages - 1) // self.pages_per_row)
-        self.max_slots = max(b for b in (*self.BUCKETS, 4, 2, 1) if b <= max(1, min(max_slots, max_rows)))
-        num_pages = self.max_slots * self.pages_per_row + 1
+        num_pages = min(int(kv_budget_bytes // page_bytes), max(1, max_slots) * self.pages_per_row + 1)
+        if num_pages - 1 < self.pages_per_row:
+            raise ValueError(f"KV budget holds {num_pages - 1} pages but one row of {max_seq_len} tokens needs {self.pages_per_row}")
+        # Pages are handed out as rows grow, so the slot count is not tied to the worst-case length;
+        # a row that cannot grow because the pool ran dry is preempted and generated again later.
+        self.max_slots = max(b for b in (*self.BUCKETS, 4, 2, 1) if b <= max(1, min(max_slots, num_pages - 1)))
         self.pool = PagePool(num_pages)
         shape = (num_pages, cfg.n_kv_heads, PAGE, cfg.head_dim)
         per = math.prod(shape)
@@ -227,12 +229,28 @@ class Generator:
         res_len = torch.zeros(N, dtype=torch.int32, device=dev)
         for t in (self.active, self.seq_len, self.gen_count, self.n_finished, self.page_table, self.forced_len):
             t.zero_()
+        self.pool = PagePool(self.pool.num_pages)      # a call that raised half way must not leak pages
         slot_row = [-1] * n
         slot_pages: List[List[int]] = [[] for _ in range(n)]
+        slot_bound = [0] * n       # upper bound on the tokens a slot holds (prompt + decode steps run since admission)
+        slot_prompt = [0] * n
         queue = list(range(N))
         retired = 0
-        counters = dict(prefill_calls=0, decode_steps=0, prefill_tokens=0, compactions=0, host_syncs=0)
+        counters = dict(prefill_calls=0, decode_steps=0, prefill_tokens=0, compactions=0, host_syncs=0, kv_pages_taken=0,
+                        kv_pages_returned=0, kv_preemptions=0, live_slots_peak=0, graph_replays=0)
         seen_finished = 0
+        horizon = self.sync_interval
+        watermark = max(1, self.pool.num_pages // 20)     # pages kept free at admission so live rows can grow
+
+        def pages_for(tokens: int) -> int:
+            return min(self.pages_per_row, (tokens + PAGE - 1) // PAGE)
+
+        def release(slots_gone: List[int]) -> None:
+            for s in slots_gone:
+                counters["kv_pages_returned"] += len(slot_pages[s])
+                self.pool.give(slot_pages[s])
+                slot_pages[s] = []
+                slot_row[s] = -1
 
         def retire(slots_done: List[int]) -> None:
             nonlocal retired
@@ -246,41 +264,96 @@ class Generator:
             self.out_tok[s_idx] = self.pad_id
             self.out_lp[s_idx] = 0
             self.page_table[s_idx] = 0
-            for s in slots_done:
-                self.pool.give(slot_pages[s])
-                slot_pages[s] = []
-                slot_row[s] = -1
+            release(slots_done)
             retired += len(slots_done)
+
+        def preempt(victims: List[int]) -> None:
+            """Give a row's pages back and queue it again from its prompt (its partial output is dropped)."""
+            s_idx = torch.tensor(victims, dtype=torch.long, device=dev)
+            for arr in (self.active, self.seq_len, self.gen_count, self.forced_len, self.page_table, self.out_lp):
+                arr[s_idx] = 0
+            self.out_tok[s_idx] = self.pad_id
+            for s in victims:
+                queue.insert(0, slot_row[s])
+            release(victims)
+            counters["kv_preemptions"] += len(victims)
+
+        def grow(live: List[int]) -> List[int]:
+            """Extend every live row's page list to cover the next ``horizon`` decode steps; preempts
+            the rows with the least progress when the pool cannot cover it. Returns the rows still live."""
+            live = list(live)
+            while True:
+                want = {s: pages_for(slot_bound[s] + horizon) - len(slot_pages[s]) for s in live}
+                total = sum(v for v in want.values() if v > 0)
+                if total <= self.pool.available() or len(live) <= 1:
+                    break
+                victim = min(live, key=lambda s: (slot_bound[s] - slot_prompt[s], -s))
+                preempt([victim])
+                live.remove(victim)
+            idx, val = [], []
+            for s in live:
+                k = want[s]
+                if k > 0:
+                    have = len(slot_pages[s])
+                    new = self.pool.take(k)
+                    counters["kv_pages_taken"] += k
+                    slot_pages[s].extend(new)
+                    idx.extend(s * self.pages_per_row + have + j for j in range(k))
+                    val.extend(new)
+            if idx:
+                self.page_table.view(-1).index_copy_(0, torch.tensor(idx, dtype=torch.long, device=dev),
+                                                     torch.tensor(val, dtype=torch.int32, device=dev))
+            return live
 
         while retired < N:
             free = [s for s in range(n) if slot_row[s] < 0]
-            if queue and free:
-                take = min(len(free), len(queue))
-                new_rows, new_slots = queue[:take], free[:take]
-                del queue[:take]
-                table = torch.zeros((take, self.pages_per_row), dtype=torch.int32)
-                for j, (r, s) in enumerate(zip(new_rows, new_slots)):
-                    need = (int(rows[r].numel()) + max_new + PAGE - 1) // PAGE
-                    pages = self.pool.take(need)
-                    slot_pages[s], slot_row[s] = pages, r
-                    table[j, :need] = torch.tensor(pages, dtype=torch.int32)
-                self.page_table[torch.tensor(new_slots, dtype=torch.long, device=dev)] = table.to(dev)
-                self._prefill([rows[r] for r in new_rows], new_slots, None if forced is None else [forced[r] for r in new_rows],
-                              temperature, greedy, seed, max_new)
-                counters["prefill_calls"] += 1
-                counters["prefill_tokens"] += sum(int(rows[r].numel()) for r in new_rows)
+            # admit in batches: a prefill call stalls decoding, so wait until several slots are free
+            if queue and len(free) >= min(len(queue), max(1, n // 8)):
+                new_rows, new_slots = [], []
+                budget = self.pool.available() - (watermark if any(r >= 0 for r in slot_row) else 0)
+                for s in free:
+                    if not queue:
+                        break
+                    need = pages_for(int(rows[queue[0]].numel()) + 1 + horizon)
+                    if need > budget:
+                        break
+                    budget -= need
+                    new_rows.append(queue.pop(0))
+                    new_slots.append(s)
+                if new_rows:
+                    table = torch.zeros((len(new_rows), self.pages_per_row), dtype=torch.int32)
+                    for j, (r, s) in enumerate(zip(new_rows, new_slots)):
+                        plen = int(rows[r].numel())
+                        need = pages_for(plen + 1 + horizon)
+                        pages = self.pool.take(need)
+                        counters["kv_pages_taken"] += need
+                        slot_pages[s], slot_row[s], slot_prompt[s], slot_bound[s] = pages, r, plen, plen + 1
+                        table[j, :need] = torch.tensor(pages, dtype=torch.int32)
+                    self.page_table[torch.tensor(new_slots, dtype=torch.long, device=dev)] = table.to(dev)
+                    self._prefill([rows[r] for r in new_rows], new_slots, None if forced is None else [forced[r] for r in new_rows],
+                                  temperature, greedy, seed, max_new)
+                    counters["prefill_calls"] += 1
+                    counters["prefill_tokens"] += sum(int(rows[r].numel()) for r in new_rows)
             live = [s for s in range(n) if slot_row[s] >= 0]
-            used = max(live) + 1 if live else 0
-            if not queue and live and len(live) <= self._bucket(used) // 2 and self._bucket(len(live)) < self._bucket(used):
-                self._compact(live, slot_row, slot_pages)
+            if not live:
+                if queue:
+                    raise RuntimeError("KV page pool cannot hold a single prompt; raise the KV budget")
+                break
+            used = max(live) + 1
+            if not queue and len(live) <= self._bucket(used) // 2 and self._bucket(len(live)) < self._bucket(used):
+                self._compact(live, slot_row, slot_pages, slot_bound, slot_prompt)
                 counters["compactions"] += 1
                 live = list(range(len(live)))
-                used = len(live)
-            if used:
-                b = self._bucket(used)
-                for _ in range(self.sync_interval):
-                    self._step(b, temperature, greedy, seed)
-                counters["decode_steps"] += self.sync_interval
+            live = grow(live)
+            used = max(live) + 1
+            counters["live_slots_peak"] = max(counters["live_slots_peak"], len(live))
+            b = self._bucket(used)
+            for _ in range(horizon):
+                self._step(b, temperature, greedy, seed)
+            counters["decode_steps"] += horizon
+            counters["graph_replays"] += horizon if self.use_graphs else 0
+            for s in live:
+                slot_bound[s] = min(slot_bound[s] + horizon, slot_prompt[s] + max_new)
             nf = int(self.n_finished.item())
             counters["host_syncs"] += 1
             if nf != seen_finished:
@@ -296,7 +369,8 @@ class Generator:
                 return b
         return self.max_slots
 
-    def _compact(self, live: List[int], slot_row: List[int], slot_pages: List[List[int]]) -> None:
+    def _compact(self, live: List[int], slot_row: List[int], slot_pages: List[List[int]], slot_bound: List[int],
+                 slot_prompt: List[int]) -> None:
         """Move live slots to the front (state and page-table rows only; KV pages stay where they are)."""
         k = len(live)
         idx = torch.tensor(live, dtype=torch.long, device=self.dev)
@@ -310,6 +384,10 @@ class Generator:
                 arr[k:] = 0
         rows = [slot_row[s] for s in live]
         pages = [slot_pages[s] for s in live]
+        bounds = [slot_bound[s] for s in live]
+        prompts = [slot_prompt[s] for s in live]
         for s in range(len(slot_row)):
             slot_row[s] = rows[s] if s < k else -1
             slot_pages[s] = pages[s] if s < k else []
+            slot_bound[s] = bounds[s] if s < k else 0
+            slot_prompt[s] = prompts[s] if s < k else 0

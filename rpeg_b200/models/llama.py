@@ -179,7 +179,7 @@ class LlamaModel:
 
     def _workspace(self) -> torch.Tensor:
         if self._ws is None:
-            self._ws = torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=self.device)
+            self._ws = torch.empty(32 * 1024 * 1024, dtype=torch.float32, device=self.device)
         return self._ws
 
     def _lin(self, x: torch.Tensor, w: torch.Tensor, decode: bool = False) -> torch.Tensor:
@@ -351,10 +351,8 @@ class LlamaModel:
             else:
                 x, _, h = K.rmsnorm_fwd(delta, p[f"l{i}.attn_norm"], cfg.rms_eps, residual=res, want_sum=True)
             qkv = K.gemm(x, p[f"l{i}.wqkv"], workspace=ws)
-            K.rope_(qkv, pos, self.cos_t, self.sin_t, 0, cfg.n_heads, cfg.head_dim)
-            K.rope_(qkv, pos, self.cos_t, self.sin_t, cfg.q_width, cfg.n_kv_heads, cfg.head_dim)
-            K.kv_append(qkv, cfg.q_width, cfg.q_width + cfg.kv_width, slot_ids, pos, page_table, kcache[i], vcache[i],
-                        cfg.n_kv_heads, cfg.head_dim)
+            K.rope_kv_append_(qkv, 0, cfg.q_width, cfg.q_width + cfg.kv_width, slot_ids, pos, self.cos_t, self.sin_t,
+                              page_table, kcache[i], vcache[i], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
             attn = K.paged_decode_attn(qkv, 0, kcache[i], vcache[i], page_table, seq_len, cfg.n_heads, cfg.n_kv_heads,
                                        cfg.head_dim, scale, nsplit=nsplit)
             o = K.gemm(attn, p[f"l{i}.wo"], workspace=ws)

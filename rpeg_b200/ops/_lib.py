@@ -46,6 +46,7 @@ _SIGNATURES = {
     "rpeg_dp_adam_push": [P, P, P, P, P, I, LL, LL, F, F, F, F, F, I, P, I, F, P],
     "rpeg_copy16": [P, P, LL, P],
     "rpeg_kv_append": [P, I, I, I, P, P, P, I, P, P, I, I, I, P],
+    "rpeg_rope_kv_append": [P, I, I, I, I, P, P, P, P, P, I, P, P, I, I, I, I, P],
     "rpeg_paged_decode_attn": [P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, F, P],
     "rpeg_symm_alloc": [c_ulonglong, P],
     "rpeg_symm_free": [P],

@@ -295,6 +295,17 @@ def kv_append(qkv, k_col0, v_col0, seq_id, pos, page_table, kcache, vcache, n_kv
                                qkv.shape[0], n_kv_heads, head_dim, _stream()), "rpeg_kv_append")
 
 
+def rope_kv_append_(qkv, q_col0, k_col0, v_col0, seq_id, pos, cos_t, sin_t, page_table, kcache, vcache, n_heads, n_kv_heads,
+                    head_dim) -> None:
+    """Rotate the query and key heads of ``qkv`` in place and write the rotated keys and the values
+    into the paged cache: one launch instead of two rotations and an append."""
+    _req(qkv, torch.bfloat16, "qkv")
+    check(lib().rpeg_rope_kv_append(qkv.data_ptr(), qkv.stride(0), q_col0, k_col0, v_col0, seq_id.data_ptr(), pos.data_ptr(),
+                                    cos_t.data_ptr(), sin_t.data_ptr(), page_table.data_ptr(), page_table.stride(0),
+                                    kcache.data_ptr(), vcache.data_ptr(), qkv.shape[0], n_heads, n_kv_heads, head_dim,
+                                    _stream()), "rpeg_rope_kv_append")
+
+
 def decode_scratch_numel(B: int, H: int, nsplit: int) -> int:
     return int(lib().rpeg_decode_attn_scratch_bytes(B, H, nsplit)) // 4
 

@@ -1,0 +1,366 @@
+"""Engine backend: gives the nodes of a runtime graph their meaning on the GPU.
+
+Every rank (one process per GPU) executes the same graph in the same order; an operator node runs the
+engine call of its vertex on this rank's share of the batch:
+
+  g_pi / g_ac   paged-KV generation with CUDA-graph decode              (engine.generation.Generator)
+  i_ref         frozen reference log-probs                               (algorithms.sequence_logprobs)
+  i_R           reward model scores, or a rule-based reward without one  (algorithms.reward_scores)
+  i_V / i_ac    critic / shared-trunk values                             (algorithms.critic_values)
+  i_pi          policy sequence log-probs of preference pairs (DPO)
+  t_pi / t_ac   policy (or shared trunk) update incl. optimizer step     (algorithms.policy_train_step / dpo_train_step)
+  t_V           critic update incl. optimizer step                       (algorithms.critic_train_step)
+
+The plan must be data parallel only (every vertex with pp = tp = 1 on all GPUs of the node) and
+synchronous (tau = 0): weights are replicated in symmetric memory and updated in place by the fused
+optimizer, so COMM and RESHARD nodes between vertices move nothing and only report their payload.
+Generation is continuously batched, so the quantile phases of a split generation vertex are not
+separate decode loops: the first phase node generates every row, and each phase node *emits* the rows
+whose length falls into its interval (what downstream split inference nodes consume).
+Checkpoints use the flat-shard format (``runtime.checkpoint``): bf16 weights from rank 0, the fp32
+master/m/v shards from every rank with their global offsets, so a resumed job may use another
+data-parallel degree. Reference entry points: run_graph_ppo / run_graph_grpo / run_graph_dpo
+(RPEG/runtime/algorithms/ppo_graph.py:1072, grpo_graph.py:25, dpo_graph.py:414).
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import os
+from pathlib import Path
+from typing import Any, Dict, List, Optional
+
+from ..passes.lower import ExecNodeType
+from . import checkpoint as ckpt
+from .containers import ContainerRef, WeightVersion
+from .errors import RuntimeConfigError, RuntimeExecutionError
+from .executor import NodeExecutionResult, model_name, node_step, split_part_index
+
+
+def llama_config_from_run(m, max_pos: int, **kw):
+    from ..models.llama import LlamaConfig
+    heads = m.num_heads or (m.hidden_dim // m.head_dim)
+    return LlamaConfig(n_layers=m.layers, d_model=m.hidden_dim, d_ff=m.ffn_dim, n_heads=heads,
+                       n_kv_heads=m.num_kv_heads or heads, head_dim=m.head_dim, vocab=m.vocab_size, rms_eps=m.rms_eps,
+                       rope_theta=m.rope_theta, max_pos=max_pos, **kw)
+
+
+def validate_engine_plan(compiled) -> None:
+    cfg = compiled.config
+    g = compiled.device_space.num_devices()
+    for v in cfg.rpeg.vertices:
+        dp, pp, tp = cfg.plan.pi[v.id]
+        if pp != 1 or tp != 1 or dp != g:
+            raise RuntimeConfigError(f"engine backend runs data-parallel plans only: {v.id} has (dp,pp,tp)=({dp},{pp},{tp}) "
+                                     f"on {g} GPU(s); expected ({g},1,1)")
+    if any(int(t) > 0 for t in cfg.rpeg.tau.values()):
+        raise RuntimeConfigError("engine backend runs synchronous plans only (tau = 0): stale serving needs disjoint devices")
+
+
+class EngineOperationHandler:
+    def __init__(self, compiled, attempt: int = 0):
+        import torch
+        import torch.distributed as dist
+        from ..engine import algorithms as A
+        validate_engine_plan(compiled)
+        self.compiled, self.attempt = compiled, attempt
+        self.torch, self.A = torch, A
+        run = compiled.run_config
+        self.run = run
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        if self.world != compiled.device_space.num_devices():
+            raise RuntimeConfigError(f"run file plans {compiled.device_space.num_devices()} GPU(s) but WORLD_SIZE={self.world}")
+        self.device = torch.device(f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}")
+        torch.cuda.set_device(self.device)
+        self.dp = None
+        if self.world > 1:
+            if not dist.is_initialized():
+                dist.init_process_group("nccl", device_id=self.device)
+            from ..parallel.dp import DPContext
+            self.dp = DPContext(self.device)
+        a, w, rt, o = run.algorithm, run.workload, run.runtime, run.optimizer_runtime
+        self.algo_name = a.name
+        self.shared = any(v.id == "g_ac" for v in compiled.config.rpeg.vertices)
+        self.algo = A.AlgoConfig(clip_eps=a.clip, kl_coef=a.kl_coef, beta=a.beta, gamma=a.gamma, gae_lambda=a.gae_lambda,
+                                 value_coef=a.value_coef, temperature=a.temperature, micro_tokens=rt.micro_tokens)
+        max_pos = w.context_length + w.generation_length
+        cfg = llama_config_from_run(run.models["actor"], max_pos)
+        from ..engine.trainers import DPOTrainer, GRPOTrainer, PPOTrainer
+        common = dict(device=self.device, algo=self.algo, dp=self.dp, recompute=rt.recompute, seed=a.seed)
+        if a.name == "grpo":
+            self.trainer = GRPOTrainer(cfg, samples_per_prompt=w.samples_per_prompt, max_new=w.generation_length,
+                                       prompt_len=w.context_length, lr=o.learning_rate_actor, gen_slots=rt.gen_slots,
+                                       eos_id=run.tokenizer.eos_token_id, use_graphs=rt.use_cuda_graphs, **common)
+        elif a.name == "ppo":
+            r = run.models.get("reward")
+            self.trainer = PPOTrainer(cfg, max_new=w.generation_length, prompt_len=w.context_length, lr_actor=o.learning_rate_actor,
+                                      lr_critic=o.learning_rate_critic, gen_slots=rt.gen_slots, eos_id=run.tokenizer.eos_token_id,
+                                      share_actor_critic=self.shared, use_graphs=rt.use_cuda_graphs,
+                                      reward_cfg=llama_config_from_run(r, max_pos) if r is not None else None, **common)
+        else:
+            self.trainer = DPOTrainer(cfg, lr=o.learning_rate_actor, **common)
+        self.latest: Dict[str, int] = {}
+        self.steps: Dict[int, Dict[str, Any]] = {}
+        self.gen_cpu = torch.Generator().manual_seed(run.data.data_seed)
+        self.vocab = cfg.vocab
+
+    # ------------------------------------------------------------------ data
+    def _local(self, n: int) -> slice:
+        per = n // self.world
+        return slice(self.rank * per, (self.rank + 1) * per)
+
+    def _prompts(self, step: int):
+        """Synthetic prompts of the workload's shape (every rank draws the global batch from the same
+        seed and keeps its slice), or rows of token ids from ``data.train_prompts`` (JSONL)."""
+        torch, w = self.torch, self.run.workload
+        if self.run.data.train_prompts:
+            rows = [json.loads(l) for l in open(self.run.resolve(self.run.data.train_prompts)) if l.strip()]
+            ids = [r["input_ids"] if isinstance(r, dict) else r for r in rows]
+            start = ((step - 1) * w.batch_size) % max(1, len(ids))
+            batch = [ids[(start + i) % len(ids)] for i in range(w.batch_size)]
+            t = torch.full((w.batch_size, w.context_length), self.run.tokenizer.pad_token_id, dtype=torch.int32)
+            for i, r in enumerate(batch):
+                r = r[-w.context_length:]
+                t[i, w.context_length - len(r):] = torch.tensor(r, dtype=torch.int32)
+        else:
+            g = torch.Generator().manual_seed(self.run.data.data_seed * 1000003 + step)
+            t = torch.randint(3, self.vocab, (w.batch_size, w.context_length), generator=g, dtype=torch.int32)
+        return t[self._local(w.batch_size)].contiguous()
+
+    def _state(self, step: int) -> Dict[str, Any]:
+        return self.steps.setdefault(step, {})
+
+    # ------------------------------------------------------------------ operators
+    def _generate(self, st, step: int) -> Dict[str, Any]:
+        tr, A, torch, w = self.trainer, self.A, self.torch, self.run.workload
+        prompts = self._prompts(step).to(self.device)
+        rep = prompts.repeat_interleave(w.samples_per_prompt, dim=0).contiguous()
+        a = self.run.algorithm
+        gen = tr.gen.generate(rep, w.generation_length, temperature=a.temperature, greedy=a.greedy, seed=a.seed + 100003 * step)
+        lens = gen.lengths.tolist()
+        st["rollout"] = A.Rollout(rep, [w.context_length] * rep.shape[0], gen.tokens, lens, gen.logprobs, gen.response_mask(),
+                                  weight_version=self.latest.get("ac_share" if self.shared else "actor", 0))
+        st["lens"] = lens
+        c = {k: v for k, v in gen.counters.items()}
+        c.update(generated_tokens=int(sum(lens)), prompt_tokens=int(rep.numel()))
+        return c
+
+    def _emitted(self, st, node) -> int:
+        """Rows of this rank whose generated length falls into the node's quantile phase."""
+        part = split_part_index(node.node_id)
+        lens = st.get("lens")
+        if lens is None:
+            return 0
+        q = self.compiled.workload.gen_quantiles
+        if part is None or not q:
+            return len(lens)
+        lo = q[part - 1][1] if part > 0 else 0
+        hi = q[part][1]
+        return sum(1 for l in lens if lo < l <= hi)
+
+    def _run_op(self, node) -> Dict[str, Any]:
+        tr, A, torch = self.trainer, self.A, self.torch
+        step = node_step(node) or 1
+        st = self._state(step)
+        vid, part = node.vertex_id, split_part_index(node.node_id)
+        first = part in (None, 0)
+        c: Dict[str, Any] = {}
+        if vid in ("g_pi", "g_ac"):
+            if "rollout" not in st:
+                c.update(self._generate(st, step))
+            c["emitted_rows"] = self._emitted(st, node)
+        elif vid == "i_ref":
+            if self.algo_name == "dpo":
+                self._dpo_inputs(st, step)
+                if "ref_seq" not in st:
+                    from ..ops import kernels as K
+                    st["ref_seq"] = K.masked_rowsum(A.sequence_logprobs(tr.ref, st["rollout"], self.algo), st["rollout"].mask)
+            elif "ref" not in st:
+                st["rollout"].ref_logp = A.sequence_logprobs(tr.ref, st["rollout"], self.algo)
+                st["ref"] = True
+        elif vid == "i_R":
+            if "scores" not in st:
+                ro = st["rollout"]
+                if hasattr(tr, "reward"):
+                    ro.scores = A.reward_scores(tr.reward, ro, self.algo)
+                else:   # rule-based stand-in: shorter completions score higher, deterministic per row
+                    ro.scores = -torch.tensor(st["lens"], dtype=torch.float32, device=self.device) / self.run.workload.generation_length
+                st["scores"] = True
+        elif vid in ("i_V", "i_ac"):
+            if "values" not in st:
+                ro = st["rollout"]
+                ro.values = A.critic_values(tr.actor if self.shared else tr.critic, ro, self.algo)
+                st["values"] = True
+        elif vid == "i_pi":
+            self._dpo_inputs(st, step)
+        elif vid in ("t_pi", "t_ac"):
+            c.update(self._train_policy(st, step))
+        elif vid == "t_V":
+            c.update(self._train_critic(st))
+        else:
+            raise RuntimeExecutionError(f"engine backend has no operator for vertex {vid}")
+        return c
+
+    def _dpo_inputs(self, st, step: int) -> None:
+        if "rollout" in st:
+            return
+        torch, A, w = self.torch, self.A, self.run.workload
+        g = torch.Generator().manual_seed(self.run.data.data_seed * 7919 + step)
+        pr = torch.randint(3, self.vocab, (w.batch_size, w.context_length), generator=g, dtype=torch.int32).repeat_interleave(2, 0)
+        rs = torch.randint(3, self.vocab, (2 * w.batch_size, w.generation_length), generator=g, dtype=torch.int32)
+        sl = slice(self.rank * 2 * (w.batch_size // self.world), (self.rank + 1) * 2 * (w.batch_size // self.world))
+        p, r = pr[sl].to(self.device), rs[sl].to(self.device)
+        N, T = r.shape
+        st["rollout"] = A.Rollout(p, [w.context_length] * N, r, [T] * N, torch.zeros((N, T), device=self.device),
+                                  torch.ones((N, T), device=self.device))
+
+    def _global(self, x: float) -> float:
+        return self.trainer._global_sum(x)
+
+    def _train_policy(self, st, step: int) -> Dict[str, Any]:
+        tr, A = self.trainer, self.A
+        ro = st["rollout"]
+        if self.algo_name == "dpo":
+            tr.policy.zero_grad()
+            m = A.dpo_train_step(tr.policy, ro, st["ref_seq"], self.algo, n_pairs_global=int(self._global(ro.tokens.shape[0] // 2)))
+            tr.opt.step()
+            m["grad_norm"] = tr.opt.grad_norm()
+        else:
+            if self.algo_name == "grpo":
+                A.grpo_advantages(ro, self.run.workload.samples_per_prompt)
+                opt = tr.opt
+            else:
+                if "targets" not in st:
+                    A.ppo_targets(ro, self.algo)
+                    st["targets"] = True
+                opt = tr.opt_actor
+            st["denom"] = self._global(ro.n_response_tokens())
+            tr.actor.zero_grad()
+            m = A.policy_train_step(tr.actor, ro, self.algo, denom_tokens=st["denom"],
+                                    **({"value_model_shared": True} if self.shared else {}))
+            opt.step()
+            m["grad_norm"] = opt.grad_norm()
+        out = {k: float(v) for k, v in tr._read(m).items()}
+        out.update(train_tokens=int(sum(ro.total_lens())), optimizer_steps=1)
+        return out
+
+    def _train_critic(self, st) -> Dict[str, Any]:
+        tr, A = self.trainer, self.A
+        ro = st["rollout"]
+        if "targets" not in st:
+            A.ppo_targets(ro, self.algo)
+            st["targets"] = True
+        denom = st.get("denom") or self._global(ro.n_response_tokens())
+        tr.critic.zero_grad()
+        m = A.critic_train_step(tr.critic, ro, self.algo, denom_tokens=denom)
+        tr.opt_critic.step()
+        m["critic_grad_norm"] = tr.opt_critic.grad_norm()
+        out = {k: float(v) for k, v in tr._read(m).items()}
+        out.update(train_tokens=int(sum(ro.total_lens())), optimizer_steps=1)
+        return out
+
+    # ------------------------------------------------------------------ executor interface
+    async def execute(self, node, context) -> NodeExecutionResult:
+        await asyncio.sleep(0)
+        from ..ops import _lib
+        from ..ops import kernels as K
+        step = node_step(node)
+        name = model_name(node.model)
+        c: Dict[str, Any] = {"kind": node.kind.value, "rank": self.rank}
+        weights: List[WeightVersion] = []
+        if node.kind is ExecNodeType.OP:
+            n0 = _lib.launch_count()
+            c.update(self._run_op(node))
+            K.check_status()
+            c["kernel_launches"] = _lib.launch_count() - n0
+            c["peak_memory_bytes"] = int(self.torch.cuda.max_memory_allocated(self.device))
+            en = node.exec_node
+            if en.n_seqs is not None:
+                c.update(partial_n_seqs=int(en.n_seqs), phase_forced_completions=0)
+                part = split_part_index(node.node_id)
+                if part is not None:
+                    c["artifact_part"] = part
+            if name in ("actor", "critic", "ac_share") and node.role in ("GEN", "INF") and step is not None:
+                c.update(weight_version=self.latest.get(name, 0), model=name, shadow=False)
+            if node.role == "TRAIN" and name is not None:
+                self.latest[name] = self.latest.get(name, 0) + 1
+                c["produced_weight"] = {"model": name, "version": self.latest[name], "shadow": False}
+                weights.append(WeightVersion(name, self.latest[name], tuple(node.parallelism or (1, 1, 1))))
+                done = [s for s in self.steps if s < (step or 0)]
+                for s in done:           # rollouts of closed steps are dead
+                    del self.steps[s]
+        else:
+            c.update(payload_in_bytes=node.payload_in_bytes, transferred_bytes=0, transport="in_place", label=node.label)
+        ref = ContainerRef(f"{node.node_id}:output", step or 0, split_part_index(node.node_id), producer=node.node_id)
+        context.store.put(ref)
+        return NodeExecutionResult(node.node_id, "ok", c, (ref,), tuple(weights))
+
+    # ------------------------------------------------------------------ checkpoints
+    def _trainables(self):
+        tr = self.trainer
+        if self.algo_name == "dpo":
+            return {"actor": (tr.policy, tr.opt)}
+        if self.algo_name == "grpo":
+            return {"actor": (tr.actor, tr.opt)}
+        out = {"ac_share" if self.shared else "actor": (tr.actor, tr.opt_actor)}
+        if tr.critic is not None:
+            out["critic"] = (tr.critic, tr.opt_critic)
+        return out
+
+    def save_checkpoint(self, step: int, path, kind: str) -> Dict[str, Any]:
+        torch = self.torch
+        torch.cuda.synchronize()
+        total_bytes = files = 0
+        for name, (model, opt) in self._trainables().items():
+            d = Path(path) / name
+            n = model.layout.total
+            tensors = {"adam.master": opt.master, "adam.m": opt.m, "adam.v": opt.v}
+            ranges = {k: (opt.shard_off, opt.shard_off + opt.shard_n, n) for k in tensors}
+            if self.rank == 0:
+                tensors["weights"] = model.w[:n]
+            part = ckpt.save_flat_shards(d, self.rank, self.world, tensors, ranges=ranges,
+                                         extra={"optimizer_step": opt.step_count, "version": self.latest.get(name, 0)})
+            total_bytes += part["file"]["bytes"]
+            files += 1
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        if self.rank == 0:
+            for name in self._trainables():
+                ckpt.finalize_worker_meta(Path(path) / name, self.world, extra={"step": step, "kind": kind})
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        return {"workers": sorted(self._trainables()), "bytes": total_bytes, "files": files}
+
+    def restore_checkpoint(self, step: int, path) -> None:
+        for name, (model, opt) in self._trainables().items():
+            d = Path(path) / name
+            n = model.layout.total
+            model.w[:n].copy_(ckpt.load_tensor(d, "weights").to(self.device))
+            lo, hi = opt.shard_off, opt.shard_off + opt.shard_n
+            opt.master.copy_(ckpt.load_flat_range(d, "adam.master", lo, hi).to(self.device))
+            opt.m.copy_(ckpt.load_flat_range(d, "adam.m", lo, hi).to(self.device))
+            opt.v.copy_(ckpt.load_flat_range(d, "adam.v", lo, hi).to(self.device))
+            meta = json.loads((d / "meta.json").read_text())
+            opt.step_count = int(meta["ranks"][0]["extra"]["optimizer_step"])
+            self.latest[name] = int(meta["ranks"][0]["extra"]["version"])
+        if hasattr(self.trainer, "ref") and self.algo_name != "dpo":
+            pass    # the frozen reference never changes; nothing to restore
+        self.steps.clear()
+        self.torch.cuda.synchronize()
+
+
+def make_engine_handler_factory(compiled):
+    """One engine (models, optimizer state, KV arena) lives for the whole run; replays reuse it and
+    restore its state from the checkpoint instead of rebuilding it."""
+    holder: Dict[str, EngineOperationHandler] = {}
+
+    def make(attempt: int):
+        if "h" not in holder:
+            holder["h"] = EngineOperationHandler(compiled, attempt)
+        holder["h"].attempt = attempt
+        return holder["h"]
+
+    return make

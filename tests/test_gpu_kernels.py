@@ -370,3 +370,35 @@ def test_flash_attn_bwd(cuda_device, lens):
     torch.cat(outs).backward(dout.float())
     for name, lo in (("dq", 0), ("dk", H * hd), ("dv", 2 * H * hd)):
         assert _rel_err(dqkv[:, lo:lo + H * hd], x.grad[:, lo:lo + H * hd]) < 2e-2, name
+
+
+@pytest.mark.gpu
+def test_fused_rope_kv_append_matches_separate_ops(cuda_device):
+    H, Hkv, hd = 8, 4, 128
+    lens = [3, 70, 129]
+    B = len(lens)
+    table, kc, vc = _paged_cache(cuda_device, [l + 1 for l in lens], Hkv, hd, 16)
+    kc2, vc2 = kc.clone(), vc.clone()
+    ld = (H + 2 * Hkv) * hd
+    qkv = torch.randn(B, ld, device=cuda_device).bfloat16()
+    ref = qkv.clone()
+    pos = torch.tensor(lens, device=cuda_device, dtype=torch.int32)
+    slots = torch.arange(B, device=cuda_device, dtype=torch.int32)
+    cos_t, sin_t = K.rope_tables(256, hd, 10000.0, cuda_device)
+    K.rope_(ref, pos, cos_t, sin_t, 0, H, hd)
+    K.rope_(ref, pos, cos_t, sin_t, H * hd, Hkv, hd)
+    K.kv_append(ref, H * hd, (H + Hkv) * hd, slots, pos, table, kc, vc, Hkv, hd)
+    K.rope_kv_append_(qkv, 0, H * hd, (H + Hkv) * hd, slots, pos, cos_t, sin_t, table, kc2, vc2, H, Hkv, hd)
+    assert torch.equal(qkv, ref) and torch.equal(kc, kc2) and torch.equal(vc, vc2)
+    assert kc2.abs().sum() > 0
+
+
+@pytest.mark.gpu
+def test_rmsnorm_wide_rows_use_the_streaming_kernel(cuda_device):
+    T, d = 5, 16384        # more than 256 threads x 4 vectors: the row no longer fits in registers
+    x = torch.randn(T, d, device=cuda_device).bfloat16()
+    w = torch.randn(d, device=cuda_device).bfloat16()
+    y, rstd, _ = K.rmsnorm_fwd(x, w, 1e-5)
+    xf = x.float()
+    ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    assert _rel_err(y, ref) < 1e-2
