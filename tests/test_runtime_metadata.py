@@ -47,10 +47,18 @@ def job_mapping(algorithm="ppo", steps=3, quantiles=True, **extra):
     return cfg
 
 
-def spread_job(tmp_path, algorithm="ppo", steps=3, ac_share=False, tau=None, width=2, **extra):
+def spread_job(tmp_path, algorithm="ppo", steps=3, ac_share=False, tau=None, width=2, space=SPACE, colocate=False, model=None,
+               workload=None, **extra):
     """A plan/run pair with every vertex on its own GPUs (so the graph has COMM and RESHARD nodes),
     built by hand instead of searched."""
     cfg = job_mapping(algorithm, steps, **extra)
+    cfg["device_space"] = {"racks": space.R, "nodes_per_rack": space.N, "gpus_per_node": space.G}
+    if model is not None:
+        for name, m in cfg["models"].items():
+            if "layers" in m:
+                cfg["models"][name] = dict(model)
+    if workload is not None:
+        cfg["workload"].update(workload)
     suite, hw = job_suite(cfg), job_hardware(cfg)
     w = cfg["workload"]
     q = w["gen_quantiles"]
@@ -62,15 +70,18 @@ def spread_job(tmp_path, algorithm="ppo", steps=3, ac_share=False, tau=None, wid
     rpeg = build_rpeg("ac_share" if ac_share else algorithm, suite, wl, tau=tau_m)
     plan = ExecutionPlan()
     for i, v in enumerate(rpeg.vertices):
-        g0 = (i * width) % SPACE.G
-        plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = Allocation((0, 0, g0), (1, 1, width)), (1, 1, width), 1
-    conf = Configuration(rpeg, plan, SPACE, False, TransferResourcePolicy("both_endpoints", "both_endpoints"))
+        if colocate:        # every vertex data parallel over all GPUs
+            plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = Allocation((0, 0, 0), (1, 1, space.G)), (space.G, 1, 1), 1
+        else:
+            g0 = (i * width) % space.G
+            plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = Allocation((0, 0, g0), (1, 1, width)), (1, 1, width), 1
+    conf = Configuration(rpeg, plan, space, False, TransferResourcePolicy("both_endpoints", "both_endpoints"))
     lowered = lower(rpeg, unroll(rpeg, steps), plan, suite, steps, workload=wl)
-    trace = schedule(lowered, NodeCostModel(hw, suite, wl, optimizer_stage=1), SPACE,
+    trace = schedule(lowered, NodeCostModel(hw, suite, wl, optimizer_stage=1), space,
                      transfer_resource_policy=conf.transfer_resource_policy)
     d = optimized_plan_to_dict(conf, algorithm, wl, None, execution_schedule_to_dict(trace, horizon=steps))
     dump_mapping(d, tmp_path / "optimized_plan.yaml")
-    run = run_config_mapping(cfg, run_id=cfg["run_id"], algorithm=algorithm, workload=wl, space=SPACE, hw=hw,
+    run = run_config_mapping(cfg, run_id=cfg["run_id"], algorithm=algorithm, workload=wl, space=space, hw=hw,
                              policy=MemoryPolicy(1, True, 0.10, float(1 << 30)), plan_file="optimized_plan.yaml",
                              plan_hash=d["plan_hash"], fusion=False)
     dump_mapping(run, tmp_path / "run.yaml")
