@@ -402,3 +402,31 @@ def test_rmsnorm_wide_rows_use_the_streaming_kernel(cuda_device):
     xf = x.float()
     ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
     assert _rel_err(y, ref) < 1e-2
+
+
+@pytest.mark.gpu
+def test_flag_barrier_timeout_reports_status(cuda_device):
+    """The device-side barrier gives up after its time limit and reports it in the status word; the
+    context stays usable. Two 'ranks' share one pad here: rank 0 waits for a flag that nothing sets."""
+    import ctypes
+    from rpeg_b200.ops._lib import check, lib
+    pad = torch.zeros(2048, dtype=torch.int32, device=cuda_device)
+    pads = (ctypes.c_void_p * 2)(pad.data_ptr(), pad.data_ptr())
+    st = K.status_word()
+    st.zero_()
+    stream = torch.cuda.current_stream().cuda_stream
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    check(lib().rpeg_flag_barrier(pads, 0, 2, 3, 1, None, None, 20_000_000, st.data_ptr(), stream), "rpeg_flag_barrier")
+    t1.record()
+    with pytest.raises(K.KernelWaitTimeout, match="code=2"):
+        K.check_status()
+    assert 15.0 < t0.elapsed_time(t1) < 500.0            # waited about 20 ms, not forever
+    assert pad[3 * 8 + 0].item() == 1 and pad[3 * 8 + 1].item() == 0
+    # the second rank arrives: its own flag is set and rank 0's flag is already there, so no timeout
+    check(lib().rpeg_flag_barrier(pads, 1, 2, 3, 1, None, None, 20_000_000, st.data_ptr(), stream), "rpeg_flag_barrier")
+    K.check_status()
+    assert pad[3 * 8 + 1].item() == 1
+    assert torch.equal(K.gemm(torch.ones(128, 64, device=cuda_device).bfloat16(), torch.ones(128, 64, device=cuda_device).bfloat16()),
+                       torch.full((128, 128), 64.0, device=cuda_device).bfloat16())

@@ -334,3 +334,18 @@ def test_metrics_alert_rules_and_fingerprints():
     ia = {"tok": tensor_fingerprint(torch.arange(10))}
     ib = {"tok": tensor_fingerprint(torch.arange(10) + (torch.arange(10) == 3))}
     assert not compare_artifact_numeric_fingerprints(ia, ib)["ok"]
+
+
+def test_full_validator_phases(tmp_path, capsys):
+    from rpeg_b200.runtime.validate_full import main as validate_main, validate_full
+    run = spread_job(tmp_path, "ppo", steps=2, width=1)
+    rep = validate_full(run, work_dir=tmp_path / "work")
+    assert rep["ok"] and [p["phase"] for p in rep["phases"]] == ["input", "unroll", "lower", "runtime_graph", "metadata_execution"]
+    lower_facts = rep["phases"][2]
+    assert lower_facts["by_kind"]["op"] > 0 and lower_facts["quantile_split_nodes"] > 0
+    bad = load_mapping(run)
+    bad["workload"]["context_length"] = 64
+    dump_mapping(bad, tmp_path / "bad.yaml")
+    assert validate_main(["--config", str(tmp_path / "bad.yaml")]) == 2
+    out = json.loads(capsys.readouterr().out)
+    assert not out["ok"] and out["phases"][-1]["phase"] == "unroll" and "context_length" in out["phases"][-1]["error"]
