@@ -164,7 +164,7 @@ def main() -> None:
         # KV pages are handed out on demand, so the slot count may exceed what the budget holds at full length.
         # One rank keeps the whole fp32 Adam state (81 GB for 7B) and has ~56 GB for KV; sharded ranks have more.
         slots = args.gen_slots or min(b_local * Kk, 96 if world == 1 else 128)
-        kv_gb = args.kv_gb or (56.0 if world == 1 else 90.0)
+        kv_gb = args.kv_gb or {1: 56.0, 2: 76.0}.get(world, 96.0)
         trainer = GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp,
                               gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)
         batches = []

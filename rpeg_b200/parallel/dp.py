@@ -26,7 +26,7 @@ from ..ops import kernels as K
 from ..ops._lib import check, lib
 from .symm import SignalPad, SymmetricBuffer
 
-BARRIER_TIMEOUT_NS = 20_000_000_000  # ranks may arrive seconds apart (uneven generation lengths)
+BARRIER_TIMEOUT_NS = 60_000_000_000  # ranks may arrive many seconds apart (uneven generation lengths, first-step graph capture)
 
 
 class DPContext:
@@ -107,5 +107,3 @@ class DPContext:
     def broadcast_weights(self, w: torch.Tensor, src: int = 0) -> None:
         if self.world > 1:
             dist.broadcast(w, src=src, group=self.group)
-EOF
-sleep 45; cat gpurun_out/call8.txt | tail -45 | cut -c1-220

@@ -1,0 +1,133 @@
+"""Multi-GPU self test of the peer-memory layer, run with one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29551 \
+        -m rpeg_b200.parallel.selftest
+
+Checks, each against values computed independently on the host or with NCCL:
+  1 symmetric buffers   every rank reads every peer's buffer through its IPC mapping
+  2 flag barrier        the payload exchange returns every rank's value; no wait times out
+  3 fused DP optimizer  reduce-scatter + Adam + all-gather over peer memory equals AdamW on the summed
+                        gradients computed with torch, and all ranks end with identical weights
+  4 GRPO steps          two data-parallel steps of the tiny model: finite loss, identical weights
+Rank 0 prints one JSON line with ``"ok": true``. Exit code 1 on any mismatch.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev)
+    from ..engine import algorithms as A
+    from ..engine.optimizer import AdamW
+    from ..engine.trainers import GRPOTrainer
+    from ..models.llama import LlamaConfig, LlamaModel
+    from ..ops import kernels as K
+    from ..ops._lib import check, lib
+    from .dp import DPContext
+    from .symm import SymmetricBuffer
+
+    report = {"world": world}
+    stream = lambda: torch.cuda.current_stream().cuda_stream
+
+    # 1 symmetric buffers
+    buf = SymmetricBuffer(1 << 20, dev)
+    buf.tensor(torch.float32).fill_(float(rank + 1))
+    torch.cuda.synchronize()
+    dist.barrier()
+    got = []
+    tmp = torch.empty(1 << 18, dtype=torch.float32, device=dev)
+    for p in range(world):
+        check(lib().rpeg_copy16(buf.peer_ptrs[p], tmp.data_ptr(), 1 << 20, stream()), "rpeg_copy16")
+        got.append((float(tmp.min()), float(tmp.max())))
+    report["peer_reads_ok"] = got == [(float(p + 1), float(p + 1)) for p in range(world)]
+    dist.barrier()
+
+    # 2 flag barrier with payload
+    dp = DPContext(dev)
+    mine = torch.tensor([10.0 + rank], device=dev)
+    out = torch.zeros(K.MAX_PEERS, device=dev)
+    for _ in range(3):
+        dp.barrier(5, payload_in=mine, payload_out=out)
+    K.check_status()
+    report["barrier_payload_ok"] = out[:world].tolist() == [10.0 + r for r in range(world)]
+
+    # 3 fused optimizer step against torch AdamW on the summed gradients
+    cfg = LlamaConfig.tiny(n_layers=2)
+    w = dp.alloc_weights(cfg)
+    g = dp.alloc_grads(cfg)
+    model = LlamaModel(cfg, dev, trainable=True, weights=w, grads=g, seed=11)
+    model.init_weights(11)
+    n = model.layout.total
+    w0 = model.w[:n].float().clone()
+    opt = AdamW(model, lr=1e-2, dp=dp, max_grad_norm=1.0)
+    gens = [torch.Generator(device="cpu").manual_seed(100 + r) for r in range(world)]
+    ref_p, ref_m, ref_v = w0.clone(), torch.zeros_like(w0), torch.zeros_like(w0)
+    ok_steps = []
+    for step in range(1, 4):
+        grads = [torch.randn(n, generator=gens[r]) * 0.01 for r in range(world)]
+        model.g[:n].copy_(grads[rank].to(dev))
+        opt.step()
+        torch.cuda.synchronize()
+        K.check_status()
+        gsum = torch.stack(grads).sum(0).to(dev)
+        norm = gsum.norm()
+        gsum = gsum * torch.clamp(1.0 / (norm + 1e-6), max=1.0)
+        ref_m = 0.9 * ref_m + 0.1 * gsum
+        ref_v = 0.999 * ref_v + 0.001 * gsum * gsum
+        ref_p = ref_p - 1e-2 * (ref_m / (1 - 0.9 ** step)) / ((ref_v / (1 - 0.999 ** step)).sqrt() + 1e-8)
+        err = (model.w[:n].float() - ref_p.bfloat16().float()).abs().max().item()
+        nerr = abs(float(opt.grad_norm()) - float(norm)) / float(norm)
+        ok_steps.append(err <= 2e-2 * ref_p.abs().max().item() and nerr < 1e-3)
+    report["fused_adam_ok"] = all(ok_steps)
+    chk = model.w[:n].float().sum().reshape(1).double()
+    lo, hi = chk.clone(), chk.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    report["weights_identical_after_adam"] = bool((lo == hi).item())
+
+    # 4 two GRPO steps, data parallel
+    algo = A.AlgoConfig(kl_coef=0.04, micro_tokens=512, head_chunk=256)
+    tr = GRPOTrainer(cfg, device=dev, samples_per_prompt=4, max_new=24, prompt_len=16, algo=algo, dp=DPContext(dev), gen_slots=8,
+                     kv_budget_bytes=1e9, seed=5, eos_id=1, lr=1e-4)
+    gcpu = torch.Generator().manual_seed(77)
+    losses = []
+    for it in range(2):
+        prompts = torch.randint(2, cfg.vocab, (4 * world, 16), generator=gcpu, dtype=torch.int32)
+        rewards = torch.randn(16 * world, generator=gcpu)
+        outm = tr.step(prompts[rank * 4:(rank + 1) * 4].contiguous(), rewards[rank * 16:(rank + 1) * 16].contiguous())
+        losses.append(outm["loss"])
+    K.check_status()
+    chk = tr.actor.w[: tr.actor.layout.total].float().sum().reshape(1).double()
+    lo, hi = chk.clone(), chk.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    report["grpo_losses_finite"] = all(x == x and abs(x) < 1e6 for x in losses)
+    report["weights_identical_after_grpo"] = bool((lo == hi).item())
+
+    flags = torch.tensor([float(all(v for k, v in report.items() if k != "world"))], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    report["ok"] = bool(flags.item() == 1.0)
+    if rank == 0:
+        print(json.dumps(report))
+    else:
+        bad = {k: v for k, v in report.items() if v is False}
+        if bad:
+            print(json.dumps({"rank": rank, "failed": bad}), file=sys.stderr)
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0 if report["ok"] else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
