@@ -1,0 +1,98 @@
+"""CPU tests of the auxiliary tools: generation profile, cost calibration, environment check,
+distributed validation over gloo, suite report, calibrate.py fits."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+from rpeg_b200.runtime.compiler import compile_runtime_plan
+from rpeg_b200.runtime.cost_calibration import calibrate_costs, fit_scale
+from rpeg_b200.runtime.environment_check import run_checks
+from rpeg_b200.runtime.generation_profile import build_profile, quantiles_from_lengths
+from rpeg_b200.runtime.suite_report import aggregate
+from rpeg_b200.analytic.cost import NodeCostModel
+from rpeg_b200.analytic.hardware import b200_nvswitch
+from test_runtime_metadata import spread_job
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_generation_profile_quantiles():
+    lengths = [10] * 50 + [300] * 40 + [2048] * 10
+    q = quantiles_from_lengths(lengths, 2048)
+    assert q == [[0.5, 64], [0.9, 320], [1.0, 2048]]
+    assert quantiles_from_lengths([5, 5, 5, 5], 128) == [[0.5, 64], [1.0, 128]]       # degenerate phases merge
+    prof = build_profile(lengths, 2048)
+    assert prof["schema_version"] == "rpeg.generation_profile.v1" and prof["truncated_fraction"] == 0.1
+    with pytest.raises(ValueError):
+        quantiles_from_lengths([], 10)
+
+
+def test_job_planner_ingests_generation_profile(tmp_path):
+    from rpeg_b200.runtime.io import dump_mapping
+    from rpeg_b200.runtime.job_plan import job_workload
+    prof = build_profile([10] * 50 + [100] * 50, 256)
+    (tmp_path / "p.json").write_text(json.dumps(prof))
+    cfg = {"workload": {"batch_size": 8, "context_length": 16, "generation_length": 256}, "generation_profile": {"path": "p.json"}}
+    wl = job_workload(cfg, tmp_path)
+    assert wl.gen_quantiles == ((0.5, 64), (0.9, 128), (1.0, 256))
+    cfg["workload"]["generation_length"] = 512
+    from rpeg_b200.runtime.errors import RuntimeConfigError
+    with pytest.raises(RuntimeConfigError, match="max_new_tokens"):
+        job_workload(cfg, tmp_path)
+
+
+def test_cost_calibration_recovers_scales(tmp_path):
+    compiled = compile_runtime_plan(spread_job(tmp_path, "ppo", steps=2, width=1))
+    hw = b200_nvswitch(mem=float(compiled.run_config.hardware.memory_per_gpu_bytes))
+    cost = NodeCostModel(hw, compiled.model_suite, compiled.workload, optimizer_stage=1, activation_checkpointing=True)
+    events, t = [], 0.0
+    factor = {"GEN": 1.5, "INF": 0.8, "TRAIN": 2.0}
+    for n in compiled.lowered.nodes:
+        f = factor[n.role.value] if n.role is not None and n.op is not None else 1.25
+        d = cost.time(n) * f
+        events.append({"node_id": n.id, "event": "start", "status": "ok", "timestamp": t, "counters": {}})
+        events.append({"node_id": n.id, "event": "finish", "status": "ok", "timestamp": t + d, "counters": {"duration_s": d}})
+        t += d
+    rep = calibrate_costs(compiled, events, hw)
+    assert rep["matched_nodes"] == len(compiled.lowered.nodes)
+    assert rep["hardware"]["op_generation_scale"] == pytest.approx(1.5, rel=1e-6)
+    assert rep["hardware"]["op_inference_scale"] == pytest.approx(0.8, rel=1e-6)
+    assert rep["hardware"]["op_training_scale"] == pytest.approx(2.0, rel=1e-6)
+    assert fit_scale([(1.0, 2.0), (2.0, 4.0)]) == pytest.approx(2.0) and fit_scale([]) is None
+
+
+def test_environment_check_and_suite_report(tmp_path):
+    rep = run_checks(need_gpu=False)
+    assert rep["schema_version"] == "rpeg.environment_check.v1" and rep["ok"]
+    names = {c["name"] for c in rep["checks"]}
+    assert {"package:torch", "kernels:built", "kernels:abi"} <= names
+    (tmp_path / "env.json").write_text(json.dumps(rep))
+    (tmp_path / "bench.json").write_text(json.dumps({"metric": "m", "value": 1.0, "gpu_launches": 5}))
+    (tmp_path / "ref.json").write_text(json.dumps({"impl": "reference", "unavailable": "x"}))
+    (tmp_path / "bad.json").write_text(json.dumps({"schema_version": "rpeg.runtime_alerts.v1", "status": "critical", "alerts": [1]}))
+    good = aggregate([str(tmp_path / "env.json"), str(tmp_path / "bench.json"), str(tmp_path / "ref.json")])
+    assert good["ok"] and [i["kind"] for i in good["items"]] == ["environment_check", "bench", "bench_reference"]
+    bad = aggregate([str(tmp_path / "env.json"), str(tmp_path / "bad.json"), str(tmp_path / "missing.json")])
+    assert not bad["ok"] and len(bad["failed"]) == 2
+
+
+def test_distributed_validate_over_gloo(tmp_path):
+    out = tmp_path / "dist.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(29700 + os.getpid() % 200), "-m", "rpeg_b200.runtime.distributed_validate", "--backend", "gloo",
+           "--output", str(out)]
+    r = subprocess.run(cmd, cwd=ROOT, env=dict(os.environ, PYTHONPATH=ROOT), capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    rep = json.loads(out.read_text())
+    assert rep["ok"] and rep["world"] == 2 and rep["all_reduce_sum"] == rep["expected_sum"] and len(rep["ranks"]) == 2
+
+
+def test_calibrate_fits():
+    sys.path.insert(0, ROOT)
+    import calibrate as c
+    a, b = c.fit_alpha_beta([1e5, 2e5, 1e6, 1e7, 1e8], [2e-5 + s * 1.3e-12 for s in (1e5, 2e5, 1e6, 1e7, 1e8)])
+    assert a == pytest.approx(2e-5, rel=1e-3) and b == pytest.approx(1.3e-12, rel=1e-6)
+    assert c.fit_gemm_m_half([128, 1024, 8192], [128 / 224, 1024 / 1120, 8192 / 8288]) == pytest.approx(96.0)
