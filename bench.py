@@ -115,13 +115,22 @@ def main() -> None:
     ap.add_argument("--micro-tokens", type=int, default=16384)
     ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"])
     args = ap.parse_args()
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1. The contract is ONE JSON line on
+    # stdout, so everything else is sent to stderr and the line goes to the saved descriptor at the end.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj) -> None:
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(obj) + "\n").encode())
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": _reference_unavailable()}))
+            emit({"impl": "reference", "unavailable": _reference_unavailable()})
         return
     if world != args.gpus:
         if args.gpus == 1 and world == 1:
@@ -248,7 +257,7 @@ def main() -> None:
             "generation_counters": dict(getattr(trainer, "last_counters", {}) or {}),
             "published_other_hw": "reference paper data: 7B PPO on 8xA100-40GB, 1.73 samples/s (different config)",
         }
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 

@@ -69,6 +69,11 @@ int rpeg_dp_adam_push(float* p32, float* m, float* v, const float* reduced, void
                       float wd, int step, const float* sumsq, int n_partials, float max_norm, void* stream);
 int rpeg_copy16(const void* src, void* dst, long long nbytes, void* stream);
 
+// ---- gemm_rs.cu: row-parallel linear = GEMM + reduce-scatter (or all-reduce) over peer memory in one launch
+int rpeg_gemm_rs(const void* A, const void* B, int M, int N, int K, int lda, int ldb, void* const* stage,
+                 void* const* counters, void* const* outs, int ldo, int rank, int world, unsigned epoch, int all_gather,
+                 int* status, void* stream);
+
 // ---- decode_attn.cu
 int rpeg_kv_append(const void* qkv, int ld, int k_col0, int v_col0, const int* seq_id, const int* pos,
                    const int* page_table, int max_pages, void* kcache, void* vcache, int T, int Hkv, int hd,

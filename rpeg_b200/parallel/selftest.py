@@ -9,6 +9,8 @@ Checks, each against values computed independently on the host or with NCCL:
   3 fused DP optimizer  reduce-scatter + Adam + all-gather over peer memory equals AdamW on the summed
                         gradients computed with torch, and all ranks end with identical weights
   4 GRPO steps          two data-parallel steps of the tiny model: finite loss, identical weights
+  5 fused GEMM+RS       the row-parallel linear (GEMM with reduce-scatter / all-reduce in one kernel) against
+                        an fp32 all-reduce of the partial products, three calls in a row
 Rank 0 prints one JSON line with ``"ok": true``. Exit code 1 on any mismatch.
 """
 from __future__ import annotations
@@ -114,6 +116,30 @@ def main() -> int:
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     report["grpo_losses_finite"] = all(x == x and abs(x) < 1e6 for x in losses)
     report["weights_identical_after_grpo"] = bool((lo == hi).item())
+
+    # 5 fused GEMM + reduce-scatter / all-reduce over peer memory against an fp32 all-reduce of the partial products
+    from .tp import RowParallelLinear
+    gq = torch.Generator().manual_seed(300 + rank)
+    Mrows, Nout, Kp = 256 * world, 1024 + 64, 512 + 64         # N and K not multiples of the tile: edge paths
+    wsh = (torch.randn(Nout, Kp, generator=gq) * 0.05).bfloat16().to(dev)
+    rs_ok = []
+    for all_red in (False, True):
+        layer = RowParallelLinear(wsh, max_rows=Mrows, device=dev, all_reduce=all_red)
+        for it in range(3):                                     # several epochs on the same counters
+            xsh = torch.randn(Mrows, Kp, generator=gq).bfloat16().to(dev)
+            y = layer.forward(xsh).float().clone()
+            ref = xsh.float() @ wsh.float().t()
+            dist.all_reduce(ref)
+            if not all_red:
+                ref = ref[rank * (Mrows // world):(rank + 1) * (Mrows // world)]
+            torch.cuda.synchronize()
+            K.check_status()
+            rs_ok.append(bool(((y - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3).item()))
+            y2 = layer.forward_unfused(xsh).float()
+            rs_ok.append(bool(((y2 - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3).item()))
+        dist.barrier()
+        layer.close()
+    report["fused_gemm_reduce_scatter_ok"] = all(rs_ok)
 
     flags = torch.tensor([float(all(v for k, v in report.items() if k != "world"))], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)

@@ -430,3 +430,19 @@ def test_flag_barrier_timeout_reports_status(cuda_device):
     assert pad[3 * 8 + 1].item() == 1
     assert torch.equal(K.gemm(torch.ones(128, 64, device=cuda_device).bfloat16(), torch.ones(128, 64, device=cuda_device).bfloat16()),
                        torch.full((128, 128), 64.0, device=cuda_device).bfloat16())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,Kd,all_reduce", [(128, 256, 64, False), (384, 1000, 520, False), (256, 4096, 2048, True)])
+def test_gemm_reduce_scatter_kernel_single_rank(cuda_device, M, N, Kd, all_reduce):
+    """With one rank the fused row-parallel kernel must equal a plain GEMM (its push and reduce phases
+    then run against local memory only)."""
+    from rpeg_b200.parallel.tp import RowParallelLinear
+    x = torch.randn(M, Kd, device=cuda_device).bfloat16()
+    w = (torch.randn(N, Kd, device=cuda_device) * 0.1).bfloat16()
+    layer = RowParallelLinear(w, max_rows=512, device=cuda_device, all_reduce=all_reduce)
+    for _ in range(2):
+        y = layer.forward(x)
+        K.check_status()
+        assert _rel_err(y, x.float() @ w.float().t()) < 1e-2
+    layer.close()
