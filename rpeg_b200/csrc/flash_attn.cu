@@ -332,7 +332,7 @@ namespace rpeg {
 // dQ_i is drained by the same threads (now lane = query row) with fp32 vector atomics into a
 // [T, H*128] fp32 accumulator; dK (scaled) and dV are written once at the end as bf16 into the
 // K and V column blocks of a packed gradient buffer with the same layout as qkv.
-// D_q = rowsum(dO * O) comes from a small pre-pass. Needs H == Hkv.
+// D_q = rowsum(dO * O) comes from a small pre-pass. Grouped-query attention (H a multiple of Hkv) is supported.
 constexpr int FB_SMEM = FA_TILE_BYTES * 5 + 1024 + 1024 + 256;
 
 __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
@@ -355,14 +355,18 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid
                       const int* __restrict__ cu_seqlens, const float* __restrict__ lse,
                       const float* __restrict__ dvec, float* __restrict__ dq_acc,
                       __nv_bfloat16* __restrict__ dqkv, int ld_dqkv, int T, int H, int q_col0, int k_col0,
-                      int v_col0, float scale, int* status) {
-  const int b = blockIdx.z, h = blockIdx.y, kt = blockIdx.x;  // early key tiles carry the most work
+                      int v_col0, float scale, int Hkv, int* status) {
+  // One CTA per (key tile, KV head, sequence). With grouped-query attention the G = H / Hkv query heads that
+  // share this KV head are processed one after the other into the same dK / dV accumulators.
+  const int b = blockIdx.z, hk = blockIdx.y, kt = blockIdx.x;  // early key tiles carry the most work
+  const int G = H / Hkv;
   const int seq0 = cu_seqlens[b];
   const int L = cu_seqlens[b + 1] - seq0;
   const int k0 = kt * FA_BN;
   if (k0 >= L) return;
   const int n_qt = (L + FA_BM - 1) / FA_BM;
   const int n_iter = n_qt - kt;  // query tiles kt .. n_qt-1
+  const int n_total = n_iter * G;  // flattened (query head of the group, query tile)
   const float scale_log2 = scale * 1.4426950408889634f;
 
   extern __shared__ uint8_t smem_raw[];
@@ -407,12 +411,13 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid
       tma_prefetch_desc(&tmap_qkv);
       tma_prefetch_desc(&tmap_do);
       mbar_expect_tx(kv_full, 2 * FA_TILE_BYTES);
-      tma_load_2d(k_sm, &tmap_qkv, kv_full, k_col0 + h * FA_HD, seq0 + k0);
-      tma_load_2d(k_sm + 16384, &tmap_qkv, kv_full, k_col0 + h * FA_HD + 64, seq0 + k0);
-      tma_load_2d(v_sm, &tmap_qkv, kv_full, v_col0 + h * FA_HD, seq0 + k0);
-      tma_load_2d(v_sm + 16384, &tmap_qkv, kv_full, v_col0 + h * FA_HD + 64, seq0 + k0);
-      for (int it = 0; it < n_iter; ++it) {
-        const int q0 = (kt + it) * FA_BM;
+      tma_load_2d(k_sm, &tmap_qkv, kv_full, k_col0 + hk * FA_HD, seq0 + k0);
+      tma_load_2d(k_sm + 16384, &tmap_qkv, kv_full, k_col0 + hk * FA_HD + 64, seq0 + k0);
+      tma_load_2d(v_sm, &tmap_qkv, kv_full, v_col0 + hk * FA_HD, seq0 + k0);
+      tma_load_2d(v_sm + 16384, &tmap_qkv, kv_full, v_col0 + hk * FA_HD + 64, seq0 + k0);
+      for (int it = 0; it < n_total; ++it) {
+        const int h = hk * G + it / n_iter;
+        const int q0 = (kt + it % n_iter) * FA_BM;
         if (!mbar_wait(qdo_empty, (static_cast<uint32_t>(it) & 1u) ^ 1u, abort_flag, status, 600)) break;
         mbar_expect_tx(qdo_full, 2 * FA_TILE_BYTES);
         tma_load_2d(q_sm, &tmap_qkv, qdo_full, q_col0 + h * FA_HD, seq0 + q0);
@@ -429,7 +434,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid
       const uint32_t ka = smem_u32(k_sm), va = smem_u32(v_sm), qa = smem_u32(q_sm), da = smem_u32(do_sm),
                      dsa = smem_u32(ds_sm);
       bool ok = mbar_wait(kv_full, 0, abort_flag, status, 610);
-      for (int it = 0; it < n_iter && ok; ++it) {
+      for (int it = 0; it < n_total && ok; ++it) {
         const uint32_t ph = static_cast<uint32_t>(it) & 1u;
         if (!mbar_wait(qdo_full, ph, abort_flag, status, 611)) break;
         if (it > 0 && !mbar_wait(dq_drained, ph ^ 1u, abort_flag, status, 612)) break;
@@ -471,9 +476,10 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const int sm_tid = threadIdx.x - 64;  // 0..127
     bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    for (int it = 0; it < n_total && ok; ++it) {
       const uint32_t ph = static_cast<uint32_t>(it) & 1u;
-      const int q0 = (kt + it) * FA_BM;
+      const int h = hk * G + it / n_iter;
+      const int q0 = (kt + it % n_iter) * FA_BM;
       // per-query vectors of this tile (lse in log2 units); +inf lse turns invalid queries into p = 0
       {
         const int qi = q0 + sm_tid;
@@ -484,7 +490,7 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (!__all_sync(0xffffffffu, mbar_wait(s_done, ph, abort_flag, status, 620))) { ok = false; break; }
       tc_fence_after_sync();
-      const bool diag = (it == 0);
+      const bool diag = (it % n_iter == 0);
       uint8_t* ds_row = ds_sm + r * 128;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
@@ -550,8 +556,8 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid
     if (ok) {
       // dq_done of the last iteration also covers the last dV / dK accumulation
       tc_fence_after_sync();
-      __nv_bfloat16* dk_row = dqkv + static_cast<size_t>(seq0 + kj) * ld_dqkv + k_col0 + h * FA_HD;
-      __nv_bfloat16* dv_row = dqkv + static_cast<size_t>(seq0 + kj) * ld_dqkv + v_col0 + h * FA_HD;
+      __nv_bfloat16* dk_row = dqkv + static_cast<size_t>(seq0 + kj) * ld_dqkv + k_col0 + hk * FA_HD;
+      __nv_bfloat16* dv_row = dqkv + static_cast<size_t>(seq0 + kj) * ld_dqkv + v_col0 + hk * FA_HD;
 #pragma unroll 1
       for (int c = 0; c < 8; ++c) {
         uint32_t v[32];
@@ -611,7 +617,7 @@ extern "C" int rpeg_flash_attn_bwd(const void* qkv, int ld, int q_col0, int k_co
                                    float* dq_acc, void* dqkv, int ld_dqkv, int* status, void* stream_v) {
   using namespace rpeg;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
-  if (hd != FA_HD || H != Hkv) return -2;
+  if (hd != FA_HD || Hkv <= 0 || H % Hkv != 0) return -2;
   if ((ld | ld_dqkv | q_col0 | k_col0 | v_col0) & 7) return -3;
   if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(dout)) & 15) return -1;
   if (B <= 0 || T <= 0 || max_seqlen <= 0) return 0;
@@ -631,10 +637,10 @@ extern "C" int rpeg_flash_attn_bwd(const void* qkv, int ld, int q_col0, int k_co
   attn_bwd_prep_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(dout), dvec, T, H);
   if (cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(T) * H * FA_HD * sizeof(float), stream) != cudaSuccess) return -22;
-  dim3 grid((max_seqlen + FA_BN - 1) / FA_BN, H, B);
+  dim3 grid((max_seqlen + FA_BN - 1) / FA_BN, Hkv, B);
   flash_attn_bwd_kernel<<<grid, FA_THREADS, FB_SMEM, stream>>>(tm_qkv, tm_do, cu_seqlens, lse, dvec, dq_acc,
                                                               static_cast<__nv_bfloat16*>(dqkv), ld_dqkv, T, H, q_col0,
-                                                              k_col0, v_col0, scale, status);
+                                                              k_col0, v_col0, scale, Hkv, status);
   const long long n = static_cast<long long>(T) * (H * FA_HD / 4);
   dq_store_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dqkv),
                                                                              ld_dqkv, q_col0, T, H * FA_HD);

@@ -41,7 +41,9 @@ constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STAGES = 4;
 constexpr int TMEM_COLS = 2 * BN;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
+constexpr int EPI_ROW_BYTES = 128 + 16;            // 64 bf16 per row, padded so 16-byte accesses spread over the banks
+constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512 + 4 * EPI_WARP_BYTES;
 constexpr unsigned long long PEER_WAIT_NS = 10ull * 1000 * 1000 * 1000;
 
 struct Peers {
@@ -61,6 +63,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint64_t* tempty_bar = tfull_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_area = bar_area + 512;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = M / BM;                       // host guarantees M % (BM * world) == 0
@@ -85,12 +88,20 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   // Tile order: start with the row blocks of the NEXT rank and end with this rank's own, so remote
   // owners receive their partials early and the local partial (no NVLink) comes last.
+  // Inside an owner's segment, groups of 8 row blocks sweep N together so the A rows stay in L2.
   auto tile_coords = [&](int t, int& tm, int& tn) {
-    const int owner_step = t / (blocks_per_rank * n_tiles);
-    const int r = t - owner_step * blocks_per_rank * n_tiles;
+    constexpr int GROUP_M = 8;
+    const int seg = blocks_per_rank * n_tiles;
+    const int owner_step = t / seg;
+    const int r = t - owner_step * seg;
     const int owner = (rank + 1 + owner_step) % world;
-    tm = owner * blocks_per_rank + (r % blocks_per_rank);
-    tn = r / blocks_per_rank;
+    const int per_group = GROUP_M * n_tiles;
+    const int g = r / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(blocks_per_rank - first_m, GROUP_M);
+    const int rr = r - g * per_group;
+    tm = owner * blocks_per_rank + first_m + (rr % gsize);
+    tn = rr / gsize;
   };
 
   if (warp == 0) {
@@ -145,32 +156,45 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int tm, tn;
       tile_coords(w, tm, tn);
       const int owner = tm / blocks_per_rank;
-      const int local_row = (tm - owner * blocks_per_rank) * BM + quad * 32 + lane;
       const int n0 = tn * BN;
       if (!__all_sync(0xffffffffu, mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, status, 720))) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(buf * BN);
-      // owner's staging: [world][rows_per_rank][N] bf16; this rank writes slab `rank`
+      // owner's staging: [world][rows_per_rank][N] bf16; this rank writes slab `rank`. The accumulator is
+      // read one row per lane, so it goes through a small per-warp shared buffer and leaves as whole
+      // 128-byte row segments (4 rows per store instruction): NVLink moves full-size packets instead of
+      // one 16-byte fragment per lane.
       __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(stage.p[owner]) +
-                           (static_cast<size_t>(rank) * rows_per_rank + local_row) * N + n0;
+                           (static_cast<size_t>(rank) * rows_per_rank + (tm - owner * blocks_per_rank) * BM + quad * 32) * N + n0;
+      uint8_t* my_epi = epi_area + quad * EPI_WARP_BYTES;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_wait_ld();
-        if (n0 + c * 32 < N) {
+      for (int c = 0; c < BN / 64; ++c) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 64 + hh * 32, r);
+          tmem_wait_ld();
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            if (n0 + c * 32 + v * 8 < N) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o;
-            }
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+            *reinterpret_cast<uint4*>(my_epi + lane * EPI_ROW_BYTES + hh * 64 + v * 16) = o;
           }
         }
+        __syncwarp();
+        const int col_base = n0 + c * 64;
+        if (col_base < N) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int rr = 4 * j + (lane >> 3), ch = lane & 7;
+            const uint4 v = *reinterpret_cast<const uint4*>(my_epi + rr * EPI_ROW_BYTES + ch * 16);
+            if (col_base + ch * 8 < N) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rr) * N + c * 64 + ch * 8) = v;
+          }
+        }
+        __syncwarp();
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -188,6 +212,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
 
   // ---- phase 2: reduce the rows this rank owns
+  __syncwarp();
   __syncthreads();
   if (*abort_flag) {
     __nanosleep(200000);
@@ -195,7 +220,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const unsigned expect = epoch * static_cast<unsigned>(n_tiles * world * 4);
     const unsigned* my_ctr = static_cast<const unsigned*>(counters.p[rank]);
     const __nv_bfloat16* my_stage = static_cast<const __nv_bfloat16*>(stage.p[rank]);
-    const int chunks = (N + 2047) / 2048;            // a chunk: 128 rows x 2048 columns
+    constexpr int CHUNK = 512;                        // a work item: 128 rows x 512 columns
+    const int chunks = (N + CHUNK - 1) / CHUNK;
     const int items = blocks_per_rank * chunks;
     __shared__ int ready;
     for (int it = blockIdx.x; it < items; it += gridDim.x) {
@@ -216,24 +242,48 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int ok = ready;
       __syncthreads();
       if (!ok) break;
-      const int c0 = ch * 2048, c1 = min(N, c0 + 2048);
+      const int c0 = ch * CHUNK, c1 = min(N, c0 + CHUNK);
       const int vec_per_row = (c1 - c0) >> 3;
-      for (int i = threadIdx.x; i < BM * vec_per_row; i += THREADS) {
-        const int row = blk * BM + i / vec_per_row, col = c0 + (i % vec_per_row) * 8;
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int s = 0; s < world; ++s) {
-          const uint4 v = __ldcg(reinterpret_cast<const uint4*>(my_stage + (static_cast<size_t>(s) * rows_per_rank + row) * N + col));
-          const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
-          acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+      // four independent 16-byte vectors per thread and pass, all loads issued before the first use, so
+      // enough bytes are in flight to run this tail at memory speed
+      constexpr int UNROLL = 4;
+      const int total = BM * vec_per_row;
+      for (int i0 = threadIdx.x; i0 < total; i0 += THREADS * UNROLL) {
+        uint4 part[UNROLL][RPEG_MAX_PEERS];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int i = i0 + u * THREADS;
+          if (i < total) {
+            const int row = blk * BM + i / vec_per_row, col = c0 + (i % vec_per_row) * 8;
+#pragma unroll
+            for (int s = 0; s < RPEG_MAX_PEERS; ++s)
+              if (s < world)
+                part[u][s] = __ldcg(reinterpret_cast<const uint4*>(my_stage + (static_cast<size_t>(s) * rows_per_rank + row) * N + col));
+          }
         }
-        uint4 o;
-        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-        if (all_gather) {
-          const size_t off = (static_cast<size_t>(rank) * rows_per_rank + row) * ldo + col;
-          for (int q = 0; q < world; ++q) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[q]) + off) = o;
-        } else {
-          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[rank]) + static_cast<size_t>(row) * ldo + col) = o;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int i = i0 + u * THREADS;
+          if (i >= total) break;
+          const int row = blk * BM + i / vec_per_row, col = c0 + (i % vec_per_row) * 8;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int s = 0; s < RPEG_MAX_PEERS; ++s) {
+            if (s < world) {
+              const uint4 v = part[u][s];
+              const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+              acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          if (all_gather) {
+            const size_t off = (static_cast<size_t>(rank) * rows_per_rank + row) * ldo + col;
+            for (int q = 0; q < world; ++q) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[q]) + off) = o;
+          } else {
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[rank]) + static_cast<size_t>(row) * ldo + col) = o;
+          }
         }
       }
     }

@@ -211,6 +211,70 @@ rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   }
 }
 
+// Per-head RMSNorm ("QK-norm"): every (token, head) slice of width 128 inside a [T, ld] buffer at column
+// col0 is normalised in place, y = x * rstd * w with one weight vector w[128] shared by all heads.
+// One warp per (token, head); a lane owns 4 elements. rstd_out [T * nheads] keeps 1/rms for backward.
+__global__ void __launch_bounds__(256)
+headnorm_fwd_kernel(__nv_bfloat16* __restrict__ buf, int ld, int col0, int nheads, const __nv_bfloat16* __restrict__ w,
+                    float* __restrict__ rstd_out, long long rows, float eps) {
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (wid >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = wid / nheads;
+  const int h = static_cast<int>(wid % nheads);
+  __nv_bfloat16* p = buf + t * ld + col0 + h * 128 + lane * 4;
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y);
+  const float ss = warp_sum(a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y);
+  const float rstd = rsqrtf(ss * (1.f / 128.f) + eps);
+  if (lane == 0 && rstd_out) rstd_out[wid] = rstd;
+  const uint2 wv = *reinterpret_cast<const uint2*>(w + lane * 4);
+  const float2 w0 = unpack_bf16x2(wv.x), w1 = unpack_bf16x2(wv.y);
+  uint2 o;
+  o.x = pack_bf16x2(a.x * rstd * w0.x, a.y * rstd * w0.y);
+  o.y = pack_bf16x2(b.x * rstd * w1.x, b.y * rstd * w1.y);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
+// Backward of the per-head norm, in place on the gradient buffer: dbuf holds dy on entry and dx on exit;
+// x is the PRE-norm input in the same layout. dx = rstd * (w*dy - xhat * mean(w*dy*xhat)), dw += dy * xhat.
+__global__ void __launch_bounds__(256)
+headnorm_bwd_kernel(__nv_bfloat16* __restrict__ dbuf, int ldd, const __nv_bfloat16* __restrict__ x, int ldx, int col0,
+                    int nheads, const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                    float* __restrict__ dw, long long rows) {
+  __shared__ float dw_sm[128];
+  if (threadIdx.x < 128) dw_sm[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint2 wv = *reinterpret_cast<const uint2*>(w + lane * 4);
+  const float2 w0 = unpack_bf16x2(wv.x), w1 = unpack_bf16x2(wv.y);
+  for (long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; wid < rows; wid += warps_total) {
+    const long long t = wid / nheads;
+    const int h = static_cast<int>(wid % nheads);
+    const uint2 xv = *reinterpret_cast<const uint2*>(x + t * ldx + col0 + h * 128 + lane * 4);
+    __nv_bfloat16* dp = dbuf + t * ldd + col0 + h * 128 + lane * 4;
+    const uint2 dv = *reinterpret_cast<const uint2*>(dp);
+    const float r = rstd[wid];
+    const float2 x0 = unpack_bf16x2(xv.x), x1 = unpack_bf16x2(xv.y), d0 = unpack_bf16x2(dv.x), d1 = unpack_bf16x2(dv.y);
+    const float xh[4] = {x0.x * r, x0.y * r, x1.x * r, x1.y * r};
+    const float dy[4] = {d0.x, d0.y, d1.x, d1.y};
+    const float wd[4] = {w0.x * dy[0], w0.y * dy[1], w1.x * dy[2], w1.y * dy[3]};
+    const float m = warp_sum(wd[0] * xh[0] + wd[1] * xh[1] + wd[2] * xh[2] + wd[3] * xh[3]) * (1.f / 128.f);
+    uint2 o;
+    o.x = pack_bf16x2(r * (wd[0] - xh[0] * m), r * (wd[1] - xh[1] * m));
+    o.y = pack_bf16x2(r * (wd[2] - xh[2] * m), r * (wd[3] - xh[3] * m));
+    *reinterpret_cast<uint2*>(dp) = o;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] += dy[k] * xh[k];
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) atomicAdd(&dw_sm[lane * 4 + k], acc[k]);
+  __syncthreads();
+  if (threadIdx.x < 128) atomicAdd(&dw[threadIdx.x], dw_sm[threadIdx.x]);
+}
+
 // RoPE, rotate-half pairing (i, i + hd/2), applied in place to `nheads` heads of width hd that sit
 // at column offset `col0` of a [T, ld] bf16 buffer. cos/sin tables are fp32 [max_pos, hd/2].
 // sign = +1 forward, -1 backward (the transpose of a rotation is the rotation by -angle).
@@ -368,6 +432,29 @@ extern "C" int rpeg_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
       static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres_in),
       static_cast<__nv_bfloat16*>(dx), dw, T, d, rows_per_cta);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_headnorm_fwd(void* buf, int ld, int col0, int nheads, int hd, const void* w, float* rstd, int T,
+                                 float eps, void* stream) {
+  if (hd != 128 || (ld & 3) || (col0 & 3)) return -2;
+  const long long rows = static_cast<long long>(T) * nheads;
+  if (rows <= 0) return 0;
+  headnorm_fwd_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, STREAM(stream)>>>(
+      static_cast<__nv_bfloat16*>(buf), ld, col0, nheads, static_cast<const __nv_bfloat16*>(w), rstd, rows, eps);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_headnorm_bwd(void* dbuf, int ldd, const void* x, int ldx, int col0, int nheads, int hd, const void* w,
+                                 const float* rstd, float* dw, int T, void* stream) {
+  if (hd != 128 || ((ldd | ldx | col0) & 3)) return -2;
+  const long long rows = static_cast<long long>(T) * nheads;
+  if (rows <= 0) return 0;
+  long long blocks = (rows * 32 + 255) / 256;
+  if (blocks > 1184) blocks = 1184;
+  headnorm_bwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, STREAM(stream)>>>(
+      static_cast<__nv_bfloat16*>(dbuf), ldd, static_cast<const __nv_bfloat16*>(x), ldx, col0, nheads,
+      static_cast<const __nv_bfloat16*>(w), rstd, dw, rows);
   return LAUNCH_OK();
 }
 

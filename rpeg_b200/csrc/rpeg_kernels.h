@@ -22,6 +22,10 @@ int rpeg_rmsnorm_fwd(const void* x, const void* res, const void* w, void* h_out,
                      int d, float eps, void* stream);
 int rpeg_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_in,
                      void* dx, float* dw, int T, int d, void* stream);
+int rpeg_headnorm_fwd(void* buf, int ld, int col0, int nheads, int hd, const void* w, float* rstd, int T, float eps,
+                      void* stream);
+int rpeg_headnorm_bwd(void* dbuf, int ldd, const void* x, int ldx, int col0, int nheads, int hd, const void* w,
+                      const float* rstd, float* dw, int T, void* stream);
 int rpeg_rope(void* buf, const int* pos, const float* cos_t, const float* sin_t, int T, int ld, int col0,
               int nheads, int hd, int backward, void* stream);
 int rpeg_swiglu_fwd(const void* gu, void* out, long long T, int f, void* stream);

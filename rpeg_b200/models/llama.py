@@ -40,6 +40,10 @@ class LlamaConfig:
     max_pos: int = 4096
     lm_head: bool = True
     scalar_head: bool = False
+    qk_norm: bool = False               # per-head RMSNorm on queries and keys before RoPE (Qwen3)
+    tie_embeddings: bool = False        # the LM head shares the embedding matrix
+    rope_scaling_factor: float = 1.0    # llama3 long-context frequency scaling
+    family: str = "llama"
 
     @property
     def q_width(self) -> int:
@@ -63,6 +67,13 @@ class LlamaConfig:
     @classmethod
     def llama13b(cls, **kw) -> "LlamaConfig":
         return cls(40, 5120, 13824, 40, 40, 128, 32000, **kw)
+
+    @classmethod
+    def qwen3_8b(cls, **kw) -> "LlamaConfig":
+        base = dict(n_layers=36, d_model=4096, d_ff=12288, n_heads=32, n_kv_heads=8, head_dim=128, vocab=151936, rms_eps=1e-6,
+                    rope_theta=1e6, qk_norm=True, family="qwen3")
+        base.update(kw)
+        return cls(**base)
 
     @classmethod
     def tiny(cls, **kw) -> "LlamaConfig":
@@ -93,12 +104,15 @@ class ParamLayout:
         for i in range(cfg.n_layers):
             add(f"l{i}.attn_norm", d)
             add(f"l{i}.wqkv", cfg.qkv_width, d)
+            if cfg.qk_norm:
+                add(f"l{i}.q_norm", cfg.head_dim)
+                add(f"l{i}.k_norm", cfg.head_dim)
             add(f"l{i}.wo", d, cfg.q_width)
             add(f"l{i}.mlp_norm", d)
             add(f"l{i}.w_gate_up", 2 * f, d)
             add(f"l{i}.w_down", d, f)
         add("final_norm", d)
-        if cfg.lm_head:
+        if cfg.lm_head and not cfg.tie_embeddings:
             add("lm_head", cfg.vocab, d)
         if cfg.scalar_head:
             add("scalar_head.w", d)
@@ -148,7 +162,11 @@ class LlamaModel:
             self.g = grads if grads is not None else torch.zeros(self.layout.total, dtype=torch.float32, device=self.device)
         self.p = {name: self.layout.view(self.w, name) for name in self.layout.entries}
         self.gp = {name: self.layout.view(self.g, name) for name in self.layout.entries} if self.g is not None else {}
-        self.cos_t, self.sin_t = K.rope_tables(cfg.max_pos, cfg.head_dim, cfg.rope_theta, self.device)
+        if cfg.lm_head and cfg.tie_embeddings:      # one matrix, two uses: both gradients accumulate into it
+            self.p["lm_head"] = self.p["embed"]
+            if self.g is not None:
+                self.gp["lm_head"] = self.gp["embed"]
+        self.cos_t, self.sin_t = K.rope_tables(cfg.max_pos, cfg.head_dim, cfg.rope_theta, self.device, cfg.rope_scaling_factor)
         self._ws: Optional[torch.Tensor] = None  # split-K scratch for decode GEMMs
         if weights is None:
             self.init_weights(seed)
@@ -185,6 +203,15 @@ class LlamaModel:
     def _lin(self, x: torch.Tensor, w: torch.Tensor, decode: bool = False) -> torch.Tensor:
         return K.gemm(x, w, workspace=self._workspace() if decode else None)
 
+    def _qk_norm(self, i: int, qkv: torch.Tensor, keep_pre: bool):
+        """Per-head RMSNorm of the query and key heads in place. Returns what backward needs (the
+        pre-norm q|k columns and the two rstd tensors) or None."""
+        cfg, p = self.cfg, self.p
+        pre = qkv[:, : cfg.q_width + cfg.kv_width].clone() if keep_pre else None
+        rq = K.headnorm_fwd_(qkv, 0, cfg.n_heads, cfg.head_dim, p[f"l{i}.q_norm"], cfg.rms_eps, want_rstd=keep_pre)
+        rk = K.headnorm_fwd_(qkv, cfg.q_width, cfg.n_kv_heads, cfg.head_dim, p[f"l{i}.k_norm"], cfg.rms_eps, want_rstd=keep_pre)
+        return (pre, rq, rk) if keep_pre else None
+
     # ------------------------------------------------------------------ full-sequence forward
     def _layer_fwd(self, i: int, res: torch.Tensor, delta: Optional[torch.Tensor], ctx: _FwdCtx, keep: bool):
         """One decoder layer on packed tokens. Input is the residual stream as ``res (+ delta)``;
@@ -197,6 +224,7 @@ class LlamaModel:
         else:
             x, rstd1, h = K.rmsnorm_fwd(delta, p[f"l{i}.attn_norm"], cfg.rms_eps, residual=res, want_sum=True)
         qkv = K.gemm(x, p[f"l{i}.wqkv"])
+        qkn = self._qk_norm(i, qkv, keep and self.recompute == "none") if cfg.qk_norm else None
         K.rope_(qkv, ctx.pos, self.cos_t, self.sin_t, 0, cfg.n_heads, cfg.head_dim)
         K.rope_(qkv, ctx.pos, self.cos_t, self.sin_t, cfg.q_width, cfg.n_kv_heads, cfg.head_dim)
         attn, lse = K.flash_attn_fwd(qkv, 0, cfg.q_width, cfg.q_width + cfg.kv_width, ctx.cu_seqlens, ctx.max_seqlen,
@@ -209,7 +237,7 @@ class LlamaModel:
         if keep:
             saved = None
             if self.recompute == "none":
-                saved = dict(x=x, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, h1=h1, x2=x2, rstd2=rstd2, gu=gu, act=act)
+                saved = dict(x=x, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, h1=h1, x2=x2, rstd2=rstd2, gu=gu, act=act, qkn=qkn)
             ctx.layers.append(_LayerCtx(h_in=h, saved=saved))
         return h1, dn, qkv
 
@@ -238,6 +266,7 @@ class LlamaModel:
         if s is None:  # recompute the layer from its input
             x, rstd1, _ = K.rmsnorm_fwd(h, p[f"l{i}.attn_norm"], cfg.rms_eps)
             qkv = K.gemm(x, p[f"l{i}.wqkv"])
+            qkn = self._qk_norm(i, qkv, True) if cfg.qk_norm else None
             K.rope_(qkv, ctx.pos, self.cos_t, self.sin_t, 0, cfg.n_heads, cfg.head_dim)
             K.rope_(qkv, ctx.pos, self.cos_t, self.sin_t, cfg.q_width, cfg.n_kv_heads, cfg.head_dim)
             attn, lse = K.flash_attn_fwd(qkv, 0, cfg.q_width, cfg.q_width + cfg.kv_width, ctx.cu_seqlens,
@@ -250,6 +279,7 @@ class LlamaModel:
         else:
             x, rstd1, qkv, attn, lse = s["x"], s["rstd1"], s["qkv"], s["attn"], s["lse"]
             h1, x2, rstd2, gu, act = s["h1"], s["x2"], s["rstd2"], s["gu"], s["act"]
+            qkn = s.get("qkn")
         # MLP
         d_act = K.gemm(d_out, p[f"l{i}.w_down"], trans_b=True)
         K.gemm(d_out, act, trans_a=True, trans_b=True, out=g[f"l{i}.w_down"], accumulate=True)
@@ -269,6 +299,13 @@ class LlamaModel:
         del d_attn, attn, qkv
         K.rope_(d_qkv, ctx.pos, self.cos_t, self.sin_t, 0, cfg.n_heads, cfg.head_dim, backward=True)
         K.rope_(d_qkv, ctx.pos, self.cos_t, self.sin_t, cfg.q_width, cfg.n_kv_heads, cfg.head_dim, backward=True)
+        if cfg.qk_norm:
+            pre, rq, rk = qkn
+            for name, col0, nh, r in (("q_norm", 0, cfg.n_heads, rq), ("k_norm", cfg.q_width, cfg.n_kv_heads, rk)):
+                dw = torch.zeros(cfg.head_dim, dtype=torch.float32, device=self.device)
+                K.headnorm_bwd_(d_qkv, pre, col0, nh, cfg.head_dim, p[f"l{i}.{name}"], r, dw)
+                g[f"l{i}.{name}"].add_(dw)
+            del pre, rq, rk, qkn
         d_x = K.gemm(d_qkv, p[f"l{i}.wqkv"], trans_b=True)
         K.gemm(d_qkv, x, trans_a=True, trans_b=True, out=g[f"l{i}.wqkv"], accumulate=True)
         del d_qkv, x
@@ -278,8 +315,6 @@ class LlamaModel:
         """Accumulate parameter gradients given ``d loss / d xf`` (``xf`` = output of ``forward``)."""
         if self.g is None:
             raise RuntimeError("model was built without gradient storage (trainable=False)")
-        if self.cfg.n_heads != self.cfg.n_kv_heads:
-            raise NotImplementedError("attention backward needs n_heads == n_kv_heads")
         d_h = K.rmsnorm_bwd(d_xf, ctx.h_last, self.p["final_norm"], ctx.rstd_f, self.gp["final_norm"])
         ctx.h_last = None
         for i in reversed(range(self.cfg.n_layers)):
@@ -351,6 +386,8 @@ class LlamaModel:
             else:
                 x, _, h = K.rmsnorm_fwd(delta, p[f"l{i}.attn_norm"], cfg.rms_eps, residual=res, want_sum=True)
             qkv = K.gemm(x, p[f"l{i}.wqkv"], workspace=ws)
+            if cfg.qk_norm:
+                self._qk_norm(i, qkv, False)
             K.rope_kv_append_(qkv, 0, cfg.q_width, cfg.q_width + cfg.kv_width, slot_ids, pos, self.cos_t, self.sin_t,
                               page_table, kcache[i], vcache[i], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
             attn = K.paged_decode_attn(qkv, 0, kcache[i], vcache[i], page_table, seq_len, cfg.n_heads, cfg.n_kv_heads,

@@ -115,8 +115,19 @@ def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.
     return dx
 
 
-def rope_tables(max_pos: int, head_dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+def rope_tables(max_pos: int, head_dim: int, theta: float, device, scaling_factor: float = 1.0,
+                original_max_pos: int = 8192) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables ``[max_pos, head_dim/2]``. ``scaling_factor > 1`` applies the llama3 frequency
+    scaling (low_freq_factor 1, high_freq_factor 4): long wavelengths are divided by the factor, short
+    ones kept, the band in between interpolated."""
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    if scaling_factor > 1.0:
+        low, high = 1.0, 4.0
+        wavelen = 2 * math.pi / inv
+        smooth = ((original_max_pos / wavelen) - low) / (high - low)
+        mid = (1 - smooth) * inv / scaling_factor + smooth * inv
+        inv = torch.where(wavelen > original_max_pos / low, inv / scaling_factor,
+                          torch.where(wavelen < original_max_pos / high, inv, mid))
     ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
     return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
 
@@ -127,6 +138,26 @@ def rope_(buf: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torc
     _req(buf, torch.bfloat16, "buf")
     check(lib().rpeg_rope(buf.data_ptr(), pos.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), buf.shape[0],
                           buf.stride(0), col0, nheads, head_dim, int(backward), _stream()), "rpeg_rope")
+
+
+def headnorm_fwd_(buf: torch.Tensor, col0: int, nheads: int, head_dim: int, w: torch.Tensor, eps: float,
+                  want_rstd: bool = True) -> torch.Tensor | None:
+    """RMS-normalise every (row, head) slice of ``buf[:, col0 : col0 + nheads*head_dim]`` in place with the
+    shared weight ``w [head_dim]`` (QK-norm). Returns ``rstd [T, nheads]`` for the backward pass."""
+    _req(buf, torch.bfloat16, "buf")
+    T = buf.shape[0]
+    rstd = torch.empty((T, nheads), dtype=torch.float32, device=buf.device) if want_rstd else None
+    check(lib().rpeg_headnorm_fwd(buf.data_ptr(), buf.stride(0), col0, nheads, head_dim, w.data_ptr(), _ptr(rstd), T, eps,
+                                  _stream()), "rpeg_headnorm_fwd")
+    return rstd
+
+
+def headnorm_bwd_(dbuf: torch.Tensor, x_pre: torch.Tensor, col0: int, nheads: int, head_dim: int, w: torch.Tensor,
+                  rstd: torch.Tensor, dw: torch.Tensor) -> None:
+    """In place on ``dbuf`` (dy -> dx) for the slices normalised by ``headnorm_fwd_``; ``x_pre`` holds the
+    pre-norm values in the same column layout; ``dw [head_dim]`` fp32 is accumulated."""
+    check(lib().rpeg_headnorm_bwd(dbuf.data_ptr(), dbuf.stride(0), x_pre.data_ptr(), x_pre.stride(0), col0, nheads, head_dim,
+                                  w.data_ptr(), rstd.data_ptr(), dw.data_ptr(), dbuf.shape[0], _stream()), "rpeg_headnorm_bwd")
 
 
 def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:

@@ -1,9 +1,9 @@
 """Benchmark of the fused row-parallel linear against GEMM + NCCL, one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29591 \\
-        -m rpeg_b200.parallel.tp_bench --rows 16384 --n 4096 --k 11008
+        -m rpeg_b200.parallel.tp_bench --rows 16384 --out-features 4096 --in-features 11008
 
-``--k`` is the full contraction size (each rank holds k / world of it). Both arms are timed on the
+``--in-features`` is the full contraction size (each rank holds 1 / world of it). Both arms are timed on the
 device with CUDA events (3 warm-up, 10 timed, median; max over ranks); between iterations the inputs
 alternate between two buffers larger than L2 in total. Prints one JSON line with the times, the
 roofline target = max(FLOPs / GEMM peak, NVLink bytes / link bandwidth) and achieved / target.
@@ -23,8 +23,8 @@ import torch.distributed as dist
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=16384)
-    ap.add_argument("--n", type=int, default=4096)
-    ap.add_argument("--k", type=int, default=11008)
+    ap.add_argument("--out-features", type=int, default=4096)
+    ap.add_argument("--in-features", type=int, default=11008)
     ap.add_argument("--all-reduce", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--peak-tflops", type=float, default=1608.7)
@@ -39,8 +39,8 @@ def main(argv=None) -> int:
     dist.init_process_group("nccl", device_id=dev)
     from ..ops import kernels as K
     from .tp import RowParallelLinear
-    kp = args.k // world // 8 * 8
-    w = (torch.randn(args.n, kp, device=dev) * 0.02).bfloat16()
+    kp = args.in_features // world // 8 * 8
+    w = (torch.randn(args.out_features, kp, device=dev) * 0.02).bfloat16()
     xs = [torch.randn(args.rows, kp, device=dev).bfloat16() for _ in range(2)]
     layer = RowParallelLinear(w, max_rows=args.rows, device=dev, all_reduce=args.all_reduce)
 
@@ -65,12 +65,12 @@ def main(argv=None) -> int:
     K.check_status()
     t_unfused = timed(layer.forward_unfused)
     t_gemm = timed(lambda x: K.gemm(x, w))
-    flops = 2.0 * args.rows * args.n * kp
+    flops = 2.0 * args.rows * args.out_features * kp
     factor = 2.0 if args.all_reduce else 1.0
-    link_bytes = factor * (world - 1) / world * args.rows * args.n * 2           # bf16 partials leaving one GPU
+    link_bytes = factor * (world - 1) / world * args.rows * args.out_features * 2           # bf16 partials leaving one GPU
     target = max(flops / (args.peak_tflops * 1e12), link_bytes / (args.link_gbs * 1e9))
     if rank == 0:
-        print(json.dumps({"world": world, "rows": args.rows, "n": args.n, "k_per_rank": kp, "all_reduce": args.all_reduce,
+        print(json.dumps({"world": world, "rows": args.rows, "n": args.out_features, "k_per_rank": kp, "all_reduce": args.all_reduce,
                           "fused_ms": round(t_fused * 1e3, 4), "gemm_plus_nccl_ms": round(t_unfused * 1e3, 4),
                           "gemm_only_ms": round(t_gemm * 1e3, 4), "speedup_vs_unfused": round(t_unfused / t_fused, 3),
                           "roofline_target_ms": round(target * 1e3, 4), "achieved_over_target": round(target / t_fused, 4),

@@ -347,29 +347,32 @@ def test_flash_attn_fwd(cuda_device, lens, H, Hkv):
 
 
 @pytest.mark.parametrize("lens", [[128], [5, 130, 257], [1000, 31, 384]])
-def test_flash_attn_bwd(cuda_device, lens):
-    H, hd = 4, 128
+@pytest.mark.parametrize("H,Hkv", [(4, 4), (4, 2), (8, 2)])
+def test_flash_attn_bwd(cuda_device, lens, H, Hkv):
+    hd = 128
+    G = H // Hkv
     T = sum(lens)
-    qkv = torch.randn(T, 3 * H * hd, device=cuda_device).bfloat16()
+    kc0, vc0, width = H * hd, (H + Hkv) * hd, (H + 2 * Hkv) * hd
+    qkv = torch.randn(T, width, device=cuda_device).bfloat16()
     dout = torch.randn(T, H * hd, device=cuda_device).bfloat16()
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=cuda_device, dtype=torch.int32)
-    out, lse = K.flash_attn_fwd(qkv, 0, H * hd, 2 * H * hd, cu, max(lens), H, H, hd)
-    dqkv = K.flash_attn_bwd(qkv, 0, H * hd, 2 * H * hd, out, dout, lse, cu, max(lens), H, H, hd)
+    out, lse = K.flash_attn_fwd(qkv, 0, kc0, vc0, cu, max(lens), H, Hkv, hd)
+    dqkv = K.flash_attn_bwd(qkv, 0, kc0, vc0, out, dout, lse, cu, max(lens), H, Hkv, hd)
     K.check_status()
     x = qkv.float().clone().requires_grad_(True)
     off = 0
     outs = []
     for l in lens:
-        q = x[off:off + l, :H * hd].view(l, H, hd).transpose(0, 1)
-        k = x[off:off + l, H * hd:2 * H * hd].view(l, H, hd).transpose(0, 1)
-        v = x[off:off + l, 2 * H * hd:].view(l, H, hd).transpose(0, 1)
+        q = x[off:off + l, :kc0].view(l, H, hd).transpose(0, 1)
+        k = x[off:off + l, kc0:vc0].view(l, Hkv, hd).transpose(0, 1).repeat_interleave(G, 0)
+        v = x[off:off + l, vc0:].view(l, Hkv, hd).transpose(0, 1).repeat_interleave(G, 0)
         s = q @ k.transpose(1, 2) / math.sqrt(hd)
         s = s.masked_fill(torch.triu(torch.ones(l, l, device=cuda_device, dtype=torch.bool), 1), float("-inf"))
         outs.append((torch.softmax(s, -1) @ v).transpose(0, 1).reshape(l, H * hd))
         off += l
     torch.cat(outs).backward(dout.float())
-    for name, lo in (("dq", 0), ("dk", H * hd), ("dv", 2 * H * hd)):
-        assert _rel_err(dqkv[:, lo:lo + H * hd], x.grad[:, lo:lo + H * hd]) < 2e-2, name
+    for name, lo, hi in (("dq", 0, kc0), ("dk", kc0, vc0), ("dv", vc0, width)):
+        assert _rel_err(dqkv[:, lo:hi], x.grad[:, lo:hi]) < 2e-2, name
 
 
 @pytest.mark.gpu
@@ -446,3 +449,26 @@ def test_gemm_reduce_scatter_kernel_single_rank(cuda_device, M, N, Kd, all_reduc
         K.check_status()
         assert _rel_err(y, x.float() @ w.float().t()) < 1e-2
     layer.close()
+
+
+@pytest.mark.gpu
+def test_headnorm_fwd_bwd(cuda_device):
+    T, H, hd, col0 = 37, 6, 128, 128
+    ld = col0 + H * hd + 64
+    x = torch.randn(T, ld, device=cuda_device).bfloat16()
+    w = (1 + 0.1 * torch.randn(hd, device=cuda_device)).bfloat16()
+    dy = torch.randn(T, ld, device=cuda_device).bfloat16()
+    y = x.clone()
+    rstd = K.headnorm_fwd_(y, col0, H, hd, w, 1e-6)
+    xr = x[:, col0:col0 + H * hd].float().view(T, H, hd).requires_grad_(True)
+    wr = w.float().requires_grad_(True)
+    ref = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    assert _rel_err(y[:, col0:col0 + H * hd], ref.reshape(T, -1)) < 1e-2
+    assert torch.equal(y[:, :col0], x[:, :col0]) and torch.equal(y[:, col0 + H * hd:], x[:, col0 + H * hd:])
+    ref.backward(dy[:, col0:col0 + H * hd].float().view(T, H, hd))
+    d = dy.clone()
+    dw = torch.zeros(hd, dtype=torch.float32, device=cuda_device)
+    K.headnorm_bwd_(d, x, col0, H, hd, w, rstd, dw)
+    assert _rel_err(d[:, col0:col0 + H * hd], xr.grad.reshape(T, -1)) < 2e-2
+    assert _rel_err(dw, wr.grad) < 2e-2
+    assert torch.equal(d[:, :col0], dy[:, :col0])

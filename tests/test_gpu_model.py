@@ -35,9 +35,13 @@ def _ref_forward(model: LlamaModel, params, tokens, lens):
         for i in range(cfg.n_layers):
             x = norm(h, params[f"l{i}.attn_norm"])
             qkv = x @ params[f"l{i}.wqkv"].t()
-            q = rope(qkv[:, :cfg.q_width].view(L, cfg.n_heads, 128))
-            k = rope(qkv[:, cfg.q_width:cfg.q_width + cfg.kv_width].view(L, cfg.n_kv_heads, 128))
-            v = qkv[:, cfg.q_width + cfg.kv_width:].view(L, cfg.n_kv_heads, 128)
+            q = qkv[:, :cfg.q_width].view(L, cfg.n_heads, 128)
+            k = qkv[:, cfg.q_width:cfg.q_width + cfg.kv_width].view(L, cfg.n_kv_heads, 128)
+            if cfg.qk_norm:
+                q, k = norm(q, params[f"l{i}.q_norm"]), norm(k, params[f"l{i}.k_norm"])
+            G = cfg.n_heads // cfg.n_kv_heads
+            q, k = rope(q), rope(k).repeat_interleave(G, 1)
+            v = qkv[:, cfg.q_width + cfg.kv_width:].view(L, cfg.n_kv_heads, 128).repeat_interleave(G, 1)
             s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(128)
             s = s.masked_fill(torch.triu(torch.ones(L, L, dtype=torch.bool, device=h.device), 1), float("-inf"))
             a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(L, cfg.q_width)
@@ -54,10 +58,11 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
-@pytest.mark.parametrize("recompute", ["full", "none"])
-def test_forward_backward_matches_pytorch(cuda_device, recompute):
+@pytest.mark.parametrize("recompute,variant", [("full", "llama"), ("none", "llama"), ("full", "qwen3"), ("none", "qwen3")])
+def test_forward_backward_matches_pytorch(cuda_device, recompute, variant):
     torch.manual_seed(0)
-    cfg = LlamaConfig.tiny()
+    cfg = LlamaConfig.tiny() if variant == "llama" else LlamaConfig.tiny(
+        d_model=512, n_heads=4, n_kv_heads=2, qk_norm=True, tie_embeddings=True, rope_scaling_factor=8.0, rms_eps=1e-6, family="qwen3")
     model = LlamaModel(cfg, cuda_device, trainable=True, recompute=recompute, seed=1)
     lens = [37, 130, 200]
     T = sum(lens)
@@ -72,14 +77,21 @@ def test_forward_backward_matches_pytorch(cuda_device, recompute):
     model.backward(ctx, d_xf)
     K.check_status()
 
-    params = {n: v.float().clone().requires_grad_(True) for n, v in model.p.items()}
+    params = {n: v.float().clone().requires_grad_(True) for n, v in model.p.items() if not (cfg.tie_embeddings and n == "lm_head")}
+    if cfg.tie_embeddings:
+        params["lm_head"] = params["embed"]
+        for i in range(cfg.n_layers):            # make the norm weights non-trivial
+            assert f"l{i}.q_norm" in params
     xf_ref = _ref_forward(model, params, tokens, lens)
     lp_ref = torch.log_softmax(xf_ref @ params["lm_head"].t(), -1).gather(1, targets.long()[:, None])[:, 0]
     (lp_ref * coef).sum().backward()
 
     assert _rel(xf, xf_ref) < 2e-2
     assert torch.allclose(logp, lp_ref, atol=5e-2)
-    for name in ("lm_head", "l1.w_down", "l1.w_gate_up", "l1.wo", "l1.wqkv", "l0.wqkv", "l0.mlp_norm", "final_norm", "embed"):
+    names = ["l1.w_down", "l1.w_gate_up", "l1.wo", "l1.wqkv", "l0.wqkv", "l0.mlp_norm", "final_norm", "embed"]
+    names += ["l0.q_norm", "l1.k_norm"] if cfg.qk_norm else []
+    names += [] if cfg.tie_embeddings else ["lm_head"]
+    for name in names:
         assert _rel(model.gp[name], params[name].grad) < 6e-2, name
 
 

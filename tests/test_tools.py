@@ -96,3 +96,63 @@ def test_calibrate_fits():
     a, b = c.fit_alpha_beta([1e5, 2e5, 1e6, 1e7, 1e8], [2e-5 + s * 1.3e-12 for s in (1e5, 2e5, 1e6, 1e7, 1e8)])
     assert a == pytest.approx(2e-5, rel=1e-3) and b == pytest.approx(1.3e-12, rel=1e-6)
     assert c.fit_gemm_m_half([128, 1024, 8192], [128 / 224, 1024 / 1120, 8192 / 8288]) == pytest.approx(96.0)
+
+
+def test_model_registry_and_hf_helpers(tmp_path):
+    import struct
+    from rpeg_b200.models.registry import config_from_hf, hf_config_dict
+    from rpeg_b200.runtime.errors import RuntimeConfigError
+    from rpeg_b200.runtime.hf import (model_spec_from_hf_config, require_pinned_revision, resolve_model_path, safetensors_header,
+                                      safetensors_parameter_count)
+    llama3 = {"model_type": "llama", "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "num_hidden_layers": 32,
+              "intermediate_size": 14336, "vocab_size": 128256, "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 131072,
+              "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                               "original_max_position_embeddings": 8192}}
+    c = config_from_hf(llama3, max_pos=4096)
+    assert (c.n_kv_heads, c.rope_scaling_factor, c.qk_norm, c.family, c.max_pos) == (8, 8.0, False, "llama", 4096)
+    q = config_from_hf({"model_type": "qwen3", "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+                        "num_hidden_layers": 36, "intermediate_size": 12288, "vocab_size": 151936, "tie_word_embeddings": False})
+    assert q.qk_norm and q.rms_eps == 1e-6 and q.rope_theta == 1e6
+    assert config_from_hf(hf_config_dict(q)) == q
+    for bad in ({**llama3, "model_type": "mixtral"}, {**llama3, "attention_bias": True}, {**llama3, "hidden_size": 4096, "num_attention_heads": 64},
+                {**llama3, "rope_scaling": {"rope_type": "yarn", "factor": 4.0}}):
+        with pytest.raises(RuntimeConfigError):
+            config_from_hf(bad)
+    spec = model_spec_from_hf_config(llama3)
+    assert (spec.L, spec.d, spec.d_ff, spec.V) == (32, 4096, 14336, 128256)
+    with pytest.raises(RuntimeConfigError):
+        require_pinned_revision("org/model", "main")
+    assert require_pinned_revision("org/model", "a" * 40) == "a" * 40
+    with pytest.raises(RuntimeConfigError):
+        resolve_model_path("hf", "org/model", None, "a" * 40)
+    # header-only parameter count on a hand-written safetensors file
+    header = json.dumps({"a": {"dtype": "BF16", "shape": [3, 4], "data_offsets": [0, 24]},
+                         "b": {"dtype": "BF16", "shape": [5], "data_offsets": [24, 34]}, "__metadata__": {"format": "pt"}}).encode()
+    (tmp_path / "m.safetensors").write_bytes(struct.pack("<Q", len(header)) + header + b"\0" * 34)
+    assert set(safetensors_header(tmp_path / "m.safetensors")) == {"a", "b", "__metadata__"}
+    assert safetensors_parameter_count(tmp_path) == 17
+
+
+def test_hf_weight_roundtrip_on_cpu(tmp_path):
+    import torch
+    from rpeg_b200.models.llama import LlamaConfig, ParamLayout
+    from rpeg_b200.runtime.hf import load_hf_weights, save_hf_weights
+
+    class Flat:                     # the part of LlamaModel the import/export touches, on the CPU
+        def __init__(self, cfg, fill):
+            self.cfg, self.layout = cfg, ParamLayout(cfg)
+            self.w = torch.zeros(self.layout.total, dtype=torch.bfloat16)
+            if fill:
+                self.w.copy_(torch.randn(self.layout.total).bfloat16())
+            self.p = {n: self.layout.view(self.w, n) for n in self.layout.entries}
+
+    cfg = LlamaConfig.tiny(n_heads=4, n_kv_heads=2, d_model=512, qk_norm=True, family="qwen3")
+    a, b = Flat(cfg, True), Flat(cfg, False)
+    save_hf_weights(a, tmp_path / "ckpt", shard_bytes=1 << 20)
+    assert len(list((tmp_path / "ckpt").glob("*.safetensors"))) > 1
+    n = load_hf_weights(b, tmp_path / "ckpt")
+    assert n == sum(int(v.numel()) for v in a.p.values())
+    for name in a.p:
+        assert torch.equal(a.p[name], b.p[name]), name
+    from rpeg_b200.models.registry import config_from_hf_path
+    assert config_from_hf_path(tmp_path / "ckpt", max_pos=cfg.max_pos) == cfg
