@@ -156,3 +156,26 @@ def test_hf_weight_roundtrip_on_cpu(tmp_path):
         assert torch.equal(a.p[name], b.p[name]), name
     from rpeg_b200.models.registry import config_from_hf_path
     assert config_from_hf_path(tmp_path / "ckpt", max_pos=cfg.max_pos) == cfg
+
+
+def test_experiment_generators_and_optimizer_bench(tmp_path):
+    sys.path.insert(0, os.path.join(ROOT, "experiments"))
+    import gen_ablation_configs as ab
+    import gen_scaling_configs as sc
+    import optimizer_bench as ob
+    from rpeg_b200.planner.pipeline import load_yaml, validate_config
+    assert sc.generate(tmp_path / "scaling") == 108
+    cfg = load_yaml(str(tmp_path / "scaling/both/128gpu_t896_tau2.yaml"))
+    validate_config(cfg)
+    assert cfg["hardware"]["racks"] * cfg["hardware"]["nodes_per_rack"] * cfg["hardware"]["gpus_per_node"] == 128
+    assert cfg["workload"]["gen_quantiles"] == [[0.5, 224], [0.85, 448], [1.0, 896]]
+    assert cfg["optimizer"]["staleness_candidates"] == {"actor": [2], "critic": [1]}
+    assert ab.generate(tmp_path / "ablation", ("tight",)) == 50
+    a1 = load_yaml(str(tmp_path / "ablation/A1_no_gen_inf_overlap/tight_16gpu_s3.yaml"))
+    base = load_yaml(str(tmp_path / "ablation/baseline/tight_16gpu_s3.yaml"))
+    assert "gen_quantiles" not in a1["workload"] and "gen_quantiles" in base["workload"] and a1["output"]["seed"] == 3
+    a1["workload"]["gen_quantiles"] = base["workload"]["gen_quantiles"]
+    a1["output"]["log_file"] = base["output"]["log_file"]
+    assert a1 == base                                     # nothing but the ablated knob differs
+    row = ob.bench_instance("micro2", seeds=2, evals=200)
+    assert row["space_size"] == 625 and row["worst_gap"] <= 0.03 and 0 < row["coverage"] <= 1
