@@ -137,6 +137,99 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(&dw[i], dw_sm[i]);
 }
 
+// Backward with fixed column ownership: 256 threads, thread t owns the 16-byte vectors t, t+256, ... of
+// every row its CTA walks, so the dw partial sums stay in registers for the whole kernel (one global
+// atomicAdd per column per CTA at the end) and the only per-row communication is the block-wide sum
+// of dy*w*x. The next row's operands are loaded before the current row's reduction completes.
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_row_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                       const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw, int T, int d) {
+  __shared__ float part[2][8];
+  const int nvec = d >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float wf[NV][8], acc[NV][8];
+  bool own[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * 256;
+    own[k] = i < nvec;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { wf[k][e] = 0.f; acc[k][e] = 0.f; }
+    if (own[k]) {
+      const uint4 wv = reinterpret_cast<const uint4*>(w)[i];
+      const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(pw[e]);
+        wf[k][2 * e] = f.x; wf[k][2 * e + 1] = f.y;
+      }
+    }
+  }
+  const float inv_d = 1.f / static_cast<float>(d);
+  int it = 0;
+  for (int row = blockIdx.x; row < T; row += gridDim.x, ++it) {
+    uint4 a[NV], b[NV], r[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * 256;
+      a[k] = b[k] = r[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (own[k]) {
+        a[k] = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * d)[i];
+        b[k] = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * d)[i];
+        if (dres_in) r[k] = reinterpret_cast<const uint4*>(dres_in + static_cast<size_t>(row) * d)[i];
+      }
+    }
+    const float rs = rstd[row];
+    float g[NV][8], xv[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const uint32_t *pa = reinterpret_cast<const uint32_t*>(&a[k]), *pb = reinterpret_cast<const uint32_t*>(&b[k]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 ga = unpack_bf16x2(pa[e]), xb = unpack_bf16x2(pb[e]);
+        g[k][2 * e] = ga.x; g[k][2 * e + 1] = ga.y; xv[k][2 * e] = xb.x; xv[k][2 * e + 1] = xb.y;
+        dot += ga.x * wf[k][2 * e] * xb.x + ga.y * wf[k][2 * e + 1] * xb.y;
+      }
+    }
+    dot = warp_sum(dot);
+    float* slot = part[it & 1];
+    if (lane == 0) slot[warp] = dot;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) tot += slot[k];
+    const float coef = tot * rs * rs * rs * inv_d;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (!own[k]) continue;
+      const uint32_t* pr = reinterpret_cast<const uint32_t*>(&r[k]);
+      uint4 o;
+      uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 rr = unpack_bf16x2(pr[e]);
+        const float o0 = rs * g[k][2 * e] * wf[k][2 * e] - xv[k][2 * e] * coef + rr.x;
+        const float o1 = rs * g[k][2 * e + 1] * wf[k][2 * e + 1] - xv[k][2 * e + 1] * coef + rr.y;
+        po[e] = pack_bf16x2(o0, o1);
+        acc[k][2 * e] += g[k][2 * e] * xv[k][2 * e] * rs;
+        acc[k][2 * e + 1] += g[k][2 * e + 1] * xv[k][2 * e + 1] * rs;
+      }
+      reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * d)[threadIdx.x + k * 256] = o;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    if (!own[k]) continue;
+    const int c0 = (threadIdx.x + k * 256) * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(&dw[c0 + e], acc[k][e]);
+  }
+}
+
 // Row-per-CTA variant: 256 threads keep the whole row in registers (NV 16-byte vectors per thread),
 // so x and res are read once and nothing is re-read for the second pass. Used for d <= 8192.
 template <int NV>
@@ -420,6 +513,16 @@ extern "C" int rpeg_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
                                 const void* dres_in, void* dx, float* dw, int T, int d, void* stream) {
   if (d & 7) return -2;
   if (T <= 0) return 0;
+  const int nv = ((d >> 3) + 255) / 256;
+  if (nv <= 2) {
+    const __nv_bfloat16 *dyp = static_cast<const __nv_bfloat16*>(dy), *xp = static_cast<const __nv_bfloat16*>(x),
+                        *wp = static_cast<const __nv_bfloat16*>(w), *rp = static_cast<const __nv_bfloat16*>(dres_in);
+    __nv_bfloat16* dxp = static_cast<__nv_bfloat16*>(dx);
+    const int grid = T < 1184 ? T : 1184;      // 8 resident CTAs on each of the 148 SMs
+    if (nv == 1) rmsnorm_bwd_row_kernel<1><<<grid, 256, 0, STREAM(stream)>>>(dyp, xp, wp, rstd, rp, dxp, dw, T, d);
+    else rmsnorm_bwd_row_kernel<2><<<grid, 256, 0, STREAM(stream)>>>(dyp, xp, wp, rstd, rp, dxp, dw, T, d);
+    return LAUNCH_OK();
+  }
   if (d * 4 > 200 * 1024) return -3;
   const int rows_per_cta = 32;
   auto kern = rmsnorm_bwd_kernel;
