@@ -318,3 +318,55 @@ extern "C" int rpeg_paged_decode_attn(const void* q, int ldq, int q_col0, const 
     decode_combine_kernel<<<dim3(H, B), HD, 0, STREAM(stream)>>>(scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
   return LAUNCH_OK();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant: the split-KV partials live in a fixed device array of this library.
+// Rules for callers are in decode_attn_static.h.
+#include "decode_attn_static.h"
+
+namespace {
+constexpr long long STATIC_PARTIAL_FLOATS = static_cast<long long>(RPEG_DECODE_STATIC_MAX_PARTIALS) * (HD + 2);
+static __device__ __align__(256) float g_decode_static_scratch[STATIC_PARTIAL_FLOATS];
+constexpr int STATIC_MAX_DEVICES = 64;
+float* g_static_scratch_ptr[STATIC_MAX_DEVICES] = {nullptr};
+}  // namespace
+
+extern "C" const char* rpeg_static_entry_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case RPEG_STATIC_ERR_BAD_SHAPE: return "unsupported shape: head_dim must be 128 and H a multiple of Hkv";
+    case RPEG_STATIC_ERR_BAD_SPLIT: return "nsplit must be between 1 and 64";
+    case RPEG_STATIC_ERR_TOO_LARGE:
+      return "B * H * nsplit exceeds RPEG_DECODE_STATIC_MAX_PARTIALS (16384): the built-in scratch is too small for this call";
+    case RPEG_STATIC_ERR_SETUP: return "set-up failed: the address of the built-in scratch could not be obtained on this device";
+    case RPEG_STATIC_ERR_LAUNCH: return "kernel launch failed";
+    default: return "unknown code";
+  }
+}
+
+extern "C" int rpeg_paged_decode_attn_static(const void* q, int ldq, int q_col0, const void* kcache, const void* vcache,
+                                             const int* page_table, int max_pages, const int* seq_lens, void* out,
+                                             int B, int H, int Hkv, int hd, int nsplit, float scale, void* stream) {
+  if (hd != HD || Hkv <= 0 || H % Hkv != 0) return RPEG_STATIC_ERR_BAD_SHAPE;
+  if (nsplit < 1 || nsplit > 64) return RPEG_STATIC_ERR_BAD_SPLIT;
+  if (B <= 0) return 0;
+  if (static_cast<long long>(B) * H * nsplit > RPEG_DECODE_STATIC_MAX_PARTIALS) return RPEG_STATIC_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= STATIC_MAX_DEVICES) return RPEG_STATIC_ERR_SETUP;
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    // set-up, once per device: the array's address in this device's copy of the module
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_decode_static_scratch) != cudaSuccess || p == nullptr)
+      return RPEG_STATIC_ERR_SETUP;
+    g_static_scratch_ptr[dev] = p;
+  }
+  float* scratch = g_static_scratch_ptr[dev];
+  const float scale_log2 = scale * 1.4426950408889634f;
+  paged_decode_attn_kernel<<<dim3(H, B, nsplit), 128, 0, STREAM(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), ldq, q_col0, static_cast<const __nv_bfloat16*>(kcache),
+      static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages, seq_lens, static_cast<__nv_bfloat16*>(out),
+      scratch, H, Hkv, nsplit, scale_log2);
+  if (nsplit > 1)
+    decode_combine_kernel<<<dim3(H, B), HD, 0, STREAM(stream)>>>(scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
+  return cudaGetLastError() == cudaSuccess ? 0 : RPEG_STATIC_ERR_LAUNCH;
+}
