@@ -88,6 +88,57 @@ rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, int ld, int q_col0, int k
   }
 }
 
+// The same job list as rope_kv_append_kernel, but the qkv row is the sum of split-K partials
+// (fp32 [splits][T][ld]): the head slice is summed, rounded to bf16, rotated (q, k) and stored: q into
+// the bf16 qkv buffer the attention kernel reads, k and v into the paged cache.
+__global__ void __launch_bounds__(256)
+rope_kv_append_partials_kernel(const float* __restrict__ parts, int splits, long long stride, __nv_bfloat16* __restrict__ qkv,
+                               int ld, int q_col0, int k_col0, int v_col0, const int* __restrict__ seq_id,
+                               const int* __restrict__ pos, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                               const int* __restrict__ page_table, int max_pages, __nv_bfloat16* __restrict__ kcache,
+                               __nv_bfloat16* __restrict__ vcache, int T, int H, int Hkv) {
+  const int jobs = H + 2 * Hkv;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (wid >= static_cast<long long>(T) * jobs) return;
+  const int lane = threadIdx.x & 31;
+  const int t = static_cast<int>(wid / jobs), job = static_cast<int>(wid % jobs);
+  const int p = pos[t];
+  const int col = job < H ? q_col0 + job * HD : (job < H + Hkv ? k_col0 + (job - H) * HD : v_col0 + (job - H - Hkv) * HD);
+  size_t dst = 0;
+  if (job >= H) {
+    const int page = page_table[static_cast<size_t>(seq_id[t]) * max_pages + p / PAGE];
+    const int hk = (job - H) % Hkv;
+    dst = ((static_cast<size_t>(page) * Hkv + hk) * PAGE + (p % PAGE)) * HD;
+  }
+  constexpr int half = HD / 2;
+  const int i = lane * 2;
+  // lane owns elements (i, i+1) and their rotation partners (i+half, i+half+1)
+  float lo0 = 0.f, lo1 = 0.f, hi0 = 0.f, hi1 = 0.f;
+  const size_t off = static_cast<size_t>(t) * ld + col;
+  for (int s = 0; s < splits; ++s) {
+    const float2 a = *reinterpret_cast<const float2*>(parts + s * stride + off + i);
+    const float2 b = *reinterpret_cast<const float2*>(parts + s * stride + off + i + half);
+    lo0 += a.x; lo1 += a.y; hi0 += b.x; hi1 += b.y;
+  }
+  uint32_t lo = pack_bf16x2(lo0, lo1), hi = pack_bf16x2(hi0, hi1);
+  if (job < H + Hkv) {
+    const float2 a = unpack_bf16x2(lo), b = unpack_bf16x2(hi);
+    const float2 c = *reinterpret_cast<const float2*>(cos_t + static_cast<size_t>(p) * half + i);
+    const float2 sn = *reinterpret_cast<const float2*>(sin_t + static_cast<size_t>(p) * half + i);
+    lo = pack_bf16x2(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y);
+    hi = pack_bf16x2(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y);
+  }
+  __nv_bfloat16* cache = job < H ? nullptr : (job < H + Hkv ? kcache : vcache);
+  if (job < H) {
+    __nv_bfloat16* base = qkv + off;
+    *reinterpret_cast<uint32_t*>(base + i) = lo;
+    *reinterpret_cast<uint32_t*>(base + i + half) = hi;
+  } else {
+    *reinterpret_cast<uint32_t*>(cache + dst + i) = lo;
+    *reinterpret_cast<uint32_t*>(cache + dst + i + half) = hi;
+  }
+}
+
 // 16 per-lane partial dot products (one per key of a half block) -> the full dot product of key
 // `lane & 15` in every lane of a 16-lane group: at each level half of the values go to the partner.
 __device__ __forceinline__ float transpose_reduce16(float (&v)[16], int lane) {
@@ -294,6 +345,20 @@ extern "C" int rpeg_rope_kv_append(void* qkv, int ld, int q_col0, int k_col0, in
   rope_kv_append_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, STREAM(stream)>>>(
       static_cast<__nv_bfloat16*>(qkv), ld, q_col0, k_col0, v_col0, seq_id, pos, cos_t, sin_t, page_table, max_pages,
       static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache), T, H, Hkv);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_rope_kv_append_partials(const float* parts, int splits, long long stride, void* qkv, int ld, int q_col0,
+                                            int k_col0, int v_col0, const int* seq_id, const int* pos, const float* cos_t,
+                                            const float* sin_t, const int* page_table, int max_pages, void* kcache,
+                                            void* vcache, int T, int H, int Hkv, int hd, void* stream) {
+  if (hd != HD || splits < 1) return -2;
+  if ((ld | q_col0 | k_col0 | v_col0) & 7) return -3;
+  const long long threads = static_cast<long long>(T) * (H + 2 * Hkv) * 32;
+  if (threads <= 0) return 0;
+  rope_kv_append_partials_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, STREAM(stream)>>>(
+      parts, splits, stride, static_cast<__nv_bfloat16*>(qkv), ld, q_col0, k_col0, v_col0, seq_id, pos, cos_t, sin_t, page_table,
+      max_pages, static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache), T, H, Hkv);
   return LAUNCH_OK();
 }
 

@@ -400,3 +400,58 @@ extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if (rc == 0 && k_splits > 1) rc = rpeg_splitk_reduce(workspace, C, M, N, ldc, k_splits, stream_v);
   return rc;
 }
+
+
+// Skinny GEMM that leaves its split-K partials for the consumer: C_s[M,N] (fp32, s = 0..splits-1, `M*N`
+// apart in `workspace`) with sum_s C_s = A[M,K] * B[N,K]^T. The split count is chosen by the same cost
+// model as rpeg_gemm_bf16 and returned in *k_splits_out; kernels that read the result (RMSNorm, SwiGLU,
+// RoPE + KV append for decode) add the partials while they load them, so the separate reduction pass
+// and its round trip through memory disappear.
+extern "C" int rpeg_gemm_bf16_partials(const void* A, const void* B, int M, int N, int K, int lda, int ldb,
+                                       float* workspace, long long workspace_elems, int* k_splits_out, int* status,
+                                       void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (k_splits_out == nullptr || workspace == nullptr) return -5;
+  *k_splits_out = 1;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(workspace)) & 15) return -1;
+  if ((lda | ldb) & 7) return -2;
+  if (N & 7) return -3;
+  const long long per_split = static_cast<long long>(M) * N;
+  if (workspace_elems < per_split) return -6;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int bn = N >= 256 ? 256 : (N >= 128 ? 128 : (N >= 64 ? 64 : 32));
+  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  const int num_kb = (K + BK - 1) / BK;
+  const double block_bytes = static_cast<double>(g_num_sms) * BK * (bn + BM) * 2.0;
+  int want = 1;
+  double best = 1e30;
+  const int max_s = num_kb / 2 > 32 ? 32 : num_kb / 2;
+  for (int sp = 1; sp <= (max_s < 1 ? 1 : max_s); ++sp) {
+    const int kb_per = (num_kb + sp - 1) / sp;
+    if ((num_kb + kb_per - 1) / kb_per != sp) continue;
+    if (workspace_elems / per_split < sp) break;
+    const int waves = (tiles * sp + g_num_sms - 1) / g_num_sms;
+    // the consumer reads every partial once; no separate reduction pass writes and re-reads them
+    const double cost = waves * (kb_per + 2.0) + sp * per_split * 8.0 / block_bytes;
+    if (cost < best - 1e-9) { best = cost; want = sp; }
+  }
+  const int kb_per = (num_kb + want - 1) / want;
+  const int k_splits = (num_kb + kb_per - 1) / kb_per;
+  *k_splits_out = k_splits;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
+  if (rc) return rc - 100;
+  switch (bn) {
+    case 256: return launch_gemm<256, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream);
+    case 128: return launch_gemm<128, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream);
+    case 64: return launch_gemm<64, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream);
+    default: return launch_gemm<32, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream);
+  }
+}

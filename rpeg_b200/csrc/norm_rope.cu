@@ -368,6 +368,105 @@ headnorm_bwd_kernel(__nv_bfloat16* __restrict__ dbuf, int ldd, const __nv_bfloat
   if (threadIdx.x < 128) atomicAdd(&dw[threadIdx.x], dw_sm[threadIdx.x]);
 }
 
+// ---- consumers of split-K partials (decode): x = sum_s parts[s] is formed while loading --------------
+__device__ __forceinline__ void load_partials8(const float* __restrict__ parts, int splits, long long stride, size_t off,
+                                               float (&v)[8]) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float4 a = *reinterpret_cast<const float4*>(parts + s * stride + off);
+    const float4 b = *reinterpret_cast<const float4*>(parts + s * stride + off + 4);
+    v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+  }
+}
+
+// y = rmsnorm(sum_s parts[s] [+ res]) * w; h_out (optional) = the bf16 sum, i.e. the new residual stream.
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_partials_kernel(const float* __restrict__ parts, int splits, long long stride,
+                            const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w,
+                            __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ y, int d, float eps) {
+  __shared__ float warp_ss[8];
+  const int row = blockIdx.x;
+  const int nvec = d >> 3;
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * 256;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[k][e] = 0.f;
+    if (i < nvec) {
+      load_partials8(parts, splits, stride, static_cast<size_t>(row) * d + i * 8, v[k]);
+      if (res) {
+        const uint4 r = reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * d)[i];
+        const uint32_t* pr = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf16x2(pr[e]);
+          v[k][2 * e] += f.x; v[k][2 * e + 1] += f.y;
+        }
+      }
+      // the residual stream is kept in bf16: round here so the norm sees exactly what is stored
+      uint4 hv;
+      uint32_t* ph = reinterpret_cast<uint32_t*>(&hv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ph[e] = pack_bf16x2(v[k][2 * e], v[k][2 * e + 1]);
+        const float2 f = unpack_bf16x2(ph[e]);
+        v[k][2 * e] = f.x; v[k][2 * e + 1] = f.y;
+        ss += f.x * f.x + f.y * f.y;
+      }
+      if (h_out) reinterpret_cast<uint4*>(h_out + static_cast<size_t>(row) * d)[i] = hv;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) warp_ss[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += warp_ss[k];
+  const float rstd = rsqrtf(tot / static_cast<float>(d) + eps);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < nvec) {
+      const uint4 wv = reinterpret_cast<const uint4*>(w)[i];
+      const uint32_t* pw = reinterpret_cast<const uint32_t*>(&wv);
+      uint4 o;
+      uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 b = unpack_bf16x2(pw[e]);
+        po[e] = pack_bf16x2(v[k][2 * e] * rstd * b.x, v[k][2 * e + 1] * rstd * b.y);
+      }
+      reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * d)[i] = o;
+    }
+  }
+}
+
+// out[t, j] = silu(g) * u with [g | u] = sum_s parts[s][t, :]
+__global__ void swiglu_fwd_partials_kernel(const float* __restrict__ parts, int splits, long long stride,
+                                           __nv_bfloat16* __restrict__ out, long long T, int f) {
+  const int fv = f >> 3;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * fv) return;
+  const long long t = idx / fv;
+  const int j = static_cast<int>(idx % fv) * 8;
+  float g[8], u[8];
+  load_partials8(parts, splits, stride, static_cast<size_t>(t) * 2 * f + j, g);
+  load_partials8(parts, splits, stride, static_cast<size_t>(t) * 2 * f + f + j, u);
+  uint4 o;
+  uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    // the unfused path rounds the GEMM output to bf16 before the activation; do the same
+    const float2 gg = unpack_bf16x2(pack_bf16x2(g[2 * e], g[2 * e + 1])), uu = unpack_bf16x2(pack_bf16x2(u[2 * e], u[2 * e + 1]));
+    po[e] = pack_bf16x2(gg.x / (1.f + __expf(-gg.x)) * uu.x, gg.y / (1.f + __expf(-gg.y)) * uu.y);
+  }
+  reinterpret_cast<uint4*>(out + t * f)[j >> 3] = o;
+}
+
 // RoPE, rotate-half pairing (i, i + hd/2), applied in place to `nheads` heads of width hd that sit
 // at column offset `col0` of a [T, ld] bf16 buffer. cos/sin tables are fp32 [max_pos, hd/2].
 // sign = +1 forward, -1 backward (the transpose of a rotation is the rotation by -angle).
@@ -558,6 +657,30 @@ extern "C" int rpeg_headnorm_bwd(void* dbuf, int ldd, const void* x, int ldx, in
   headnorm_bwd_kernel<<<static_cast<unsigned>(blocks), 256, 0, STREAM(stream)>>>(
       static_cast<__nv_bfloat16*>(dbuf), ldd, static_cast<const __nv_bfloat16*>(x), ldx, col0, nheads,
       static_cast<const __nv_bfloat16*>(w), rstd, dw, rows);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_rmsnorm_fwd_partials(const float* parts, int splits, long long stride, const void* res, const void* w,
+                                         void* h_out, void* y, int T, int d, float eps, void* stream) {
+  if ((d & 7) || splits < 1) return -2;
+  if (T <= 0) return 0;
+  const __nv_bfloat16 *rp = static_cast<const __nv_bfloat16*>(res), *wp = static_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16 *hp = static_cast<__nv_bfloat16*>(h_out), *yp = static_cast<__nv_bfloat16*>(y);
+  const int nv = ((d >> 3) + 255) / 256;
+  if (nv == 1) rmsnorm_fwd_partials_kernel<1><<<T, 256, 0, STREAM(stream)>>>(parts, splits, stride, rp, wp, hp, yp, d, eps);
+  else if (nv == 2) rmsnorm_fwd_partials_kernel<2><<<T, 256, 0, STREAM(stream)>>>(parts, splits, stride, rp, wp, hp, yp, d, eps);
+  else if (nv <= 4) rmsnorm_fwd_partials_kernel<4><<<T, 256, 0, STREAM(stream)>>>(parts, splits, stride, rp, wp, hp, yp, d, eps);
+  else return -3;
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_swiglu_fwd_partials(const float* parts, int splits, long long stride, void* out, long long T, int f,
+                                        void* stream) {
+  if ((f & 7) || splits < 1) return -2;
+  const long long n = T * (f >> 3);
+  if (n <= 0) return 0;
+  swiglu_fwd_partials_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
+      parts, splits, stride, static_cast<__nv_bfloat16*>(out), T, f);
   return LAUNCH_OK();
 }
 

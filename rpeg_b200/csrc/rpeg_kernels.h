@@ -26,6 +26,16 @@ int rpeg_headnorm_fwd(void* buf, int ld, int col0, int nheads, int hd, const voi
                       void* stream);
 int rpeg_headnorm_bwd(void* dbuf, int ldd, const void* x, int ldx, int col0, int nheads, int hd, const void* w,
                       const float* rstd, float* dw, int T, void* stream);
+// consumers of split-K partials: parts is fp32 [splits][rows][width], `stride` elements between splits
+int rpeg_gemm_bf16_partials(const void* A, const void* B, int M, int N, int K, int lda, int ldb, float* workspace,
+                            long long workspace_elems, int* k_splits_out, int* status, void* stream);
+int rpeg_rmsnorm_fwd_partials(const float* parts, int splits, long long stride, const void* res, const void* w, void* h_out,
+                              void* y, int T, int d, float eps, void* stream);
+int rpeg_swiglu_fwd_partials(const float* parts, int splits, long long stride, void* out, long long T, int f, void* stream);
+int rpeg_rope_kv_append_partials(const float* parts, int splits, long long stride, void* qkv, int ld, int q_col0, int k_col0,
+                                 int v_col0, const int* seq_id, const int* pos, const float* cos_t, const float* sin_t,
+                                 const int* page_table, int max_pages, void* kcache, void* vcache, int T, int H, int Hkv,
+                                 int hd, void* stream);
 int rpeg_rope(void* buf, const int* pos, const float* cos_t, const float* sin_t, int T, int ld, int col0,
               int nheads, int hd, int backward, void* stream);
 int rpeg_swiglu_fwd(const void* gu, void* out, long long T, int f, void* stream);

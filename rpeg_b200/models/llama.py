@@ -378,6 +378,35 @@ class LlamaModel:
         cfg, p = self.cfg, self.p
         ws = self._workspace()
         scale = 1.0 / math.sqrt(cfg.head_dim)
+        if cfg.qk_norm:
+            return self._decode_step_unfused(token, pos, slot_ids, seq_len, page_table, kcache, vcache, nsplit)
+        # Every GEMM leaves its split-K partials in the workspace and the next kernel adds them up while it
+        # loads them (one stream, so a consumer always runs before the next GEMM reuses the workspace).
+        B = token.shape[0]
+        h = K.embed_fwd(token, p["embed"])
+        x, _, _ = K.rmsnorm_fwd(h, p["l0.attn_norm"], cfg.rms_eps)
+        qkv = torch.empty((B, cfg.qkv_width), dtype=torch.bfloat16, device=self.device)
+        for i in range(cfg.n_layers):
+            parts = K.gemm_partials(x, p[f"l{i}.wqkv"], ws)
+            K.rope_kv_append_partials_(parts, qkv, 0, cfg.q_width, cfg.q_width + cfg.kv_width, slot_ids, pos, self.cos_t,
+                                       self.sin_t, page_table, kcache[i], vcache[i], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
+            attn = K.paged_decode_attn(qkv, 0, kcache[i], vcache[i], page_table, seq_len, cfg.n_heads, cfg.n_kv_heads,
+                                       cfg.head_dim, scale, nsplit=nsplit)
+            parts = K.gemm_partials(attn, p[f"l{i}.wo"], ws)
+            x2, h1 = K.rmsnorm_fwd_partials(parts, p[f"l{i}.mlp_norm"], cfg.rms_eps, residual=h, want_sum=True)
+            parts = K.gemm_partials(x2, p[f"l{i}.w_gate_up"], ws)
+            act = K.swiglu_fwd_partials(parts)
+            parts = K.gemm_partials(act, p[f"l{i}.w_down"], ws)
+            last = i + 1 == cfg.n_layers
+            x, h = K.rmsnorm_fwd_partials(parts, p["final_norm"] if last else p[f"l{i + 1}.attn_norm"], cfg.rms_eps, residual=h1,
+                                          want_sum=not last)
+        return x
+
+    def _decode_step_unfused(self, token, pos, slot_ids, seq_len, page_table, kcache, vcache, nsplit: int = 1) -> torch.Tensor:
+        """The same step with reduced GEMM outputs (needed when q and k are normalised per head before RoPE)."""
+        cfg, p = self.cfg, self.p
+        ws = self._workspace()
+        scale = 1.0 / math.sqrt(cfg.head_dim)
         res, delta = K.embed_fwd(token, p["embed"]), None
         for i in range(cfg.n_layers):
             if delta is None:

@@ -45,6 +45,10 @@ _SIGNATURES = {
     "rpeg_dp_reduce_norm": [P, I, LL, LL, F, P, P, P],
     "rpeg_dp_adam_push": [P, P, P, P, P, I, LL, LL, F, F, F, F, F, I, P, I, F, P],
     "rpeg_copy16": [P, P, LL, P],
+    "rpeg_gemm_bf16_partials": [P, P, I, I, I, I, I, P, c_longlong, P, P, P],
+    "rpeg_rmsnorm_fwd_partials": [P, I, c_longlong, P, P, P, P, I, I, F, P],
+    "rpeg_swiglu_fwd_partials": [P, I, c_longlong, P, c_longlong, I, P],
+    "rpeg_rope_kv_append_partials": [P, I, c_longlong, P, I, I, I, I, P, P, P, P, P, I, P, P, I, I, I, I, P],
     "rpeg_headnorm_fwd": [P, I, I, I, I, P, P, I, F, P],
     "rpeg_headnorm_bwd": [P, I, P, I, I, I, I, P, P, P, I, P],
     "rpeg_gemm_rs": [P, P, I, I, I, I, I, P, P, P, I, I, I, c_uint, I, P, P],

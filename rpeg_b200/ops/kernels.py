@@ -7,6 +7,7 @@ synchronises) and raises ``KernelWaitTimeout`` if any wait ran out.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 
 import torch
@@ -317,6 +318,66 @@ def adamw_(p32, m, v, grad, w16, *, lr, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0
 
 def sumsq(x: torch.Tensor, out: torch.Tensor) -> None:
     check(lib().rpeg_sumsq(x.data_ptr(), x.numel(), out.data_ptr(), _stream()), "rpeg_sumsq")
+
+
+# --------------------------------------------------------------------------- split-K partials and their consumers
+class Partials:
+    """fp32 split-K partial products ``[splits, M, N]`` living in a workspace: ``sum(0)`` is the GEMM result."""
+
+    __slots__ = ("buf", "splits", "M", "N")
+
+    def __init__(self, buf: torch.Tensor, splits: int, M: int, N: int):
+        self.buf, self.splits, self.M, self.N = buf, splits, M, N
+
+    @property
+    def stride(self) -> int:
+        return self.M * self.N
+
+    def reduce(self) -> torch.Tensor:
+        return self.buf[: self.splits * self.stride].view(self.splits, self.M, self.N).sum(0)
+
+
+def gemm_partials(a: torch.Tensor, b: torch.Tensor, workspace: torch.Tensor) -> Partials:
+    """``a [M,K] @ b [N,K]^T`` for skinny ``M`` (decode): returns the split-K partials in ``workspace`` instead
+    of reducing them; ``rmsnorm_fwd_partials`` / ``swiglu_fwd_partials`` / ``rope_kv_append_partials_`` add them
+    up while loading. The split count is fixed by the shapes, so the call is CUDA-graph friendly."""
+    _req(a, torch.bfloat16, "a")
+    _req(b, torch.bfloat16, "b")
+    M, Kd = a.shape
+    N = b.shape[0]
+    splits = ctypes.c_int(1)
+    check(lib().rpeg_gemm_bf16_partials(a.data_ptr(), b.data_ptr(), M, N, Kd, a.stride(0), b.stride(0), workspace.data_ptr(),
+                                        workspace.numel(), ctypes.byref(splits), status_word(a.device).data_ptr(), _stream()),
+          "rpeg_gemm_bf16_partials")
+    return Partials(workspace, int(splits.value), M, N)
+
+
+def rmsnorm_fwd_partials(parts: Partials, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None,
+                         want_sum: bool = False):
+    """``y = rmsnorm(sum(parts) [+ residual]) * w``; with ``want_sum`` also returns the bf16 sum (the new residual stream)."""
+    y = torch.empty((parts.M, parts.N), dtype=torch.bfloat16, device=w.device)
+    h = torch.empty_like(y) if want_sum else None
+    check(lib().rpeg_rmsnorm_fwd_partials(parts.buf.data_ptr(), parts.splits, parts.stride, _ptr(residual), w.data_ptr(), _ptr(h),
+                                          y.data_ptr(), parts.M, parts.N, eps, _stream()), "rpeg_rmsnorm_fwd_partials")
+    return y, h
+
+
+def swiglu_fwd_partials(parts: Partials) -> torch.Tensor:
+    f = parts.N // 2
+    out = torch.empty((parts.M, f), dtype=torch.bfloat16, device=parts.buf.device)
+    check(lib().rpeg_swiglu_fwd_partials(parts.buf.data_ptr(), parts.splits, parts.stride, out.data_ptr(), parts.M, f, _stream()),
+          "rpeg_swiglu_fwd_partials")
+    return out
+
+
+def rope_kv_append_partials_(parts: Partials, qkv: torch.Tensor, q_col0, k_col0, v_col0, seq_id, pos, cos_t, sin_t, page_table,
+                             kcache, vcache, n_heads, n_kv_heads, head_dim) -> None:
+    """Sum the partials of a QKV projection, rotate q and k, store q into ``qkv`` (bf16, the attention
+    kernel's query input) and k, v into the paged cache."""
+    check(lib().rpeg_rope_kv_append_partials(parts.buf.data_ptr(), parts.splits, parts.stride, qkv.data_ptr(), qkv.stride(0), q_col0,
+                                             k_col0, v_col0, seq_id.data_ptr(), pos.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
+                                             page_table.data_ptr(), page_table.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+                                             parts.M, n_heads, n_kv_heads, head_dim, _stream()), "rpeg_rope_kv_append_partials")
 
 
 # --------------------------------------------------------------------------- attention

@@ -223,7 +223,7 @@ class EngineOperationHandler:
         ro = st["rollout"]
         if self.algo_name == "dpo":
             tr.policy.zero_grad()
-            m = A.dpo_train_step(tr.policy, ro, st["ref_seq"], self.algo, n_pairs_global=int(self._global(ro.tokens.shape[0] // 2)))
+            m = A.dpo_train_step(tr.policy, ro, st["ref_seq"], self.algo, n_pairs_global=int(self._global(ro.n // 2)))
             tr.opt.step()
             m["grad_norm"] = tr.opt.grad_norm()
         else:

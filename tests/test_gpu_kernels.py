@@ -472,3 +472,42 @@ def test_headnorm_fwd_bwd(cuda_device):
     assert _rel_err(d[:, col0:col0 + H * hd], xr.grad.reshape(T, -1)) < 2e-2
     assert _rel_err(dw, wr.grad) < 2e-2
     assert torch.equal(d[:, :col0], dy[:, :col0])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [3, 32, 200])
+def test_split_k_partials_and_their_consumers(cuda_device, M):
+    d, f, H, Hkv, hd = 1024, 1408, 8, 4, 128
+    ws = torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=cuda_device)
+    x = torch.randn(M, d, device=cuda_device).bfloat16()
+    res = torch.randn(M, d, device=cuda_device).bfloat16()
+    w_norm = (1 + 0.1 * torch.randn(d, device=cuda_device)).bfloat16()
+    # GEMM partials sum to the GEMM
+    wo = (torch.randn(d, d, device=cuda_device) * 0.05).bfloat16()
+    parts = K.gemm_partials(x, wo, ws)
+    assert parts.splits >= 1 and _rel_err(parts.reduce(), x.float() @ wo.float().t()) < 1e-2
+    # RMSNorm over partials + residual == unfused sequence
+    y, h = K.rmsnorm_fwd_partials(parts, w_norm, 1e-5, residual=res, want_sum=True)
+    o_ref = K.gemm(x, wo, workspace=torch.empty_like(ws))
+    y_ref, _, h_ref = K.rmsnorm_fwd(o_ref, w_norm, 1e-5, residual=res, want_sum=True)
+    assert _rel_err(h, h_ref) < 1e-2 and _rel_err(y, y_ref) < 1e-2
+    # SwiGLU over partials
+    wgu = (torch.randn(2 * f, d, device=cuda_device) * 0.05).bfloat16()
+    pg = K.gemm_partials(x, wgu, ws)
+    assert _rel_err(K.swiglu_fwd_partials(pg), K.swiglu_fwd(K.gemm(x, wgu))) < 1e-2
+    # RoPE + append over partials == reduce, rotate, append
+    lens = [5 + (7 * i) % 100 for i in range(M)]
+    table, kc, vc = _paged_cache(cuda_device, [l + 1 for l in lens], Hkv, hd, 2 * M + 8)
+    kc2, vc2 = kc.clone(), vc.clone()
+    wqkv = (torch.randn((H + 2 * Hkv) * hd, d, device=cuda_device) * 0.05).bfloat16()
+    pos = torch.tensor(lens, device=cuda_device, dtype=torch.int32)
+    slots = torch.arange(M, device=cuda_device, dtype=torch.int32)
+    cos_t, sin_t = K.rope_tables(1024, hd, 10000.0, cuda_device)
+    ref = K.gemm(x, wqkv)
+    K.rope_kv_append_(ref, 0, H * hd, (H + Hkv) * hd, slots, pos, cos_t, sin_t, table, kc, vc, H, Hkv, hd)
+    pq = K.gemm_partials(x, wqkv, ws)
+    qkv = torch.zeros_like(ref)
+    K.rope_kv_append_partials_(pq, qkv, 0, H * hd, (H + Hkv) * hd, slots, pos, cos_t, sin_t, table, kc2, vc2, H, Hkv, hd)
+    assert _rel_err(qkv[:, :H * hd], ref[:, :H * hd]) < 1e-2
+    assert _rel_err(kc2, kc) < 1e-2 and _rel_err(vc2, vc) < 1e-2
+    K.check_status()
