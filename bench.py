@@ -33,6 +33,13 @@ CONFIGS = {
     "grpo_tiny": dict(algo="grpo", model="tiny", prompts=16, k=4, prompt_len=32, max_new=64,
                       quantiles=((0.5, 16), (0.9, 32), (1.0, 64))),
     "dpo_7b": dict(algo="dpo", model="llama7b", prompts=64, k=2, prompt_len=256, max_new=768, quantiles=None),
+    # PPO with four 7B-shape models (actor, critic, reference, reward); needs >= 4 GPUs for the two Adam states
+    "ppo_7b": dict(algo="ppo", model="llama7b", prompts=64, k=1, prompt_len=128, max_new=512,
+                   quantiles=((0.5, 128), (0.85, 256), (1.0, 512)), min_gpus=4),
+    # PPO with a shared 13B actor/critic trunk (LM head + value head) and a 7B-shape reward model
+    "ppo_acshare_13b": dict(algo="ppo", model="llama13b", prompts=128, k=1, prompt_len=256, max_new=1024, shared=True,
+                            quantiles=((0.5, 256), (0.85, 512), (1.0, 1024)), min_gpus=4),
+    "ppo_tiny": dict(algo="ppo", model="tiny", prompts=16, k=1, prompt_len=32, max_new=64, quantiles=((0.5, 16), (0.9, 32), (1.0, 64))),
 }
 
 
@@ -157,7 +164,10 @@ def main() -> None:
         dp = DPContext(device)
 
     spec = CONFIGS[args.config]
-    cfg = LlamaConfig.llama7b(max_pos=4096) if spec["model"] == "llama7b" else LlamaConfig.tiny()
+    if world < spec.get("min_gpus", 1):
+        raise SystemExit(f"config {args.config} needs at least {spec['min_gpus']} GPUs (optimizer state of its trainable models)")
+    cfg = {"llama7b": lambda: LlamaConfig.llama7b(max_pos=4096), "llama13b": lambda: LlamaConfig.llama13b(max_pos=4096),
+           "tiny": LlamaConfig.tiny}[spec["model"]]()
     B, Kk, S, T = spec["prompts"], spec["k"], spec["prompt_len"], spec["max_new"]
     if B % world:
         raise SystemExit(f"{B} prompts do not split over {world} ranks")
@@ -189,6 +199,25 @@ def main() -> None:
             if on_device:
                 p, r = p.to(device), r.to(device)
             return trainer.step(p, r, forced_lens=l)
+    elif spec["algo"] == "ppo":
+        from rpeg_b200.engine.trainers import PPOTrainer
+        slots = args.gen_slots or min(b_local * Kk, 128)
+        reward_cfg = LlamaConfig.llama7b(max_pos=4096) if spec["model"] == "llama13b" else None
+        trainer = PPOTrainer(cfg, device=device, max_new=T, prompt_len=S, algo=algo, dp=dp, gen_slots=slots,
+                             kv_budget_bytes=(args.kv_gb or 40.0) * 1e9, recompute=recompute, seed=42, eos_id=2,
+                             share_actor_critic=bool(spec.get("shared", False)), reward_cfg=reward_cfg)
+        batches = []
+        for _ in range(n_iters):
+            prompts = torch.randint(3, cfg.vocab, (B, S), generator=gen_host, dtype=torch.int32)
+            lens = torch.tensor(draw_lengths(B, spec["quantiles"], gen_host), dtype=torch.int32)
+            sl = slice(rank * b_local, (rank + 1) * b_local)
+            batches.append((prompts[sl].contiguous().pin_memory(), lens[sl].contiguous()))
+
+        def run(i, on_device):
+            p, l = batches[i]
+            if on_device:
+                p = p.to(device)
+            return trainer.step(p, forced_lens=l)
     else:
         trainer = DPOTrainer(cfg, device=device, algo=algo, dp=dp, recompute=recompute, seed=42)
         batches = []
@@ -243,11 +272,11 @@ def main() -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "gen_tokens_per_sec": stats[1] / secs, "train_tokens_per_sec": stats[2] / secs,
-            "config": {"model": f"{spec['model']} x2 (actor + frozen reference), random init", "algorithm": spec["algo"],
+            "config": {"model": {"grpo": f"{spec['model']} x2 (actor + frozen reference)", "dpo": f"{spec['model']} x2 (policy + frozen reference)", "ppo": f"{spec['model']} actor" + ("+critic shared trunk" if spec.get("shared") else ", critic") + ", reference, reward"}[spec["algo"]] + ", random init", "algorithm": spec["algo"],
                        "global_batch": B * Kk if spec["algo"] == "grpo" else B, "prompts": B, "samples_per_prompt": Kk,
                        "seq_len": S + T, "prompt_len": S, "max_new_tokens": T, "gen_quantiles": spec["quantiles"],
                        "parallelism": f"dp{world}", "optimizer": "adamw fp32 master, sharded over dp",
-                       "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if spec["algo"] == "grpo" else None,
+                       "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if spec["algo"] in ("grpo", "ppo") else None,
                        "l2": "working set (13.5 GB of weights per model) far exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": stats_e2e[0] / (ms_e2e / 1e3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "wall_s_per_step": wall_e2e / args.steps, "h2d_bytes_per_step": int(trainer.h2d_bytes),

@@ -29,7 +29,7 @@ from .workload import Workload
 
 
 def training_activation_bytes_per_microbatch(node: ExecNode, suite: ModelSuite, workload: Workload, *,
-                                             activation_checkpointing: bool) -> float:
+                                             activation_checkpointing: bool, token_cap: int = 0) -> float:
     if node.model is None or node.pi is None or node.mb is None:
         raise ValueError(f"{node.id}: training activation accounting needs model, pi and mb")
     spec = suite.specs[node.model]
@@ -42,7 +42,10 @@ def training_activation_bytes_per_microbatch(node: ExecNode, suite: ModelSuite, 
         per_token = math.ceil(L_pp / c) * spec.d + c * layer_peak
     else:
         per_token = L_pp * layer_peak
-    return spec.dtype_bytes * b_local * (workload.S + workload.T) * per_token
+    tokens = b_local * (workload.S + workload.T)
+    if token_cap > 0:           # the engine packs sequences into microbatches of at most this many tokens
+        tokens = min(tokens, token_cap)
+    return spec.dtype_bytes * tokens * per_token
 
 
 @dataclass(frozen=True)
@@ -53,6 +56,8 @@ class MemoryPolicy:
     worker_overhead_bytes: float = 0.0
     semantic_activation_cache_bytes: float = 0.0
     max_worker_groups_per_gpu: int = 0
+    kv_cache_budget_bytes: float = 0.0      # > 0: paged KV with a fixed pool per GPU instead of a static full-length cache
+    activation_token_cap: int = 0           # > 0: tokens per packed microbatch, bounds every activation estimate
 
     def __post_init__(self):
         if self.optimizer_stage not in (0, 1, 2):
@@ -85,6 +90,8 @@ class NodeMemoryModel:
     semantic_activation_cache_bytes: float = 0.0
     max_worker_groups_per_gpu: int = 0
     activation_checkpointing: bool = True
+    kv_cache_budget_bytes: float = 0.0
+    activation_token_cap: int = 0
     _shard_cache: dict = field(default_factory=dict, compare=False, repr=False)
 
     @classmethod
@@ -94,7 +101,8 @@ class NodeMemoryModel:
                    worker_overhead_bytes=policy.worker_overhead_bytes,
                    semantic_activation_cache_bytes=policy.semantic_activation_cache_bytes,
                    max_worker_groups_per_gpu=policy.max_worker_groups_per_gpu,
-                   activation_checkpointing=policy.activation_checkpointing)
+                   activation_checkpointing=policy.activation_checkpointing,
+                   kv_cache_budget_bytes=policy.kv_cache_budget_bytes, activation_token_cap=policy.activation_token_cap)
 
     def __post_init__(self):
         if self.optimizer_stage not in (0, 1, 2):
@@ -165,7 +173,8 @@ class NodeMemoryModel:
 
     def train_activation_bytes(self, node: ExecNode) -> float:
         per_mb = training_activation_bytes_per_microbatch(node, self.suite, self.workload,
-                                                          activation_checkpointing=self.activation_checkpointing)
+                                                          activation_checkpointing=self.activation_checkpointing,
+                                                          token_cap=self.activation_token_cap)
         return min(node.mb, node.pi[1]) * per_mb
 
     def inference_activation_bytes(self, node: ExecNode) -> float:
@@ -174,12 +183,17 @@ class NodeMemoryModel:
         b_local = w.B * w.K / (dp * (node.mb if node.mb is not None else 1))
         seq = w.S if node.role is Role.GENERATION else w.S + w.T
         per_token = max(2 * s.d + 6 * s.d / tp, 2 * s.d + 2 * s.d_ff / tp, s.d + s.V)
-        return s.dtype_bytes * b_local * seq * per_token
+        tokens = b_local * seq
+        if self.activation_token_cap > 0:
+            tokens = min(tokens, self.activation_token_cap)
+        return s.dtype_bytes * tokens * per_token
 
     def kv_cache_bytes(self, node: ExecNode) -> float:
         s, w = self.suite.specs[node.model], self.workload
         dp, pp, tp = node.pi
-        return 2 * s.dtype_bytes * (w.B / dp) * w.K * (w.S + w.T) * (s.L / pp) * (s.d / tp)
+        full = 2 * s.dtype_bytes * (w.B / dp) * w.K * (w.S + w.T) * (s.L / pp) * (s.d / tp)
+        # A paged cache with continuous batching holds only the rows in flight: the pool is a fixed budget.
+        return min(full, self.kv_cache_budget_bytes) if self.kv_cache_budget_bytes > 0 else full
 
     def static_bytes(self, model: Model, shard: int, trained: bool, dp: int = 1) -> float:
         sb = self.suite.specs[model].dtype_bytes

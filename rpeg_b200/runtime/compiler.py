@@ -256,7 +256,9 @@ def memory_policy_from_run(run: RuntimeRunConfig) -> MemoryPolicy:
                         runtime_overhead_fraction=run.hardware.memory_reserve_fraction,
                         worker_overhead_bytes=run.hardware.worker_overhead_bytes,
                         semantic_activation_cache_bytes=run.hardware.semantic_activation_cache_bytes,
-                        max_worker_groups_per_gpu=run.hardware.max_worker_groups_per_gpu)
+                        max_worker_groups_per_gpu=run.hardware.max_worker_groups_per_gpu,
+                        kv_cache_budget_bytes=float(run.hardware.kv_cache_budget_bytes),
+                        activation_token_cap=int(run.hardware.activation_token_cap))
 
 
 def compile_runtime_plan(run_config, *, dry_run: bool = False, inventory: Optional[ClusterInventory] = None) -> CompiledRuntimePlan:

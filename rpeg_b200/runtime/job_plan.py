@@ -132,7 +132,9 @@ def job_memory_policy(cfg: dict) -> MemoryPolicy:
         runtime_overhead_fraction=float(opt.get("memory_reserve_fraction", rh.get("memory_reserve_fraction", 0.10))),
         worker_overhead_bytes=float(rh.get("worker_overhead_bytes", 10 * 1024 ** 3)),
         semantic_activation_cache_bytes=float(rh.get("semantic_activation_cache_bytes", 0)),
-        max_worker_groups_per_gpu=int(rh.get("max_worker_groups_per_gpu", 0)))
+        max_worker_groups_per_gpu=int(rh.get("max_worker_groups_per_gpu", 0)),
+        kv_cache_budget_bytes=float(rh.get("kv_cache_budget_bytes", 0)),
+        activation_token_cap=int(rh.get("activation_token_cap", 0)))
 
 
 def job_transfer_policy(cfg: dict) -> TransferResourcePolicy:
@@ -172,6 +174,8 @@ def job_optimizer_config(cfg: dict, algorithm: str, policy: MemoryPolicy, ac_sha
         memory_worker_overhead_bytes=policy.worker_overhead_bytes,
         memory_semantic_activation_cache_bytes=policy.semantic_activation_cache_bytes,
         memory_max_worker_groups_per_gpu=policy.max_worker_groups_per_gpu,
+        memory_kv_cache_budget_bytes=policy.kv_cache_budget_bytes,
+        memory_activation_token_cap=policy.activation_token_cap,
         seed=seed, workers=int(o.get("workers", 1)), verbose=bool(o.get("verbose", False)))
 
 
@@ -257,7 +261,9 @@ def run_config_mapping(cfg: dict, *, run_id: str, algorithm: str, workload: Work
                      "memory_per_gpu_bytes": int(hw.memory_per_gpu), "memory_reserve_fraction": policy.runtime_overhead_fraction,
                      "worker_overhead_bytes": int(policy.worker_overhead_bytes),
                      "semantic_activation_cache_bytes": int(policy.semantic_activation_cache_bytes),
-                     "max_worker_groups_per_gpu": policy.max_worker_groups_per_gpu},
+                     "max_worker_groups_per_gpu": policy.max_worker_groups_per_gpu,
+                     "kv_cache_budget_bytes": int(policy.kv_cache_budget_bytes),
+                     "activation_token_cap": int(policy.activation_token_cap)},
         "cluster": {"scheduler": "local", "launcher": {"type": "local"}, **dict(cfg.get("cluster") or {})},
         "runtime": runtime, "data": {"synthetic": True, **dict(cfg.get("data") or {})}, "optimizer_runtime": opt_rt,
         "checkpoints": {"output_dir": "checkpoints", **dict(cfg.get("checkpoints") or {})}, "monitoring": monitoring,

@@ -161,6 +161,8 @@ class HardwareConfig:
     worker_overhead_bytes: int = 0
     semantic_activation_cache_bytes: int = 0
     max_worker_groups_per_gpu: int = 0
+    kv_cache_budget_bytes: int = 0
+    activation_token_cap: int = 0
     memory_reserve_fraction: float = 0.10
     calibration_path: Optional[str] = None
 

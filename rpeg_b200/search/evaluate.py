@@ -121,7 +121,9 @@ def evaluation_cache_key(config: Configuration, policy: MemoryPolicy = MemoryPol
     return (f"{config_hash(config.rpeg, config.plan)}:mem:fusion={int(config.intra_stage_fusion)}:"
             f"transfer={','.join(tp.values())}:{policy.optimizer_stage}:{int(policy.activation_checkpointing)}:"
             f"{policy.runtime_overhead_fraction:.12g}:{policy.worker_overhead_bytes:.12g}:"
-            f"activation_cache={policy.semantic_activation_cache_bytes:.12g}:groups={policy.max_worker_groups_per_gpu}")
+            f"activation_cache={policy.semantic_activation_cache_bytes:.12g}:groups={policy.max_worker_groups_per_gpu}"
+            + (f":kv={policy.kv_cache_budget_bytes:.12g}:tok={policy.activation_token_cap}"
+               if (policy.kv_cache_budget_bytes or policy.activation_token_cap) else ""))
 
 
 def _penalised(raw: float, lowered, mem_model: NodeMemoryModel) -> Tuple[float, bool]:

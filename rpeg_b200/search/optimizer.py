@@ -83,6 +83,8 @@ class OptimizerConfig:
     memory_worker_overhead_bytes: float = 0.0
     memory_semantic_activation_cache_bytes: float = 0.0
     memory_max_worker_groups_per_gpu: int = 0
+    memory_kv_cache_budget_bytes: float = 0.0
+    memory_activation_token_cap: int = 0
     seed: Optional[int] = None
     workers: Optional[int] = None   # process-pool size; default min(K_x, cpu count); 1 disables the pool
     verbose: bool = False
@@ -101,7 +103,8 @@ class OptimizerConfig:
     def memory_policy(self) -> MemoryPolicy:
         return MemoryPolicy(self.memory_optimizer_stage, self.memory_activation_checkpointing,
                             self.memory_runtime_overhead_fraction, self.memory_worker_overhead_bytes,
-                            self.memory_semantic_activation_cache_bytes, self.memory_max_worker_groups_per_gpu)
+                            self.memory_semantic_activation_cache_bytes, self.memory_max_worker_groups_per_gpu,
+                            self.memory_kv_cache_budget_bytes, self.memory_activation_token_cap)
 
     def flags(self) -> SearchFlags:
         return SearchFlags(self.fixed_mb, self.uniform_vertex)
