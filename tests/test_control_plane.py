@@ -76,7 +76,8 @@ def test_rank_failure_is_detected_and_the_group_is_aborted(tmp_path, op, match):
     finally:
         l.stop_all()
     hb0 = HeartbeatStore(tmp_path / "hb").read("grp", 0)
-    assert hb0 is not None and hb0.state in ("starting", "ready", "running", "stopped", "error")
+    # rank 0 may have been torn down before it wrote its first heartbeat; if it wrote one, it never reached "finished"
+    assert hb0 is None or hb0.state in ("starting", "ready", "running", "stopped", "error")
 
 
 def test_rank_that_never_becomes_ready_times_out(tmp_path):
