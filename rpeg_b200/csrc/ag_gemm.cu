@@ -1,0 +1,286 @@
+// Column-parallel linear layer with a sequence-parallel input in ONE kernel: all-gather of the activation
+// rows over NVLink and the tcgen05 GEMM that consumes them, overlapped block by block.
+//
+//   every rank holds its own rows of x inside a symmetric buffer X [M, K] (rows of rank q at q * M / world)
+//   rank r computes y_r [M, N_r] = X w_r^T with its slice w_r [N_r, K] of the output features
+//
+// Inside the kernel (persistent, one CTA per SM, 256 threads):
+//   warps 6-7  pull the peers' row blocks through their peer pointers into this GPU's copy of X, 16-row
+//              chunks spread over all CTAs in the order the GEMM will need them, and count each finished
+//              chunk in ready[row block] (device-scope release)
+//   warp 0     TMA producer: before the first tile of a row block that came from a peer it waits (bounded)
+//              until all chunks of that block have landed, then loads A tiles from the LOCAL X, so every
+//              remote byte crosses NVLink exactly once and the tensor cores read local memory
+//   warp 1     tcgen05.mma into double-buffered TMEM accumulators
+//   warps 2-5  epilogue: TMEM -> bf16 -> y
+// Tiles are ordered so that this rank's own rows come first; the pull of the next peer's rows runs under
+// those MMAs. The copy warps never wait, so the producer's wait always ends; all waits are bounded.
+// The caller orders calls with a cross-rank barrier (every shard written, previous pulls finished).
+//
+// The reference gets this through Megatron's ColumnParallelLinear with sequence parallelism: an NCCL
+// all-gather followed by a cuBLAS GEMM (RPEG/runtime/workers/megatron_worker.py:124-303, 676-715).
+#include "common.cuh"
+#include "rpeg_kernels.h"
+
+namespace rpeg {
+
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer);
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int THREADS = 256;
+constexpr int COPY_THREADS = 64;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int STAGES = 4;
+constexpr int TMEM_COLS = 2 * BN;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
+constexpr int CHUNK_ROWS = 16;
+constexpr int CHUNKS_PER_BLOCK = BM / CHUNK_ROWS;
+constexpr unsigned long long READY_WAIT_NS = 10ull * 1000 * 1000 * 1000;
+
+struct Peers {
+  void* p[RPEG_MAX_PEERS];
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Peers xs,
+               unsigned* __restrict__ ready, __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldx, int ldy, int rank,
+               int world, unsigned epoch, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_area = smem + STAGES * STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = M / BM;                      // host guarantees M % (BM * world) == 0
+  const int n_tiles = (N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + BK - 1) / BK;
+  const int blocks_per_rank = m_tiles / world;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmap_a); tma_prefetch_desc(&tmap_b); }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Tile order: the owner of the rows advances rank, rank+1, ...; inside an owner's segment groups of 8
+  // row blocks sweep N together (A rows stay in L2).
+  auto tile_coords = [&](int t, int& tm, int& tn) {
+    constexpr int GROUP_M = 8;
+    const int seg = blocks_per_rank * n_tiles;
+    const int owner_step = t / seg;
+    const int r = t - owner_step * seg;
+    const int owner = (rank + owner_step) % world;
+    const int per_group = GROUP_M * n_tiles;
+    const int g = r / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(blocks_per_rank - first_m, GROUP_M);
+    const int rr = r - g * per_group;
+    tm = owner * blocks_per_rank + first_m + (rr % gsize);
+    tn = rr / gsize;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stg = 0;
+      uint32_t phase = 0;
+      int last_ready_block = -1;
+      const unsigned expect = epoch * static_cast<unsigned>(CHUNKS_PER_BLOCK);
+      for (int w = blockIdx.x; w < num_tiles; w += gridDim.x) {
+        int tm, tn;
+        tile_coords(w, tm, tn);
+        if (tm / blocks_per_rank != rank && tm != last_ready_block) {
+          // rows of a peer: wait until the copy warps (of all CTAs) have brought the whole block in
+          unsigned seen = 0;
+          const uint64_t t0 = global_timer_ns();
+          for (;;) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ready + tm) : "memory");
+            if (static_cast<int>(seen - expect) >= 0) break;
+            if (*abort_flag) goto producer_done;
+            if (global_timer_ns() - t0 > READY_WAIT_NS) {
+              record_error(status, RPEG_ERR_FLAG_TIMEOUT, 800, tm);
+              *abort_flag = 1;
+              goto producer_done;
+            }
+            __nanosleep(200);
+          }
+          // the rows were written with ordinary stores; the loads below go through the async proxy
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          last_ready_block = tm;
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stg], phase ^ 1u, abort_flag, status, 801)) goto producer_done;
+          uint8_t* sa = smem + stg * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stg], STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, &full_bar[stg], kb * BK, tm * BM);
+          tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[stg], kb * BK, tn * BN);
+          if (++stg == STAGES) { stg = 0; phase ^= 1u; }
+        }
+      }
+    producer_done:;
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, 0);
+      int stg = 0, buf = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int w = blockIdx.x; w < num_tiles; w += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1u, abort_flag, status, 810)) goto mma_done;
+        tc_fence_after_sync();
+        const uint32_t tacc = tmem_base + static_cast<uint32_t>(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stg], phase, abort_flag, status, 811)) goto mma_done;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stg * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16_ss(tacc, make_smem_desc_sw128(sa + k * 32, 16, 1024), make_smem_desc_sw128(sb + k * 32, 16, 1024), idesc,
+                         (kb > 0 || k != 0) ? 1u : 0u);
+          umma_commit(&empty_bar[stg]);
+          if (++stg == STAGES) { stg = 0; phase ^= 1u; }
+        }
+        umma_commit(&tfull_bar[buf]);
+        if (++buf == 2) { buf = 0; acc_phase ^= 1u; }
+      }
+    mma_done:;
+    }
+  } else if (warp < 6) {
+    const int quad = warp & 3;
+    int buf = 0;
+    uint32_t acc_phase = 0;
+    for (int w = blockIdx.x; w < num_tiles; w += gridDim.x) {
+      int tm, tn;
+      tile_coords(w, tm, tn);
+      const int row = tm * BM + quad * 32 + lane;
+      const int n0 = tn * BN;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, status, 820))) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(buf * BN);
+      __nv_bfloat16* crow = Y + static_cast<size_t>(row) * ldy + n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_wait_ld();
+        if (n0 + c * 32 < N) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (n0 + c * 32 + v * 8 < N) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(crow + c * 32 + v * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      if (++buf == 2) { buf = 0; acc_phase ^= 1u; }
+    }
+  } else {
+    // ---- copy warps: bring the peers' rows into the local X, in the order the tiles will need them
+    const int ct = threadIdx.x - (THREADS - COPY_THREADS);          // 0..63
+    __nv_bfloat16* x_local = static_cast<__nv_bfloat16*>(xs.p[rank]);
+    const int vec_per_row = K >> 3;                                  // 16-byte vectors of one row
+    const int chunk_vecs = CHUNK_ROWS * vec_per_row;
+    const int remote_chunks = (world - 1) * blocks_per_rank * CHUNKS_PER_BLOCK;
+    for (int g = blockIdx.x; g < remote_chunks; g += gridDim.x) {
+      const int blk_seq = g / CHUNKS_PER_BLOCK, ch = g % CHUNKS_PER_BLOCK;
+      const int owner = (rank + 1 + blk_seq / blocks_per_rank) % world;
+      const int blk = owner * blocks_per_rank + blk_seq % blocks_per_rank;
+      const int row0 = blk * BM + ch * CHUNK_ROWS;
+      const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(xs.p[owner]);
+      constexpr int UNROLL = 8;
+      for (int i0 = ct; i0 < chunk_vecs; i0 += COPY_THREADS * UNROLL) {
+        uint4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int i = i0 + u * COPY_THREADS;
+          if (i < chunk_vecs)
+            v[u] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int i = i0 + u * COPY_THREADS;
+          if (i < chunk_vecs)
+            *reinterpret_cast<uint4*>(x_local + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8) = v[u];
+        }
+      }
+      // both copy warps are done with the chunk: publish it (generic-proxy stores, then async-proxy readers)
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence();
+      asm volatile("bar.sync 2, 64;" ::: "memory");
+      if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ready + blk) : "memory");
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+}  // namespace rpeg
+
+using namespace rpeg;
+
+// xs[q]: rank q's X buffer ([M, ldx] bf16, symmetric); on entry rank q's own rows are valid in xs[q] on
+// every rank's view. W [N, ldw] bf16 local; Y [M, ldy] bf16 local. `ready`: local uint32[M / 128], zeroed
+// once; `epoch` counts calls from 1. M must be a multiple of 128 * world; N, K, ld* multiples of 8.
+extern "C" int rpeg_ag_gemm(void* const* xs, const void* W, void* Y, unsigned* ready, int M, int N, int K, int ldx, int ldw,
+                            int ldy, int rank, int world, unsigned epoch, int* status, void* stream_v) {
+  if (world < 1 || world > RPEG_MAX_PEERS || rank < 0 || rank >= world) return -2;
+  if (M <= 0 || N <= 0 || K <= 0 || (M % (BM * world)) != 0 || (N & 7) || (K & 7) || (ldx & 7) || (ldw & 7) || (ldy & 7)) return -3;
+  static int num_sms = 0;
+  static bool configured = false;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (!configured) {
+    if (cudaFuncSetAttribute(ag_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -20;
+    configured = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_bf16_2d(&ta, xs[rank], K, M, ldx, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tb, W, K, N, ldw, BK, BN);
+  if (rc) return rc - 100;
+  Peers px;
+  for (int i = 0; i < RPEG_MAX_PEERS; ++i) px.p[i] = i < world ? xs[i] : nullptr;
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  ag_gemm_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream_v)>>>(ta, tb, px, ready, static_cast<__nv_bfloat16*>(Y), M, N,
+                                                                                   K, ldx, ldy, rank, world, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

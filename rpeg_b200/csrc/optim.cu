@@ -269,6 +269,37 @@ extern "C" int rpeg_dp_adam_push(float* p32, float* m, float* v, const float* re
   return LAUNCH_OK();
 }
 
+// Strided rectangle copy (rows x row_bytes, pitches in bytes), source or destination may be peer memory.
+// 16-byte vectors when pitches, row length and both bases allow it, else 2-byte elements.
+template <typename V>
+__global__ void copy2d_kernel(const uint8_t* __restrict__ src, long long src_pitch, uint8_t* __restrict__ dst,
+                              long long dst_pitch, long long rows, long long vec_per_row) {
+  const long long total = rows * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row, c = i % vec_per_row;
+    reinterpret_cast<V*>(dst + r * dst_pitch)[c] = reinterpret_cast<const V*>(src + r * src_pitch)[c];
+  }
+}
+
+extern "C" int rpeg_copy2d(const void* src, long long src_pitch, void* dst, long long dst_pitch, long long rows,
+                           long long row_bytes, void* stream) {
+  if (rows <= 0 || row_bytes <= 0) return 0;
+  if ((row_bytes & 1) || (src_pitch & 1) || (dst_pitch & 1)) return -2;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | static_cast<uintptr_t>(src_pitch) |
+                        static_cast<uintptr_t>(dst_pitch) | static_cast<uintptr_t>(row_bytes);
+  if ((all & 15) == 0) {
+    const long long v = row_bytes >> 4;
+    copy2d_kernel<uint4><<<sat_grid(rows * v, 256), 256, 0, STREAM(stream)>>>(static_cast<const uint8_t*>(src), src_pitch,
+                                                                            static_cast<uint8_t*>(dst), dst_pitch, rows, v);
+  } else {
+    const long long v = row_bytes >> 1;
+    copy2d_kernel<uint16_t><<<sat_grid(rows * v, 256), 256, 0, STREAM(stream)>>>(static_cast<const uint8_t*>(src), src_pitch,
+                                                                               static_cast<uint8_t*>(dst), dst_pitch, rows, v);
+  }
+  return LAUNCH_OK();
+}
+
 extern "C" int rpeg_copy16(const void* src, void* dst, long long nbytes, void* stream) {
   if (nbytes <= 0) return 0;
   if ((nbytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -2;

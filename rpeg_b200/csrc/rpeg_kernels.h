@@ -82,11 +82,17 @@ int rpeg_dp_adam_push(float* p32, float* m, float* v, const float* reduced, void
                       long long shard_off, long long shard_n, float lr, float beta1, float beta2, float eps,
                       float wd, int step, const float* sumsq, int n_partials, float max_norm, void* stream);
 int rpeg_copy16(const void* src, void* dst, long long nbytes, void* stream);
+int rpeg_copy2d(const void* src, long long src_pitch, void* dst, long long dst_pitch, long long rows, long long row_bytes,
+                void* stream);
 
 // ---- gemm_rs.cu: row-parallel linear = GEMM + reduce-scatter (or all-reduce) over peer memory in one launch
 int rpeg_gemm_rs(const void* A, const void* B, int M, int N, int K, int lda, int ldb, void* const* stage,
                  void* const* counters, void* const* outs, int ldo, int rank, int world, unsigned epoch, int all_gather,
                  int* status, void* stream);
+
+// ---- ag_gemm.cu: column-parallel linear = all-gather of the activation rows + GEMM in one launch
+int rpeg_ag_gemm(void* const* xs, const void* W, void* Y, unsigned* ready, int M, int N, int K, int ldx, int ldw, int ldy,
+                 int rank, int world, unsigned epoch, int* status, void* stream);
 
 // ---- decode_attn.cu
 int rpeg_kv_append(const void* qkv, int ld, int k_col0, int v_col0, const int* seq_id, const int* pos,

@@ -11,6 +11,10 @@ Checks, each against values computed independently on the host or with NCCL:
   4 GRPO steps          two data-parallel steps of the tiny model: finite loss, identical weights
   5 fused GEMM+RS       the row-parallel linear (GEMM with reduce-scatter / all-reduce in one kernel) against
                         an fp32 all-reduce of the partial products, three calls in a row
+  6 fused AG+GEMM       the column-parallel linear (all-gather of activation rows + GEMM in one kernel) against
+                        fp32, four calls in a row over the two input buffers
+  7 reshard             tensor-parallel shards -> data-parallel replicas and back with the strided peer-copy executor,
+                        bit-exact against the host-side oracle
 Rank 0 prints one JSON line with ``"ok": true``. Exit code 1 on any mismatch.
 """
 from __future__ import annotations
@@ -140,6 +144,53 @@ def main() -> int:
         dist.barrier()
         layer.close()
     report["fused_gemm_reduce_scatter_ok"] = all(rs_ok)
+
+    # 6 fused all-gather + GEMM (column-parallel linear): every rank contributes its rows, result against fp32
+    from .tp import ColumnParallelLinear
+    gx = torch.Generator().manual_seed(900)                 # the same activation on every rank; each keeps its rows
+    Mrows, Kin, Nloc = 256 * world, 512 + 64, 320
+    wcol = (torch.randn(Nloc, Kin, generator=gq) * 0.05).bfloat16().to(dev)
+    col = ColumnParallelLinear(wcol, max_rows=Mrows, device=dev)
+    ag_ok = []
+    per = Mrows // world
+    for it in range(4):
+        x_full = torch.randn(Mrows, Kin, generator=gx).bfloat16()
+        col.input_rows(Mrows).copy_(x_full[rank * per:(rank + 1) * per].to(dev))
+        y = col.forward(Mrows).float()
+        ref = x_full.to(dev).float() @ wcol.float().t()
+        torch.cuda.synchronize()
+        K.check_status()
+        ag_ok.append(bool(((y - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3).item()))
+        y2 = col.forward_unfused(x_full[rank * per:(rank + 1) * per].to(dev)).float()
+        ag_ok.append(bool(((y2 - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3).item()))
+    dist.barrier()
+    col.close()
+    report["fused_all_gather_gemm_ok"] = all(ag_ok)
+
+    # 7 weight reshard TP=world -> DP=world (every rank ends with the whole model) and back, against the host oracle
+    from .reshard import Layout, ReshardExecutor, param_shapes, piece_offsets, rank_pieces, shard_state_dict
+    rcfg = LlamaConfig.tiny(n_layers=2, d_model=512, d_ff=1024, n_heads=8, n_kv_heads=8, vocab=1024)
+    gfull = torch.Generator().manual_seed(4242)
+    full = {nm: torch.randn(sh, generator=gfull).bfloat16() for nm, sh in param_shapes(rcfg).items()}
+    rs_ok = []
+    for src_l, dst_l in ((Layout(1, 1, world), Layout(world, 1, 1)), (Layout(world, 1, 1), Layout(1, 1, world))):
+        ex = ReshardExecutor(rcfg, src_l, dst_l, dev)
+        mine = shard_state_dict(rcfg, full, src_l)[rank]
+        offs, _ = piece_offsets(rank_pieces(rcfg, src_l, rank))
+        src_flat = ex.source()
+        for key, off in offs.items():
+            src_flat[off:off + mine[key].numel()].copy_(mine[key].reshape(-1).to(dev))
+        for _ in range(2):
+            ex.dst_buf.zero_()
+            ex.run()
+        torch.cuda.synchronize()
+        K.check_status()
+        want = shard_state_dict(rcfg, full, dst_l)[rank]
+        doffs, _ = piece_offsets(rank_pieces(rcfg, dst_l, rank))
+        rs_ok.append(all(torch.equal(ex.dst_buf[o:o + want[k].numel()].cpu().view(want[k].shape), want[k]) for k, o in doffs.items()))
+        dist.barrier()
+        ex.close()
+    report["reshard_executor_ok"] = all(rs_ok)
 
     flags = torch.tensor([float(all(v for k, v in report.items() if k != "world"))], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)

@@ -22,9 +22,10 @@ import torch.distributed as dist
 
 from ..ops import kernels as K
 from ..ops._lib import check, lib
-from .symm import SymmetricBuffer
+from .symm import SignalPad, SymmetricBuffer
 
 ROW_BLOCK = 128
+BARRIER_TIMEOUT_NS = 30_000_000_000
 
 
 class RowParallelLinear:
@@ -88,3 +89,77 @@ class RowParallelLinear:
     def close(self) -> None:
         for b in (self.stage, self.counters, self.out):
             b.close()
+
+
+class ColumnParallelLinear:
+    """First half of a tensor-parallel block with a sequence-parallel input: every rank holds ``M / world``
+    rows of the activation and a slice ``w_r [N / world, K]`` of the output features. ``forward`` runs a
+    device-side barrier (every rank's rows are written) and then ONE kernel (``csrc/ag_gemm.cu``) that pulls
+    the peers' rows over NVLink into the local copy of ``X`` while its tensor-core tiles already work on the
+    rows that are there. ``X`` is double buffered so a rank may write its next input while a slower peer
+    still reads the previous one."""
+
+    def __init__(self, weight_shard: torch.Tensor, max_rows: int, device, group=None):
+        self.w = weight_shard
+        self.device = torch.device(device)
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.N, self.K = int(weight_shard.shape[0]), int(weight_shard.shape[1])
+        if max_rows % (ROW_BLOCK * self.world):
+            raise ValueError(f"max_rows must be a multiple of {ROW_BLOCK * self.world}")
+        self.max_rows = max_rows
+        self.x = [SymmetricBuffer(max_rows * self.K * 2, self.device, group) for _ in range(2)]
+        self.ready = torch.zeros(2 * (max_rows // ROW_BLOCK), dtype=torch.int32, device=self.device)
+        self.pad = SignalPad(self.device, group) if self.world > 1 else None
+        self.epoch = 0
+        self._last_m: Optional[int] = None
+
+    def input_rows(self, M: int) -> torch.Tensor:
+        """This rank's slice ``[M / world, K]`` of the buffer the NEXT ``forward`` call will read: write the
+        activation shard here (it is the GEMM's operand, no staging copy)."""
+        buf = self.x[(self.epoch + 1) % 2]
+        per = M // self.world
+        return buf.tensor(torch.bfloat16, M * self.K).view(M, self.K)[self.rank * per:(self.rank + 1) * per]
+
+    def forward(self, M: int) -> torch.Tensor:
+        """Consume the shards written through ``input_rows(M)`` on every rank; returns ``y_r [M, N / world]``."""
+        if M % (ROW_BLOCK * self.world) or M > self.max_rows:
+            raise ValueError(f"M={M} must be a multiple of {ROW_BLOCK * self.world} and at most {self.max_rows}")
+        if self._last_m is not None and self._last_m != M:
+            torch.cuda.synchronize(self.device)
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            self.ready.zero_()
+            self.epoch = self.epoch % 2          # keep the buffer parity, restart the counters
+            torch.cuda.synchronize(self.device)
+        self._last_m = M
+        self.epoch += 1
+        buf = self.x[self.epoch % 2]
+        stream = torch.cuda.current_stream().cuda_stream
+        if self.world > 1:
+            self.pad.epochs[0] += 1
+            check(lib().rpeg_flag_barrier(self.pad.ptr_array(), self.rank, self.world, 0, self.pad.epochs[0], None, None,
+                                          BARRIER_TIMEOUT_NS, K.status_word(self.device).data_ptr(), stream), "rpeg_flag_barrier")
+        y = torch.empty((M, self.N), dtype=torch.bfloat16, device=self.device)
+        half = self.ready.numel() // 2
+        ready = self.ready[(self.epoch % 2) * half:]
+        calls = (self.epoch + 1) // 2            # how many times this buffer (and its counters) has been used
+        check(lib().rpeg_ag_gemm(buf.ptr_array(), self.w.data_ptr(), y.data_ptr(), ready.data_ptr(), M, self.N, self.K, self.K,
+                                 self.w.stride(0), self.N, self.rank, self.world, calls, K.status_word(self.device).data_ptr(), stream),
+              "rpeg_ag_gemm")
+        return y
+
+    def forward_unfused(self, x_shard: torch.Tensor) -> torch.Tensor:
+        """NCCL all-gather followed by a plain GEMM (the baseline)."""
+        if self.world == 1:
+            return K.gemm(x_shard, self.w)
+        full = torch.empty((x_shard.shape[0] * self.world, self.K), dtype=x_shard.dtype, device=x_shard.device)
+        dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
+        return K.gemm(full, self.w)
+
+    def close(self) -> None:
+        for b in self.x:
+            b.close()
+        if self.pad is not None:
+            self.pad.close()

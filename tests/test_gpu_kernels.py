@@ -511,3 +511,19 @@ def test_split_k_partials_and_their_consumers(cuda_device, M):
     assert _rel_err(qkv[:, :H * hd], ref[:, :H * hd]) < 1e-2
     assert _rel_err(kc2, kc) < 1e-2 and _rel_err(vc2, vc) < 1e-2
     K.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (384, 1000, 520), (256, 2048, 4096)])
+def test_all_gather_gemm_kernel_single_rank(cuda_device, M, N, Kd):
+    """With one rank the fused column-parallel kernel has nothing to gather and must equal a plain GEMM."""
+    from rpeg_b200.parallel.tp import ColumnParallelLinear
+    w = (torch.randn(N, Kd, device=cuda_device) * 0.1).bfloat16()
+    layer = ColumnParallelLinear(w, max_rows=512, device=cuda_device)
+    for _ in range(3):
+        x = torch.randn(M, Kd, device=cuda_device).bfloat16()
+        layer.input_rows(M).copy_(x)
+        y = layer.forward(M)
+        K.check_status()
+        assert _rel_err(y, x.float() @ w.float().t()) < 1e-2
+    layer.close()
