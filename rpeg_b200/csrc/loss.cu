@@ -344,6 +344,82 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int V, int ld, float inv
   }
 }
 
+// Sampling restricted to the top-k tokens and/or the smallest set whose probability mass reaches top_p.
+// Both cut-offs are found as a threshold on the (temperature-scaled) logit by bisection: for a candidate
+// threshold one pass over the row counts the tokens above it and adds up their probability, so no sort
+// and no scratch memory is needed (26 passes over a row that stays in L1/L2). The token is then drawn by
+// Gumbel-max among the survivors. The reported log-prob is taken under the FULL softmax, which is what the
+// training passes recompute. top_k <= 0 and top_p >= 1 switch the respective filter off.
+__global__ void __launch_bounds__(LP_THREADS)
+sample_filtered_kernel(const __nv_bfloat16* __restrict__ logits, int V, int ld, float inv_temp, int top_k, float top_p,
+                       unsigned long long seed, const unsigned long long* __restrict__ seed_offset,
+                       const int* __restrict__ forced, int* __restrict__ token_out, float* __restrict__ logp_out) {
+  __shared__ float sm_m[32], sm_s[32], sm_best[32], sm_cnt[32], sm_mass[32];
+  __shared__ int sm_idx[32];
+  __shared__ float sm_bc[2];
+  const int row = blockIdx.x;
+  if (seed_offset != nullptr) seed += seed_offset[0] * 0xD1B54A32D192ED03ull;
+  const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < V; i += LP_THREADS) online_merge(m, s, __bfloat162float(lr[i]) * inv_temp, 1.f);
+  block_lse(m, s, sm_m, sm_s);                       // m, s now hold the row's max and sum(exp(x - m)) in every thread
+  const float lse = m + __logf(s);
+  const bool use_k = top_k > 0 && top_k < V, use_p = top_p < 1.f;
+  float lo_k = m - 40.f, hi_k = m, lo_p = m - 40.f, hi_p = m;
+  if (use_k || use_p) {
+    for (int it = 0; it < 26; ++it) {
+      const float mid_k = 0.5f * (lo_k + hi_k), mid_p = 0.5f * (lo_p + hi_p);
+      float cnt = 0.f, mass = 0.f;
+      for (int i = threadIdx.x; i < V; i += LP_THREADS) {
+        const float x = __bfloat162float(lr[i]) * inv_temp;
+        cnt += x >= mid_k ? 1.f : 0.f;
+        mass += x >= mid_p ? __expf(x - lse) : 0.f;
+      }
+      cnt = warp_sum(cnt);
+      mass = warp_sum(mass);
+      __syncthreads();
+      if (lane == 0) { sm_cnt[warp] = cnt; sm_mass[warp] = mass; }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float c = 0.f, p = 0.f;
+        for (int w = 0; w < nw; ++w) { c += sm_cnt[w]; p += sm_mass[w]; }
+        sm_bc[0] = c; sm_bc[1] = p;
+      }
+      __syncthreads();
+      if (sm_bc[0] >= static_cast<float>(top_k)) lo_k = mid_k; else hi_k = mid_k;     // still at least k tokens above: raise the bar
+      if (sm_bc[1] >= top_p) lo_p = mid_p; else hi_p = mid_p;                          // still at least top_p mass above
+    }
+  }
+  float thr = -INFINITY;
+  if (use_k) thr = fmaxf(thr, lo_k);
+  if (use_p) thr = fmaxf(thr, lo_p);
+  float best = -INFINITY;
+  int best_i = 0;
+  for (int i = threadIdx.x; i < V; i += LP_THREADS) {
+    const float x = __bfloat162float(lr[i]) * inv_temp;
+    if (x < thr) continue;
+    const float key = x - __logf(-__logf(hash_uniform(seed, row, i)));
+    if (key > best) { best = key; best_i = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float b2 = __shfl_xor_sync(0xffffffffu, best, o);
+    const int i2 = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (b2 > best || (b2 == best && i2 < best_i)) { best = b2; best_i = i2; }
+  }
+  __syncthreads();
+  if (lane == 0) { sm_best[warp] = best; sm_idx[warp] = best_i; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < nw; ++w)
+      if (sm_best[w] > best || (sm_best[w] == best && sm_idx[w] < best_i)) { best = sm_best[w]; best_i = sm_idx[w]; }
+    if (forced != nullptr && forced[row] >= 0) best_i = forced[row];
+    token_out[row] = best_i;
+    logp_out[row] = __bfloat162float(lr[best_i]) * inv_temp - lse;
+  }
+}
+
 // Value / reward head: out[t] = dot(h[t, :], w) + bias. One warp per row.
 __global__ void head_gemv_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ w,
                                  const float* __restrict__ bias, float* __restrict__ out, int T, int d) {
@@ -471,6 +547,15 @@ extern "C" int rpeg_sample(const void* logits, int B, int V, int ld, float tempe
   if (B <= 0) return 0;
   sample_kernel<<<B, LP_THREADS, 0, STREAM(stream)>>>(static_cast<const __nv_bfloat16*>(logits), V, ld,
                                                      1.f / temperature, greedy, seed, seed_offset, forced, token_out, logp_out);
+  return LAUNCH_OK();
+}
+extern "C" int rpeg_sample_filtered(const void* logits, int B, int V, int ld, float temperature, int top_k, float top_p,
+                                    unsigned long long seed, const unsigned long long* seed_offset, const int* forced,
+                                    int* token_out, float* logp_out, void* stream) {
+  if (B <= 0) return 0;
+  if (!(temperature > 0.f) || !(top_p > 0.f)) return -2;
+  sample_filtered_kernel<<<B, LP_THREADS, 0, STREAM(stream)>>>(static_cast<const __nv_bfloat16*>(logits), V, ld, 1.f / temperature,
+                                                              top_k, top_p, seed, seed_offset, forced, token_out, logp_out);
   return LAUNCH_OK();
 }
 extern "C" int rpeg_head_gemv(const void* h, const void* w, const float* bias, float* out, int T, int d,

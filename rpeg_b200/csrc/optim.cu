@@ -300,6 +300,37 @@ extern "C" int rpeg_copy2d(const void* src, long long src_pitch, void* dst, long
   return LAUNCH_OK();
 }
 
+// Rows of a local [n, row_bytes] buffer go to the rank that owns their GLOBAL index (owner = idx / rows_per_rank,
+// slot = idx % rows_per_rank) inside symmetric destination buffers: the hand-over of rollout rows (tokens,
+// log-probs, values, rewards) between vertices whose data-parallel layouts differ. One warp per row.
+__global__ void scatter_rows_by_index_kernel(const uint8_t* __restrict__ src, long long n, long long row_bytes,
+                                             const long long* __restrict__ global_idx, long long rows_per_rank, PeerPtrs dst,
+                                             int world) {
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (w >= n) return;
+  const int lane = threadIdx.x & 31;
+  const long long g = global_idx[w];
+  const long long owner = g / rows_per_rank;
+  if (g < 0 || owner >= world) return;
+  uint8_t* out = static_cast<uint8_t*>(dst.p[owner]) + (g - owner * rows_per_rank) * row_bytes;
+  const uint8_t* in = src + w * row_bytes;
+  if (((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in) | static_cast<uintptr_t>(row_bytes)) & 15) == 0) {
+    for (long long i = lane; i < (row_bytes >> 4); i += 32) reinterpret_cast<uint4*>(out)[i] = reinterpret_cast<const uint4*>(in)[i];
+  } else {
+    for (long long i = lane; i < (row_bytes >> 2); i += 32) reinterpret_cast<uint32_t*>(out)[i] = reinterpret_cast<const uint32_t*>(in)[i];
+  }
+}
+
+extern "C" int rpeg_scatter_rows_by_index(const void* src, long long n, long long row_bytes, const long long* global_idx,
+                                          long long rows_per_rank, void* const* dst, int world, void* stream) {
+  if (world < 1 || world > RPEG_MAX_PEERS || rows_per_rank <= 0) return -2;
+  if (row_bytes <= 0 || (row_bytes & 3)) return -3;
+  if (n <= 0) return 0;
+  scatter_rows_by_index_kernel<<<static_cast<unsigned>((n * 32 + 255) / 256), 256, 0, STREAM(stream)>>>(
+      static_cast<const uint8_t*>(src), n, row_bytes, global_idx, rows_per_rank, make_peers(dst, world), world);
+  return LAUNCH_OK();
+}
+
 extern "C" int rpeg_copy16(const void* src, void* dst, long long nbytes, void* stream) {
   if (nbytes <= 0) return 0;
   if ((nbytes & 15) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -2;

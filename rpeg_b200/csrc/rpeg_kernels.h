@@ -65,6 +65,9 @@ int rpeg_group_advantage(const float* rewards, float* out, int G, int K, void* s
 int rpeg_sample(const void* logits, int B, int V, int ld, float temperature, int greedy,
                 unsigned long long seed, const unsigned long long* seed_offset, const int* forced, int* token_out,
                 float* logp_out, void* stream);
+int rpeg_sample_filtered(const void* logits, int B, int V, int ld, float temperature, int top_k, float top_p,
+                         unsigned long long seed, const unsigned long long* seed_offset, const int* forced, int* token_out,
+                         float* logp_out, void* stream);
 int rpeg_head_gemv(const void* h, const void* w, const float* bias, float* out, int T, int d, void* stream);
 int rpeg_head_gemv_bwd(const void* h, const void* w, const float* dout, void* dh, float* dw, float* db, int T,
                        int d, void* stream);
@@ -82,6 +85,8 @@ int rpeg_dp_adam_push(float* p32, float* m, float* v, const float* reduced, void
                       long long shard_off, long long shard_n, float lr, float beta1, float beta2, float eps,
                       float wd, int step, const float* sumsq, int n_partials, float max_norm, void* stream);
 int rpeg_copy16(const void* src, void* dst, long long nbytes, void* stream);
+int rpeg_scatter_rows_by_index(const void* src, long long n, long long row_bytes, const long long* global_idx,
+                               long long rows_per_rank, void* const* dst, int world, void* stream);
 int rpeg_copy2d(const void* src, long long src_pitch, void* dst, long long dst_pitch, long long rows, long long row_bytes,
                 void* stream);
 

@@ -53,6 +53,8 @@ _SIGNATURES = {
     "rpeg_headnorm_bwd": [P, I, P, I, I, I, I, P, P, P, I, P],
     "rpeg_ag_gemm": [P, P, P, P, I, I, I, I, I, I, I, I, c_uint, P, P],
     "rpeg_copy2d": [P, c_longlong, P, c_longlong, c_longlong, c_longlong, P],
+    "rpeg_scatter_rows_by_index": [P, c_longlong, c_longlong, P, c_longlong, P, I, P],
+    "rpeg_sample_filtered": [P, I, I, I, F, I, F, c_ulonglong, P, P, P, P, P],
     "rpeg_gemm_rs": [P, P, I, I, I, I, I, P, P, P, I, I, I, c_uint, I, P, P],
     "rpeg_kv_append": [P, I, I, I, P, P, P, I, P, P, I, I, I, P],
     "rpeg_rope_kv_append": [P, I, I, I, I, P, P, P, P, P, I, P, P, I, I, I, I, P],

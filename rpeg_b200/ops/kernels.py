@@ -278,12 +278,18 @@ def group_advantage(rewards: torch.Tensor, group: int) -> torch.Tensor:
 
 def sample(logits: torch.Tensor, temperature: float, greedy: bool, seed: int, forced: torch.Tensor | None = None,
            token_out: torch.Tensor | None = None, logp_out: torch.Tensor | None = None,
-           seed_offset: torch.Tensor | None = None):
+           seed_offset: torch.Tensor | None = None, top_k: int = 0, top_p: float = 1.0):
     """Gumbel-max sample (or argmax) per row with its log-prob; ``seed_offset`` is an int64 device
-    scalar mixed into the seed so graph replays draw fresh noise."""
+    scalar mixed into the seed so graph replays draw fresh noise. ``top_k`` / ``top_p`` restrict the draw to
+    the k most likely tokens / the smallest set reaching mass ``top_p``; the log-prob is under the full softmax."""
     B, V = logits.shape
     tok = torch.empty(B, dtype=torch.int32, device=logits.device) if token_out is None else token_out
     lp = torch.empty(B, dtype=torch.float32, device=logits.device) if logp_out is None else logp_out
+    if not greedy and (0 < top_k < V or top_p < 1.0):
+        check(lib().rpeg_sample_filtered(logits.data_ptr(), B, V, logits.stride(0), temperature, int(top_k), float(top_p),
+                                         seed & 0xFFFFFFFFFFFFFFFF, _ptr(seed_offset), _ptr(forced), tok.data_ptr(), lp.data_ptr(),
+                                         _stream()), "rpeg_sample_filtered")
+        return tok, lp
     check(lib().rpeg_sample(logits.data_ptr(), B, V, logits.stride(0), temperature, int(greedy),
                             seed & 0xFFFFFFFFFFFFFFFF, _ptr(seed_offset), _ptr(forced), tok.data_ptr(), lp.data_ptr(),
                             _stream()),
@@ -378,6 +384,15 @@ def rope_kv_append_partials_(parts: Partials, qkv: torch.Tensor, q_col0, k_col0,
                                              k_col0, v_col0, seq_id.data_ptr(), pos.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
                                              page_table.data_ptr(), page_table.stride(0), kcache.data_ptr(), vcache.data_ptr(),
                                              parts.M, n_heads, n_kv_heads, head_dim, _stream()), "rpeg_rope_kv_append_partials")
+
+
+def scatter_rows_by_index(src: torch.Tensor, global_idx: torch.Tensor, rows_per_rank: int, dst_ptr_array, world: int) -> None:
+    """Send every row of ``src [n, ...]`` to the rank owning its global index (``idx // rows_per_rank``), slot
+    ``idx % rows_per_rank`` of that rank's symmetric buffer (``dst_ptr_array`` = ctypes ``void*[world]``)."""
+    n = src.shape[0]
+    row_bytes = src[0].numel() * src.element_size() if n else 0
+    check(lib().rpeg_scatter_rows_by_index(src.data_ptr(), n, row_bytes, global_idx.data_ptr(), rows_per_rank, dst_ptr_array, world,
+                                           _stream()), "rpeg_scatter_rows_by_index")
 
 
 # --------------------------------------------------------------------------- attention

@@ -108,7 +108,7 @@ def summarize_trace(events: Sequence[Mapping[str, Any]]) -> Dict[str, Any]:
         finished += 1
         st = starts.get(nid) or {}
         info = {**(st.get("counters") or {}), **c}
-        kind, role, model = info.get("kind", "OP"), info.get("role"), info.get("model")
+        kind, role, model = str(info.get("kind", "op")).lower(), info.get("role"), info.get("model")
         dur = float(c.get("duration_s", (ts - st["timestamp"]) if st and _finite(ts) else 0.0) or 0.0)
         by_kind[kind] += 1
         dur_kind[kind] += dur
@@ -120,7 +120,7 @@ def summarize_trace(events: Sequence[Mapping[str, Any]]) -> Dict[str, Any]:
                 w[0] = min(w[0], st["timestamp"])
             if _finite(ts):
                 w[1] = max(w[1], ts)
-        if kind == "OP":
+        if kind == "op":
             if role:
                 by_role[role] += 1
                 dur_role[role] += dur
@@ -152,7 +152,7 @@ def summarize_trace(events: Sequence[Mapping[str, Any]]) -> Dict[str, Any]:
             transport = str(c.get("transport", "metadata"))
             label = "weight" if str(info.get("label") or "").startswith("W_") else "activation"
             nbytes = int(c.get("transferred_bytes", c.get("payload_in_bytes", 0)) or 0)
-            for key in (kind.lower(), label, f"transport_{transport}"):
+            for key in (kind, label, f"transport_{transport}"):
                 xfer_bytes[key] += nbytes
                 xfer_s[key] += dur
         for k, name in SUM_COUNTERS.items():
@@ -168,8 +168,8 @@ def summarize_trace(events: Sequence[Mapping[str, Any]]) -> Dict[str, Any]:
              replay_attempts=replay, recoveries=recover, checkpoint_saves=ckpt_saves, checkpoint_restores=ckpt_restores,
              errors=errors[:20], nonfinite_losses=nonfinite, lifecycle_nodes=lifecycle)
     for k, v in by_kind.items():
-        s[f"nodes_{k.lower()}"] = v
-        s[f"node_seconds_{k.lower()}"] = dur_kind[k]
+        s[f"nodes_{k}"] = v
+        s[f"node_seconds_{k}"] = dur_kind[k]
     for k, v in by_role.items():
         s[f"operators_{k.lower()}"] = v
         s[f"operator_seconds_{k.lower()}"] = dur_role[k]

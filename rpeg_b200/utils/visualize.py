@@ -96,8 +96,8 @@ def runtime_trace_to_gantt_svg(events: Iterable[dict], path: str, space: Optiona
             s = starts.pop(e["node_id"])
             c = s.get("counters") or {}
             res = [r for r in c.get("resources", ()) if r.startswith("gpu:")] or [f"worker:{s.get('worker_id')}"]
-            kind = c.get("kind", "OP")
-            colour = TRANSFER_COLOUR if kind != "OP" else _shade(MODEL_COLOURS.get(c.get("model"), "#777777"),
+            kind = str(c.get("kind", "op")).lower()
+            colour = TRANSFER_COLOUR if kind != "op" else _shade(MODEL_COLOURS.get(c.get("model"), "#777777"),
                                                                  ROLE_SHADE.get(c.get("role"), 0.8))
             if e.get("status") != "ok":
                 colour = "#d62728"

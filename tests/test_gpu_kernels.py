@@ -527,3 +527,47 @@ def test_all_gather_gemm_kernel_single_rank(cuda_device, M, N, Kd):
         K.check_status()
         assert _rel_err(y, x.float() @ w.float().t()) < 1e-2
     layer.close()
+
+
+@pytest.mark.gpu
+def test_top_k_top_p_sampling(cuda_device):
+    B, V = 64, 4000
+    logits = (torch.randn(B, V, device=cuda_device) * 3).bfloat16()
+    lf = logits.float()
+    full_lp = torch.log_softmax(lf, -1)
+    order = lf.argsort(-1, descending=True)
+    # top-k: the draw stays inside the k most likely tokens; log-prob is the full-softmax one
+    for seed in range(3):
+        tok, lp = K.sample(logits, 1.0, False, seed, top_k=5)
+        rank_of = (order == tok.long()[:, None]).float().argmax(-1)
+        assert int(rank_of.max()) < 5 + 1          # bf16 ties may let one extra token through
+        assert torch.allclose(lp, full_lp.gather(1, tok.long()[:, None])[:, 0], atol=2e-2)
+    # top-p: the drawn token lies inside the smallest prefix of the sorted distribution reaching the mass
+    probs = full_lp.exp()
+    csum = probs.gather(1, order).cumsum(-1)
+    tok, _ = K.sample(logits, 1.0, False, 7, top_p=0.5)
+    rank_of = (order == tok.long()[:, None]).float().argmax(-1)
+    nucleus = (csum < 0.5).sum(-1) + 1
+    assert bool((rank_of <= nucleus).all())
+    # k = 1 is the argmax; over many draws top-k = 3 visits only (and all of) the three best tokens of a peaked row
+    tok1, _ = K.sample(logits, 1.0, False, 3, top_k=1)
+    assert torch.equal(tok1.long(), order[:, 0])
+    row = torch.zeros(256, V, device=cuda_device)
+    row[:, 10], row[:, 20], row[:, 30] = 5.0, 4.5, 4.0
+    seen = set()
+    for seed in range(4):
+        seen |= set(K.sample(row.bfloat16(), 1.0, False, 100 + seed, top_k=3)[0].tolist())
+    assert seen == {10, 20, 30}
+
+
+@pytest.mark.gpu
+def test_scatter_rows_by_index_single_rank(cuda_device):
+    import ctypes
+    n, width = 37, 24
+    src = torch.randn(n, width, device=cuda_device)
+    idx = torch.randperm(64, device=cuda_device)[:n].to(torch.int64)
+    dst = torch.zeros(64, width, device=cuda_device)
+    K.scatter_rows_by_index(src, idx, 64, (ctypes.c_void_p * 1)(dst.data_ptr()), 1)
+    ref = torch.zeros_like(dst)
+    ref[idx] = src
+    assert torch.equal(dst, ref)
