@@ -42,16 +42,27 @@ class RowParallelLinear:
         if max_rows % (ROW_BLOCK * self.world):
             raise ValueError(f"max_rows must be a multiple of {ROW_BLOCK * self.world}")
         self.max_rows = max_rows
-        self.stage = SymmetricBuffer(max_rows * self.N * 2, self.device, group)                 # [world][M/world][N] bf16
-        self.counters = SymmetricBuffer(max(256, max_rows // ROW_BLOCK * 4), self.device, group, zero=True)
+        # Two sets of staging / counters / output, used alternately: a fast rank may already push the partials of
+        # call e+1 while a slow owner still reduces call e, and call e+2 cannot start anywhere before every
+        # owner has received (hence finished reducing) call e+1's predecessor.
         out_rows = max_rows if all_reduce else max_rows // self.world
-        self.out = SymmetricBuffer(out_rows * self.N * 2, self.device, group)
+        self.stage = [SymmetricBuffer(max_rows * self.N * 2, self.device, group) for _ in range(2)]   # [world][M/world][N] bf16
+        self.counters = [SymmetricBuffer(max(256, max_rows // ROW_BLOCK * 4), self.device, group, zero=True) for _ in range(2)]
+        self.out = [SymmetricBuffer(out_rows * self.N * 2, self.device, group) for _ in range(2)]
         self.epoch = 0
         self._last_m: Optional[int] = None
 
+    def use_weight(self, weight_shard: torch.Tensor) -> "RowParallelLinear":
+        """Switch to another weight with the same number of output features: layers that run one after the other
+        can share one set of staging / counter / output buffers."""
+        if int(weight_shard.shape[0]) != self.N:
+            raise ValueError(f"shared buffers are sized for {self.N} output features, got {weight_shard.shape[0]}")
+        self.w = weight_shard
+        return self
+
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         """``x_shard [M, K/p]`` bf16 -> ``[M/world, N]`` (reduce-scatter) or ``[M, N]`` (all-reduce), a view
-        of this layer's symmetric output buffer (valid until the next call)."""
+        of one of this layer's two symmetric output buffers (valid until the call after the next one)."""
         M, Kp = x_shard.shape
         if M % (ROW_BLOCK * self.world) or M > self.max_rows:
             raise ValueError(f"M={M} must be a multiple of {ROW_BLOCK * self.world} and at most {self.max_rows}")
@@ -60,19 +71,22 @@ class RowParallelLinear:
             torch.cuda.synchronize(self.device)
             if self.world > 1:
                 dist.barrier(group=self.group)
-            self.counters.bytes_view.zero_()
+            for c in self.counters:
+                c.bytes_view.zero_()
             torch.cuda.synchronize(self.device)
             if self.world > 1:
                 dist.barrier(group=self.group)
             self.epoch = 0
         self._last_m = M
         self.epoch += 1
+        b = self.epoch % 2
+        calls = (self.epoch + 1) // 2            # how often this buffer set (and its counters) has been used
         check(lib().rpeg_gemm_rs(x_shard.data_ptr(), self.w.data_ptr(), M, self.N, Kp, x_shard.stride(0), self.w.stride(0),
-                                 self.stage.ptr_array(), self.counters.ptr_array(), self.out.ptr_array(), self.N, self.rank,
-                                 self.world, self.epoch, int(self.all_reduce), K.status_word(self.device).data_ptr(),
+                                 self.stage[b].ptr_array(), self.counters[b].ptr_array(), self.out[b].ptr_array(), self.N, self.rank,
+                                 self.world, calls, int(self.all_reduce), K.status_word(self.device).data_ptr(),
                                  torch.cuda.current_stream().cuda_stream), "rpeg_gemm_rs")
         rows = M if self.all_reduce else M // self.world
-        return self.out.tensor(torch.bfloat16, rows * self.N).view(rows, self.N)
+        return self.out[b].tensor(torch.bfloat16, rows * self.N).view(rows, self.N)
 
     def forward_unfused(self, x_shard: torch.Tensor) -> torch.Tensor:
         """Same result from a plain GEMM followed by an NCCL collective (the baseline)."""
@@ -87,7 +101,7 @@ class RowParallelLinear:
         return out
 
     def close(self) -> None:
-        for b in (self.stage, self.counters, self.out):
+        for b in (*self.stage, *self.counters, *self.out):
             b.close()
 
 
@@ -114,6 +128,13 @@ class ColumnParallelLinear:
         self.pad = SignalPad(self.device, group) if self.world > 1 else None
         self.epoch = 0
         self._last_m: Optional[int] = None
+
+    def use_weight(self, weight_shard: torch.Tensor) -> "ColumnParallelLinear":
+        """Switch to another weight with the same number of input features (shared input buffers)."""
+        if int(weight_shard.shape[1]) != self.K:
+            raise ValueError(f"shared buffers are sized for {self.K} input features, got {weight_shard.shape[1]}")
+        self.w, self.N = weight_shard, int(weight_shard.shape[0])
+        return self
 
     def input_rows(self, M: int) -> torch.Tensor:
         """This rank's slice ``[M / world, K]`` of the buffer the NEXT ``forward`` call will read: write the

@@ -539,19 +539,19 @@ def test_top_k_top_p_sampling(cuda_device):
     # top-k: the draw stays inside the k most likely tokens; log-prob is the full-softmax one
     for seed in range(3):
         tok, lp = K.sample(logits, 1.0, False, seed, top_k=5)
-        rank_of = (order == tok.long()[:, None]).float().argmax(-1)
-        assert int(rank_of.max()) < 5 + 1          # bf16 ties may let one extra token through
+        chosen = lf.gather(1, tok.long()[:, None])[:, 0]
+        assert bool((chosen >= lf.gather(1, order[:, 4:5])[:, 0]).all())        # at least as large as the 5th largest logit
         assert torch.allclose(lp, full_lp.gather(1, tok.long()[:, None])[:, 0], atol=2e-2)
     # top-p: the drawn token lies inside the smallest prefix of the sorted distribution reaching the mass
     probs = full_lp.exp()
     csum = probs.gather(1, order).cumsum(-1)
     tok, _ = K.sample(logits, 1.0, False, 7, top_p=0.5)
-    rank_of = (order == tok.long()[:, None]).float().argmax(-1)
-    nucleus = (csum < 0.5).sum(-1) + 1
-    assert bool((rank_of <= nucleus).all())
+    nucleus = ((csum < 0.5).sum(-1) + 1).clamp(max=V - 1)                    # size of the smallest prefix reaching the mass
+    floor = lf.gather(1, order.gather(1, nucleus[:, None]))[:, 0]            # logit of the first token outside (ties tolerated)
+    assert bool((lf.gather(1, tok.long()[:, None])[:, 0] >= floor).all())
     # k = 1 is the argmax; over many draws top-k = 3 visits only (and all of) the three best tokens of a peaked row
     tok1, _ = K.sample(logits, 1.0, False, 3, top_k=1)
-    assert torch.equal(tok1.long(), order[:, 0])
+    assert torch.equal(lf.gather(1, tok1.long()[:, None])[:, 0], lf.max(-1).values)   # a maximal logit (bf16 ties exist)
     row = torch.zeros(256, V, device=cuda_device)
     row[:, 10], row[:, 20], row[:, 30] = 5.0, 4.5, 4.0
     seen = set()
