@@ -4,8 +4,8 @@
 //   every rank holds its own rows of x inside a symmetric buffer X [M, K] (rows of rank q at q * M / world)
 //   rank r computes y_r [M, N_r] = X w_r^T with its slice w_r [N_r, K] of the output features
 //
-// Inside the kernel (persistent, one CTA per SM, 256 threads):
-//   warps 6-7  pull the peers' row blocks through their peer pointers into this GPU's copy of X, 16-row
+// Inside the kernel (persistent, one CTA per SM, 320 threads):
+//   warps 6-9  pull the peers' row blocks through their peer pointers into this GPU's copy of X, 16-row
 //              chunks spread over all CTAs in the order the GEMM will need them, and count each finished
 //              chunk in ready[row block] (device-scope release)
 //   warp 0     TMA producer: before the first tile of a row block that came from a peer it waits (bounded)
@@ -32,8 +32,8 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int THREADS = 256;
-constexpr int COPY_THREADS = 64;
+constexpr int THREADS = 320;
+constexpr int COPY_THREADS = 128;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -51,7 +51,7 @@ struct Peers {
 __global__ void __launch_bounds__(THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Peers xs,
                unsigned* __restrict__ ready, __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldx, int ldy, int rank,
-               int world, unsigned epoch, int* status) {
+               int world, unsigned epoch, int* status, int probe) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* bar_area = smem + STAGES * STAGE_BYTES;
@@ -65,7 +65,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = M / BM;                      // host guarantees M % (BM * world) == 0
   const int n_tiles = (N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
+  const int num_tiles = (probe & 4) ? 0 : m_tiles * n_tiles;
   const int num_kb = (K + BK - 1) / BK;
   const int blocks_per_rank = m_tiles / world;
 
@@ -203,7 +203,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ---- copy warps: bring the peers' rows into the local X, in the order the tiles will need them
-    const int ct = threadIdx.x - (THREADS - COPY_THREADS);          // 0..63
+    const int ct = threadIdx.x - (THREADS - COPY_THREADS);          // 0..127
     __nv_bfloat16* x_local = static_cast<__nv_bfloat16*>(xs.p[rank]);
     const int vec_per_row = K >> 3;                                  // 16-byte vectors of one row
     const int chunk_vecs = CHUNK_ROWS * vec_per_row;
@@ -214,14 +214,20 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int blk = owner * blocks_per_rank + blk_seq % blocks_per_rank;
       const int row0 = blk * BM + ch * CHUNK_ROWS;
       const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(xs.p[owner]);
-      constexpr int UNROLL = 8;
-      for (int i0 = ct; i0 < chunk_vecs; i0 += COPY_THREADS * UNROLL) {
+      constexpr int UNROLL = 16;       // 128 threads x 16 x 16 bytes = 32 KiB of peer loads in flight per CTA
+      unsigned sink = 0;
+      for (int i0 = ct; i0 < chunk_vecs && !(probe & 1); i0 += COPY_THREADS * UNROLL) {
         uint4 v[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const int i = i0 + u * COPY_THREADS;
           if (i < chunk_vecs)
             v[u] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8);
+        }
+        if (probe & 2) {
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) sink ^= v[u].x ^ v[u].w;
+          continue;
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -230,10 +236,11 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             *reinterpret_cast<uint4*>(x_local + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8) = v[u];
         }
       }
-      // both copy warps are done with the chunk: publish it (generic-proxy stores, then async-proxy readers)
+      if ((probe & 2) && sink == 0x12345u) record_error(status, RPEG_ERR_FLAG_TIMEOUT, 899, static_cast<int>(sink));
+      // all copy warps are done with the chunk: publish it (generic-proxy stores, then async-proxy readers)
       asm volatile("fence.proxy.async.global;" ::: "memory");
       __threadfence();
-      asm volatile("bar.sync 2, 64;" ::: "memory");
+      asm volatile("bar.sync 2, 128;" ::: "memory");
       if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ready + blk) : "memory");
     }
   }
@@ -252,6 +259,11 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 }  // namespace rpeg
 
 using namespace rpeg;
+
+static int g_ag_probe = 0;
+// Timing aid for development: bit 0 skips the pulls, bit 1 drops the local stores, bit 2 skips the GEMM tiles.
+// Results are wrong with any bit set.
+extern "C" void rpeg_ag_gemm_set_probe(int bits) { g_ag_probe = bits; }
 
 // xs[q]: rank q's X buffer ([M, ldx] bf16, symmetric); on entry rank q's own rows are valid in xs[q] on
 // every rank's view. W [N, ldw] bf16 local; Y [M, ldy] bf16 local. `ready`: local uint32[M / 128], zeroed
@@ -281,6 +293,6 @@ extern "C" int rpeg_ag_gemm(void* const* xs, const void* W, void* Y, unsigned* r
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   ag_gemm_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream_v)>>>(ta, tb, px, ready, static_cast<__nv_bfloat16*>(Y), M, N,
-                                                                                   K, ldx, ldy, rank, world, epoch, status);
+                                                                                   K, ldx, ldy, rank, world, epoch, status, g_ag_probe);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

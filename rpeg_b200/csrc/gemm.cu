@@ -41,11 +41,21 @@ struct GemmCfg {
 
 enum { EPI_BF16 = 0, EPI_F32 = 1 };
 
+// Optional gate in front of the first operand load: `n` version words (written by the GPUs that push new weights
+// into B's buffer, system-scope release) must all have reached `min_version` before any tile of this GEMM is
+// read. The wait is bounded by `timeout_ns`; on expiry the kernel records RPEG_ERR_FLAG_TIMEOUT and drains.
+struct WeightGate {
+  const unsigned* flags;
+  int n;
+  unsigned min_version;
+  unsigned long long timeout_ns;
+};
+
 template <int BN, int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          void* __restrict__ Cout, int M, int N, int K, int ldc, int accumulate, int k_splits,
-                         long long split_stride, int* status) {
+                         long long split_stride, int* status, WeightGate gate) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -110,6 +120,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      if (gate.flags != nullptr) {
+        const uint64_t t0 = global_timer_ns();
+        for (int i = 0; i < gate.n; ++i) {
+          for (;;) {
+            unsigned seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(gate.flags + i) : "memory");
+            if (static_cast<int>(seen - gate.min_version) >= 0) break;
+            if (global_timer_ns() - t0 > gate.timeout_ns) {
+              record_error(status, RPEG_ERR_FLAG_TIMEOUT, 150, i);
+              *abort_flag = 1;
+              goto producer_done;
+            }
+            __nanosleep(500);
+          }
+        }
+        // the new weights were written with ordinary (peer) stores; the loads below go through the async proxy
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+      }
       for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
         int tm, tn;
         tile_coords(w / k_splits, tm, tn);
@@ -278,7 +306,7 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
 template <int BN, int EPI, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, int ldc,
                        int accumulate, int k_splits, long long split_stride, int* status, int num_sms,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, A_MN, B_MN>;
   static bool configured = false;
@@ -290,19 +318,19 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, in
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
   const int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride,
-                                                        status);
+                                                        status, gate);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 template <int BN, int EPI>
 static int dispatch_major(int transA, int transB, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M,
                           int N, int K, int ldc, int accumulate, int k_splits, long long split_stride, int* status,
-                          int num_sms, cudaStream_t stream) {
-  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream);
-  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream);
+                          int num_sms, cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}) {
+  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate);
+  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate);
   if constexpr (BN >= 64) {  // an MN-major B tile is built from 64-column TMA boxes
-    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream);
-    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream);
+    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate);
+    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate);
   }
   return -30;
 }
@@ -313,9 +341,36 @@ static int g_num_sms = 0;
 
 using namespace rpeg;
 
+static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int transA,
+                     int transB, int out_fp32, int accumulate, int bn_hint, float* workspace, long long workspace_elems,
+                     int* status, void* stream_v, WeightGate gate);
+
 extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                               int ldc, int transA, int transB, int out_fp32, int accumulate, int bn_hint,
                               float* workspace, long long workspace_elems, int* status, void* stream_v) {
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, transA, transB, out_fp32, accumulate, bn_hint, workspace,
+                   workspace_elems, status, stream_v, WeightGate{nullptr, 0, 0u, 0ull});
+}
+
+// The same GEMM behind a weight-version gate: no operand tile is loaded before gate_flags[0..gate_words) have all
+// reached min_version (see WeightGate). The first GEMM of a generation phase uses it on the weight buffer that
+// the training ranks push into, so waiting for the push and the first use of the weights are one launch. The
+// in-kernel wait is capped at 1.5 s (below the pipeline's own wait limit); longer waits belong on the host.
+extern "C" int rpeg_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                                    int ldc, int transA, int transB, int out_fp32, int accumulate, int bn_hint,
+                                    float* workspace, long long workspace_elems, const unsigned* gate_flags,
+                                    int gate_words, unsigned min_version, unsigned long long timeout_ns, int* status,
+                                    void* stream_v) {
+  if (gate_flags == nullptr || gate_words < 1) return -6;
+  const unsigned long long cap = 1500000000ull;
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, transA, transB, out_fp32, accumulate, bn_hint, workspace,
+                   workspace_elems, status, stream_v,
+                   WeightGate{gate_flags, gate_words, min_version, timeout_ns < cap ? timeout_ns : cap});
+}
+
+static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int transA,
+                     int transB, int out_fp32, int accumulate, int bn_hint, float* workspace, long long workspace_elems,
+                     int* status, void* stream_v, WeightGate gate) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row pitches; the vector epilogue needs N and ldc % 8 == 0.
@@ -384,9 +439,9 @@ extern "C" int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int 
 #define RPEG_GEMM_CASE(BN_)                                                                                      \
   case BN_:                                                                                                       \
     rc = gemm_fp32 ? dispatch_major<BN_, EPI_F32>(transA, transB, ta, tb, gemm_out, M, N, K, gemm_ldc, accumulate, \
-                                                  k_splits, split_stride, status, g_num_sms, stream)              \
+                                                  k_splits, split_stride, status, g_num_sms, stream, gate)        \
                    : dispatch_major<BN_, EPI_BF16>(transA, transB, ta, tb, gemm_out, M, N, K, gemm_ldc, accumulate, \
-                                                   k_splits, split_stride, status, g_num_sms, stream);            \
+                                                   k_splits, split_stride, status, g_num_sms, stream, gate);      \
     break;
   switch (bn) {
     RPEG_GEMM_CASE(256)

@@ -53,7 +53,7 @@ struct Peers {
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Peers stage,
                Peers counters, Peers outs, int M, int N, int K, int ldo, int rank, int world, unsigned epoch,
-               int all_gather, int* status) {
+               int all_gather, int probe, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* bar_area = smem + STAGES * STAGE_BYTES;
@@ -201,7 +201,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       // this warp's 32 rows of the tile are stored: publish them to the owner (4 arrivals per tile, one
       // per epilogue warp, so no cross-warp barrier is needed on this path)
-      __threadfence_system();
+      if (!(probe & 1)) __threadfence_system();
       __syncwarp();
       if (lane == 0) {
         unsigned* ctr = static_cast<unsigned*>(counters.p[owner]) + (tm - owner * blocks_per_rank);
@@ -216,7 +216,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   if (*abort_flag) {
     __nanosleep(200000);
-  } else {
+  } else if (!(probe & 2)) {
     const unsigned expect = epoch * static_cast<unsigned>(n_tiles * world * 4);
     const unsigned* my_ctr = static_cast<const unsigned*>(counters.p[rank]);
     const __nv_bfloat16* my_stage = static_cast<const __nv_bfloat16*>(stage.p[rank]);
@@ -244,21 +244,32 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!ok) break;
       const int c0 = ch * CHUNK, c1 = min(N, c0 + CHUNK);
       const int vec_per_row = (c1 - c0) >> 3;
-      // four independent 16-byte vectors per thread and pass, all loads issued before the first use, so
-      // enough bytes are in flight to run this tail at memory speed
-      constexpr int UNROLL = 4;
+      // eight independent 16-byte vectors per thread and pass, per source rank: all loads of a pass are issued
+      // before the first use, so enough bytes are in flight to run this tail at memory speed
+      constexpr int UNROLL = 8;
       const int total = BM * vec_per_row;
       for (int i0 = threadIdx.x; i0 < total; i0 += THREADS * UNROLL) {
-        uint4 part[UNROLL][RPEG_MAX_PEERS];
+        float acc[UNROLL][8];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-          const int i = i0 + u * THREADS;
-          if (i < total) {
-            const int row = blk * BM + i / vec_per_row, col = c0 + (i % vec_per_row) * 8;
+        for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
-            for (int s = 0; s < RPEG_MAX_PEERS; ++s)
-              if (s < world)
-                part[u][s] = __ldcg(reinterpret_cast<const uint4*>(my_stage + (static_cast<size_t>(s) * rows_per_rank + row) * N + col));
+          for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+        for (int s = 0; s < world; ++s) {
+          uint4 v[UNROLL];
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const int i = i0 + u * THREADS;
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < total) {
+              const int row = blk * BM + i / vec_per_row, col = c0 + (i % vec_per_row) * 8;
+              v[u] = __ldcg(reinterpret_cast<const uint4*>(my_stage + (static_cast<size_t>(s) * rows_per_rank + row) * N + col));
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const float2 a = unpack_bf16x2(v[u].x), b = unpack_bf16x2(v[u].y), c = unpack_bf16x2(v[u].z), d = unpack_bf16x2(v[u].w);
+            acc[u][0] += a.x; acc[u][1] += a.y; acc[u][2] += b.x; acc[u][3] += b.y;
+            acc[u][4] += c.x; acc[u][5] += c.y; acc[u][6] += d.x; acc[u][7] += d.y;
           }
         }
 #pragma unroll
@@ -266,18 +277,9 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int i = i0 + u * THREADS;
           if (i >= total) break;
           const int row = blk * BM + i / vec_per_row, col = c0 + (i % vec_per_row) * 8;
-          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int s = 0; s < RPEG_MAX_PEERS; ++s) {
-            if (s < world) {
-              const uint4 v = part[u][s];
-              const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
-              acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
-            }
-          }
           uint4 o;
-          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          o.x = pack_bf16x2(acc[u][0], acc[u][1]); o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+          o.z = pack_bf16x2(acc[u][4], acc[u][5]); o.w = pack_bf16x2(acc[u][6], acc[u][7]);
           if (all_gather) {
             const size_t off = (static_cast<size_t>(rank) * rows_per_rank + row) * ldo + col;
             for (int q = 0; q < world; ++q) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[q]) + off) = o;
@@ -300,6 +302,11 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 }  // namespace rpeg
 
 using namespace rpeg;
+
+// Timing probe for development (0 in normal use): bit 0 drops the system fence before the arrival counter, bit 1 skips the
+// owner's reduction. Results are wrong with either bit set.
+static int g_probe = 0;
+extern "C" void rpeg_gemm_rs_set_probe(int bits) { g_probe = bits; }
 
 // A [M, K] (lda), B [N, K] (ldb), both K-major bf16 in this rank's memory. stage[q]: rank q's staging
 // buffer of world * (M / world) * N bf16; counters[q]: rank q's M / world / 128 arrival counters
@@ -335,6 +342,6 @@ extern "C" int rpeg_gemm_rs(const void* A, const void* B, int M, int N, int K, i
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   gemm_rs_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream_v)>>>(ta, tb, ps, pc, po, M, N, K, ldo, rank, world,
-                                                                                   epoch, all_gather, status);
+                                                                                   epoch, all_gather, g_probe, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -124,6 +124,40 @@ __global__ void flag_barrier_kernel(PeerPtrs pads, int rank, int world, int slot
   }
 }
 
+// Version words for pushed data (weights for generation ranks, rollout rows for training ranks). The pusher
+// runs its copy kernels, then this kernel on the same stream: a system-scope fence followed by a release
+// store of `version` into the word `word` of every destination's flag array. A consumer that sees the word
+// has the data (reference: weight-version bookkeeping of RPEG/runtime/weight_versions.py:25-90, where a
+// consumer of step k needs version max(0, k - 1 - tau)).
+__global__ void publish_version_kernel(PeerPtrs flags, int n_dst, int word, unsigned version) {
+  const int t = threadIdx.x;
+  if (t < n_dst) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(static_cast<unsigned*>(flags.p[t]) + word), "r"(version)
+                 : "memory");
+  }
+}
+
+// result[0] = 1 when flags[0..n) all reached `min_version` within `timeout_ns`, else 0 (a poll that runs out is
+// not an error: the host repeats it, so that no kernel ever waits longer than the caller's short bound).
+__global__ void wait_flags_kernel(const unsigned* __restrict__ flags, int n, unsigned min_version,
+                                  unsigned long long timeout_ns, int* __restrict__ result) {
+  const int t = threadIdx.x;
+  bool ok = true;
+  if (t < n) {
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+      unsigned seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + t) : "memory");
+      if (static_cast<int>(seen - min_version) >= 0) break;
+      if (global_timer_ns() - t0 > timeout_ns) { ok = false; break; }
+      __nanosleep(1000);
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (t == 0) result[0] = ok ? 1 : 0;
+}
+
 // reduced[i] = scale * sum_p grads[p][shard_off + i], i in [0, shard_n); sumsq[0] += sum reduced^2.
 __global__ void dp_reduce_norm_kernel(PeerPtrs grads, int world, long long shard_off, long long shard_n,
                                       float scale, float* __restrict__ reduced, float* __restrict__ sumsq) {
@@ -240,6 +274,19 @@ extern "C" int rpeg_flag_barrier(void* const* pads, int rank, int world, int slo
   if (world < 1 || world > RPEG_MAX_PEERS || slot < 0 || slot >= 64) return -2;
   flag_barrier_kernel<<<1, 32, 0, STREAM(stream)>>>(make_peers(pads, world), rank, world, slot, epoch,
                                                    payload_in, payload_out, timeout_ns, status);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_publish_version(void* const* flag_arrays, int n_dst, int word, unsigned version, void* stream) {
+  if (n_dst < 1 || n_dst > RPEG_MAX_PEERS || word < 0) return -2;
+  publish_version_kernel<<<1, 32, 0, STREAM(stream)>>>(make_peers(flag_arrays, n_dst), n_dst, word, version);
+  return LAUNCH_OK();
+}
+
+extern "C" int rpeg_wait_flags(const unsigned* flags, int n, unsigned min_version, unsigned long long timeout_ns,
+                               int* result, void* stream) {
+  if (n < 1 || n > 32 || result == nullptr) return -2;
+  wait_flags_kernel<<<1, 32, 0, STREAM(stream)>>>(flags, n, min_version, timeout_ns, result);
   return LAUNCH_OK();
 }
 

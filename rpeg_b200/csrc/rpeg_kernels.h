@@ -16,6 +16,11 @@ extern "C" {
 int rpeg_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                    int transA, int transB, int out_fp32, int accumulate, int bn_hint, float* workspace,
                    long long workspace_elems, int* status, void* stream);
+// Same GEMM, but no operand is read before gate_flags[0..gate_words) all reached min_version (bounded wait).
+int rpeg_gemm_bf16_gated(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                         int transA, int transB, int out_fp32, int accumulate, int bn_hint, float* workspace,
+                         long long workspace_elems, const unsigned* gate_flags, int gate_words, unsigned min_version,
+                         unsigned long long timeout_ns, int* status, void* stream);
 
 // ---- norm_rope.cu
 int rpeg_rmsnorm_fwd(const void* x, const void* res, const void* w, void* h_out, void* y, float* rstd, int T,
@@ -87,6 +92,11 @@ int rpeg_dp_adam_push(float* p32, float* m, float* v, const float* reduced, void
 int rpeg_copy16(const void* src, void* dst, long long nbytes, void* stream);
 int rpeg_scatter_rows_by_index(const void* src, long long n, long long row_bytes, const long long* global_idx,
                                long long rows_per_rank, void* const* dst, int world, void* stream);
+// Version words of pushed data: release-store `version` into word `word` of every destination flag array after
+// the copies queued before it; poll flags[0..n) >= min_version with a bound (result[0] = 1 reached, 0 not yet).
+int rpeg_publish_version(void* const* flag_arrays, int n_dst, int word, unsigned version, void* stream);
+int rpeg_wait_flags(const unsigned* flags, int n, unsigned min_version, unsigned long long timeout_ns, int* result,
+                    void* stream);
 int rpeg_copy2d(const void* src, long long src_pitch, void* dst, long long dst_pitch, long long rows, long long row_bytes,
                 void* stream);
 

@@ -71,14 +71,22 @@ def _micro(ro: Rollout, cfg: AlgoConfig, group: int = 1) -> List[PackedBatch]:
 
 # ---------------------------------------------------------------------------------- inference ops
 @torch.no_grad()
-def sequence_logprobs(model: LlamaModel, ro: Rollout, cfg: AlgoConfig) -> torch.Tensor:
-    """Per-token log-probs of the responses under ``model`` -> ``[N, T]`` (zeros outside the mask)."""
+def sequence_logprobs(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, pipeline=None) -> torch.Tensor:
+    """Per-token log-probs of the responses under ``model`` -> ``[N, T]`` (zeros outside the mask). With a
+    ``parallel.pp.PipelineRunner`` the microbatches stream through the stages and the last stage's result is
+    relayed to all of them."""
     out = torch.zeros_like(ro.old_logp)
     flat_out = out.view(-1)
+
+    def head(mb, xf):
+        flat_out[mb.flat] = model.token_logprobs(K.gather_rows(xf, mb.sel), mb.targets, cfg.head_chunk, cfg.temperature)
+
+    if pipeline is not None:
+        pipeline.run(_micro(ro, cfg), head, train=False)
+        return pipeline.broadcast_from_last(out)
     for mb in _micro(ro, cfg):
         xf, _ = model.forward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen)
-        lp = model.token_logprobs(K.gather_rows(xf, mb.sel), mb.targets, cfg.head_chunk, cfg.temperature)
-        flat_out[mb.flat] = lp
+        head(mb, xf)
     return out
 
 
@@ -123,18 +131,20 @@ def _scatter_head_grad(xf: torch.Tensor, sel: torch.Tensor, d_rows: torch.Tensor
 
 
 def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None,
-                      value_model_shared: bool = False) -> Dict[str, torch.Tensor]:
+                      value_model_shared: bool = False, pipeline=None) -> Dict[str, torch.Tensor]:
     """Forward + backward of the clipped policy objective over the whole rollout (gradients are
     accumulated over microbatches; the caller runs the optimizer). ``denom_tokens`` is the GLOBAL
     response-token count when the batch is sharded over data-parallel ranks. With
-    ``value_model_shared`` the same trunk also fits the value head (actor-critic sharing)."""
+    ``value_model_shared`` the same trunk also fits the value head (actor-critic sharing). With a
+    ``parallel.pp.PipelineRunner`` (``model`` being this rank's stage) the microbatches run in 1F1B order, the
+    loss is evaluated on the last stage and the metrics are relayed to every stage."""
     denom = float(denom_tokens if denom_tokens is not None else max(1, ro.n_response_tokens()))
     acc = torch.zeros(4, dtype=torch.float32, device=model.device)
     vacc = torch.zeros(4, dtype=torch.float32, device=model.device)
     old, adv, mask = ro.old_logp.view(-1), ro.adv.view(-1), ro.mask.view(-1)
     ref = ro.ref_logp.view(-1) if (ro.ref_logp is not None and cfg.kl_coef != 0.0) else None
-    for mb in _micro(ro, cfg):
-        xf, ctx = model.forward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen, keep=True)
+
+    def head(mb, xf):
         rows = K.gather_rows(xf, mb.sel)
         o_mb, a_mb, m_mb = old[mb.flat], adv[mb.flat], mask[mb.flat]
         r_mb = ref[mb.flat] if ref is not None else None
@@ -151,21 +161,39 @@ def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_
             dv, part = K.value_loss(v, ro.returns.view(-1)[mb.flat], m_mb, 1.0 / denom)
             vacc.add_(part)
             d_rows = K.add_bf16(d_rows, model.scalar_head_bwd(rows, dv * cfg.value_coef))
-        model.backward(ctx, _scatter_head_grad(xf, mb.sel, d_rows))
+        return _scatter_head_grad(xf, mb.sel, d_rows)
+
+    if pipeline is not None:
+        pipeline.run(_micro(ro, cfg), head, train=True)
+        pipeline.broadcast_from_last(acc)
+        pipeline.broadcast_from_last(vacc)
+    else:
+        for mb in _micro(ro, cfg):
+            xf, ctx = model.forward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen, keep=True)
+            model.backward(ctx, head(mb, xf))
     return {"loss": acc[0], "kl_sum": acc[1], "clipped": acc[2], "approx_kl_sum": acc[3], "value_loss": vacc[0]}
 
 
-def critic_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None) -> Dict[str, torch.Tensor]:
+def critic_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None,
+                      pipeline=None) -> Dict[str, torch.Tensor]:
     denom = float(denom_tokens if denom_tokens is not None else max(1, ro.n_response_tokens()))
     acc = torch.zeros(4, dtype=torch.float32, device=model.device)
     ret, mask = ro.returns.view(-1), ro.mask.view(-1)
-    for mb in _micro(ro, cfg):
-        xf, ctx = model.forward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen, keep=True)
+
+    def head(mb, xf):
         rows = K.gather_rows(xf, mb.sel)
         v = model.scalar_values(rows)
         dv, part = K.value_loss(v, ret[mb.flat], mask[mb.flat], 1.0 / denom)
         acc.add_(part)
-        model.backward(ctx, _scatter_head_grad(xf, mb.sel, model.scalar_head_bwd(rows, dv)))
+        return _scatter_head_grad(xf, mb.sel, model.scalar_head_bwd(rows, dv))
+
+    if pipeline is not None:
+        pipeline.run(_micro(ro, cfg), head, train=True)
+        pipeline.broadcast_from_last(acc)
+    else:
+        for mb in _micro(ro, cfg):
+            xf, ctx = model.forward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen, keep=True)
+            model.backward(ctx, head(mb, xf))
     return {"value_loss": acc[0]}
 
 

@@ -85,12 +85,31 @@ class LlamaConfig:
 _ALIGN = 64  # elements; keeps every tensor 128-byte aligned in the flat buffers
 
 
+def stage_layers(n_layers: int, stage: Optional[Tuple[int, int]]) -> Tuple[int, int]:
+    """Layer range ``[lo, hi)`` of pipeline stage ``(index, n_stages)``: contiguous blocks, the first
+    ``n_layers % n_stages`` stages one layer longer (the rule of RPEG/runtime/reshard.py:60-98)."""
+    if stage is None:
+        return 0, n_layers
+    idx, n = stage
+    if not 0 <= idx < n or n > n_layers:
+        raise ValueError(f"bad pipeline stage {stage} for {n_layers} layers")
+    per, extra = divmod(n_layers, n)
+    lo = idx * per + min(idx, extra)
+    return lo, lo + per + (1 if idx < extra else 0)
+
+
 class ParamLayout:
     """Name -> (offset, shape) of every parameter inside the flat buffer."""
 
-    def __init__(self, cfg: LlamaConfig):
+    def __init__(self, cfg: LlamaConfig, stage: Optional[Tuple[int, int]] = None):
+        """``stage = (index, n_stages)`` keeps only that pipeline stage's parameters: its block of layers, the
+        embedding on the first stage, the final norm and the heads on the last (a tied LM head keeps its own
+        copy of the embedding matrix on the last stage when the two stages differ)."""
         self.cfg = cfg
         self.entries: Dict[str, Tuple[int, Tuple[int, ...]]] = {}
+        self.layer_lo, self.layer_hi = stage_layers(cfg.n_layers, stage)
+        self.first = stage is None or stage[0] == 0
+        self.last = stage is None or stage[0] == stage[1] - 1
         off = 0
 
         def add(name: str, *shape: int) -> None:
@@ -100,8 +119,10 @@ class ParamLayout:
             off += (n + _ALIGN - 1) // _ALIGN * _ALIGN
 
         d, f = cfg.d_model, cfg.d_ff
-        add("embed", cfg.vocab, d)
-        for i in range(cfg.n_layers):
+        tied_head = cfg.lm_head and cfg.tie_embeddings
+        if self.first or (self.last and tied_head):
+            add("embed", cfg.vocab, d)
+        for i in range(self.layer_lo, self.layer_hi):
             add(f"l{i}.attn_norm", d)
             add(f"l{i}.wqkv", cfg.qkv_width, d)
             if cfg.qk_norm:
@@ -111,12 +132,13 @@ class ParamLayout:
             add(f"l{i}.mlp_norm", d)
             add(f"l{i}.w_gate_up", 2 * f, d)
             add(f"l{i}.w_down", d, f)
-        add("final_norm", d)
-        if cfg.lm_head and not cfg.tie_embeddings:
-            add("lm_head", cfg.vocab, d)
-        if cfg.scalar_head:
-            add("scalar_head.w", d)
-            add("scalar_head.b", 8)  # element 0 is the bias; padded to a 16-byte slot
+        if self.last:
+            add("final_norm", d)
+            if cfg.lm_head and not cfg.tie_embeddings:
+                add("lm_head", cfg.vocab, d)
+            if cfg.scalar_head:
+                add("scalar_head.w", d)
+                add("scalar_head.b", 8)  # element 0 is the bias; padded to a 16-byte slot
         self.total = off
 
     def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
@@ -145,14 +167,20 @@ class LlamaModel:
     """Weights + kernels for one model instance on one GPU."""
 
     def __init__(self, cfg: LlamaConfig, device, *, trainable: bool = False, recompute: str = "full",
-                 weights: Optional[torch.Tensor] = None, grads: Optional[torch.Tensor] = None, seed: int = 0):
+                 weights: Optional[torch.Tensor] = None, grads: Optional[torch.Tensor] = None, seed: int = 0,
+                 stage: Optional[Tuple[int, int]] = None):
+        """``stage = (index, n_stages)`` builds one pipeline stage: ``forward`` then takes the previous stage's
+        hidden states (``h_in``) unless it is the first, and returns raw hidden states unless it is the last."""
         if cfg.head_dim != 128:
             raise ValueError("the attention kernels are specialised for head_dim = 128")
         if recompute not in ("full", "none"):
             raise ValueError("recompute must be 'full' or 'none'")
         self.cfg = cfg
         self.device = torch.device(device)
-        self.layout = ParamLayout(cfg)
+        self.layout = ParamLayout(cfg, stage)
+        self.stage = stage
+        self.layer_lo, self.layer_hi = self.layout.layer_lo, self.layout.layer_hi
+        self.is_first, self.is_last = self.layout.first, self.layout.last
         self.recompute = recompute
         self.w = weights if weights is not None else torch.empty(self.layout.total, dtype=torch.bfloat16, device=self.device)
         if self.w.numel() < self.layout.total:
@@ -162,12 +190,16 @@ class LlamaModel:
             self.g = grads if grads is not None else torch.zeros(self.layout.total, dtype=torch.float32, device=self.device)
         self.p = {name: self.layout.view(self.w, name) for name in self.layout.entries}
         self.gp = {name: self.layout.view(self.g, name) for name in self.layout.entries} if self.g is not None else {}
-        if cfg.lm_head and cfg.tie_embeddings:      # one matrix, two uses: both gradients accumulate into it
+        if cfg.lm_head and cfg.tie_embeddings and self.is_last:      # one matrix, two uses: both gradients accumulate into it
             self.p["lm_head"] = self.p["embed"]
             if self.g is not None:
                 self.gp["lm_head"] = self.gp["embed"]
         self.cos_t, self.sin_t = K.rope_tables(cfg.max_pos, cfg.head_dim, cfg.rope_theta, self.device, cfg.rope_scaling_factor)
         self._ws: Optional[torch.Tensor] = None  # split-K scratch for decode GEMMs
+        # One-shot weight-version gate (flags, min_version, timeout_s): the next full-sequence forward hands it to
+        # its first GEMM, which then loads no weight tile before the version is complete (weights that other GPUs
+        # are pushing into this model's buffer).
+        self.weight_gate = None
         if weights is None:
             self.init_weights(seed)
 
@@ -213,7 +245,7 @@ class LlamaModel:
         return (pre, rq, rk) if keep_pre else None
 
     # ------------------------------------------------------------------ full-sequence forward
-    def _layer_fwd(self, i: int, res: torch.Tensor, delta: Optional[torch.Tensor], ctx: _FwdCtx, keep: bool):
+    def _layer_fwd(self, i: int, res: torch.Tensor, delta: Optional[torch.Tensor], ctx: _FwdCtx, keep: bool, gate=None):
         """One decoder layer on packed tokens. Input is the residual stream as ``res (+ delta)``;
         returns ``(h1, dn)`` with the layer output being ``h1 + dn`` (the add is fused into the next
         RMSNorm)."""
@@ -223,7 +255,7 @@ class LlamaModel:
             x, rstd1, _ = K.rmsnorm_fwd(h, p[f"l{i}.attn_norm"], cfg.rms_eps)
         else:
             x, rstd1, h = K.rmsnorm_fwd(delta, p[f"l{i}.attn_norm"], cfg.rms_eps, residual=res, want_sum=True)
-        qkv = K.gemm(x, p[f"l{i}.wqkv"])
+        qkv = K.gemm(x, p[f"l{i}.wqkv"], gate=gate)
         qkn = self._qk_norm(i, qkv, keep and self.recompute == "none") if cfg.qk_norm else None
         K.rope_(qkv, ctx.pos, self.cos_t, self.sin_t, 0, cfg.n_heads, cfg.head_dim)
         K.rope_(qkv, ctx.pos, self.cos_t, self.sin_t, cfg.q_width, cfg.n_kv_heads, cfg.head_dim)
@@ -242,17 +274,27 @@ class LlamaModel:
         return h1, dn, qkv
 
     def forward(self, tokens: torch.Tensor, pos: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int,
-                keep: bool = False, kv_sink=None) -> Tuple[torch.Tensor, Optional[_FwdCtx]]:
+                keep: bool = False, kv_sink=None, h_in: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[_FwdCtx]]:
         """Packed causal forward. Returns the final normalised hidden states ``[T, d]`` and, with
         ``keep=True``, the context ``backward`` needs. ``kv_sink(layer, qkv)`` receives each layer's
-        rotated QKV (generation prefill stores K/V into the paged cache through it)."""
+        rotated QKV (generation prefill stores K/V into the paged cache through it). A pipeline stage
+        other than the first starts from ``h_in [T, d]``; one other than the last returns the raw
+        residual stream for the next stage."""
         cfg = self.cfg
         ctx = _FwdCtx(tokens, pos, cu_seqlens, int(max_seqlen))
-        res, delta = K.embed_fwd(tokens, self.p["embed"]), None
-        for i in range(cfg.n_layers):
-            res, delta, qkv = self._layer_fwd(i, res, delta, ctx, keep)
+        if self.is_first:
+            res, delta = K.embed_fwd(tokens, self.p["embed"]), None
+        else:
+            if h_in is None:
+                raise ValueError("a pipeline stage after the first needs h_in")
+            res, delta = h_in, None
+        gate, self.weight_gate = self.weight_gate, None
+        for i in range(self.layer_lo, self.layer_hi):
+            res, delta, qkv = self._layer_fwd(i, res, delta, ctx, keep, gate if i == self.layer_lo else None)
             if kv_sink is not None:
                 kv_sink(i, qkv)
+        if not self.is_last:
+            return K.add_bf16(res, delta), (ctx if keep else None)
         xf, rstd_f, h_last = K.rmsnorm_fwd(delta, self.p["final_norm"], cfg.rms_eps, residual=res, want_sum=True)
         if keep:
             ctx.h_last, ctx.rstd_f = h_last, rstd_f
@@ -311,16 +353,23 @@ class LlamaModel:
         del d_qkv, x
         return K.rmsnorm_bwd(d_x, h, p[f"l{i}.attn_norm"], rstd1, g[f"l{i}.attn_norm"], dres_in=d_h1)
 
-    def backward(self, ctx: _FwdCtx, d_xf: torch.Tensor) -> None:
-        """Accumulate parameter gradients given ``d loss / d xf`` (``xf`` = output of ``forward``)."""
+    def backward(self, ctx: _FwdCtx, d_xf: torch.Tensor) -> Optional[torch.Tensor]:
+        """Accumulate parameter gradients given ``d loss / d xf`` (``xf`` = output of ``forward``). A pipeline
+        stage other than the first returns the gradient of its input for the previous stage."""
         if self.g is None:
             raise RuntimeError("model was built without gradient storage (trainable=False)")
-        d_h = K.rmsnorm_bwd(d_xf, ctx.h_last, self.p["final_norm"], ctx.rstd_f, self.gp["final_norm"])
-        ctx.h_last = None
-        for i in reversed(range(self.cfg.n_layers)):
+        if self.is_last:
+            d_h = K.rmsnorm_bwd(d_xf, ctx.h_last, self.p["final_norm"], ctx.rstd_f, self.gp["final_norm"])
+            ctx.h_last = None
+        else:
+            d_h = d_xf
+        for i in reversed(range(self.layer_lo, self.layer_hi)):
             lc = ctx.layers.pop()
             d_h = self._layer_bwd(i, lc, d_h, ctx)
+        if not self.is_first:
+            return d_h
         K.embed_bwd(ctx.tokens, d_h, self.gp["embed"])
+        return None
 
     # ------------------------------------------------------------------ heads
     def token_logprobs(self, xf_rows: torch.Tensor, targets: torch.Tensor, chunk: int = 8192,

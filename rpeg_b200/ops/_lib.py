@@ -19,6 +19,9 @@ LL = c_longlong
 
 _SIGNATURES = {
     "rpeg_gemm_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, LL, P, P],
+    "rpeg_gemm_bf16_gated": [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, LL, P, I, c_uint, c_ulonglong, P, P],
+    "rpeg_publish_version": [P, I, I, c_uint, P],
+    "rpeg_wait_flags": [P, I, c_uint, c_ulonglong, P, P],
     "rpeg_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
     "rpeg_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, P],
     "rpeg_rope": [P, P, P, P, I, I, I, I, I, I, P],

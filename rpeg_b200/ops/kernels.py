@@ -55,8 +55,11 @@ def _req(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
 # --------------------------------------------------------------------------- GEMM
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
-         bn: int = 0, workspace: torch.Tensor | None = None) -> torch.Tensor:
+         bn: int = 0, workspace: torch.Tensor | None = None, gate: tuple | None = None) -> torch.Tensor:
     """``C[M,N] = op(a) @ op(b).T`` on tcgen05 tensor cores with fp32 accumulation.
+
+    ``gate = (flags uint32 tensor, min_version, timeout_s)`` holds back every operand load until all words of
+    ``flags`` reached ``min_version`` (weights being pushed into ``b`` by other GPUs); the wait is bounded.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` with ``trans_a``); ``b`` is ``[N,K]`` — the ``[out,in]`` layout
     of a linear weight — or ``[K,N]`` with ``trans_b``. Rows may be strided (last dim contiguous).
@@ -84,12 +87,34 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         raise TypeError("gemm output must be bf16 or fp32")
     if M == 0 or N == 0:
         return out
+    if gate is not None:
+        flags, min_version, timeout_s = gate
+        rc = lib().rpeg_gemm_bf16_gated(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                        out.stride(0), int(trans_a), int(trans_b), int(out_dtype == torch.float32),
+                                        int(accumulate), bn, _ptr(workspace), 0 if workspace is None else workspace.numel(),
+                                        flags.data_ptr(), flags.numel(), int(min_version), int(timeout_s * 1e9),
+                                        status_word(a.device).data_ptr(), _stream())
+        check(rc, "rpeg_gemm_bf16_gated")
+        return out
     rc = lib().rpeg_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
                               out.stride(0), int(trans_a), int(trans_b), int(out_dtype == torch.float32),
                               int(accumulate), bn, _ptr(workspace), 0 if workspace is None else workspace.numel(),
                               status_word(a.device).data_ptr(), _stream())
     check(rc, "rpeg_gemm_bf16")
     return out
+
+
+def publish_version(flag_ptrs, word: int, version: int) -> None:
+    """After the copies queued on this stream: store ``version`` into word ``word`` of every flag array in
+    ``flag_ptrs`` (device pointers, local or peer) with system-scope release."""
+    arr = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
+    check(lib().rpeg_publish_version(arr, len(flag_ptrs), int(word), int(version), _stream()), "rpeg_publish_version")
+
+
+def wait_flags(flags: torch.Tensor, min_version: int, timeout_s: float, result: torch.Tensor) -> None:
+    """``result[0] = 1`` (int32) once all words of ``flags`` reached ``min_version``, ``0`` if ``timeout_s`` ran out first."""
+    check(lib().rpeg_wait_flags(flags.data_ptr(), flags.numel(), int(min_version), int(timeout_s * 1e9), result.data_ptr(), _stream()),
+          "rpeg_wait_flags")
 
 
 # --------------------------------------------------------------------------- norm / rope / swiglu

@@ -15,6 +15,8 @@ Checks, each against values computed independently on the host or with NCCL:
                         fp32, four calls in a row over the two input buffers
   7 reshard             tensor-parallel shards -> data-parallel replicas and back with the strided peer-copy executor,
                         bit-exact against the host-side oracle
+  8 TP forward          a two-layer model's token log-probs through the tensor-parallel forward (two all-gather+GEMM and
+                        two GEMM+reduce-scatter launches per layer, vocabulary-parallel head) against the plain forward
 Rank 0 prints one JSON line with ``"ok": true``. Exit code 1 on any mismatch.
 """
 from __future__ import annotations
@@ -192,7 +194,93 @@ def main() -> int:
         ex.close()
     report["reshard_executor_ok"] = all(rs_ok)
 
-    flags = torch.tensor([float(all(v for k, v in report.items() if k != "world"))], device=dev)
+    # 8 tensor-parallel forward (sequence-parallel layers from the fused linears) against the single-GPU forward
+    from ..models.tp_llama import TPLlamaForward
+    tcfg = LlamaConfig.tiny(n_layers=2, d_model=1024, d_ff=1024, n_heads=8, n_kv_heads=8, vocab=1024)
+    tmodel = LlamaModel(tcfg, dev, seed=21)
+    lens = [37, 130, 200]
+    gt = torch.Generator().manual_seed(5)
+    toks = torch.randint(0, tcfg.vocab, (sum(lens),), generator=gt, dtype=torch.int32).to(dev)
+    tgts = torch.randint(0, tcfg.vocab, (sum(lens),), generator=gt, dtype=torch.int32).to(dev)
+    tpos = torch.cat([torch.arange(l) for l in lens]).to(dev, torch.int32)
+    tcu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=dev, dtype=torch.int32)
+    xf_ref, _ = tmodel.forward(toks, tpos, tcu, max(lens))
+    lp_ref = tmodel.token_logprobs(xf_ref, tgts)
+    tp_fwd = TPLlamaForward(tmodel, max_tokens=sum(lens))
+    tp_ok = []
+    for _ in range(2):
+        lp_tp = tp_fwd.token_logprobs(toks, tpos, tcu, max(lens), tgts)
+        torch.cuda.synchronize()
+        K.check_status()
+        tp_ok.append(bool(((lp_tp - lp_ref).abs().max() < 8e-2).item()))
+    dist.barrier()
+    tp_fwd.close()
+    report["tensor_parallel_forward_ok"] = all(tp_ok)
+
+    # 9 pipeline-parallel policy step (1F1B over all ranks as stages) against the same step on the whole model
+    from .pp import PipelineRunner
+    pcfg = LlamaConfig.tiny(n_layers=max(2, world), vocab=512)
+    whole = LlamaModel(pcfg, dev, trainable=True, seed=33)
+    stage_m = LlamaModel(pcfg, dev, trainable=True, seed=1, stage=(rank, world))
+    for name in stage_m.layout.entries:
+        stage_m.p[name].copy_(whole.p[name])
+    gp_ = torch.Generator().manual_seed(91)
+    Np, Sp, Tp_ = 8, 12, 20
+    pl = [int(x) for x in torch.randint(4, Sp + 1, (Np,), generator=gp_)]
+    rl = [int(x) for x in torch.randint(3, Tp_ + 1, (Np,), generator=gp_)]
+    mask_p = torch.zeros(Np, Tp_)
+    for r_, l_ in enumerate(rl):
+        mask_p[r_, :l_] = 1.0
+    ro_p = A.Rollout(prompt_ids=torch.randint(2, pcfg.vocab, (Np, Sp), generator=gp_, dtype=torch.int32).to(dev), prompt_lens=pl,
+                     resp_ids=torch.randint(2, pcfg.vocab, (Np, Tp_), generator=gp_, dtype=torch.int32).to(dev), resp_lens=rl,
+                     old_logp=(-torch.rand(Np, Tp_, generator=gp_) * 3 * mask_p).to(dev), mask=mask_p.to(dev))
+    ro_p.ref_logp = (ro_p.old_logp * 1.05).contiguous()
+    ro_p.adv = (torch.randn(Np, Tp_, generator=gp_) * mask_p).to(dev)
+    palgo = A.AlgoConfig(kl_coef=0.05, micro_tokens=64, head_chunk=64)
+    want_m = A.policy_train_step(whole, ro_p, palgo)
+    runner = PipelineRunner(stage_m)
+    got_m = A.policy_train_step(stage_m, ro_p, palgo, pipeline=runner)
+    lp_whole = A.sequence_logprobs(whole, ro_p, palgo)
+    lp_pipe = A.sequence_logprobs(stage_m, ro_p, palgo, pipeline=runner)
+    torch.cuda.synchronize()
+    K.check_status()
+    pp_ok = [abs(float(got_m["loss"]) - float(want_m["loss"])) < 2e-3 * max(1.0, abs(float(want_m["loss"]))),
+             bool(((lp_whole - lp_pipe).abs().max() < 5e-2).item())]
+    for name in stage_m.layout.entries:
+        a_, b_ = stage_m.gp[name].float(), whole.gp[name].float()
+        pp_ok.append(bool(((a_ - b_).norm() <= 3e-2 * b_.norm() + 1e-6).item()))
+    report["pipeline_parallel_ok"] = all(pp_ok)
+    report["pipeline_p2p_calls"] = runner.p2p_calls
+    dist.barrier()
+
+    # 10 disaggregated GRPO with staleness 1: the first half of the ranks generate, the second half train; weights and
+    #    rollouts cross through versioned peer-memory channels only
+    from ..engine.async_rl import AsyncGRPO
+    half = world // 2
+    acfg = LlamaConfig.tiny(n_layers=2, vocab=512)
+    eng = AsyncGRPO(acfg, gen_ranks=list(range(half)), train_ranks=list(range(half, world)), prompts_per_step=2 * half,
+                    samples_per_prompt=4, max_new=16, prompt_len=8, tau=1, algo=A.AlgoConfig(kl_coef=0.04, micro_tokens=256, head_chunk=128),
+                    lr=1e-3, gen_slots=8, kv_budget_bytes=5e8, seed=3, eos_id=1, device=dev, wait_timeout_s=120.0)
+    ga = torch.Generator().manual_seed(17)
+    seen = []
+    for it in range(3):
+        pr = torch.randint(2, acfg.vocab, (2 * half, 8), generator=ga, dtype=torch.int32)
+        rw = torch.randn(2 * half * 4, generator=ga)
+        seen.append(eng.step(pr, rw))
+    if eng.is_gen:
+        async_ok = [m["weight_version"] for m in seen] == [0.0, 0.0, 1.0] and eng.weights.ready(3, 60.0)
+        final = eng.weights.slot_weights(3).float().sum().reshape(1).double() if async_ok else torch.zeros(1, dtype=torch.float64, device=dev)
+    else:
+        async_ok = [m["published_version"] for m in seen] == [1.0, 2.0, 3.0] and all(m["loss"] == m["loss"] for m in seen)
+        final = eng.actor.w[: eng.actor.layout.total].float().sum().reshape(1).double()
+    torch.cuda.synchronize()
+    lo, hi = final.clone(), final.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    report["async_staleness_ok"] = bool(async_ok) and bool((lo == hi).item())
+    eng.close()
+
+    flags = torch.tensor([float(all(v for k, v in report.items() if k not in ("world", "pipeline_p2p_calls")))], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     report["ok"] = bool(flags.item() == 1.0)
     if rank == 0:

@@ -93,7 +93,7 @@ class LocalWorkerGroupLauncher:
 
     def wait_ready(self, group_id: str, timeout_s: float = 120.0):
         try:
-            return self.control.wait_for_state(group_id, self.launches[group_id].world, ("ready", "running"), timeout_s,
+            return self.control.wait_for_state(group_id, self.launches[group_id].world, ("ready", "running", "finished"), timeout_s,
                                                alive=self.alive(group_id))
         except RuntimeExecutionError:
             self.stop(group_id, grace_s=1.0)      # a group that failed to come up is torn down as a whole

@@ -571,3 +571,39 @@ def test_scatter_rows_by_index_single_rank(cuda_device):
     ref = torch.zeros_like(dst)
     ref[idx] = src
     assert torch.equal(dst, ref)
+
+
+@pytest.mark.gpu
+def test_version_words_publish_wait_and_gated_gemm(cuda_device):
+    """Version words on one GPU (publisher and consumer in the same process, publish first): the poll sees a
+    published version at once and runs out of time for one that nothing publishes; a GEMM behind an open gate
+    equals the plain GEMM; a GEMM behind a gate that never opens gives up within its bound, reports the timeout
+    through the status word and leaves the context usable."""
+    flags = torch.zeros(8, dtype=torch.int32, device=cuda_device)
+    result = torch.zeros(1, dtype=torch.int32, device=cuda_device)
+    K.publish_version([flags.data_ptr()], 0, 5)
+    K.publish_version([flags.data_ptr()], 1, 5)
+    K.wait_flags(flags[:2], 5, 0.05, result)
+    assert result.item() == 1 and flags[:3].tolist() == [5, 5, 0]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    K.wait_flags(flags[:2], 6, 0.02, result)               # version 6 never comes: a poll that runs out, not an error
+    t1.record()
+    assert result.item() == 0
+    assert 15.0 < t0.elapsed_time(t1) < 500.0
+    K.check_status()
+    g = torch.Generator(device=cuda_device).manual_seed(4)
+    a = torch.randn(300, 512, device=cuda_device, generator=g).bfloat16()
+    w = (torch.randn(384, 512, device=cuda_device, generator=g) * 0.05).bfloat16()
+    want = K.gemm(a, w)
+    got = K.gemm(a, w, gate=(flags[:2], 5, 0.5))
+    assert torch.equal(want, got)
+    K.check_status()
+    t0.record()
+    K.gemm(a, w, gate=(flags[:2], 6, 0.03))                 # closed gate: bounded wait, status word, no hang
+    t1.record()
+    with pytest.raises(K.KernelWaitTimeout):
+        K.check_status()
+    assert 20.0 < t0.elapsed_time(t1) < 1500.0
+    assert torch.equal(K.gemm(a, w), want)                  # context and kernel still fine
+    K.check_status()
