@@ -142,6 +142,48 @@ def bench_non_gemm(dev, batch: int = 64, seq: int = 640) -> Dict[str, float]:
             "parts": {"rmsnorm": t_norm, "rope": t_rope, "swiglu": t_act, "flash_attn": t_attn}}
 
 
+def bench_engine_terms(dev, peak: float, parts: Dict[str, float], batch: int = 64, seq: int = 640) -> Dict[str, float]:
+    """The cost model's engine terms: GEMM rate held over seconds (power cap) relative to the burst rate, the rate
+    attention FLOPs reach in a training mix (two forwards with recompute, one backward) relative to the sustained
+    GEMM rate, and the elementwise kernels' seconds per token and layer."""
+    import time
+    import torch
+    from rpeg_b200.ops import kernels as K
+    a = torch.randn(8192, 8192, device=dev).bfloat16()
+    w = torch.randn(8192, 8192, device=dev).bfloat16()
+    out = torch.empty(8192, 8192, dtype=torch.bfloat16, device=dev)
+    for _ in range(3):
+        K.gemm(a, w, out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t_host = 0, time.monotonic()
+    e0.record()
+    while time.monotonic() - t_host < 2.5:
+        for _ in range(50):
+            K.gemm(a, w, out=out)
+        n += 50
+        torch.cuda.synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    sustained = 2 * 8192 ** 3 * n / (e0.elapsed_time(e1) * 1e-3)
+    del a, w, out
+    d, H, hd, s_att, b_att = 4096, 32, 128, 2048, 8
+    T = b_att * s_att
+    qkv = torch.randn(T, 3 * d, device=dev).bfloat16()
+    cu = torch.arange(0, T + 1, s_att, device=dev, dtype=torch.int32)
+    o, lse = K.flash_attn_fwd(qkv, 0, d, 2 * d, cu, s_att, H, H, hd)
+    do = torch.randn_like(o)
+    t_f = timed(lambda: K.flash_attn_fwd(qkv, 0, d, 2 * d, cu, s_att, H, H, hd))
+    t_b = timed(lambda: K.flash_attn_bwd(qkv, 0, d, 2 * d, o, do, lse, cu, s_att, H, H, hd))
+    causal_fwd_flops = T * 2.0 * s_att * d                   # what the cost model counts per layer: 2 * ctx * d per token
+    att_eff = 4.0 * causal_fwd_flops / (2 * t_f + t_b) / sustained
+    elementwise = (2 * parts["rmsnorm"] + parts["rope"] + parts["swiglu"]) / (batch * seq)
+    return {"sustained_flops_fraction": min(1.0, sustained / peak), "attention_flops_eff": min(1.0, att_eff),
+            "elementwise_s_per_token_layer": elementwise, "ffn_matrices": 3.0,
+            "detail": {"sustained_flops": sustained, "flash_fwd_s": t_f, "flash_bwd_s": t_b,
+                       "flash_fwd_tflops": causal_fwd_flops / t_f / 1e12, "flash_bwd_tflops": 2.5 * causal_fwd_flops / t_b / 1e12}}
+
+
 def bench_collectives(dev, world: int) -> Dict[str, float]:
     """NCCL all-reduce sweep (bf16) and rank 0 <-> rank 1 ping-pong; device time, max over ranks."""
     import torch
@@ -180,7 +222,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="Calibrate the planner's hardware model on this machine")
     ap.add_argument("--output", default="hw.yaml")
     ap.add_argument("--decode-layers", type=int, default=32, help="layers of the 7B-shape model used for the decode step")
-    ap.add_argument("--skip", default="", help="comma list of: memory,gemm,decode,non_gemm,collectives")
+    ap.add_argument("--skip", default="", help="comma list of: memory,gemm,decode,non_gemm,engine,collectives")
     args = ap.parse_args(argv)
     import torch
     import torch.distributed as dist
@@ -208,6 +250,10 @@ def main(argv=None) -> int:
             n = bench_non_gemm(dev)
             hw.update({k: n[k] for k in ("non_gemm_constant", "non_gemm_scaling", "non_gemm_batch_cal")})
             detail["non_gemm_parts_s"] = n["parts"]
+            if "engine" not in skip and "gemm" not in skip:
+                e = bench_engine_terms(dev, float(hw["flops_per_gpu"]), n["parts"])
+                hw.update({k: e[k] for k in ("sustained_flops_fraction", "attention_flops_eff", "elementwise_s_per_token_layer", "ffn_matrices")})
+                detail["engine_terms"] = e["detail"]
         if "decode" not in skip:
             d = bench_decode(dev, float(hw["memory_bandwidth"]), args.decode_layers)
             hw["decode_bw_eff"] = d["decode_bw_eff"]
@@ -232,7 +278,8 @@ def main(argv=None) -> int:
             json.dump(detail, f, indent=1)
         print(json.dumps({"output": args.output, **{k: out[k] for k in ("flops_per_gpu", "memory_bandwidth", "gemm_m_half", "decode_bw_eff",
                                                                         "non_gemm_constant", "non_gemm_scaling", "alpha_coll_g", "beta_coll_g",
-                                                                        "alpha_p2p_g", "beta_p2p_g")}}))
+                                                                        "alpha_p2p_g", "beta_p2p_g", "sustained_flops_fraction",
+                                                                        "attention_flops_eff", "elementwise_s_per_token_layer")}}))
     return 0
 
 

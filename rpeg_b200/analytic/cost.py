@@ -46,10 +46,13 @@ class _Shape:
     f: int
     V: int
     sb: int
+    ffn: float = 2.0     # matrices of d x d_ff in the MLP (hardware.ffn_matrices)
 
     @property
-    def layer_params(self) -> int:
-        return 4 * self.d * self.d + 2 * self.d * self.f
+    def layer_params(self) -> float:
+        if self.ffn == 2.0:
+            return 4 * self.d * self.d + 2 * self.d * self.f
+        return 4 * self.d * self.d + self.ffn * self.d * self.f
 
     def layer_flops_per_token(self, ctx: float) -> float:
         """FLOPs / 2 of one layer for one token that attends to ``ctx`` positions."""
@@ -109,13 +112,13 @@ class NodeCostModel:
             opt = self._shape(node.model).params / (dp_shards * pp * pt) * 18 / self.hw.memory_bandwidth
         scale = {Role.GENERATION: self.hw.op_generation_scale, Role.INFERENCE: self.hw.op_inference_scale,
                  Role.TRAINING: self.hw.op_training_scale}.get(role, 1.0)
-        parts = (gemm, bubble, self._intra_comm(node), self._non_gemm(node), opt)
+        parts = (gemm, bubble, self._intra_comm(node), self._non_gemm(node) + self._engine_terms(node), opt)
         return OpTimeBreakdown(*(p * scale for p in parts))
 
     # ------------------------------------------------------------------ batch geometry
     def _shape(self, model: Model) -> _Shape:
         s = self.suite.specs[model]
-        return _Shape(s.L, s.d, s.d_ff, s.V, s.dtype_bytes)
+        return _Shape(s.L, s.d, s.d_ff, s.V, s.dtype_bytes, float(self.hw.ffn_matrices))
 
     def _effective_batch(self, node: ExecNode) -> float:
         if node.n_active is not None:
@@ -172,8 +175,47 @@ class NodeCostModel:
         nbytes = Lpp / pt * sh.layer_params * sh.sb + 2 * b * seq * sh.d * Lpp * sh.sb
         intensity = flops / nbytes if nbytes > 0 else float("inf")
         if intensity >= hw.flops_per_gpu / hw.memory_bandwidth:
-            return hw.flops_per_gpu * self._gemm_efficiency(node, b * seq)
+            return hw.flops_per_gpu * hw.sustained_flops_fraction * self._gemm_efficiency(node, b * seq)
         return intensity * hw.memory_bandwidth
+
+    def _gen_concurrency(self, node: ExecNode, b: float, past: float) -> float:
+        """Rows of one replica that decode together: the microbatch, capped by the generator's slots and by how
+        many contexts of the mean length ``past`` fit into the paged KV pool."""
+        hw, sh = self.hw, self._shape(node.model)
+        c = b
+        if hw.gen_max_concurrency > 0:
+            c = min(c, hw.gen_max_concurrency)
+        if hw.gen_kv_budget_bytes > 0:
+            pd, pp, pt = node.pi
+            per_token = 2 * (sh.d / pt) * sh.sb * (sh.L / pp)
+            c = min(c, hw.gen_kv_budget_bytes / (per_token * max(1.0, past)))
+        return max(1.0, c)
+
+    def _engine_terms(self, node: ExecNode) -> float:
+        """Time the reference's model leaves out and the engine spends: attention FLOPs below the GEMM rate,
+        elementwise kernels, per-step overhead of the decode loop. All zero with the default hardware fields."""
+        hw, sh, w = self.hw, self._shape(node.model), self.workload
+        pd, pp, pt = node.pi
+        P = pd * pp * pt
+        extra = 0.0
+        if node.role is Role.GENERATION:
+            if hw.decode_step_overhead_s > 0:
+                if node.phase_steps is not None:
+                    steps, past = node.phase_steps, w.S + node.phase_t_start + node.phase_steps / 2
+                else:
+                    steps, past = w.T - 1, w.S + w.T / 2
+                b = self._b_local(node)
+                extra += hw.decode_step_overhead_s * steps * b / self._gen_concurrency(node, b, past) * self._effective_mb(node)
+            return extra
+        seq = w.S + w.T
+        n = node.n_seqs if node.n_seqs is not None else w.B * w.K
+        mult = 1.0 if node.role is Role.INFERENCE else (4.0 if self.activation_checkpointing else 3.0)
+        if hw.attention_flops_eff < 1.0:
+            att = mult * n * seq * 2 * sh.L * seq * sh.d
+            extra += att / (P * hw.flops_per_gpu * hw.sustained_flops_fraction) * (1.0 / hw.attention_flops_eff - 1.0)
+        if hw.elementwise_s_per_token_layer > 0:
+            extra += mult * n * seq * sh.L / P * hw.elementwise_s_per_token_layer
+        return extra
 
     def _gemm_efficiency(self, node: ExecNode, m_rows: float) -> float:
         hw = self.hw
@@ -206,10 +248,11 @@ class NodeCostModel:
             flops = b * S * (2 * Lpp / pt) * sh.layer_flops_per_token(S)
             nbytes = w_bytes + 2 * b * S * sh.d * Lpp * sh.sb
             inten = flops / nbytes if nbytes > 0 else float("inf")
-            F = hw.flops_per_gpu * eta if inten >= ridge else inten * hw.memory_bandwidth
+            F = hw.flops_per_gpu * hw.sustained_flops_fraction * eta if inten >= ridge else inten * hw.memory_bandwidth
             w_prefill = self._effective_batch(node) * (S * 2 * sh.L * sh.layer_flops_per_token(S) + 2 * sh.V * sh.d)
             t_total += w_prefill / (P * F) if F > 0 else 0.0
         if steps > 0:
+            b = self._gen_concurrency(node, b, past)
             eta = b / (b + m_half) if m_half > 0 else 1.0
             flops = b * (2 * Lpp / pt) * sh.layer_flops_per_token(past)
             a_bytes = 2 * b * sh.d * Lpp * sh.sb

@@ -10,6 +10,9 @@ Two additions describe an NVSwitch machine such as an 8xB200 node:
     (every GPU reaches every peer at full link bandwidth; all-reduce can reduce in the switch);
   * ``fused_overlap`` in [0, 1] is the measured fraction of a tensor-parallel or data-parallel
     collective that the fused compute+collective kernels hide behind math.
+A third group ("engine terms") prices what this framework's engine does differently from the reference's
+assumptions: a three-matrix MLP, sustained instead of burst GEMM rate, attention and elementwise kernels at their
+own measured rates, and a generator whose concurrency is bounded by its slots and its paged KV pool.
 """
 from __future__ import annotations
 
@@ -51,6 +54,15 @@ class Hardware:
     # --- NVSwitch / fused-kernel extensions (defaults keep the reference's ring model exactly)
     fabric: str = "ring"
     fused_overlap: float = 0.0
+    # --- engine terms, measured by calibrate.py on this framework's kernels (defaults reproduce the reference's
+    #     model exactly; see NodeCostModel._engine_terms)
+    ffn_matrices: float = 2.0                  # 3 for the gated (SwiGLU) MLP the engine runs
+    sustained_flops_fraction: float = 1.0      # long compute-bound operators run under the power cap
+    attention_flops_eff: float = 1.0           # fraction of the GEMM rate that attention FLOPs reach
+    elementwise_s_per_token_layer: float = 0.0 # norms, RoPE, SwiGLU, residual adds: seconds per token and layer (forward)
+    gen_max_concurrency: float = 0.0           # generator slots: rows decoding at once per replica (0 = whole batch)
+    gen_kv_budget_bytes: float = 0.0           # paged KV pool per GPU; caps the concurrency by the mean context (0 = no cap)
+    decode_step_overhead_s: float = 0.0        # per decode step: graph launch, sampling, bookkeeping
 
     @staticmethod
     def _span(allocs: Iterable[Allocation]) -> Tuple[int, int]:

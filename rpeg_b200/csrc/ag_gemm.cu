@@ -5,17 +5,18 @@
 //   rank r computes y_r [M, N_r] = X w_r^T with its slice w_r [N_r, K] of the output features
 //
 // Inside the kernel (persistent, one CTA per SM, 320 threads):
-//   warps 6-9  pull the peers' row blocks through their peer pointers into this GPU's copy of X, 16-row
-//              chunks spread over all CTAs in the order the GEMM will need them, and count each finished
-//              chunk in ready[row block] (device-scope release)
+//   warps 6-9  push this rank's own row blocks through the peer pointers into every peer's copy of X, 16-row
+//              chunks spread over all CTAs, nearest consumer first, and count each finished part of a chunk
+//              in the CONSUMER's ready[row block] (system-scope release). Stores to peer memory are posted and
+//              reach link speed; loads from peer memory measured an order of magnitude slower here.
 //   warp 0     TMA producer: before the first tile of a row block that came from a peer it waits (bounded)
 //              until all chunks of that block have landed, then loads A tiles from the LOCAL X, so every
 //              remote byte crosses NVLink exactly once and the tensor cores read local memory
 //   warp 1     tcgen05.mma into double-buffered TMEM accumulators
 //   warps 2-5  epilogue: TMEM -> bf16 -> y
-// Tiles are ordered so that this rank's own rows come first; the pull of the next peer's rows runs under
-// those MMAs. The copy warps never wait, so the producer's wait always ends; all waits are bounded.
-// The caller orders calls with a cross-rank barrier (every shard written, previous pulls finished).
+// Tiles are ordered so that this rank's own rows come first; the peers' rows arrive under those MMAs.
+// The copy warps never wait, so every rank's pushes complete and the producers' waits end; all waits are bounded.
+// The caller orders calls with a cross-rank barrier (nobody still reads the buffer that is about to be overwritten).
 //
 // The reference gets this through Megatron's ColumnParallelLinear with sequence parallelism: an NCCL
 // all-gather followed by a cuBLAS GEMM (RPEG/runtime/workers/megatron_worker.py:124-303, 676-715).
@@ -50,7 +51,7 @@ struct Peers {
 
 __global__ void __launch_bounds__(THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, Peers xs,
-               unsigned* __restrict__ ready, __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldx, int ldy, int rank,
+               Peers readys, __nv_bfloat16* __restrict__ Y, int M, int N, int K, int ldx, int ldy, int rank,
                int world, unsigned epoch, int* status, int probe) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -104,16 +105,17 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stg = 0;
       uint32_t phase = 0;
       int last_ready_block = -1;
-      const unsigned expect = epoch * static_cast<unsigned>(CHUNKS_PER_BLOCK);
+      const unsigned expect = epoch * static_cast<unsigned>(CHUNKS_PER_BLOCK * (COPY_THREADS / 32));
+      const unsigned* ready = static_cast<const unsigned*>(readys.p[rank]);
       for (int w = blockIdx.x; w < num_tiles; w += gridDim.x) {
         int tm, tn;
         tile_coords(w, tm, tn);
         if (tm / blocks_per_rank != rank && tm != last_ready_block) {
-          // rows of a peer: wait until the copy warps (of all CTAs) have brought the whole block in
+          // rows of a peer: wait until that peer's copy warps have pushed the whole block into this GPU's X
           unsigned seen = 0;
           const uint64_t t0 = global_timer_ns();
           for (;;) {
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ready + tm) : "memory");
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(ready + tm) : "memory");
             if (static_cast<int>(seen - expect) >= 0) break;
             if (*abort_flag) goto producer_done;
             if (global_timer_ns() - t0 > READY_WAIT_NS) {
@@ -202,46 +204,46 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (++buf == 2) { buf = 0; acc_phase ^= 1u; }
     }
   } else {
-    // ---- copy warps: bring the peers' rows into the local X, in the order the tiles will need them
+    // ---- copy warps: PUSH this rank's own rows into every peer's X (remote stores are posted and run at link
+    // speed; remote loads are not), nearest consumer first: rank r - 1 multiplies these rows second, r - 2 third, ...
     const int ct = threadIdx.x - (THREADS - COPY_THREADS);          // 0..127
-    __nv_bfloat16* x_local = static_cast<__nv_bfloat16*>(xs.p[rank]);
+    const int cw = ct >> 5;                                          // copy warp 0..3
+    const __nv_bfloat16* x_local = static_cast<const __nv_bfloat16*>(xs.p[rank]);
     const int vec_per_row = K >> 3;                                  // 16-byte vectors of one row
     const int chunk_vecs = CHUNK_ROWS * vec_per_row;
-    const int remote_chunks = (world - 1) * blocks_per_rank * CHUNKS_PER_BLOCK;
-    for (int g = blockIdx.x; g < remote_chunks; g += gridDim.x) {
-      const int blk_seq = g / CHUNKS_PER_BLOCK, ch = g % CHUNKS_PER_BLOCK;
-      const int owner = (rank + 1 + blk_seq / blocks_per_rank) % world;
-      const int blk = owner * blocks_per_rank + blk_seq % blocks_per_rank;
-      const int row0 = blk * BM + ch * CHUNK_ROWS;
-      const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(xs.p[owner]);
-      constexpr int UNROLL = 16;       // 128 threads x 16 x 16 bytes = 32 KiB of peer loads in flight per CTA
-      unsigned sink = 0;
-      for (int i0 = ct; i0 < chunk_vecs && !(probe & 1); i0 += COPY_THREADS * UNROLL) {
+    const int per_peer = blocks_per_rank * CHUNKS_PER_BLOCK;
+    const int push_chunks = (world - 1) * per_peer;
+    for (int g = blockIdx.x; g < push_chunks && !(probe & 1); g += gridDim.x) {
+      const int step = g / per_peer, rest = g - step * per_peer;
+      const int dst_rank = (rank - 1 - step + 2 * world) % world;
+      const int blk = rank * blocks_per_rank + rest / CHUNKS_PER_BLOCK;
+      const int row0 = blk * BM + (rest % CHUNKS_PER_BLOCK) * CHUNK_ROWS;
+      __nv_bfloat16* x_peer = static_cast<__nv_bfloat16*>(xs.p[dst_rank]);
+      constexpr int UNROLL = 8;
+      for (int i0 = ct; i0 < chunk_vecs; i0 += COPY_THREADS * UNROLL) {
         uint4 v[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const int i = i0 + u * COPY_THREADS;
           if (i < chunk_vecs)
-            v[u] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8);
+            v[u] = *reinterpret_cast<const uint4*>(x_local + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8);
         }
-        if (probe & 2) {
-#pragma unroll
-          for (int u = 0; u < UNROLL; ++u) sink ^= v[u].x ^ v[u].w;
-          continue;
-        }
+        if (probe & 2) continue;
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const int i = i0 + u * COPY_THREADS;
           if (i < chunk_vecs)
-            *reinterpret_cast<uint4*>(x_local + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8) = v[u];
+            *reinterpret_cast<uint4*>(x_peer + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8) = v[u];
         }
       }
-      if ((probe & 2) && sink == 0x12345u) record_error(status, RPEG_ERR_FLAG_TIMEOUT, 899, static_cast<int>(sink));
-      // all copy warps are done with the chunk: publish it (generic-proxy stores, then async-proxy readers)
-      asm volatile("fence.proxy.async.global;" ::: "memory");
-      __threadfence();
-      asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ready + blk) : "memory");
+      // this warp's part of the chunk is on its way: make it visible system-wide, then count it at the consumer
+      __threadfence_system();
+      __syncwarp();
+      if ((ct & 31) == 0) {
+        unsigned* ctr = static_cast<unsigned*>(readys.p[dst_rank]) + blk;
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+      }
+      (void)cw;
     }
   }
 
@@ -265,10 +267,10 @@ static int g_ag_probe = 0;
 // Results are wrong with any bit set.
 extern "C" void rpeg_ag_gemm_set_probe(int bits) { g_ag_probe = bits; }
 
-// xs[q]: rank q's X buffer ([M, ldx] bf16, symmetric); on entry rank q's own rows are valid in xs[q] on
-// every rank's view. W [N, ldw] bf16 local; Y [M, ldy] bf16 local. `ready`: local uint32[M / 128], zeroed
-// once; `epoch` counts calls from 1. M must be a multiple of 128 * world; N, K, ld* multiples of 8.
-extern "C" int rpeg_ag_gemm(void* const* xs, const void* W, void* Y, unsigned* ready, int M, int N, int K, int ldx, int ldw,
+// xs[q]: rank q's X buffer ([M, ldx] bf16, symmetric); on entry rank q's own rows are valid in xs[q]. W [N, ldw]
+// bf16 local; Y [M, ldy] bf16 local. readys[q]: rank q's arrival counters uint32[M / 128] (symmetric, zeroed once);
+// `epoch` counts calls from 1. M must be a multiple of 128 * world; N, K, ld* multiples of 8.
+extern "C" int rpeg_ag_gemm(void* const* xs, const void* W, void* Y, void* const* readys, int M, int N, int K, int ldx, int ldw,
                             int ldy, int rank, int world, unsigned epoch, int* status, void* stream_v) {
   if (world < 1 || world > RPEG_MAX_PEERS || rank < 0 || rank >= world) return -2;
   if (M <= 0 || N <= 0 || K <= 0 || (M % (BM * world)) != 0 || (N & 7) || (K & 7) || (ldx & 7) || (ldw & 7) || (ldy & 7)) return -3;
@@ -288,11 +290,14 @@ extern "C" int rpeg_ag_gemm(void* const* xs, const void* W, void* Y, unsigned* r
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tb, W, K, N, ldw, BK, BN);
   if (rc) return rc - 100;
-  Peers px;
-  for (int i = 0; i < RPEG_MAX_PEERS; ++i) px.p[i] = i < world ? xs[i] : nullptr;
+  Peers px, pr;
+  for (int i = 0; i < RPEG_MAX_PEERS; ++i) {
+    px.p[i] = i < world ? xs[i] : nullptr;
+    pr.p[i] = i < world ? readys[i] : nullptr;
+  }
   const int tiles = (M / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  ag_gemm_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream_v)>>>(ta, tb, px, ready, static_cast<__nv_bfloat16*>(Y), M, N,
+  ag_gemm_kernel<<<grid, THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream_v)>>>(ta, tb, px, pr, static_cast<__nv_bfloat16*>(Y), M, N,
                                                                                    K, ldx, ldy, rank, world, epoch, status, g_ag_probe);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -13,9 +13,9 @@
 // an epilogue warp is done with its 32 rows of a tile, it makes the stores visible system-wide and adds 1
 // to the owner's arrival counter of that 128-row block. Transfers of tile i overlap the MMAs of tile
 // i+1 because the accumulator is double buffered in TMEM.
-// Phase 2: all threads of all CTAs take (row block, column chunk) items of the rows this rank owns,
-// wait (bounded) until the block's counter reached epoch * n_tiles * world * 4 (one arrival per epilogue warp), sum the `world` partials
-// in fp32 and write bf16.
+// Phase 2: all CTAs take 16-row items of the rows this rank owns, wait (bounded) until the block's counter
+// reached epoch * n_tiles * world * 4 (one arrival per epilogue warp), stream the `world` partials through shared
+// memory with bulk copies, sum them in fp32 and write bf16.
 // No CTA waits on a peer before it has issued all of its own pushes, so the ranks cannot deadlock;
 // every wait is bounded by %globaltimer and reports through the status word.
 //
@@ -211,84 +211,121 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   }
 
-  // ---- phase 2: reduce the rows this rank owns
+  // ---- phase 2: reduce the rows this rank owns.
+  // A work item is 16 consecutive rows of a 128-row block: one contiguous 32 * N byte region per source rank in
+  // the staging buffer. One elected thread streams the `world` regions through the (now idle) operand stages with
+  // bulk copies (cp.async.bulk global -> shared, complete_tx on an mbarrier), 8 KiB per source and step and up to
+  // 192 KiB in flight per SM, so the tail runs at memory speed with one CTA per SM; five warps add the slots up in
+  // fp32 and store bf16. Plain loads from six warps kept too few bytes in flight: measured ~1 TB/s.
   __syncwarp();
   __syncthreads();
   if (*abort_flag) {
     __nanosleep(200000);
   } else if (!(probe & 2)) {
+    constexpr int SLOT_BYTES = 8192;
+    constexpr int MAX_GROUPS = 24;
+    constexpr int SUB_ROWS = 16;
+    constexpr int CONSUMER_WARPS = THREADS / 32 - 1;
+    const int group_bytes = world * SLOT_BYTES;
+    const int n_groups = min(MAX_GROUPS, (STAGES * STAGE_BYTES) / group_bytes);
+    uint64_t* rfull = reinterpret_cast<uint64_t*>(bar_area + 128);
+    uint64_t* rempty = rfull + MAX_GROUPS;
+    if (threadIdx.x == 0) {
+      for (int g = 0; g < n_groups; ++g) { mbar_init(&rfull[g], 1); mbar_init(&rempty[g], CONSUMER_WARPS); }
+      fence_mbar_init();
+    }
+    __syncthreads();
     const unsigned expect = epoch * static_cast<unsigned>(n_tiles * world * 4);
     const unsigned* my_ctr = static_cast<const unsigned*>(counters.p[rank]);
-    const __nv_bfloat16* my_stage = static_cast<const __nv_bfloat16*>(stage.p[rank]);
-    constexpr int CHUNK = 512;                        // a work item: 128 rows x 512 columns
-    const int chunks = (N + CHUNK - 1) / CHUNK;
-    const int items = blocks_per_rank * chunks;
-    __shared__ int ready;
-    for (int it = blockIdx.x; it < items; it += gridDim.x) {
-      const int blk = it / chunks, ch = it % chunks;
-      if (threadIdx.x == 0) {
-        unsigned seen = 0;
-        const uint64_t t0 = global_timer_ns();
-        int ok = 1;
-        for (;;) {
-          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_ctr + blk) : "memory");
-          if (static_cast<int>(seen - expect) >= 0) break;
-          if (global_timer_ns() - t0 > PEER_WAIT_NS) { record_error(status, RPEG_ERR_FLAG_TIMEOUT, 730, blk); ok = 0; break; }
-          __nanosleep(100);
+    const uint8_t* my_stage = static_cast<const uint8_t*>(stage.p[rank]);
+    const int items = blocks_per_rank * (BM / SUB_ROWS);
+    const long long region_bytes = static_cast<long long>(SUB_ROWS) * N * 2;
+    const int steps = static_cast<int>((region_bytes + SLOT_BYTES - 1) / SLOT_BYTES);
+    if (warp == 0) {
+      if (lane == 0) {
+        int g = 0;
+        uint32_t ph = 0;
+        int waited_blk = -1;
+        for (int it = blockIdx.x; it < items; it += gridDim.x) {
+          const int blk = it / (BM / SUB_ROWS), sub = it % (BM / SUB_ROWS);
+          if (blk != waited_blk) {
+            unsigned seen = 0;
+            const uint64_t t0 = global_timer_ns();
+            for (;;) {
+              asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(my_ctr + blk) : "memory");
+              if (static_cast<int>(seen - expect) >= 0) break;
+              if (*abort_flag) goto reduce_producer_done;
+              if (global_timer_ns() - t0 > PEER_WAIT_NS) {
+                record_error(status, RPEG_ERR_FLAG_TIMEOUT, 730, blk);
+                *abort_flag = 1;
+                goto reduce_producer_done;
+              }
+              __nanosleep(100);
+            }
+            // the partials were written with ordinary (local and peer) stores; the bulk copies read through the async proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            waited_blk = blk;
+          }
+          const size_t row_off = (static_cast<size_t>(blk) * BM + sub * SUB_ROWS) * N * 2;
+          for (int c = 0; c < steps; ++c) {
+            if (!mbar_wait(&rempty[g], ph ^ 1u, abort_flag, status, 731)) goto reduce_producer_done;
+            const long long off = static_cast<long long>(c) * SLOT_BYTES;
+            const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long long>(SLOT_BYTES), region_bytes - off));
+            mbar_expect_tx(&rfull[g], bytes * world);
+            for (int sr = 0; sr < world; ++sr) {
+              const uint8_t* src = my_stage + static_cast<size_t>(sr) * rows_per_rank * N * 2 + row_off + off;
+              asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                               smem_u32(smem + g * group_bytes + sr * SLOT_BYTES)),
+                           "l"(src), "r"(bytes), "r"(smem_u32(&rfull[g]))
+                           : "memory");
+            }
+            if (++g == n_groups) { g = 0; ph ^= 1u; }
+          }
         }
-        ready = ok;
+      reduce_producer_done:;
       }
-      __syncthreads();
-      const int ok = ready;
-      __syncthreads();
-      if (!ok) break;
-      const int c0 = ch * CHUNK, c1 = min(N, c0 + CHUNK);
-      const int vec_per_row = (c1 - c0) >> 3;
-      // eight independent 16-byte vectors per thread and pass, per source rank: all loads of a pass are issued
-      // before the first use, so enough bytes are in flight to run this tail at memory speed
-      constexpr int UNROLL = 8;
-      const int total = BM * vec_per_row;
-      for (int i0 = threadIdx.x; i0 < total; i0 += THREADS * UNROLL) {
-        float acc[UNROLL][8];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
-        for (int s = 0; s < world; ++s) {
-          uint4 v[UNROLL];
-#pragma unroll
-          for (int u = 0; u < UNROLL; ++u) {
-            const int i = i0 + u * THREADS;
-            v[u] = make_uint4(0u, 0u, 0u, 0u);
-            if (i < total) {
-              const int row = blk * BM + i / vec_per_row, col = c0 + (i % vec_per_row) * 8;
-              v[u] = __ldcg(reinterpret_cast<const uint4*>(my_stage + (static_cast<size_t>(s) * rows_per_rank + row) * N + col));
+    } else {
+      const int ctid = threadIdx.x - 32;
+      constexpr int CONSUMERS = CONSUMER_WARPS * 32;
+      int g = 0;
+      uint32_t ph = 0;
+      bool alive = true;
+      for (int it = blockIdx.x; it < items && alive; it += gridDim.x) {
+        const int blk = it / (BM / SUB_ROWS), sub = it % (BM / SUB_ROWS);
+        const int row_base = blk * BM + sub * SUB_ROWS;
+        for (int c = 0; c < steps; ++c) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&rfull[g], ph, abort_flag, status, 732))) { alive = false; break; }
+          const long long off = static_cast<long long>(c) * SLOT_BYTES;
+          const int nvec = static_cast<int>(min(static_cast<long long>(SLOT_BYTES), region_bytes - off) >> 4);
+          const uint8_t* slot0 = smem + g * group_bytes;
+          for (int v = ctid; v < nvec; v += CONSUMERS) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int sr = 0; sr < world; ++sr) {
+              const uint4 x = *reinterpret_cast<const uint4*>(slot0 + sr * SLOT_BYTES + v * 16);
+              const float2 a = unpack_bf16x2(x.x), b2 = unpack_bf16x2(x.y), c2 = unpack_bf16x2(x.z), d2 = unpack_bf16x2(x.w);
+              acc[0] += a.x; acc[1] += a.y; acc[2] += b2.x; acc[3] += b2.y;
+              acc[4] += c2.x; acc[5] += c2.y; acc[6] += d2.x; acc[7] += d2.y;
+            }
+            const long long e = (off >> 1) + static_cast<long long>(v) * 8;      // element inside the 16-row region
+            const int row = row_base + static_cast<int>(e / N), col = static_cast<int>(e % N);
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+            if (all_gather) {
+              const size_t o_off = (static_cast<size_t>(rank) * rows_per_rank + row) * ldo + col;
+              for (int q = 0; q < world; ++q) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[q]) + o_off) = o;
+            } else {
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[rank]) + static_cast<size_t>(row) * ldo + col) = o;
             }
           }
-#pragma unroll
-          for (int u = 0; u < UNROLL; ++u) {
-            const float2 a = unpack_bf16x2(v[u].x), b = unpack_bf16x2(v[u].y), c = unpack_bf16x2(v[u].z), d = unpack_bf16x2(v[u].w);
-            acc[u][0] += a.x; acc[u][1] += a.y; acc[u][2] += b.x; acc[u][3] += b.y;
-            acc[u][4] += c.x; acc[u][5] += c.y; acc[u][6] += d.x; acc[u][7] += d.y;
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-          const int i = i0 + u * THREADS;
-          if (i >= total) break;
-          const int row = blk * BM + i / vec_per_row, col = c0 + (i % vec_per_row) * 8;
-          uint4 o;
-          o.x = pack_bf16x2(acc[u][0], acc[u][1]); o.y = pack_bf16x2(acc[u][2], acc[u][3]);
-          o.z = pack_bf16x2(acc[u][4], acc[u][5]); o.w = pack_bf16x2(acc[u][6], acc[u][7]);
-          if (all_gather) {
-            const size_t off = (static_cast<size_t>(rank) * rows_per_rank + row) * ldo + col;
-            for (int q = 0; q < world; ++q) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[q]) + off) = o;
-          } else {
-            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(outs.p[rank]) + static_cast<size_t>(row) * ldo + col) = o;
-          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&rempty[g]);
+          if (++g == n_groups) { g = 0; ph ^= 1u; }
         }
       }
     }
+    __syncwarp();
+    if (*abort_flag) __nanosleep(200000);        // bulk copies that were in flight when a wait gave up
   }
   tc_fence_before_sync();
   __syncthreads();

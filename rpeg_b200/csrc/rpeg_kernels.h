@@ -106,7 +106,7 @@ int rpeg_gemm_rs(const void* A, const void* B, int M, int N, int K, int lda, int
                  int* status, void* stream);
 
 // ---- ag_gemm.cu: column-parallel linear = all-gather of the activation rows + GEMM in one launch
-int rpeg_ag_gemm(void* const* xs, const void* W, void* Y, unsigned* ready, int M, int N, int K, int ldx, int ldw, int ldy,
+int rpeg_ag_gemm(void* const* xs, const void* W, void* Y, void* const* readys, int M, int N, int K, int ldx, int ldw, int ldy,
                  int rank, int world, unsigned epoch, int* status, void* stream);
 
 // ---- decode_attn.cu

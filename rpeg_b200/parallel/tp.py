@@ -108,9 +108,9 @@ class RowParallelLinear:
 class ColumnParallelLinear:
     """First half of a tensor-parallel block with a sequence-parallel input: every rank holds ``M / world``
     rows of the activation and a slice ``w_r [N / world, K]`` of the output features. ``forward`` runs a
-    device-side barrier (every rank's rows are written) and then ONE kernel (``csrc/ag_gemm.cu``) that pulls
-    the peers' rows over NVLink into the local copy of ``X`` while its tensor-core tiles already work on the
-    rows that are there. ``X`` is double buffered so a rank may write its next input while a slower peer
+    device-side barrier (nobody still reads the buffer about to be overwritten) and then ONE kernel
+    (``csrc/ag_gemm.cu``) whose copy warps push this rank's rows over NVLink into every peer's copy of ``X`` while
+    its tensor-core tiles already work on the rows that are there. ``X`` is double buffered so a rank may write its next input while a slower peer
     still reads the previous one."""
 
     def __init__(self, weight_shard: torch.Tensor, max_rows: int, device, group=None):
@@ -124,7 +124,7 @@ class ColumnParallelLinear:
             raise ValueError(f"max_rows must be a multiple of {ROW_BLOCK * self.world}")
         self.max_rows = max_rows
         self.x = [SymmetricBuffer(max_rows * self.K * 2, self.device, group) for _ in range(2)]
-        self.ready = torch.zeros(2 * (max_rows // ROW_BLOCK), dtype=torch.int32, device=self.device)
+        self.ready = SymmetricBuffer(2 * (max_rows // ROW_BLOCK) * 4, self.device, group, zero=True)   # arrival counters, one half per X buffer
         self.pad = SignalPad(self.device, group) if self.world > 1 else None
         self.epoch = 0
         self._last_m: Optional[int] = None
@@ -151,7 +151,7 @@ class ColumnParallelLinear:
             torch.cuda.synchronize(self.device)
             if self.world > 1:
                 dist.barrier(group=self.group)
-            self.ready.zero_()
+            self.ready.bytes_view.zero_()
             self.epoch = self.epoch % 2          # keep the buffer parity, restart the counters
             torch.cuda.synchronize(self.device)
         self._last_m = M
@@ -163,10 +163,9 @@ class ColumnParallelLinear:
             check(lib().rpeg_flag_barrier(self.pad.ptr_array(), self.rank, self.world, 0, self.pad.epochs[0], None, None,
                                           BARRIER_TIMEOUT_NS, K.status_word(self.device).data_ptr(), stream), "rpeg_flag_barrier")
         y = torch.empty((M, self.N), dtype=torch.bfloat16, device=self.device)
-        half = self.ready.numel() // 2
-        ready = self.ready[(self.epoch % 2) * half:]
+        ready = self.ready.ptr_array((self.epoch % 2) * (self.max_rows // ROW_BLOCK) * 4)
         calls = (self.epoch + 1) // 2            # how many times this buffer (and its counters) has been used
-        check(lib().rpeg_ag_gemm(buf.ptr_array(), self.w.data_ptr(), y.data_ptr(), ready.data_ptr(), M, self.N, self.K, self.K,
+        check(lib().rpeg_ag_gemm(buf.ptr_array(), self.w.data_ptr(), y.data_ptr(), ready, M, self.N, self.K, self.K,
                                  self.w.stride(0), self.N, self.rank, self.world, calls, K.status_word(self.device).data_ptr(), stream),
               "rpeg_ag_gemm")
         return y
@@ -180,7 +179,7 @@ class ColumnParallelLinear:
         return K.gemm(full, self.w)
 
     def close(self) -> None:
-        for b in self.x:
+        for b in (*self.x, self.ready):
             b.close()
         if self.pad is not None:
             self.pad.close()

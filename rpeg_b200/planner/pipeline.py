@@ -43,7 +43,9 @@ _HW_REQUIRED = ("flops_per_gpu", "memory_per_gpu", "memory_bandwidth",
                 "alpha_p2p_g", "beta_p2p_g", "alpha_p2p_n", "beta_p2p_n", "alpha_p2p_r", "beta_p2p_r")
 _HW_OPTIONAL = ("gemm_m_half", "gemm_k_half", "decode_bw_eff", "non_gemm_constant", "non_gemm_scaling",
                 "non_gemm_batch_cal", "op_generation_scale", "op_inference_scale", "op_training_scale",
-                "activation_comm_overhead_s", "weight_comm_scale", "reshard_scale", "fabric", "fused_overlap")
+                "activation_comm_overhead_s", "weight_comm_scale", "reshard_scale", "fabric", "fused_overlap",
+                "ffn_matrices", "sustained_flops_fraction", "attention_flops_eff", "elementwise_s_per_token_layer",
+                "gen_max_concurrency", "gen_kv_budget_bytes", "decode_step_overhead_s")
 
 
 def make_yaml_loader():

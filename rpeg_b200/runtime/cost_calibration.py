@@ -48,9 +48,48 @@ def fit_scale(pairs: Sequence[Tuple[float, float]]) -> Optional[float]:
     return sum(p * m for p, m in pairs) / den if den > 0 else None
 
 
+def hardware_for_run(run, files: Sequence[str] = ()):
+    """The B200 preset with the run's memory size, overlaid with hardware files in order (a ``calibrate.py``
+    output, then fragments written by earlier fits) and, for the engine backend, with the generator's limits from
+    the run file (slots, paged KV pool) unless a file already sets them."""
+    import yaml
+    from ..analytic.hardware import Hardware
+    hw = b200_nvswitch(mem=float(run.hardware.memory_per_gpu_bytes))
+    names = set(Hardware.field_names())
+    seen = set()
+    for path in files:
+        with open(path) as fh:
+            data = yaml.safe_load(fh) or {}
+        upd = {k: (v if k == "fabric" else float(v)) for k, v in data.items() if k in names and k != "memory_per_gpu"}
+        seen |= set(upd)
+        hw = hw.with_updates(**upd)
+    rt = getattr(run, "runtime", None)
+    extra = {}
+    slots = getattr(rt, "gen_slots", None) if rt is not None else None
+    if slots and "gen_max_concurrency" not in seen:
+        extra["gen_max_concurrency"] = float(slots)
+    kvb = float(getattr(run.hardware, "kv_cache_budget_bytes", 0) or 0)
+    if kvb > 0 and "gen_kv_budget_bytes" not in seen:
+        extra["gen_kv_budget_bytes"] = kvb
+    return hw.with_updates(**extra) if extra else hw
+
+
+def prediction_error(rep: Dict[str, Any]) -> Dict[str, Any]:
+    """Per node class and overall: sum of predicted against sum of measured seconds (signed relative error)."""
+    acc: Dict[str, List[float]] = {}
+    for r in rep["nodes"]:
+        a = acc.setdefault(r["class"], [0.0, 0.0])
+        a[0] += r["predicted_s"]
+        a[1] += r["measured_s"]
+    out = {k: {"predicted_s": p, "measured_s": m, "relative_error": (p - m) / m if m > 0 else None} for k, (p, m) in acc.items()}
+    tp, tm = sum(p for p, _ in acc.values()), sum(m for _, m in acc.values())
+    out["total"] = {"predicted_s": tp, "measured_s": tm, "relative_error": (tp - tm) / tm if tm > 0 else None}
+    return out
+
+
 def calibrate_costs(compiled, events: Sequence[dict], hw=None) -> Dict[str, Any]:
     run = compiled.run_config
-    hw = hw or b200_nvswitch(mem=float(run.hardware.memory_per_gpu_bytes))
+    hw = hw or hardware_for_run(run)
     pol = memory_policy_from_run(run)
     cost = NodeCostModel(hw, compiled.model_suite, compiled.workload, optimizer_stage=pol.optimizer_stage,
                          activation_checkpointing=pol.activation_checkpointing)
@@ -91,13 +130,16 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--config", required=True)
     ap.add_argument("--trace", required=True)
     ap.add_argument("--output", default=None, help="hardware fragment (yaml or json)")
+    ap.add_argument("--hw", action="append", default=[], help="hardware file(s) laid over the B200 preset before predicting: "
+                    "a calibrate.py output and/or a fragment from an earlier fit (validation of that fit on this run)")
     args = ap.parse_args(argv)
     try:
         compiled = compile_runtime_plan(args.config, dry_run=True)
     except RuntimeConfigError as exc:
         print(f"runtime error: {exc}", file=sys.stderr)
         return 2
-    rep = calibrate_costs(compiled, read_trace(args.trace))
+    rep = calibrate_costs(compiled, read_trace(args.trace), hardware_for_run(compiled.run_config, args.hw))
+    rep["prediction_error"] = prediction_error(rep)
     if args.output:
         dump_mapping(rep["hardware"], args.output)
     print(json.dumps({k: v for k, v in rep.items() if k != "nodes"}, indent=2))

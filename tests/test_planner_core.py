@@ -194,6 +194,44 @@ def test_nvswitch_fabric_cheaper_collectives_and_overlap():
     assert hidden.time_breakdown(node).gemm == sw.time_breakdown(node).gemm
 
 
+def test_engine_terms_of_the_cost_model():
+    """The engine terms are off by default and each one moves the prediction the way the engine behaves."""
+    r = build_PPO_RPEG(SUITE, WL)
+    plan = ExecutionPlan()
+    for v in r.vertices:                                       # colocated: generation and inference stay unsplit
+        plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = Allocation((0, 0, 0), (1, 1, 4)), (4, 1, 1), 1
+    low = lower(r, unroll(r, 1), plan, SUITE, 1, workload=WL).by_id()
+    train, inf, gen = low["t_pi@0"], low["i_ref@0"], low["g_pi@0"]
+    base_hw = b200_nvswitch()
+    base = NodeCostModel(base_hw, SUITE, WL)
+    # gated MLP: the GEMM term grows by the parameter ratio (4 d^2 + 3 d f) / (4 d^2 + 2 d f), the attention part stays
+    gated = NodeCostModel(base_hw.with_updates(ffn_matrices=3.0), SUITE, WL)
+    d, f, seq = SPEC.d, SPEC.d_ff, WL.S + WL.T
+    ratio = (4 * d * d + 3 * d * f + seq * d) / (4 * d * d + 2 * d * f + seq * d)
+    assert gated.time_breakdown(inf).gemm / base.time_breakdown(inf).gemm == pytest.approx(ratio, rel=0.02)
+    # sustained rate: compute-bound operators slow down by exactly the fraction
+    sust = NodeCostModel(base_hw.with_updates(sustained_flops_fraction=0.8), SUITE, WL)
+    assert sust.time_breakdown(train).gemm == pytest.approx(base.time_breakdown(train).gemm / 0.8)
+    # attention at half the GEMM rate costs the attention FLOPs once more; elementwise time is linear in tokens
+    att = NodeCostModel(base_hw.with_updates(attention_flops_eff=0.5), SUITE, WL)
+    extra = att.time_breakdown(train).non_gemm - base.time_breakdown(train).non_gemm
+    att_flops = 4 * WL.B * WL.K * seq * 2 * SPEC.L * seq * d
+    assert extra == pytest.approx(att_flops / (4 * base_hw.flops_per_gpu))
+    ew = NodeCostModel(base_hw.with_updates(elementwise_s_per_token_layer=1e-8), SUITE, WL)
+    assert ew.time_breakdown(inf).non_gemm - base.time_breakdown(inf).non_gemm == pytest.approx(WL.B * WL.K * seq * SPEC.L / 4 * 1e-8)
+    # generator limits: fewer rows decoding together -> the weights are streamed more often -> slower; a pool too small
+    # for the batch acts like a slot limit
+    t0 = base.time(gen)
+    slots = NodeCostModel(base_hw.with_updates(gen_max_concurrency=4.0), SUITE, WL).time(gen)
+    pool = NodeCostModel(base_hw.with_updates(gen_kv_budget_bytes=4.0 * 2 * d * 2 * SPEC.L * (WL.S + WL.T / 2)), SUITE, WL).time(gen)
+    roomy = NodeCostModel(base_hw.with_updates(gen_max_concurrency=1e6, gen_kv_budget_bytes=1e15), SUITE, WL).time(gen)
+    assert slots > 1.5 * t0 and roomy == pytest.approx(t0)
+    if gen.phase_steps is None:
+        assert pool == pytest.approx(slots, rel=1e-6)
+    step = NodeCostModel(base_hw.with_updates(decode_step_overhead_s=1e-3), SUITE, WL).time(gen) - t0
+    assert step > 0
+
+
 def test_validity_gate():
     r = build_PPO_RPEG(SUITE, WL)
     mm = NodeMemoryModel.from_policy(example_hw(), SUITE, WL, MemoryPolicy(), trainable=frozenset(r.trainable))
