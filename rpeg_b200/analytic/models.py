@@ -20,6 +20,11 @@ class ModelSpec:
     parameter_count: Optional[int] = None
 
 
+# Stand-in for a reward that is a rule, not a network (length penalties, exact-match checkers, host-provided scores):
+# the algorithm graph still has a reward vertex, but it must cost (almost) nothing in time and memory.
+RULE_REWARD_SPEC = ModelSpec(1, 128, 128, 128)
+
+
 def base_transformer_params(spec: ModelSpec) -> int:
     if spec.parameter_count is not None:
         return int(spec.parameter_count)

@@ -22,7 +22,7 @@ from typing import Any, Dict, List, Optional, Tuple
 
 from ..analytic.hardware import Hardware, b200_nvswitch
 from ..analytic.memory import MemoryPolicy, NodeMemoryModel, mem_worst_violation, optimizer_stage
-from ..analytic.models import ModelSpec, ModelSuite
+from ..analytic.models import RULE_REWARD_SPEC, ModelSpec, ModelSuite
 from ..analytic.workload import Workload
 from ..core.types import Allocation, DeviceSpace, Model, Role, TransferResourcePolicy, packing_geometry
 from ..ir.plan import ExecutionPlan
@@ -127,8 +127,8 @@ def _suite(run: RuntimeRunConfig) -> ModelSuite:
              Model.REFERENCE: spec(run.models["reference"]) if "reference" in run.models else actor}
     if "critic" in run.models:
         specs[Model.CRITIC] = spec(run.models["critic"])
-    # a rule-based reward has no model entry; the template's reward vertex is then priced like the actor
-    specs[Model.REWARD] = spec(run.models["reward"]) if "reward" in run.models else actor
+    # a rule-based reward has no model entry; the template's reward vertex then costs (almost) nothing
+    specs[Model.REWARD] = spec(run.models["reward"]) if "reward" in run.models else RULE_REWARD_SPEC
     return ModelSuite(specs)
 
 

@@ -56,20 +56,18 @@ def hardware_for_run(run, files: Sequence[str] = ()):
     from ..analytic.hardware import Hardware
     hw = b200_nvswitch(mem=float(run.hardware.memory_per_gpu_bytes))
     names = set(Hardware.field_names())
-    seen = set()
     for path in files:
         with open(path) as fh:
             data = yaml.safe_load(fh) or {}
         upd = {k: (v if k == "fabric" else float(v)) for k, v in data.items() if k in names and k != "memory_per_gpu"}
-        seen |= set(upd)
         hw = hw.with_updates(**upd)
     rt = getattr(run, "runtime", None)
     extra = {}
     slots = getattr(rt, "gen_slots", None) if rt is not None else None
-    if slots and "gen_max_concurrency" not in seen:
+    if slots and not hw.gen_max_concurrency > 0:
         extra["gen_max_concurrency"] = float(slots)
     kvb = float(getattr(run.hardware, "kv_cache_budget_bytes", 0) or 0)
-    if kvb > 0 and "gen_kv_budget_bytes" not in seen:
+    if kvb > 0 and not hw.gen_kv_budget_bytes > 0:
         extra["gen_kv_budget_bytes"] = kvb
     return hw.with_updates(**extra) if extra else hw
 

@@ -28,7 +28,7 @@ from typing import Any, Dict, List, Optional, Tuple
 from ..analytic.cost import NodeCostModel
 from ..analytic.hardware import Hardware, b200_nvswitch
 from ..analytic.memory import MemoryPolicy, NodeMemoryModel, optimizer_stage
-from ..analytic.models import ModelSpec, ModelSuite
+from ..analytic.models import RULE_REWARD_SPEC, ModelSpec, ModelSuite
 from ..analytic.workload import Workload
 from ..core.types import DeviceSpace, Model, TransferResourcePolicy
 from ..ir.serialize import execution_schedule_to_dict, load_plan, optimized_plan_to_dict, plan_to_dict
@@ -120,7 +120,8 @@ def job_suite(cfg: dict) -> ModelSuite:
     specs = {Model.ACTOR: actor, Model.AC_SHARE: actor, Model.REFERENCE: of("reference")}
     if "critic" in models:
         specs[Model.CRITIC] = of("critic")
-    specs[Model.REWARD] = of("reward")      # without an entry the reward vertex is priced like the actor
+    # without an entry the reward is a rule computed on the host: the vertex stays in the graph at (almost) no cost
+    specs[Model.REWARD] = of("reward") if "reward" in models else RULE_REWARD_SPEC
     return ModelSuite(specs)
 
 
@@ -194,6 +195,30 @@ def predicted_schedule(config: Configuration, suite, workload, hw, horizon: int,
                          activation_checkpointing=policy.activation_checkpointing)
     kw = {} if config.transfer_resource_policy is None else {"transfer_resource_policy": config.transfer_resource_policy}
     return schedule(lowered, cost, config.device_space, **kw), lowered
+
+
+def data_parallel_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k_eval: int, policy: MemoryPolicy, fusion: bool,
+                                transfer_policy) -> Optional[Configuration]:
+    """The plan family the engine backend executes: every vertex data parallel over all GPUs (``pi = (G, 1, 1)`` on
+    the whole device space), with the smallest microbatch count that the memory model accepts."""
+    from ..core.types import Allocation
+    from ..ir.plan import ExecutionPlan
+    from ..search.evaluate import evaluate_uncached
+    g = space.num_devices()
+    full = Allocation((0, 0, 0), (space.R, space.N, space.G))
+    last = None
+    for mb in (1, 2, 4, 8, 16, 32, 64):
+        plan = ExecutionPlan()
+        for v in rpeg.vertices:
+            plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (g, 1, 1), mb
+        last = Configuration(rpeg, plan, space, fusion, transfer_policy)
+        try:
+            feasible = evaluate_uncached(last, suite, workload, hw, k_eval, policy)[2]
+        except Exception:
+            feasible = False
+        if feasible:
+            return last
+    return None
 
 
 def validated_seed_plan(cfg: dict, base_dir: Path, rpeg, space: DeviceSpace, algorithm: str, ac_share: bool):
@@ -309,6 +334,17 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, qu
     start = Configuration(rpeg, start_plan, space, fusion, transfer_policy)
     t0 = time.perf_counter()
     best, feasible, reports = None, False, []
+    # ``optimizer.plan_family``: "search" explores placements and (dp, pp, tp) per vertex; "data_parallel" emits the one
+    # plan the engine backend executes (it is the default for engine jobs on more than one GPU).
+    engine_job = str((cfg.get("runtime") or {}).get("default_backend", "")) == "engine"
+    family = str(options.get("plan_family", "data_parallel" if engine_job and space.num_devices() > 1 else "search"))
+    if family not in ("search", "data_parallel"):
+        raise RuntimeConfigError(f"[optimizer] unknown plan_family {family!r}")
+    if family == "data_parallel":
+        best = data_parallel_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy)
+        if best is None:
+            raise RuntimeConfigError("the data-parallel plan does not fit into memory on this machine")
+        feasible, attempts = True, 0
     for attempt in range(attempts):
         oc = job_optimizer_config(cfg, algorithm, policy, ac_share, seed0 + attempt)
         cache, rep = EvalCache(), []

@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 from typing import Any, Dict, List, Optional
 
@@ -30,6 +31,12 @@ def execute_compiled(compiled: CompiledRuntimePlan, backend: str, *, trace_path=
     run = compiled.run_config
     graph = compiled.runtime_graph()
     trace_file = run.resolve(trace_path or run.runtime.trace_path)
+    # One process per GPU runs the same graph: rank 0 owns the run's trace, summary and alert files, the other
+    # ranks keep their own trace next to it (``run.rank3.jsonl``) and verify it without writing summaries.
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    secondary = backend == "engine" and world > 1 and rank > 0
+    if secondary:
+        trace_file = trace_file.with_name(f"{trace_file.stem}.rank{rank}{trace_file.suffix}")
     if backend == "metadata":
         make_handler = lambda attempt: MetadataOnlyOperationHandler(compiled)
     elif backend == "engine":
@@ -50,6 +57,10 @@ def execute_compiled(compiled: CompiledRuntimePlan, backend: str, *, trace_path=
     events = read_trace(trace_file)
     report = verify_runtime_trace(compiled, graph, events, raise_on_error=False,
                                   completed_before=outcome.get("completed_before", ()) if run.checkpoints.resume_from else ())
+    if secondary:
+        return {"run_id": run.run_id, "backend": backend, "rank": rank, "trace": str(trace_file), "events": len(events),
+                "verification": report, "alerts": None, "attempts": outcome.get("attempts"),
+                "error": None if error is None else str(error), "summary": {}}
     written = write_runtime_summary_for_run(run, events, verification=report,
                                             extra={"backend": backend, "attempts": outcome.get("attempts"),
                                                    "restored_step": outcome.get("restored_step")})

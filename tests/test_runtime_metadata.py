@@ -100,6 +100,25 @@ def execute(compiled, tmp_path, handler=None, name="trace.jsonl", **kw):
     return graph, ctx, read_trace(tmp_path / name)
 
 
+def test_engine_jobs_get_the_data_parallel_plan_family(tmp_path):
+    """A job for the engine backend on several GPUs is planned as the one family that backend executes:
+    every vertex (G, 1, 1) on the whole node; the pair compiles and passes the backend's own plan check."""
+    from rpeg_b200.runtime.engine_backend import validate_engine_plan
+    cfg = job_mapping("grpo", steps=2, runtime={"default_backend": "engine", "gen_slots": 8, "micro_tokens": 1024})
+    cfg["device_space"] = {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4}
+    job = tmp_path / "job.yaml"
+    dump_mapping(cfg, job)
+    res = plan_runtime_job(job, tmp_path / "out", quiet=True)
+    compiled = res["compiled"]
+    assert {tuple(pi) for pi in compiled.config.plan.pi.values()} == {(4, 1, 1)}
+    validate_engine_plan(compiled)
+    assert res["comparison"]["evaluations"] == 0                      # nothing was searched
+    cfg["optimizer"]["plan_family"] = "bogus"
+    dump_mapping(cfg, job)
+    with pytest.raises(RuntimeConfigError):
+        plan_runtime_job(job, tmp_path / "out2", quiet=True)
+
+
 def test_job_planner_emits_a_compilable_pair(tmp_path):
     job = tmp_path / "job.yaml"
     dump_mapping(job_mapping("ppo"), job)
