@@ -40,6 +40,7 @@ CONFIGS = {
     "ppo_acshare_13b": dict(algo="ppo", model="llama13b", prompts=128, k=1, prompt_len=256, max_new=1024, shared=True,
                             quantiles=((0.5, 256), (0.85, 512), (1.0, 1024)), min_gpus=4),
     "ppo_tiny": dict(algo="ppo", model="tiny", prompts=16, k=1, prompt_len=32, max_new=64, quantiles=((0.5, 16), (0.9, 32), (1.0, 64))),
+    "dpo_tiny": dict(algo="dpo", model="tiny", prompts=16, k=2, prompt_len=32, max_new=64, quantiles=None),
 }
 
 
@@ -182,7 +183,8 @@ def main() -> None:
     if spec["algo"] == "grpo":
         # KV pages are handed out on demand, so the slot count may exceed what the budget holds at full length.
         # One rank keeps the whole fp32 Adam state (81 GB for 7B) and has ~56 GB for KV; sharded ranks have more.
-        slots = args.gen_slots or min(b_local * Kk, 96 if world == 1 else 128)
+        # the K samples of a prompt share its KV pages, so the pool holds every row of the rank at once
+        slots = args.gen_slots or min(b_local * Kk, 256)
         kv_gb = args.kv_gb or {1: 56.0, 2: 76.0}.get(world, 96.0)
         trainer = GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp,
                               gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)

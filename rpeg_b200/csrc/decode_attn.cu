@@ -196,6 +196,7 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
                          const int* __restrict__ page_table, int max_pages, const int* __restrict__ seq_lens,
                          __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int H, int Hkv,
                          int nsplit, float scale_log2) {
+  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
   __shared__ float red_m[4], red_l[4];
   __shared__ __align__(16) float red_o[4][HD];
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
@@ -302,6 +303,7 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
 
 __global__ void __launch_bounds__(HD)
 decode_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int H, int nsplit) {
+  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
   const int h = blockIdx.x, b = blockIdx.y;
   const float* pp = partial + (static_cast<size_t>(b) * H + h) * nsplit * (HD + 2);
   float gm = -INFINITY;

@@ -18,6 +18,7 @@
 // Replaces the cuBLASLt / TransformerEngine GEMMs the reference reaches through megatron-core
 // (reference: RPEG/runtime/workers/megatron_worker.py:676-715 builds the GPTModel whose
 // linear_qkv / linear_proj / linear_fc1 / linear_fc2 / output_layer run them).
+#include <cstdlib>
 #include "common.cuh"
 #include "rpeg_kernels.h"
 
@@ -55,7 +56,7 @@ template <int BN, int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          void* __restrict__ Cout, int M, int N, int K, int ldc, int accumulate, int k_splits,
-                         long long split_stride, int* status, WeightGate gate) {
+                         long long split_stride, int* status, WeightGate gate, int pdl) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -103,6 +104,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched as a programmatic dependent (decode: B is a weight matrix that no kernel of the step writes): the
+  // set-up above already ran under the previous kernel's tail, and the producer streams the first weight tiles
+  // before it waits for that kernel; every other thread waits here, before it can touch A, C or the workspace.
+  if (pdl && threadIdx.x != 0) griddep_wait();
 
   // Tile order: groups of 8 M-tiles sweep N together so the A rows stay in L2.
   constexpr int GROUP_M = 8;
@@ -120,6 +125,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      int skip = 0;                      // k-blocks of the first item that the early weight prefetch already issued
       if (gate.flags != nullptr) {
         const uint64_t t0 = global_timer_ns();
         for (int i = 0; i < gate.n; ++i) {
@@ -138,12 +144,37 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         // the new weights were written with ordinary (peer) stores; the loads below go through the async proxy
         asm volatile("fence.proxy.async.global;" ::: "memory");
       }
+      if (pdl) {
+        if constexpr (!A_MN && !B_MN) {
+          if (static_cast<int>(blockIdx.x) < num_items) {
+            int tm, tn;
+            tile_coords(blockIdx.x / k_splits, tm, tn);
+            const int kb0 = (blockIdx.x % k_splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+            const int pre = min(STAGES, kb1 - kb0);
+            for (int i = 0; i < pre; ++i) {            // weights first: they do not depend on the previous kernel
+              mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+              tma_load_2d(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmap_b, &full_bar[i], (kb0 + i) * BK, tn * BN);
+            }
+            griddep_wait();
+            for (int i = 0; i < pre; ++i)
+              tma_load_2d(smem + i * Cfg::STAGE_BYTES, &tmap_a, &full_bar[i], (kb0 + i) * BK, tm * BM);
+            skip = pre;
+            if (pre == STAGES) phase = 1u; else stage = pre;
+          } else {
+            griddep_wait();
+          }
+        } else {
+          griddep_wait();
+        }
+      }
       for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
         int tm, tn;
         tile_coords(w / k_splits, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
         const int kb0 = (w % k_splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        const int kb_first = kb0 + skip;
+        skip = 0;
+        for (int kb = kb_first; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, 100)) goto producer_done;
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
@@ -306,7 +337,7 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
 template <int BN, int EPI, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, int ldc,
                        int accumulate, int k_splits, long long split_stride, int* status, int num_sms,
-                       cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}) {
+                       cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}, int pdl = 0) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, A_MN, B_MN>;
   static bool configured = false;
@@ -317,25 +348,50 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, in
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * k_splits;
   const int grid = tiles < num_sms ? tiles : num_sms;
+  if (pdl) {
+    // programmatic dependent launch: this grid may be scheduled while the previous kernel of the stream drains
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, gate, 1) == cudaSuccess
+               ? 0 : -21;
+  }
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride,
-                                                        status, gate);
+                                                        status, gate, 0);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 template <int BN, int EPI>
 static int dispatch_major(int transA, int transB, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M,
                           int N, int K, int ldc, int accumulate, int k_splits, long long split_stride, int* status,
-                          int num_sms, cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}) {
-  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate);
-  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate);
+                          int num_sms, cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}, int pdl = 0) {
+  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl);
+  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl);
   if constexpr (BN >= 64) {  // an MN-major B tile is built from 64-column TMA boxes
-    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate);
-    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate);
+    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl);
+    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl);
   }
   return -30;
 }
 
 static int g_num_sms = 0;
+
+// Programmatic dependent launch of the decode GEMMs (RPEG_PDL=0 turns it off).
+static int pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RPEG_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v;
+}
 
 }  // namespace rpeg
 
@@ -428,6 +484,9 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
       gemm_fp32 = 1;
     }
   }
+  // Decode GEMMs (the caller passes the split-K workspace): activation x weight^T, and no kernel of a decode step
+  // writes the weights, so the grid may start under the previous kernel's tail and prefetch weight tiles.
+  const int pdl = (workspace != nullptr && !transA && !transB && !accumulate && gate.flags == nullptr) ? pdl_enabled() : 0;
   CUtensorMap ta, tb;
   int rc;
   if (!transA) rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
@@ -439,9 +498,9 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
 #define RPEG_GEMM_CASE(BN_)                                                                                      \
   case BN_:                                                                                                       \
     rc = gemm_fp32 ? dispatch_major<BN_, EPI_F32>(transA, transB, ta, tb, gemm_out, M, N, K, gemm_ldc, accumulate, \
-                                                  k_splits, split_stride, status, g_num_sms, stream, gate)        \
+                                                  k_splits, split_stride, status, g_num_sms, stream, gate, pdl)   \
                    : dispatch_major<BN_, EPI_BF16>(transA, transB, ta, tb, gemm_out, M, N, K, gemm_ldc, accumulate, \
-                                                   k_splits, split_stride, status, g_num_sms, stream, gate);      \
+                                                   k_splits, split_stride, status, g_num_sms, stream, gate, pdl); \
     break;
   switch (bn) {
     RPEG_GEMM_CASE(256)
@@ -504,9 +563,13 @@ extern "C" int rpeg_gemm_bf16_partials(const void* A, const void* B, int M, int 
   rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
   if (rc) return rc - 100;
   switch (bn) {
-    case 256: return launch_gemm<256, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream);
-    case 128: return launch_gemm<128, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream);
-    case 64: return launch_gemm<64, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream);
-    default: return launch_gemm<32, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream);
+    case 256: return launch_gemm<256, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
+                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled());
+    case 128: return launch_gemm<128, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
+                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled());
+    case 64: return launch_gemm<64, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
+                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled());
+    default: return launch_gemm<32, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
+                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled());
   }
 }

@@ -237,6 +237,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
                        __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int d, float eps) {
+  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
   __shared__ float warp_ss[8];
   const int row = blockIdx.x;
   const int nvec = d >> 3;
@@ -386,6 +387,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_fwd_partials_kernel(const float* __restrict__ parts, int splits, long long stride,
                             const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w,
                             __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ y, int d, float eps) {
+  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
   __shared__ float warp_ss[8];
   const int row = blockIdx.x;
   const int nvec = d >> 3;
@@ -448,6 +450,7 @@ rmsnorm_fwd_partials_kernel(const float* __restrict__ parts, int splits, long lo
 // out[t, j] = silu(g) * u with [g | u] = sum_s parts[s][t, :]
 __global__ void swiglu_fwd_partials_kernel(const float* __restrict__ parts, int splits, long long stride,
                                            __nv_bfloat16* __restrict__ out, long long T, int f) {
+  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
   const int fv = f >> 3;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * fv) return;
@@ -499,6 +502,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const int* __restri
 // out[t, j] = silu(gu[t, j]) * gu[t, f + j]
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                   long long T, int f) {
+  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
   const int fv = f >> 3;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * fv) return;

@@ -130,15 +130,10 @@ def _scatter_head_grad(xf: torch.Tensor, sel: torch.Tensor, d_rows: torch.Tensor
     return d_xf
 
 
-def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None,
-                      value_model_shared: bool = False, pipeline=None) -> Dict[str, torch.Tensor]:
-    """Forward + backward of the clipped policy objective over the whole rollout (gradients are
-    accumulated over microbatches; the caller runs the optimizer). ``denom_tokens`` is the GLOBAL
-    response-token count when the batch is sharded over data-parallel ranks. With
-    ``value_model_shared`` the same trunk also fits the value head (actor-critic sharing). With a
-    ``parallel.pp.PipelineRunner`` (``model`` being this rank's stage) the microbatches run in 1F1B order, the
-    loss is evaluated on the last stage and the metrics are relayed to every stage."""
-    denom = float(denom_tokens if denom_tokens is not None else max(1, ro.n_response_tokens()))
+def make_policy_head(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, denom: float, value_model_shared: bool = False):
+    """``head(mb, xf) -> d_xf`` of the clipped policy objective for one microbatch (LM head forward/backward fused with
+    the loss), plus the accumulators it adds its partial sums to: ``(head, acc[4], vacc[4])``. The closure is what a
+    plain microbatch loop, a pipeline's last stage or a fused two-model pipeline calls on the final hidden states."""
     acc = torch.zeros(4, dtype=torch.float32, device=model.device)
     vacc = torch.zeros(4, dtype=torch.float32, device=model.device)
     old, adv, mask = ro.old_logp.view(-1), ro.adv.view(-1), ro.mask.view(-1)
@@ -163,6 +158,34 @@ def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_
             d_rows = K.add_bf16(d_rows, model.scalar_head_bwd(rows, dv * cfg.value_coef))
         return _scatter_head_grad(xf, mb.sel, d_rows)
 
+    return head, acc, vacc
+
+
+def make_critic_head(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, denom: float):
+    """``head(mb, xf) -> d_xf`` of the masked value loss and its accumulator ``acc[4]``."""
+    acc = torch.zeros(4, dtype=torch.float32, device=model.device)
+    ret, mask = ro.returns.view(-1), ro.mask.view(-1)
+
+    def head(mb, xf):
+        rows = K.gather_rows(xf, mb.sel)
+        v = model.scalar_values(rows)
+        dv, part = K.value_loss(v, ret[mb.flat], mask[mb.flat], 1.0 / denom)
+        acc.add_(part)
+        return _scatter_head_grad(xf, mb.sel, model.scalar_head_bwd(rows, dv))
+
+    return head, acc
+
+
+def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None,
+                      value_model_shared: bool = False, pipeline=None) -> Dict[str, torch.Tensor]:
+    """Forward + backward of the clipped policy objective over the whole rollout (gradients are
+    accumulated over microbatches; the caller runs the optimizer). ``denom_tokens`` is the GLOBAL
+    response-token count when the batch is sharded over data-parallel ranks. With
+    ``value_model_shared`` the same trunk also fits the value head (actor-critic sharing). With a
+    ``parallel.pp.PipelineRunner`` (``model`` being this rank's stage) the microbatches run in 1F1B order, the
+    loss is evaluated on the last stage and the metrics are relayed to every stage."""
+    denom = float(denom_tokens if denom_tokens is not None else max(1, ro.n_response_tokens()))
+    head, acc, vacc = make_policy_head(model, ro, cfg, denom, value_model_shared)
     if pipeline is not None:
         pipeline.run(_micro(ro, cfg), head, train=True)
         pipeline.broadcast_from_last(acc)
@@ -177,16 +200,7 @@ def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_
 def critic_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None,
                       pipeline=None) -> Dict[str, torch.Tensor]:
     denom = float(denom_tokens if denom_tokens is not None else max(1, ro.n_response_tokens()))
-    acc = torch.zeros(4, dtype=torch.float32, device=model.device)
-    ret, mask = ro.returns.view(-1), ro.mask.view(-1)
-
-    def head(mb, xf):
-        rows = K.gather_rows(xf, mb.sel)
-        v = model.scalar_values(rows)
-        dv, part = K.value_loss(v, ret[mb.flat], mask[mb.flat], 1.0 / denom)
-        acc.add_(part)
-        return _scatter_head_grad(xf, mb.sel, model.scalar_head_bwd(rows, dv))
-
+    head, acc = make_critic_head(model, ro, cfg, denom)
     if pipeline is not None:
         pipeline.run(_micro(ro, cfg), head, train=True)
         pipeline.broadcast_from_last(acc)
@@ -195,6 +209,22 @@ def critic_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_
             xf, ctx = model.forward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen, keep=True)
             model.backward(ctx, head(mb, xf))
     return {"value_loss": acc[0]}
+
+
+def fused_actor_critic_train_step(actor_stage: LlamaModel, critic_stage: LlamaModel, ro: Rollout, cfg: AlgoConfig, executor, *,
+                                  denom_tokens: Optional[float] = None) -> Dict[str, torch.Tensor]:
+    """PPO's two training vertices as ONE interleaved pipeline step (``parallel.fused_pp.FusedPipelineExecutor``):
+    the actor's stages run in device order, the critic's in reverse order on the same GPUs, and every device
+    follows the precomputed instruction stream that mixes the two models' forward and backward microtasks.
+    The actor's loss lives on the last device, the critic's on the first; metrics are relayed to all ranks."""
+    denom = float(denom_tokens if denom_tokens is not None else max(1, ro.n_response_tokens()))
+    a_head, acc, _ = make_policy_head(actor_stage, ro, cfg, denom)
+    c_head, cacc = make_critic_head(critic_stage, ro, cfg, denom)
+    mbs = _micro(ro, cfg)
+    executor.run({"actor": mbs, "critic": mbs}, {"actor": a_head, "critic": c_head})
+    executor.broadcast_from_last("actor", acc)
+    executor.broadcast_from_last("critic", cacc)
+    return {"loss": acc[0], "kl_sum": acc[1], "clipped": acc[2], "approx_kl_sum": acc[3], "value_loss": cacc[0]}
 
 
 def dpo_train_step(model: LlamaModel, ro: Rollout, ref_seq_logp: torch.Tensor, cfg: AlgoConfig, *,

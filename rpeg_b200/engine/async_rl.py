@@ -114,7 +114,8 @@ class AsyncGRPO:
             model.weight_gate = self.weights.gate(v)
         rows = self._rows_of(self.gen_ranks.index(self.rank), len(self.gen_ranks))
         rep = prompts.to(self.device, torch.int32).repeat_interleave(self.K, dim=0)[rows.start:rows.stop].contiguous()
-        res = gen.generate(rep, self.max_new, temperature=self.algo.temperature, seed=self.seed + 100003 * k + self.rank)
+        res = gen.generate(rep, self.max_new, temperature=self.algo.temperature, seed=self.seed + 100003 * k + self.rank,
+                           group_size=self.K if (rows.start % self.K == 0 and len(rows) % self.K == 0) else 1)
         idx = torch.arange(rows.start, rows.stop, dtype=torch.int64, device=self.device)
         self.rollouts.send(k, idx, res.tokens, res.logprobs, res.lengths)
         K.check_status()

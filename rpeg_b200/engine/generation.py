@@ -171,11 +171,11 @@ class Generator:
         _lib.add_launches(self._graph_launches[key])
 
     # ------------------------------------------------------------------ prefill of admitted rows
-    def _prefill(self, prompts: List[torch.Tensor], slots: List[int], forced: Optional[List[int]], temperature: float,
-                 greedy: bool, seed: int, max_new: int) -> None:
+    def _prefill(self, prompts: List[torch.Tensor], slots: List[int]) -> torch.Tensor:
+        """Run the prompts through the model, store their K/V through the page-table rows of ``slots`` and return
+        the logits at each prompt's last position ``[len(prompts), V]``."""
         cfg, dev = self.cfg, self.dev
         lens = [int(p.numel()) for p in prompts]
-        sl = torch.tensor(slots, dtype=torch.long, device=dev)
         tokens = torch.cat(prompts).to(device=dev, dtype=torch.int32)
         pos = torch.cat([torch.arange(l, dtype=torch.int32) for l in lens]).to(dev)
         seq_id = torch.cat([torch.full((l,), s, dtype=torch.int32) for l, s in zip(lens, slots)]).to(dev)
@@ -187,7 +187,14 @@ class Generator:
 
         xf, _ = self.model.forward(tokens, pos, cu, max(lens), keep=False, kv_sink=sink)
         last = (cu[1:] - 1).contiguous()
-        logits = self.model.lm_logits(K.gather_rows(xf, last))
+        return self.model.lm_logits(K.gather_rows(xf, last))
+
+    def _start_rows(self, logits: torch.Tensor, lens: List[int], slots: List[int], forced: Optional[List[int]], temperature: float,
+                    greedy: bool, seed: int, max_new: int) -> None:
+        """Sample the first token of every admitted row from its prompt's last-position logits (one row of ``logits``
+        per slot) and initialise the slot state for decoding."""
+        dev = self.dev
+        sl = torch.tensor(slots, dtype=torch.long, device=dev)
         lens_t = torch.tensor(lens, dtype=torch.int32, device=dev)
         f_len = torch.tensor(forced if forced is not None else [0] * len(slots), dtype=torch.int32, device=dev)
         first_forced = torch.where(f_len == 1, torch.full_like(f_len, self.eos_id), torch.full_like(f_len, -1))
@@ -206,13 +213,22 @@ class Generator:
     # ------------------------------------------------------------------ public entry
     @torch.no_grad()
     def generate(self, prompts, max_new: int, *, temperature: float = 1.0, greedy: bool = False, seed: int = 0,
-                 forced_lens=None) -> GenerationResult:
+                 forced_lens=None, group_size: int = 1) -> GenerationResult:
         """Generate up to ``max_new`` tokens for every prompt (a ``[N, S]`` int tensor or a list of
         1-D tensors). ``forced_lens[i] > 0`` makes row ``i`` emit EOS as its ``forced_lens[i]``-th
-        token (synthetic length control for benchmarks); natural EOS and the cap apply regardless."""
+        token (synthetic length control for benchmarks); natural EOS and the cap apply regardless.
+
+        ``group_size = K`` declares that rows ``g*K .. g*K + K - 1`` carry the SAME prompt (K samples per prompt,
+        GRPO): the prompt is prefilled once per group, its full KV pages are shared by the group's page-table
+        rows (a reference count frees them with the last row), and the first token of every row is drawn from the
+        one set of last-position logits. Rows of a group decode next to each other, so the shared pages are read
+        from HBM about once per group and step instead of once per row."""
         dev = self.dev
         rows = [p for p in prompts] if not isinstance(prompts, torch.Tensor) else [prompts[i] for i in range(prompts.shape[0])]
         N = len(rows)
+        G = max(1, int(group_size))
+        if N % G:
+            raise ValueError(f"{N} rows do not form groups of {G}")
         longest = max(int(r.numel()) for r in rows)
         if longest + max_new > self.max_seq_len:
             raise ValueError(f"prompt ({longest}) + max_new ({max_new}) exceeds max_seq_len ({self.max_seq_len})")
@@ -231,19 +247,27 @@ class Generator:
             t.zero_()
         self.pool = PagePool(self.pool.num_pages)      # a call that raised half way must not leak pages
         slot_row = [-1] * n
-        slot_pages: List[List[int]] = [[] for _ in range(n)]
+        slot_pages: List[List[int]] = [[] for _ in range(n)]   # pages a slot owns (the shared prompt pages are not in here)
+        slot_shared = [0] * n      # leading page-table entries that alias the group's shared prompt pages
         slot_bound = [0] * n       # upper bound on the tokens a slot holds (prompt + decode steps run since admission)
         slot_prompt = [0] * n
         queue = list(range(N))
         retired = 0
         counters = dict(prefill_calls=0, decode_steps=0, prefill_tokens=0, compactions=0, host_syncs=0, kv_pages_taken=0,
-                        kv_pages_returned=0, kv_preemptions=0, live_slots_peak=0, graph_replays=0)
+                        kv_pages_returned=0, kv_preemptions=0, live_slots_peak=0, graph_replays=0, shared_prompt_pages=0,
+                        prompts_prefilled=0)
         seen_finished = 0
         horizon = self.sync_interval
         watermark = max(1, self.pool.num_pages // 20)     # pages kept free at admission so live rows can grow
+        # per group of rows with one prompt: the shared full pages, the page that holds the prompt's ragged tail (rows copy
+        # it into their own first page), the last-position logits, and how many of its rows have not retired yet
+        groups: Dict[int, dict] = {}
 
         def pages_for(tokens: int) -> int:
             return min(self.pages_per_row, (tokens + PAGE - 1) // PAGE)
+
+        def shared_pages_of(plen: int) -> int:
+            return plen // PAGE if G > 1 else 0
 
         def release(slots_gone: List[int]) -> None:
             for s in slots_gone:
@@ -251,6 +275,7 @@ class Generator:
                 self.pool.give(slot_pages[s])
                 slot_pages[s] = []
                 slot_row[s] = -1
+                slot_shared[s] = 0
 
         def retire(slots_done: List[int]) -> None:
             nonlocal retired
@@ -264,11 +289,21 @@ class Generator:
             self.out_tok[s_idx] = self.pad_id
             self.out_lp[s_idx] = 0
             self.page_table[s_idx] = 0
+            for s in slots_done:
+                g = groups.get(slot_row[s] // G)
+                if g is not None:
+                    g["refs"] -= 1
+                    if g["refs"] == 0:                   # last row of the group: the shared prompt pages go back
+                        back = g["pages"] + ([g["tail"]] if g["tail"] else [])
+                        counters["kv_pages_returned"] += len(back)
+                        self.pool.give(back)
+                        del groups[slot_row[s] // G]
             release(slots_done)
             retired += len(slots_done)
 
         def preempt(victims: List[int]) -> None:
-            """Give a row's pages back and queue it again from its prompt (its partial output is dropped)."""
+            """Give a row's own pages back and queue it again from its prompt (its partial output is dropped; the
+            group's shared prompt pages stay, the row is still owed)."""
             s_idx = torch.tensor(victims, dtype=torch.long, device=dev)
             for arr in (self.active, self.seq_len, self.gen_count, self.forced_len, self.page_table, self.out_lp):
                 arr[s_idx] = 0
@@ -283,7 +318,7 @@ class Generator:
             the rows with the least progress when the pool cannot cover it. Returns the rows still live."""
             live = list(live)
             while True:
-                want = {s: pages_for(slot_bound[s] + horizon) - len(slot_pages[s]) for s in live}
+                want = {s: pages_for(slot_bound[s] + horizon) - slot_shared[s] - len(slot_pages[s]) for s in live}
                 total = sum(v for v in want.values() if v > 0)
                 if total <= self.pool.available() or len(live) <= 1:
                     break
@@ -294,7 +329,7 @@ class Generator:
             for s in live:
                 k = want[s]
                 if k > 0:
-                    have = len(slot_pages[s])
+                    have = slot_shared[s] + len(slot_pages[s])
                     new = self.pool.take(k)
                     counters["kv_pages_taken"] += k
                     slot_pages[s].extend(new)
@@ -305,35 +340,85 @@ class Generator:
                                                      torch.tensor(val, dtype=torch.int32, device=dev))
             return live
 
+        def copy_page(src: int, dst: List[int]) -> None:
+            """Copy one KV page (all layers, K and V) onto the pages ``dst``."""
+            per = self.kcache[0].numel()
+            flat = self.kcache[0].new_empty(0).set_(self.kcache[0].untyped_storage(), self.kcache[0].storage_offset(),
+                                                    (2 * self.cfg.n_layers, self.kcache[0].shape[0], per // self.kcache[0].shape[0]))
+            d = torch.tensor(dst, dtype=torch.long, device=dev)
+            flat[:, d] = flat[:, src].unsqueeze(1)
+
         while retired < N:
             free = [s for s in range(n) if slot_row[s] < 0]
             # admit in batches: a prefill call stalls decoding, so wait until several slots are free
             if queue and len(free) >= min(len(queue), max(1, n // 8)):
                 new_rows, new_slots = [], []
                 budget = self.pool.available() - (watermark if any(r >= 0 for r in slot_row) else 0)
+                opening = set()                                  # groups whose prompt this admission prefills
                 for s in free:
                     if not queue:
                         break
-                    need = pages_for(int(rows[queue[0]].numel()) + 1 + horizon)
+                    r = queue[0]
+                    plen = int(rows[r].numel())
+                    sh = shared_pages_of(plen)
+                    need = pages_for(plen + 1 + horizon) - sh
+                    g = r // G
+                    if sh and g not in groups and g not in opening:
+                        need += sh + (1 if plen % PAGE else 0)   # the group's shared pages (+ its tail page) come with its first row
                     if need > budget:
                         break
                     budget -= need
+                    if sh:
+                        opening.add(g)
                     new_rows.append(queue.pop(0))
                     new_slots.append(s)
                 if new_rows:
                     table = torch.zeros((len(new_rows), self.pages_per_row), dtype=torch.int32)
+                    prefill_rows, prefill_slots = [], []
                     for j, (r, s) in enumerate(zip(new_rows, new_slots)):
                         plen = int(rows[r].numel())
-                        need = pages_for(plen + 1 + horizon)
-                        pages = self.pool.take(need)
-                        counters["kv_pages_taken"] += need
-                        slot_pages[s], slot_row[s], slot_prompt[s], slot_bound[s] = pages, r, plen, plen + 1
-                        table[j, :need] = torch.tensor(pages, dtype=torch.int32)
+                        sh = shared_pages_of(plen)
+                        g = r // G
+                        if sh and g not in groups:
+                            shared = self.pool.take(sh)
+                            tail = self.pool.take(1)[0] if plen % PAGE else 0
+                            counters["kv_pages_taken"] += sh + (1 if tail else 0)
+                            counters["shared_prompt_pages"] += sh
+                            groups[g] = dict(pages=shared, tail=tail, refs=G, logits=None, plen=plen)
+                            prefill_rows.append(r)
+                            prefill_slots.append(s)
+                        elif not sh:
+                            prefill_rows.append(r)
+                            prefill_slots.append(s)
+                        own = self.pool.take(pages_for(plen + 1 + horizon) - sh)
+                        counters["kv_pages_taken"] += len(own)
+                        slot_pages[s], slot_row[s], slot_prompt[s], slot_bound[s], slot_shared[s] = own, r, plen, plen + 1, sh
+                        if sh:
+                            table[j, :sh] = torch.tensor(groups[g]["pages"], dtype=torch.int32)
+                        table[j, sh:sh + len(own)] = torch.tensor(own, dtype=torch.int32)
                     self.page_table[torch.tensor(new_slots, dtype=torch.long, device=dev)] = table.to(dev)
-                    self._prefill([rows[r] for r in new_rows], new_slots, None if forced is None else [forced[r] for r in new_rows],
-                                  temperature, greedy, seed, max_new)
-                    counters["prefill_calls"] += 1
-                    counters["prefill_tokens"] += sum(int(rows[r].numel()) for r in new_rows)
+                    if prefill_rows:
+                        logits = self._prefill([rows[r] for r in prefill_rows], prefill_slots)
+                        counters["prefill_calls"] += 1
+                        counters["prompts_prefilled"] += len(prefill_rows)
+                        counters["prefill_tokens"] += sum(int(rows[r].numel()) for r in prefill_rows)
+                    if G > 1:
+                        for j, (r, s) in enumerate(zip(prefill_rows, prefill_slots)):
+                            g = groups.get(r // G)
+                            if g is not None and g["logits"] is None:
+                                g["logits"] = logits[j].clone()
+                                if g["tail"]:               # keep the prompt's ragged tail for the rows that come later
+                                    copy_page(slot_pages[s][0], [g["tail"]])
+                        for r, s in zip(new_rows, new_slots):   # rows that alias an already prefilled prompt need its tail
+                            g = groups.get(r // G)
+                            if g is not None and g["tail"] and not (r in prefill_rows):
+                                copy_page(g["tail"], [slot_pages[s][0]])
+                        row_logits = torch.stack([groups[r // G]["logits"] if (r // G) in groups else logits[prefill_rows.index(r)]
+                                                  for r in new_rows])
+                    else:
+                        row_logits = logits
+                    self._start_rows(row_logits, [int(rows[r].numel()) for r in new_rows], new_slots,
+                                     None if forced is None else [forced[r] for r in new_rows], temperature, greedy, seed, max_new)
             live = [s for s in range(n) if slot_row[s] >= 0]
             if not live:
                 if queue:
@@ -341,7 +426,7 @@ class Generator:
                 break
             used = max(live) + 1
             if not queue and len(live) <= self._bucket(used) // 2 and self._bucket(len(live)) < self._bucket(used):
-                self._compact(live, slot_row, slot_pages, slot_bound, slot_prompt)
+                self._compact(live, slot_row, slot_pages, slot_bound, slot_prompt, slot_shared)
                 counters["compactions"] += 1
                 live = list(range(len(live)))
             live = grow(live)
@@ -370,7 +455,7 @@ class Generator:
         return self.max_slots
 
     def _compact(self, live: List[int], slot_row: List[int], slot_pages: List[List[int]], slot_bound: List[int],
-                 slot_prompt: List[int]) -> None:
+                 slot_prompt: List[int], slot_shared: List[int]) -> None:
         """Move live slots to the front (state and page-table rows only; KV pages stay where they are)."""
         k = len(live)
         idx = torch.tensor(live, dtype=torch.long, device=self.dev)
@@ -386,7 +471,9 @@ class Generator:
         pages = [slot_pages[s] for s in live]
         bounds = [slot_bound[s] for s in live]
         prompts = [slot_prompt[s] for s in live]
+        shared = [slot_shared[s] for s in live]
         for s in range(len(slot_row)):
+            slot_shared[s] = shared[s] if s < k else 0
             slot_row[s] = rows[s] if s < k else -1
             slot_pages[s] = pages[s] if s < k else []
             slot_bound[s] = bounds[s] if s < k else 0

@@ -123,7 +123,7 @@ class GRPOTrainer(_Base):
         rep = p_dev.repeat_interleave(self.K, dim=0).contiguous()
         self._mark("begin")
         gen = self.gen.generate(rep, self.max_new, temperature=self.algo.temperature,
-                                seed=self.seed + 100003 * self.iteration, forced_lens=forced_lens)
+                                seed=self.seed + 100003 * self.iteration, forced_lens=forced_lens, group_size=self.K)
         resp_lens = gen.lengths.tolist()
         self._mark("generate")
         ro = A.Rollout(rep, [S] * N, gen.tokens, resp_lens, gen.logprobs, gen.response_mask(),

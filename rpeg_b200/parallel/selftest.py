@@ -29,6 +29,12 @@ import torch
 import torch.distributed as dist
 
 
+def _progress(rank: int, step: str) -> None:
+    """One line per step on stderr (rank 0), so that a run that stops shows where."""
+    if rank == 0:
+        print(f"[selftest] step {step}", file=sys.stderr, flush=True)
+
+
 def main() -> int:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -48,6 +54,7 @@ def main() -> int:
     report = {"world": world}
     stream = lambda: torch.cuda.current_stream().cuda_stream
 
+    _progress(rank, "1")
     # 1 symmetric buffers
     buf = SymmetricBuffer(1 << 20, dev)
     buf.tensor(torch.float32).fill_(float(rank + 1))
@@ -61,6 +68,7 @@ def main() -> int:
     report["peer_reads_ok"] = got == [(float(p + 1), float(p + 1)) for p in range(world)]
     dist.barrier()
 
+    _progress(rank, "2")
     # 2 flag barrier with payload
     dp = DPContext(dev)
     mine = torch.tensor([10.0 + rank], device=dev)
@@ -70,6 +78,7 @@ def main() -> int:
     K.check_status()
     report["barrier_payload_ok"] = out[:world].tolist() == [10.0 + r for r in range(world)]
 
+    _progress(rank, "3")
     # 3 fused optimizer step against torch AdamW on the summed gradients
     cfg = LlamaConfig.tiny(n_layers=2)
     w = dp.alloc_weights(cfg)
@@ -104,6 +113,7 @@ def main() -> int:
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     report["weights_identical_after_adam"] = bool((lo == hi).item())
 
+    _progress(rank, "4")
     # 4 two GRPO steps, data parallel
     algo = A.AlgoConfig(kl_coef=0.04, micro_tokens=512, head_chunk=256)
     tr = GRPOTrainer(cfg, device=dev, samples_per_prompt=4, max_new=24, prompt_len=16, algo=algo, dp=DPContext(dev), gen_slots=8,
@@ -123,6 +133,7 @@ def main() -> int:
     report["grpo_losses_finite"] = all(x == x and abs(x) < 1e6 for x in losses)
     report["weights_identical_after_grpo"] = bool((lo == hi).item())
 
+    _progress(rank, "5")
     # 5 fused GEMM + reduce-scatter / all-reduce over peer memory against an fp32 all-reduce of the partial products
     from .tp import RowParallelLinear
     gq = torch.Generator().manual_seed(300 + rank)
@@ -147,6 +158,7 @@ def main() -> int:
         layer.close()
     report["fused_gemm_reduce_scatter_ok"] = all(rs_ok)
 
+    _progress(rank, "6")
     # 6 fused all-gather + GEMM (column-parallel linear): every rank contributes its rows, result against fp32
     from .tp import ColumnParallelLinear
     gx = torch.Generator().manual_seed(900)                 # the same activation on every rank; each keeps its rows
@@ -169,6 +181,7 @@ def main() -> int:
     col.close()
     report["fused_all_gather_gemm_ok"] = all(ag_ok)
 
+    _progress(rank, "7")
     # 7 weight reshard TP=world -> DP=world (every rank ends with the whole model) and back, against the host oracle
     from .reshard import Layout, ReshardExecutor, param_shapes, piece_offsets, rank_pieces, shard_state_dict
     rcfg = LlamaConfig.tiny(n_layers=2, d_model=512, d_ff=1024, n_heads=8, n_kv_heads=8, vocab=1024)
@@ -194,6 +207,7 @@ def main() -> int:
         ex.close()
     report["reshard_executor_ok"] = all(rs_ok)
 
+    _progress(rank, "8")
     # 8 tensor-parallel forward (sequence-parallel layers from the fused linears) against the single-GPU forward
     from ..models.tp_llama import TPLlamaForward
     tcfg = LlamaConfig.tiny(n_layers=2, d_model=1024, d_ff=1024, n_heads=8, n_kv_heads=8, vocab=1024)
@@ -217,6 +231,7 @@ def main() -> int:
     tp_fwd.close()
     report["tensor_parallel_forward_ok"] = all(tp_ok)
 
+    _progress(rank, "9")
     # 9 pipeline-parallel policy step (1F1B over all ranks as stages) against the same step on the whole model
     from .pp import PipelineRunner
     pcfg = LlamaConfig.tiny(n_layers=max(2, world), vocab=512)
@@ -253,6 +268,52 @@ def main() -> int:
     report["pipeline_p2p_calls"] = runner.p2p_calls
     dist.barrier()
 
+    _progress(rank, "9b")
+    # 9b fused bidirectional actor/critic pipeline: actor stages in rank order, critic stages in reverse order, one
+    #    interleaved instruction stream per rank, against the two unfused whole-model steps
+    from dataclasses import replace as _replace
+    from .fused_pp import FusedPipelineExecutor, logical_stage, uniform_schedule
+    fcfg_a = LlamaConfig.tiny(n_layers=max(2, world), vocab=512)
+    fcfg_c = _replace(fcfg_a, lm_head=False, scalar_head=True)
+    whole_a = LlamaModel(fcfg_a, dev, trainable=True, seed=41)
+    whole_c = LlamaModel(fcfg_c, dev, trainable=True, seed=42)
+    Nf = 4 * world
+    gf = torch.Generator().manual_seed(97)
+    plf = [int(x) for x in torch.randint(4, 13, (Nf,), generator=gf)]
+    rlf = [int(x) for x in torch.randint(3, 21, (Nf,), generator=gf)]
+    mask_f = torch.zeros(Nf, 20)
+    for r_, l_ in enumerate(rlf):
+        mask_f[r_, :l_] = 1.0
+    ro_f = A.Rollout(prompt_ids=torch.randint(2, 512, (Nf, 12), generator=gf, dtype=torch.int32).to(dev), prompt_lens=plf,
+                     resp_ids=torch.randint(2, 512, (Nf, 20), generator=gf, dtype=torch.int32).to(dev), resp_lens=rlf,
+                     old_logp=(-torch.rand(Nf, 20, generator=gf) * 3 * mask_f).to(dev), mask=mask_f.to(dev))
+    ro_f.adv = (torch.randn(Nf, 20, generator=gf) * mask_f).to(dev)
+    ro_f.returns = (torch.randn(Nf, 20, generator=gf) * mask_f).to(dev)
+    falgo = A.AlgoConfig(kl_coef=0.0, micro_tokens=64, head_chunk=64)
+    n_mb = len(A._micro(ro_f, falgo))
+    want_a = A.policy_train_step(whole_a, ro_f, falgo)
+    want_c = A.critic_train_step(whole_c, ro_f, falgo)
+    sched = uniform_schedule(world, {"actor": n_mb, "critic": n_mb})
+    spec = {m.name: m for m in sched.models}
+    st_a = LlamaModel(fcfg_a, dev, trainable=True, seed=1, stage=(logical_stage(spec["actor"], rank), world))
+    st_c = LlamaModel(fcfg_c, dev, trainable=True, seed=1, stage=(logical_stage(spec["critic"], rank), world))
+    for stg, whole_m in ((st_a, whole_a), (st_c, whole_c)):
+        for name in stg.layout.entries:
+            stg.p[name].copy_(whole_m.p[name])
+    fx = FusedPipelineExecutor({"actor": st_a, "critic": st_c}, sched)
+    got_f = A.fused_actor_critic_train_step(st_a, st_c, ro_f, falgo, fx)
+    torch.cuda.synchronize()
+    K.check_status()
+    f_ok = [n_mb >= world, abs(float(got_f["loss"]) - float(want_a["loss"])) < 2e-3 * max(1.0, abs(float(want_a["loss"]))),
+            abs(float(got_f["value_loss"]) - float(want_c["value_loss"])) < 2e-3 * max(1.0, abs(float(want_c["value_loss"])))]
+    for stg, whole_m in ((st_a, whole_a), (st_c, whole_c)):
+        for name in stg.layout.entries:
+            a_, b_ = stg.gp[name].float(), whole_m.gp[name].float()
+            f_ok.append(bool(((a_ - b_).norm() <= 3e-2 * b_.norm() + 1e-6).item()))
+    report["fused_actor_critic_pipeline_ok"] = all(f_ok)
+    dist.barrier()
+
+    _progress(rank, "10")
     # 10 disaggregated GRPO with staleness 1: the first half of the ranks generate, the second half train; weights and
     #    rollouts cross through versioned peer-memory channels only
     from ..engine.async_rl import AsyncGRPO

@@ -196,3 +196,44 @@ def test_generation_with_page_preemption_matches_roomy_pool(cuda_device):
     for r in (a, b):
         assert r.counters["kv_pages_taken"] == r.counters["kv_pages_returned"]
     assert tight.pool.available() == tight.pool.num_pages - 1
+
+
+@pytest.mark.parametrize("S", [128, 150])
+def test_generation_with_shared_prompt_pages(cuda_device, S):
+    """K samples per prompt with the prompt's KV pages shared by the group: one prefill per prompt, fewer pages, and
+    every sampled row consistent with a packed forward over its own tokens. Prompt lengths: a whole number of pages
+    and a ragged tail (the tail page is copied per row). A tight pool forces preemptions and late admissions that
+    alias prompts prefilled earlier; every page must come back."""
+    cfg = LlamaConfig.tiny(n_layers=2)
+    model = LlamaModel(cfg, cuda_device, seed=9)
+    P, Kq, T = 5, 4, 90
+    uniq = torch.randint(2, cfg.vocab, (P, S), device=cuda_device, dtype=torch.int32)
+    prompts = uniq.repeat_interleave(Kq, dim=0).contiguous()
+    N = P * Kq
+    forced = [(17 * i) % T + 1 for i in range(N)]
+    page_bytes = 2 * cfg.n_layers * cfg.n_kv_heads * K.KV_PAGE * cfg.head_dim * 2
+    plain = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=1e9, eos_id=1, sync_interval=4)
+    shared = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=1e9, eos_id=1, sync_interval=4)
+    tight = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=14.5 * page_bytes, eos_id=1, sync_interval=4)
+    a = plain.generate(prompts, T, seed=11, forced_lens=forced)
+    b = shared.generate(prompts, T, seed=11, forced_lens=forced, group_size=Kq)
+    c = tight.generate(prompts, T, seed=11, forced_lens=forced, group_size=Kq)
+    K.check_status()
+    assert a.counters["prompts_prefilled"] == N and b.counters["prompts_prefilled"] == P and c.counters["prompts_prefilled"] == P
+    assert b.counters["shared_prompt_pages"] == P * (S // K.KV_PAGE)
+    assert b.counters["kv_pages_taken"] < a.counters["kv_pages_taken"]
+    assert c.counters["kv_preemptions"] > 0
+    for res, g in ((a, plain), (b, shared), (c, tight)):
+        assert res.counters["kv_pages_taken"] == res.counters["kv_pages_returned"]
+        assert g.pool.available() == g.pool.num_pages - 1
+        lens = res.lengths.tolist()
+        assert all(1 <= l <= f for l, f in zip(lens, forced))
+        ro = A.Rollout(prompts, [S] * N, res.tokens, lens, res.logprobs, res.response_mask())
+        lp = A.sequence_logprobs(model, ro, A.AlgoConfig(micro_tokens=1024, head_chunk=64))
+        mask = res.response_mask().bool()
+        assert torch.allclose(lp[mask], res.logprobs[mask], atol=6e-2)
+    # greedy decoding: sharing must not change what a row generates (up to near-tie flips from the batch composition)
+    ga = plain.generate(prompts, 24, greedy=True)
+    gb = shared.generate(prompts, 24, greedy=True, group_size=Kq)
+    same = sum(int(torch.equal(ga.tokens[i], gb.tokens[i])) for i in range(N))
+    assert same >= N - 2, f"only {same} of {N} rows identical"

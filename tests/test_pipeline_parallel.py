@@ -64,3 +64,26 @@ def test_stage_param_tables_partition_the_full_table():
         names += list(lay.entries)
     assert sorted(names) == sorted(full.entries)
     assert ParamLayout(cfg, (0, 2)).total + ParamLayout(cfg, (1, 2)).total == full.total
+
+
+@pytest.mark.parametrize("p,m", [(2, 4), (4, 8), (8, 8)])
+def test_fused_pipeline_streams_are_in_order_per_model_and_phase(p, m):
+    """What the fused actor/critic executor relies on: for every (model, phase) the messages between two
+    neighbouring devices are sent and received in the same order, the actor and the reversed critic meet every
+    device exactly once per stage, and every device's instruction stream holds all of its tasks."""
+    from rpeg_b200.parallel.fused_pp import logical_stage, uniform_schedule
+    sched = uniform_schedule(p, {"actor": m, "critic": m})
+    spec = {mm.name: mm for mm in sched.models}
+    tasks = {t.task_id: t for t in sched.tasks}
+    assert [logical_stage(spec["actor"], d) for d in range(p)] == list(range(p))
+    assert [logical_stage(spec["critic"], d) for d in range(p)] == list(reversed(range(p)))
+    assert all(len(o) == 4 * m for o in sched.device_order)
+    for name, mm in spec.items():
+        for phase in ("F", "B"):
+            for s in range(p - 1):
+                src_stage, dst_stage = (s, s + 1) if phase == "F" else (s + 1, s)
+                sent = [tasks[t].microbatch for t in sched.device_order[mm.device_stage(src_stage)]
+                        if tasks[t].model == name and tasks[t].phase == phase and tasks[t].stage == src_stage]
+                got = [tasks[t].microbatch for t in sched.device_order[mm.device_stage(dst_stage)]
+                       if tasks[t].model == name and tasks[t].phase == phase and tasks[t].stage == dst_stage]
+                assert sent == got == list(range(m))
