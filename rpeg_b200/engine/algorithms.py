@@ -49,6 +49,14 @@ class Rollout:
     def n_response_tokens(self) -> int:
         return int(sum(self.resp_lens))
 
+    def subset(self, rows: Sequence[int]) -> "Rollout":
+        """The rollout restricted to ``rows`` (a minibatch of an update epoch); tensors are gathered copies."""
+        idx = torch.tensor(list(rows), dtype=torch.long, device=self.resp_ids.device)
+        pick = lambda t: None if t is None else t[idx].contiguous()
+        return Rollout(pick(self.prompt_ids), [self.prompt_lens[i] for i in rows], pick(self.resp_ids), [self.resp_lens[i] for i in rows],
+                       pick(self.old_logp), pick(self.mask), pick(self.ref_logp), pick(self.values), pick(self.scores), pick(self.adv),
+                       pick(self.returns), self.weight_version)
+
 
 @dataclass
 class AlgoConfig:

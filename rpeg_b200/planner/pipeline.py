@@ -406,13 +406,21 @@ def run_pipeline(cfg: dict, *, time_budget_s: Optional[float] = None, seed_plan:
     do_plots = out.get("plots", False) if make_plots is None else make_plots
     if do_plots:
         try:
-            from ..utils.visualize import exec_to_dot, trace_to_gantt_svg
+            from ..utils.visualize import exec_to_dot, rpeg_to_dot, trace_to_gantt_svg, unrolled_to_dot
             import os
             d = out.get("plots_dir", "figures")
             os.makedirs(d, exist_ok=True)
             trace_to_gantt_svg(rows[-1]["trace"], os.path.join(d, "optimized.gantt.svg"), space)
             if rows[1]:
                 trace_to_gantt_svg(rows[1]["trace"], os.path.join(d, "baseline.gantt.svg"), space)
+            # the three graphs of the compilation: algorithm template, unrolled iterations, lowered executable
+            rpeg_to_dot(best.rpeg, os.path.join(d, "rpeg.dot"))
+            from ..passes.lower import lower
+            from ..passes.unroll import unroll
+            un = unroll(best.rpeg, K_eval)
+            unrolled_to_dot(un, os.path.join(d, "unrolled.dot"))
+            exec_to_dot(lower(best.rpeg, un, best.plan, suite, K_eval, workload=workload,
+                              intra_stage_fusion=best.intra_stage_fusion), os.path.join(d, "executable.dot"))
         except Exception as exc:  # plotting never fails a search
             print(f"  (plots skipped: {exc})")
     return {"rows": rows, "best": best, "report": report[0], "wall_s": wall, "cache": st}

@@ -198,7 +198,7 @@ class EngineOperationHandler:
         elif vid in ("t_pi", "t_ac"):
             c.update(self._train_policy(st, step))
         elif vid == "t_V":
-            c.update(self._train_critic(st))
+            c.update(self._train_critic(st, step))
         else:
             raise RuntimeExecutionError(f"engine backend has no operator for vertex {vid}")
         return c
@@ -237,28 +237,50 @@ class EngineOperationHandler:
                     st["targets"] = True
                 opt = tr.opt_actor
             st["denom"] = self._global(ro.n_response_tokens())
-            tr.actor.zero_grad()
-            m = A.policy_train_step(tr.actor, ro, self.algo, denom_tokens=st["denom"],
-                                    **({"value_model_shared": True} if self.shared else {}))
-            opt.step()
+            steps = 0
+            for part in self._minibatches(ro, step):       # epochs x minibatches, one optimizer step each
+                denom = st["denom"] if part is ro else self._global(part.n_response_tokens())
+                tr.actor.zero_grad()
+                m = A.policy_train_step(tr.actor, part, self.algo, denom_tokens=denom,
+                                        **({"value_model_shared": True} if self.shared else {}))
+                opt.step()
+                steps += 1
             m["grad_norm"] = opt.grad_norm()
+            out = {k: float(v) for k, v in tr._read(m).items()}
+            out.update(train_tokens=int(sum(ro.total_lens())) * self.run.algorithm.epochs, optimizer_steps=steps)
+            return out
         out = {k: float(v) for k, v in tr._read(m).items()}
         out.update(train_tokens=int(sum(ro.total_lens())), optimizer_steps=1)
         return out
 
-    def _train_critic(self, st) -> Dict[str, Any]:
+    def _minibatches(self, ro, step: int):
+        """The rollout parts of the update epochs (``algorithm.epochs``, ``algorithm.minibatch_size`` sequences of
+        the GLOBAL batch per optimizer step; every rank cuts its own rows the same way). One epoch without a
+        minibatch size is the rollout itself."""
+        a = self.run.algorithm
+        if a.epochs == 1 and not a.minibatch_size:
+            return [ro]
+        from .data import minibatch_indices
+        local = None if not a.minibatch_size else max(1, int(a.minibatch_size) // self.world)
+        return [ro.subset(rows) for rows in minibatch_indices(ro.n, local, a.epochs, seed=a.seed + step)]
+
+    def _train_critic(self, st, step: int = 0) -> Dict[str, Any]:
         tr, A = self.trainer, self.A
         ro = st["rollout"]
         if "targets" not in st:
             A.ppo_targets(ro, self.algo)
             st["targets"] = True
-        denom = st.get("denom") or self._global(ro.n_response_tokens())
-        tr.critic.zero_grad()
-        m = A.critic_train_step(tr.critic, ro, self.algo, denom_tokens=denom)
-        tr.opt_critic.step()
+        denom_all = st.get("denom") or self._global(ro.n_response_tokens())
+        steps = 0
+        for part in self._minibatches(ro, step):
+            denom = denom_all if part is ro else self._global(part.n_response_tokens())
+            tr.critic.zero_grad()
+            m = A.critic_train_step(tr.critic, part, self.algo, denom_tokens=denom)
+            tr.opt_critic.step()
+            steps += 1
         m["critic_grad_norm"] = tr.opt_critic.grad_norm()
         out = {k: float(v) for k, v in tr._read(m).items()}
-        out.update(train_tokens=int(sum(ro.total_lens())), optimizer_steps=1)
+        out.update(train_tokens=int(sum(ro.total_lens())) * self.run.algorithm.epochs, optimizer_steps=steps)
         return out
 
     # ------------------------------------------------------------------ executor interface

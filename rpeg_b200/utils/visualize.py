@@ -118,10 +118,36 @@ def rpeg_to_dot(rpeg, path: Optional[str] = None) -> str:
     for v in rpeg.vertices:
         colour = MODEL_COLOURS.get(v.kind.model.value, "#cccccc")
         lines.append(f'  "{v.id}" [label="{v.id}\\n{v.kind.role.value}", fillcolor="{colour}", fontcolor=white];')
-    for e in rpeg.edges:
-        style = "dashed" if e.kind.value != "Act" else "solid"
-        label = getattr(e, "label", None) or ",".join(sorted(c.name for c in getattr(e, "containers", ()) or ()))
-        lines.append(f'  "{e.src.id}" -> "{e.dst.id}" [label="{label}", style={style}];')
+    for pub, edges in ((False, rpeg.data_edges), (True, rpeg.pub_edges)):
+        for e in edges:
+            label = getattr(e.container, "name", str(e.container))
+            lines.append(f'  "{e.src.id}" -> "{e.dst.id}" [label="{label}", style={"dashed" if pub else "solid"}];')
+    lines.append("}")
+    text = "\n".join(lines)
+    if path:
+        with open(path, "w") as fh:
+            fh.write(text)
+    return text
+
+
+def unrolled_to_dot(unrolled, path: Optional[str] = None) -> str:
+    """The template unrolled over iterations: one cluster per iteration, publication edges (weights of an earlier
+    iteration's training node) dashed and labelled with the iteration they come from."""
+    lines = ["digraph unrolled {", "  rankdir=LR; node [shape=box, style=filled, fontname=monospace, fontsize=9];"]
+    by_k: Dict[int, list] = {}
+    for n in unrolled.nodes:
+        by_k.setdefault(n.k, []).append(n)
+    for k in sorted(by_k):
+        lines.append(f'  subgraph cluster_{k} {{ label="iteration {k}"; color="#bbbbbb";')
+        for n in by_k[k]:
+            colour = MODEL_COLOURS.get(n.template_vertex.kind.model.value, "#cccccc")
+            lines.append(f'    "{n.id}" [fillcolor="{colour}", fontcolor=white];')
+        lines.append("  }")
+    for pub, edges in ((False, unrolled.data_edges), (True, unrolled.pub_edges)):
+        for e in edges:
+            name = getattr(e.container, "name", str(e.container))
+            label = f"{name}@{e.src.k}" if pub else name
+            lines.append(f'  "{e.src.id}" -> "{e.dst.id}" [label="{label}", style={"dashed" if pub else "solid"}];')
     lines.append("}")
     text = "\n".join(lines)
     if path:

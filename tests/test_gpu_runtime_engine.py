@@ -59,3 +59,15 @@ def test_engine_checkpoint_replay_restores_weights_and_optimizer(tmp_path, cuda_
     assert w2.shape == w3.shape and not torch.equal(w2, w3)
     meta = json.loads((tmp_path / "checkpoints/final/actor/meta.json").read_text())
     assert meta["ranks"][0]["extra"] == {"optimizer_step": 3, "version": 3}
+
+
+def test_engine_runs_update_epochs_over_minibatches(tmp_path, cuda_device):
+    """``algorithm.epochs`` x ``algorithm.minibatch_size``: the policy and the critic take one optimizer step per
+    minibatch of every epoch (8 rows, minibatches of 4, 2 epochs -> 4 steps per training node)."""
+    run = tiny_job(tmp_path, "ppo", steps=1, algorithm={"epochs": 2, "minibatch_size": 4, "seed": 5})
+    res = execute_compiled(compile_runtime_plan(run), "engine")
+    assert res["error"] is None and res["verification"]["ok"], (res["error"], res["verification"]["errors"])
+    events = read_trace(tmp_path / "traces/run.jsonl")
+    for prefix in ("t_pi@", "t_V@"):
+        fin = [e for e in events if e["event"] == "finish" and e["node_id"].startswith(prefix)]
+        assert len(fin) == 1 and fin[0]["counters"]["optimizer_steps"] == 4

@@ -179,3 +179,46 @@ def test_experiment_generators_and_optimizer_bench(tmp_path):
     assert a1 == base                                     # nothing but the ablated knob differs
     row = ob.bench_instance("micro2", seeds=2, evals=200)
     assert row["space_size"] == 625 and row["worst_gap"] <= 0.03 and 0 < row["coverage"] <= 1
+
+
+def test_dataset_and_minibatch_indices():
+    from rpeg_b200.runtime.data import dataset_batch_indices, minibatch_indices
+    assert dataset_batch_indices(10, 4, 1) == [0, 1, 2, 3]
+    assert dataset_batch_indices(10, 4, 3) == [8, 9, 0, 1]                      # windows wrap around
+    a = dataset_batch_indices(10, 4, 2, seed=5, shuffle=True)
+    assert a == dataset_batch_indices(10, 4, 2, seed=5, shuffle=True) and len(set(a)) == 4
+    seen = sorted(i for s in (1, 2, 3) for i in dataset_batch_indices(12, 4, s, seed=1, shuffle=True))
+    assert seen == list(range(12))                                              # one pass visits every row once
+    mbs = minibatch_indices(10, 4, epochs=2, seed=3)
+    assert [len(m) for m in mbs] == [4, 4, 2, 4, 4, 2]
+    assert sorted(i for m in mbs[:3] for i in m) == list(range(10)) == sorted(i for m in mbs[3:] for i in m)
+    assert mbs[:3] != mbs[3:]                                                   # a fresh order every epoch
+    assert minibatch_indices(6, None, epochs=2) == [list(range(6))] * 2
+    assert [len(m) for m in minibatch_indices(10, 4, drop_last=True)] == [4, 4]
+    with pytest.raises(ValueError):
+        minibatch_indices(0, 4)
+
+
+def test_dot_writers_cover_template_unrolled_and_lowered_graphs(tmp_path):
+    from rpeg_b200.analytic.models import ModelSpec, ModelSuite
+    from rpeg_b200.analytic.workload import Workload
+    from rpeg_b200.core.types import Allocation, Model
+    from rpeg_b200.ir.plan import ExecutionPlan
+    from rpeg_b200.ir.templates import build_PPO_RPEG
+    from rpeg_b200.passes.lower import lower
+    from rpeg_b200.passes.unroll import unroll
+    from rpeg_b200.utils.visualize import exec_to_dot, rpeg_to_dot, unrolled_to_dot
+    spec = ModelSpec(8, 1024, 2816, 32000)
+    suite = ModelSuite({m: spec for m in Model})
+    wl = Workload(16, 1, 64, 128, ((0.5, 32), (1.0, 128)))
+    r = build_PPO_RPEG(suite, wl, tau={Model.ACTOR: 1, Model.CRITIC: 0})
+    un = unroll(r, 3)
+    plan = ExecutionPlan()
+    for i, v in enumerate(r.vertices):
+        plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = Allocation((0, 0, i % 4), (1, 1, 1)), (1, 1, 1), 1
+    low = lower(r, un, plan, suite, 3, workload=wl)
+    t1, t2, t3 = rpeg_to_dot(r, str(tmp_path / "a.dot")), unrolled_to_dot(un, str(tmp_path / "b.dot")), exec_to_dot(low, str(tmp_path / "c.dot"))
+    assert t1.startswith("digraph") and all(v.id in t1 for v in r.vertices)
+    assert t2.count("subgraph cluster_") == 3 and '"t_pi@0" -> "g_pi@2"' in t2 and "style=dashed" in t2   # staleness 1: weights of step 0 serve step 2
+    assert all(n.id in t3 for n in low.nodes)
+    assert (tmp_path / "b.dot").read_text() == t2
