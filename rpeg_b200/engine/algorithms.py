@@ -219,6 +219,34 @@ def critic_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_
     return {"value_loss": acc[0]}
 
 
+def policy_train_step_tp(tp_model, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None) -> Dict[str, torch.Tensor]:
+    """The clipped policy objective on a tensor-parallel model (``models.tp_llama.TPLlamaTrain``): every rank of
+    the tensor-parallel group calls this with the SAME rollout; linear layers run through the fused all-gather /
+    reduce-scatter GEMMs in both directions and the vocabulary-parallel head closes the loss on all ranks at once."""
+    denom = float(denom_tokens if denom_tokens is not None else max(1, ro.n_response_tokens()))
+    dev = ro.resp_ids.device
+    acc = torch.zeros(4, dtype=torch.float32, device=dev)
+    old, adv, mask = ro.old_logp.view(-1), ro.adv.view(-1), ro.mask.view(-1)
+    ref = ro.ref_logp.view(-1) if (ro.ref_logp is not None and cfg.kl_coef != 0.0) else None
+    for mb in _micro(ro, cfg):
+        T = int(mb.tokens.numel())
+        sel = mb.sel.long()
+        targets = torch.full((T,), -1, dtype=torch.int32, device=dev)
+        targets[sel] = mb.targets.to(torch.int32)
+        o_mb, a_mb, m_mb = old[mb.flat].contiguous(), adv[mb.flat].contiguous(), mask[mb.flat].contiguous()
+        r_mb = ref[mb.flat].contiguous() if ref is not None else None
+
+        def coef_fn(logp_full):
+            coef_sel, part = K.policy_loss(logp_full[sel].contiguous(), o_mb, r_mb, a_mb, m_mb, cfg.clip_eps, cfg.kl_coef, 1.0 / denom)
+            acc.add_(part)
+            out = torch.zeros(T, dtype=torch.float32, device=dev)
+            out[sel] = coef_sel
+            return out
+
+        tp_model.forward_backward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen, targets, coef_fn, cfg.temperature)
+    return {"loss": acc[0], "kl_sum": acc[1], "clipped": acc[2], "approx_kl_sum": acc[3]}
+
+
 def fused_actor_critic_train_step(actor_stage: LlamaModel, critic_stage: LlamaModel, ro: Rollout, cfg: AlgoConfig, executor, *,
                                   denom_tokens: Optional[float] = None) -> Dict[str, torch.Tensor]:
     """PPO's two training vertices as ONE interleaved pipeline step (``parallel.fused_pp.FusedPipelineExecutor``):

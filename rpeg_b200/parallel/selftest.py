@@ -231,6 +231,56 @@ def main() -> int:
     tp_fwd.close()
     report["tensor_parallel_forward_ok"] = all(tp_ok)
 
+    _progress(rank, "8b")
+    # 8b tensor-parallel TRAINING step (fused linears in both directions, vocabulary-parallel loss, sharded AdamW)
+    #    against the same step on the whole model
+    from ..models.tp_llama import TPAdamW, TPLlamaTrain
+    from ..engine.optimizer import AdamW
+    from .reshard import param_shapes as _shapes, tp_pieces as _pieces
+    wcfg = LlamaConfig.tiny(n_layers=2, d_model=1024, d_ff=1024, n_heads=8, n_kv_heads=8, vocab=1024)
+    whole_t = LlamaModel(wcfg, dev, trainable=True, seed=51)
+    gq_ = torch.Generator().manual_seed(61)
+    Nt, St, Tt = 6, 40, 60
+    plt_ = [int(x) for x in torch.randint(8, St + 1, (Nt,), generator=gq_)]
+    rlt_ = [int(x) for x in torch.randint(5, Tt + 1, (Nt,), generator=gq_)]
+    mask_t = torch.zeros(Nt, Tt)
+    for r_, l_ in enumerate(rlt_):
+        mask_t[r_, :l_] = 1.0
+    ro_t = A.Rollout(prompt_ids=torch.randint(2, wcfg.vocab, (Nt, St), generator=gq_, dtype=torch.int32).to(dev), prompt_lens=plt_,
+                     resp_ids=torch.randint(2, wcfg.vocab, (Nt, Tt), generator=gq_, dtype=torch.int32).to(dev), resp_lens=rlt_,
+                     old_logp=(-torch.rand(Nt, Tt, generator=gq_) * 3 * mask_t).to(dev), mask=mask_t.to(dev))
+    ro_t.ref_logp = (ro_t.old_logp * 1.05).contiguous()
+    ro_t.adv = (torch.randn(Nt, Tt, generator=gq_) * mask_t).to(dev)
+    talgo = A.AlgoConfig(kl_coef=0.05, micro_tokens=320, head_chunk=256)
+    tpm = TPLlamaTrain(whole_t, max_tokens=512)
+    want_t = A.policy_train_step(whole_t, ro_t, talgo)
+    got_t = A.policy_train_step_tp(tpm, ro_t, talgo)
+    tpm.sync_replicated_grads()
+    torch.cuda.synchronize()
+    K.check_status()
+    shapes_t = _shapes(wcfg)
+    tpt_ok = [abs(float(got_t["loss"]) - float(want_t["loss"])) < 3e-3 * max(1.0, abs(float(want_t["loss"])))]
+
+    def _piece_of(t_full, name):
+        ps = [t_full[r0:r1, c0:c1] for r0, r1, c0, c1 in _pieces(wcfg, name, shapes_t[name], world, rank)]
+        return torch.cat(ps, 0) if len(ps) > 1 else ps[0]
+
+    for name in tpm.entries:
+        ref_g = whole_t.gp[name].float() if name in tpm.entries and tpm.entries[name][0] < tpm.n_replicated else _piece_of(whole_t.gp[name].float(), name)
+        got_g = tpm.gp[name].float()
+        tpt_ok.append(bool(((got_g - ref_g).norm() <= 4e-2 * ref_g.norm() + 1e-6).item()))
+    opt_w, opt_tp = AdamW(whole_t, lr=1e-3), TPAdamW(tpm, lr=1e-3)
+    opt_w.step()
+    opt_tp.step(sync_replicated=False)                          # summed above for the comparison
+    torch.cuda.synchronize()
+    tpt_ok.append(abs(float(opt_w.grad_norm()) - float(opt_tp.grad_norm())) < 4e-2 * float(opt_w.grad_norm()) + 1e-6)
+    for name in ("l1.w_down", "l0.wqkv", "lm_head", "final_norm"):
+        ref_w = whole_t.p[name].float() if tpm.entries[name][0] < tpm.n_replicated else _piece_of(whole_t.p[name].float(), name)
+        tpt_ok.append(bool(((tpm.p[name].float() - ref_w).abs().max() < 4e-3).item()))
+    report["tensor_parallel_training_ok"] = all(tpt_ok)
+    dist.barrier()
+    tpm.close()
+
     _progress(rank, "9")
     # 9 pipeline-parallel policy step (1F1B over all ranks as stages) against the same step on the whole model
     from .pp import PipelineRunner

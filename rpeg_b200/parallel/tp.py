@@ -170,6 +170,11 @@ class ColumnParallelLinear:
               "rpeg_ag_gemm")
         return y
 
+    def gathered(self, M: int) -> torch.Tensor:
+        """All ranks' rows ``[M, K]`` as the last ``forward(M)`` left them in this rank's operand buffer (a view that
+        stays valid until the next-but-one ``forward``): weight-gradient GEMMs read the gathered operand from here."""
+        return self.x[self.epoch % 2].tensor(torch.bfloat16, M * self.K).view(M, self.K)
+
     def forward_unfused(self, x_shard: torch.Tensor) -> torch.Tensor:
         """NCCL all-gather followed by a plain GEMM (the baseline)."""
         if self.world == 1:

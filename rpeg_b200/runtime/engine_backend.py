@@ -170,7 +170,8 @@ class EngineOperationHandler:
         if vid in ("g_pi", "g_ac"):
             if "rollout" not in st:
                 c.update(self._generate(st, step))
-            c["emitted_rows"] = self._emitted(st, node)
+            c["emitted_rows"] = self._emitted(st, node)        # this rank's rows; the batch is cut evenly over the ranks
+            c["data_parallel_ranks"] = self.world
         elif vid == "i_ref":
             if self.algo_name == "dpo":
                 self._dpo_inputs(st, step)
