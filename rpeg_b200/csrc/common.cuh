@@ -6,6 +6,7 @@
 //    code in a global status word and returns false; callers unwind, free their TMEM and return.
 //  * status word layout: int32[4] = {code, where, blockIdx.x, extra}; 0 means "no error".
 #pragma once
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -96,6 +97,34 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 // griddep_launch() lets a dependent that was launched that way be scheduled from here on (no effect otherwise).
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Host side: RPEG_PDL=0 turns programmatic dependent launches off (plain stream order).
+inline int pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RPEG_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v;
+}
+
+// Launch `kernel` as a programmatic dependent of the previous kernel in `stream`: its blocks may become resident
+// while that kernel drains, and its first statements must be griddep_launch(); griddep_wait();. The kernels of a
+// decode step are chained this way, so the launch latency of each is hidden behind its predecessor.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {

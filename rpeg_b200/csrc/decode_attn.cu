@@ -97,6 +97,8 @@ rope_kv_append_partials_kernel(const float* __restrict__ parts, int splits, long
                                const int* __restrict__ pos, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                const int* __restrict__ page_table, int max_pages, __nv_bfloat16* __restrict__ kcache,
                                __nv_bfloat16* __restrict__ vcache, int T, int H, int Hkv) {
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   const int jobs = H + 2 * Hkv;
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (wid >= static_cast<long long>(T) * jobs) return;
@@ -196,7 +198,8 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
                          const int* __restrict__ page_table, int max_pages, const int* __restrict__ seq_lens,
                          __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int H, int Hkv,
                          int nsplit, float scale_log2) {
-  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   __shared__ float red_m[4], red_l[4];
   __shared__ __align__(16) float red_o[4][HD];
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
@@ -303,7 +306,8 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
 
 __global__ void __launch_bounds__(HD)
 decode_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int H, int nsplit) {
-  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   const int h = blockIdx.x, b = blockIdx.y;
   const float* pp = partial + (static_cast<size_t>(b) * H + h) * nsplit * (HD + 2);
   float gm = -INFINITY;
@@ -358,7 +362,7 @@ extern "C" int rpeg_rope_kv_append_partials(const float* parts, int splits, long
   if ((ld | q_col0 | k_col0 | v_col0) & 7) return -3;
   const long long threads = static_cast<long long>(T) * (H + 2 * Hkv) * 32;
   if (threads <= 0) return 0;
-  rope_kv_append_partials_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, STREAM(stream)>>>(
+  launch_pdl(rope_kv_append_partials_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0, STREAM(stream), 
       parts, splits, stride, static_cast<__nv_bfloat16*>(qkv), ld, q_col0, k_col0, v_col0, seq_id, pos, cos_t, sin_t, page_table,
       max_pages, static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache), T, H, Hkv);
   return LAUNCH_OK();
@@ -377,12 +381,12 @@ extern "C" int rpeg_paged_decode_attn(const void* q, int ldq, int q_col0, const 
   if (nsplit > 1 && scratch == nullptr) return -4;
   if (B <= 0) return 0;
   const float scale_log2 = scale * 1.4426950408889634f;
-  paged_decode_attn_kernel<<<dim3(H, B, nsplit), 128, 0, STREAM(stream)>>>(
+  launch_pdl(paged_decode_attn_kernel, dim3(dim3(H, B, nsplit)), dim3(128), 0, STREAM(stream), 
       static_cast<const __nv_bfloat16*>(q), ldq, q_col0, static_cast<const __nv_bfloat16*>(kcache),
       static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages, seq_lens,
       static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2);
   if (nsplit > 1)
-    decode_combine_kernel<<<dim3(H, B), HD, 0, STREAM(stream)>>>(scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
+    launch_pdl(decode_combine_kernel, dim3(dim3(H, B)), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
   return LAUNCH_OK();
 }
 
@@ -429,11 +433,11 @@ extern "C" int rpeg_paged_decode_attn_static(const void* q, int ldq, int q_col0,
   }
   float* scratch = g_static_scratch_ptr[dev];
   const float scale_log2 = scale * 1.4426950408889634f;
-  paged_decode_attn_kernel<<<dim3(H, B, nsplit), 128, 0, STREAM(stream)>>>(
+  launch_pdl(paged_decode_attn_kernel, dim3(dim3(H, B, nsplit)), dim3(128), 0, STREAM(stream), 
       static_cast<const __nv_bfloat16*>(q), ldq, q_col0, static_cast<const __nv_bfloat16*>(kcache),
       static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages, seq_lens, static_cast<__nv_bfloat16*>(out),
       scratch, H, Hkv, nsplit, scale_log2);
   if (nsplit > 1)
-    decode_combine_kernel<<<dim3(H, B), HD, 0, STREAM(stream)>>>(scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
+    launch_pdl(decode_combine_kernel, dim3(dim3(H, B)), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
   return cudaGetLastError() == cudaSuccess ? 0 : RPEG_STATIC_ERR_LAUNCH;
 }

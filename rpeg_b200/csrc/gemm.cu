@@ -107,7 +107,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   // Launched as a programmatic dependent (decode: B is a weight matrix that no kernel of the step writes): the
   // set-up above already ran under the previous kernel's tail, and the producer streams the first weight tiles
   // before it waits for that kernel; every other thread waits here, before it can touch A, C or the workspace.
-  if (pdl && threadIdx.x != 0) griddep_wait();
+  if (pdl) {
+    griddep_launch();
+    if (threadIdx.x != 0) griddep_wait();
+  }
 
   // Tile order: groups of 8 M-tiles sweep N together so the A rows stay in L2.
   constexpr int GROUP_M = 8;
@@ -383,15 +386,6 @@ static int dispatch_major(int transA, int transB, const CUtensorMap& ta, const C
 
 static int g_num_sms = 0;
 
-// Programmatic dependent launch of the decode GEMMs (RPEG_PDL=0 turns it off).
-static int pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("RPEG_PDL");
-    v = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  return v;
-}
 
 }  // namespace rpeg
 

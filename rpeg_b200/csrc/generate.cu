@@ -19,6 +19,8 @@ namespace rpeg {
 __global__ void decode_prepare_kernel(const int* __restrict__ active, const int* __restrict__ gen_count,
                                       const int* __restrict__ forced_len, int* __restrict__ forced, int n_slots,
                                       int eos) {
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= n_slots) return;
   int f = -1;
@@ -33,6 +35,8 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, const flo
                                       int* __restrict__ out_tok, float* __restrict__ out_lp, int n_slots,
                                       int max_new, int eos, int* __restrict__ n_finished,
                                       unsigned long long* __restrict__ step_counter) {
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s == 0 && step_counter != nullptr) step_counter[0] += 1;
   if (s >= n_slots || !active[s]) return;
@@ -87,6 +91,8 @@ __global__ void scatter_add_rows_kernel(__nv_bfloat16* __restrict__ x, const int
 // Split-K partial sums -> bf16: out[m, n] = sum_s part[s, m, n]
 __global__ void splitk_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int M, int N,
                                      int ldc, int splits) {
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   const int nv = N >> 2;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(M) * nv) return;
@@ -111,7 +117,7 @@ using namespace rpeg;
 extern "C" int rpeg_decode_prepare(const int* active, const int* gen_count, const int* forced_len, int* forced,
                                    int n_slots, int eos, void* stream) {
   if (n_slots <= 0) return 0;
-  decode_prepare_kernel<<<(n_slots + 127) / 128, 128, 0, STREAM(stream)>>>(active, gen_count, forced_len, forced,
+  launch_pdl(decode_prepare_kernel, dim3((n_slots + 127) / 128), dim3(128), 0, STREAM(stream), active, gen_count, forced_len, forced,
                                                                          n_slots, eos);
   return LAUNCH_OK();
 }
@@ -121,7 +127,7 @@ extern "C" int rpeg_decode_advance(const int* sampled, const float* sampled_lp, 
                                    int max_new, int eos, int* n_finished, unsigned long long* step_counter,
                                    void* stream) {
   if (n_slots <= 0) return 0;
-  decode_advance_kernel<<<(n_slots + 127) / 128, 128, 0, STREAM(stream)>>>(
+  launch_pdl(decode_advance_kernel, dim3((n_slots + 127) / 128), dim3(128), 0, STREAM(stream), 
       sampled, sampled_lp, token, pos, seq_len, active, gen_count, out_tok, out_lp, n_slots, max_new, eos, n_finished,
       step_counter);
   return LAUNCH_OK();
@@ -150,7 +156,7 @@ extern "C" int rpeg_splitk_reduce(const float* part, void* out, int M, int N, in
   if ((N & 3) || (ldc & 3)) return -2;
   const long long total = static_cast<long long>(M) * (N >> 2);
   if (total <= 0) return 0;
-  splitk_reduce_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, STREAM(stream)>>>(
+  launch_pdl(splitk_reduce_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, STREAM(stream), 
       part, static_cast<__nv_bfloat16*>(out), M, N, ldc, splits);
   return LAUNCH_OK();
 }

@@ -310,6 +310,8 @@ __global__ void __launch_bounds__(LP_THREADS)
 sample_kernel(const __nv_bfloat16* __restrict__ logits, int V, int ld, float inv_temp, int greedy,
               unsigned long long seed, const unsigned long long* __restrict__ seed_offset,
               const int* __restrict__ forced, int* __restrict__ token_out, float* __restrict__ logp_out) {
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   __shared__ float sm_m[32], sm_s[32], sm_best[32];
   __shared__ int sm_idx[32];
   const int row = blockIdx.x;
@@ -545,7 +547,7 @@ extern "C" int rpeg_sample(const void* logits, int B, int V, int ld, float tempe
                            unsigned long long seed, const unsigned long long* seed_offset, const int* forced,
                            int* token_out, float* logp_out, void* stream) {
   if (B <= 0) return 0;
-  sample_kernel<<<B, LP_THREADS, 0, STREAM(stream)>>>(static_cast<const __nv_bfloat16*>(logits), V, ld,
+  launch_pdl(sample_kernel, dim3(B), dim3(LP_THREADS), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(logits), V, ld,
                                                      1.f / temperature, greedy, seed, seed_offset, forced, token_out, logp_out);
   return LAUNCH_OK();
 }

@@ -237,7 +237,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ h_out,
                        __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int d, float eps) {
-  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   __shared__ float warp_ss[8];
   const int row = blockIdx.x;
   const int nvec = d >> 3;
@@ -387,7 +388,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_fwd_partials_kernel(const float* __restrict__ parts, int splits, long long stride,
                             const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w,
                             __nv_bfloat16* __restrict__ h_out, __nv_bfloat16* __restrict__ y, int d, float eps) {
-  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   __shared__ float warp_ss[8];
   const int row = blockIdx.x;
   const int nvec = d >> 3;
@@ -450,7 +452,8 @@ rmsnorm_fwd_partials_kernel(const float* __restrict__ parts, int splits, long lo
 // out[t, j] = silu(g) * u with [g | u] = sum_s parts[s][t, :]
 __global__ void swiglu_fwd_partials_kernel(const float* __restrict__ parts, int splits, long long stride,
                                            __nv_bfloat16* __restrict__ out, long long T, int f) {
-  griddep_launch();   // a following decode GEMM may start its set-up and weight prefetch now
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   const int fv = f >> 3;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * fv) return;
@@ -569,6 +572,8 @@ __global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_
 // Row gather of an embedding table and its backward scatter-add into an fp32 gradient.
 __global__ void embed_fwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                  __nv_bfloat16* __restrict__ out, int T, int d) {
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   const int dv = d >> 3;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(T) * dv) return;
@@ -604,9 +609,9 @@ extern "C" int rpeg_rmsnorm_fwd(const void* x, const void* res, const void* w, v
   __nv_bfloat16* hp = static_cast<__nv_bfloat16*>(h_out);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
   const int nv = ((d >> 3) + 255) / 256;
-  if (nv == 1) rmsnorm_fwd_row_kernel<1><<<T, 256, 0, STREAM(stream)>>>(xp, rp, wp, hp, yp, rstd, d, eps);
-  else if (nv == 2) rmsnorm_fwd_row_kernel<2><<<T, 256, 0, STREAM(stream)>>>(xp, rp, wp, hp, yp, rstd, d, eps);
-  else if (nv <= 4) rmsnorm_fwd_row_kernel<4><<<T, 256, 0, STREAM(stream)>>>(xp, rp, wp, hp, yp, rstd, d, eps);
+  if (nv == 1) launch_pdl(rmsnorm_fwd_row_kernel<1>, dim3(T), dim3(256), 0, STREAM(stream), xp, rp, wp, hp, yp, rstd, d, eps);
+  else if (nv == 2) launch_pdl(rmsnorm_fwd_row_kernel<2>, dim3(T), dim3(256), 0, STREAM(stream), xp, rp, wp, hp, yp, rstd, d, eps);
+  else if (nv <= 4) launch_pdl(rmsnorm_fwd_row_kernel<4>, dim3(T), dim3(256), 0, STREAM(stream), xp, rp, wp, hp, yp, rstd, d, eps);
   else
     rmsnorm_fwd_kernel<<<(T + ROW_WARPS - 1) / ROW_WARPS, ROW_WARPS * 32, 0, STREAM(stream)>>>(xp, rp, wp, hp, yp, rstd, T, d, eps);
   return LAUNCH_OK();
@@ -671,9 +676,9 @@ extern "C" int rpeg_rmsnorm_fwd_partials(const float* parts, int splits, long lo
   const __nv_bfloat16 *rp = static_cast<const __nv_bfloat16*>(res), *wp = static_cast<const __nv_bfloat16*>(w);
   __nv_bfloat16 *hp = static_cast<__nv_bfloat16*>(h_out), *yp = static_cast<__nv_bfloat16*>(y);
   const int nv = ((d >> 3) + 255) / 256;
-  if (nv == 1) rmsnorm_fwd_partials_kernel<1><<<T, 256, 0, STREAM(stream)>>>(parts, splits, stride, rp, wp, hp, yp, d, eps);
-  else if (nv == 2) rmsnorm_fwd_partials_kernel<2><<<T, 256, 0, STREAM(stream)>>>(parts, splits, stride, rp, wp, hp, yp, d, eps);
-  else if (nv <= 4) rmsnorm_fwd_partials_kernel<4><<<T, 256, 0, STREAM(stream)>>>(parts, splits, stride, rp, wp, hp, yp, d, eps);
+  if (nv == 1) launch_pdl(rmsnorm_fwd_partials_kernel<1>, dim3(T), dim3(256), 0, STREAM(stream), parts, splits, stride, rp, wp, hp, yp, d, eps);
+  else if (nv == 2) launch_pdl(rmsnorm_fwd_partials_kernel<2>, dim3(T), dim3(256), 0, STREAM(stream), parts, splits, stride, rp, wp, hp, yp, d, eps);
+  else if (nv <= 4) launch_pdl(rmsnorm_fwd_partials_kernel<4>, dim3(T), dim3(256), 0, STREAM(stream), parts, splits, stride, rp, wp, hp, yp, d, eps);
   else return -3;
   return LAUNCH_OK();
 }
@@ -683,7 +688,7 @@ extern "C" int rpeg_swiglu_fwd_partials(const float* parts, int splits, long lon
   if ((f & 7) || splits < 1) return -2;
   const long long n = T * (f >> 3);
   if (n <= 0) return 0;
-  swiglu_fwd_partials_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
+  launch_pdl(swiglu_fwd_partials_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, STREAM(stream), 
       parts, splits, stride, static_cast<__nv_bfloat16*>(out), T, f);
   return LAUNCH_OK();
 }
@@ -731,7 +736,7 @@ extern "C" int rpeg_embed_fwd(const int* ids, const void* table, void* out, int 
   if (d & 7) return -2;
   const long long n = static_cast<long long>(T) * (d >> 3);
   if (n <= 0) return 0;
-  embed_fwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, STREAM(stream)>>>(
+  launch_pdl(embed_fwd_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, STREAM(stream), 
       ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), T, d);
   return LAUNCH_OK();
 }

@@ -72,8 +72,20 @@ class PipelineRunner:
             raise ValueError("a pipeline group of more than one rank needs stage models")
         self.first, self.last = self.stage == 0, self.stage == self.n_stages - 1
         self._pending: List[Tuple[object, torch.Tensor]] = []   # sends in flight: (work, buffer kept alive)
-        if self.n_stages > 1:                                   # build the communicator now, all ranks together
-            dist.all_reduce(torch.zeros(1, device=model.device), group=group)
+        if self.n_stages > 1:
+            # Build the communicator and both neighbour connections now, all ranks together: NCCL sets a point-to-point
+            # connection up on first use with a host-side handshake, which is better done outside the schedule.
+            dev = model.device
+            dist.all_reduce(torch.zeros(1, device=dev), group=group)
+            ops, bufs = [], []
+            for peer in (self.stage - 1, self.stage + 1):
+                if 0 <= peer < self.n_stages:
+                    out, inp = torch.zeros(4, device=dev), torch.zeros(4, device=dev)
+                    bufs += [out, inp]
+                    ops += [dist.P2POp(dist.isend, out, self._global(peer), group), dist.P2POp(dist.irecv, inp, self._global(peer), group)]
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+            torch.cuda.synchronize(dev)
         self.sent_bytes = 0
         self.p2p_calls = 0
 

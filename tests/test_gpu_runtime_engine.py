@@ -64,7 +64,11 @@ def test_engine_checkpoint_replay_restores_weights_and_optimizer(tmp_path, cuda_
 def test_engine_runs_update_epochs_over_minibatches(tmp_path, cuda_device):
     """``algorithm.epochs`` x ``algorithm.minibatch_size``: the policy and the critic take one optimizer step per
     minibatch of every epoch (8 rows, minibatches of 4, 2 epochs -> 4 steps per training node)."""
-    run = tiny_job(tmp_path, "ppo", steps=1, algorithm={"epochs": 2, "minibatch_size": 4, "seed": 5})
+    from rpeg_b200.runtime.io import dump_mapping, load_mapping
+    run = tiny_job(tmp_path, "ppo", steps=1)
+    m = load_mapping(run)
+    m.setdefault("algorithm", {}).update(epochs=2, minibatch_size=4)
+    dump_mapping(m, run)
     res = execute_compiled(compile_runtime_plan(run), "engine")
     assert res["error"] is None and res["verification"]["ok"], (res["error"], res["verification"]["errors"])
     events = read_trace(tmp_path / "traces/run.jsonl")
