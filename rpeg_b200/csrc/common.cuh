@@ -98,14 +98,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Host side: RPEG_PDL=0 turns programmatic dependent launches off (plain stream order).
+// Host side: RPEG_PDL=0 turns programmatic dependent launches off for good (plain stream order); otherwise
+// rpeg_set_pdl() switches them per phase (they pay off for the small-batch decode step, not for large batches).
+inline int& pdl_state() {
+  static int v = -1;            // -1 = not read yet, 0 = off, 1 = on, 2 = off by the environment
+  return v;
+}
 inline int pdl_enabled() {
-  static int v = -1;
+  int& v = pdl_state();
   if (v < 0) {
     const char* e = getenv("RPEG_PDL");
-    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    v = (e != nullptr && e[0] == '0') ? 2 : 1;
   }
-  return v;
+  return v == 1;
 }
 
 // Launch `kernel` as a programmatic dependent of the previous kernel in `stream`: its blocks may become resident

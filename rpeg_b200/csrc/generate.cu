@@ -160,3 +160,12 @@ extern "C" int rpeg_splitk_reduce(const float* part, void* out, int M, int N, in
       part, static_cast<__nv_bfloat16*>(out), M, N, ldc, splits);
   return LAUNCH_OK();
 }
+
+// Switch programmatic dependent launches on or off for the kernels launched from now on (a CUDA graph keeps what was
+// in force while it was captured). The environment's RPEG_PDL=0 wins.
+extern "C" void rpeg_set_pdl(int on) {
+  pdl_enabled();
+  int& v = pdl_state();
+  if (v != 2) v = on ? 1 : 0;
+}
+

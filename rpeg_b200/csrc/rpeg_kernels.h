@@ -94,6 +94,8 @@ int rpeg_scatter_rows_by_index(const void* src, long long n, long long row_bytes
                                long long rows_per_rank, void* const* dst, int world, void* stream);
 // Version words of pushed data: release-store `version` into word `word` of every destination flag array after
 // the copies queued before it; poll flags[0..n) >= min_version with a bound (result[0] = 1 reached, 0 not yet).
+// Programmatic dependent launches on/off for subsequent launches (graphs keep the setting of their capture).
+void rpeg_set_pdl(int on);
 int rpeg_publish_version(void* const* flag_arrays, int n_dst, int word, unsigned version, void* stream);
 int rpeg_wait_flags(const unsigned* flags, int n, unsigned min_version, unsigned long long timeout_ns, int* result,
                     void* stream);

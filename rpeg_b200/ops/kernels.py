@@ -104,6 +104,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     return out
 
 
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launches for the kernels launched from now on (a captured graph keeps its setting)."""
+    lib().rpeg_set_pdl(int(bool(on)))
+
+
 def publish_version(flag_ptrs, word: int, version: int) -> None:
     """After the copies queued on this stream: store ``version`` into word ``word`` of every flag array in
     ``flag_ptrs`` (device pointers, local or peer) with system-scope release."""

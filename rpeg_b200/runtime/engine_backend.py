@@ -138,7 +138,7 @@ class EngineOperationHandler:
         rep = prompts.repeat_interleave(w.samples_per_prompt, dim=0).contiguous()
         a = self.run.algorithm
         gen = tr.gen.generate(rep, w.generation_length, temperature=a.temperature, greedy=a.greedy, seed=a.seed + 100003 * step,
-                              group_size=w.samples_per_prompt)
+                              group_size=w.samples_per_prompt, top_k=a.top_k, top_p=a.top_p)
         lens = gen.lengths.tolist()
         st["rollout"] = A.Rollout(rep, [w.context_length] * rep.shape[0], gen.tokens, lens, gen.logprobs, gen.response_mask(),
                                   weight_version=self.latest.get("ac_share" if self.shared else "actor", 0))

@@ -301,8 +301,34 @@ def launch_script(run_file: Path, space: DeviceSpace) -> str:
             f"--master-port 29511 -m rpeg_b200.runtime.run --config {run_file}\n")
 
 
+def sbatch_script(run_file: Path, space: DeviceSpace, cfg: dict) -> str:
+    """A Slurm batch file for the planned job: one task per node, each starting one process per GPU with torchrun;
+    the first node of the allocation is the rendezvous host. ``slurm: {partition, account, time, job_name,
+    extra: [...]}`` of the job file fills the directives (reference: RPEG/runtime/job_plan.py:240-327, which
+    emits ``submit.sbatch`` for its srun launcher). Nothing is submitted."""
+    sl = dict(cfg.get("slurm") or {})
+    nodes = space.R * space.N
+    lines = ["#!/bin/bash", f"#SBATCH --job-name={sl.get('job_name', cfg.get('run_id', 'rpeg'))}", f"#SBATCH --nodes={nodes}",
+             "#SBATCH --ntasks-per-node=1", f"#SBATCH --gpus-per-node={space.G}", f"#SBATCH --time={sl.get('time', '02:00:00')}",
+             f"#SBATCH --output={run_file.parent}/slurm-%j.out"]
+    for key in ("partition", "account", "qos", "constraint"):
+        if sl.get(key):
+            lines.append(f"#SBATCH --{key}={sl[key]}")
+    lines += [f"#SBATCH {x}" for x in sl.get("extra", ())]
+    lines += ["", "set -euo pipefail",
+              'MASTER_ADDR=$(scontrol show hostnames "$SLURM_JOB_NODELIST" | head -n 1)',
+              "export MASTER_ADDR MASTER_PORT=${MASTER_PORT:-29511}",
+              f"srun --ntasks-per-node=1 python -m torch.distributed.run --nnodes={nodes} --nproc-per-node {space.G} \\",
+              '     --node-rank "$SLURM_NODEID" --master-addr "$MASTER_ADDR" --master-port "$MASTER_PORT" \\',
+              f"     -m rpeg_b200.runtime.run --config {run_file}", ""]
+    if nodes > 1:
+        lines.insert(7, "# the engine backend executes plans of ONE NVSwitch node; multi-node plans run with the metadata backend only")
+    return "\n".join(lines)
+
+
 # ------------------------------------------------------------------------------ driver
-def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, quiet: bool = False) -> Dict[str, Any]:
+def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, emit_sbatch: bool = False,
+                     quiet: bool = False) -> Dict[str, Any]:
     cfg_path = Path(config_path).resolve()
     cfg = load_mapping(cfg_path)
     base = cfg_path.parent
@@ -391,6 +417,8 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, qu
     compiled = compile_runtime_plan(root / "run.yaml", dry_run=True)
     if emit_launch or bool((cfg.get("outputs") or {}).get("emit_launch", False)):
         (root / "submit.sh").write_text(launch_script(root / "run.yaml", space))
+    if emit_sbatch or bool((cfg.get("outputs") or {}).get("emit_sbatch", False)):
+        (root / "submit.sbatch").write_text(sbatch_script(root / "run.yaml", space, cfg))
     if not quiet:
         print(f"job planned in {root}: {comparison['input']['makespan_s']:.3f} s -> {comparison['output']['makespan_s']:.3f} s "
               f"({comparison['speedup']:.2f}x), plan {plan_dict['plan_hash'][:12]}, {len(compiled.lowered.nodes)} runtime nodes")
@@ -403,9 +431,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--config", required=True)
     ap.add_argument("--out-dir", default=None)
     ap.add_argument("--emit-launch", action="store_true", help="also write submit.sh (a torchrun line; nothing is launched)")
+    ap.add_argument("--emit-sbatch", action="store_true", help="also write submit.sbatch (a Slurm batch file; nothing is submitted)")
     args = ap.parse_args(argv)
     try:
-        plan_runtime_job(args.config, args.out_dir, emit_launch=args.emit_launch)
+        plan_runtime_job(args.config, args.out_dir, emit_launch=args.emit_launch, emit_sbatch=args.emit_sbatch)
     except (RuntimeConfigError, ValueError, KeyError) as exc:
         print(f"job planning error: {exc}", file=sys.stderr)
         return 2

@@ -6,7 +6,8 @@ gives each its rendezvous environment (loopback address, one port per job) and t
 assignment, waits for ``ready`` heartbeats and stops the group with SIGTERM followed by SIGKILL
 after a grace period. ``torchrun_command`` renders the equivalent ``torch.distributed.run`` line for
 a user who launches by hand. Reference: RPEG/runtime/launcher.py:27-211 (local launcher); the
-reference's Slurm launcher (:212-407) has no counterpart here: a job is one NVSwitch node.
+reference's Slurm launcher (:212-407) is replaced by a batch file that `runtime.job_plan --emit-sbatch` writes
+(one task per node running torchrun); the engine backend itself executes plans of one NVSwitch node.
 """
 from __future__ import annotations
 

@@ -237,3 +237,25 @@ def test_generation_with_shared_prompt_pages(cuda_device, S):
     gb = shared.generate(prompts, 24, greedy=True, group_size=Kq)
     same = sum(int(torch.equal(ga.tokens[i], gb.tokens[i])) for i in range(N))
     assert same >= N - 2, f"only {same} of {N} rows identical"
+
+
+def test_generation_with_top_k_stays_inside_the_top_k(cuda_device):
+    """``top_k = 1`` through the whole generator (prefill sampling, graph decode steps) equals greedy decoding, and the
+    recorded log-probs are those of the full softmax."""
+    cfg = LlamaConfig.tiny(n_layers=2)
+    model = LlamaModel(cfg, cuda_device, seed=4)
+    gen = Generator(model, max_slots=8, max_seq_len=128, kv_budget_bytes=5e8, eos_id=1, sync_interval=4)
+    prompts = torch.randint(2, cfg.vocab, (6, 20), device=cuda_device, dtype=torch.int32)
+    a = gen.generate(prompts, 24, greedy=True)
+    b = gen.generate(prompts, 24, temperature=1.0, seed=3, top_k=1)
+    K.check_status()
+    same = sum(int(torch.equal(a.tokens[i], b.tokens[i])) for i in range(6))
+    assert same >= 5, f"only {same} of 6 rows identical"          # a bf16 tie may flip one choice
+    lens = b.lengths.tolist()
+    ro = A.Rollout(prompts, [20] * 6, b.tokens, lens, b.logprobs, b.response_mask())
+    lp = A.sequence_logprobs(model, ro, A.AlgoConfig(micro_tokens=512, head_chunk=64))
+    mask = b.response_mask().bool()
+    assert torch.allclose(lp[mask], b.logprobs[mask], atol=6e-2)
+    c = gen.generate(prompts, 24, temperature=1.0, seed=3, top_p=0.3)
+    K.check_status()
+    assert int(c.lengths.min()) >= 1

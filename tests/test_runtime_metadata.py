@@ -122,8 +122,10 @@ def test_engine_jobs_get_the_data_parallel_plan_family(tmp_path):
 def test_job_planner_emits_a_compilable_pair(tmp_path):
     job = tmp_path / "job.yaml"
     dump_mapping(job_mapping("ppo"), job)
-    res = plan_runtime_job(job, tmp_path / "out", emit_launch=True, quiet=True)
+    res = plan_runtime_job(job, tmp_path / "out", emit_launch=True, emit_sbatch=True, quiet=True)
     out = res["out_dir"]
+    sb = (out / "submit.sbatch").read_text()
+    assert "#SBATCH --nodes=1" in sb and "#SBATCH --gpus-per-node=8" in sb and "srun" in sb and "rpeg_b200.runtime.run" in sb
     for f in ("baseline_plan.yaml", "optimized_plan.yaml", "run.yaml", "plots/optimizer_input.gantt.svg",
               "plots/optimizer_output.gantt.svg", "metrics/analytical_comparison.json", "submit.sh"):
         assert (out / f).exists(), f
