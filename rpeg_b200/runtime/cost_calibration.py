@@ -128,6 +128,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--config", required=True)
     ap.add_argument("--trace", required=True)
     ap.add_argument("--output", default=None, help="hardware fragment (yaml or json)")
+    ap.add_argument("--report", default=None, help="write the full report (one row per node with predicted and measured seconds) "
+                    "as JSON, the input of experiments/plot_cost_model_validation.py")
     ap.add_argument("--hw", action="append", default=[], help="hardware file(s) laid over the B200 preset before predicting: "
                     "a calibrate.py output and/or a fragment from an earlier fit (validation of that fit on this run)")
     args = ap.parse_args(argv)
@@ -138,6 +140,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 2
     rep = calibrate_costs(compiled, read_trace(args.trace), hardware_for_run(compiled.run_config, args.hw))
     rep["prediction_error"] = prediction_error(rep)
+    if args.report:
+        with open(args.report, "w") as fh:
+            json.dump(rep, fh, indent=1)
     if args.output:
         dump_mapping(rep["hardware"], args.output)
     print(json.dumps({k: v for k, v in rep.items() if k != "nodes"}, indent=2))

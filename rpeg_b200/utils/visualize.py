@@ -173,3 +173,56 @@ def exec_to_dot(executable, path: Optional[str] = None) -> str:
         with open(path, "w") as fh:
             fh.write(text)
     return text
+
+
+def chart_svg(series: Sequence[Tuple[str, Sequence[Tuple[float, float]]]], path: str, *, title: str = "", xlabel: str = "", ylabel: str = "",
+              log_x: bool = False, log_y: bool = False, lines: bool = True, diagonal: bool = False, width: int = 720,
+              height: int = 480) -> str:
+    """A small line / scatter chart as SVG: ``series`` = [(name, [(x, y), ...])]. ``diagonal`` draws y = x (for
+    predicted-against-measured scatters); log axes take positive values only."""
+    import math
+    pts = [(x, y) for _, s in series for x, y in s if (not log_x or x > 0) and (not log_y or y > 0)]
+    if not pts:
+        raise ValueError("nothing to plot")
+    tx = (lambda v: math.log10(v)) if log_x else (lambda v: v)
+    ty = (lambda v: math.log10(v)) if log_y else (lambda v: v)
+    x0, x1 = min(tx(x) for x, _ in pts), max(tx(x) for x, _ in pts)
+    y0, y1 = min(ty(y) for _, y in pts), max(ty(y) for _, y in pts)
+    if diagonal:
+        x0 = y0 = min(x0, y0)
+        x1 = y1 = max(x1, y1)
+    x1, y1 = (x1 if x1 > x0 else x0 + 1.0), (y1 if y1 > y0 else y0 + 1.0)
+    left, top, right, bottom = 70, 40, 20, 50
+    sx = lambda v: left + (tx(v) - x0) / (x1 - x0) * (width - left - right)
+    sy = lambda v: height - bottom - (ty(v) - y0) / (y1 - y0) * (height - top - bottom)
+    colours = ["#4c78a8", "#f58518", "#54a24b", "#e45756", "#b279a2", "#72b7b2", "#9d755d", "#bab0ac"]
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" font-family="monospace" font-size="11">',
+           f'<rect width="{width}" height="{height}" fill="white"/>', f'<text x="{left}" y="20" font-size="13">{escape(title)}</text>',
+           f'<rect x="{left}" y="{top}" width="{width - left - right}" height="{height - top - bottom}" fill="none" stroke="#888"/>',
+           f'<text x="{(left + width - right) / 2:.0f}" y="{height - 12}" text-anchor="middle">{escape(xlabel)}</text>',
+           f'<text x="14" y="{(top + height - bottom) / 2:.0f}" transform="rotate(-90 14 {(top + height - bottom) / 2:.0f})" text-anchor="middle">{escape(ylabel)}</text>']
+    for k in range(6):
+        fx, fy = x0 + (x1 - x0) * k / 5, y0 + (y1 - y0) * k / 5
+        vx, vy = (10 ** fx if log_x else fx), (10 ** fy if log_y else fy)
+        px, py = left + (width - left - right) * k / 5, height - bottom - (height - top - bottom) * k / 5
+        out.append(f'<line x1="{px:.1f}" y1="{top}" x2="{px:.1f}" y2="{height - bottom}" stroke="#eee"/>')
+        out.append(f'<line x1="{left}" y1="{py:.1f}" x2="{width - right}" y2="{py:.1f}" stroke="#eee"/>')
+        out.append(f'<text x="{px:.1f}" y="{height - bottom + 14}" text-anchor="middle">{vx:.3g}</text>')
+        out.append(f'<text x="{left - 6}" y="{py + 4:.1f}" text-anchor="end">{vy:.3g}</text>')
+    if diagonal:
+        out.append(f'<line x1="{left}" y1="{height - bottom}" x2="{width - right}" y2="{top}" stroke="#999" stroke-dasharray="4 3"/>')
+    for i, (name, s) in enumerate(series):
+        c = colours[i % len(colours)]
+        ok = [(x, y) for x, y in s if (not log_x or x > 0) and (not log_y or y > 0)]
+        if lines and len(ok) > 1:
+            out.append(f'<polyline fill="none" stroke="{c}" stroke-width="1.5" points="' + " ".join(f"{sx(x):.1f},{sy(y):.1f}" for x, y in ok) + '"/>')
+        for x, y in ok:
+            out.append(f'<circle cx="{sx(x):.1f}" cy="{sy(y):.1f}" r="3" fill="{c}"><title>{escape(name)}: ({x:.4g}, {y:.4g})</title></circle>')
+        out.append(f'<rect x="{width - right - 170}" y="{top + 8 + 14 * i}" width="9" height="9" fill="{c}"/>')
+        out.append(f'<text x="{width - right - 156}" y="{top + 17 + 14 * i}">{escape(name)}</text>')
+    out.append("</svg>")
+    text = "\n".join(out)
+    if path:
+        with open(path, "w") as fh:
+            fh.write(text)
+    return text

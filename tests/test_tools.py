@@ -222,3 +222,19 @@ def test_dot_writers_cover_template_unrolled_and_lowered_graphs(tmp_path):
     assert t2.count("subgraph cluster_") == 3 and '"t_pi@0" -> "g_pi@2"' in t2 and "style=dashed" in t2   # staleness 1: weights of step 0 serve step 2
     assert all(n.id in t3 for n in low.nodes)
     assert (tmp_path / "b.dot").read_text() == t2
+
+
+def test_cost_model_validation_statistics_and_chart(tmp_path):
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("pcv", os.path.join(ROOT, "experiments", "plot_cost_model_validation.py"))
+    pcv = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(pcv)
+    st = pcv.validation_stats([(1.0, 1.0), (2.2, 2.0), (0.5, 1.0)])
+    assert st["n"] == 3 and st["mape"] == pytest.approx((0 + 0.1 + 0.5) / 3) and st["within_25pct"] == pytest.approx(2 / 3)
+    assert pcv.validation_stats([(3.0, 3.0), (9.0, 9.0)])["log_r2"] == pytest.approx(1.0)
+    rep = {"nodes": [{"class": "GEN", "predicted_s": 10.0, "measured_s": 11.0}, {"class": "TRAIN", "predicted_s": 5.0, "measured_s": 4.0},
+                     {"class": "INF", "predicted_s": 0.001, "measured_s": 0.002}]}
+    (tmp_path / "r.json").write_text(json.dumps(rep))
+    assert pcv.main([str(tmp_path / "r.json"), "--output", str(tmp_path / "v.svg")]) == 0
+    svg = (tmp_path / "v.svg").read_text()
+    assert svg.startswith("<svg") and svg.count("<circle") == 2          # the 2 ms node is below --min-seconds
