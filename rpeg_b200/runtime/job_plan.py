@@ -74,18 +74,28 @@ def job_device_space(cfg: dict) -> DeviceSpace:
     return DeviceSpace(int(ds.get("racks", 1)), int(ds.get("nodes_per_rack", 1)), int(ds.get("gpus_per_node", 1)))
 
 
-def job_hardware(cfg: dict) -> Hardware:
+def job_hardware(cfg: dict, base_dir: Optional[Path] = None) -> Hardware:
     """Three forms: ``preset: b200_nvswitch`` (measured B200 numbers, fields may be overridden), flat
-    alpha/beta keys, or ``network: {intra_node, intra_rack, inter_rack}: {latency, bandwidth}``."""
+    alpha/beta keys, or ``network: {intra_node, intra_rack, inter_rack}: {latency, bandwidth}``. ``file: hw.yaml``
+    (a ``calibrate.py`` output or a ``cost_calibration`` fragment, relative to the job file) is laid under the keys
+    written in the job file itself, so a job can be planned with this machine's measured constants."""
     hw = dict(cfg.get("hardware") or {})
     names = set(Hardware.field_names())
+    if hw.get("file"):
+        path = Path(str(hw["file"]))
+        if not path.is_absolute() and base_dir is not None:
+            path = Path(base_dir) / path
+        if not path.exists():
+            raise RuntimeConfigError(f"[hardware] file {path} does not exist")
+        measured = load_mapping(path) or {}
+        hw = {**{k: v for k, v in measured.items() if k in names}, **hw}
     extra = {k: (hw[k] if k == "fabric" else float(hw[k])) for k in hw if k in names}
     if "memory_per_gpu_bytes" in hw and "memory_per_gpu" not in hw:
         extra["memory_per_gpu"] = float(hw["memory_per_gpu_bytes"])
     if str(hw.get("preset", "b200_nvswitch" if "alpha_coll_g" not in hw and "network" not in hw else "")) == "b200_nvswitch":
-        return b200_nvswitch().with_updates(**extra)
+        return _engine_limits(b200_nvswitch().with_updates(**extra), cfg)
     if "alpha_coll_g" in hw:
-        return Hardware(**extra)
+        return _engine_limits(Hardware(**extra), cfg)
     net = hw.get("network") or {}
     tiers = {"g": net.get("intra_node") or {"latency": 1e-6, "bandwidth": 270e9},
              "n": net.get("intra_rack") or {"latency": 50e-6, "bandwidth": 22e9},
@@ -95,7 +105,21 @@ def job_hardware(cfg: dict) -> Hardware:
         for kind in ("coll", "p2p"):
             kw[f"alpha_{kind}_{t}"], kw[f"beta_{kind}_{t}"] = float(link["latency"]), 1.0 / float(link["bandwidth"])
     kw.update(extra)
-    return Hardware(**kw)
+    return _engine_limits(Hardware(**kw), cfg)
+
+
+def _engine_limits(hw: Hardware, cfg: dict) -> Hardware:
+    """Jobs for the engine backend: the generator's slot count and paged KV pool bound how many rows decode
+    together; the cost model prices generation with them unless the job file set the fields itself."""
+    rt, rh = cfg.get("runtime") or {}, cfg.get("runtime_hardware") or {}
+    if str(rt.get("default_backend", "")) != "engine":
+        return hw
+    upd = {}
+    if not hw.gen_max_concurrency > 0 and rt.get("gen_slots"):
+        upd["gen_max_concurrency"] = float(rt["gen_slots"])
+    if not hw.gen_kv_budget_bytes > 0 and float(rh.get("kv_cache_budget_bytes", 0) or 0) > 0:
+        upd["gen_kv_budget_bytes"] = float(rh["kv_cache_budget_bytes"])
+    return hw.with_updates(**upd) if upd else hw
 
 
 def _spec(m: dict) -> ModelSpec:
@@ -340,7 +364,7 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
     if algorithm not in ("ppo", "grpo", "dpo"):
         raise RuntimeConfigError(f"unknown algorithm {algorithm!r}")
     ac_share = bool(pol.get("ac_share", False)) and algorithm == "ppo"
-    workload, space, hw, suite = job_workload(cfg, base), job_device_space(cfg), job_hardware(cfg), job_suite(cfg)
+    workload, space, hw, suite = job_workload(cfg, base), job_device_space(cfg), job_hardware(cfg, base), job_suite(cfg)
     policy = job_memory_policy(cfg)
     transfer_policy = job_transfer_policy(cfg)
     fusion = bool((cfg.get("runtime") or {}).get("intra_stage_fusion", False))
