@@ -55,6 +55,8 @@ def validate_engine_plan(compiled) -> None:
                                      f"on {g} GPU(s); expected ({g},1,1)")
     if any(int(t) > 0 for t in cfg.rpeg.tau.values()):
         raise RuntimeConfigError("engine backend runs synchronous plans only (tau = 0): stale serving needs disjoint devices")
+    if float(getattr(compiled.run_config.algorithm, "entropy_coef", 0.0) or 0.0) != 0.0:
+        raise RuntimeConfigError("engine backend: algorithm.entropy_coef is not implemented (the fused policy loss has no entropy term); set it to 0")
 
 
 class EngineOperationHandler:
