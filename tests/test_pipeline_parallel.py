@@ -87,3 +87,20 @@ def test_fused_pipeline_streams_are_in_order_per_model_and_phase(p, m):
                 got = [tasks[t].microbatch for t in sched.device_order[mm.device_stage(dst_stage)]
                        if tasks[t].model == name and tasks[t].phase == phase and tasks[t].stage == dst_stage]
                 assert sent == got == list(range(m))
+
+
+def test_version_and_slot_arithmetic_of_the_staleness_channels():
+    """Iteration k consumes weight version max(0, k - 1 - tau) and produces version k; with tau + 2 slots the
+    slot a producer writes is never one a consumer may still read."""
+    from rpeg_b200.parallel.publish import consumed_version, slots_for
+    from rpeg_b200.runtime.weight_versions import consumer_weight_version
+    for tau in (0, 1, 2, 3):
+        slots = slots_for(tau)
+        assert slots == tau + 2
+        for k in range(1, 12):
+            v = consumed_version(k, tau)
+            assert v == max(0, k - 1 - tau) == consumer_weight_version(k, tau)
+            # while iteration k generates (reads slot v % slots) the trainers may be writing any version in
+            # (v, k]: generation of k only starts after version v exists, training of k needs k's rollouts
+            for w in range(v + 1, k + 1):
+                assert w % slots != v % slots
