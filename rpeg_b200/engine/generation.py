@@ -236,6 +236,10 @@ class Generator:
         G = max(1, int(group_size))
         if N % G:
             raise ValueError(f"{N} rows do not form groups of {G}")
+        if G > 1 and isinstance(prompts, torch.Tensor):
+            grouped = prompts.reshape(N // G, G, -1)
+            if not bool((grouped == grouped[:, :1]).all()):
+                raise ValueError(f"group_size={G}: the rows of a group must carry the same prompt")
         longest = max(int(r.numel()) for r in rows)
         if longest + max_new > self.max_seq_len:
             raise ValueError(f"prompt ({longest}) + max_new ({max_new}) exceeds max_seq_len ({self.max_seq_len})")
