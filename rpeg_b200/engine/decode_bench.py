@@ -29,6 +29,8 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--hbm-gbs", type=float, default=6528.7)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--share", default="", help="K:S - groups of K consecutive rows alias the KV pages of their first S tokens "
+                    "(K samples of one prompt), to measure what the shared pages save")
     args = ap.parse_args(argv)
 
     from ..models.llama import LlamaConfig, LlamaModel
@@ -44,6 +46,11 @@ def main(argv=None) -> int:
     gen.out_tok = torch.zeros((n, 4096), dtype=torch.int32, device=dev)
     gen.out_lp = torch.zeros((n, 4096), dtype=torch.float32, device=dev)
     gen.page_table.copy_(torch.arange(1, 1 + n * gen.pages_per_row, dtype=torch.int32, device=dev).view(n, -1))
+    if args.share:
+        k_share, s_share = (int(x) for x in args.share.split(":"))
+        shared_pages = s_share // 64
+        leader = (torch.arange(n, device=dev) // k_share) * k_share
+        gen.page_table[:, :shared_pages] = gen.page_table[leader, :shared_pages]
     weight_bytes = 2 * sum(int(t.numel()) for name, t in model.p.items() if name != "embed" and not name.startswith("scalar_head"))
     kv_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2
 
