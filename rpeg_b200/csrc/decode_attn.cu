@@ -197,7 +197,7 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
                          const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
                          const int* __restrict__ page_table, int max_pages, const int* __restrict__ seq_lens,
                          __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int H, int Hkv,
-                         int nsplit, float scale_log2) {
+                         int nsplit, float scale_log2, const int* __restrict__ row_key0, int slot_base, int nslots) {
   griddep_launch();
   griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   __shared__ float red_m[4], red_l[4];
@@ -208,8 +208,12 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
   const int grp = lane >> 4, c = lane & 15;
   const int L = seq_lens[b];
   const int nblk = (L + 31) / 32;                  // 32-key blocks
-  const int blk_per_split = (nblk + nsplit - 1) / nsplit;
-  const int blk0 = split * blk_per_split;
+  // keys before row_key0[b] (a multiple of 64: whole shared prompt pages) are covered by the group kernel below,
+  // which leaves its result in partial slot 0; this kernel then fills slots slot_base .. slot_base + nsplit - 1
+  const int key0 = row_key0 != nullptr ? min(row_key0[b], L) : 0;
+  const int blk_first = key0 / 32;
+  const int blk_per_split = (max(nblk - blk_first, 0) + nsplit - 1) / nsplit;
+  const int blk0 = blk_first + split * blk_per_split;
   const int blk1 = min(nblk, blk0 + blk_per_split);
 
   float qr[8];
@@ -294,13 +298,136 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
       gl += red_l[w] * a;
       o += red_o[w][threadIdx.x] * a;
     }
-    if (nsplit == 1) {
+    if (nslots == 1) {
       out[(static_cast<size_t>(b) * H + h) * HD + threadIdx.x] = __float2bfloat16(gl > 0.f ? o / gl : 0.f);
     } else {
-      float* pp = partial + ((static_cast<size_t>(b) * H + h) * nsplit + split) * (HD + 2);
+      float* pp = partial + ((static_cast<size_t>(b) * H + h) * nslots + slot_base + split) * (HD + 2);
       pp[threadIdx.x] = o;
       if (threadIdx.x == 0) { pp[HD] = gm; pp[HD + 1] = gl; }
+      if (slot_base > 0 && split == 0 && key0 == 0) {       // no shared part for this row: slot 0 is empty
+        float* p0 = partial + (static_cast<size_t>(b) * H + h) * nslots * (HD + 2);
+        p0[threadIdx.x] = 0.f;
+        if (threadIdx.x == 0) { p0[HD] = -INFINITY; p0[HD + 1] = 0.f; }
+      }
     }
+  }
+}
+
+// Shared prompt pages: the K samples of one prompt alias the prompt's KV pages, so their queries can be scored
+// against each K/V tile while it is in registers instead of streaming it once per row. One CTA per (head, group):
+// group_rows[g][0..7] are the batch rows of the group (-1 = none, rows[0] is valid whenever group_shared[g] > 0),
+// group_shared[g] the number of shared keys (a multiple of 64). Same lane layout as the per-row kernel; the 8
+// queries sit in shared memory, their softmax state and output accumulators in registers. The result of every
+// member row goes to partial slot 0 in the split-KV format {o[HD], m, l}; the per-row kernel covers the rest.
+constexpr int GROUP_MAX = 8;
+
+__global__ void __launch_bounds__(128)
+paged_decode_attn_shared_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col0,
+                                const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
+                                const int* __restrict__ page_table, int max_pages, const int* __restrict__ group_rows,
+                                const int* __restrict__ group_shared, float* __restrict__ partial, int H, int Hkv,
+                                int nslots, float scale_log2) {
+  griddep_launch();
+  griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
+  __shared__ __align__(16) float q_s[GROUP_MAX][HD];
+  __shared__ float p_s[4][GROUP_MAX][32];
+  __shared__ float red_m[4][GROUP_MAX], red_l[4][GROUP_MAX];
+  __shared__ __align__(16) float red_o[4][GROUP_MAX][HD];
+  __shared__ int rows_s[GROUP_MAX];
+  const int h = blockIdx.x, g = blockIdx.y;
+  const int S = group_shared[g];
+  if (S <= 0) return;
+  const int hk = h / (H / Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int grp = lane >> 4, c = lane & 15;
+  if (threadIdx.x < GROUP_MAX) rows_s[threadIdx.x] = group_rows[g * GROUP_MAX + threadIdx.x];
+  __syncthreads();
+#pragma unroll
+  for (int qi = 0; qi < GROUP_MAX; ++qi) {
+    const int r = rows_s[qi];
+    q_s[qi][threadIdx.x] = r >= 0 ? __bfloat162float(q[static_cast<size_t>(r) * ldq + q_col0 + h * HD + threadIdx.x]) * scale_log2 : 0.f;
+  }
+  __syncthreads();
+  const int leader = rows_s[0];
+  const int* pt = page_table + static_cast<size_t>(leader) * max_pages;
+  const int nblk = S / 32;
+
+  float m[GROUP_MAX], l[GROUP_MAX], acc[GROUP_MAX][8];
+#pragma unroll
+  for (int qi = 0; qi < GROUP_MAX; ++qi) {
+    m[qi] = -INFINITY;
+    l[qi] = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[qi][k] = 0.f;
+  }
+  for (int blk = warp; blk < nblk; blk += 4) {
+    const int page = pt[(blk * 32) / PAGE];
+    const size_t base = ((static_cast<size_t>(page) * Hkv + hk) * PAGE + ((blk * 32) % PAGE) + grp * 16) * HD + c * 8;
+    const uint4* kp = reinterpret_cast<const uint4*>(kcache + base);
+    const uint4* vp = reinterpret_cast<const uint4*>(vcache + base);
+    {
+      uint4 kv[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) kv[j] = kp[j * (HD / 8)];
+#pragma unroll
+      for (int qi = 0; qi < GROUP_MAX; ++qi) {
+        float qr[8];
+        const float4 q0 = *reinterpret_cast<const float4*>(&q_s[qi][c * 8]);
+        const float4 q1 = *reinterpret_cast<const float4*>(&q_s[qi][c * 8 + 4]);
+        qr[0] = q0.x; qr[1] = q0.y; qr[2] = q0.z; qr[3] = q0.w; qr[4] = q1.x; qr[5] = q1.y; qr[6] = q1.z; qr[7] = q1.w;
+        float part[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part[j] = dot8(kv[j], qr);
+        const float sc = transpose_reduce16(part, lane);     // score of key blk*32 + lane for query qi
+        const float nm = fmaxf(m[qi], warp_max(sc));
+        const float alpha = exp2f(m[qi] - nm);
+        const float pr = exp2f(sc - nm);
+        l[qi] = l[qi] * alpha + warp_sum(pr);
+        m[qi] = nm;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[qi][k] *= alpha;
+        p_s[warp][qi][lane] = pr;
+      }
+    }
+    __syncwarp();
+    {
+      uint4 vv[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) vv[j] = vp[j * (HD / 8)];
+#pragma unroll
+      for (int qi = 0; qi < GROUP_MAX; ++qi) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) axpy8(acc[qi], p_s[warp][qi][grp * 16 + j], vv[j]);
+      }
+    }
+    __syncwarp();
+  }
+  // add the two key groups of a warp, then merge the 4 warps per query
+#pragma unroll
+  for (int qi = 0; qi < GROUP_MAX; ++qi) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[qi][k] += __shfl_xor_sync(0xffffffffu, acc[qi][k], 16);
+    if (lane == 0) { red_m[warp][qi] = m[qi]; red_l[warp][qi] = l[qi]; }
+    if (grp == 0) {
+      *reinterpret_cast<float4*>(&red_o[warp][qi][c * 8]) = make_float4(acc[qi][0], acc[qi][1], acc[qi][2], acc[qi][3]);
+      *reinterpret_cast<float4*>(&red_o[warp][qi][c * 8 + 4]) = make_float4(acc[qi][4], acc[qi][5], acc[qi][6], acc[qi][7]);
+    }
+  }
+  __syncthreads();
+  for (int qi = 0; qi < GROUP_MAX; ++qi) {
+    const int r = rows_s[qi];
+    if (r < 0) continue;
+    const float gm = fmaxf(fmaxf(red_m[0][qi], red_m[1][qi]), fmaxf(red_m[2][qi], red_m[3][qi]));
+    float gl = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float a = (red_m[w][qi] == -INFINITY) ? 0.f : exp2f(red_m[w][qi] - gm);
+      gl += red_l[w][qi] * a;
+      o += red_o[w][qi][threadIdx.x] * a;
+    }
+    float* pp = partial + (static_cast<size_t>(r) * H + h) * nslots * (HD + 2);
+    pp[threadIdx.x] = o;
+    if (threadIdx.x == 0) { pp[HD] = gm; pp[HD + 1] = gl; }
   }
 }
 
@@ -384,9 +511,35 @@ extern "C" int rpeg_paged_decode_attn(const void* q, int ldq, int q_col0, const 
   launch_pdl(paged_decode_attn_kernel, dim3(dim3(H, B, nsplit)), dim3(128), 0, STREAM(stream), 
       static_cast<const __nv_bfloat16*>(q), ldq, q_col0, static_cast<const __nv_bfloat16*>(kcache),
       static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages, seq_lens,
-      static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2);
+      static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, static_cast<const int*>(nullptr), 0, nsplit);
   if (nsplit > 1)
     launch_pdl(decode_combine_kernel, dim3(dim3(H, B)), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
+  return LAUNCH_OK();
+}
+
+// Decode attention for batches in which groups of rows share their first keys (K samples of one prompt aliasing
+// the prompt's KV pages). group_rows [B, 8] (batch rows of group g, -1 padded; unused groups all -1), group_shared
+// [B] (shared keys of group g, a multiple of 64, 0 = unused), row_key0 [B] (shared keys of ROW b, 0 if the row is in
+// no group). The shared keys are read once per group, the rest once per row; the two parts meet in the split-KV
+// combine. scratch: rpeg_decode_attn_scratch_bytes(B, H, nsplit + 1).
+extern "C" int rpeg_paged_decode_attn_grouped(const void* q, int ldq, int q_col0, const void* kcache, const void* vcache,
+                                              const int* page_table, int max_pages, const int* seq_lens, void* out,
+                                              float* scratch, int B, int H, int Hkv, int hd, int nsplit, float scale,
+                                              const int* group_rows, const int* group_shared, const int* row_key0,
+                                              void* stream) {
+  if (hd != HD || H % Hkv != 0) return -2;
+  if (nsplit < 1 || nsplit > 63) return -3;
+  if (scratch == nullptr || group_rows == nullptr || group_shared == nullptr || row_key0 == nullptr) return -4;
+  if (B <= 0) return 0;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const int nslots = nsplit + 1;
+  launch_pdl(paged_decode_attn_shared_kernel, dim3(H, B), dim3(128), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(q), ldq,
+             q_col0, static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages,
+             group_rows, group_shared, scratch, H, Hkv, nslots, scale_log2);
+  launch_pdl(paged_decode_attn_kernel, dim3(H, B, nsplit), dim3(128), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(q), ldq,
+             q_col0, static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages,
+             seq_lens, static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, row_key0, 1, nslots);
+  launch_pdl(decode_combine_kernel, dim3(H, B), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nslots);
   return LAUNCH_OK();
 }
 
@@ -436,7 +589,7 @@ extern "C" int rpeg_paged_decode_attn_static(const void* q, int ldq, int q_col0,
   launch_pdl(paged_decode_attn_kernel, dim3(dim3(H, B, nsplit)), dim3(128), 0, STREAM(stream), 
       static_cast<const __nv_bfloat16*>(q), ldq, q_col0, static_cast<const __nv_bfloat16*>(kcache),
       static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages, seq_lens, static_cast<__nv_bfloat16*>(out),
-      scratch, H, Hkv, nsplit, scale_log2);
+      scratch, H, Hkv, nsplit, scale_log2, static_cast<const int*>(nullptr), 0, nsplit);
   if (nsplit > 1)
     launch_pdl(decode_combine_kernel, dim3(dim3(H, B)), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
   return cudaGetLastError() == cudaSuccess ? 0 : RPEG_STATIC_ERR_LAUNCH;

@@ -122,6 +122,12 @@ long long rpeg_decode_attn_scratch_bytes(int B, int H, int nsplit);
 int rpeg_paged_decode_attn(const void* q, int ldq, int q_col0, const void* kcache, const void* vcache,
                            const int* page_table, int max_pages, const int* seq_lens, void* out, float* scratch,
                            int B, int H, int Hkv, int hd, int nsplit, float scale, void* stream);
+// Same, for batches whose rows share their first keys in groups (page-table aliasing): group_rows [B, 8], group_shared [B],
+// row_key0 [B]; scratch sized for nsplit + 1 partials.
+int rpeg_paged_decode_attn_grouped(const void* q, int ldq, int q_col0, const void* kcache, const void* vcache,
+                                   const int* page_table, int max_pages, const int* seq_lens, void* out, float* scratch,
+                                   int B, int H, int Hkv, int hd, int nsplit, float scale, const int* group_rows,
+                                   const int* group_shared, const int* row_key0, void* stream);
 
 // ---- symm.cu
 int rpeg_symm_alloc(unsigned long long bytes, void** out);

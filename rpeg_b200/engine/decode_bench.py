@@ -29,6 +29,8 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--hbm-gbs", type=float, default=6528.7)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--group-attention", action="store_true", help="with --share: score each group's queries against the shared "
+                    "keys in one pass (the group kernel) instead of relying on L2 hits")
     ap.add_argument("--share", default="", help="K:S - groups of K consecutive rows alias the KV pages of their first S tokens "
                     "(K samples of one prompt), to measure what the shared pages save")
     args = ap.parse_args(argv)
@@ -51,6 +53,15 @@ def main(argv=None) -> int:
         shared_pages = s_share // 64
         leader = (torch.arange(n, device=dev) // k_share) * k_share
         gen.page_table[:, :shared_pages] = gen.page_table[leader, :shared_pages]
+        if args.group_attention:
+            if k_share > gen.GROUP_MAX:
+                raise SystemExit(f"--group-attention handles groups of at most {gen.GROUP_MAX} rows")
+            gen.group_attention = True
+            n_groups = n // k_share
+            gen.group_rows.fill_(-1)
+            gen.group_rows[:n_groups, :k_share] = torch.arange(n_groups * k_share, dtype=torch.int32, device=dev).view(n_groups, k_share)
+            gen.group_shared[:n_groups] = shared_pages * 64
+            gen.row_key0[: n_groups * k_share] = shared_pages * 64
     weight_bytes = 2 * sum(int(t.numel()) for name, t in model.p.items() if name != "embed" and not name.startswith("scalar_head"))
     kv_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2
 

@@ -69,6 +69,8 @@ class GenerationResult:
 class Generator:
     BUCKETS = (256, 192, 128, 96, 64, 48, 32, 24, 16, 8)
     PDL_MAX_BATCH = 64
+    GROUP_MAX = 8              # queries the group attention kernel scores per K/V tile
+    GROUP_MIN = 3              # smaller groups are cheaper row by row
 
     @staticmethod
     def kv_bytes_for(cfg, slots: int, max_seq_len: int) -> int:
@@ -78,12 +80,14 @@ class Generator:
 
     def __init__(self, model: LlamaModel, *, max_slots: int = 64, max_seq_len: int = 2048, kv_budget_bytes: float = 16e9,
                  eos_id: int = 2, pad_id: int = 0, sync_interval: int = 8, use_graphs: bool = True,
-                 kv_storage: Optional[torch.Tensor] = None):
+                 kv_storage: Optional[torch.Tensor] = None, group_attention: bool = False):
         """``kv_storage``: optional flat bf16 tensor to carve the KV pages from instead of allocating
         them; lets the cache share memory with buffers that are dead during generation (gradients)."""
         cfg = model.cfg
         self.model, self.cfg, self.dev = model, cfg, model.device
         self.eos_id, self.pad_id = eos_id, pad_id
+        # rows that alias a prompt's KV pages are attended to as a group: the shared keys are read once per group
+        self.group_attention = bool(group_attention) and not cfg.qk_norm
         self.sync_interval = max(1, sync_interval)
         self.use_graphs = use_graphs
         self.max_seq_len = max_seq_len
@@ -106,6 +110,10 @@ class Generator:
         self.vcache = [kv_storage[(2 * l + 1) * per:(2 * l + 2) * per].view(shape) for l in range(cfg.n_layers)]
         n = self.max_slots
         i32 = dict(dtype=torch.int32, device=self.dev)
+        self.group_rows = torch.full((n, self.GROUP_MAX), -1, **i32)
+        self.group_shared = torch.zeros(n, **i32)
+        self.row_key0 = torch.zeros(n, **i32)
+        self._group_state = None
         self.token = torch.zeros(n, **i32)
         self.pos = torch.zeros(n, **i32)
         self.seq_len = torch.zeros(n, **i32)
@@ -135,8 +143,9 @@ class Generator:
         # chaining the step's kernels as programmatic dependents hides launch gaps at small batches (-3.7 % at 8 rows)
         # and costs a little once the kernels are long (+0.8 % at 128 rows and more)
         K.set_pdl(b <= self.PDL_MAX_BATCH)
+        groups = (self.group_rows[:b], self.group_shared[:b], self.row_key0[:b]) if self.group_attention else None
         xf = m.decode_step(self.token[:b], self.pos[:b], self.slot_ids[:b], self.seq_len[:b], self.page_table[:b],
-                           self.kcache, self.vcache, nsplit=self._nsplit(b))
+                           self.kcache, self.vcache, nsplit=self._nsplit(b), groups=groups)
         logits = m.lm_logits(xf, decode=True)
         K.decode_prepare(self.active[:b], self.gen_count[:b], self.forced_len[:b], self.forced[:b], self.eos_id)
         K.sample(logits, temperature, greedy, seed, forced=self.forced[:b], token_out=self.sampled[:b],
@@ -150,7 +159,8 @@ class Generator:
         if not self.use_graphs:
             self._decode_body(b, temperature, greedy, seed, top_k, top_p)
             return
-        key = (b, self.out_tok.shape[1], float(temperature), bool(greedy), int(seed), self.out_tok.data_ptr(), int(top_k), float(top_p))
+        key = (b, self.out_tok.shape[1], float(temperature), bool(greedy), int(seed), self.out_tok.data_ptr(), int(top_k), float(top_p),
+               self.group_attention)
         g = self._graphs.get(key)
         if g is None:
             # warm up and capture with every slot parked, so neither pass advances real rows
@@ -257,6 +267,9 @@ class Generator:
         for t in (self.active, self.seq_len, self.gen_count, self.n_finished, self.page_table, self.forced_len):
             t.zero_()
         self.pool = PagePool(self.pool.num_pages)      # a call that raised half way must not leak pages
+        self._group_state = None
+        self.group_shared.zero_()
+        self.row_key0.zero_()
         slot_row = [-1] * n
         slot_pages: List[List[int]] = [[] for _ in range(n)]   # pages a slot owns (the shared prompt pages are not in here)
         slot_shared = [0] * n      # leading page-table entries that alias the group's shared prompt pages
@@ -445,6 +458,8 @@ class Generator:
             used = max(live) + 1
             counters["live_slots_peak"] = max(counters["live_slots_peak"], len(live))
             b = self._bucket(used)
+            if self.group_attention:
+                self._sync_groups(live, slot_row, slot_shared, G)
             for _ in range(horizon):
                 self._step(b, temperature, greedy, seed, top_k, top_p)
             counters["decode_steps"] += horizon
@@ -459,6 +474,41 @@ class Generator:
                 retire([s for s in range(n) if slot_row[s] >= 0 and not act[s]])
         counters["kv_bytes"] = float(self.kv_bytes)
         return GenerationResult(res_tok, res_lp, res_len, counters)
+
+    def _sync_groups(self, live: List[int], slot_row: List[int], slot_shared: List[int], G: int) -> None:
+        """Tell the attention kernel which live slots share prompt pages: members of a prompt group (at least
+        ``GROUP_MIN`` of them live, at most ``GROUP_MAX`` per kernel group) and the number of shared keys."""
+        by_prompt: Dict[int, List[int]] = {}
+        for s in live:
+            if slot_shared[s] > 0:
+                by_prompt.setdefault(slot_row[s] // G, []).append(s)
+        rows, shared, key0 = [], [], {}
+        for g in sorted(by_prompt):
+            members = sorted(by_prompt[g])
+            for i in range(0, len(members), self.GROUP_MAX):
+                chunk = members[i:i + self.GROUP_MAX]
+                if len(chunk) < self.GROUP_MIN:
+                    continue
+                rows.append(chunk + [-1] * (self.GROUP_MAX - len(chunk)))
+                shared.append(slot_shared[chunk[0]] * PAGE)
+                for s in chunk:
+                    key0[s] = shared[-1]
+        state = (tuple(map(tuple, rows)), tuple(shared))
+        if state == self._group_state:
+            return
+        self._group_state = state
+        n = self.max_slots
+        gr = torch.full((n, self.GROUP_MAX), -1, dtype=torch.int32)
+        gs = torch.zeros(n, dtype=torch.int32)
+        k0 = torch.zeros(n, dtype=torch.int32)
+        if rows:
+            gr[: len(rows)] = torch.tensor(rows, dtype=torch.int32)
+            gs[: len(shared)] = torch.tensor(shared, dtype=torch.int32)
+            for s, v in key0.items():
+                k0[s] = v
+        self.group_rows.copy_(gr.to(self.dev))
+        self.group_shared.copy_(gs.to(self.dev))
+        self.row_key0.copy_(k0.to(self.dev))
 
     def _bucket(self, used: int) -> int:
         for b in sorted((*self.BUCKETS, 4, 2, 1)):

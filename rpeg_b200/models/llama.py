@@ -420,10 +420,11 @@ class LlamaModel:
     # ------------------------------------------------------------------ decode (one token per slot)
     def decode_step(self, token: torch.Tensor, pos: torch.Tensor, slot_ids: torch.Tensor, seq_len: torch.Tensor,
                     page_table: torch.Tensor, kcache: List[torch.Tensor], vcache: List[torch.Tensor],
-                    nsplit: int = 1) -> torch.Tensor:
+                    nsplit: int = 1, groups=None) -> torch.Tensor:
         """One autoregressive step for ``B`` slots: appends this token's K/V to the paged cache at
         ``pos`` and attends over ``seq_len`` cached keys. Returns the final normalised hidden ``[B, d]``.
-        All GEMMs have ``M = B <= 256`` and run split-K so every SM streams a slice of the weights."""
+        All GEMMs have ``M = B <= 256`` and run split-K so every SM streams a slice of the weights.
+        ``groups`` (see ``ops.kernels.paged_decode_attn``) names the rows that share their first KV pages."""
         cfg, p = self.cfg, self.p
         ws = self._workspace()
         scale = 1.0 / math.sqrt(cfg.head_dim)
@@ -440,7 +441,7 @@ class LlamaModel:
             K.rope_kv_append_partials_(parts, qkv, 0, cfg.q_width, cfg.q_width + cfg.kv_width, slot_ids, pos, self.cos_t,
                                        self.sin_t, page_table, kcache[i], vcache[i], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
             attn = K.paged_decode_attn(qkv, 0, kcache[i], vcache[i], page_table, seq_len, cfg.n_heads, cfg.n_kv_heads,
-                                       cfg.head_dim, scale, nsplit=nsplit)
+                                       cfg.head_dim, scale, nsplit=nsplit, groups=groups)
             parts = K.gemm_partials(attn, p[f"l{i}.wo"], ws)
             x2, h1 = K.rmsnorm_fwd_partials(parts, p[f"l{i}.mlp_norm"], cfg.rms_eps, residual=h, want_sum=True)
             parts = K.gemm_partials(x2, p[f"l{i}.w_gate_up"], ws)

@@ -448,9 +448,22 @@ def decode_scratch_numel(B: int, H: int, nsplit: int) -> int:
 
 
 def paged_decode_attn(q, q_col0, kcache, vcache, page_table, seq_lens, n_heads, n_kv_heads, head_dim, scale,
-                      nsplit: int = 1, scratch: torch.Tensor | None = None, out: torch.Tensor | None = None):
+                      nsplit: int = 1, scratch: torch.Tensor | None = None, out: torch.Tensor | None = None, groups=None):
+    """``groups = (group_rows [B, 8] int32, group_shared [B] int32, row_key0 [B] int32)``: rows that alias their first
+    KV pages in groups (K samples of one prompt); the shared keys are then read once per group (``scratch`` must
+    hold ``nsplit + 1`` partials per row and head)."""
     B = q.shape[0]
     out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device) if out is None else out
+    if groups is not None:
+        group_rows, group_shared, row_key0 = groups
+        if scratch is None:
+            scratch = torch.empty(decode_scratch_numel(B, n_heads, nsplit + 1), dtype=torch.float32, device=q.device)
+        check(lib().rpeg_paged_decode_attn_grouped(q.data_ptr(), q.stride(0), q_col0, kcache.data_ptr(), vcache.data_ptr(),
+                                                   page_table.data_ptr(), page_table.stride(0), seq_lens.data_ptr(), out.data_ptr(),
+                                                   scratch.data_ptr(), B, n_heads, n_kv_heads, head_dim, nsplit, scale,
+                                                   group_rows.data_ptr(), group_shared.data_ptr(), row_key0.data_ptr(), _stream()),
+              "rpeg_paged_decode_attn_grouped")
+        return out
     if nsplit > 1 and scratch is None:
         scratch = torch.empty(decode_scratch_numel(B, n_heads, nsplit), dtype=torch.float32, device=q.device)
     check(lib().rpeg_paged_decode_attn(q.data_ptr(), q.stride(0), q_col0, kcache.data_ptr(), vcache.data_ptr(),

@@ -214,7 +214,8 @@ def test_generation_with_shared_prompt_pages(cuda_device, S):
     page_bytes = 2 * cfg.n_layers * cfg.n_kv_heads * K.KV_PAGE * cfg.head_dim * 2
     plain = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=1e9, eos_id=1, sync_interval=4)
     shared = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=1e9, eos_id=1, sync_interval=4)
-    tight = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=14.5 * page_bytes, eos_id=1, sync_interval=4)
+    tight = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=14.5 * page_bytes, eos_id=1, sync_interval=4,
+                      group_attention=True)
     a = plain.generate(prompts, T, seed=11, forced_lens=forced)
     b = shared.generate(prompts, T, seed=11, forced_lens=forced, group_size=Kq)
     c = tight.generate(prompts, T, seed=11, forced_lens=forced, group_size=Kq)
@@ -237,6 +238,18 @@ def test_generation_with_shared_prompt_pages(cuda_device, S):
     gb = shared.generate(prompts, 24, greedy=True, group_size=Kq)
     same = sum(int(torch.equal(ga.tokens[i], gb.tokens[i])) for i in range(N))
     assert same >= N - 2, f"only {same} of {N} rows identical"
+    # the group attention kernel (shared keys scored once per group) must agree with the row-by-row kernel
+    grouped = Generator(model, max_slots=32, max_seq_len=S + T, kv_budget_bytes=1e9, eos_id=1, sync_interval=4, group_attention=True)
+    gc = grouped.generate(prompts, 24, greedy=True, group_size=Kq)
+    K.check_status()
+    same = sum(int(torch.equal(ga.tokens[i], gc.tokens[i])) for i in range(N))
+    assert same >= N - 2, f"group attention: only {same} of {N} rows identical"
+    gd = grouped.generate(prompts, T, seed=11, forced_lens=forced, group_size=Kq)
+    lens = gd.lengths.tolist()
+    ro = A.Rollout(prompts, [S] * N, gd.tokens, lens, gd.logprobs, gd.response_mask())
+    lp = A.sequence_logprobs(model, ro, A.AlgoConfig(micro_tokens=1024, head_chunk=64))
+    mask = gd.response_mask().bool()
+    assert torch.allclose(lp[mask], gd.logprobs[mask], atol=6e-2)
 
 
 def test_generation_with_top_k_stays_inside_the_top_k(cuda_device):
