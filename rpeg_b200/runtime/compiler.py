@@ -16,6 +16,7 @@ Workers: operators of the same model on the same allocation share one worker ``w
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any, Dict, List, Optional, Tuple
@@ -32,7 +33,7 @@ from ..passes.lower import ExecNodeType, ExecutableRPEG, lower
 from ..passes.transfer_resources import reserved_allocations
 from ..passes.unroll import UnrolledRPEG, unroll
 from ..search.evaluate import Configuration, is_compatible, stale_publication_layout_valid
-from .cluster import ClusterInventory, GPURef, inventory_from_file, local_inventory
+from .cluster import ClusterInventory, GPURef, inventory_from_file, local_inventory, slurm_inventory
 from .errors import RuntimeConfigError
 from .graph import RuntimeGraph, build_runtime_graph
 from .schema import OptimizedPlan, RuntimeRunConfig
@@ -287,7 +288,14 @@ def compile_runtime_plan(run_config, *, dry_run: bool = False, inventory: Option
     unrolled = unroll(rpeg, K)
     lowered = lower(rpeg, unrolled, eplan, suite, K, workload=wl, intra_stage_fusion=cfg.intra_stage_fusion)
     order = _validated_order(run, plan, lowered, policy)
-    inv = inventory or (inventory_from_file(run.resolve(run.cluster.inventory), space) if run.cluster.inventory else local_inventory(space))
+    if inventory is not None:
+        inv = inventory
+    elif run.cluster.inventory:
+        inv = inventory_from_file(run.resolve(run.cluster.inventory), space)
+    elif run.cluster.launcher.type == "slurm" and (os.environ.get("SLURM_JOB_NODELIST") or os.environ.get("SLURM_NODELIST")):
+        inv = slurm_inventory(space)                      # inside an allocation: the hosts Slurm gave this job
+    else:
+        inv = local_inventory(space)
     workers = _worker_specs(cfg, inv, run.runtime.default_backend)
     hw = b200_nvswitch(mem=float(run.hardware.memory_per_gpu_bytes))
     mm = NodeMemoryModel.from_policy(hw, suite, wl, memory_policy_from_run(run), trainable=frozenset(rpeg.trainable),

@@ -238,3 +238,19 @@ def test_cost_model_validation_statistics_and_chart(tmp_path):
     assert pcv.main([str(tmp_path / "r.json"), "--output", str(tmp_path / "v.svg")]) == 0
     svg = (tmp_path / "v.svg").read_text()
     assert svg.startswith("<svg") and svg.count("<circle") == 2          # the 2 ms node is below --min-seconds
+
+
+def test_slurm_inventory_from_the_environment():
+    from rpeg_b200.core.types import Allocation, DeviceSpace
+    from rpeg_b200.runtime.cluster import expand_nodelist, slurm_inventory
+    from rpeg_b200.runtime.errors import RuntimeConfigError
+    assert expand_nodelist("gpu[01-03,07],login1") == ("gpu01", "gpu02", "gpu03", "gpu07", "login1")
+    assert expand_nodelist("nid005") == ("nid005",)
+    space = DeviceSpace(1, 2, 4)
+    inv = slurm_inventory(space, {"SLURM_JOB_NODELIST": "b200-[10-11]"})
+    refs = inv.resolve_allocation(Allocation((0, 1, 2), (1, 1, 2)))
+    assert [(r.hostname, r.local_cuda_index, r.global_rank) for r in refs] == [("b200-11", 2, 6), ("b200-11", 3, 7)]
+    with pytest.raises(RuntimeConfigError):
+        slurm_inventory(space, {"SLURM_JOB_NODELIST": "b200-10"})
+    with pytest.raises(RuntimeConfigError):
+        slurm_inventory(space, {})
