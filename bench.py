@@ -41,6 +41,12 @@ CONFIGS = {
                             quantiles=((0.5, 256), (0.85, 512), (1.0, 1024)), min_gpus=4),
     "ppo_tiny": dict(algo="ppo", model="tiny", prompts=16, k=1, prompt_len=32, max_new=64, quantiles=((0.5, 16), (0.9, 32), (1.0, 64))),
     "dpo_tiny": dict(algo="dpo", model="tiny", prompts=16, k=2, prompt_len=32, max_new=64, quantiles=None),
+    # GRPO with generation and training on disjoint halves of the GPUs and one step of bounded staleness: generation of
+    # iteration k + 1 overlaps training of iteration k; weights and rollouts cross through versioned peer-memory channels
+    "grpo_7b_async": dict(algo="grpo_async", model="llama7b", prompts=32, k=8, prompt_len=512, max_new=2048, tau=1,
+                          quantiles=((0.5, 512), (0.9, 1024), (1.0, 2048)), min_gpus=2),
+    "grpo_tiny_async": dict(algo="grpo_async", model="tiny", prompts=16, k=4, prompt_len=32, max_new=64, tau=1,
+                            quantiles=((0.5, 16), (0.9, 32), (1.0, 64)), min_gpus=2),
 }
 
 
@@ -157,20 +163,21 @@ def main() -> None:
 
     torch.cuda.set_device(local_rank)
     device = torch.device(f"cuda:{local_rank}")
+    spec = CONFIGS[args.config]
     dp = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
-        from rpeg_b200.parallel.dp import DPContext
-        dp = DPContext(device)
+        if spec["algo"] != "grpo_async":            # the asynchronous engine builds its own groups
+            from rpeg_b200.parallel.dp import DPContext
+            dp = DPContext(device)
 
-    spec = CONFIGS[args.config]
     if world < spec.get("min_gpus", 1):
         raise SystemExit(f"config {args.config} needs at least {spec['min_gpus']} GPUs (optimizer state of its trainable models)")
     cfg = {"llama7b": lambda: LlamaConfig.llama7b(max_pos=4096), "llama13b": lambda: LlamaConfig.llama13b(max_pos=4096),
            "tiny": LlamaConfig.tiny}[spec["model"]]()
     B, Kk, S, T = spec["prompts"], spec["k"], spec["prompt_len"], spec["max_new"]
-    if B % world:
+    if B % world and spec["algo"] != "grpo_async":
         raise SystemExit(f"{B} prompts do not split over {world} ranks")
     b_local = B // world
     recompute = args.recompute
@@ -201,6 +208,35 @@ def main() -> None:
             if on_device:
                 p, r = p.to(device), r.to(device)
             return trainer.step(p, r, forced_lens=l)
+    elif spec["algo"] == "grpo_async":
+        import types
+        from rpeg_b200.engine.async_rl import AsyncGRPO
+        half = world // 2
+        n_gen_rows = B * Kk // half
+        slots = args.gen_slots or min(n_gen_rows, 256)
+        eng = AsyncGRPO(cfg, gen_ranks=list(range(half)), train_ranks=list(range(half, world)), prompts_per_step=B,
+                        samples_per_prompt=Kk, max_new=T, prompt_len=S, tau=int(spec.get("tau", 1)), algo=algo, gen_slots=slots,
+                        kv_budget_bytes=(args.kv_gb or 96.0) * 1e9, seed=42, eos_id=2, device=device, wait_timeout_s=900.0)
+        trainer = types.SimpleNamespace(h2d_bytes=0, d2h_bytes=0, last_counters={})
+        batches = []
+        for _ in range(n_iters):
+            prompts = torch.randint(3, cfg.vocab, (B, S), generator=gen_host, dtype=torch.int32)
+            rewards = torch.randn(B * Kk, generator=gen_host)
+            lens = draw_lengths(B * Kk, spec["quantiles"], gen_host)
+            batches.append((prompts.pin_memory(), rewards.pin_memory(), lens))
+
+        def run(i, on_device):
+            p, r, l = batches[i]
+            trainer.h2d_bytes = p.numel() * p.element_size() + (r.numel() * r.element_size() if eng.is_train else 0)
+            trainer.d2h_bytes = 8
+            if on_device:
+                p, r = p.to(device), r.to(device)
+            out = eng.step(p, r, forced_lens=l)
+            trainer.last_counters = dict(eng.counters)
+            out.setdefault("samples", 0.0)
+            out.setdefault("gen_tokens", 0.0)
+            out.setdefault("train_tokens", 0.0)
+            return out
     elif spec["algo"] == "ppo":
         from rpeg_b200.engine.trainers import PPOTrainer
         slots = args.gen_slots or min(b_local * Kk, 128)
@@ -274,11 +310,11 @@ def main() -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "gen_tokens_per_sec": stats[1] / secs, "train_tokens_per_sec": stats[2] / secs,
-            "config": {"model": {"grpo": f"{spec['model']} x2 (actor + frozen reference)", "dpo": f"{spec['model']} x2 (policy + frozen reference)", "ppo": f"{spec['model']} actor" + ("+critic shared trunk" if spec.get("shared") else ", critic") + ", reference, reward"}[spec["algo"]] + ", random init", "algorithm": spec["algo"],
-                       "global_batch": B * Kk if spec["algo"] == "grpo" else B, "prompts": B, "samples_per_prompt": Kk,
+            "config": {"model": {"grpo": f"{spec['model']} x2 (actor + frozen reference)", "grpo_async": f"{spec['model']} x2 (actor + frozen reference)", "dpo": f"{spec['model']} x2 (policy + frozen reference)", "ppo": f"{spec['model']} actor" + ("+critic shared trunk" if spec.get("shared") else ", critic") + ", reference, reward"}[spec["algo"]] + ", random init", "algorithm": spec["algo"],
+                       "global_batch": B * Kk if spec["algo"] in ("grpo", "grpo_async") else B, "prompts": B, "samples_per_prompt": Kk,
                        "seq_len": S + T, "prompt_len": S, "max_new_tokens": T, "gen_quantiles": spec["quantiles"],
-                       "parallelism": f"dp{world}", "optimizer": "adamw fp32 master, sharded over dp",
-                       "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if spec["algo"] in ("grpo", "ppo") else None,
+                       "parallelism": (f"gen{world // 2}+train{world - world // 2}, staleness {spec.get('tau', 1)}" if spec["algo"] == "grpo_async" else f"dp{world}"), "optimizer": "adamw fp32 master, sharded over dp",
+                       "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if spec["algo"] in ("grpo", "grpo_async", "ppo") else None,
                        "l2": "working set (13.5 GB of weights per model) far exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": stats_e2e[0] / (ms_e2e / 1e3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
                     "wall_s_per_step": wall_e2e / args.steps, "h2d_bytes_per_step": int(trainer.h2d_bytes),

@@ -87,13 +87,14 @@ class AsyncGRPO:
         dist.barrier()
 
     # ------------------------------------------------------------------ one iteration on this rank's side
-    def step(self, prompts: torch.Tensor, rewards: torch.Tensor) -> Dict[str, float]:
+    def step(self, prompts: torch.Tensor, rewards: torch.Tensor, forced_lens=None) -> Dict[str, float]:
         """``prompts [B, S]`` int32 and ``rewards [B * K]`` fp32 are the GLOBAL host tensors of this iteration (the
-        same on every rank; each rank takes the rows it owns). Returns this rank's metrics."""
+        same on every rank; each rank takes the rows it owns). ``forced_lens [B * K]`` optionally fixes the EOS
+        position of every row (synthetic length control). Returns this rank's metrics."""
         self.step_no += 1
         k = self.step_no
         t0 = time.perf_counter()
-        out = self._generate(k, prompts) if self.is_gen else self._train(k, prompts, rewards)
+        out = self._generate(k, prompts, forced_lens) if self.is_gen else self._train(k, prompts, rewards)
         out["wall_s"] = time.perf_counter() - t0
         out["step"] = float(k)
         return out
@@ -102,7 +103,7 @@ class AsyncGRPO:
         per = self.n_rows // parts
         return range(index * per, (index + 1) * per)
 
-    def _generate(self, k: int, prompts: torch.Tensor) -> Dict[str, float]:
+    def _generate(self, k: int, prompts: torch.Tensor, forced_lens=None) -> Dict[str, float]:
         v = consumed_version(k, self.tau)
         t0 = time.perf_counter()
         if v > 0 and not self.weights.ready(v, self.timeout):
@@ -114,11 +115,13 @@ class AsyncGRPO:
             model.weight_gate = self.weights.gate(v)
         rows = self._rows_of(self.gen_ranks.index(self.rank), len(self.gen_ranks))
         rep = prompts.to(self.device, torch.int32).repeat_interleave(self.K, dim=0)[rows.start:rows.stop].contiguous()
+        forced = None if forced_lens is None else [int(x) for x in forced_lens[rows.start:rows.stop]]
         res = gen.generate(rep, self.max_new, temperature=self.algo.temperature, seed=self.seed + 100003 * k + self.rank,
-                           group_size=self.K if (rows.start % self.K == 0 and len(rows) % self.K == 0) else 1)
+                           forced_lens=forced, group_size=self.K if (rows.start % self.K == 0 and len(rows) % self.K == 0) else 1)
         idx = torch.arange(rows.start, rows.stop, dtype=torch.int64, device=self.device)
         self.rollouts.send(k, idx, res.tokens, res.logprobs, res.lengths)
         K.check_status()
+        self.counters = dict(res.counters)
         return {"role": 0.0, "weight_version": float(v), "gen_tokens": float(res.lengths.sum().item()),
                 "waited_for_weights_s": waited}
 
@@ -147,7 +150,7 @@ class AsyncGRPO:
         self.opt.step()
         self.weights.publish(self.actor.w, k)
         K.check_status()
-        return {"role": 1.0, "loss": float(m["loss"]), "grad_norm": float(self.opt.grad_norm()), "trained_on_version": float(ro.weight_version),
+        return {"role": 1.0, "samples": float(ro.n), "loss": float(m["loss"]), "grad_norm": float(self.opt.grad_norm()), "trained_on_version": float(ro.weight_version),
                 "published_version": float(k), "train_tokens": float(sum(ro.total_lens())), "waited_for_rollouts_s": waited}
 
     def close(self) -> None:

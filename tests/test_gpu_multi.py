@@ -69,3 +69,13 @@ def test_runtime_graph_on_two_ranks_with_the_engine_backend(tmp_path):
     assert summary["nodes_failed"] == 0 and summary["logical_steps"] == 2 and summary["nonfinite_losses"] == 0
     other = read_trace(tmp_path / "out/traces/run.rank1.jsonl")
     assert sum(1 for e in other if e["event"] == "finish" and e["node_id"].startswith("t_pi@")) == 2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_bench_tiny_async_two_ranks():
+    """Generation and training on disjoint ranks with one step of staleness, through bench.py's own loop."""
+    r = _torchrun(2, 29564, "bench.py", "--config", "grpo_tiny_async", "--gpus", "2", "--steps", "1", "--warmup", "1")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = _last_json(r.stdout)
+    assert line["n_gpus"] == 2 and line["value"] > 0 and line["config"]["algorithm"] == "grpo_async"
+    assert line["config"]["parallelism"].startswith("gen1+train1")
