@@ -254,3 +254,15 @@ def test_slurm_inventory_from_the_environment():
         slurm_inventory(space, {"SLURM_JOB_NODELIST": "b200-10"})
     with pytest.raises(RuntimeConfigError):
         slurm_inventory(space, {})
+
+
+def test_scaling_sweep_script_writes_csv_and_chart(tmp_path):
+    gen = subprocess.run([sys.executable, os.path.join(ROOT, "experiments", "gen_scaling_configs.py"), "--out", str(tmp_path / "cfg")],
+                         capture_output=True, text=True, cwd=ROOT)
+    assert gen.returncode == 0, gen.stderr[-2000:]
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "experiments", "run_scaling.py"), str(tmp_path / "cfg"), "--match", "actor/16gpu_t128_sync",
+                        "--time", "1", "--csv", str(tmp_path / "s.csv"), "--plot", str(tmp_path / "s.svg")], capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    rows = (tmp_path / "s.csv").read_text().strip().splitlines()
+    assert len(rows) == 2 and "optimized_tokens_per_s" in rows[0] and rows[1].startswith("16gpu_t128_sync.yaml,16,")
+    assert (tmp_path / "s.svg").read_text().startswith("<svg")
