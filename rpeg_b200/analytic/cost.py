@@ -104,7 +104,10 @@ class NodeCostModel:
         role = node.role
         pd, pp, pt = node.pi
         m = self._effective_mb(node)
-        gemm = self._work(node) / (self._effective_flops(node) * pd * pp * pt)
+        if role is Role.GENERATION and node.n_active is None and self._length_bins() is not None:
+            gemm = self._generation_time_by_lengths(node)
+        else:
+            gemm = self._work(node) / (self._effective_flops(node) * pd * pp * pt)
         bubble = gemm * (pp - 1) / m
         opt = 0.0
         if role is Role.TRAINING:
@@ -148,7 +151,7 @@ class NodeCostModel:
                 return work + (n * prefill_row if node.is_prefill_phase else 0)
             decode_row = 2 * (T - 1) * sh.L * sh.layer_flops_per_token(S + T / 2) + 2 * (T - 1) * sh.V * sh.d
             return BK * (prefill_row + decode_row)
-        seq = S + T
+        seq = self._seq_len(node)
         trunk = 2 * sh.L * sh.layer_flops_per_token(seq)
         if role is Role.INFERENCE:
             n = node.n_seqs if node.n_seqs is not None else BK
@@ -168,7 +171,7 @@ class NodeCostModel:
             return self._generation_flops(node)
         hw, sh = self.hw, self._shape(node.model)
         pd, pp, pt = node.pi
-        seq = self.workload.S + self.workload.T
+        seq = self._seq_len(node)
         b = self._b_local(node)
         Lpp = sh.L / pp
         flops = b * seq * (2 * Lpp / pt) * sh.layer_flops_per_token(seq)
@@ -177,6 +180,82 @@ class NodeCostModel:
         if intensity >= hw.flops_per_gpu / hw.memory_bandwidth:
             return hw.flops_per_gpu * hw.sustained_flops_fraction * self._gemm_efficiency(node, b * seq)
         return intensity * hw.memory_bandwidth
+
+    def _length_bins(self):
+        """``[(row fraction, first step, last step), ...]`` of the workload's length quantiles (rows of a bin stop
+        uniformly inside it), or ``None`` when lengths are not to be used."""
+        q = self.workload.gen_quantiles
+        if not (self.hw.expected_lengths > 0 and q):
+            return None
+        bins, prev_f, prev_t = [], 0.0, 0
+        for f, t in q:
+            if f > prev_f:
+                bins.append((float(f) - prev_f, int(prev_t), int(t)))
+            prev_f, prev_t = float(f), int(t)
+        return bins or None
+
+    def _seq_len(self, node: ExecNode) -> float:
+        """Tokens per row of an inference / training vertex: prompt + cap, or prompt + expected response length when
+        the length quantiles are in use and the vertex is not already split by them."""
+        if node.n_seqs is None and self._length_bins() is not None:
+            return self.workload.S + self._mean_len()
+        return float(self.workload.S + self.workload.T)
+
+    def _mean_len(self) -> float:
+        """Expected response length under the quantiles (``T`` without them)."""
+        bins = self._length_bins()
+        if bins is None:
+            return float(self.workload.T)
+        return sum(frac * (a + b) / 2.0 for frac, a, b in bins)
+
+    def _generation_time_by_lengths(self, node: ExecNode) -> float:
+        """Seconds of an unsplit generation vertex when rows stop at their own length: the decode loop runs until
+        the longest row ends, the number of live rows falls along the length distribution (rows beyond the
+        generator's concurrency wait and are decoded later), every step streams the weights once and the K/V of the
+        live rows (a shared prompt token at ``gen_shared_prompt_cost`` of a private one)."""
+        hw, sh, w = self.hw, self._shape(node.model), self.workload
+        pd, pp, pt = node.pi
+        Lpp = sh.L / pp
+        rows = self._b_local(node) * self._effective_mb(node)           # rows of one replica
+        bw = hw.memory_bandwidth
+        w_bytes = Lpp / pt * sh.layer_params * sh.sb
+        e_w = hw.decode_bw_eff
+        e_kv = min(1.0, 3.5 * e_w)
+        kv_tok = 2 * (sh.d / pt) * sh.sb * Lpp                          # K/V bytes of one cached token on one GPU
+        share = hw.gen_shared_prompt_cost if (hw.gen_shared_prompt_cost < 1.0 and w.K > 1) else 1.0
+        prompt_rows = rows / w.K if share < 1.0 else rows
+        # prefill (once per prompt when the samples share it)
+        m_half = hw.gemm_m_half
+        tok = prompt_rows * w.S
+        eta = tok / (tok + m_half) if m_half > 0 else 1.0
+        flops = tok * (2 * Lpp / pt) * sh.layer_flops_per_token(w.S) + prompt_rows * 2 * sh.V * sh.d / pt
+        t_total = flops / (hw.flops_per_gpu * hw.sustained_flops_fraction * max(eta, 1e-6))
+        cap = self._gen_concurrency(node, rows, w.S + self._mean_len() / 2.0)
+        backlog = 0.0                                                   # row-steps that waited for a free slot
+        live_frac = 1.0
+        sub = 32
+        for frac, a, b in self._length_bins():
+            steps = max(0, b - a)
+            for i in range(sub):
+                t_mid = a + (i + 0.5) * steps / sub
+                dt = steps / sub
+                live = rows * (live_frac - frac * (i + 0.5) / sub)
+                run = min(live, cap)
+                if live > cap:
+                    backlog += (live - cap) * dt
+                elif backlog > 0 and dt > 0:
+                    extra = min(cap - live, backlog / dt)
+                    backlog -= extra * dt
+                    run = live + extra
+                ctx = w.S * share + t_mid
+                step_bytes = w_bytes / e_w + run * kv_tok * ctx / e_kv + 2 * run * sh.d * Lpp * sh.sb
+                t_total += dt * (step_bytes / bw + hw.decode_step_overhead_s)
+            live_frac -= frac
+        if backlog > 0:                                                 # the rows that waited run on after the others
+            ctx = w.S * share + self._mean_len() / 2.0
+            step_bytes = w_bytes / e_w + cap * kv_tok * ctx / e_kv
+            t_total += backlog / cap * (step_bytes / bw + hw.decode_step_overhead_s)
+        return t_total
 
     def _gen_concurrency(self, node: ExecNode, b: float, past: float) -> float:
         """Rows of one replica that decode together: the microbatch, capped by the generator's slots and by how
@@ -199,6 +278,8 @@ class NodeCostModel:
         P = pd * pp * pt
         extra = 0.0
         if node.role is Role.GENERATION:
+            if node.n_active is None and self._length_bins() is not None:
+                return 0.0                                   # _generation_time_by_lengths already counts the steps
             if hw.decode_step_overhead_s > 0:
                 if node.phase_steps is not None:
                     steps, past = node.phase_steps, w.S + node.phase_t_start + node.phase_steps / 2
@@ -207,7 +288,7 @@ class NodeCostModel:
                 b = self._b_local(node)
                 extra += hw.decode_step_overhead_s * steps * b / self._gen_concurrency(node, b, past) * self._effective_mb(node)
             return extra
-        seq = w.S + w.T
+        seq = self._seq_len(node)
         n = node.n_seqs if node.n_seqs is not None else w.B * w.K
         mult = 1.0 if node.role is Role.INFERENCE else (4.0 if self.activation_checkpointing else 3.0)
         if hw.attention_flops_eff < 1.0:

@@ -63,6 +63,10 @@ class Hardware:
     gen_max_concurrency: float = 0.0           # generator slots: rows decoding at once per replica (0 = whole batch)
     gen_kv_budget_bytes: float = 0.0           # paged KV pool per GPU; caps the concurrency by the mean context (0 = no cap)
     decode_step_overhead_s: float = 0.0        # per decode step: graph launch, sampling, bookkeeping
+    expected_lengths: float = 0.0              # > 0: unsplit vertices are priced with the workload's length quantiles
+    #                                            (rows stop at their own length) instead of every row running to the cap
+    gen_shared_prompt_cost: float = 1.0        # < 1: the K samples of a prompt share its KV pages; a shared prompt token
+    #                                            costs this fraction of a private one per decode step, prefill runs once per prompt
 
     @staticmethod
     def _span(allocs: Iterable[Allocation]) -> Tuple[int, int]:

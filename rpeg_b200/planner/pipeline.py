@@ -45,7 +45,8 @@ _HW_OPTIONAL = ("gemm_m_half", "gemm_k_half", "decode_bw_eff", "non_gemm_constan
                 "non_gemm_batch_cal", "op_generation_scale", "op_inference_scale", "op_training_scale",
                 "activation_comm_overhead_s", "weight_comm_scale", "reshard_scale", "fabric", "fused_overlap",
                 "ffn_matrices", "sustained_flops_fraction", "attention_flops_eff", "elementwise_s_per_token_layer",
-                "gen_max_concurrency", "gen_kv_budget_bytes", "decode_step_overhead_s")
+                "gen_max_concurrency", "gen_kv_budget_bytes", "decode_step_overhead_s", "expected_lengths",
+                "gen_shared_prompt_cost")
 
 
 def make_yaml_loader():

@@ -139,8 +139,15 @@ class EngineOperationHandler:
         prompts = self._prompts(step).to(self.device)
         rep = prompts.repeat_interleave(w.samples_per_prompt, dim=0).contiguous()
         a = self.run.algorithm
+        forced = None
+        if self.run.data.synthetic_response_lengths == "quantiles" and w.gen_quantiles:
+            from .data import quantile_lengths
+            rows = w.batch_size * w.samples_per_prompt                 # drawn for the global batch, cut like the prompts
+            all_lens = quantile_lengths(rows, w.quantile_tuples(), seed=self.run.data.data_seed * 1000003 + step)
+            sl = self._local(w.batch_size)
+            forced = all_lens[sl.start * w.samples_per_prompt:sl.stop * w.samples_per_prompt]
         gen = tr.gen.generate(rep, w.generation_length, temperature=a.temperature, greedy=a.greedy, seed=a.seed + 100003 * step,
-                              group_size=w.samples_per_prompt, top_k=a.top_k, top_p=a.top_p)
+                              group_size=w.samples_per_prompt, top_k=a.top_k, top_p=a.top_p, forced_lens=forced)
         lens = gen.lengths.tolist()
         st["rollout"] = A.Rollout(rep, [w.context_length] * rep.shape[0], gen.tokens, lens, gen.logprobs, gen.response_mask(),
                                   weight_version=self.latest.get("ac_share" if self.shared else "actor", 0))

@@ -429,7 +429,8 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
         "input": {"makespan_s": base_trace.makespan(), "tokens_per_s": base_trace.throughput(w_step, horizon),
                   "utilization": base_trace.utilization()},
         "output": {"makespan_s": opt_trace.makespan(), "tokens_per_s": opt_trace.throughput(w_step, horizon),
-                   "utilization": opt_trace.utilization(), "plan_hash": plan_dict["plan_hash"]},
+                   "utilization": opt_trace.utilization(), "plan_hash": plan_dict["plan_hash"],
+                   "seconds_by_kind": opt_trace.seconds_by_kind()},
         "speedup": base_trace.makespan() / opt_trace.makespan(),
     }
     (root / "metrics" / "analytical_comparison.json").write_text(json.dumps(comparison, indent=2))

@@ -236,6 +236,12 @@ class DataConfig:
     synthetic: bool = True
     data_seed: int = 0
     shuffle: bool = False
+    # "cap": synthetic rows generate until EOS or the length cap (random weights: the cap); "quantiles": every row is
+    # ended at a length drawn from workload.gen_quantiles, the distribution the planner assumes
+    synthetic_response_lengths: str = "cap"
+
+    def validate(self):
+        _choice(self.synthetic_response_lengths, ("cap", "quantiles"), "data.synthetic_response_lengths")
 
 
 @dataclass

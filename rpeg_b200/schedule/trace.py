@@ -25,6 +25,15 @@ class Trace:
     def throughput(self, W_step: float, K: int) -> float:
         return K * W_step / self.makespan()
 
+    def seconds_by_kind(self) -> Dict[str, float]:
+        """Scheduled duration summed per operator role (``GEN``, ``INF``, ``TRAIN``) and per transfer kind
+        (``comm``, ``reshard``): what a measured trace's per-class totals are compared with."""
+        out: Dict[str, float] = defaultdict(float)
+        for node, s in self.start.items():
+            key = node.role.value if node.kind is ExecNodeType.OP and node.role is not None else node.kind.value
+            out[key] += self.finish[node] - s
+        return dict(out)
+
     def _busy_allocs(self, node: ExecNode) -> Tuple[Allocation, ...]:
         if self.reserved_allocations is not None:
             return self.reserved_allocations[node]

@@ -232,6 +232,43 @@ def test_engine_terms_of_the_cost_model():
     assert step > 0
 
 
+def test_cost_model_with_expected_lengths():
+    """With ``expected_lengths`` set, unsplit vertices are priced on the length quantiles: rows that stop early make
+    generation, inference and training cheaper; shared prompt pages lower generation further; off by default."""
+    import dataclasses
+    wl = dataclasses.replace(WL, gen_quantiles=((0.5, WL.T // 4), (0.9, WL.T // 2), (1.0, WL.T)))
+    r = build_PPO_RPEG(SUITE, wl)
+    plan = ExecutionPlan()
+    for v in r.vertices:
+        plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = Allocation((0, 0, 0), (1, 1, 4)), (4, 1, 1), 1
+    low = lower(r, unroll(r, 1), plan, SUITE, 1, workload=wl).by_id()
+    train, inf, gen = low["t_pi@0"], low["i_ref@0"], low["g_pi@0"]
+    assert gen.n_active is None and inf.n_seqs is None               # colocated plan: not split by the quantiles
+    hw = b200_nvswitch().with_updates(decode_step_overhead_s=1e-4)
+    cap = NodeCostModel(hw, SUITE, wl)
+    lens = NodeCostModel(hw.with_updates(expected_lengths=1.0), SUITE, wl)
+    mean = 0.5 * wl.T / 8 + 0.4 * (wl.T / 4 + wl.T / 2) / 2 + 0.1 * (wl.T / 2 + wl.T) / 2
+    assert lens._mean_len() == pytest.approx(mean) and cap._mean_len() == wl.T
+    assert lens._seq_len(inf) == pytest.approx(wl.S + mean) and cap._seq_len(inf) == wl.S + wl.T
+    for node in (train, inf, gen):
+        assert lens.time(node) < cap.time(node)
+    # the decode loop still runs to the longest row: generation shrinks by less than the token count does
+    assert lens.time(gen) / cap.time(gen) > mean / wl.T * 0.5
+    shared = NodeCostModel(hw.with_updates(expected_lengths=1.0, gen_shared_prompt_cost=0.5), SUITE, wl)
+    if wl.K > 1:
+        assert shared.time(gen) < lens.time(gen)
+    else:
+        assert shared.time(gen) == pytest.approx(lens.time(gen))
+    # a generator with few slots decodes the rows in waves: slower, and never faster than the unlimited one
+    few = NodeCostModel(hw.with_updates(expected_lengths=1.0, gen_max_concurrency=2.0), SUITE, wl)
+    assert few.time(gen) > lens.time(gen)
+    # without quantiles in the workload the switch changes nothing
+    nq = dataclasses.replace(WL, gen_quantiles=None)
+    r2 = build_PPO_RPEG(SUITE, nq)
+    plain = lower(r2, unroll(r2, 1), plan, SUITE, 1, workload=nq).by_id()["g_pi@0"]
+    assert NodeCostModel(hw.with_updates(expected_lengths=1.0), SUITE, nq).time(plain) == pytest.approx(NodeCostModel(hw, SUITE, nq).time(plain))
+
+
 def test_validity_gate():
     r = build_PPO_RPEG(SUITE, WL)
     mm = NodeMemoryModel.from_policy(example_hw(), SUITE, WL, MemoryPolicy(), trainable=frozenset(r.trainable))

@@ -199,6 +199,25 @@ def test_dataset_and_minibatch_indices():
         minibatch_indices(0, 4)
 
 
+def test_quantile_lengths_follow_the_workload_phases():
+    from rpeg_b200.runtime.data import quantile_lengths
+    from rpeg_b200.runtime.errors import RuntimeConfigError
+    from rpeg_b200.runtime.schema import DataConfig, _build
+    q = ((0.5, 128), (0.85, 256), (1.0, 512))
+    lens = quantile_lengths(4000, q, seed=7)
+    assert lens == quantile_lengths(4000, q, seed=7) != quantile_lengths(4000, q, seed=8)
+    assert min(lens) >= 1 and max(lens) <= 512
+    frac = [sum(1 for l in lens if l <= b) / len(lens) for _, b in q]
+    assert frac[0] == pytest.approx(0.5, abs=0.03) and frac[1] == pytest.approx(0.85, abs=0.03) and frac[2] == 1.0
+    mean = 0.5 * 64.5 + 0.35 * 192.5 + 0.15 * 384.5
+    assert sum(lens) / len(lens) == pytest.approx(mean, rel=0.05)
+    assert quantile_lengths(0, q) == []
+    assert _build(DataConfig, {"synthetic_response_lengths": "quantiles"}, "data").synthetic_response_lengths == "quantiles"
+    assert _build(DataConfig, {}, "data").synthetic_response_lengths == "cap"
+    with pytest.raises(RuntimeConfigError):
+        _build(DataConfig, {"synthetic_response_lengths": "short"}, "data")
+
+
 def test_dot_writers_cover_template_unrolled_and_lowered_graphs(tmp_path):
     from rpeg_b200.analytic.models import ModelSpec, ModelSuite
     from rpeg_b200.analytic.workload import Workload
