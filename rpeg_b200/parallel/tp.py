@@ -49,6 +49,10 @@ class RowParallelLinear:
         self.stage = [SymmetricBuffer(max_rows * self.N * 2, self.device, group) for _ in range(2)]   # [world][M/world][N] bf16
         self.counters = [SymmetricBuffer(max(256, max_rows // ROW_BLOCK * 4), self.device, group, zero=True) for _ in range(2)]
         self.out = [SymmetricBuffer(out_rows * self.N * 2, self.device, group) for _ in range(2)]
+        # All-reduce mode: an owner stores its reduced rows into every peer's output, and a rank's kernel ends when ITS
+        # rows are done, not when the peers' rows have landed here. A flag barrier after the kernel (every rank signals
+        # once its own stores are issued and complete) closes that window before the next kernel reads the output.
+        self.pad = SignalPad(self.device, group) if (all_reduce and self.world > 1) else None
         self.epoch = 0
         self._last_m: Optional[int] = None
 
@@ -85,6 +89,11 @@ class RowParallelLinear:
                                  self.stage[b].ptr_array(), self.counters[b].ptr_array(), self.out[b].ptr_array(), self.N, self.rank,
                                  self.world, calls, int(self.all_reduce), K.status_word(self.device).data_ptr(),
                                  torch.cuda.current_stream().cuda_stream), "rpeg_gemm_rs")
+        if self.pad is not None:
+            self.pad.epochs[0] += 1
+            check(lib().rpeg_flag_barrier(self.pad.ptr_array(), self.rank, self.world, 0, self.pad.epochs[0], None, None,
+                                          BARRIER_TIMEOUT_NS, K.status_word(self.device).data_ptr(),
+                                          torch.cuda.current_stream().cuda_stream), "rpeg_flag_barrier")
         rows = M if self.all_reduce else M // self.world
         return self.out[b].tensor(torch.bfloat16, rows * self.N).view(rows, self.N)
 
@@ -103,6 +112,8 @@ class RowParallelLinear:
     def close(self) -> None:
         for b in (*self.stage, *self.counters, *self.out):
             b.close()
+        if self.pad is not None:
+            self.pad.close()
 
 
 class ColumnParallelLinear:
