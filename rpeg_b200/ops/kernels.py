@@ -3,7 +3,8 @@
 Every wrapper validates shapes/dtypes/contiguity on the host, passes raw device pointers plus the
 current CUDA stream to the C ABI in ``csrc/rpeg_kernels.h`` and raises on a non-zero return code.
 Kernels with bounded waits share one per-device status word; ``check_status()`` reads it (this
-synchronises) and raises ``KernelWaitTimeout`` if any wait ran out.
+synchronises) and raises ``KernelWaitTimeout`` if any wait ran out. With ``RPEG_CHECK_ARGS=1`` the wrappers also
+validate the index VALUES held by tensor arguments before the launch (``ops/checked.py``).
 """
 from __future__ import annotations
 
@@ -12,6 +13,7 @@ import math
 
 import torch
 
+from . import checked as _chk
 from ._lib import check, lib
 
 KV_PAGE = 64
@@ -167,6 +169,8 @@ def rope_(buf: torch.Tensor, pos: torch.Tensor, cos_t: torch.Tensor, sin_t: torc
           head_dim: int, backward: bool = False) -> None:
     """Rotate ``nheads`` heads starting at column ``col0`` of the 2-D ``buf`` in place."""
     _req(buf, torch.bfloat16, "buf")
+    if _chk.active():
+        _chk.rope("rpeg_rope", pos, buf.shape[0], cos_t)
     check(lib().rpeg_rope(buf.data_ptr(), pos.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(), buf.shape[0],
                           buf.stride(0), col0, nheads, head_dim, int(backward), _stream()), "rpeg_rope")
 
@@ -214,6 +218,8 @@ def add_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) 
 
 def embed_fwd(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     _req(ids, torch.int32, "ids")
+    if _chk.active():
+        _chk.embed("rpeg_embed_fwd", ids, table.shape[0])
     out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
     check(lib().rpeg_embed_fwd(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(), table.shape[1],
                                _stream()), "rpeg_embed_fwd")
@@ -221,6 +227,8 @@ def embed_fwd(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 
 
 def embed_bwd(ids: torch.Tensor, dout: torch.Tensor, dtable: torch.Tensor) -> None:
+    if _chk.active():
+        _chk.embed("rpeg_embed_bwd", ids, dtable.numel() // dout.shape[1])
     check(lib().rpeg_embed_bwd(ids.data_ptr(), dout.data_ptr(), dtable.data_ptr(), ids.numel(), dout.shape[1],
                                _stream()), "rpeg_embed_bwd")
 
@@ -410,6 +418,8 @@ def rope_kv_append_partials_(parts: Partials, qkv: torch.Tensor, q_col0, k_col0,
                              kcache, vcache, n_heads, n_kv_heads, head_dim) -> None:
     """Sum the partials of a QKV projection, rotate q and k, store q into ``qkv`` (bf16, the attention
     kernel's query input) and k, v into the paged cache."""
+    if _chk.active():
+        _chk.kv_append("rpeg_rope_kv_append_partials", parts.M, seq_id, pos, page_table, kcache, n_kv_heads, head_dim, cos_t)
     check(lib().rpeg_rope_kv_append_partials(parts.buf.data_ptr(), parts.splits, parts.stride, qkv.data_ptr(), qkv.stride(0), q_col0,
                                              k_col0, v_col0, seq_id.data_ptr(), pos.data_ptr(), cos_t.data_ptr(), sin_t.data_ptr(),
                                              page_table.data_ptr(), page_table.stride(0), kcache.data_ptr(), vcache.data_ptr(),
@@ -421,12 +431,16 @@ def scatter_rows_by_index(src: torch.Tensor, global_idx: torch.Tensor, rows_per_
     ``idx % rows_per_rank`` of that rank's symmetric buffer (``dst_ptr_array`` = ctypes ``void*[world]``)."""
     n = src.shape[0]
     row_bytes = src[0].numel() * src.element_size() if n else 0
+    if _chk.active():
+        _chk.global_rows("rpeg_scatter_rows_by_index", global_idx, rows_per_rank, world)
     check(lib().rpeg_scatter_rows_by_index(src.data_ptr(), n, row_bytes, global_idx.data_ptr(), rows_per_rank, dst_ptr_array, world,
                                            _stream()), "rpeg_scatter_rows_by_index")
 
 
 # --------------------------------------------------------------------------- attention
 def kv_append(qkv, k_col0, v_col0, seq_id, pos, page_table, kcache, vcache, n_kv_heads, head_dim) -> None:
+    if _chk.active():
+        _chk.kv_append("rpeg_kv_append", qkv.shape[0], seq_id, pos, page_table, kcache, n_kv_heads, head_dim)
     check(lib().rpeg_kv_append(qkv.data_ptr(), qkv.stride(0), k_col0, v_col0, seq_id.data_ptr(), pos.data_ptr(),
                                page_table.data_ptr(), page_table.stride(0), kcache.data_ptr(), vcache.data_ptr(),
                                qkv.shape[0], n_kv_heads, head_dim, _stream()), "rpeg_kv_append")
@@ -437,6 +451,8 @@ def rope_kv_append_(qkv, q_col0, k_col0, v_col0, seq_id, pos, cos_t, sin_t, page
     """Rotate the query and key heads of ``qkv`` in place and write the rotated keys and the values
     into the paged cache: one launch instead of two rotations and an append."""
     _req(qkv, torch.bfloat16, "qkv")
+    if _chk.active():
+        _chk.kv_append("rpeg_rope_kv_append", qkv.shape[0], seq_id, pos, page_table, kcache, n_kv_heads, head_dim, cos_t)
     check(lib().rpeg_rope_kv_append(qkv.data_ptr(), qkv.stride(0), q_col0, k_col0, v_col0, seq_id.data_ptr(), pos.data_ptr(),
                                     cos_t.data_ptr(), sin_t.data_ptr(), page_table.data_ptr(), page_table.stride(0),
                                     kcache.data_ptr(), vcache.data_ptr(), qkv.shape[0], n_heads, n_kv_heads, head_dim,
@@ -453,6 +469,8 @@ def paged_decode_attn(q, q_col0, kcache, vcache, page_table, seq_lens, n_heads, 
     KV pages in groups (K samples of one prompt); the shared keys are then read once per group (``scratch`` must
     hold ``nsplit + 1`` partials per row and head)."""
     B = q.shape[0]
+    if _chk.active():
+        _chk.paged_attention("rpeg_paged_decode_attn", B, seq_lens, page_table, kcache, n_kv_heads, head_dim)
     out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device) if out is None else out
     if groups is not None:
         group_rows, group_shared, row_key0 = groups
@@ -477,6 +495,8 @@ def flash_attn_fwd(qkv, q_col0, k_col0, v_col0, cu_seqlens, max_seqlen, n_heads,
     """Causal attention over packed sequences. Returns ``(out [T, H*hd] bf16, lse [H, T] fp32)``."""
     _req(qkv, torch.bfloat16, "qkv")
     T = qkv.shape[0]
+    if _chk.active():
+        _chk.packed_sequences("rpeg_flash_attn_fwd", cu_seqlens, T, max_seqlen)
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
     out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     lse = torch.empty((n_heads, T), dtype=torch.float32, device=qkv.device)
@@ -492,6 +512,8 @@ def flash_attn_bwd(qkv, q_col0, k_col0, v_col0, out, dout, lse, cu_seqlens, max_
     """Gradient of ``flash_attn_fwd`` w.r.t. the packed qkv buffer (same column blocks). ``dqkv``
     may be passed in to reuse a buffer; columns outside the three blocks are left untouched."""
     T = qkv.shape[0]
+    if _chk.active():
+        _chk.packed_sequences("rpeg_flash_attn_bwd", cu_seqlens, T, max_seqlen)
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
     if dqkv is None:
         dqkv = torch.empty_like(qkv)
@@ -520,6 +542,8 @@ def decode_advance(sampled, sampled_lp, token, pos, seq_len, active, gen_count, 
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    if _chk.active():
+        _chk.row_indices("rpeg_gather_rows", rows, x.shape[0])
     out = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
     check(lib().rpeg_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), rows.numel(), x.shape[1], _stream()),
           "rpeg_gather_rows")
@@ -527,5 +551,7 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
 
 
 def scatter_rows_(x: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, overwrite: bool = False) -> None:
+    if _chk.active():
+        _chk.row_indices("rpeg_scatter_rows", rows, x.shape[0])
     check(lib().rpeg_scatter_rows(x.data_ptr(), rows.data_ptr(), src.data_ptr(), rows.numel(), x.shape[1],
                                   int(overwrite), _stream()), "rpeg_scatter_rows")

@@ -49,7 +49,19 @@ def main() -> int:
     from ..ops import kernels as K
     from ..ops._lib import check, lib
     from .dp import DPContext
-    from .symm import SymmetricBuffer
+    from .symm import SymmetricBuffer, SymmetricMemoryCorruption, check_canaries
+    guards: list = []
+
+    def guards_intact(where: str) -> None:
+        """Guard bytes around every live symmetric buffer of this rank (a peer's kernel may have written them)."""
+        torch.cuda.synchronize()
+        dist.barrier()
+        try:
+            check_canaries()
+            guards.append(True)
+        except SymmetricMemoryCorruption as exc:
+            print(json.dumps({"rank": rank, "where": where, "error": str(exc)}), file=sys.stderr)
+            guards.append(False)
 
     report = {"world": world}
     stream = lambda: torch.cuda.current_stream().cuda_stream
@@ -112,6 +124,7 @@ def main() -> int:
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     report["weights_identical_after_adam"] = bool((lo == hi).item())
+    guards_intact("fused data-parallel optimizer step")
 
     _progress(rank, "4")
     # 4 two GRPO steps, data parallel
@@ -154,7 +167,7 @@ def main() -> int:
             rs_ok.append(bool(((y - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3).item()))
             y2 = layer.forward_unfused(xsh).float()
             rs_ok.append(bool(((y2 - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3).item()))
-        dist.barrier()
+        guards_intact("gemm + reduce-scatter")
         layer.close()
     report["fused_gemm_reduce_scatter_ok"] = all(rs_ok)
 
@@ -177,7 +190,7 @@ def main() -> int:
         ag_ok.append(bool(((y - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3).item()))
         y2 = col.forward_unfused(x_full[rank * per:(rank + 1) * per].to(dev)).float()
         ag_ok.append(bool(((y2 - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3).item()))
-    dist.barrier()
+    guards_intact("all-gather + gemm")
     col.close()
     report["fused_all_gather_gemm_ok"] = all(ag_ok)
 
@@ -203,7 +216,7 @@ def main() -> int:
         want = shard_state_dict(rcfg, full, dst_l)[rank]
         doffs, _ = piece_offsets(rank_pieces(rcfg, dst_l, rank))
         rs_ok.append(all(torch.equal(ex.dst_buf[o:o + want[k].numel()].cpu().view(want[k].shape), want[k]) for k, o in doffs.items()))
-        dist.barrier()
+        guards_intact("reshard executor")
         ex.close()
     report["reshard_executor_ok"] = all(rs_ok)
 
@@ -227,7 +240,7 @@ def main() -> int:
         torch.cuda.synchronize()
         K.check_status()
         tp_ok.append(bool(((lp_tp - lp_ref).abs().max() < 8e-2).item()))
-    dist.barrier()
+    guards_intact("tensor-parallel forward")
     tp_fwd.close()
     report["tensor_parallel_forward_ok"] = all(tp_ok)
 
@@ -278,7 +291,7 @@ def main() -> int:
         ref_w = whole_t.p[name].float() if tpm.entries[name][0] < tpm.n_replicated else _piece_of(whole_t.p[name].float(), name)
         tpt_ok.append(bool(((tpm.p[name].float() - ref_w).abs().max() < 4e-3).item()))
     report["tensor_parallel_training_ok"] = all(tpt_ok)
-    dist.barrier()
+    guards_intact("tensor-parallel training")
     tpm.close()
 
     _progress(rank, "9")
@@ -389,7 +402,9 @@ def main() -> int:
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     report["async_staleness_ok"] = bool(async_ok) and bool((lo == hi).item())
+    guards_intact("asynchronous GRPO channels")
     eng.close()
+    report["symmetric_guards_intact"] = all(guards)
 
     flags = torch.tensor([float(all(v for k, v in report.items() if k not in ("world", "pipeline_p2p_calls")))], device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)

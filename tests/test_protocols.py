@@ -62,3 +62,105 @@ def test_staleness_slot_count(tau):
         progs, init = pc.staleness_programs(tau, 6 + tau, slots=tau)
         r = pc.explore("too few", progs, init)
         assert not r.ok and "being overwritten" in r.finding.message
+
+
+def test_guard_bytes_around_symmetric_buffers_catch_overruns(monkeypatch):
+    """The allocator's canary logic, on host memory standing in for device memory: writes inside the buffer leave
+    the guards alone; one byte past either end is reported with its side and offset."""
+    import ctypes
+
+    import torch
+
+    from rpeg_b200.parallel import symm
+
+    keep = {}
+
+    class FakeLib:
+        def rpeg_symm_alloc(self, nbytes, out):
+            buf = (ctypes.c_ubyte * (int(nbytes) + 256))()                # cudaMalloc returns 256-byte aligned memory
+            addr = (ctypes.addressof(buf) + 255) // 256 * 256
+            keep[addr] = buf
+            out._obj.value = addr
+            return 0
+
+        def rpeg_symm_free(self, ptr):
+            keep.pop(int(ptr))
+            return 0
+
+    monkeypatch.setattr(symm, "lib", lambda: FakeLib())
+    monkeypatch.setattr(symm, "wrap_device_memory",
+                        lambda ptr, n, dev: torch.frombuffer((ctypes.c_ubyte * n).from_address(ptr), dtype=torch.uint8))
+    buf = symm.SymmetricBuffer(1000, "cpu", zero=True)
+    assert buf.nbytes == 1024 and buf.ptr % 256 == 0 and buf.ptr == buf.peer_ptrs[0]
+    assert buf.bytes_view.data_ptr() == buf.ptr and int(buf.bytes_view.sum()) == 0
+    buf.tensor(torch.float32)[:] = 1.0                                   # the whole usable range
+    assert symm.check_canaries() >= 1 and buf.corrupted_guards() == []
+    raw = (ctypes.c_ubyte * (buf.nbytes + 2 * symm.GUARD)).from_address(buf.ptr - symm.GUARD)
+    raw[symm.GUARD + buf.nbytes + 3] = 0                                 # 4th byte past the end
+    assert buf.corrupted_guards() == ["back+3"]
+    with pytest.raises(symm.SymmetricMemoryCorruption, match=r"back\+3"):
+        symm.check_canaries()
+    raw[symm.GUARD + buf.nbytes + 3] = symm.CANARY
+    raw[symm.GUARD - 1] = 7                                              # last byte before the start
+    assert buf.corrupted_guards() == [f"front+{symm.GUARD - 1}"]
+    raw[symm.GUARD - 1] = symm.CANARY
+    buf.close()
+    assert not keep and buf.ptr == 0 and buf.corrupted_guards() == []
+    symm.check_canaries()
+
+
+def test_checked_mode_validators_name_the_offending_index():
+    """``ops/checked.py`` on CPU tensors: in-range arguments pass, every kind of stray index is reported with the
+    kernel, the argument, the value and the allowed range."""
+    import torch
+
+    from rpeg_b200.ops import checked as C
+
+    E = C.KernelArgumentError
+    C.embed("k", torch.tensor([0, 5, 99], dtype=torch.int32), 100)
+    with pytest.raises(E, match=r"k: ids\[1\] = 100 outside \[0, 100\)"):
+        C.embed("k", torch.tensor([0, 100], dtype=torch.int32), 100)
+    with pytest.raises(E, match=r"ids\[0\] = -1"):
+        C.embed("k", torch.tensor([-1, 3], dtype=torch.int32), 100)
+    cos = torch.zeros(128, 64)
+    C.rope("k", torch.tensor([0, 127], dtype=torch.int32), 2, cos)
+    with pytest.raises(E, match="pos"):
+        C.rope("k", torch.tensor([0, 128], dtype=torch.int32), 2, cos)
+    with pytest.raises(E, match="reads 3"):
+        C.rope("k", torch.tensor([0, 1], dtype=torch.int32), 3, cos)
+    # paged KV: pool of 6 pages (2 KV heads, head dim 128), 3 sequences x 4 pages
+    kc = torch.zeros(6 * 2 * 64 * 128, dtype=torch.bfloat16)
+    table = torch.tensor([[0, 1, 2, 3], [4, 5, 9, 9], [0, 0, 0, 0]], dtype=torch.int32)       # 9 = never used
+    assert C.pool_pages(kc, 2, 128) == 6
+    seq, pos = torch.tensor([0, 1, 1], dtype=torch.int32), torch.tensor([255, 0, 127], dtype=torch.int32)
+    C.kv_append("k", 3, seq, pos, table, kc, 2, 128, torch.zeros(256, 64))
+    with pytest.raises(E, match=r"page_table\[seq_id, pos // 64\]\[2\] = 9 outside \[0, 6\)"):
+        C.kv_append("k", 3, seq, torch.tensor([255, 0, 128], dtype=torch.int32), table, kc, 2, 128)
+    with pytest.raises(E, match="seq_id"):
+        C.kv_append("k", 3, torch.tensor([0, 1, 3], dtype=torch.int32), pos, table, kc, 2, 128)
+    with pytest.raises(E, match=r"pos\[0\] = 256 outside \[0, 256\)"):
+        C.kv_append("k", 3, seq, torch.tensor([256, 0, 0], dtype=torch.int32), table, kc, 2, 128)
+    with pytest.raises(E, match="rotary"):
+        C.kv_append("k", 3, seq, pos, table, kc, 2, 128, torch.zeros(200, 64))
+    C.kv_append("k", 2, seq, torch.tensor([255, 0, 999], dtype=torch.int32), table, kc, 2, 128)   # only the first 2 tokens count
+    C.paged_attention("k", 3, torch.tensor([256, 128, 0], dtype=torch.int32), table, kc, 2, 128)
+    with pytest.raises(E, match="pages in use"):
+        C.paged_attention("k", 2, torch.tensor([256, 129], dtype=torch.int32), table, kc, 2, 128)  # reaches the stale entry
+    with pytest.raises(E, match="seq_lens"):
+        C.paged_attention("k", 1, torch.tensor([257], dtype=torch.int32), table, kc, 2, 128)
+    with pytest.raises(E, match="4 rows"):
+        C.paged_attention("k", 4, torch.tensor([1, 1, 1, 1], dtype=torch.int32), table, kc, 2, 128)
+    C.packed_sequences("k", torch.tensor([0, 3, 3, 10], dtype=torch.int32), 10, 7)
+    for cu, n, mx in (([1, 3, 10], 10, 9), ([0, 5, 4, 10], 10, 9), ([0, 3, 9], 10, 9), ([0, 3, 10], 10, 6), ([0], 0, 1)):
+        with pytest.raises(E):
+            C.packed_sequences("k", torch.tensor(cu, dtype=torch.int32), n, mx)
+    C.global_rows("k", torch.tensor([0, 7], dtype=torch.int64), 4, 2)
+    with pytest.raises(E, match=r"global_idx\[1\] = 8"):
+        C.global_rows("k", torch.tensor([0, 8], dtype=torch.int64), 4, 2)
+    C.row_indices("k", torch.tensor([], dtype=torch.int32), 0)
+    prev = C.set_enabled(True)
+    try:
+        assert C.active()                      # no capture is running on a machine without a GPU
+    finally:
+        C.set_enabled(prev)
+    assert C.active() == prev
