@@ -6,8 +6,8 @@ Checks Python packages, the CUDA toolchain, the in-tree kernel library (present,
 C ABI), the GPUs (count, name, memory, compute capability 10.x, peer access between every pair) and,
 with ``--config``, that the node has the GPUs and the memory the run file plans for. Read-only: no
 GPU setting is touched. Every check yields ``{name, ok, detail}``; exit code 0 only if all required
-checks pass. Reference: RPEG/runtime/environment_check.py:80-189 and the per-node GPU health part of
-RPEG/runtime/slurm_preflight.py:63-275 (its Slurm contract has no counterpart: one node, no scheduler).
+checks pass. Reference: RPEG/runtime/environment_check.py:80-189. The per-node health line and the
+cluster contract of a Slurm allocation are in ``runtime/slurm_preflight.py``.
 """
 from __future__ import annotations
 

@@ -78,7 +78,9 @@ def job_hardware(cfg: dict, base_dir: Optional[Path] = None) -> Hardware:
     """Three forms: ``preset: b200_nvswitch`` (measured B200 numbers, fields may be overridden), flat
     alpha/beta keys, or ``network: {intra_node, intra_rack, inter_rack}: {latency, bandwidth}``. ``file: hw.yaml``
     (a ``calibrate.py`` output or a ``cost_calibration`` fragment, relative to the job file) is laid under the keys
-    written in the job file itself, so a job can be planned with this machine's measured constants."""
+    written in the job file itself, so a job can be planned with this machine's measured constants.
+    ``preflight: preflight.jsonl`` (the per-node lines of ``runtime.slurm_preflight``) sets ``memory_per_gpu`` to the
+    smallest GPU found unless the job file gives it."""
     hw = dict(cfg.get("hardware") or {})
     names = set(Hardware.field_names())
     if hw.get("file"):
@@ -89,6 +91,17 @@ def job_hardware(cfg: dict, base_dir: Optional[Path] = None) -> Hardware:
             raise RuntimeConfigError(f"[hardware] file {path} does not exist")
         measured = load_mapping(path) or {}
         hw = {**{k: v for k, v in measured.items() if k in names}, **hw}
+    if hw.get("preflight") and "memory_per_gpu" not in hw and "memory_per_gpu_bytes" not in hw:
+        # lines written by runtime.slurm_preflight on every node: plan with the smallest GPU that was actually found
+        from .slurm_preflight import hardware_from_preflight, read_rows
+        path = Path(str(hw["preflight"]))
+        if not path.is_absolute() and base_dir is not None:
+            path = Path(base_dir) / path
+        if not path.exists():
+            raise RuntimeConfigError(f"[hardware] preflight file {path} does not exist")
+        ds = cfg.get("device_space") or {}
+        nodes = int(ds.get("racks", 1)) * int(ds.get("nodes_per_rack", 1))
+        hw["memory_per_gpu"] = float(hardware_from_preflight(read_rows(path), expected_nodes=nodes)[1])
     extra = {k: (hw[k] if k == "fabric" else float(hw[k])) for k in hw if k in names}
     if "memory_per_gpu_bytes" in hw and "memory_per_gpu" not in hw:
         extra["memory_per_gpu"] = float(hw["memory_per_gpu_bytes"])
@@ -342,12 +355,23 @@ def sbatch_script(run_file: Path, space: DeviceSpace, cfg: dict) -> str:
     lines += ["", "set -euo pipefail",
               'MASTER_ADDR=$(scontrol show hostnames "$SLURM_JOB_NODELIST" | head -n 1)',
               "export MASTER_ADDR MASTER_PORT=${MASTER_PORT:-29511}",
+              *_preflight_lines(run_file, space, nodes, sl),
               f"srun --ntasks-per-node=1 python -m torch.distributed.run --nnodes={nodes} --nproc-per-node {space.G} \\",
               '     --node-rank "$SLURM_NODEID" --master-addr "$MASTER_ADDR" --master-port "$MASTER_PORT" \\',
               f"     -m rpeg_b200.runtime.run --config {run_file}", ""]
     if nodes > 1:
         lines.insert(7, "# the engine backend executes plans of ONE NVSwitch node; multi-node plans run with the metadata backend only")
     return "\n".join(lines)
+
+
+def _preflight_lines(run_file: Path, space: DeviceSpace, nodes: int, sl: dict) -> List[str]:
+    """GPU health of every node and the cluster contract, before the ranks start (``slurm.preflight: false`` drops it)."""
+    if not sl.get("preflight", True):
+        return []
+    d = run_file.parent
+    return [f"srun --ntasks-per-node=1 python -m rpeg_b200.runtime.slurm_preflight --expected-gpus {space.G} > {d}/preflight.jsonl",
+            f"python -m rpeg_b200.runtime.slurm_preflight --contract-from {d}/preflight.jsonl --contract-output {d}/cluster_contract.json "
+            f"--expected-nodes {nodes}" + (" --strict" if sl.get("preflight_strict", False) else "")]
 
 
 # ------------------------------------------------------------------------------ driver
@@ -427,10 +451,11 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
         "schema_version": COMPARISON_SCHEMA, "run_id": run_id, "algorithm": algorithm, "horizon": horizon,
         "search_wall_s": search_s, "evaluations": sum(r.evaluations for r in reports),
         "input": {"makespan_s": base_trace.makespan(), "tokens_per_s": base_trace.throughput(w_step, horizon),
-                  "utilization": base_trace.utilization()},
+                  "utilization": base_trace.utilization(), "seconds_by_kind": base_trace.seconds_by_kind(),
+                  "seconds_by_vertex": base_trace.seconds_by_vertex()},
         "output": {"makespan_s": opt_trace.makespan(), "tokens_per_s": opt_trace.throughput(w_step, horizon),
                    "utilization": opt_trace.utilization(), "plan_hash": plan_dict["plan_hash"],
-                   "seconds_by_kind": opt_trace.seconds_by_kind()},
+                   "seconds_by_kind": opt_trace.seconds_by_kind(), "seconds_by_vertex": opt_trace.seconds_by_vertex()},
         "speedup": base_trace.makespan() / opt_trace.makespan(),
     }
     (root / "metrics" / "analytical_comparison.json").write_text(json.dumps(comparison, indent=2))

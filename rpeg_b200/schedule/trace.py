@@ -34,6 +34,15 @@ class Trace:
             out[key] += self.finish[node] - s
         return dict(out)
 
+    def seconds_by_vertex(self) -> Dict[str, float]:
+        """Scheduled duration of the operator nodes summed per template vertex (``g_pi``, ``i_ref``, ``t_pi``, ...)
+        over all logical steps and quantile phases."""
+        out: Dict[str, float] = defaultdict(float)
+        for node, s in self.start.items():
+            if node.kind is ExecNodeType.OP:
+                out[node.template_id or node.id] += self.finish[node] - s
+        return dict(out)
+
     def _busy_allocs(self, node: ExecNode) -> Tuple[Allocation, ...]:
         if self.reserved_allocations is not None:
             return self.reserved_allocations[node]

@@ -226,3 +226,51 @@ def chart_svg(series: Sequence[Tuple[str, Sequence[Tuple[float, float]]]], path:
         with open(path, "w") as fh:
             fh.write(text)
     return text
+
+
+def bars_svg(groups: Sequence[Tuple[str, Sequence[Tuple[str, float]]]], path: str, *, title: str = "", ylabel: str = "",
+             width: int = 760, height: int = 420) -> str:
+    """Grouped bars as SVG: ``groups`` = [(group label, [(series name, value), ...])]; a series keeps its colour
+    across groups (operator-by-operator comparisons of plans, phase times at several GPU counts)."""
+    names: List[str] = []
+    for _, items in groups:
+        for name, _ in items:
+            if name not in names:
+                names.append(name)
+    vals = [v for _, items in groups for _, v in items]
+    if not vals:
+        raise ValueError("nothing to plot")
+    top_v = max(max(vals), 1e-12)
+    left, top, right, bottom = 70, 40, 20, 60
+    pw, ph = width - left - right, height - top - bottom
+    colours = ["#8c8c8c", "#4c78a8", "#e45756", "#54a24b", "#f58518", "#b279a2", "#72b7b2", "#9d755d"]
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" font-family="monospace" font-size="11">',
+           f'<rect width="{width}" height="{height}" fill="white"/>', f'<text x="{left}" y="20" font-size="13">{escape(title)}</text>',
+           f'<text x="14" y="{top + ph / 2:.0f}" transform="rotate(-90 14 {top + ph / 2:.0f})" text-anchor="middle">{escape(ylabel)}</text>']
+    for k in range(6):
+        y = top + ph - ph * k / 5
+        out.append(f'<line x1="{left}" y1="{y:.1f}" x2="{width - right}" y2="{y:.1f}" stroke="#eee"/>')
+        out.append(f'<text x="{left - 6}" y="{y + 4:.1f}" text-anchor="end">{top_v * k / 5:.3g}</text>')
+    gw = pw / max(1, len(groups))
+    bw = gw * 0.8 / max(1, len(names))
+    for gi, (label, items) in enumerate(groups):
+        gx = left + gi * gw + gw * 0.1
+        have = dict(items)
+        for si, name in enumerate(names):
+            if name not in have:
+                continue
+            h = ph * have[name] / top_v
+            out.append(f'<rect x="{gx + si * bw:.1f}" y="{top + ph - h:.1f}" width="{bw * 0.92:.1f}" height="{h:.1f}" fill="{colours[si % len(colours)]}">'
+                       f'<title>{escape(label)} / {escape(name)}: {have[name]:.4g}</title></rect>')
+        for li, part in enumerate(str(label).split("\n")):
+            out.append(f'<text x="{gx + gw * 0.4:.1f}" y="{top + ph + 14 + 12 * li}" text-anchor="middle">{escape(part)}</text>')
+    for si, name in enumerate(names):
+        out.append(f'<rect x="{left + 8 + 150 * si}" y="{height - 16}" width="9" height="9" fill="{colours[si % len(colours)]}"/>')
+        out.append(f'<text x="{left + 22 + 150 * si}" y="{height - 7}">{escape(name)}</text>')
+    out.append(f'<rect x="{left}" y="{top}" width="{pw}" height="{ph}" fill="none" stroke="#888"/>')
+    out.append("</svg>")
+    text = "\n".join(out)
+    if path:
+        with open(path, "w") as fh:
+            fh.write(text)
+    return text

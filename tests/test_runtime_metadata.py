@@ -126,6 +126,8 @@ def test_job_planner_emits_a_compilable_pair(tmp_path):
     out = res["out_dir"]
     sb = (out / "submit.sbatch").read_text()
     assert "#SBATCH --nodes=1" in sb and "#SBATCH --gpus-per-node=8" in sb and "srun" in sb and "rpeg_b200.runtime.run" in sb
+    assert sb.index("slurm_preflight --expected-gpus 8") < sb.index("--contract-from") < sb.index("rpeg_b200.runtime.run")
+    assert (out / "metrics/analytical_comparison.json").exists()
     for f in ("baseline_plan.yaml", "optimized_plan.yaml", "run.yaml", "plots/optimizer_input.gantt.svg",
               "plots/optimizer_output.gantt.svg", "metrics/analytical_comparison.json", "submit.sh"):
         assert (out / f).exists(), f

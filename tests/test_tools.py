@@ -4,6 +4,7 @@ import json
 import os
 import subprocess
 import sys
+from pathlib import Path
 
 import pytest
 
@@ -285,3 +286,104 @@ def test_scaling_sweep_script_writes_csv_and_chart(tmp_path):
     rows = (tmp_path / "s.csv").read_text().strip().splitlines()
     assert len(rows) == 2 and "optimized_tokens_per_s" in rows[0] and rows[1].startswith("16gpu_t128_sync.yaml,16,")
     assert (tmp_path / "s.svg").read_text().startswith("<svg")
+
+
+def test_slurm_preflight_node_health_and_cluster_contract(tmp_path, capsys):
+    """Node health from injected probes (no GPU needed) and the contract over several nodes' lines."""
+    from rpeg_b200.runtime import slurm_preflight as sp
+    from rpeg_b200.runtime.errors import RuntimeConfigError
+
+    def torch_probe(n=8, mem=183 * 2 ** 30, cap="10.0", name="NVIDIA B200"):
+        return lambda: {"available": n > 0, "count": n, "names": [name] * n, "memory": [mem] * n, "capabilities": [cap] * n,
+                        "torch_version": "2.11.0", "cuda_version": "12.8", "nccl_version": "2.28.9"}
+
+    def smi(n=8, driver="580.159"):
+        return lambda: {"count": n, "driver": driver}
+
+    good = sp.check_node(8, torch_probe=torch_probe(), smi_probe=smi(), nic_probe=lambda: ["mlx5_0:28.39"], hostname="n0",
+                         clock_ns=lambda: 1_000_000_000, min_memory_bytes=150 * 2 ** 30, require_capability="10.0")
+    assert good.ok and good.message == "ok" and good.to_dict()["min_total_memory_bytes"] == 183 * 2 ** 30
+    few = sp.check_node(8, torch_probe=torch_probe(7), smi_probe=smi(8), nic_probe=list, hostname="n1")
+    assert not few.ok and "expected 8" in few.message and "nvidia-smi lists 8" in few.message
+    old = sp.check_node(8, torch_probe=torch_probe(cap="9.0"), smi_probe=smi(), nic_probe=list, hostname="n2", require_capability="10.0")
+    assert not old.ok and "compute capability 10.0" in old.message
+    small = sp.check_node(8, torch_probe=torch_probe(mem=80 * 2 ** 30), smi_probe=smi(), nic_probe=list, min_memory_bytes=150 * 2 ** 30)
+    assert not small.ok and "less than" in small.message
+    none = sp.check_node(8, torch_probe=torch_probe(0), smi_probe=lambda: {"count": None, "driver": None}, nic_probe=list)
+    assert not none.ok and "no CUDA device" in none.message
+    # the real probes run anywhere and never raise
+    here = sp.check_node(0, nic_probe=lambda: sp.probe_nic_firmware(str(tmp_path / "absent")))
+    assert here.hostname and here.torch_version and isinstance(here.to_dict()["wall_time_ns"], int)
+
+    rows = [sp.check_node(8, torch_probe=torch_probe(), smi_probe=smi(), nic_probe=lambda: ["mlx5_0:28.39"], hostname=f"n{i}",
+                          clock_ns=lambda i=i: 10 ** 9 + i * 10 ** 8).to_dict() for i in range(3)]
+    c = sp.cluster_contract(rows, expected_nodes=3)
+    assert c["schema_version"] == "rpeg.cluster_contract.v1" and c["performance_comparable"] and c["nodes"] == 3
+    assert c["clock_skew_s"] == pytest.approx(0.2) and c["gpus_per_node"] == [8] and c["min_gpu_memory_bytes"] == 183 * 2 ** 30
+    odd = dict(rows[2], driver_version="570.00", wall_time_ns=rows[2]["wall_time_ns"] + 3 * 10 ** 9, nic_firmware=["mlx5_0:20.1"])
+    c2 = sp.cluster_contract([rows[0], rows[1], odd, few.to_dict()], expected_nodes=3)
+    text = " | ".join(c2["non_comparable_reasons"])
+    assert not c2["performance_comparable"]
+    for piece in ("driver versions", "NIC firmware", "clock skew", "unhealthy nodes: ['n1']", "reported more than once", "expected 3"):
+        assert piece in text, piece
+    assert sp.hardware_from_preflight(rows, expected_nodes=3) == ("NVIDIA B200", 183 * 2 ** 30)
+    with pytest.raises(RuntimeConfigError, match="2 of 3"):
+        sp.hardware_from_preflight(rows[:2], expected_nodes=3)
+    assert sp.hardware_from_preflight(None, expected_nodes=1, explicit_memory_bytes=10, explicit_gpu_type="B200") == ("B200", 10)
+    with pytest.raises(RuntimeConfigError):
+        sp.hardware_from_preflight(None, expected_nodes=1)
+    # CLI: contract from a file of lines; --strict turns "not comparable" into exit code 2
+    lines = tmp_path / "preflight.jsonl"
+    lines.write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    from rpeg_b200.runtime.job_plan import job_hardware
+    job = {"hardware": {"preset": "b200_nvswitch", "preflight": "preflight.jsonl"}, "device_space": {"racks": 1, "nodes_per_rack": 3, "gpus_per_node": 8}}
+    assert job_hardware(job, tmp_path).memory_per_gpu == 183 * 2 ** 30       # the smallest GPU the nodes reported
+    job["hardware"]["memory_per_gpu"] = 1e11
+    assert job_hardware(job, tmp_path).memory_per_gpu == 1e11                 # an explicit value wins
+    assert sp.main(["--contract-from", str(lines), "--contract-output", str(tmp_path / "c.json"), "--expected-nodes", "3", "--strict"]) == 0
+    assert json.loads((tmp_path / "c.json").read_text())["performance_comparable"]
+    lines.write_text(json.dumps(rows[0]) + "\n" + json.dumps(odd) + "\n")
+    assert sp.main(["--contract-from", str(lines), "--strict"]) == 2
+    assert sp.main(["--contract-from", str(lines)]) == 0
+    lines.write_text("not json\n")
+    assert sp.main(["--contract-from", str(lines)]) == 2
+    capsys.readouterr()
+
+
+def test_operator_breakdown_and_strong_scaling_scripts(tmp_path, capsys):
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent / "experiments"))
+    import plot_operator_breakdown as pob
+    import plot_strong_scaling as pss
+    rep = {"run_id": "demo", "input": {"seconds_by_vertex": {"g_pi": 4.0, "i_ref": 0.5, "t_pi": 2.0}, "seconds_by_kind": {"GEN": 4.0, "INF": 0.5, "TRAIN": 2.0}},
+           "output": {"seconds_by_vertex": {"g_pi": 3.0, "i_ref": 0.5, "t_pi": 1.5, "x_new": 0.1}, "seconds_by_kind": {"GEN": 3.0, "INF": 0.5, "TRAIN": 1.5, "comm": 0.2}}}
+    a = tmp_path / "a.json"
+    a.write_text(json.dumps(rep))
+    trace = tmp_path / "run.jsonl"
+    trace.write_text("\n".join(json.dumps(e) for e in [
+        {"event": "start", "node_id": "g_pi@0"}, {"event": "finish", "node_id": "g_pi@0", "counters": {"duration_s": 3.2}},
+        {"event": "finish", "node_id": "g_pi@1", "counters": {"duration_s": 3.3}}, {"event": "finish", "node_id": "t_pi@0", "duration_s": 1.4}]) + "\n")
+    groups = pob.breakdown_groups([str(a)], "vertex", str(trace))
+    assert [g[0] for g in groups] == ["actor\ngen.", "ref.\ninf.", "actor\ntrain", "x_new"]
+    assert groups[0][1] == [("input plan", 4.0), ("optimized plan", 3.0), ("measured", 6.5)]
+    assert groups[2][1][2] == ("measured", 1.4)
+    assert pob.main([str(a), "--output", str(tmp_path / "b.svg")]) == 0 and "<rect" in (tmp_path / "b.svg").read_text()
+    assert pob.main([str(a), str(a), "--by", "kind", "--output", str(tmp_path / "k.svg")]) == 0
+    assert len(pob.breakdown_groups([str(a), str(a)], "kind")) == 4
+    old = tmp_path / "old.json"
+    old.write_text(json.dumps({"input": {}, "output": {}}))
+    with pytest.raises(SystemExit):
+        pob.breakdown_groups([str(old)])
+    # strong scaling: JSON lines mixed with log text, a JSON list, two series
+    (tmp_path / "n.log").write_text('warm-up\n{"n_gpus": 1, "value": 6.4, "impl": "ours"}\n{"n_gpus": 8, "value": 19.2, "impl": "ours"}\nnot json {\n')
+    (tmp_path / "r.json").write_text(json.dumps([{"n_gpus": 1, "value": 3.0, "impl": "reference"}, {"n_gpus": 8, "value": 12.0, "impl": "reference"},
+                                                 {"impl": "reference", "unavailable": "x"}]))
+    pts = pss.read_points([str(tmp_path / "n.log"), str(tmp_path / "r.json")], series_key="impl")
+    assert pts == {"ours": [(1, 6.4), (8, 19.2)], "reference": [(1, 3.0), (8, 12.0)]}
+    rows = pss.scaling_table(pts["ours"])
+    assert rows[1]["speedup"] == pytest.approx(3.0) and rows[1]["efficiency"] == pytest.approx(0.375)
+    assert pss.scaling_table([(2, 10.0), (4, 6.0)], higher_is_better=False)[1]["efficiency"] == pytest.approx(10 / 6 / 2)
+    assert pss.main([str(tmp_path / "n.log"), str(tmp_path / "r.json"), "--series-key", "impl", "--output", str(tmp_path / "s.svg")]) == 0
+    assert "ideal" in (tmp_path / "s.svg").read_text()
+    (tmp_path / "empty.json").write_text("")
+    assert pss.main([str(tmp_path / "empty.json")]) == 2
+    capsys.readouterr()
