@@ -387,3 +387,18 @@ def test_operator_breakdown_and_strong_scaling_scripts(tmp_path, capsys):
     (tmp_path / "empty.json").write_text("")
     assert pss.main([str(tmp_path / "empty.json")]) == 2
     capsys.readouterr()
+
+
+def test_engine_validate_cli_without_a_gpu(capsys):
+    """On a machine without a GPU the smoke worker says so and exits 2; its model arguments are validated."""
+    import torch
+
+    from rpeg_b200.runtime import engine_validate as ev
+    args = ev.build_parser().parse_args(["--layers", "4", "--hidden", "1024", "--ffn", "2816", "--kv-heads", "2"])
+    cfg = ev.model_config(args)
+    assert (cfg.n_layers, cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff) == (4, 1024, 8, 2, 2816)
+    with pytest.raises(SystemExit):
+        ev.model_config(ev.build_parser().parse_args(["--hidden", "200"]))
+    if not torch.cuda.is_available():
+        assert ev.main(["--json"]) == 2
+        assert json.loads(capsys.readouterr().out)["error"] == "no CUDA device visible"

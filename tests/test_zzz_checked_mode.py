@@ -55,3 +55,15 @@ def test_stray_indices_are_refused_before_the_launch(cuda_device, checked_mode):
     K.embed_fwd(torch.tensor([1, cfg.vocab - 1], dtype=torch.int32, device=cuda_device), table)
     K.gather_rows(x, torch.tensor([0, 3], dtype=torch.int32, device=cuda_device))
     torch.cuda.synchronize()
+
+
+def test_engine_smoke_worker_passes_on_one_gpu(cuda_device, tmp_path, capsys):
+    """``runtime.engine_validate``: training step, two-token PPO exercise and checkpoint round trip, as a user runs it."""
+    import json
+
+    from rpeg_b200.runtime import engine_validate as ev
+    rc = ev.main(["--json", "--ppo-exercise", "--checkpoint-dir", str(tmp_path)])
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["schema_version"] == "rpeg.engine_validate.v1"
+    assert rc == 0 and rep["ok"], [c for c in rep["checks"] if not c["ok"]]
+    assert [c["name"] for c in rep["checks"]] == ["build", "train_step", "ppo_exercise", "checkpoint", "device_status"]
