@@ -24,12 +24,16 @@ from ..ops import kernels as K
 
 class AdamW:
     def __init__(self, model: LlamaModel, *, lr: float = 1e-6, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 0.0, max_grad_norm: float = 1.0, dp=None):
+                 weight_decay: float = 0.0, max_grad_norm: float = 1.0, dp=None, norm_group=None):
+        """``norm_group``: the model is ONE PART of a larger one (a pipeline stage); the squared gradient norms of the
+        parts are summed over this process group before the clip coefficient is formed, so all parts are clipped by
+        the norm of the whole model."""
         if model.g is None:
             raise ValueError("optimizer needs a trainable model")
         self.model, self.lr, self.betas, self.eps, self.wd = model, lr, betas, eps, weight_decay
         self.max_grad_norm = max_grad_norm
         self.dp = dp
+        self.norm_group = norm_group
         self.step_count = 0
         total = model.layout.total
         if dp is None or dp.world == 1:
@@ -63,6 +67,9 @@ class AdamW:
             K.sumsq(m.g, self.sumsq)
             if grad_scale != 1.0:
                 self.sumsq.mul_(grad_scale * grad_scale)
+            if self.norm_group is not None:
+                import torch.distributed as dist
+                dist.all_reduce(self.sumsq, group=self.norm_group)
             K.adamw_(self.master, self.m, self.v, m.g, m.w, lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, wd=self.wd,
                      step=self.step_count, grad_scale=grad_scale, sumsq=self.sumsq, max_norm=self.max_grad_norm)
             return

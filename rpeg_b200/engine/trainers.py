@@ -267,3 +267,153 @@ class PPOTrainer(_Base):
                    wall_s=time.perf_counter() - t0)
         self.last_counters = dict(gen.counters)
         return out
+
+
+class PipelineGRPOTrainer(_Base):
+    """GRPO whose policy update is PIPELINE parallel over all ranks while generation and the reference pass stay data
+    parallel: the plan ``g_pi, i_ref: (dp, pp, tp) = (G, 1, 1)``, ``t_pi: (1, G, 1)``.
+
+    Every rank keeps the whole bf16 policy (``actor``, what the generator and nothing else reads) and a frozen
+    reference copy, but gradients, fp32 master weights and Adam moments only for ITS pipeline stage: the stage model's
+    weights are a view into the whole policy's flat buffer (a stage's parameters are one contiguous range of it), so
+    the optimizer writes the updated stage where the generator will read it. One iteration:
+
+        generate this rank's prompts (K samples each) -> reference log-probs of its rows        data parallel
+        all-gather the rollouts: every stage needs every microbatch                            NCCL all-gather, a few MB
+        group advantages, 1F1B policy step over the global batch (``parallel.pp``)             pipeline parallel
+        Adam on the stage, clipped by the norm of the WHOLE model                              one all-reduce of a scalar
+        layout switch: every stage's range is broadcast into all ranks' whole policy           NCCL broadcast per stage
+
+    Compared with the data-parallel trainer a rank holds 1/G of the gradients and optimizer state without any
+    gradient reduction; the price is the pipeline bubble and the weight broadcast (the reference's in-place layout
+    switch between a training and a generation layout, RPEG/runtime/semantic_worker.py:5503-5872, with Megatron's
+    1F1B schedule for the update, RPEG/runtime/workers/megatron_worker.py:1657,3808)."""
+
+    def __init__(self, cfg: LlamaConfig, *, device="cuda:0", samples_per_prompt: int = 8, max_new: int = 2048,
+                 prompt_len: int = 512, algo: Optional[A.AlgoConfig] = None, lr: float = 1e-6, gen_slots: int = 64,
+                 kv_budget_bytes: float = 40e9, recompute: str = "full", seed: int = 0, eos_id: int = 2,
+                 sync_interval: int = 8, use_graphs: bool = True, group=None):
+        import torch.distributed as dist
+
+        from ..models.llama import ParamLayout
+        from ..parallel.pp import PipelineRunner
+        super().__init__(device, None)
+        if not dist.is_initialized():
+            raise RuntimeError("PipelineGRPOTrainer needs an initialised process group (one rank per stage)")
+        self.group = group
+        self.rank, self.n_stages = dist.get_rank(group), dist.get_world_size(group)
+        if cfg.tie_embeddings:
+            raise ValueError("tied embeddings put one matrix on two stages; not supported by the pipeline trainer")
+        if cfg.n_layers < self.n_stages:
+            raise ValueError(f"{cfg.n_layers} layers cannot fill {self.n_stages} pipeline stages")
+        self.cfg, self.K, self.max_new, self.seed = cfg, samples_per_prompt, max_new, seed
+        self.algo = algo or A.AlgoConfig(kl_coef=0.04)
+        full = ParamLayout(cfg)
+        # (offset, length) of every stage inside the whole model's flat buffer
+        self.spans: List[tuple] = []
+        for s in range(self.n_stages):
+            lay = ParamLayout(cfg, (s, self.n_stages))
+            base = full.entries[next(iter(lay.entries))][0]
+            for name, (off, shape) in lay.entries.items():
+                if full.entries[name] != (base + off, shape):
+                    raise AssertionError(f"stage {s}: {name} is not where the whole model keeps it")
+            self.spans.append((base, lay.total))
+        base, n_stage = self.spans[self.rank]
+        self.full_w = torch.empty(full.total, dtype=torch.bfloat16, device=self.device)
+        self.actor = LlamaModel(cfg, self.device, weights=self.full_w, seed=seed)
+        self.actor.init_weights(seed)                                  # same seed, same weights on every rank
+        self.ref = LlamaModel(cfg, self.device, seed=seed)
+        self.ref.load_flat(self.actor)
+        self.stage = LlamaModel(cfg, self.device, trainable=True, recompute=recompute, stage=(self.rank, self.n_stages),
+                                weights=self.full_w[base:base + n_stage], seed=seed)
+        self.opt = AdamW(self.stage, lr=lr, norm_group=group if group is not None else dist.group.WORLD)
+        self.opt.shard_off = base                                      # where this stage's optimizer state sits in the whole flat space
+        self.runner = PipelineRunner(self.stage, group)
+        self.gen = Generator(self.actor, max_slots=gen_slots, max_seq_len=prompt_len + max_new, kv_budget_bytes=kv_budget_bytes,
+                             eos_id=eos_id, sync_interval=sync_interval, use_graphs=use_graphs)
+        self._scalar = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.published_bytes = 0
+        self.last_counters: Dict[str, float] = {}
+
+    @property
+    def world(self) -> int:
+        return self.n_stages
+
+    def _global_sum(self, value: float) -> float:
+        import torch.distributed as dist
+        self._scalar.fill_(float(value))
+        dist.all_reduce(self._scalar, group=self.group)
+        return float(self._scalar.item())
+
+    def _gather(self, t: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+        t = t.contiguous()
+        out = torch.empty((self.n_stages * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t, group=self.group)
+        return out
+
+    def gather_rollout(self, ro: A.Rollout) -> A.Rollout:
+        """The rollouts of all ranks, in rank order (every rank holds the same number of rows)."""
+        lens = self._gather(torch.tensor(ro.resp_lens, dtype=torch.int32, device=self.device)).tolist()
+        plens = self._gather(torch.tensor(ro.prompt_lens, dtype=torch.int32, device=self.device)).tolist()
+        g = lambda t: None if t is None else self._gather(t)
+        return A.Rollout(g(ro.prompt_ids), plens, g(ro.resp_ids), lens, g(ro.old_logp), g(ro.mask), g(ro.ref_logp), g(ro.values),
+                         g(ro.scores), None, None, ro.weight_version)
+
+    def train_policy(self, ro_global: A.Rollout, denom_tokens: float) -> Dict[str, torch.Tensor]:
+        """One optimizer step on a GLOBAL rollout (the same on every stage): 1F1B forward/backward, Adam on the stage."""
+        self.stage.zero_grad()
+        m = A.policy_train_step(self.stage, ro_global, self.algo, denom_tokens=denom_tokens, pipeline=self.runner)
+        self.opt.step()
+        return m
+
+    def publish(self) -> int:
+        """Layout switch after an update: every stage's range of the whole policy goes to all ranks. Returns the bytes
+        this rank received."""
+        import torch.distributed as dist
+        got = 0
+        for s, (base, n) in enumerate(self.spans):
+            src = dist.get_global_rank(self.group, s) if self.group is not None else s
+            dist.broadcast(self.full_w[base:base + n], src=src, group=self.group)
+            if s != self.rank:
+                got += 2 * n
+        self.published_bytes += got
+        return got
+
+    def step(self, prompts: torch.Tensor, rewards: Optional[torch.Tensor] = None,
+             forced_lens: Optional[torch.Tensor] = None) -> Dict[str, float]:
+        """``prompts [B_local, S]`` and ``rewards [B_local * K]``: THIS rank's share, as for the data-parallel trainer."""
+        t0 = time.perf_counter()
+        self.h2d_bytes = prompts.numel() * prompts.element_size()
+        p_dev = _h2d(prompts, self.device, torch.int32)
+        B, S = p_dev.shape
+        N = B * self.K
+        rep = p_dev.repeat_interleave(self.K, dim=0).contiguous()
+        self._mark("begin")
+        gen = self.gen.generate(rep, self.max_new, temperature=self.algo.temperature, seed=self.seed + 100003 * self.iteration + self.rank,
+                                forced_lens=forced_lens, group_size=self.K)
+        resp_lens = gen.lengths.tolist()
+        self._mark("generate")
+        ro = A.Rollout(rep, [S] * N, gen.tokens, resp_lens, gen.logprobs, gen.response_mask(), weight_version=self.weight_version)
+        if self.algo.kl_coef != 0.0:
+            ro.ref_logp = A.sequence_logprobs(self.ref, ro, self.algo)
+        self._mark("reference")
+        if rewards is None:
+            raise ValueError("PipelineGRPOTrainer.step needs per-sample rewards (the reward model's output)")
+        self.h2d_bytes += rewards.numel() * rewards.element_size()
+        ro.scores = _h2d(rewards, self.device, torch.float32)
+        glob = self.gather_rollout(ro)
+        A.grpo_advantages(glob, self.K)
+        m = self.train_policy(glob, float(glob.n_response_tokens()))
+        self._mark("train")
+        self.publish()
+        self._mark("publish")
+        self.weight_version += 1
+        self.iteration += 1
+        m["grad_norm"] = self.opt.grad_norm()
+        out = self._read(m)
+        out.update(self._phase_ms())
+        out.update(samples=float(N), gen_tokens=float(sum(resp_lens)), train_tokens=float(sum(ro.total_lens())),
+                   wall_s=time.perf_counter() - t0)
+        self.last_counters = dict(gen.counters)
+        return out

@@ -11,9 +11,12 @@ engine call of its vertex on this rank's share of the batch:
   t_pi / t_ac   policy (or shared trunk) update incl. optimizer step     (algorithms.policy_train_step / dpo_train_step)
   t_V           critic update incl. optimizer step                       (algorithms.critic_train_step)
 
-The plan must be data parallel only (every vertex with pp = tp = 1 on all GPUs of the node) and
-synchronous (tau = 0): weights are replicated in symmetric memory and updated in place by the fused
-optimizer, so COMM and RESHARD nodes between vertices move nothing and only report their payload.
+The plan must be synchronous (tau = 0) and of one of two families on all GPUs of the node. Data parallel
+(every vertex pp = tp = 1): weights are replicated in symmetric memory and updated in place by the fused
+optimizer, so COMM and RESHARD nodes between vertices move nothing and only report their payload. Pipeline-trained
+(GRPO; generation and inference data parallel, training vertices pp = G): the update runs 1F1B over all ranks
+(``engine.trainers.PipelineGRPOTrainer``), each rank keeps gradients and optimizer state of its stage only, and the
+layout switch back to the replicated generation copy (a broadcast per stage) runs at the end of the training node.
 Generation is continuously batched, so the quantile phases of a split generation vertex are not
 separate decode loops: the first phase node generates every row, and each phase node *emits* the rows
 whose length falls into its interval (what downstream split inference nodes consume).
@@ -45,18 +48,37 @@ def llama_config_from_run(m, max_pos: int, **kw):
                        rope_theta=m.rope_theta, max_pos=max_pos, **kw)
 
 
-def validate_engine_plan(compiled) -> None:
+def validate_engine_plan(compiled) -> str:
+    """The plan families this backend executes, both on all ``G`` GPUs of the node. Returns the family:
+
+      ``"data_parallel"``    every vertex ``(dp, pp, tp) = (G, 1, 1)``
+      ``"pipeline_train"``   generation / inference vertices ``(G, 1, 1)``, every training vertex ``(1, G, 1)`` (GRPO):
+                             the update runs 1F1B over all ranks as stages, the publication edge is a real layout
+                             switch (stage weights broadcast into the replicated generation copy)"""
+    from ..core.types import Role
     cfg = compiled.config
     g = compiled.device_space.num_devices()
+    train = [v for v in cfg.rpeg.vertices if v.kind.role is Role.TRAINING]
+    piped = g > 1 and bool(train) and all(tuple(cfg.plan.pi[v.id]) == (1, g, 1) for v in train)
     for v in cfg.rpeg.vertices:
         dp, pp, tp = cfg.plan.pi[v.id]
+        if piped and v in train:
+            continue
         if pp != 1 or tp != 1 or dp != g:
-            raise RuntimeConfigError(f"engine backend runs data-parallel plans only: {v.id} has (dp,pp,tp)=({dp},{pp},{tp}) "
-                                     f"on {g} GPU(s); expected ({g},1,1)")
+            raise RuntimeConfigError(f"engine backend runs data-parallel plans, or data-parallel generation with pipeline-parallel "
+                                     f"training: {v.id} has (dp,pp,tp)=({dp},{pp},{tp}) on {g} GPU(s); expected ({g},1,1)"
+                                     + (f" or, for training vertices, (1,{g},1)" if g > 1 else ""))
+    if piped:
+        if compiled.run_config.algorithm.name != "grpo":
+            raise RuntimeConfigError("engine backend: pipeline-parallel training vertices are implemented for GRPO only")
+        layers = compiled.run_config.models["actor"].layers
+        if layers < g:
+            raise RuntimeConfigError(f"engine backend: {layers} layers cannot fill {g} pipeline stages")
     if any(int(t) > 0 for t in cfg.rpeg.tau.values()):
         raise RuntimeConfigError("engine backend runs synchronous plans only (tau = 0): stale serving needs disjoint devices")
     if float(getattr(compiled.run_config.algorithm, "entropy_coef", 0.0) or 0.0) != 0.0:
         raise RuntimeConfigError("engine backend: algorithm.entropy_coef is not implemented (the fused policy loss has no entropy term); set it to 0")
+    return "pipeline_train" if piped else "data_parallel"
 
 
 class EngineOperationHandler:
@@ -64,7 +86,7 @@ class EngineOperationHandler:
         import torch
         import torch.distributed as dist
         from ..engine import algorithms as A
-        validate_engine_plan(compiled)
+        self.family = validate_engine_plan(compiled)
         self.compiled, self.attempt = compiled, attempt
         self.torch, self.A = torch, A
         run = compiled.run_config
@@ -79,8 +101,9 @@ class EngineOperationHandler:
         if self.world > 1:
             if not dist.is_initialized():
                 dist.init_process_group("nccl", device_id=self.device)
-            from ..parallel.dp import DPContext
-            self.dp = DPContext(self.device)
+            if self.family == "data_parallel":
+                from ..parallel.dp import DPContext
+                self.dp = DPContext(self.device)
         a, w, rt, o = run.algorithm, run.workload, run.runtime, run.optimizer_runtime
         self.algo_name = a.name
         self.shared = any(v.id == "g_ac" for v in compiled.config.rpeg.vertices)
@@ -90,7 +113,13 @@ class EngineOperationHandler:
         cfg = llama_config_from_run(run.models["actor"], max_pos)
         from ..engine.trainers import DPOTrainer, GRPOTrainer, PPOTrainer
         common = dict(device=self.device, algo=self.algo, dp=self.dp, recompute=rt.recompute, seed=a.seed)
-        if a.name == "grpo":
+        if self.family == "pipeline_train":
+            from ..engine.trainers import PipelineGRPOTrainer
+            self.trainer = PipelineGRPOTrainer(cfg, device=self.device, algo=self.algo, recompute=rt.recompute, seed=a.seed,
+                                               samples_per_prompt=w.samples_per_prompt, max_new=w.generation_length,
+                                               prompt_len=w.context_length, lr=o.learning_rate_actor, gen_slots=rt.gen_slots,
+                                               eos_id=run.tokenizer.eos_token_id, use_graphs=rt.use_cuda_graphs)
+        elif a.name == "grpo":
             self.trainer = GRPOTrainer(cfg, samples_per_prompt=w.samples_per_prompt, max_new=w.generation_length,
                                        prompt_len=w.context_length, lr=o.learning_rate_actor, gen_slots=rt.gen_slots,
                                        eos_id=run.tokenizer.eos_token_id, use_graphs=rt.use_cuda_graphs, **common)
@@ -232,6 +261,22 @@ class EngineOperationHandler:
     def _train_policy(self, st, step: int) -> Dict[str, Any]:
         tr, A = self.trainer, self.A
         ro = st["rollout"]
+        if self.family == "pipeline_train":
+            # every stage needs every microbatch: the ranks' rollouts (with reference log-probs and scores) are gathered,
+            # the update runs 1F1B over the global batch, then the stages' weights go back to the replicated layout
+            glob = tr.gather_rollout(ro)
+            A.grpo_advantages(glob, self.run.workload.samples_per_prompt)
+            st["denom"] = float(glob.n_response_tokens())
+            steps = 0
+            for part in self._minibatches(glob, step, ranks=1):
+                m = tr.train_policy(part, st["denom"] if part is glob else float(part.n_response_tokens()))
+                steps += 1
+            received = tr.publish()
+            m["grad_norm"] = tr.opt.grad_norm()
+            out = {k: float(v) for k, v in tr._read(m).items()}
+            out.update(train_tokens=int(sum(ro.total_lens())) * self.run.algorithm.epochs, optimizer_steps=steps,
+                       pipeline_stages=self.world, pipeline_p2p_calls=tr.runner.p2p_calls, layout_switch_bytes=received)
+            return out
         if self.algo_name == "dpo":
             tr.policy.zero_grad()
             m = A.dpo_train_step(tr.policy, ro, st["ref_seq"], self.algo, n_pairs_global=int(self._global(ro.n // 2)))
@@ -263,7 +308,7 @@ class EngineOperationHandler:
         out.update(train_tokens=int(sum(ro.total_lens())), optimizer_steps=1)
         return out
 
-    def _minibatches(self, ro, step: int):
+    def _minibatches(self, ro, step: int, ranks: Optional[int] = None):
         """The rollout parts of the update epochs (``algorithm.epochs``, ``algorithm.minibatch_size`` sequences of
         the GLOBAL batch per optimizer step; every rank cuts its own rows the same way). One epoch without a
         minibatch size is the rollout itself."""
@@ -271,7 +316,7 @@ class EngineOperationHandler:
         if a.epochs == 1 and not a.minibatch_size:
             return [ro]
         from .data import minibatch_indices
-        local = None if not a.minibatch_size else max(1, int(a.minibatch_size) // self.world)
+        local = None if not a.minibatch_size else max(1, int(a.minibatch_size) // (ranks or self.world))
         return [ro.subset(rows) for rows in minibatch_indices(ro.n, local, a.epochs, seed=a.seed + step)]
 
     def _train_critic(self, st, step: int = 0) -> Dict[str, Any]:

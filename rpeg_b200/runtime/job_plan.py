@@ -235,10 +235,13 @@ def predicted_schedule(config: Configuration, suite, workload, hw, horizon: int,
 
 
 def data_parallel_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k_eval: int, policy: MemoryPolicy, fusion: bool,
-                                transfer_policy) -> Optional[Configuration]:
-    """The plan family the engine backend executes: every vertex data parallel over all GPUs (``pi = (G, 1, 1)`` on
-    the whole device space), with the smallest microbatch count that the memory model accepts."""
-    from ..core.types import Allocation
+                                transfer_policy, *, pipeline_train: bool = False) -> Optional[Configuration]:
+    """The plan families the engine backend executes, all on the whole device space: every vertex data parallel over
+    all GPUs (``pi = (G, 1, 1)``), or, with ``pipeline_train``, generation and inference data parallel and every
+    training vertex pipeline parallel over all GPUs (``pi = (1, G, 1)``: gradients and optimizer state of a stage
+    only, weights switched back to the replicated layout after each update). The smallest microbatch count that the
+    memory model accepts is taken (a pipeline needs at least as many microbatches as stages to fill)."""
+    from ..core.types import Allocation, Role
     from ..ir.plan import ExecutionPlan
     from ..search.evaluate import evaluate_uncached
     g = space.num_devices()
@@ -247,7 +250,10 @@ def data_parallel_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k
     for mb in (1, 2, 4, 8, 16, 32, 64):
         plan = ExecutionPlan()
         for v in rpeg.vertices:
-            plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (g, 1, 1), mb
+            if pipeline_train and v.kind.role is Role.TRAINING:
+                plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (1, g, 1), max(mb, g)
+            else:
+                plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (g, 1, 1), mb
         last = Configuration(rpeg, plan, space, fusion, transfer_policy)
         try:
             feasible = evaluate_uncached(last, suite, workload, hw, k_eval, policy)[2]
@@ -408,16 +414,18 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
     start = Configuration(rpeg, start_plan, space, fusion, transfer_policy)
     t0 = time.perf_counter()
     best, feasible, reports = None, False, []
-    # ``optimizer.plan_family``: "search" explores placements and (dp, pp, tp) per vertex; "data_parallel" emits the one
-    # plan the engine backend executes (it is the default for engine jobs on more than one GPU).
+    # ``optimizer.plan_family``: "search" explores placements and (dp, pp, tp) per vertex; "data_parallel" emits the
+    # all-data-parallel plan (the default for engine jobs on more than one GPU); "pipeline_train" the plan with
+    # pipeline-parallel training vertices, which the engine backend executes for GRPO.
     engine_job = str((cfg.get("runtime") or {}).get("default_backend", "")) == "engine"
     family = str(options.get("plan_family", "data_parallel" if engine_job and space.num_devices() > 1 else "search"))
-    if family not in ("search", "data_parallel"):
+    if family not in ("search", "data_parallel", "pipeline_train"):
         raise RuntimeConfigError(f"[optimizer] unknown plan_family {family!r}")
-    if family == "data_parallel":
-        best = data_parallel_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy)
+    if family in ("data_parallel", "pipeline_train"):
+        best = data_parallel_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy,
+                                           pipeline_train=family == "pipeline_train")
         if best is None:
-            raise RuntimeConfigError("the data-parallel plan does not fit into memory on this machine")
+            raise RuntimeConfigError(f"the {family} plan does not fit into memory on this machine")
         feasible, attempts = True, 0
     for attempt in range(attempts):
         oc = job_optimizer_config(cfg, algorithm, policy, ac_share, seed0 + attempt)

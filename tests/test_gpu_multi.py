@@ -79,3 +79,36 @@ def test_bench_tiny_async_two_ranks():
     line = _last_json(r.stdout)
     assert line["n_gpus"] == 2 and line["value"] > 0 and line["config"]["algorithm"] == "grpo_async"
     assert line["config"]["parallelism"].startswith("gen1+train1")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_runtime_graph_with_pipeline_parallel_training_on_two_ranks(tmp_path):
+    """The ``pipeline_train`` plan family through the engine backend: generation and the reference pass data parallel,
+    the policy update 1F1B over the two ranks as stages, weights switched back to the replicated layout in the
+    training node; both ranks' traces carry the pipeline counters and the losses are finite."""
+    from rpeg_b200.runtime.io import dump_mapping
+    from rpeg_b200.runtime.job_plan import plan_runtime_job
+    from rpeg_b200.runtime.trace import read_trace
+    tiny = {"layers": 2, "hidden_dim": 256, "ffn_dim": 512, "vocab_size": 512, "head_dim": 128}
+    cfg = {"run_id": "grpo-2gpu-pp", "policy": {"algorithm": "grpo"}, "hardware": {"preset": "b200_nvswitch"},
+           "device_space": {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 2},
+           "models": {"actor": tiny, "reference": {"source": "actor"}},
+           "workload": {"batch_size": 8, "samples_per_prompt": 2, "context_length": 32, "generation_length": 48,
+                        "gen_quantiles": [[0.5, 16], [1.0, 48]]},
+           "training": {"max_steps": 2}, "optimizer": {"k_eval": 2, "plan_family": "pipeline_train"},
+           "runtime_hardware": {"worker_overhead_bytes": 0},
+           "runtime": {"default_backend": "engine", "gen_slots": 8, "micro_tokens": 256}, "outputs": {"seed": 3}}
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    res = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out", quiet=True)
+    r = _torchrun(2, 29565, "-m", "rpeg_b200.runtime.run", "--config", str(res["run_file"]))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    for trace in ("run.jsonl", "run.rank1.jsonl"):
+        events = read_trace(tmp_path / "out/traces" / trace)
+        train = [e for e in events if e["event"] == "finish" and e["node_id"].startswith("t_pi@")]
+        assert len(train) == 2 and all(e["status"] == "ok" for e in train)
+        for e in train:
+            c = e["counters"]
+            assert c["pipeline_stages"] == 2 and c["pipeline_p2p_calls"] > 0 and c["layout_switch_bytes"] > 0
+            assert c["loss"] == c["loss"] and c["grad_norm"] > 0
+    summary = json.loads((tmp_path / "out/metrics/summary.json").read_text())
+    assert summary["nodes_failed"] == 0 and summary["logical_steps"] == 2 and summary["nonfinite_losses"] == 0

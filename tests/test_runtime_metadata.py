@@ -119,6 +119,34 @@ def test_engine_jobs_get_the_data_parallel_plan_family(tmp_path):
         plan_runtime_job(job, tmp_path / "out2", quiet=True)
 
 
+def test_engine_jobs_can_ask_for_pipeline_parallel_training(tmp_path):
+    """``optimizer.plan_family: pipeline_train``: generation / inference vertices stay (G, 1, 1), training vertices become
+    (1, G, 1) with at least G microbatches; the pair compiles, the engine backend recognises the family (GRPO only), and
+    the graph (now with real layout switches on the publication edges) executes and verifies with the metadata backend."""
+    from rpeg_b200.runtime.engine_backend import validate_engine_plan
+    cfg = job_mapping("grpo", steps=2, runtime={"default_backend": "engine", "gen_slots": 8, "micro_tokens": 1024})
+    cfg["device_space"] = {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4}
+    cfg["optimizer"]["plan_family"] = "pipeline_train"
+    job = tmp_path / "job.yaml"
+    dump_mapping(cfg, job)
+    res = plan_runtime_job(job, tmp_path / "out", quiet=True)
+    compiled = res["compiled"]
+    pi, mb = compiled.config.plan.pi, compiled.config.plan.mb
+    assert tuple(pi["t_pi"]) == (1, 4, 1) and mb["t_pi"] >= 4
+    assert {tuple(pi[v]) for v in pi if v != "t_pi"} == {(4, 1, 1)}
+    assert validate_engine_plan(compiled) == "pipeline_train"
+    assert any(n.kind.value == "reshard" for n in compiled.lowered.nodes)
+    graph, ctx, events = execute(compile_runtime_plan(res["run_file"]), tmp_path)
+    assert verify_runtime_trace(compiled, graph, events)["ok"]
+    ppo = job_mapping("ppo", steps=1, runtime={"default_backend": "engine", "gen_slots": 8, "micro_tokens": 1024})
+    ppo["device_space"] = {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4}
+    ppo["optimizer"]["plan_family"] = "pipeline_train"
+    dump_mapping(ppo, job)
+    res2 = plan_runtime_job(job, tmp_path / "out2", quiet=True)
+    with pytest.raises(RuntimeConfigError, match="GRPO only"):
+        validate_engine_plan(res2["compiled"])
+
+
 def test_job_planner_emits_a_compilable_pair(tmp_path):
     job = tmp_path / "job.yaml"
     dump_mapping(job_mapping("ppo"), job)
