@@ -117,6 +117,80 @@ token_logprob_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int* __restri
   }
 }
 
+// Entropy of every row's softmax from the logits and the saved log-sum-exp: with x = logits / temperature and
+// p_v = exp(x_v - lse), H = -sum_v p_v log p_v = lse - sum_v p_v x_v. One CTA per row (a second pass over the chunk's
+// logits, taken only when the objective has an entropy bonus).
+__global__ void __launch_bounds__(LP_THREADS)
+token_entropy_kernel(const __nv_bfloat16* __restrict__ logits, const float* __restrict__ lse, float* __restrict__ ent,
+                     int V, int ld, float inv_temp) {
+  __shared__ float sm[32];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+  const uint4* lv = reinterpret_cast<const uint4*>(lr);
+  const int nvec = V >> 3;
+  const float l = lse[row];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += LP_THREADS) {
+    const uint4 v = lv[i];
+    const uint32_t* pv = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16x2(pv[k]);
+      const float x0 = a.x * inv_temp, x1 = a.y * inv_temp;
+      acc += __expf(x0 - l) * x0 + __expf(x1 - l) * x1;
+    }
+  }
+  for (int i = (nvec << 3) + threadIdx.x; i < V; i += LP_THREADS) {
+    const float x = __bfloat162float(lr[i]) * inv_temp;
+    acc += __expf(x - l) * x;
+  }
+  acc = warp_sum(acc);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sm[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    acc = lane < (LP_THREADS >> 5) ? sm[lane] : 0.f;
+    acc = warp_sum(acc);
+    if (lane == 0) ent[row] = l - acc;
+  }
+}
+
+// In place, log-prob and entropy terms together:
+//   logits[t, v] <- coef[t] * (1[v == y_t] - p_v) / temperature  -  ecoef[t] * p_v * (log p_v + H_t) / temperature
+// (d H / d x_v = -p_v (log p_v + H); ecoef = d loss / d H per row, e.g. -entropy_coef * mask / denominator).
+__global__ void __launch_bounds__(LP_THREADS)
+token_logprob_entropy_bwd_kernel(__nv_bfloat16* __restrict__ logits, const int* __restrict__ targets,
+                                 const float* __restrict__ lse, const float* __restrict__ coef,
+                                 const float* __restrict__ ent, const float* __restrict__ ecoef, int V, int ld,
+                                 float inv_temp) {
+  const int row = blockIdx.x;
+  __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+  uint4* lv = reinterpret_cast<uint4*>(lr);
+  const int nvec = V >> 3;
+  const float c = coef[row] * inv_temp, ec = ecoef[row] * inv_temp, l = lse[row], h = ent[row];
+  const int y = targets[row];
+  for (int i = threadIdx.x; i < nvec; i += LP_THREADS) {
+    uint4 v = lv[i];
+    uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = unpack_bf16x2(pv[k]);
+      const int col = i * 8 + 2 * k;
+      const float q0 = a.x * inv_temp - l, q1 = a.y * inv_temp - l;          // log p
+      const float p0 = __expf(q0), p1 = __expf(q1);
+      const float g0 = c * ((col == y ? 1.f : 0.f) - p0) - ec * p0 * (q0 + h);
+      const float g1 = c * ((col + 1 == y ? 1.f : 0.f) - p1) - ec * p1 * (q1 + h);
+      pv[k] = pack_bf16x2(g0, g1);
+    }
+    lv[i] = v;
+  }
+  for (int i = (nvec << 3) + threadIdx.x; i < V; i += LP_THREADS) {
+    const float q = __bfloat162float(lr[i]) * inv_temp - l;
+    const float p = __expf(q);
+    lr[i] = __float2bfloat16(c * ((i == y ? 1.f : 0.f) - p) - ec * p * (q + h));
+  }
+}
+
 // Clipped policy-gradient loss per token, PPO and GRPO in one kernel:
 //   ratio = exp(lp - old);  pg = -min(ratio*A, clip(ratio, 1-eps, 1+eps)*A)
 //   loss  = sum_t mask * (pg + kl_coef * (lp - ref)) * inv_denom
@@ -495,6 +569,23 @@ extern "C" int rpeg_token_logprob_bwd(void* logits, const int* targets, const fl
   if (ld & 7) return -2;
   token_logprob_bwd_kernel<<<T, LP_THREADS, 0, STREAM(stream)>>>(static_cast<__nv_bfloat16*>(logits), targets, lse,
                                                                 coef, V, ld, 1.f / temperature);
+  return LAUNCH_OK();
+}
+extern "C" int rpeg_token_entropy(const void* logits, const float* lse, float* ent, int T, int V, int ld,
+                                  float temperature, void* stream) {
+  if (T <= 0) return 0;
+  if (ld & 7) return -2;
+  token_entropy_kernel<<<T, LP_THREADS, 0, STREAM(stream)>>>(static_cast<const __nv_bfloat16*>(logits), lse, ent, V, ld,
+                                                            1.f / temperature);
+  return LAUNCH_OK();
+}
+extern "C" int rpeg_token_logprob_entropy_bwd(void* logits, const int* targets, const float* lse, const float* coef,
+                                              const float* ent, const float* ecoef, int T, int V, int ld,
+                                              float temperature, void* stream) {
+  if (T <= 0) return 0;
+  if (ld & 7) return -2;
+  token_logprob_entropy_bwd_kernel<<<T, LP_THREADS, 0, STREAM(stream)>>>(static_cast<__nv_bfloat16*>(logits), targets, lse,
+                                                                        coef, ent, ecoef, V, ld, 1.f / temperature);
   return LAUNCH_OK();
 }
 extern "C" int rpeg_policy_loss(const float* lp, const float* old_lp, const float* ref_lp, const float* adv,

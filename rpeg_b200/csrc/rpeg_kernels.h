@@ -54,6 +54,11 @@ int rpeg_token_logprob_fwd(const void* logits, const int* targets, float* logp, 
                            int ld, float temperature, void* stream);
 int rpeg_token_logprob_bwd(void* logits, const int* targets, const float* lse, const float* coef, int T,
                            int V, int ld, float temperature, void* stream);
+int rpeg_token_entropy(const void* logits, const float* lse, float* ent, int T, int V, int ld, float temperature,
+                       void* stream);
+int rpeg_token_logprob_entropy_bwd(void* logits, const int* targets, const float* lse, const float* coef,
+                                   const float* ent, const float* ecoef, int T, int V, int ld, float temperature,
+                                   void* stream);
 int rpeg_policy_loss(const float* lp, const float* old_lp, const float* ref_lp, const float* adv,
                      const float* mask, float* coef, float* acc, long long n, float clip_eps, float kl_coef,
                      float inv_denom, void* stream);

@@ -66,6 +66,7 @@ class AlgoConfig:
     gamma: float = 1.0
     gae_lambda: float = 0.95
     value_coef: float = 0.5
+    entropy_coef: float = 0.0    # the policy objective gets  - entropy_coef * mean token entropy  (an exploration bonus)
     normalize_advantages: bool = True
     temperature: float = 1.0
     micro_tokens: int = 16384    # packed tokens per microbatch
@@ -158,7 +159,14 @@ def make_policy_head(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, denom: flo
             acc.add_(part)
             return coef
 
-        _, d_rows = model.lm_head_fwd_bwd(rows, mb.targets, coef_fn, cfg.head_chunk, cfg.temperature)
+        def entropy_fn(s, e, ent):
+            ecoef = m_mb[s:e] * (-cfg.entropy_coef / denom)          # d loss / d H per token
+            acc[0].add_((ecoef * ent).sum())
+            vacc[1].add_((m_mb[s:e] * ent).sum())
+            return ecoef.contiguous()
+
+        _, d_rows = model.lm_head_fwd_bwd(rows, mb.targets, coef_fn, cfg.head_chunk, cfg.temperature,
+                                          entropy_fn=entropy_fn if cfg.entropy_coef != 0.0 else None)
         if value_model_shared:
             v = model.scalar_values(rows)
             dv, part = K.value_loss(v, ro.returns.view(-1)[mb.flat], m_mb, 1.0 / denom)
@@ -202,7 +210,8 @@ def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_
         for mb in _micro(ro, cfg):
             xf, ctx = model.forward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen, keep=True)
             model.backward(ctx, head(mb, xf))
-    return {"loss": acc[0], "kl_sum": acc[1], "clipped": acc[2], "approx_kl_sum": acc[3], "value_loss": vacc[0]}
+    return {"loss": acc[0], "kl_sum": acc[1], "clipped": acc[2], "approx_kl_sum": acc[3], "value_loss": vacc[0],
+            "entropy_sum": vacc[1]}
 
 
 def critic_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None,

@@ -384,13 +384,15 @@ class LlamaModel:
         return out
 
     def lm_head_fwd_bwd(self, xf_rows: torch.Tensor, targets: torch.Tensor, coef_fn, chunk: int = 8192,
-                        temperature: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+                        temperature: float = 1.0, entropy_fn=None) -> Tuple[torch.Tensor, torch.Tensor]:
         """LM head forward and backward in one pass per chunk.
 
         ``coef_fn(start, end, logp_chunk) -> d loss / d logp`` for rows ``[start, end)`` (any loss
         that is separable per token can be evaluated right after the chunk's log-probs exist, so
         the logits are produced once, turned into their own gradient in place and consumed by the
-        dgrad / wgrad GEMMs). Returns ``(logp [n], d_xf_rows [n, d])``."""
+        dgrad / wgrad GEMMs). ``entropy_fn(start, end, entropy_chunk) -> d loss / d entropy`` adds a term in the
+        per-token entropy of the softmax (an entropy bonus): the chunk's entropies are computed from the same logits
+        and both gradients are written in one pass. Returns ``(logp [n], d_xf_rows [n, d])``."""
         n, d = xf_rows.shape
         logp = torch.empty(n, dtype=torch.float32, device=self.device)
         d_x = torch.empty((n, d), dtype=torch.bfloat16, device=self.device)
@@ -401,7 +403,11 @@ class LlamaModel:
             lp, lse = K.token_logprob_fwd(logits, targets[s:e], temperature)
             logp[s:e] = lp
             coef = coef_fn(s, e, lp)
-            K.token_logprob_bwd_(logits, targets[s:e], lse, coef, temperature)
+            if entropy_fn is None:
+                K.token_logprob_bwd_(logits, targets[s:e], lse, coef, temperature)
+            else:
+                ent = K.token_entropy(logits, lse, temperature)
+                K.token_logprob_entropy_bwd_(logits, targets[s:e], lse, coef, ent, entropy_fn(s, e, ent), temperature)
             K.gemm(logits, self.p["lm_head"], trans_b=True, out=d_x[s:e])
             K.gemm(logits, xs, trans_a=True, trans_b=True, out=self.gp["lm_head"], accumulate=True)
         return logp, d_x

@@ -32,6 +32,8 @@ _SIGNATURES = {
     "rpeg_embed_bwd": [P, P, P, I, I, P],
     "rpeg_token_logprob_fwd": [P, P, P, P, I, I, I, F, P],
     "rpeg_token_logprob_bwd": [P, P, P, P, I, I, I, F, P],
+    "rpeg_token_entropy": [P, P, P, I, I, I, F, P],
+    "rpeg_token_logprob_entropy_bwd": [P, P, P, P, P, P, I, I, I, F, P],
     "rpeg_policy_loss": [P, P, P, P, P, P, P, LL, F, F, F, P],
     "rpeg_masked_rowsum": [P, P, P, I, I, P],
     "rpeg_dpo_loss": [P, P, P, P, I, F, P],

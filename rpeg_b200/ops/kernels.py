@@ -254,6 +254,26 @@ def token_logprob_bwd_(logits: torch.Tensor, targets: torch.Tensor, lse: torch.T
     return logits
 
 
+def token_entropy(logits: torch.Tensor, lse: torch.Tensor, temperature: float = 1.0) -> torch.Tensor:
+    """Entropy of every row's softmax (at ``temperature``) from the logits and the log-sum-exp ``token_logprob_fwd`` returned."""
+    _req(logits, torch.bfloat16, "logits")
+    T, V = logits.shape
+    ent = torch.empty(T, dtype=torch.float32, device=logits.device)
+    check(lib().rpeg_token_entropy(logits.data_ptr(), lse.data_ptr(), ent.data_ptr(), T, V, logits.stride(0), temperature, _stream()),
+          "rpeg_token_entropy")
+    return ent
+
+
+def token_logprob_entropy_bwd_(logits: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, coef: torch.Tensor, ent: torch.Tensor,
+                               ecoef: torch.Tensor, temperature: float = 1.0) -> torch.Tensor:
+    """Overwrite ``logits`` with ``d loss / d logits`` given ``coef = d loss / d logp`` and ``ecoef = d loss / d entropy`` per row."""
+    T, V = logits.shape
+    check(lib().rpeg_token_logprob_entropy_bwd(logits.data_ptr(), targets.data_ptr(), lse.data_ptr(), coef.data_ptr(), ent.data_ptr(),
+                                               ecoef.data_ptr(), T, V, logits.stride(0), temperature, _stream()),
+          "rpeg_token_logprob_entropy_bwd")
+    return logits
+
+
 def policy_loss(lp, old_lp, ref_lp, adv, mask, clip_eps: float, kl_coef: float, inv_denom: float):
     """Clipped PPO/GRPO loss. Returns ``(coef, acc)``; ``acc = [loss, sum(lp-ref), n_clipped, sum(old-lp)]``."""
     coef = torch.empty_like(lp)

@@ -76,8 +76,8 @@ def validate_engine_plan(compiled) -> str:
             raise RuntimeConfigError(f"engine backend: {layers} layers cannot fill {g} pipeline stages")
     if any(int(t) > 0 for t in cfg.rpeg.tau.values()):
         raise RuntimeConfigError("engine backend runs synchronous plans only (tau = 0): stale serving needs disjoint devices")
-    if float(getattr(compiled.run_config.algorithm, "entropy_coef", 0.0) or 0.0) != 0.0:
-        raise RuntimeConfigError("engine backend: algorithm.entropy_coef is not implemented (the fused policy loss has no entropy term); set it to 0")
+    if float(getattr(compiled.run_config.algorithm, "entropy_coef", 0.0) or 0.0) != 0.0 and compiled.run_config.algorithm.name == "dpo":
+        raise RuntimeConfigError("engine backend: algorithm.entropy_coef applies to the PPO / GRPO policy objective, not to DPO; set it to 0")
     return "pipeline_train" if piped else "data_parallel"
 
 
@@ -108,7 +108,8 @@ class EngineOperationHandler:
         self.algo_name = a.name
         self.shared = any(v.id == "g_ac" for v in compiled.config.rpeg.vertices)
         self.algo = A.AlgoConfig(clip_eps=a.clip, kl_coef=a.kl_coef, beta=a.beta, gamma=a.gamma, gae_lambda=a.gae_lambda,
-                                 value_coef=a.value_coef, temperature=a.temperature, micro_tokens=rt.micro_tokens)
+                                 value_coef=a.value_coef, entropy_coef=a.entropy_coef, temperature=a.temperature,
+                                 micro_tokens=rt.micro_tokens)
         max_pos = w.context_length + w.generation_length
         cfg = llama_config_from_run(run.models["actor"], max_pos)
         from ..engine.trainers import DPOTrainer, GRPOTrainer, PPOTrainer

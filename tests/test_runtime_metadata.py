@@ -111,8 +111,14 @@ def test_engine_jobs_get_the_data_parallel_plan_family(tmp_path):
     res = plan_runtime_job(job, tmp_path / "out", quiet=True)
     compiled = res["compiled"]
     assert {tuple(pi) for pi in compiled.config.plan.pi.values()} == {(4, 1, 1)}
-    validate_engine_plan(compiled)
+    assert validate_engine_plan(compiled) == "data_parallel"
     assert res["comparison"]["evaluations"] == 0                      # nothing was searched
+    compiled.run_config.algorithm.entropy_coef = 0.01                 # an entropy bonus is part of the PPO / GRPO objective ...
+    assert validate_engine_plan(compiled) == "data_parallel"
+    compiled.run_config.algorithm.name = "dpo"                        # ... and meaningless for DPO
+    with pytest.raises(RuntimeConfigError, match="entropy_coef"):
+        validate_engine_plan(compiled)
+    compiled.run_config.algorithm.name, compiled.run_config.algorithm.entropy_coef = "grpo", 0.0
     cfg["optimizer"]["plan_family"] = "bogus"
     dump_mapping(cfg, job)
     with pytest.raises(RuntimeConfigError):
