@@ -416,16 +416,26 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
     best, feasible, reports = None, False, []
     # ``optimizer.plan_family``: "search" explores placements and (dp, pp, tp) per vertex; "data_parallel" emits the
     # all-data-parallel plan (the default for engine jobs on more than one GPU); "pipeline_train" the plan with
-    # pipeline-parallel training vertices, which the engine backend executes for GRPO.
+    # pipeline-parallel training vertices, which the engine backend executes for GRPO; "engine" the better of the two.
     engine_job = str((cfg.get("runtime") or {}).get("default_backend", "")) == "engine"
     family = str(options.get("plan_family", "data_parallel" if engine_job and space.num_devices() > 1 else "search"))
-    if family not in ("search", "data_parallel", "pipeline_train"):
+    if family not in ("search", "data_parallel", "pipeline_train", "engine"):
         raise RuntimeConfigError(f"[optimizer] unknown plan_family {family!r}")
-    if family in ("data_parallel", "pipeline_train"):
-        best = data_parallel_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy,
-                                           pipeline_train=family == "pipeline_train")
+    if family in ("data_parallel", "pipeline_train", "engine"):
+        # "engine": whichever of the two executable families fits into memory and is predicted faster
+        if family == "pipeline_train" and algorithm != "grpo":
+            raise RuntimeConfigError("[optimizer] plan_family pipeline_train: the engine backend runs pipeline-parallel training for GRPO only")
+        cands = []
+        for piped in ((False, True) if family == "engine" else (family == "pipeline_train",)):
+            if piped and (algorithm != "grpo" or space.num_devices() < 2):
+                continue
+            c = data_parallel_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy,
+                                            pipeline_train=piped)
+            if c is not None:
+                cands.append((predicted_schedule(c, suite, workload, hw, horizon, policy)[0].makespan(), len(cands), c))
+        best = min(cands)[2] if cands else None
         if best is None:
-            raise RuntimeConfigError(f"the {family} plan does not fit into memory on this machine")
+            raise RuntimeConfigError(f"no plan of family {family!r} fits into memory on this machine")
         feasible, attempts = True, 0
     for attempt in range(attempts):
         oc = job_optimizer_config(cfg, algorithm, policy, ac_share, seed0 + attempt)

@@ -144,13 +144,25 @@ def test_engine_jobs_can_ask_for_pipeline_parallel_training(tmp_path):
     assert any(n.kind.value == "reshard" for n in compiled.lowered.nodes)
     graph, ctx, events = execute(compile_runtime_plan(res["run_file"]), tmp_path)
     assert verify_runtime_trace(compiled, graph, events)["ok"]
+    cfg["optimizer"]["plan_family"] = "engine"                        # the better of the two executable families
+    dump_mapping(cfg, job)
+    auto = plan_runtime_job(job, tmp_path / "out3", quiet=True)
+    fam = validate_engine_plan(auto["compiled"])
+    both = {"pipeline_train": res["comparison"]["output"]["makespan_s"]}
+    cfg["optimizer"]["plan_family"] = "data_parallel"
+    dump_mapping(cfg, job)
+    both["data_parallel"] = plan_runtime_job(job, tmp_path / "out4", quiet=True)["comparison"]["output"]["makespan_s"]
+    assert fam == min(both, key=both.get) and auto["comparison"]["output"]["makespan_s"] == pytest.approx(min(both.values()))
     ppo = job_mapping("ppo", steps=1, runtime={"default_backend": "engine", "gen_slots": 8, "micro_tokens": 1024})
     ppo["device_space"] = {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4}
     ppo["optimizer"]["plan_family"] = "pipeline_train"
     dump_mapping(ppo, job)
-    res2 = plan_runtime_job(job, tmp_path / "out2", quiet=True)
     with pytest.raises(RuntimeConfigError, match="GRPO only"):
-        validate_engine_plan(res2["compiled"])
+        plan_runtime_job(job, tmp_path / "out2", quiet=True)
+    compiled.run_config.algorithm.name = "ppo"                        # the backend checks the same on its side
+    with pytest.raises(RuntimeConfigError, match="GRPO only"):
+        validate_engine_plan(compiled)
+    compiled.run_config.algorithm.name = "grpo"
 
 
 def test_job_planner_emits_a_compilable_pair(tmp_path):
