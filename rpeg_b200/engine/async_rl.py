@@ -61,6 +61,8 @@ class AsyncGRPO:
         train_group = dist.new_group(self.train_ranks)            # collective over all ranks
         self.step_no = 0
         self.counters: Dict[str, float] = {}
+        self.last_lengths: List[int] = []
+        self.waited_for_rollouts_s = 0.0
         if self.is_gen:
             kv = torch.zeros(int(min(kv_budget_bytes, Generator.kv_bytes_for(cfg, gen_slots, prompt_len + max_new))) // 2,
                              dtype=torch.bfloat16, device=self.device)
@@ -122,14 +124,17 @@ class AsyncGRPO:
         self.rollouts.send(k, idx, res.tokens, res.logprobs, res.lengths)
         K.check_status()
         self.counters = dict(res.counters)
+        self.last_lengths = [int(x) for x in res.lengths.tolist()]
         return {"role": 0.0, "weight_version": float(v), "gen_tokens": float(res.lengths.sum().item()),
                 "waited_for_weights_s": waited}
 
-    def _train(self, k: int, prompts: torch.Tensor, rewards: torch.Tensor) -> Dict[str, float]:
+    def collect(self, k: int, prompts: torch.Tensor) -> A.Rollout:
+        """Training side, first half of iteration ``k``: wait for the rollouts of ``k``, take this rank's rows and
+        compute their reference log-probs. ``self.waited_for_rollouts_s`` holds the time spent waiting."""
         t0 = time.perf_counter()
         if not self.rollouts.ready(k, self.timeout):
             raise TimeoutError(f"rollouts of iteration {k} did not arrive within {self.timeout} s")
-        waited = time.perf_counter() - t0
+        self.waited_for_rollouts_s = time.perf_counter() - t0
         ids, logp, lens = self.rollouts.receive(k)
         rows = self._rows_of(self.train_ranks.index(self.rank), len(self.train_ranks))
         rep = prompts.to(self.device, torch.int32).repeat_interleave(self.K, dim=0)[rows.start:rows.stop].contiguous()
@@ -140,7 +145,11 @@ class AsyncGRPO:
                        weight_version=consumed_version(k, self.tau))
         if self.algo.kl_coef != 0.0:
             ro.ref_logp = A.sequence_logprobs(self.ref, ro, self.algo)
-        ro.scores = rewards[rows.start:rows.stop].to(self.device, torch.float32)
+        return ro
+
+    def update(self, k: int, ro: A.Rollout) -> Dict[str, float]:
+        """Training side, second half: group advantages from ``ro.scores``, the clipped policy step (data parallel among
+        the trainers), and the push of weight version ``k`` to every generation rank."""
         A.grpo_advantages(ro, self.K)
         denom = float(ro.n_response_tokens())
         if self.dp is not None:
@@ -151,7 +160,13 @@ class AsyncGRPO:
         self.weights.publish(self.actor.w, k)
         K.check_status()
         return {"role": 1.0, "samples": float(ro.n), "loss": float(m["loss"]), "grad_norm": float(self.opt.grad_norm()), "trained_on_version": float(ro.weight_version),
-                "published_version": float(k), "train_tokens": float(sum(ro.total_lens())), "waited_for_rollouts_s": waited}
+                "published_version": float(k), "train_tokens": float(sum(ro.total_lens())), "waited_for_rollouts_s": self.waited_for_rollouts_s}
+
+    def _train(self, k: int, prompts: torch.Tensor, rewards: torch.Tensor) -> Dict[str, float]:
+        ro = self.collect(k, prompts)
+        rows = self._rows_of(self.train_ranks.index(self.rank), len(self.train_ranks))
+        ro.scores = rewards[rows.start:rows.stop].to(self.device, torch.float32)
+        return self.update(k, ro)
 
     def close(self) -> None:
         torch.cuda.synchronize(self.device)

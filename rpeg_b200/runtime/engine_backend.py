@@ -38,6 +38,7 @@ from . import checkpoint as ckpt
 from .containers import ContainerRef, WeightVersion
 from .errors import RuntimeConfigError, RuntimeExecutionError
 from .executor import NodeExecutionResult, model_name, node_step, split_part_index
+from .weight_versions import consumer_weight_version as consumed_version_of
 
 
 def llama_config_from_run(m, max_pos: int, **kw):
@@ -48,16 +49,49 @@ def llama_config_from_run(m, max_pos: int, **kw):
                        rope_theta=m.rope_theta, max_pos=max_pos, **kw)
 
 
+def disaggregated_ranks(compiled):
+    """``(generation ranks, training ranks)`` when the plan puts every generation vertex, data parallel, on one set of GPUs
+    of the node and every other vertex, data parallel, on the remaining GPUs; ``None`` for any other plan."""
+    from ..core.types import Role
+    cfg = compiled.config
+    if compiled.device_space.R * compiled.device_space.N != 1:
+        return None
+    sets = {"gen": set(), "rest": set()}
+    for v in cfg.rpeg.vertices:
+        devs = {c[2] for c in cfg.plan.sigma[v.id].coords()}
+        dp, pp, tp = cfg.plan.pi[v.id]
+        if pp != 1 or tp != 1 or dp != len(devs):
+            return None
+        key = "gen" if v.kind.role is Role.GENERATION else "rest"
+        if sets[key] and sets[key] != devs:
+            return None
+        sets[key] = devs
+    gen, rest = sets["gen"], sets["rest"]
+    if not gen or not rest or gen & rest or len(gen | rest) != compiled.device_space.G:
+        return None
+    return sorted(gen), sorted(rest)
+
+
 def validate_engine_plan(compiled) -> str:
     """The plan families this backend executes, both on all ``G`` GPUs of the node. Returns the family:
 
       ``"data_parallel"``    every vertex ``(dp, pp, tp) = (G, 1, 1)``
       ``"pipeline_train"``   generation / inference vertices ``(G, 1, 1)``, every training vertex ``(1, G, 1)`` (GRPO):
                              the update runs 1F1B over all ranks as stages, the publication edge is a real layout
-                             switch (stage weights broadcast into the replicated generation copy)"""
+                             switch (stage weights broadcast into the replicated generation copy)
+      ``"disaggregated"``    generation data parallel on some GPUs, everything else data parallel on the others (GRPO),
+                             any staleness ``tau >= 0``: the two sides run concurrently and meet through versioned
+                             peer-memory channels (``engine.async_rl.AsyncGRPO``)"""
     from ..core.types import Role
     cfg = compiled.config
     g = compiled.device_space.num_devices()
+    split = disaggregated_ranks(compiled)
+    if split is not None:
+        if compiled.run_config.algorithm.name != "grpo":
+            raise RuntimeConfigError("engine backend: generation and training on disjoint GPUs is implemented for GRPO only")
+        if compiled.run_config.checkpoints.resume_from:
+            raise RuntimeConfigError("engine backend: a run with generation and training on disjoint GPUs cannot resume from a checkpoint")
+        return "disaggregated"
     train = [v for v in cfg.rpeg.vertices if v.kind.role is Role.TRAINING]
     piped = g > 1 and bool(train) and all(tuple(cfg.plan.pi[v.id]) == (1, g, 1) for v in train)
     for v in cfg.rpeg.vertices:
@@ -75,7 +109,8 @@ def validate_engine_plan(compiled) -> str:
         if layers < g:
             raise RuntimeConfigError(f"engine backend: {layers} layers cannot fill {g} pipeline stages")
     if any(int(t) > 0 for t in cfg.rpeg.tau.values()):
-        raise RuntimeConfigError("engine backend runs synchronous plans only (tau = 0): stale serving needs disjoint devices")
+        raise RuntimeConfigError("engine backend: staleness (tau > 0) needs generation and training on disjoint GPUs "
+                                 "(optimizer.plan_family: disaggregated)")
     if float(getattr(compiled.run_config.algorithm, "entropy_coef", 0.0) or 0.0) != 0.0 and compiled.run_config.algorithm.name == "dpo":
         raise RuntimeConfigError("engine backend: algorithm.entropy_coef applies to the PPO / GRPO policy objective, not to DPO; set it to 0")
     return "pipeline_train" if piped else "data_parallel"
@@ -114,7 +149,20 @@ class EngineOperationHandler:
         cfg = llama_config_from_run(run.models["actor"], max_pos)
         from ..engine.trainers import DPOTrainer, GRPOTrainer, PPOTrainer
         common = dict(device=self.device, algo=self.algo, dp=self.dp, recompute=rt.recompute, seed=a.seed)
-        if self.family == "pipeline_train":
+        self.async_engine = None
+        if self.family == "disaggregated":
+            from ..core.types import Model
+            from ..engine.async_rl import AsyncGRPO
+            gen_ranks, train_ranks = disaggregated_ranks(compiled)
+            self.tau = int(compiled.config.rpeg.tau.get(Model.ACTOR, 0))
+            kv = float(getattr(run.hardware, "kv_cache_budget_bytes", 0) or 16e9)
+            self.async_engine = AsyncGRPO(cfg, gen_ranks=gen_ranks, train_ranks=train_ranks, prompts_per_step=w.batch_size,
+                                          samples_per_prompt=w.samples_per_prompt, max_new=w.generation_length,
+                                          prompt_len=w.context_length, tau=self.tau, algo=self.algo, lr=o.learning_rate_actor,
+                                          gen_slots=rt.gen_slots, kv_budget_bytes=kv, seed=a.seed, eos_id=run.tokenizer.eos_token_id,
+                                          device=self.device, use_graphs=rt.use_cuda_graphs, wait_timeout_s=float(rt.node_timeout_s or 600.0))
+            self.trainer = None
+        elif self.family == "pipeline_train":
             from ..engine.trainers import PipelineGRPOTrainer
             self.trainer = PipelineGRPOTrainer(cfg, device=self.device, algo=self.algo, recompute=rt.recompute, seed=a.seed,
                                                samples_per_prompt=w.samples_per_prompt, max_new=w.generation_length,
@@ -199,7 +247,60 @@ class EngineOperationHandler:
         hi = q[part][1]
         return sum(1 for l in lens if lo < l <= hi)
 
+    def _prompts_global(self, step: int):
+        """The whole synthetic prompt batch of a step (every rank draws the same one)."""
+        torch, w = self.torch, self.run.workload
+        g = torch.Generator().manual_seed(self.run.data.data_seed * 1000003 + step)
+        return torch.randint(3, self.vocab, (w.batch_size, w.context_length), generator=g, dtype=torch.int32)
+
+    def _run_op_disaggregated(self, node) -> Dict[str, Any]:
+        """Generation ranks execute the generation vertices, training ranks everything else; a vertex of the other side
+        is a no-op here (its effect reaches this rank through the versioned channels: a generation rank waits for the
+        weight version its iteration consumes, a training rank for the rollouts of its iteration)."""
+        eng, torch, w = self.async_engine, self.torch, self.run.workload
+        step = node_step(node) or 1
+        st = self._state(step)
+        vid = node.vertex_id
+        c: Dict[str, Any] = {"side": "generation" if eng.is_gen else "training"}
+        if vid == "t_pi" and step == int(self.run.training.max_steps):
+            self._leave_together = True                   # see execute(): no rank exits while a peer may still write to it
+        if vid == "g_pi":
+            if not eng.is_gen:
+                return c
+            if "generated" not in st:
+                forced = None
+                if self.run.data.synthetic_response_lengths == "quantiles" and w.gen_quantiles:
+                    from .data import quantile_lengths
+                    forced = quantile_lengths(w.batch_size * w.samples_per_prompt, w.quantile_tuples(), seed=self.run.data.data_seed * 1000003 + step)
+                eng.step_no = step
+                out = eng._generate(step, self._prompts_global(step), forced)
+                st["generated"], st["lens"] = True, list(eng.last_lengths)
+                c.update({k: v for k, v in eng.counters.items()})
+                c.update(generated_tokens=int(out["gen_tokens"]), waited_for_weights_s=out["waited_for_weights_s"])
+            c.update(emitted_rows=self._emitted(st, node), data_parallel_ranks=len(eng.gen_ranks),
+                     weight_version=int(consumed_version_of(step, self.tau)), model="actor", shadow=self.tau > 0)
+            return c
+        if not eng.is_train:
+            return c
+        if vid == "i_ref":
+            if "rollout" not in st:
+                eng.step_no = step
+                st["rollout"] = eng.collect(step, self._prompts_global(step))
+                c["waited_for_rollouts_s"] = eng.waited_for_rollouts_s
+        elif vid == "i_R":
+            ro = st["rollout"]                              # rule-based stand-in: shorter completions score higher
+            ro.scores = -torch.tensor(ro.resp_lens, dtype=torch.float32, device=self.device) / w.generation_length
+        elif vid == "t_pi":
+            out = eng.update(step, st["rollout"])
+            c.update({k: out[k] for k in ("loss", "grad_norm", "trained_on_version", "published_version", "train_tokens")})
+            c["optimizer_steps"] = 1
+        else:
+            raise RuntimeExecutionError(f"engine backend (disaggregated GRPO) has no operator for vertex {vid}")
+        return c
+
     def _run_op(self, node) -> Dict[str, Any]:
+        if self.family == "disaggregated":
+            return self._run_op_disaggregated(node)
         tr, A, torch = self.trainer, self.A, self.torch
         step = node_step(node) or 1
         st = self._state(step)
@@ -360,9 +461,27 @@ class EngineOperationHandler:
                 part = split_part_index(node.node_id)
                 if part is not None:
                     c["artifact_part"] = part
-            if name in ("actor", "critic", "ac_share") and node.role in ("GEN", "INF") and step is not None:
+            if self.family == "disaggregated" and getattr(self, "_leave_together", False):
+                # Last training vertex of the run. The trainers push the final weights into the generation ranks' memory:
+                # a generation rank (long done) first waits on the host for that version, then all ranks meet, so that
+                # no process leaves while a peer's kernel may still write into its buffers.
+                import torch.distributed as dist
+                self._leave_together = False
+                eng = self.async_engine
+                if eng.is_gen and not eng.weights.ready(int(step or 0), float(self.run.runtime.node_timeout_s)):
+                    raise RuntimeExecutionError(f"final weight version {step} did not arrive")
+                self.torch.cuda.synchronize()
+                dist.barrier()
+            if self.family == "disaggregated":
+                if node.role == "TRAIN" and name is not None and self.async_engine.is_train:
+                    self.latest[name] = int(step or 0)
+                    c["produced_weight"] = {"model": name, "version": self.latest[name], "shadow": self.tau > 0}
+                    weights.append(WeightVersion(name, self.latest[name], tuple(node.parallelism or (1, 1, 1))))
+                for s in [s for s in self.steps if s < (step or 0) - self.tau - 1]:
+                    del self.steps[s]
+            elif name in ("actor", "critic", "ac_share") and node.role in ("GEN", "INF") and step is not None:
                 c.update(weight_version=self.latest.get(name, 0), model=name, shadow=False)
-            if node.role == "TRAIN" and name is not None:
+            if self.family != "disaggregated" and node.role == "TRAIN" and name is not None:
                 self.latest[name] = self.latest.get(name, 0) + 1
                 c["produced_weight"] = {"model": name, "version": self.latest[name], "shadow": False}
                 weights.append(WeightVersion(name, self.latest[name], tuple(node.parallelism or (1, 1, 1))))
@@ -377,6 +496,8 @@ class EngineOperationHandler:
 
     # ------------------------------------------------------------------ checkpoints
     def _trainables(self):
+        if self.family == "disaggregated":
+            return {}          # weights and optimizer state live on the training ranks only; no checkpoint is taken in this family
         tr = self.trainer
         if self.algo_name == "dpo":
             return {"actor": (tr.policy, tr.opt)}

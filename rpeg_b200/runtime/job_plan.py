@@ -264,6 +264,36 @@ def data_parallel_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k
     return None
 
 
+def disaggregated_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k_eval: int, policy: MemoryPolicy, fusion: bool,
+                                transfer_policy, gen_gpus: Optional[int] = None) -> Optional[Configuration]:
+    """Generation data parallel on the first ``gen_gpus`` GPUs of the node (default: half), every other vertex data
+    parallel on the rest: the placement under which a staleness ``tau > 0`` lets generation of the next iterations overlap
+    training of the current one. The engine backend executes it for GRPO (``engine.async_rl``)."""
+    from ..core.types import Allocation, Role
+    from ..ir.plan import ExecutionPlan
+    from ..search.evaluate import evaluate_uncached
+    if space.R * space.N != 1 or space.G < 2:
+        raise RuntimeConfigError("[optimizer] plan_family disaggregated needs one node with at least two GPUs")
+    ng = int(gen_gpus) if gen_gpus else space.G // 2
+    if not 0 < ng < space.G:
+        raise RuntimeConfigError(f"[optimizer] gen_gpus must be between 1 and {space.G - 1}")
+    gen_alloc, rest_alloc = Allocation((0, 0, 0), (1, 1, ng)), Allocation((0, 0, ng), (1, 1, space.G - ng))
+    for mb in (1, 2, 4, 8, 16, 32, 64):
+        plan = ExecutionPlan()
+        for v in rpeg.vertices:
+            if v.kind.role is Role.GENERATION:
+                plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = gen_alloc, (ng, 1, 1), mb
+            else:
+                plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = rest_alloc, (space.G - ng, 1, 1), mb
+        conf = Configuration(rpeg, plan, space, fusion, transfer_policy)
+        try:
+            if evaluate_uncached(conf, suite, workload, hw, k_eval, policy)[2]:
+                return conf
+        except Exception:
+            continue
+    return None
+
+
 def validated_seed_plan(cfg: dict, base_dir: Path, rpeg, space: DeviceSpace, algorithm: str, ac_share: bool):
     """Optional ``optimizer.seed_plan_path``: must describe the same algorithm, device space,
     vertex set, staleness and structure as the job (reference: RPEG/runtime/job_plan.py:335-433)."""
@@ -416,11 +446,18 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
     best, feasible, reports = None, False, []
     # ``optimizer.plan_family``: "search" explores placements and (dp, pp, tp) per vertex; "data_parallel" emits the
     # all-data-parallel plan (the default for engine jobs on more than one GPU); "pipeline_train" the plan with
-    # pipeline-parallel training vertices, which the engine backend executes for GRPO; "engine" the better of the two.
+    # pipeline-parallel training vertices, which the engine backend executes for GRPO; "engine" the better of the two;
+    # "disaggregated" generation on ``optimizer.gen_gpus`` GPUs and the rest elsewhere (what ``policy.tau > 0`` needs).
     engine_job = str((cfg.get("runtime") or {}).get("default_backend", "")) == "engine"
     family = str(options.get("plan_family", "data_parallel" if engine_job and space.num_devices() > 1 else "search"))
-    if family not in ("search", "data_parallel", "pipeline_train", "engine"):
+    if family not in ("search", "data_parallel", "pipeline_train", "engine", "disaggregated"):
         raise RuntimeConfigError(f"[optimizer] unknown plan_family {family!r}")
+    if family == "disaggregated":
+        best = disaggregated_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy,
+                                           options.get("gen_gpus"))
+        if best is None:
+            raise RuntimeConfigError("the disaggregated plan does not fit into memory on this machine")
+        feasible, attempts = True, 0
     if family in ("data_parallel", "pipeline_train", "engine"):
         # "engine": whichever of the two executable families fits into memory and is predicted faster
         if family == "pipeline_train" and algorithm != "grpo":

@@ -112,3 +112,36 @@ def test_runtime_graph_with_pipeline_parallel_training_on_two_ranks(tmp_path):
             assert c["loss"] == c["loss"] and c["grad_norm"] > 0
     summary = json.loads((tmp_path / "out/metrics/summary.json").read_text())
     assert summary["nodes_failed"] == 0 and summary["logical_steps"] == 2 and summary["nonfinite_losses"] == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_runtime_graph_with_generation_and_training_on_disjoint_gpus(tmp_path):
+    """The ``disaggregated`` plan family with one step of staleness through the engine backend: rank 0 generates, rank 1
+    trains; each side's trace shows its own work (consumed versions 0, 0, 1 on the generation side, published versions
+    1, 2, 3 on the training side) and both verify."""
+    from rpeg_b200.runtime.io import dump_mapping
+    from rpeg_b200.runtime.job_plan import plan_runtime_job
+    from rpeg_b200.runtime.trace import read_trace
+    tiny = {"layers": 2, "hidden_dim": 256, "ffn_dim": 512, "vocab_size": 512, "head_dim": 128}
+    cfg = {"run_id": "grpo-2gpu-async", "policy": {"algorithm": "grpo", "tau": {"actor": 1}}, "hardware": {"preset": "b200_nvswitch"},
+           "device_space": {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 2},
+           "models": {"actor": tiny, "reference": {"source": "actor"}},
+           "workload": {"batch_size": 8, "samples_per_prompt": 2, "context_length": 32, "generation_length": 48,
+                        "gen_quantiles": [[0.5, 16], [1.0, 48]]},
+           "training": {"max_steps": 3}, "optimizer": {"k_eval": 3, "plan_family": "disaggregated"},
+           "runtime_hardware": {"worker_overhead_bytes": 0}, "checkpoints": {"interval_steps": 0, "save_final": False},
+           "runtime": {"default_backend": "engine", "gen_slots": 16, "micro_tokens": 1024, "node_timeout_s": 120}, "outputs": {"seed": 3}}
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    res = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out", quiet=True)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29566", "-m", "rpeg_b200.runtime.run", "--config", str(res["run_file"])]
+    env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    gen = [e for e in read_trace(tmp_path / "out/traces/run.jsonl") if e["event"] == "finish" and e["node_id"].startswith("g_pi@")
+           and "generated_tokens" in e["counters"]]
+    assert [e["counters"]["weight_version"] for e in gen] == [0, 0, 1] and all(e["counters"]["generated_tokens"] > 0 for e in gen)
+    train = [e for e in read_trace(tmp_path / "out/traces/run.rank1.jsonl") if e["event"] == "finish" and e["node_id"].startswith("t_pi@")]
+    assert [e["counters"]["published_version"] for e in train] == [1.0, 2.0, 3.0]
+    assert all(e["counters"]["loss"] == e["counters"]["loss"] and e["counters"]["grad_norm"] > 0 for e in train)

@@ -165,6 +165,41 @@ def test_engine_jobs_can_ask_for_pipeline_parallel_training(tmp_path):
     compiled.run_config.algorithm.name = "grpo"
 
 
+@pytest.mark.parametrize("tau", [0, 1])
+def test_engine_jobs_can_put_generation_and_training_on_disjoint_gpus(tmp_path, tau):
+    """``optimizer.plan_family: disaggregated``: generation data parallel on ``gen_gpus`` GPUs, the rest on the others; with
+    ``policy.tau`` the graph carries stale weight versions. The pair compiles, the engine backend recognises the family and
+    its rank split, and the graph executes and verifies with the metadata backend."""
+    from rpeg_b200.runtime.engine_backend import disaggregated_ranks, validate_engine_plan
+    cfg = job_mapping("grpo", steps=3, runtime={"default_backend": "engine", "gen_slots": 8, "micro_tokens": 1024})
+    cfg["device_space"] = {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4}
+    cfg["optimizer"].update(plan_family="disaggregated")          # default: half of the GPUs generate
+    if tau:
+        cfg["policy"]["tau"] = {"actor": tau}
+    job = tmp_path / "job.yaml"
+    dump_mapping(cfg, job)
+    res = plan_runtime_job(job, tmp_path / "out", quiet=True)
+    compiled = res["compiled"]
+    assert disaggregated_ranks(compiled) == ([0, 1], [2, 3])
+    assert validate_engine_plan(compiled) == "disaggregated"
+    assert tuple(compiled.config.plan.pi["g_pi"]) == (2, 1, 1) and tuple(compiled.config.plan.pi["t_pi"]) == (2, 1, 1)
+    graph, ctx, events = execute(compile_runtime_plan(res["run_file"]), tmp_path)
+    assert verify_runtime_trace(compiled, graph, events)["ok"]
+    compiled.run_config.algorithm.name = "ppo"
+    with pytest.raises(RuntimeConfigError, match="GRPO only"):
+        validate_engine_plan(compiled)
+    compiled.run_config.algorithm.name = "grpo"
+    if tau:                                   # the same staleness on shared GPUs is refused by the planner: nothing could overlap
+        cfg["optimizer"].update(plan_family="data_parallel")
+        dump_mapping(cfg, job)
+        with pytest.raises(RuntimeConfigError):
+            plan_runtime_job(job, tmp_path / "out2", quiet=True)
+    bad = dict(cfg, optimizer=dict(cfg["optimizer"], plan_family="disaggregated", gen_gpus=4))
+    dump_mapping(bad, job)
+    with pytest.raises(RuntimeConfigError, match="gen_gpus"):
+        plan_runtime_job(job, tmp_path / "out3", quiet=True)
+
+
 def test_job_planner_emits_a_compilable_pair(tmp_path):
     job = tmp_path / "job.yaml"
     dump_mapping(job_mapping("ppo"), job)
