@@ -282,20 +282,21 @@ class EngineOperationHandler:
             return c
         if not eng.is_train:
             return c
-        if vid == "i_ref":
-            if "rollout" not in st:
-                eng.step_no = step
-                st["rollout"] = eng.collect(step, self._prompts_global(step))
-                c["waited_for_rollouts_s"] = eng.waited_for_rollouts_s
-        elif vid == "i_R":
-            ro = st["rollout"]                              # rule-based stand-in: shorter completions score higher
+        if vid not in ("i_ref", "i_R", "t_pi"):
+            raise RuntimeExecutionError(f"engine backend (disaggregated GRPO) has no operator for vertex {vid}")
+        # The inference vertices of a step may be dispatched in any order (and in quantile parts): whichever comes first
+        # receives the step's rollouts (waiting for the generation ranks) and computes the reference log-probs.
+        if "rollout" not in st:
+            eng.step_no = step
+            st["rollout"] = eng.collect(step, self._prompts_global(step))
+            c["waited_for_rollouts_s"] = eng.waited_for_rollouts_s
+        ro = st["rollout"]
+        if ro.scores is None:                               # rule-based stand-in: shorter completions score higher
             ro.scores = -torch.tensor(ro.resp_lens, dtype=torch.float32, device=self.device) / w.generation_length
-        elif vid == "t_pi":
-            out = eng.update(step, st["rollout"])
+        if vid == "t_pi":
+            out = eng.update(step, ro)
             c.update({k: out[k] for k in ("loss", "grad_norm", "trained_on_version", "published_version", "train_tokens")})
             c["optimizer_steps"] = 1
-        else:
-            raise RuntimeExecutionError(f"engine backend (disaggregated GRPO) has no operator for vertex {vid}")
         return c
 
     def _run_op(self, node) -> Dict[str, Any]:

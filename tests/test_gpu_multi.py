@@ -129,7 +129,7 @@ def test_runtime_graph_with_generation_and_training_on_disjoint_gpus(tmp_path):
            "workload": {"batch_size": 8, "samples_per_prompt": 2, "context_length": 32, "generation_length": 48,
                         "gen_quantiles": [[0.5, 16], [1.0, 48]]},
            "training": {"max_steps": 3}, "optimizer": {"k_eval": 3, "plan_family": "disaggregated"},
-           "runtime_hardware": {"worker_overhead_bytes": 0}, "checkpoints": {"interval_steps": 0, "save_final": False},
+           "runtime_hardware": {"worker_overhead_bytes": 0}, "checkpoints": {"interval_steps": 100, "save_final": False},
            "runtime": {"default_backend": "engine", "gen_slots": 16, "micro_tokens": 1024, "node_timeout_s": 120}, "outputs": {"seed": 3}}
     dump_mapping(cfg, tmp_path / "job.yaml")
     res = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out", quiet=True)
