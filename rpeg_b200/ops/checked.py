@@ -104,14 +104,15 @@ def paged_attention(kernel: str, n_rows: int, seq_lens: torch.Tensor, page_table
 
 
 def packed_sequences(kernel: str, cu_seqlens: torch.Tensor, n_tokens: int, max_seqlen: int) -> None:
-    """``cu_seqlens``: starts at 0, never decreases, ends at the number of packed tokens, no sequence longer than
-    ``max_seqlen`` (the kernel sizes its grid from it)."""
+    """``cu_seqlens``: starts at 0, never decreases, ends inside the packed buffer (tensor-parallel callers pad the
+    token dimension, so the last boundary may lie before the buffer's end), no sequence longer than ``max_seqlen`` (the
+    kernel sizes its grid from it)."""
     cu = cu_seqlens.reshape(-1).long()
     if cu.numel() < 2:
         raise KernelArgumentError(f"{kernel}: cu_seqlens needs at least two entries")
     d = cu[1:] - cu[:-1]
-    if int(cu[0]) != 0 or int(cu[-1]) != n_tokens or int(d.min()) < 0:
-        raise KernelArgumentError(f"{kernel}: cu_seqlens must rise from 0 to {n_tokens}, got {cu[:4].tolist()} ... {int(cu[-1])}")
+    if int(cu[0]) != 0 or int(cu[-1]) > n_tokens or int(d.min()) < 0:
+        raise KernelArgumentError(f"{kernel}: cu_seqlens must rise from 0 to at most {n_tokens}, got {cu[:4].tolist()} ... {int(cu[-1])}")
     if int(d.max()) > max_seqlen:
         raise KernelArgumentError(f"{kernel}: a sequence of {int(d.max())} tokens exceeds max_seqlen = {max_seqlen}")
 

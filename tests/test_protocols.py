@@ -151,7 +151,8 @@ def test_checked_mode_validators_name_the_offending_index():
     with pytest.raises(E, match="4 rows"):
         C.paged_attention("k", 4, torch.tensor([1, 1, 1, 1], dtype=torch.int32), table, kc, 2, 128)
     C.packed_sequences("k", torch.tensor([0, 3, 3, 10], dtype=torch.int32), 10, 7)
-    for cu, n, mx in (([1, 3, 10], 10, 9), ([0, 5, 4, 10], 10, 9), ([0, 3, 9], 10, 9), ([0, 3, 10], 10, 6), ([0], 0, 1)):
+    C.packed_sequences("k", torch.tensor([0, 3, 9], dtype=torch.int32), 10, 7)         # a padded token buffer
+    for cu, n, mx in (([1, 3, 10], 10, 9), ([0, 5, 4, 10], 10, 9), ([0, 3, 11], 10, 9), ([0, 3, 10], 10, 6), ([0], 0, 1)):
         with pytest.raises(E):
             C.packed_sequences("k", torch.tensor(cu, dtype=torch.int32), n, mx)
     C.global_rows("k", torch.tensor([0, 7], dtype=torch.int64), 4, 2)
