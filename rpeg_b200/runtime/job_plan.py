@@ -401,13 +401,19 @@ def sbatch_script(run_file: Path, space: DeviceSpace, cfg: dict) -> str:
 
 
 def _preflight_lines(run_file: Path, space: DeviceSpace, nodes: int, sl: dict) -> List[str]:
-    """GPU health of every node and the cluster contract, before the ranks start (``slurm.preflight: false`` drops it)."""
+    """GPU health of every node and the cluster contract, before the ranks start (``slurm.preflight: false`` drops it);
+    ``slurm.engine_validate: true`` adds the engine's smoke worker on a single-node job."""
     if not sl.get("preflight", True):
         return []
     d = run_file.parent
-    return [f"srun --ntasks-per-node=1 python -m rpeg_b200.runtime.slurm_preflight --expected-gpus {space.G} > {d}/preflight.jsonl",
-            f"python -m rpeg_b200.runtime.slurm_preflight --contract-from {d}/preflight.jsonl --contract-output {d}/cluster_contract.json "
-            f"--expected-nodes {nodes}" + (" --strict" if sl.get("preflight_strict", False) else "")]
+    lines = [f"srun --ntasks-per-node=1 python -m rpeg_b200.runtime.slurm_preflight --expected-gpus {space.G} > {d}/preflight.jsonl",
+             f"python -m rpeg_b200.runtime.slurm_preflight --contract-from {d}/preflight.jsonl --contract-output {d}/cluster_contract.json "
+             f"--expected-nodes {nodes}" + (" --strict" if sl.get("preflight_strict", False) else "")]
+    if sl.get("engine_validate", False) and nodes == 1:
+        # the engine's smoke worker on all GPUs of the node: training step, two-token PPO exercise, checkpoint round trip
+        lines.append(f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {space.G} --master-addr 127.0.0.1 --master-port 29513 "
+                     f"-m rpeg_b200.runtime.engine_validate --ppo-exercise --checkpoint-dir {d}/validate_ckpt --json > {d}/engine_validate.json")
+    return lines
 
 
 # ------------------------------------------------------------------------------ driver
