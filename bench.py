@@ -45,6 +45,12 @@ CONFIGS = {
     # iteration k + 1 overlaps training of iteration k; weights and rollouts cross through versioned peer-memory channels
     "grpo_7b_async": dict(algo="grpo_async", model="llama7b", prompts=32, k=8, prompt_len=512, max_new=2048, tau=1,
                           quantiles=((0.5, 512), (0.9, 1024), (1.0, 2048)), min_gpus=2),
+    # GRPO with data-parallel generation and a pipeline-parallel policy update (1F1B over all ranks, one stage's optimizer
+    # state per GPU, weights broadcast back into the replicated generation copy after the step)
+    "grpo_7b_pp": dict(algo="grpo", model="llama7b", prompts=32, k=8, prompt_len=512, max_new=2048, pipeline_train=True,
+                       quantiles=((0.5, 512), (0.9, 1024), (1.0, 2048)), min_gpus=2),
+    "grpo_tiny_pp": dict(algo="grpo", model="tiny", prompts=16, k=4, prompt_len=32, max_new=64, pipeline_train=True,
+                         quantiles=((0.5, 16), (0.9, 32), (1.0, 64)), min_gpus=2),
     "grpo_tiny_async": dict(algo="grpo_async", model="tiny", prompts=16, k=4, prompt_len=32, max_new=64, tau=1,
                             quantiles=((0.5, 16), (0.9, 32), (1.0, 64)), min_gpus=2),
 }
@@ -168,7 +174,7 @@ def main() -> None:
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
-        if spec["algo"] != "grpo_async":            # the asynchronous engine builds its own groups
+        if spec["algo"] != "grpo_async" and not spec.get("pipeline_train"):   # those engines build their own groups
             from rpeg_b200.parallel.dp import DPContext
             dp = DPContext(device)
 
@@ -193,8 +199,13 @@ def main() -> None:
         # the K samples of a prompt share its KV pages, so the pool holds every row of the rank at once
         slots = args.gen_slots or min(b_local * Kk, 256)
         kv_gb = args.kv_gb or {1: 56.0, 2: 76.0}.get(world, 96.0)
-        trainer = GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp,
-                              gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)
+        if spec.get("pipeline_train"):
+            from rpeg_b200.engine.trainers import PipelineGRPOTrainer
+            trainer = PipelineGRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo,
+                                          gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)
+        else:
+            trainer = GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp,
+                                  gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)
         batches = []
         for _ in range(n_iters):
             prompts = torch.randint(3, cfg.vocab, (B, S), generator=gen_host, dtype=torch.int32)
@@ -313,7 +324,7 @@ def main() -> None:
             "config": {"model": {"grpo": f"{spec['model']} x2 (actor + frozen reference)", "grpo_async": f"{spec['model']} x2 (actor + frozen reference)", "dpo": f"{spec['model']} x2 (policy + frozen reference)", "ppo": f"{spec['model']} actor" + ("+critic shared trunk" if spec.get("shared") else ", critic") + ", reference, reward"}[spec["algo"]] + ", random init", "algorithm": spec["algo"],
                        "global_batch": B * Kk if spec["algo"] in ("grpo", "grpo_async") else B, "prompts": B, "samples_per_prompt": Kk,
                        "seq_len": S + T, "prompt_len": S, "max_new_tokens": T, "gen_quantiles": spec["quantiles"],
-                       "parallelism": (f"gen{world // 2}+train{world - world // 2}, staleness {spec.get('tau', 1)}" if spec["algo"] == "grpo_async" else f"dp{world}"), "optimizer": "adamw fp32 master, sharded over dp",
+                       "parallelism": (f"gen{world // 2}+train{world - world // 2}, staleness {spec.get('tau', 1)}" if spec["algo"] == "grpo_async" else (f"generation dp{world}, training pp{world}" if spec.get("pipeline_train") else f"dp{world}")), "optimizer": "adamw fp32 master, sharded over dp",
                        "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if spec["algo"] in ("grpo", "grpo_async", "ppo") else None,
                        "l2": "working set (13.5 GB of weights per model) far exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": stats_e2e[0] / (ms_e2e / 1e3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,

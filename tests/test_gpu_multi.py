@@ -145,3 +145,12 @@ def test_runtime_graph_with_generation_and_training_on_disjoint_gpus(tmp_path):
     train = [e for e in read_trace(tmp_path / "out/traces/run.rank1.jsonl") if e["event"] == "finish" and e["node_id"].startswith("t_pi@")]
     assert [e["counters"]["published_version"] for e in train] == [1.0, 2.0, 3.0]
     assert all(e["counters"]["loss"] == e["counters"]["loss"] and e["counters"]["grad_norm"] > 0 for e in train)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_bench_tiny_pipeline_trained_two_ranks():
+    """Data-parallel generation with a pipeline-parallel policy update, through bench.py's own loop."""
+    r = _torchrun(2, 29567, "bench.py", "--config", "grpo_tiny_pp", "--gpus", "2", "--steps", "1", "--warmup", "3")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = _last_json(r.stdout)
+    assert line["n_gpus"] == 2 and line["value"] > 0 and line["config"]["parallelism"] == "generation dp2, training pp2"
