@@ -44,8 +44,11 @@ class DPContext:
         self._scalar = torch.zeros(1, dtype=torch.float64, device=self.device)
 
     def clone(self, tag: str) -> "DPContext":
-        """Context for another model sharing this one's signal pad (own barrier slots)."""
-        return DPContext(self.device, self.group, tag, self.pad, self.slot_base + 8)
+        """Context for another model sharing this one's signal pad (own barrier slots) and buffer table: buffers are
+        keyed by tag (``alloc_weights(cfg, tag=...)`` on either context), so the clone finds what was allocated for it."""
+        c = DPContext(self.device, self.group, tag, self.pad, self.slot_base + 8)
+        c.buffers = self.buffers
+        return c
 
     # -- layout
     def shard_range(self, total: int) -> Tuple[int, int]:
