@@ -154,3 +154,30 @@ def test_bench_tiny_pipeline_trained_two_ranks():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = _last_json(r.stdout)
     assert line["n_gpus"] == 2 and line["value"] > 0 and line["config"]["parallelism"] == "generation dp2, training pp2"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_runtime_graph_ppo_on_two_ranks(tmp_path):
+    """PPO (actor, critic, reward, reference) through the engine backend on two data-parallel ranks: both optimizers run
+    their fused data-parallel step (the critic's through a cloned context with its own barrier slots)."""
+    from rpeg_b200.runtime.io import dump_mapping
+    from rpeg_b200.runtime.job_plan import plan_runtime_job
+    from rpeg_b200.runtime.trace import read_trace
+    tiny = {"layers": 2, "hidden_dim": 256, "ffn_dim": 512, "vocab_size": 512, "head_dim": 128}
+    cfg = {"run_id": "ppo-2gpu", "policy": {"algorithm": "ppo"}, "hardware": {"preset": "b200_nvswitch"},
+           "device_space": {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 2},
+           "models": {"actor": tiny, "critic": dict(tiny), "reward": dict(tiny), "reference": {"source": "actor"}},
+           "workload": {"batch_size": 8, "samples_per_prompt": 1, "context_length": 32, "generation_length": 48,
+                        "gen_quantiles": [[0.5, 16], [1.0, 48]]},
+           "training": {"max_steps": 2}, "optimizer": {"k_eval": 2}, "runtime_hardware": {"worker_overhead_bytes": 0},
+           "runtime": {"default_backend": "engine", "gen_slots": 8, "micro_tokens": 1024}, "outputs": {"seed": 3}}
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    res = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out", quiet=True)
+    r = _torchrun(2, 29568, "-m", "rpeg_b200.runtime.run", "--config", str(res["run_file"]))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    events = read_trace(tmp_path / "out/traces/run.jsonl")
+    for prefix, key in (("t_pi@", "grad_norm"), ("t_V@", "critic_grad_norm")):
+        fin = [e for e in events if e["event"] == "finish" and e["node_id"].startswith(prefix)]
+        assert len(fin) == 2 and all(e["status"] == "ok" and e["counters"][key] > 0 for e in fin)
+    summary = json.loads((tmp_path / "out/metrics/summary.json").read_text())
+    assert summary["nodes_failed"] == 0 and summary["nonfinite_losses"] == 0
