@@ -29,6 +29,12 @@ def classify(doc: Dict[str, Any]) -> Dict[str, Any]:
         if sv == "rpeg.environment_check.v1":
             detail = {"failed": [c["name"] for c in doc.get("checks", ()) if c.get("required") and not c.get("ok")]}
         return {"kind": sv.split(".")[1], "ok": bool(doc.get("ok")), "detail": detail}
+    if sv == "rpeg.engine_validate.v1":
+        return {"kind": "engine_validate", "ok": bool(doc.get("ok")),
+                "detail": {"world": doc.get("world"), "failed": [c["name"] for c in doc.get("checks", ()) if not c.get("ok")], "error": doc.get("error")}}
+    if sv == "rpeg.cluster_contract.v1":
+        return {"kind": "cluster_contract", "ok": bool(doc.get("performance_comparable")),
+                "detail": {"nodes": doc.get("nodes"), "reasons": doc.get("non_comparable_reasons", [])}}
     if sv == "rpeg.runtime_alerts.v1":
         return {"kind": "alerts", "ok": doc.get("status") != "critical", "detail": {"status": doc.get("status"), "alerts": len(doc.get("alerts", ()))}}
     if sv == "rpeg.runtime_summary.v1":

@@ -76,6 +76,10 @@ def test_environment_check_and_suite_report(tmp_path):
     (tmp_path / "bad.json").write_text(json.dumps({"schema_version": "rpeg.runtime_alerts.v1", "status": "critical", "alerts": [1]}))
     good = aggregate([str(tmp_path / "env.json"), str(tmp_path / "bench.json"), str(tmp_path / "ref.json")])
     assert good["ok"] and [i["kind"] for i in good["items"]] == ["environment_check", "bench", "bench_reference"]
+    from rpeg_b200.runtime.suite_report import classify
+    assert classify({"schema_version": "rpeg.engine_validate.v1", "ok": False, "world": 8, "checks": [{"name": "train_step", "ok": False}]}) == \
+        {"kind": "engine_validate", "ok": False, "detail": {"world": 8, "failed": ["train_step"], "error": None}}
+    assert classify({"schema_version": "rpeg.cluster_contract.v1", "performance_comparable": True, "nodes": 2})["ok"] is True
     bad = aggregate([str(tmp_path / "env.json"), str(tmp_path / "bad.json"), str(tmp_path / "missing.json")])
     assert not bad["ok"] and len(bad["failed"]) == 2
 
