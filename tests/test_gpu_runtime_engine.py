@@ -75,24 +75,3 @@ def test_engine_runs_update_epochs_over_minibatches(tmp_path, cuda_device):
     for prefix in ("t_pi@", "t_V@"):
         fin = [e for e in events if e["event"] == "finish" and e["node_id"].startswith(prefix)]
         assert len(fin) == 1 and fin[0]["counters"]["optimizer_steps"] == 4
-
-
-def test_engine_ends_synthetic_rows_at_quantile_lengths(tmp_path, cuda_device):
-    """``data.synthetic_response_lengths: quantiles``: every row is ended at the length drawn for it from the
-    workload's quantile phases (a natural EOS may still come earlier), so the phases emit rows as the planner assumes."""
-    from rpeg_b200.runtime.data import quantile_lengths
-    from rpeg_b200.runtime.io import dump_mapping, load_mapping
-    run = tiny_job(tmp_path, "grpo", steps=1)
-    m = load_mapping(run)
-    m.setdefault("data", {}).update(synthetic_response_lengths="quantiles")
-    dump_mapping(m, run)
-    compiled = compile_runtime_plan(run)
-    res = execute_compiled(compiled, "engine")
-    assert res["error"] is None and res["verification"]["ok"], (res["error"], res["verification"]["errors"])
-    w = compiled.run_config.workload
-    rows = w.batch_size * w.samples_per_prompt
-    want = quantile_lengths(rows, w.quantile_tuples(), seed=1)               # data_seed 0, logical step 1
-    events = read_trace(tmp_path / "traces/run.jsonl")
-    gen = [e for e in events if e["event"] == "finish" and e["node_id"].startswith("g_pi@") and "generated_tokens" in e["counters"]]
-    assert len(gen) == 1
-    assert 0 < gen[0]["counters"]["generated_tokens"] <= sum(want) < rows * w.generation_length

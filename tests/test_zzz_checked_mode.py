@@ -67,3 +67,28 @@ def test_engine_smoke_worker_passes_on_one_gpu(cuda_device, tmp_path, capsys):
     assert rep["schema_version"] == "rpeg.engine_validate.v1"
     assert rc == 0 and rep["ok"], [c for c in rep["checks"] if not c["ok"]]
     assert [c["name"] for c in rep["checks"]] == ["build", "train_step", "ppo_exercise", "checkpoint", "device_status"]
+
+
+def test_engine_ends_synthetic_rows_at_quantile_lengths(tmp_path, cuda_device):
+    """``data.synthetic_response_lengths: quantiles``: every row is ended at the length drawn for it from the
+    workload's quantile phases (a natural EOS may still come earlier), so the phases emit rows as the planner assumes."""
+    from rpeg_b200.runtime.data import quantile_lengths
+    from rpeg_b200.runtime.io import dump_mapping, load_mapping
+    from test_gpu_runtime_engine import tiny_job
+    run = tiny_job(tmp_path, "grpo", steps=1)
+    m = load_mapping(run)
+    m.setdefault("data", {}).update(synthetic_response_lengths="quantiles")
+    dump_mapping(m, run)
+    from rpeg_b200.runtime.compiler import compile_runtime_plan
+    from rpeg_b200.runtime.run import execute_compiled
+    from rpeg_b200.runtime.trace import read_trace
+    compiled = compile_runtime_plan(run)
+    res = execute_compiled(compiled, "engine")
+    assert res["error"] is None and res["verification"]["ok"], (res["error"], res["verification"]["errors"])
+    w = compiled.run_config.workload
+    rows = w.batch_size * w.samples_per_prompt
+    want = quantile_lengths(rows, w.quantile_tuples(), seed=1)               # data_seed 0, logical step 1
+    events = read_trace(tmp_path / "traces/run.jsonl")
+    gen = [e for e in events if e["event"] == "finish" and e["node_id"].startswith("g_pi@") and "generated_tokens" in e["counters"]]
+    assert len(gen) == 1
+    assert 0 < gen[0]["counters"]["generated_tokens"] <= sum(want) < rows * w.generation_length
