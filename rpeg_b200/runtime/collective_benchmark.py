@@ -43,10 +43,23 @@ def _timed(fn: Callable[[], None], dist, dev, warm: int = 3, iters: int = 10) ->
     return statistics.median(out)
 
 
+def large_message_gate(rows: List[Dict[str, float]], min_gbps: float) -> Dict[str, object]:
+    """The all-reduce bus bandwidth of the LARGEST message against a floor: a job on a node whose NVLink fabric is
+    degraded should fail here, before it trains (reference: ``--min-large-message-gbps`` of
+    RPEG/runtime/collective_benchmark.py:125-164)."""
+    if not rows:
+        return {"ok": False, "min_large_message_gbps": float(min_gbps), "measured_gbps": None, "bytes": None}
+    big = max(rows, key=lambda r: r.get("bytes", 0))
+    got = float(big.get("nccl_all_reduce_busbw_gbs", 0.0))
+    return {"ok": got >= float(min_gbps), "min_large_message_gbps": float(min_gbps), "measured_gbps": got, "bytes": int(big.get("bytes", 0))}
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes", default="1e6,1e7,1e8,1e9", help="bytes per rank, comma separated")
     ap.add_argument("--output", default=None)
+    ap.add_argument("--min-large-message-gbps", type=float, default=0.0,
+                    help="exit 2 when the all-reduce bus bandwidth of the largest message is below this (GB/s)")
     args = ap.parse_args(argv)
     import torch
     import torch.distributed as dist
@@ -89,15 +102,16 @@ def main(argv: Optional[List[str]] = None) -> int:
         dist.barrier()
         sym.close()
         rows.append(row)
+    gate = large_message_gate(rows, args.min_large_message_gbps)
     if rank == 0:
-        rep = {"schema_version": SCHEMA, "world": world, "device": torch.cuda.get_device_name(dev), "rows": rows}
+        rep = {"schema_version": SCHEMA, "world": world, "device": torch.cuda.get_device_name(dev), "rows": rows, "gate": gate}
         if args.output:
             with open(args.output, "w") as f:
                 json.dump(rep, f, indent=1)
         print(json.dumps(rep))
     dist.barrier()
     dist.destroy_process_group()
-    return 0
+    return 0 if gate["ok"] else 2
 
 
 if __name__ == "__main__":

@@ -42,7 +42,7 @@ def classify(doc: Dict[str, Any]) -> Dict[str, Any]:
         return {"kind": "runtime_summary", "ok": ok, "detail": {k: doc.get(k) for k in ("nodes_finished", "nodes_failed", "wall_time_s", "logical_steps")}}
     if sv == "rpeg.collective_benchmark.v1":
         rows = doc.get("rows", ())
-        return {"kind": "collective_benchmark", "ok": bool(rows), "detail": {"world": doc.get("world"),
+        return {"kind": "collective_benchmark", "ok": bool(rows) and bool((doc.get("gate") or {}).get("ok", True)), "detail": {"world": doc.get("world"),
                 "all_reduce_busbw_gbs": max((r.get("nccl_all_reduce_busbw_gbs", 0) for r in rows), default=0)}}
     if sv == "rpeg.cost_calibration.v1":
         return {"kind": "cost_calibration", "ok": doc.get("matched_nodes", 0) > 0, "detail": doc.get("hardware", {})}

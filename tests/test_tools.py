@@ -80,6 +80,12 @@ def test_environment_check_and_suite_report(tmp_path):
     assert classify({"schema_version": "rpeg.engine_validate.v1", "ok": False, "world": 8, "checks": [{"name": "train_step", "ok": False}]}) == \
         {"kind": "engine_validate", "ok": False, "detail": {"world": 8, "failed": ["train_step"], "error": None}}
     assert classify({"schema_version": "rpeg.cluster_contract.v1", "performance_comparable": True, "nodes": 2})["ok"] is True
+    from rpeg_b200.runtime.collective_benchmark import large_message_gate
+    rows = [{"bytes": 10 ** 6, "nccl_all_reduce_busbw_gbs": 40.0}, {"bytes": 10 ** 9, "nccl_all_reduce_busbw_gbs": 550.0}]
+    assert large_message_gate(rows, 300.0) == {"ok": True, "min_large_message_gbps": 300.0, "measured_gbps": 550.0, "bytes": 10 ** 9}
+    assert not large_message_gate(rows, 600.0)["ok"] and not large_message_gate([], 0.0)["ok"] and large_message_gate(rows, 0.0)["ok"]
+    slow = {"schema_version": "rpeg.collective_benchmark.v1", "world": 8, "rows": rows, "gate": large_message_gate(rows, 600.0)}
+    assert classify(slow)["ok"] is False and classify(dict(slow, gate=large_message_gate(rows, 300.0)))["ok"] is True
     bad = aggregate([str(tmp_path / "env.json"), str(tmp_path / "bad.json"), str(tmp_path / "missing.json")])
     assert not bad["ok"] and len(bad["failed"]) == 2
 
