@@ -134,6 +134,8 @@ def main() -> None:
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV cache budget per GPU in GB (0 = pick by world size)")
     ap.add_argument("--micro-tokens", type=int, default=16384)
     ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"])
+    ap.add_argument("--budget-s", type=float, default=420.0,
+                    help="wall-clock budget for warm-up plus timed steps; the timed step count is cut to fit and reported")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) write to file descriptor 1. The contract is ONE JSON line on
     # stdout, so everything else is sent to stderr and the line goes to the saved descriptor at the end.
@@ -192,7 +194,7 @@ def main() -> None:
     algo = A.AlgoConfig(kl_coef=0.04, beta=0.1, micro_tokens=args.micro_tokens, head_chunk=8192)
 
     gen_host = torch.Generator().manual_seed(42)
-    n_iters = args.warmup + 2 * args.steps
+    n_iters = min(args.warmup + args.steps, 12)   # distinct synthetic batches; the loop cycles through them
     if spec["algo"] == "grpo":
         # KV pages are handed out on demand, so the slot count may exceed what the budget holds at full length.
         # One rank keeps the whole fp32 Adam state (81 GB for 7B) and has ~56 GB for KV; sharded ranks have more.
@@ -282,59 +284,147 @@ def main() -> None:
                 p, r = p.to(device), r.to(device)
             return trainer.step(p, r)
 
+    parallelism_text = getattr(trainer, "parallelism", None) or f"dp{world}"
+
+    def extra_metrics(line: dict) -> dict:
+        """The two remaining headline quantities: device time of the weight hand-over from the training layout to the
+        generation layout per iteration, and the planner's predicted step time against the measured one."""
+        extra = {}
+        reshard = getattr(trainer, "last_reshard_us", None)
+        if reshard is not None:
+            extra["reshard_us"] = float(reshard)
+        try:
+            from rpeg_b200.analytic.predict import predict_step_seconds
+            pred = predict_step_seconds(spec, world, parallelism=line["config"]["parallelism"])
+            meas = line["ms_per_step"] / 1e3
+            extra["cost_model"] = {"predicted_s": pred["step_s"], "measured_s": meas, "err": (pred["step_s"] - meas) / meas,
+                                   "phases_s": pred.get("phases_s"), "hardware": pred.get("hardware")}
+            extra["cost_model_err"] = abs(pred["step_s"] - meas) / meas
+        except Exception as exc:  # noqa: BLE001 - the prediction is a report, it must not fail the measurement
+            extra["cost_model"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+        return extra
+
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(first, count, on_device):
-        barrier()
-        launches0 = _lib.launch_count()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        ev0.record()
-        outs = [run(first + j, on_device) for j in range(count)]
-        ev1.record()
-        barrier()
-        ms = torch.tensor([ev0.elapsed_time(ev1)], device=device, dtype=torch.float64)
-        stats = torch.tensor([sum(o["samples"] for o in outs), sum(o.get("gen_tokens", 0.0) for o in outs),
-                              sum(o["train_tokens"] for o in outs)], device=device, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-            dist.all_reduce(stats)
-        return ms.item(), stats.tolist(), _lib.launch_count() - launches0, time.perf_counter() - t0, outs
+    def fail(where: str, exc: BaseException) -> None:
+        """A failed step ends the run at once: the line carries the error, the exit code is non-zero."""
+        emit({"metric": "rlhf_samples_per_sec", "value": None, "impl": "ours", "n_gpus": world, "rank": rank,
+              "error": f"{where}: {type(exc).__name__}: {exc}"})
+        sys.stderr.flush()
+        os._exit(1)
 
-    for i in range(args.warmup):
-        run(i, on_device=False)
+    def checked_run(i: int, tag: str):
+        """One iteration through the public API (pinned host inputs in, python floats out), then the device status
+        word: a kernel whose bounded wait ran out must not let later steps run on its output."""
+        t = time.perf_counter()
+        try:
+            out = run(i % len(batches), on_device=False)
+            K.check_status()
+        except BaseException as exc:  # noqa: BLE001 - reported and re-raised as the exit code
+            fail(f"{tag} step {i}", exc)
+        if rank == 0:
+            print(f"[bench] {tag} {i}: {time.perf_counter() - t:.2f} s  " +
+                  " ".join(f"{k}={v:.0f}" for k, v in out.items() if k.endswith("_ms")), file=sys.stderr, flush=True)
+        return out
+
+    def agree(value: float) -> float:
+        """The same number on every rank (the slowest rank's), so all ranks take the same decisions."""
+        if world == 1:
+            return value
+        t = torch.tensor([value], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # Warm-up: at least three steps (graph capture, allocator growth, clocks), more only while they are cheap.
+    t_begin = time.perf_counter()
+    budget = float(args.budget_s)
+    n_warm = 0
+    step_s = 0.0
+    while n_warm < max(args.warmup, 0):
+        t = time.perf_counter()
+        checked_run(n_warm, "warmup")
+        step_s = agree(time.perf_counter() - t)
+        n_warm += 1
+        spent = agree(time.perf_counter() - t_begin)
+        if n_warm >= min(3, args.warmup) and spent + step_s * 2 > 0.35 * budget:
+            break
+    spent = agree(time.perf_counter() - t_begin)
+    n_steps = args.steps
+    if step_s > 0.0:
+        n_steps = max(1, min(args.steps, int((budget - spent) / (1.08 * step_s))))
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    ms, stats, launches, _, outs = timed(args.warmup, args.steps, on_device=True)
-    ms_e2e, stats_e2e, _, wall_e2e, outs_e2e = timed(args.warmup + args.steps, args.steps, on_device=False)
+    barrier()
+    launches0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    ev0.record()
+    outs = [checked_run(n_warm + j, "timed") for j in range(n_steps)]
+    ev1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    launches = _lib.launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
-    K.check_status()
+    # e2e: CUDA events around the K public-API calls (pinned-host inputs copied in, metrics read back, every step).
+    # value: the same K steps without the copies - per step, the events the trainer records after its inputs are on
+    # the device and after its last optimizer kernel. Both are the maximum over ranks.
+    dev_ms = sum(o.get("device_ms", 0.0) for o in outs)
+    times = torch.tensor([ev0.elapsed_time(ev1), dev_ms if dev_ms > 0.0 else ev0.elapsed_time(ev1)], device=device, dtype=torch.float64)
+    stats = torch.tensor([sum(o["samples"] for o in outs), sum(o.get("gen_tokens", 0.0) for o in outs),
+                          sum(o["train_tokens"] for o in outs)], device=device, dtype=torch.float64)
+    phase_keys = sorted({k for o in outs for k in o if k.endswith("_ms") and k != "device_ms"})
+    phases = torch.tensor([sum(o.get(k, 0.0) for o in outs) / n_steps for k in phase_keys], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(stats)
+        if len(phase_keys):
+            dist.all_reduce(phases, op=dist.ReduceOp.MAX)
+    ms_e2e, ms = times.tolist()
+    stats = stats.tolist()
 
     if rank == 0:
         secs = ms / 1e3
+        algo_name = spec["algo"]
+        model_txt = {"grpo": f"{spec['model']} x2 (actor + frozen reference)", "grpo_async": f"{spec['model']} x2 (actor + frozen reference)",
+                     "dpo": f"{spec['model']} x2 (policy + frozen reference)",
+                     "ppo": f"{spec['model']} actor" + ("+critic shared trunk" if spec.get("shared") else ", critic") + ", reference, reward"}[algo_name]
+        if algo_name == "grpo_async":
+            par = f"gen{world // 2}+train{world - world // 2}, staleness {spec.get('tau', 1)}"
+        elif spec.get("pipeline_train"):
+            par = f"generation dp{world}, training pp{world}"
+        else:
+            par = parallelism_text
+        phase_ms = {k: round(v, 3) for k, v in zip(phase_keys, phases.tolist())}
         line = {
             "metric": "rlhf_samples_per_sec", "value": stats[0] / secs, "unit": "samples/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "steps": n_steps, "warmup": n_warm, "steps_requested": args.steps, "warmup_requested": args.warmup,
+            "ms_per_step": ms / n_steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "gen_tokens_per_sec": stats[1] / secs, "train_tokens_per_sec": stats[2] / secs,
-            "config": {"model": {"grpo": f"{spec['model']} x2 (actor + frozen reference)", "grpo_async": f"{spec['model']} x2 (actor + frozen reference)", "dpo": f"{spec['model']} x2 (policy + frozen reference)", "ppo": f"{spec['model']} actor" + ("+critic shared trunk" if spec.get("shared") else ", critic") + ", reference, reward"}[spec["algo"]] + ", random init", "algorithm": spec["algo"],
-                       "global_batch": B * Kk if spec["algo"] in ("grpo", "grpo_async") else B, "prompts": B, "samples_per_prompt": Kk,
+            "config": {"model": model_txt + ", random init", "algorithm": algo_name,
+                       "global_batch": B * Kk if algo_name in ("grpo", "grpo_async") else B, "prompts": B, "samples_per_prompt": Kk,
                        "seq_len": S + T, "prompt_len": S, "max_new_tokens": T, "gen_quantiles": spec["quantiles"],
-                       "parallelism": (f"gen{world // 2}+train{world - world // 2}, staleness {spec.get('tau', 1)}" if spec["algo"] == "grpo_async" else (f"generation dp{world}, training pp{world}" if spec.get("pipeline_train") else f"dp{world}")), "optimizer": "adamw fp32 master, sharded over dp",
-                       "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if spec["algo"] in ("grpo", "grpo_async", "ppo") else None,
-                       "l2": "working set (13.5 GB of weights per model) far exceeds the 126 MB L2; no flush needed"},
-            "e2e": {"value": stats_e2e[0] / (ms_e2e / 1e3), "unit": "samples/s", "ms_per_step": ms_e2e / args.steps,
-                    "wall_s_per_step": wall_e2e / args.steps, "h2d_bytes_per_step": int(trainer.h2d_bytes),
-                    "d2h_bytes_per_step": int(trainer.d2h_bytes), "gen_tokens_per_sec": stats_e2e[1] / (ms_e2e / 1e3)},
+                       "parallelism": par, "optimizer": "adamw fp32 master, sharded over dp",
+                       "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if algo_name in ("grpo", "grpo_async", "ppo") else None,
+                       "l2": "working set (13.5 GB of weights per model) far exceeds the 126 MB L2; no flush needed",
+                       "time_budget_s": budget},
+            "e2e": {"value": stats[0] / (ms_e2e / 1e3), "unit": "samples/s", "ms_per_step": ms_e2e / n_steps,
+                    "wall_s_per_step": wall / n_steps, "h2d_bytes_per_step": int(trainer.h2d_bytes),
+                    "d2h_bytes_per_step": int(trainer.d2h_bytes), "gen_tokens_per_sec": stats[1] / (ms_e2e / 1e3)},
+            "timing": "one loop of public-API steps; e2e = CUDA events around the loop (pinned H2D + metric D2H every step); "
+                      "value = sum of the per-step device intervals (inputs on device -> last optimizer kernel); max over ranks",
             "gpu_launches": int(launches), "clocks": clocks,
-            "last_step": {k: round(v, 6) for k, v in outs_e2e[-1].items()},
+            "phase_ms_per_step": phase_ms,
+            "last_step": {k: round(v, 6) for k, v in outs[-1].items()},
             "generation_counters": dict(getattr(trainer, "last_counters", {}) or {}),
             "published_other_hw": "reference paper data: 7B PPO on 8xA100-40GB, 1.73 samples/s (different config)",
         }
+        line.update(extra_metrics(line))
         emit(line)
     if world > 1:
         dist.destroy_process_group()

@@ -60,8 +60,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const int* _
   uint64_t* v_empty = v_full + FA_KV_STAGES;
   uint64_t* s_full = v_empty + FA_KV_STAGES;  // [2]
   uint64_t* p_full = s_full + 2;              // [2]
-  uint64_t* pv_done = p_full + 2;             // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+  uint64_t* pv_done = p_full + 2;             // [2]: PV_j completes pv_done[j & 1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -72,7 +72,8 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const int* _
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4); }
-    mbar_init(pv_done, 1);
+    mbar_init(&pv_done[0], 1);
+    mbar_init(&pv_done[1], 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -152,7 +153,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const int* _
                          (j | k) != 0 ? 1u : 0u);
           }
           umma_commit(&v_empty[st]);
-          umma_commit(pv_done);
+          umma_commit(&pv_done[j & 1]);
         }
       }
     }
@@ -164,22 +165,21 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const int* _
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    // pv_done completes once per KV tile. A parity wait only tells "that phase is over" when the
-    // waiter is at most one phase behind, so every completion is consumed in order: completion
-    // j-2 is already implied by s_full[j] (QK_j is issued after PV_{j-2}) and costs nothing.
-    int pv_seen = 0;
-    auto wait_pv = [&](int upto, int where) -> bool {
-      while (pv_seen <= upto) {
-        if (!__all_sync(0xffffffffu, mbar_wait(pv_done, static_cast<uint32_t>(pv_seen) & 1u, abort_flag, status, where)))
-          return false;
-        ++pv_seen;
-      }
-      return true;
+    // PV_j arrives on pv_done[j & 1], so each of the two barriers completes once per TWO tiles and its
+    // completion number for PV_j is j >> 1. A parity wait is only right when the waiter is at most one
+    // phase behind. That holds here: a warp that has seen s_full[j] knows every MMA issued before QK_j
+    // has completed, PV_{j-2} and PV_{j-3} among them, and PV_{j+1} cannot be issued before this warp
+    // has delivered P_{j+1}. So when it asks for PV_{j-1} (or, after the loop, for PV_{n-1}) the
+    // barrier of that parity has finished either exactly the completions before the wanted one, or the
+    // wanted one too. (With ONE barrier completing every tile a warp could be two phases behind and
+    // then waited for a completion that needed its own next arrival.)
+    auto wait_pv = [&](int tile, int where) -> bool {
+      return __all_sync(0xffffffffu, mbar_wait(&pv_done[tile & 1], static_cast<uint32_t>(tile >> 1) & 1u, abort_flag,
+                                               status, where));
     };
     for (int j = 0; j < n_tiles && ok; ++j) {
       const uint32_t ts = tmem_base + lane_base + static_cast<uint32_t>((j & 1) * 128);
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, status, 520))) { ok = false; break; }
-      if (!wait_pv(j - 2, 523)) { ok = false; break; }
       tc_fence_after_sync();
       const int k0 = j * FA_BN;
       const bool need_mask = (k0 + FA_BN - 1 > q0) || (k0 + FA_BN > L);

@@ -56,6 +56,9 @@ class _Base:
         out: Dict[str, float] = {}
         for (_, a), (name, b) in zip(self._marks, self._marks[1:]):
             out[f"{name}_ms"] = out.get(f"{name}_ms", 0.0) + a.elapsed_time(b)
+        if len(self._marks) > 1:
+            # first mark (inputs are on the device) to last mark (the optimizer's last kernel)
+            out["device_ms"] = self._marks[0][1].elapsed_time(self._marks[-1][1])
         self._marks = []
         return out
 
@@ -176,20 +179,25 @@ class DPOTrainer(_Base):
         r_dev = _h2d(resp_ids, self.device, torch.int32)
         N, S = p_dev.shape
         T = r_dev.shape[1]
+        self._mark("begin")
         lens = [T] * N if resp_lens is None else [int(x) for x in resp_lens.tolist()]
         lens_t = torch.tensor(lens, device=self.device)
         mask = (torch.arange(T, device=self.device)[None, :] < lens_t[:, None]).float()
         ro = A.Rollout(p_dev, [S] * N, r_dev, lens, torch.zeros((N, T), dtype=torch.float32, device=self.device), mask)
         ref_lp = A.sequence_logprobs(self.ref, ro, self.algo)
         ref_seq = K.masked_rowsum(ref_lp, mask)
+        self._mark("reference")
         pairs = int(self._global_sum(N // 2))
         self.policy.zero_grad()
         m = A.dpo_train_step(self.policy, ro, ref_seq, self.algo, n_pairs_global=pairs)
+        self._mark("train")
         self.opt.step()
+        self._mark("optimizer")
         self.iteration += 1
         self.weight_version += 1
         m["grad_norm"] = self.opt.grad_norm()
         out = self._read(m)
+        out.update(self._phase_ms())
         out.update(samples=float(N // 2), train_tokens=float(sum(ro.total_lens())), wall_s=time.perf_counter() - t0)
         return out
 
@@ -241,28 +249,38 @@ class PPOTrainer(_Base):
         self.h2d_bytes = prompts.numel() * prompts.element_size()
         p_dev = _h2d(prompts, self.device, torch.int32).contiguous()
         N, S = p_dev.shape
+        self._mark("begin")
         gen = self.gen.generate(p_dev, self.max_new, temperature=self.algo.temperature,
                                 seed=self.seed + 100003 * self.iteration, forced_lens=forced_lens)
         resp_lens = gen.lengths.tolist()
+        self._mark("generate")
         ro = A.Rollout(p_dev, [S] * N, gen.tokens, resp_lens, gen.logprobs, gen.response_mask(),
                        weight_version=self.weight_version)
         ro.ref_logp = A.sequence_logprobs(self.ref, ro, self.algo)
+        self._mark("reference")
         ro.scores = A.reward_scores(self.reward, ro, self.algo)
+        self._mark("reward")
         ro.values = A.critic_values(self.actor if self.shared else self.critic, ro, self.algo)
         A.ppo_targets(ro, self.algo)
+        self._mark("values")
         denom = self._global_sum(ro.n_response_tokens())
         self.actor.zero_grad()
         m = A.policy_train_step(self.actor, ro, self.algo, denom_tokens=denom, value_model_shared=self.shared)
+        self._mark("train")
         self.opt_actor.step()
+        self._mark("optimizer")
         if self.critic is not None:
             self.critic.zero_grad()
             m.update(A.critic_train_step(self.critic, ro, self.algo, denom_tokens=denom))
+            self._mark("critic_train")
             self.opt_critic.step()
+            self._mark("critic_optimizer")
         self.weight_version += 1
         self.iteration += 1
         m["grad_norm"] = self.opt_actor.grad_norm()
         m["mean_score"] = ro.scores.mean()
         out = self._read(m)
+        out.update(self._phase_ms())
         out.update(samples=float(N), gen_tokens=float(sum(resp_lens)), train_tokens=float(sum(ro.total_lens())),
                    wall_s=time.perf_counter() - t0)
         self.last_counters = dict(gen.counters)

@@ -1,9 +1,6 @@
 """GPU test of checked mode (``RPEG_CHECK_ARGS`` / ``ops.checked.set_enabled``): a whole GRPO step (generation without
 graphs, reference pass, policy step) runs with every data-dependent index validated before its launch, and a stray
-index is refused BEFORE the kernel that would have followed it is launched.
-
-Collected after the other GPU tests (file name): it exercises the same kernels with extra host checks and adds
-nothing to their numerics coverage."""
+index is refused BEFORE the kernel that would have followed it is launched."""
 import pytest
 import torch
 

@@ -1,7 +1,5 @@
 """GPU numerics of the entropy bonus: the entropy kernel and the combined log-prob + entropy backward against PyTorch
-fp32 autograd on the same bf16 logits, and a policy step whose loss moves by ``-entropy_coef * mean entropy``.
-
-Collected after the other GPU tests (file name)."""
+fp32 autograd on the same bf16 logits, and a policy step whose loss moves by ``-entropy_coef * mean entropy``."""
 import pytest
 import torch
 

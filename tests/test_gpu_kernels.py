@@ -346,6 +346,32 @@ def test_flash_attn_fwd(cuda_device, lens, H, Hkv):
         off += l
 
 
+def test_flash_attn_fwd_long_rows_many_heads(cuda_device):
+    """32 heads, sequences of 20 to 24 key tiles, several waves of CTAs and repeated launches: the shape of the
+    training step, where late K tiles let a P*V product finish before a softmax warp looks at its barrier."""
+    hd, H = 128, 32
+    lens = [2560, 3072, 2561, 2944]
+    T = sum(lens)
+    qkv = (torch.randn(T, 3 * H * hd, device=cuda_device) * 0.5).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=cuda_device, dtype=torch.int32)
+    out = lse = None
+    for _ in range(20):
+        out, lse = K.flash_attn_fwd(qkv, 0, H * hd, 2 * H * hd, cu, max(lens), H, H, hd)
+    K.check_status()
+    off = 0
+    for l in lens:
+        for h in (0, 13, 31):
+            q = qkv[off:off + l, h * hd:(h + 1) * hd].float()
+            k = qkv[off:off + l, (H + h) * hd:(H + h + 1) * hd].float()
+            v = qkv[off:off + l, (2 * H + h) * hd:(2 * H + h + 1) * hd].float()
+            s = q @ k.t() / math.sqrt(hd)
+            s = s.masked_fill(torch.triu(torch.ones(l, l, device=cuda_device, dtype=torch.bool), 1), float("-inf"))
+            ref = torch.softmax(s, -1) @ v
+            assert _rel_err(out[off:off + l, h * hd:(h + 1) * hd], ref) < 1e-2
+            assert torch.allclose(lse[h, off:off + l], torch.logsumexp(s, -1), atol=2e-2, rtol=1e-3)
+        off += l
+
+
 @pytest.mark.parametrize("lens", [[128], [5, 130, 257], [1000, 31, 384]])
 @pytest.mark.parametrize("H,Hkv", [(4, 4), (4, 2), (8, 2)])
 def test_flash_attn_bwd(cuda_device, lens, H, Hkv):

@@ -1,7 +1,5 @@
-"""Multi-GPU tests of the newer engine plan families and of PPO on two ranks (skipped on a single-GPU box).
-
-Collected after the other GPU tests (file name): these have not run on a GPU as often as the ones in
-``test_gpu_multi.py``, whose launch helpers they share."""
+"""Multi-GPU tests of the engine plan families (pipeline-parallel training, disjoint generation and training GPUs)
+and of PPO on two ranks; skipped on a single-GPU box. The launch helpers are those of ``test_gpu_multi.py``."""
 import json
 import os
 import subprocess
