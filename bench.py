@@ -56,9 +56,74 @@ CONFIGS = {
 }
 
 
-def _reference_unavailable() -> str:
-    return ("reference not installable offline: build backend 'hatchling' missing from the wheelhouse, its runtime "
-            "needs megatron-core==0.17.0 + Slurm (absent), and the shipped tree has import-time errors")
+MODEL_SHAPES = {
+    "llama7b": dict(layers=32, hidden=4096, ffn=11008, heads=32, kv_heads=32, vocab=32000),
+    "llama13b": dict(layers=40, hidden=5120, ffn=13824, heads=40, kv_heads=40, vocab=32000),
+    "tiny": dict(layers=2, hidden=256, ffn=512, heads=2, kv_heads=2, vocab=512),
+}
+PLANNER_CONFIG = os.path.join(os.path.dirname(os.path.abspath(__file__)), "configs", "example_ppo_32gpu.yaml")
+
+
+def reference_arm(args, spec, world: int) -> dict:
+    """Runs the reference's own code (baseline/ref_arm.py) and returns the JSON line of the reference arm."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    import ref_arm
+    from pathlib import Path
+    base = {"impl": "reference", "n_gpus": world, "steps": args.steps, "warmup": args.warmup}
+    try:
+        if args.config == "planner_32gpu":
+            r = ref_arm.planner_arm(Path(PLANNER_CONFIG))
+            return {**base, "metric": "planner_predicted_tokens_per_sec", "value": r["optimized_tokens_per_s"], "unit": "tokens/s (predicted)",
+                    "higher_is_better": True, "search_wall_s": r["search_wall_s"], "detail": r,
+                    "config": {"model": "PPO, 3 x 7B-shape, 32 GPUs (1 x 8 x 4), example alpha-beta constants", "seed": 42}}
+        if world > 1:
+            try:
+                import megatron.core  # noqa: F401
+                why = "its multi-GPU backend also needs a Slurm launcher, which this box does not have"
+            except Exception as exc:  # noqa: BLE001
+                why = f"its multi-GPU backend (runtime.default_backend=megatron) needs megatron-core==0.17.0: {type(exc).__name__}: {exc}"
+            return {**base, "unavailable": f"reference cannot run on {world} GPUs here: {why}; its torch backend accepts single-device plans only "
+                                          "(RPEG/runtime/algorithms/ppo_graph.py:950-963)"}
+        import tempfile
+        work = Path(tempfile.mkdtemp(prefix="rpeg_ref_arm_"))
+        r = ref_arm.torch_arm(algo=spec["algo"], model=MODEL_SHAPES[spec["model"]], prompts=spec["prompts"], samples_per_prompt=spec["k"],
+                              prompt_len=spec["prompt_len"], max_new=spec["max_new"], quantiles=spec["quantiles"], steps=max(1, min(args.steps, 3)),
+                              warmup=min(args.warmup, 1), workdir=work)
+        return {**base, "metric": "rlhf_samples_per_sec", "value": r["samples_per_s"], "unit": "samples/s", "higher_is_better": True,
+                "steps": r["steps"], "ms_per_step": 1e3 * r["seconds"] / r["steps"], "gen_tokens_per_sec": r["gen_tokens_per_s"],
+                "e2e": {"value": r["samples_per_s"], "unit": "samples/s", "note": "the reference's trace is host-timed around each node, input tokenisation and copies included"},
+                "dtype": "bf16", "data": "synthetic",
+                "config": {"model": f"{spec['model']} (HF LlamaForCausalLM, random init)", "algorithm": spec["algo"], "prompts": spec["prompts"],
+                           "samples_per_prompt": spec["k"], "prompt_len": spec["prompt_len"], "max_new_tokens": spec["max_new"],
+                           "parallelism": "single device, runtime.default_backend=torch_grpo",
+                           "note": "the stock path has no forced EOS lengths: rows stop at EOS or at max_new_tokens"}}
+    except ref_arm.ReferenceUnavailable as exc:
+        return {**base, "unavailable": str(exc)}
+    except Exception as exc:  # noqa: BLE001
+        return {**base, "unavailable": f"{type(exc).__name__}: {exc}"}
+
+
+def planner_bench(args) -> dict:
+    """Our planner on the 32-GPU PPO example (CPU only): predicted throughput of the optimized plan and search wall time."""
+    import contextlib
+    import io
+    import re
+    from rpeg_b200.planner import pipeline as planner
+    buf = io.StringIO()
+    t0 = time.perf_counter()
+    with contextlib.redirect_stdout(buf):
+        planner.main(["--config", PLANNER_CONFIG])
+    wall = time.perf_counter() - t0
+    out = buf.getvalue()
+    m = re.search(r"Throughput \(tokens/s\)\s+(\S+)\s+(\S+)\s+(\S+)", out)
+    mw = re.search(r"wall time\s+([0-9.]+)\s*s", out)
+    if not m:
+        raise SystemExit("planner printed no result table:\n" + out[-2000:])
+    return {"impl": "ours", "metric": "planner_predicted_tokens_per_sec", "value": float(m.group(3)), "unit": "tokens/s (predicted)",
+            "higher_is_better": True, "n_gpus": 0, "steps": 1, "warmup": 0, "search_wall_s": float(mw.group(1)) if mw else wall,
+            "process_wall_s": wall, "greedy_tokens_per_s": float(m.group(1)), "heuristic_tokens_per_s": float(m.group(2)),
+            "gpu_launches": 0, "data": "synthetic",
+            "config": {"model": "PPO, 3 x 7B-shape, 32 GPUs (1 x 8 x 4), example alpha-beta constants", "seed": 42}}
 
 
 class ClockSampler:
@@ -129,7 +194,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="grpo_7b", choices=sorted(CONFIGS))
+    ap.add_argument("--config", default="grpo_7b", choices=sorted(CONFIGS) + ["planner_32gpu"])
     ap.add_argument("--gen-slots", type=int, default=0)
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV cache budget per GPU in GB (0 = pick by world size)")
     ap.add_argument("--micro-tokens", type=int, default=16384)
@@ -152,7 +217,11 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         if rank == 0:
-            emit({"impl": "reference", "unavailable": _reference_unavailable()})
+            emit(reference_arm(args, CONFIGS.get(args.config), world))
+        return
+    if args.config == "planner_32gpu":
+        if rank == 0:
+            emit(planner_bench(args))
         return
     if world != args.gpus:
         if args.gpus == 1 and world == 1:

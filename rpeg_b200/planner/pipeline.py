@@ -330,21 +330,56 @@ def summarize(name: str, cfg: Optional[Configuration], cache, suite, workload, h
     cm = NodeCostModel(hw, suite, workload, optimizer_stage=policy.optimizer_stage,
                        activation_checkpointing=policy.activation_checkpointing)
     flops = sum(cm._work(n) for n in trace.start if n.kind.value == "op")
-    return {"name": name, "tokens_per_s": score, "makespan_s": trace.makespan(), "pflops": flops / trace.makespan() / 1e15,
+    # the trace spans K_eval iterations while tokens/s and the makespan are per iteration: so is the FLOP rate
+    return {"name": name, "tokens_per_s": score, "makespan_s": trace.makespan(), "pflops": flops / max(K_eval, 1) / trace.makespan() / 1e15,
             "utilization": trace.utilization(), "active_gpus": trace.n_active(), "feasible": feasible, "trace": trace}
 
 
+def _span(lo: int, n: int) -> str:
+    return f"{lo}" if n == 1 else f"{lo}-{lo + n - 1}"
+
+
+def _where(a) -> str:
+    (r0, n0, g0), (re, ne, ge) = a.origin, a.extent
+    return f"r{_span(r0, re)} n[{_span(n0, ne)}] g[{_span(g0, ge)}]"
+
+
+def print_plan_changes(base: Optional[Configuration], best: Configuration) -> None:
+    """One line per vertex: parallelism, microbatches and placement of the starting plan and, after ``->``, what the
+    search changed. The layout and the labels are those of the reference's result listing (pipeline.py:1741-1747),
+    so scripts that read its logs read these too."""
+    print("\n  Per-vertex plan (base \u2192 optimal):")
+    print(f"    {'':2} {'vertex':<7} {'parallelism (dp,pp,tp)':<24} {'mb':>5}  placement (rack, nodes, gpus)")
+    print(f"    {'':2} {'\u2500' * 6:<7} {'\u2500' * 22:<24} {'\u2500' * 5:>5}  {'\u2500' * 42}")
+    for vid in sorted(best.plan.pi):
+        new_pi, new_mb, new_at = best.plan.pi[vid], best.plan.mb.get(vid, 1), _where(best.plan.sigma[vid])
+        if base is not None and vid in base.plan.pi:
+            old_pi, old_mb, old_at = base.plan.pi[vid], base.plan.mb.get(vid, 1), _where(base.plan.sigma[vid])
+        else:
+            old_pi, old_mb, old_at = new_pi, new_mb, new_at
+        fmt = lambda t: "(" + ",".join(str(x) for x in t) + ")"
+        par = fmt(old_pi) if old_pi == new_pi else f"{fmt(old_pi)} -> {fmt(new_pi)}"
+        mb = f"{old_mb}" if old_mb == new_mb else f"{old_mb}->{new_mb}"
+        at = old_at if old_at == new_at else f"{old_at}  ->  {new_at}"
+        changed = "*" if (old_pi, old_mb, old_at) != (new_pi, new_mb, new_at) else " "
+        print(f"    {changed:2} {vid:<7} {par:<24} {mb:>5}  {at}")
+
+
 def print_table(rows: List[dict], total_gpus: int) -> None:
+    """Result table with the reference's row labels and column order (Greedy, Conc. Heuristic, Optimized, delta against
+    greedy)."""
     rows = [r for r in rows if r]
-    print("\n  " + "-" * 74)
-    print(f"  {'':<16}" + "".join(f"{r['name']:>19}" for r in rows))
-    print("  " + "-" * 74)
-    print(f"  {'tokens/s':<16}" + "".join(f"{r['tokens_per_s']:>19.4e}" for r in rows))
-    print(f"  {'makespan (s)':<16}" + "".join(f"{r['makespan_s']:>19.3f}" for r in rows))
-    print(f"  {'PFLOP/s':<16}" + "".join(f"{r['pflops']:>19.4f}" for r in rows))
-    print(f"  {'GPU util (%)':<16}" + "".join(f"{100 * r['utilization']:>19.1f}" for r in rows))
-    print(f"  {'active GPUs':<16}" + "".join(f"{str(r['active_gpus']) + '/' + str(total_gpus):>19}" for r in rows))
-    print("  " + "-" * 74)
+    first, last = rows[0], rows[-1]
+    delta = f"{100 * (last['tokens_per_s'] / first['tokens_per_s'] - 1):+.1f}%" if len(rows) > 1 and first["tokens_per_s"] > 0 else ""
+    head = f"  {'Metric':<28}" + "".join(f"  {r['name']:>16}" for r in rows) + f"  {'\u0394 (vs greedy)':>14}"
+    print("\n" + head)
+    print(f"  {'\u2500' * 28}" + "".join(f"  {'\u2500' * 16}" for _ in rows) + f"  {'\u2500' * 14}")
+    print(f"  {'Throughput (tokens/s)':<28}" + "".join(f"  {r['tokens_per_s']:>16.4e}" for r in rows) + f"  {delta:>14}")
+    print(f"  {'Makespan (s)':<28}" + "".join(f"  {r['makespan_s']:>16.4e}" for r in rows))
+    print(f"  {'Throughput (PFLOP/s)':<28}" + "".join(f"  {r['pflops']:>16.4f}" for r in rows) + f"  {delta:>14}")
+    print(f"  {'GPU utilization':<28}" + "".join(f"  {100 * r['utilization']:>15.1f}%" for r in rows))
+    print(f"  {'Active GPUs':<28}" + "".join(f"  {r['active_gpus']:>16}" for r in rows))
+    print(f"  baseline_feasible: {bool(first['feasible'])}")
 
 
 def run_pipeline(cfg: dict, *, time_budget_s: Optional[float] = None, seed_plan: Optional[str] = None,
@@ -394,13 +429,19 @@ def run_pipeline(cfg: dict, *, time_budget_s: Optional[float] = None, seed_plan:
         best = polish(best, suite, workload, hw, K_eval, opt_cfg, cache, ac_share=Model.AC_SHARE in best.rpeg.trainable)
     wall = time.perf_counter() - t0
     rows.append(summarize("Optimized", best, cache, suite, workload, hw, K_eval, mem_policy))
+    st = cache.stats()
+    print("\n  Search statistics")
+    print(f"    wall time   {wall:.1f}s")
+    print(f"    cache       hits={st['hits']}  misses={st['misses']}  total={st['hits'] + st['misses']}  hit_rate={100 * st['hit_rate']:.1f}%")
+    print(f"    evaluations {report[0].evaluations}")
+    print("\n  Structure")
+    print(f"    ac_share    {Model.AC_SHARE in best.rpeg.trainable}")
+    print("    tau         {" + ", ".join(f"{getattr(m, 'value', m)}:{t}" for m, t in sorted(best.rpeg.tau.items(), key=lambda kv: str(kv[0]))) + "}")
+    print_plan_changes(seed_cfg, best)
     print_table(rows, space.num_devices())
     ref = rows[1] or rows[0]
     if ref and rows[2]:
         print(f"  Improvement over {ref['name']}: {100 * (rows[2]['tokens_per_s'] / ref['tokens_per_s'] - 1):+.1f}%")
-    st = cache.stats()
-    print(f"  Search wall time: {wall:.1f} s | evaluations: {report[0].evaluations} | cache hits {st['hits']} / misses "
-          f"{st['misses']} ({100 * st['hit_rate']:.1f}%)")
     print(report[0].moves)
     if out.get("opt_plan"):
         save_plan(best, out["opt_plan"])
