@@ -199,6 +199,11 @@ def main() -> None:
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV cache budget per GPU in GB (0 = pick by world size)")
     ap.add_argument("--micro-tokens", type=int, default=16384)
     ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"])
+    ap.add_argument("--gen-parallel", default="auto", choices=["auto", "dp", "tp"],
+                    help="generation layout on more than one GPU: tensor parallel over all ranks (every rank decodes the whole "
+                         "batch on its weight shard) or data parallel (every rank decodes its rows on the whole model); auto = tp")
+    ap.add_argument("--tp-comm", default=None, choices=["auto", "nvls", "peer"],
+                    help="tensor-parallel decode collectives: NVLS multimem or plain peer loads/stores (default: RPEG_TP_COMM or auto)")
     ap.add_argument("--budget-s", type=float, default=420.0,
                     help="wall-clock budget for warm-up plus timed steps; the timed step count is cut to fit and reported")
     args = ap.parse_args()
@@ -268,7 +273,8 @@ def main() -> None:
         # KV pages are handed out on demand, so the slot count may exceed what the budget holds at full length.
         # One rank keeps the whole fp32 Adam state (81 GB for 7B) and has ~56 GB for KV; sharded ranks have more.
         # the K samples of a prompt share its KV pages, so the pool holds every row of the rank at once
-        slots = args.gen_slots or min(b_local * Kk, 256)
+        gen_tp = world > 1 and args.gen_parallel in ("auto", "tp") and not spec.get("pipeline_train")
+        slots = args.gen_slots or min((B if gen_tp else b_local) * Kk, 256)
         kv_gb = args.kv_gb or {1: 56.0, 2: 76.0}.get(world, 96.0)
         if spec.get("pipeline_train"):
             from rpeg_b200.engine.trainers import PipelineGRPOTrainer
@@ -276,7 +282,8 @@ def main() -> None:
                                           gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)
         else:
             trainer = GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp,
-                                  gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)
+                                  gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2,
+                                  gen_tp=gen_tp, tp_comm=args.tp_comm)
         batches = []
         for _ in range(n_iters):
             prompts = torch.randint(3, cfg.vocab, (B, S), generator=gen_host, dtype=torch.int32)
@@ -383,6 +390,10 @@ def main() -> None:
         emit({"metric": "rlhf_samples_per_sec", "value": None, "impl": "ours", "n_gpus": world, "rank": rank,
               "error": f"{where}: {type(exc).__name__}: {exc}"})
         sys.stderr.flush()
+        if world > 1:
+            # The peers find out through their own bounded waits (2 s). Leave only after they had time to stop
+            # launching kernels that address this rank's memory.
+            time.sleep(6.0)
         os._exit(1)
 
     def checked_run(i: int, tag: str):
@@ -496,6 +507,9 @@ def main() -> None:
         line.update(extra_metrics(line))
         emit(line)
     if world > 1:
+        gm = getattr(trainer, "gen_model", None)
+        if getattr(gm, "comm", None) is not None:
+            gm.comm.close()                      # no kernel addresses a peer after this barrier
         dist.destroy_process_group()
 
 

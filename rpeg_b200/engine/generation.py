@@ -73,10 +73,11 @@ class Generator:
     GROUP_MIN = 3              # smaller groups are cheaper row by row
 
     @staticmethod
-    def kv_bytes_for(cfg, slots: int, max_seq_len: int) -> int:
-        """Bytes of KV storage that ``slots`` rows of up to ``max_seq_len`` tokens need (+ scratch page)."""
+    def kv_bytes_for(cfg, slots: int, max_seq_len: int, tp: int = 1) -> int:
+        """Bytes of KV storage that ``slots`` rows of up to ``max_seq_len`` tokens need (+ scratch page) on one of
+        ``tp`` tensor-parallel ranks (each keeps its own KV heads)."""
         pages = slots * ((max_seq_len + PAGE - 1) // PAGE) + 1
-        return 2 * cfg.n_layers * pages * cfg.n_kv_heads * PAGE * cfg.head_dim * 2
+        return 2 * cfg.n_layers * pages * (cfg.n_kv_heads // tp) * PAGE * cfg.head_dim * 2
 
     def __init__(self, model: LlamaModel, *, max_slots: int = 64, max_seq_len: int = 2048, kv_budget_bytes: float = 16e9,
                  eos_id: int = 2, pad_id: int = 0, sync_interval: int = 8, use_graphs: bool = True,
@@ -85,6 +86,11 @@ class Generator:
         them; lets the cache share memory with buffers that are dead during generation (gradients)."""
         cfg = model.cfg
         self.model, self.cfg, self.dev = model, cfg, model.device
+        # a tensor-parallel model (models.tp_decode.TPDecodeModel) keeps only its own heads in the cache
+        # with peers in the decode step a lost rank must end the loop at the next host sync, not at the length cap
+        self.check_status_every_sync = getattr(model, "tp", 1) > 1
+        self.n_kv = getattr(model, "n_kv_local", cfg.n_kv_heads)
+        self.n_heads = getattr(model, "n_heads_local", cfg.n_heads)
         self.eos_id, self.pad_id = eos_id, pad_id
         # rows that alias a prompt's KV pages are attended to as a group: the shared keys are read once per group
         self.group_attention = bool(group_attention) and not cfg.qk_norm
@@ -92,7 +98,7 @@ class Generator:
         self.use_graphs = use_graphs
         self.max_seq_len = max_seq_len
         self.pages_per_row = (max_seq_len + PAGE - 1) // PAGE
-        page_bytes = 2 * cfg.n_layers * cfg.n_kv_heads * PAGE * cfg.head_dim * 2
+        page_bytes = 2 * cfg.n_layers * self.n_kv * PAGE * cfg.head_dim * 2
         if kv_storage is not None:
             kv_budget_bytes = kv_storage.numel() * 2
         num_pages = min(int(kv_budget_bytes // page_bytes), max(1, max_slots) * self.pages_per_row + 1)
@@ -102,7 +108,7 @@ class Generator:
         # a row that cannot grow because the pool ran dry is preempted and generated again later.
         self.max_slots = max(b for b in (*self.BUCKETS, 4, 2, 1) if b <= max(1, min(max_slots, num_pages - 1)))
         self.pool = PagePool(num_pages)
-        shape = (num_pages, cfg.n_kv_heads, PAGE, cfg.head_dim)
+        shape = (num_pages, self.n_kv, PAGE, cfg.head_dim)
         per = math.prod(shape)
         if kv_storage is None:
             kv_storage = torch.zeros(2 * cfg.n_layers * per, dtype=torch.bfloat16, device=self.dev)
@@ -135,7 +141,7 @@ class Generator:
 
     # ------------------------------------------------------------------ decode step (graph body)
     def _nsplit(self, b: int) -> int:
-        ctas = b * self.cfg.n_heads
+        ctas = b * self.n_heads
         return 1 if ctas >= 296 else min(8, (296 + ctas - 1) // ctas)
 
     def _decode_body(self, b: int, temperature: float, greedy: bool, seed: int, top_k: int = 0, top_p: float = 1.0) -> None:
@@ -196,9 +202,11 @@ class Generator:
         seq_id = torch.cat([torch.full((l,), s, dtype=torch.int32) for l, s in zip(lens, slots)]).to(dev)
         cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
 
+        k_col0, v_col0, n_kv = self.model.kv_columns()
+
         def sink(layer: int, qkv: torch.Tensor) -> None:
-            K.kv_append(qkv, cfg.q_width, cfg.q_width + cfg.kv_width, seq_id, pos, self.page_table, self.kcache[layer],
-                        self.vcache[layer], cfg.n_kv_heads, cfg.head_dim)
+            K.kv_append(qkv, k_col0, v_col0, seq_id, pos, self.page_table, self.kcache[layer],
+                        self.vcache[layer], n_kv, cfg.head_dim)
 
         xf, _ = self.model.forward(tokens, pos, cu, max(lens), keep=False, kv_sink=sink)
         last = (cu[1:] - 1).contiguous()
@@ -468,6 +476,8 @@ class Generator:
                 slot_bound[s] = min(slot_bound[s] + horizon, slot_prompt[s] + max_new)
             nf = int(self.n_finished.item())
             counters["host_syncs"] += 1
+            if self.check_status_every_sync:
+                K.check_status()
             if nf != seen_finished:
                 seen_finished = nf
                 act = self.active.tolist()

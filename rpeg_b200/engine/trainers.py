@@ -82,18 +82,23 @@ class GRPOTrainer(_Base):
     def __init__(self, cfg: LlamaConfig, *, device="cuda:0", samples_per_prompt: int = 8, max_new: int = 2048,
                  prompt_len: int = 512, algo: Optional[A.AlgoConfig] = None, lr: float = 1e-6, gen_slots: int = 64,
                  kv_budget_bytes: float = 40e9, recompute: str = "full", dp=None, seed: int = 0, eos_id: int = 2,
-                 sync_interval: int = 8, use_graphs: bool = True):
+                 sync_interval: int = 8, use_graphs: bool = True, gen_tp: bool = False, tp_comm: Optional[str] = None):
+        """``gen_tp``: generate tensor parallel over all ranks of ``dp`` (every rank decodes ALL rows of the global batch
+        on 1/world of the weights and KV heads, ``models.tp_decode``) while the reference pass, the policy update and the
+        optimizer stay data parallel; ``gen_slots`` is then the number of rows of the whole batch decoded at once."""
         super().__init__(device, dp)
         self.cfg = cfg
         self.K = samples_per_prompt
         self.max_new = max_new
         self.algo = algo or A.AlgoConfig(kl_coef=0.04)
         self.seed = seed
+        self.gen_tp = bool(gen_tp) and dp is not None and dp.world > 1
+        tp = dp.world if self.gen_tp else 1
         # Gradients are dead while generating and the KV cache is dead while training, so both live
         # in one arena sized for the larger of the two.
         from ..models.llama import ParamLayout
         n_par = ParamLayout(cfg).total
-        kv_need = min(int(kv_budget_bytes), Generator.kv_bytes_for(cfg, gen_slots, prompt_len + max_new))
+        kv_need = min(int(kv_budget_bytes), Generator.kv_bytes_for(cfg, gen_slots, prompt_len + max_new, tp))
         arena_bytes = max(4 * n_par, kv_need)
         multi = dp is not None and dp.world > 1
         w = dp.alloc_weights(cfg) if multi else None
@@ -109,10 +114,24 @@ class GRPOTrainer(_Base):
         self.ref = LlamaModel(cfg, self.device, weights=None, seed=seed)
         self.ref.load_flat(self.actor)
         self.opt = AdamW(self.actor, lr=lr, dp=dp)
-        self.gen = Generator(self.actor, max_slots=gen_slots, max_seq_len=prompt_len + max_new, eos_id=eos_id,
+        self.gen_model = self.actor
+        if self.gen_tp:
+            from ..models.tp_decode import TPDecodeModel
+            self.gen_model = TPDecodeModel(self.actor, dp.group, max_batch=gen_slots, comm_mode=tp_comm)
+            self.parallelism = f"generation tp{dp.world} ({self.gen_model.comm.backend}), reference + training dp{dp.world}"
+        self.gen = Generator(self.gen_model, max_slots=gen_slots, max_seq_len=prompt_len + max_new, eos_id=eos_id,
                              sync_interval=sync_interval, use_graphs=use_graphs,
                              kv_storage=arena[: arena_bytes // 2 * 2].view(torch.bfloat16))
         self.last_counters: Dict[str, float] = {}
+        self.last_reshard_us: Optional[float] = None
+
+    def _all_ranks(self, t: torch.Tensor) -> torch.Tensor:
+        """Rows of every rank, in rank order (tensor-parallel generation works on the whole batch)."""
+        import torch.distributed as dist
+        t = t.contiguous()
+        out = torch.empty((self.dp.world * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t, group=self.dp.group)
+        return out
 
     def step(self, prompts: torch.Tensor, rewards: Optional[torch.Tensor] = None,
              forced_lens: Optional[torch.Tensor] = None) -> Dict[str, float]:
@@ -125,8 +144,19 @@ class GRPOTrainer(_Base):
         N = B * self.K
         rep = p_dev.repeat_interleave(self.K, dim=0).contiguous()
         self._mark("begin")
-        gen = self.gen.generate(rep, self.max_new, temperature=self.algo.temperature,
-                                seed=self.seed + 100003 * self.iteration, forced_lens=forced_lens, group_size=self.K)
+        if self.gen_tp:
+            from .generation import GenerationResult
+            f_all = None
+            if forced_lens is not None:
+                f_all = self._all_ranks(torch.as_tensor(forced_lens, dtype=torch.int32).to(self.device)).tolist()
+            whole = self.gen.generate(self._all_ranks(rep), self.max_new, temperature=self.algo.temperature,
+                                      seed=self.seed + 100003 * self.iteration, forced_lens=f_all, group_size=self.K)
+            lo = self.dp.rank * N
+            gen = GenerationResult(whole.tokens[lo:lo + N].contiguous(), whole.logprobs[lo:lo + N].contiguous(),
+                                   whole.lengths[lo:lo + N].contiguous(), whole.counters)
+        else:
+            gen = self.gen.generate(rep, self.max_new, temperature=self.algo.temperature,
+                                    seed=self.seed + 100003 * self.iteration, forced_lens=forced_lens, group_size=self.K)
         resp_lens = gen.lengths.tolist()
         self._mark("generate")
         ro = A.Rollout(rep, [S] * N, gen.tokens, resp_lens, gen.logprobs, gen.response_mask(),
@@ -145,11 +175,17 @@ class GRPOTrainer(_Base):
         self._mark("train")
         self.opt.step()
         self._mark("optimizer")
+        if self.gen_tp:
+            self.gen_model.refresh()      # layout switch: the updated replicated weights -> this rank's generation shards
+            self._mark("reshard")
         self.weight_version += 1
         self.iteration += 1
         m["grad_norm"] = self.opt.grad_norm()
         out = self._read(m)
         out.update(self._phase_ms())
+        if self.gen_tp:
+            self.last_reshard_us = self.gen_model.last_reshard_us
+            out["reshard_us"] = float(self.last_reshard_us or 0.0)
         out.update(samples=float(N), gen_tokens=float(sum(resp_lens)), train_tokens=float(sum(ro.total_lens())),
                    wall_s=time.perf_counter() - t0)
         self.last_counters = dict(gen.counters)

@@ -227,6 +227,11 @@ class LlamaModel:
         n = min(self.layout.total, other.layout.total)
         self.w[:n].copy_(other.w[:n])
 
+    def kv_columns(self):
+        """(first K column, first V column, KV heads) of the heads this model keeps in a generator's KV cache,
+        inside the QKV activation a full-sequence forward hands to ``kv_sink``."""
+        return self.cfg.q_width, self.cfg.q_width + self.cfg.kv_width, self.cfg.n_kv_heads
+
     def _workspace(self) -> torch.Tensor:
         if self._ws is None:
             self._ws = torch.empty(32 * 1024 * 1024, dtype=torch.float32, device=self.device)

@@ -216,11 +216,14 @@ def add_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
-def embed_fwd(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+def embed_fwd(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     _req(ids, torch.int32, "ids")
     if _chk.active():
         _chk.embed("rpeg_embed_fwd", ids, table.shape[0])
-    out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    if out is None:
+        out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    elif out.shape != (ids.numel(), table.shape[1]) or not out.is_contiguous() or out.dtype != table.dtype:
+        raise ValueError("embed_fwd: `out` must be a contiguous [tokens, d] tensor of the table's dtype")
     check(lib().rpeg_embed_fwd(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(), table.shape[1],
                                _stream()), "rpeg_embed_fwd")
     return out

@@ -1,0 +1,154 @@
+"""Numerics self test of tensor-parallel decoding, for any number of ranks (one GPU each).
+
+    python -m rpeg_b200.parallel.tp_decode_selftest                                   # one rank
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \\
+        -m rpeg_b200.parallel.tp_decode_selftest [--comm peer|nvls|auto]              # 2, 4 or 8 ranks
+
+Checks, each against the whole model on the same GPU or against fp32 PyTorch:
+  1. ``allreduce_rmsnorm``: rank-dependent partial sums -> rmsnorm(sum + residual) and the new residual stream,
+     against an NCCL all-reduce of the fp32 partials followed by fp32 PyTorch; identical bits on every rank.
+  2. ``allgather_cols`` against ``all_gather``.
+  3. three decode steps of ``TPDecodeModel`` against ``LlamaModel.decode_step`` (separate KV caches).
+  4. a greedy generation through ``Generator(TPDecodeModel)``: same tokens on every rank, log-probs close to the
+     single-GPU generator's wherever both chose the same token.
+Rank 0 prints one JSON line; the exit code is non-zero when a check fails.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--comm", default=None, help="peer | nvls | auto (default: RPEG_TP_COMM or auto)")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from rpeg_b200.engine.generation import Generator
+    from rpeg_b200.models.llama import LlamaConfig, LlamaModel
+    from rpeg_b200.models.tp_decode import TPDecodeModel
+    from rpeg_b200.ops import kernels as K
+
+    cfg = LlamaConfig(n_layers=2, d_model=1024, d_ff=2048, n_heads=8, n_kv_heads=8, head_dim=128, vocab=2048, max_pos=256)
+    full = LlamaModel(cfg, dev, seed=5)
+    tpm = TPDecodeModel(full, None, max_batch=32, comm_mode=args.comm)
+    R = tpm.comm
+    rep = {"world": world, "backend": R.backend, "multicast_error": getattr(R, "multicast_error", None)}
+
+    def same_everywhere(t: torch.Tensor) -> bool:
+        if world == 1:
+            return True
+        ref = t.clone()
+        dist.broadcast(ref, src=0)
+        ok = torch.tensor([int(torch.equal(ref, t))], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        return bool(ok.item())
+
+    # 1. all-reduce + residual + RMSNorm ------------------------------------------------------------
+    B, d = 24, cfg.d_model
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    part = (torch.randn(B, d, generator=g) * 0.5).bfloat16().to(dev)
+    g0 = torch.Generator(device="cpu").manual_seed(7)
+    res = torch.randn(B, d, generator=g0).bfloat16().to(dev)
+    w = (1.0 + 0.1 * torch.randn(d, generator=g0)).bfloat16().to(dev)
+    errs = []
+    for call in range(3):                       # repeated calls: the device-side call counter must keep the ranks in step
+        R.view("part", (B, d)).copy_(part * (call + 1))
+        R.view("h", (B, d)).copy_(res)
+        R.allreduce_rmsnorm("part", R.view("h", (B, d)), w, "x", "h", B, d, cfg.rms_eps)
+        total = (part * (call + 1)).float()
+        if world > 1:
+            dist.all_reduce(total)
+        hs = (total + res.float()).bfloat16().float()
+        want_y = hs * torch.rsqrt((hs * hs).mean(-1, keepdim=True) + cfg.rms_eps) * w.float()
+        got_y, got_h = R.view("x", (B, d)).float(), R.view("h", (B, d)).float()
+        errs.append(float(((got_y - want_y).abs().max() / want_y.abs().max()).item()))
+        errs.append(float(((got_h - hs).abs().max() / hs.abs().max()).item()))
+        rep.setdefault("ar_identical", True)
+        rep["ar_identical"] = rep["ar_identical"] and same_everywhere(R.view("x", (B, d))) and same_everywhere(R.view("h", (B, d)))
+    rep["ar_max_rel_err"] = max(errs)
+
+    # 2. column all-gather ---------------------------------------------------------------------------
+    V, vl = cfg.vocab, cfg.vocab // world
+    logits = R.view("logits", (B, V))
+    logits.zero_()
+    mine = torch.full((B, vl), float(rank + 1), device=dev).bfloat16() + torch.arange(vl, device=dev).bfloat16()[None, :] / 256
+    logits[:, rank * vl:(rank + 1) * vl] = mine
+    if world > 1:
+        dist.barrier()                              # nobody pushes into a buffer a peer is still clearing
+    R.allgather_cols("logits", B, vl, V)
+    want = torch.cat([torch.full((B, vl), float(r + 1), device=dev).bfloat16() + torch.arange(vl, device=dev).bfloat16()[None, :] / 256
+                      for r in range(world)], 1)
+    rep["allgather_ok"] = bool(torch.equal(logits, want))
+
+    # 3. decode steps against the whole model --------------------------------------------------------
+    Bd, pages = 16, 40
+    i32 = dict(dtype=torch.int32, device=dev)
+    kc_f = [torch.zeros(pages, cfg.n_kv_heads, K.KV_PAGE, 128, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+    vc_f = [torch.zeros_like(t) for t in kc_f]
+    kc_t = [torch.zeros(pages, tpm.n_kv_local, K.KV_PAGE, 128, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+    vc_t = [torch.zeros_like(t) for t in kc_t]
+    table = (torch.arange(Bd, **i32) + 1).view(Bd, 1).contiguous()
+    slot_ids = torch.arange(Bd, **i32)
+    gt = torch.Generator(device="cpu").manual_seed(11)
+    step_err = 0.0
+    for t in range(3):
+        tok = torch.randint(0, cfg.vocab, (Bd,), generator=gt, dtype=torch.int32).to(dev)
+        pos = torch.full((Bd,), t, **i32)
+        seq = torch.full((Bd,), t + 1, **i32)
+        want_x = full.decode_step(tok, pos, slot_ids, seq, table, kc_f, vc_f, nsplit=1)
+        got_x = tpm.decode_step(tok, pos, slot_ids, seq, table, kc_t, vc_t, nsplit=1).clone()
+        step_err = max(step_err, float(((got_x.float() - want_x.float()).abs().max() / want_x.float().abs().max()).item()))
+        want_l = full.lm_logits(want_x, decode=True).float()
+        got_l = tpm.lm_logits(got_x, decode=True).float()
+        step_err = max(step_err, float(((got_l - want_l).abs().max() / want_l.abs().max()).item()))
+    rep["decode_step_max_rel_err"] = step_err
+    r0 = tpm.rank * tpm.n_kv_local
+    rep["kv_cache_matches"] = bool(torch.allclose(kc_t[1][:, :, :3].float(), kc_f[1][:, r0:r0 + tpm.n_kv_local, :3].float(), atol=2e-2, rtol=2e-2))
+
+    # 4. generation -----------------------------------------------------------------------------------
+    gp = torch.Generator(device="cpu").manual_seed(3)
+    prompts = torch.randint(3, cfg.vocab, (4, 70), generator=gp, dtype=torch.int32).repeat_interleave(2, 0).to(dev)
+    gen_f = Generator(full, max_slots=8, max_seq_len=128, kv_budget_bytes=2e8, eos_id=1)
+    gen_t = Generator(tpm, max_slots=8, max_seq_len=128, kv_budget_bytes=2e8, eos_id=1)
+    want_g = gen_f.generate(prompts, 24, greedy=True, seed=1, group_size=2)
+    got_g = gen_t.generate(prompts, 24, greedy=True, seed=1, group_size=2)
+    same = (want_g.tokens == got_g.tokens)
+    # greedy rows stay equal until the first near-tie resolves differently; compare log-probs on the common prefix
+    prefix = same.int().cumprod(1).bool()
+    rep["gen_token_match"] = float(same.float().mean().item())
+    rep["gen_prefix_share"] = float(prefix.float().mean().item())
+    rep["gen_logprob_max_diff"] = float(((want_g.logprobs - got_g.logprobs).abs() * prefix).max().item())
+    rep["gen_identical_on_ranks"] = same_everywhere(got_g.tokens) and same_everywhere(got_g.logprobs)
+    rep["reshard_us"] = tpm.last_reshard_us
+    K.check_status()
+    rep["ok"] = bool(rep["ar_max_rel_err"] < 2e-2 and rep["ar_identical"] and rep["allgather_ok"] and step_err < 4e-2
+                     and rep["kv_cache_matches"] and rep["gen_prefix_share"] > 0.6 and rep["gen_logprob_max_diff"] < 0.15
+                     and rep["gen_identical_on_ranks"])
+    oks = torch.tensor([int(rep["ok"])], device=dev)
+    if world > 1:
+        dist.all_reduce(oks, op=dist.ReduceOp.MIN)
+        rep["ok"] = bool(oks.item())
+    if rank == 0:
+        print(json.dumps(rep), flush=True)
+    tpm.comm.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0 if rep["ok"] else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
