@@ -49,56 +49,91 @@ def load_index(output_dir) -> Dict[str, Any]:
     return idx
 
 
+def entry_path(output_dir, entry: Mapping[str, Any]) -> Path:
+    """Directory of an index entry. ``path`` is stored as a path under ``output_dir`` (what the reference's index
+    holds); a bare directory name, as older index files of this framework have it, is taken relative to it."""
+    p = Path(entry["path"])
+    if p.is_absolute() or p.exists():
+        return p
+    return Path(output_dir) / p.name
+
+
+def _sort_key(c: Mapping[str, Any]):
+    return (int(c["step"]), c["kind"] == "final", str(c["name"]))
+
+
 def register_checkpoint(output_dir, *, name: str, kind: str, step: int, workers: Sequence[str],
                         extra: Optional[Mapping[str, Any]] = None) -> Dict[str, Any]:
-    """Add (or replace) an entry and update ``latest_final`` / ``latest_interval``; atomic."""
+    """Add (or replace) an entry and update ``latest_final`` / ``latest_interval`` (paths under ``output_dir``, as in
+    the reference's index); atomic. Call it from ONE process of a job (rank 0)."""
     if kind not in ("interval", "final"):
         raise ValueError("checkpoint kind must be 'interval' or 'final'")
     idx = load_index(output_dir)
-    entry = {"name": name, "kind": kind, "step": int(step), "path": name, "workers": sorted(workers), "created": time.time(),
+    path = str(Path(output_dir) / name)
+    entry = {"name": name, "kind": kind, "step": int(step), "path": path, "workers": sorted(workers), "created": time.time(),
              **dict(extra or {})}
     idx["checkpoints"] = [c for c in idx["checkpoints"] if c["name"] != name] + [entry]
-    idx["checkpoints"].sort(key=lambda c: (c["step"], c["kind"] == "final"))
-    idx["latest_final" if kind == "final" else "latest_interval"] = name
+    idx["checkpoints"].sort(key=_sort_key)
+    idx["latest_final" if kind == "final" else "latest_interval"] = path
     atomic_write_text(Path(output_dir) / INDEX_FILE, json.dumps(idx, indent=2))
     return entry
 
 
-def prune_checkpoints(output_dir, keep_last_interval_steps: Optional[int], current_step: int) -> List[str]:
-    """Delete interval checkpoints older than ``current_step - keep_last_interval_steps`` (the newest
-    interval checkpoint and final ones always stay). Returns the removed names."""
+def prune_checkpoints(output_dir, keep_last_interval_steps: Optional[int], current_step: Optional[int] = None) -> List[str]:
+    """Keep the newest ``keep_last_interval_steps`` INTERVAL checkpoints and delete the older ones; ``0`` deletes them
+    all, ``None`` keeps everything. The setting counts checkpoints, not steps, as in the reference
+    (RPEG/runtime/algorithms/megatron_ppo_graph.py:4349-4380); final checkpoints always stay. ``latest_interval`` is
+    recomputed afterwards. Returns the removed names. Call it from ONE process of a job (rank 0)."""
     if keep_last_interval_steps is None:
         return []
+    keep = max(0, int(keep_last_interval_steps))
     idx = load_index(output_dir)
+    intervals = sorted((c for c in idx["checkpoints"] if c["kind"] == "interval"), key=_sort_key)
+    doomed = intervals[: max(0, len(intervals) - keep)]
     removed = []
-    for c in list(idx["checkpoints"]):
-        if c["kind"] != "interval" or c["name"] == idx.get("latest_interval"):
-            continue
-        if c["step"] < current_step - int(keep_last_interval_steps):
-            target = Path(output_dir) / c["path"]
-            if target.is_dir() and target.parent == Path(output_dir):
-                shutil.rmtree(target)
-            idx["checkpoints"].remove(c)
-            removed.append(c["name"])
+    for c in doomed:
+        target = entry_path(output_dir, c)
+        if target.is_dir() and target.parent.resolve() == Path(output_dir).resolve():
+            shutil.rmtree(target, ignore_errors=True)
+        idx["checkpoints"].remove(c)
+        removed.append(c["name"])
     if removed:
+        left = [c for c in idx["checkpoints"] if c["kind"] == "interval"]
+        idx["latest_interval"] = max(left, key=_sort_key)["path"] if left else None
         atomic_write_text(Path(output_dir) / INDEX_FILE, json.dumps(idx, indent=2))
     return removed
 
 
-def latest_usable_checkpoint(output_dir, *, max_step: Optional[int] = None, verify: bool = True) -> Optional[Dict[str, Any]]:
-    """Newest indexed checkpoint (step <= ``max_step``) whose files are all present with the recorded
-    sizes; damaged or incomplete ones are skipped."""
+def latest_usable_checkpoint(output_dir, *, max_step: Optional[int] = None, verify: bool = True,
+                             verify_hashes: bool = False) -> Optional[Dict[str, Any]]:
+    """Newest indexed checkpoint (step <= ``max_step``) that can be restored from: every worker directory present with
+    the recorded file sizes (and, with ``verify_hashes``, the recorded sha256). An entry without any worker directory
+    holds no tensors and is only accepted when it says so itself (``metadata_only``, written by handlers that keep
+    no tensor state); damaged or incomplete checkpoints are skipped."""
     idx = load_index(output_dir)
-    for c in sorted(idx["checkpoints"], key=lambda c: (c["step"], c["kind"] == "final"), reverse=True):
+    for c in sorted(idx["checkpoints"], key=_sort_key, reverse=True):
         if max_step is not None and c["step"] > max_step:
             continue
-        if not verify or not verify_checkpoint(Path(output_dir) / c["path"], c["workers"])["errors"]:
+        if not verify:
+            return c
+        if not c.get("workers") and not c.get("metadata_only"):
+            continue
+        if not verify_checkpoint(entry_path(output_dir, c), c["workers"], hashes=verify_hashes)["errors"]:
             return c
     return None
 
 
-def verify_checkpoint(path, workers: Iterable[str]) -> Dict[str, Any]:
-    """File counts and byte sizes of every worker directory against its ``meta.json``."""
+def _sha256_of(path: Path) -> str:
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for block in iter(lambda: f.read(1 << 24), b""):
+            h.update(block)
+    return h.hexdigest()
+
+
+def verify_checkpoint(path, workers: Iterable[str], hashes: bool = False) -> Dict[str, Any]:
+    """File counts and byte sizes of every worker directory against its ``meta.json``; with ``hashes`` also the
+    sha256 of every rank file (a damaged file of the right size is otherwise indistinguishable)."""
     path = Path(path)
     errors: List[str] = []
     files = nbytes = 0
@@ -119,6 +154,8 @@ def verify_checkpoint(path, workers: Iterable[str]) -> Dict[str, Any]:
                 errors.append(f"{path.name}/{w}: missing {f['name']}")
             elif fp.stat().st_size != int(f["bytes"]):
                 errors.append(f"{path.name}/{w}: {f['name']} has {fp.stat().st_size} bytes, expected {f['bytes']}")
+            elif hashes and f.get("sha256") and _sha256_of(fp) != f["sha256"]:
+                errors.append(f"{path.name}/{w}: {f['name']} does not match its recorded sha256")
             else:
                 files += 1
                 nbytes += int(f["bytes"])
@@ -251,7 +288,11 @@ def load_flat_range(worker_dir, name: str, start: int, stop: int):
             if lo < hi:
                 pieces.append((lo, _read_entry(d, r["file"], e, lo - e["global_start"], hi - e["global_start"])))
     pieces.sort(key=lambda p: p[0])
-    got = sum(int(p.numel()) for _, p in pieces)
-    if got != stop - start:
-        raise RuntimeExecutionError(f"{name}[{start}:{stop}] is only partly present in {d} ({got} elements)")
+    at = start
+    for lo, piece in pieces:                 # the shards must tile the range: no gap, no overlap
+        if lo != at:
+            raise RuntimeExecutionError(f"{name}[{start}:{stop}] in {d}: shards {'overlap' if lo < at else 'leave a gap'} at element {min(lo, at)}")
+        at = lo + int(piece.numel())
+    if at != stop:
+        raise RuntimeExecutionError(f"{name}[{start}:{stop}] is only partly present in {d} ({at - start} elements)")
     return torch.cat([p for _, p in pieces]) if len(pieces) != 1 else pieces[0][1]

@@ -91,6 +91,11 @@ def validate_engine_plan(compiled) -> str:
             raise RuntimeConfigError("engine backend: generation and training on disjoint GPUs is implemented for GRPO only")
         if compiled.run_config.checkpoints.resume_from:
             raise RuntimeConfigError("engine backend: a run with generation and training on disjoint GPUs cannot resume from a checkpoint")
+        # This family writes no tensor checkpoints, so a replay would "restore" nothing: the engine would keep its
+        # advanced weights, Adam state and version words and apply the replayed updates a second time.
+        if int(compiled.run_config.monitoring.graph_replay_retries) > 0:
+            raise RuntimeConfigError("engine backend: monitoring.graph_replay_retries > 0 is not supported with generation and "
+                                     "training on disjoint GPUs (no checkpoint to replay from); set it to 0")
         return "disaggregated"
     train = [v for v in cfg.rpeg.vertices if v.kind.role is Role.TRAINING]
     piped = g > 1 and bool(train) and all(tuple(cfg.plan.pi[v.id]) == (1, g, 1) for v in train)

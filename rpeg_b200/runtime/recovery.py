@@ -95,12 +95,18 @@ class CheckpointingHook:
         if self.trace is not None:
             self.trace.emit("runtime.checkpoint.save", "start", step=step, counters={"name": name, "kind": kind})
         saver = getattr(self.inner, "save_checkpoint", None)
+        # every rank writes its own shards (the handler synchronises the ranks around that); the manifest, the index
+        # entry and the pruning of old checkpoints are the work of ONE process, or the ranks race on the same files
         info = saver(step, path, kind) if saver is not None else {"workers": [], "bytes": 0, "files": 0}
-        tau = self._tau()
-        retained = {m: [v for v in ckpt.versions_needed_after(latest, tau.get(m, 0))] for m, latest in self.latest.items()}
-        ckpt.write_weight_versions(path, step=step, latest=self.latest, retained=retained, tau=tau)
-        ckpt.register_checkpoint(out, name=name, kind=kind, step=step, workers=info.get("workers", ()))
-        ckpt.prune_checkpoints(out, self.run.checkpoints.keep_last_interval_steps, step)
+        if _is_rank0():
+            tau = self._tau()
+            retained = {m: [v for v in ckpt.versions_needed_after(latest, tau.get(m, 0))] for m, latest in self.latest.items()}
+            ckpt.write_weight_versions(path, step=step, latest=self.latest, retained=retained, tau=tau)
+            if saver is None or info.get("workers"):
+                ckpt.register_checkpoint(out, name=name, kind=kind, step=step, workers=info.get("workers", ()),
+                                         extra={"metadata_only": True} if saver is None else None)
+                ckpt.prune_checkpoints(out, self.run.checkpoints.keep_last_interval_steps)
+        _rank_barrier()
         self.saved_steps.append(step)
         if self.trace is not None:
             self.trace.emit("runtime.checkpoint.save", "finish", step=step,
@@ -137,12 +143,15 @@ def run_with_replay(compiled, graph: RuntimeGraph, make_handler: Callable[[int],
     current, restored_step, latest = graph, 0, {}
     completed_before: Set[str] = set()
     last_error: Optional[Exception] = None
+    restore_path = None                     # directory of the verified entry the next attempt restores from
     if run.checkpoints.resume_from:
-        entry = ckpt.latest_usable_checkpoint(run.resolve(run.checkpoints.resume_from))
+        src0 = run.resolve(run.checkpoints.resume_from)
+        entry = ckpt.latest_usable_checkpoint(src0, verify_hashes=True)
         if entry is None:
             raise RuntimeExecutionError(f"checkpoints.resume_from={run.checkpoints.resume_from} holds no usable checkpoint")
         restored_step = int(entry["step"])
-        latest = dict(ckpt.read_weight_versions(run.resolve(run.checkpoints.resume_from) / entry["path"])["latest"])
+        restore_path = ckpt.entry_path(src0, entry)
+        latest = dict(ckpt.read_weight_versions(restore_path)["latest"])
         current = suffix_graph(graph, restored_step)
         completed_before = set(graph.nodes) - set(current.nodes)
     for attempt in range(retries + 1):
@@ -156,7 +165,8 @@ def run_with_replay(compiled, graph: RuntimeGraph, make_handler: Callable[[int],
             if trace is not None:
                 trace.emit("runtime.checkpoint.restore", "start", step=restored_step, counters={"attempt": attempt})
             if restore is not None:
-                restore(restored_step, src / (f"step_{restored_step}" if (src / f"step_{restored_step}").exists() else "final"))
+                restore(restored_step, restore_path if restore_path is not None else
+                        src / (f"step_{restored_step}" if (src / f"step_{restored_step}").exists() else "final"))
             if trace is not None:
                 trace.emit("runtime.checkpoint.restore", "finish", step=restored_step, counters={"attempt": attempt})
         ex = RuntimeExecutor(current, run_id=run.run_id, handler=hook, trace=trace, node_timeout_s=node_timeout_s,
@@ -171,16 +181,39 @@ def run_with_replay(compiled, graph: RuntimeGraph, make_handler: Callable[[int],
                 break
             if trace is not None:
                 trace.emit("runtime.graph", "replay", status="error", counters={"attempt": attempt + 1, "reason": str(exc)[:300]})
-            entry = ckpt.latest_usable_checkpoint(out_dir)
+            entry = ckpt.latest_usable_checkpoint(out_dir, verify_hashes=True)
             if entry is not None and entry["kind"] == "interval":
                 restored_step = int(entry["step"])
-                latest = dict(ckpt.read_weight_versions(out_dir / entry["path"])["latest"])
+                restore_path = ckpt.entry_path(out_dir, entry)
+                latest = dict(ckpt.read_weight_versions(restore_path)["latest"])
                 current = suffix_graph(graph, restored_step)
             else:
-                restored_step, latest, current = 0, {}, graph
+                restored_step, latest, current, restore_path = 0, {}, graph, None
             completed_before = set(graph.nodes) - set(current.nodes)
             if trace is not None:
                 trace.emit("runtime.graph", "recover", counters={"attempt": attempt + 1, "restored_step": restored_step,
                                                                  "skipped_nodes": len(completed_before),
                                                                  "suffix_nodes": len(current.nodes), "weight_versions": latest})
     raise RuntimeExecutionError(f"graph execution failed after {retries + 1} attempt(s): {last_error}") from last_error
+
+
+def _is_rank0() -> bool:
+    """True in the one process of a job that owns the checkpoint index (rank 0, or a job without ranks)."""
+    try:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            return dist.get_rank() == 0
+    except ImportError:
+        pass
+    import os
+    return int(os.environ.get("RANK", "0")) == 0
+
+
+def _rank_barrier() -> None:
+    """All ranks leave a checkpoint together, after rank 0 has registered it and pruned the old ones."""
+    try:
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            dist.barrier()
+    except ImportError:
+        pass

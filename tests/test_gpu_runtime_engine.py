@@ -53,7 +53,7 @@ def test_engine_checkpoint_replay_restores_weights_and_optimizer(tmp_path, cuda_
     idx = ckpt.load_index(tmp_path / "checkpoints")
     assert [c["name"] for c in idx["checkpoints"]] == ["step_1", "step_2", "final"]
     for c in idx["checkpoints"]:
-        assert ckpt.verify_checkpoint(tmp_path / "checkpoints" / c["path"], c["workers"])["errors"] == []
+        assert ckpt.verify_checkpoint(ckpt.entry_path(tmp_path / "checkpoints", c), c["workers"], hashes=True)["errors"] == []
     w2 = ckpt.load_tensor(tmp_path / "checkpoints/step_2/actor", "weights")
     w3 = ckpt.load_tensor(tmp_path / "checkpoints/final/actor", "weights")
     assert w2.shape == w3.shape and not torch.equal(w2, w3)

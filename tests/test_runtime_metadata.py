@@ -363,7 +363,7 @@ def test_replay_restores_the_interval_checkpoint_and_runs_the_suffix(tmp_path):
             if e["event"] == "finish" and e["node_id"].startswith("t_pi@") and e["status"] == "ok"]
     assert t_pi == [(1, 1), (2, 2), (3, 3), (4, 4)]
     idx = ckpt.load_index(tmp_path / "checkpoints")
-    assert idx["latest_interval"] == "step_2" and idx["latest_final"] == "final"
+    assert idx["latest_interval"] == str(tmp_path / "checkpoints/step_2") and idx["latest_final"] == str(tmp_path / "checkpoints/final")
     assert ckpt.read_weight_versions(tmp_path / "checkpoints/final")["latest"] == {"actor": 4}
     alerts = json.loads((tmp_path / "metrics/alerts.json").read_text())
     assert alerts["schema_version"] == "rpeg.runtime_alerts.v1" and alerts["status"] == "critical"
@@ -407,6 +407,80 @@ def test_checkpoint_flat_shards_reslice_across_dp_degrees(tmp_path):
     f = tmp_path / "step_1/actor/rank2.bin"
     f.write_bytes(f.read_bytes()[:-8])
     assert ckpt.latest_usable_checkpoint(tmp_path) is None
+
+
+def _tiny_checkpoint(root, name, step, kind="interval", payload=None):
+    import torch
+    from rpeg_b200.runtime import checkpoint as ckpt
+    t = payload if payload is not None else torch.arange(64, dtype=torch.float32) + step
+    ckpt.save_flat_shards(root / name / "actor", 0, 1, {"adam.m": t}, ranges={"adam.m": (0, 64, 64)})
+    ckpt.finalize_worker_meta(root / name / "actor", 1)
+    ckpt.write_weight_versions(root / name, step=step, latest={"actor": step}, retained={"actor": [step]}, tau={"actor": 0})
+    return ckpt.register_checkpoint(root, name=name, kind=kind, step=step, workers=["actor"])
+
+
+def test_interval_checkpoints_are_pruned_by_count_like_the_reference(tmp_path):
+    """``keep_last_interval_steps`` is the NUMBER of interval checkpoints kept (0 removes all of them), final checkpoints
+    stay, and the index holds paths under the output directory with ``latest_interval`` recomputed after pruning."""
+    from rpeg_b200.runtime import checkpoint as ckpt
+    for step in (100, 200, 300, 400):
+        _tiny_checkpoint(tmp_path, f"step_{step}", step)
+    _tiny_checkpoint(tmp_path, "final", 400, kind="final")
+    assert ckpt.prune_checkpoints(tmp_path, None) == []
+    assert ckpt.prune_checkpoints(tmp_path, 2) == ["step_100", "step_200"]
+    idx = ckpt.load_index(tmp_path)
+    assert [c["name"] for c in idx["checkpoints"]] == ["step_300", "step_400", "final"]
+    assert idx["latest_interval"] == str(tmp_path / "step_400") and idx["latest_final"] == str(tmp_path / "final")
+    assert not (tmp_path / "step_100").exists() and (tmp_path / "step_300").is_dir()
+    assert all(c["path"] == str(tmp_path / c["name"]) for c in idx["checkpoints"])
+    assert ckpt.prune_checkpoints(tmp_path, 0) == ["step_300", "step_400"]
+    idx = ckpt.load_index(tmp_path)
+    assert idx["latest_interval"] is None and [c["name"] for c in idx["checkpoints"]] == ["final"]
+    assert ckpt.latest_usable_checkpoint(tmp_path)["name"] == "final"
+
+
+def test_checkpoint_selection_rejects_empty_and_silently_damaged_entries(tmp_path):
+    """An entry without worker directories is not something to restore from unless it declares itself metadata only; a
+    rank file of the right size with changed bytes is caught by its sha256; overlapping shards are refused on load."""
+    import torch
+    from rpeg_b200.runtime import checkpoint as ckpt
+    _tiny_checkpoint(tmp_path, "step_1", 1)
+    (tmp_path / "step_2").mkdir()
+    ckpt.write_weight_versions(tmp_path / "step_2", step=2, latest={"actor": 2}, retained={"actor": [2]}, tau={"actor": 0})
+    ckpt.register_checkpoint(tmp_path, name="step_2", kind="interval", step=2, workers=[])
+    assert ckpt.latest_usable_checkpoint(tmp_path)["name"] == "step_1"          # the empty newer entry is skipped
+    ckpt.register_checkpoint(tmp_path, name="step_2", kind="interval", step=2, workers=[], extra={"metadata_only": True})
+    assert ckpt.latest_usable_checkpoint(tmp_path)["name"] == "step_2"
+    ckpt.register_checkpoint(tmp_path, name="step_2", kind="interval", step=2, workers=[])
+    f = tmp_path / "step_1/actor/rank0.bin"
+    raw = bytearray(f.read_bytes())
+    raw[10] ^= 0xFF
+    f.write_bytes(bytes(raw))                                                   # same size, different content
+    assert ckpt.latest_usable_checkpoint(tmp_path)["name"] == "step_1"          # sizes alone do not see it
+    assert ckpt.latest_usable_checkpoint(tmp_path, verify_hashes=True) is None
+    assert any("sha256" in e for e in ckpt.verify_checkpoint(tmp_path / "step_1", ["actor"], hashes=True)["errors"])
+    # two ranks that both claim elements 40..49
+    full = torch.arange(100, dtype=torch.float32)
+    ckpt.save_flat_shards(tmp_path / "ov/actor", 0, 2, {"adam.m": full[:50]}, ranges={"adam.m": (0, 50, 100)})
+    ckpt.save_flat_shards(tmp_path / "ov/actor", 1, 2, {"adam.m": full[40:100]}, ranges={"adam.m": (40, 100, 100)})
+    ckpt.finalize_worker_meta(tmp_path / "ov/actor", 2)
+    with pytest.raises(RuntimeExecutionError, match="overlap"):
+        ckpt.load_flat_range(tmp_path / "ov/actor", "adam.m", 0, 100)
+
+
+def test_disaggregated_family_refuses_graph_replay(tmp_path):
+    """Generation and training on disjoint GPUs write no tensor checkpoint, so a replay could only re-apply updates on
+    top of the advanced state: the engine backend refuses ``graph_replay_retries > 0`` for this family."""
+    from rpeg_b200.runtime.engine_backend import validate_engine_plan
+    cfg = job_mapping("grpo", steps=3, runtime={"default_backend": "engine", "gen_slots": 8, "micro_tokens": 1024})
+    cfg["device_space"] = {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4}
+    cfg["optimizer"].update(plan_family="disaggregated")
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    compiled = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out", quiet=True)["compiled"]
+    assert validate_engine_plan(compiled) == "disaggregated"
+    compiled.run_config.monitoring.graph_replay_retries = 1
+    with pytest.raises(RuntimeConfigError, match="graph_replay_retries"):
+        validate_engine_plan(compiled)
 
 
 def test_metrics_alert_rules_and_fingerprints():
@@ -453,3 +527,50 @@ def test_full_validator_phases(tmp_path, capsys):
     assert validate_main(["--config", str(tmp_path / "bad.yaml")]) == 2
     out = json.loads(capsys.readouterr().out)
     assert not out["ok"] and out["phases"][-1]["phase"] == "unroll" and "context_length" in out["phases"][-1]["error"]
+
+
+def _checkpoint_rank(rank: int, world: int, root: str, port: int) -> None:
+    """One gloo rank: saves three interval checkpoints through the hook with a handler that writes a shard per rank."""
+    import os
+    from pathlib import Path
+    from types import SimpleNamespace
+
+    import torch
+    import torch.distributed as dist
+    from rpeg_b200.runtime import checkpoint as ckpt
+    from rpeg_b200.runtime.recovery import CheckpointingHook
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    class Handler:
+        def save_checkpoint(self, step, path, kind):
+            ckpt.save_flat_shards(Path(path) / "actor", rank, world, {"adam.m": torch.full((8,), float(step))},
+                                  ranges={"adam.m": (rank * 8, rank * 8 + 8, world * 8)})
+            dist.barrier()
+            if rank == 0:
+                ckpt.finalize_worker_meta(Path(path) / "actor", world)
+            dist.barrier()
+            return {"workers": ["actor"], "bytes": 32, "files": 1}
+
+    run = SimpleNamespace(checkpoints=SimpleNamespace(output_dir=root, keep_last_interval_steps=2, interval_steps=1, save_final=False),
+                          monitoring=SimpleNamespace(), training=SimpleNamespace(max_steps=9), resolve=lambda p: Path(p))
+    graph = SimpleNamespace(nodes={})
+    hook = CheckpointingHook.__new__(CheckpointingHook)
+    hook.inner, hook.graph, hook.run, hook.trace, hook.attempt, hook.latest, hook.saved_steps = Handler(), graph, run, None, 0, {"actor": 0}, []
+    for step in (1, 2, 3):
+        hook.latest["actor"] = step
+        hook.save(step, "interval")
+    dist.destroy_process_group()
+
+
+def test_only_one_rank_registers_and_prunes_checkpoints(tmp_path):
+    """Three gloo ranks save through the same hook: every rank writes its shard, the index is written by rank 0 alone
+    (one entry per checkpoint, pruning by count) and no rank trips over a directory another one is removing."""
+    import torch.multiprocessing as mp
+    from rpeg_b200.runtime import checkpoint as ckpt
+    mp.spawn(_checkpoint_rank, args=(3, str(tmp_path), 29631), nprocs=3, join=True)
+    idx = ckpt.load_index(tmp_path)
+    assert [c["name"] for c in idx["checkpoints"]] == ["step_2", "step_3"] and not (tmp_path / "step_1").exists()
+    entry = ckpt.latest_usable_checkpoint(tmp_path, verify_hashes=True)
+    assert entry["name"] == "step_3" and entry["workers"] == ["actor"]
+    assert ckpt.load_flat_range(tmp_path / "step_3/actor", "adam.m", 0, 24).tolist() == [3.0] * 24
