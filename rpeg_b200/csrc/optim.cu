@@ -159,21 +159,57 @@ __global__ void wait_flags_kernel(const unsigned* __restrict__ flags, int n, uns
 }
 
 // reduced[i] = scale * sum_p grads[p][shard_off + i], i in [0, shard_n); sumsq[0] += sum reduced^2.
-__global__ void dp_reduce_norm_kernel(PeerPtrs grads, int world, long long shard_off, long long shard_n,
-                                      float scale, float* __restrict__ reduced, float* __restrict__ sumsq) {
+// Loads from peer memory are latency bound per request, so every thread keeps 2 x world independent 16-byte loads
+// in flight (all peers of two vectors) before it adds anything up. With a multicast mapping of the gradient
+// buffers (`mc` != nullptr) one multimem.ld_reduce per vector lets NVSwitch add the ranks' copies instead: the
+// owner then receives its shard once, not once per peer.
+__global__ void __launch_bounds__(256)
+dp_reduce_norm_kernel(PeerPtrs grads, const float* __restrict__ mc, int world, long long shard_off, long long shard_n,
+                      float scale, float* __restrict__ reduced, float* __restrict__ sumsq) {
   __shared__ float red[32];
   float s = 0.f;
   const long long nv = shard_n >> 2;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < world; ++p) {
-      const float4 g = reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + shard_off)[i];
-      a.x += g.x; a.y += g.y; a.z += g.z; a.w += g.w;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nv; i0 += 2 * stride) {
+    const long long i1 = i0 + stride;
+    const bool two = i1 < nv;
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    if (mc != nullptr) {
+      asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(a0.x), "=f"(a0.y), "=f"(a0.z), "=f"(a0.w)
+                   : "l"(reinterpret_cast<const float4*>(mc + shard_off) + i0)
+                   : "memory");
+      if (two)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(a1.x), "=f"(a1.y), "=f"(a1.z), "=f"(a1.w)
+                     : "l"(reinterpret_cast<const float4*>(mc + shard_off) + i1)
+                     : "memory");
+    } else {
+      float4 g0[RPEG_MAX_PEERS], g1[RPEG_MAX_PEERS];
+#pragma unroll
+      for (int p = 0; p < RPEG_MAX_PEERS; ++p) {
+        if (p < world) {
+          const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[p]) + shard_off);
+          g0[p] = src[i0];
+          if (two) g1[p] = src[i1];
+        }
+      }
+#pragma unroll
+      for (int p = 0; p < RPEG_MAX_PEERS; ++p) {
+        if (p < world) {
+          a0.x += g0[p].x; a0.y += g0[p].y; a0.z += g0[p].z; a0.w += g0[p].w;
+          if (two) { a1.x += g1[p].x; a1.y += g1[p].y; a1.z += g1[p].z; a1.w += g1[p].w; }
+        }
+      }
     }
-    a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
-    reinterpret_cast<float4*>(reduced)[i] = a;
-    s += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    a0.x *= scale; a0.y *= scale; a0.z *= scale; a0.w *= scale;
+    reinterpret_cast<float4*>(reduced)[i0] = a0;
+    s += a0.x * a0.x + a0.y * a0.y + a0.z * a0.z + a0.w * a0.w;
+    if (two) {
+      a1.x *= scale; a1.y *= scale; a1.z *= scale; a1.w *= scale;
+      reinterpret_cast<float4*>(reduced)[i1] = a1;
+      s += a1.x * a1.x + a1.y * a1.y + a1.z * a1.z + a1.w * a1.w;
+    }
   }
   s = warp_sum(s);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
@@ -290,15 +326,29 @@ extern "C" int rpeg_wait_flags(const unsigned* flags, int n, unsigned min_versio
   return LAUNCH_OK();
 }
 
-extern "C" int rpeg_dp_reduce_norm(void* const* grads, int world, long long shard_off, long long shard_n,
-                                   float scale, float* reduced, float* sumsq, void* stream) {
+static int reduce_norm_impl(void* const* grads, const float* mc, int world, long long shard_off, long long shard_n,
+                            float scale, float* reduced, float* sumsq, void* stream) {
   if (world < 1 || world > RPEG_MAX_PEERS) return -2;
   if ((shard_off | shard_n) & 3) return -3;
   if (shard_n <= 0) return 0;
-  dp_reduce_norm_kernel<<<sat_grid(shard_n >> 2, 256), 256, 0, STREAM(stream)>>>(make_peers(grads, world), world,
+  dp_reduce_norm_kernel<<<sat_grid(shard_n >> 3, 256), 256, 0, STREAM(stream)>>>(make_peers(grads, world), mc, world,
                                                                                shard_off, shard_n, scale,
                                                                                reduced, sumsq);
   return LAUNCH_OK();
+}
+
+extern "C" int rpeg_dp_reduce_norm(void* const* grads, int world, long long shard_off, long long shard_n,
+                                   float scale, float* reduced, float* sumsq, void* stream) {
+  return reduce_norm_impl(grads, nullptr, world, shard_off, shard_n, scale, reduced, sumsq, stream);
+}
+
+// The same reduction through an NVLink multicast mapping of the gradient buffers (`mc` = multicast address of the
+// buffers' base): NVSwitch adds the ranks' copies, the owner receives the sum.
+extern "C" int rpeg_dp_reduce_norm_mc(const float* mc, int world, long long shard_off, long long shard_n, float scale,
+                                      float* reduced, float* sumsq, void* stream) {
+  if (mc == nullptr) return -4;
+  void* none[RPEG_MAX_PEERS] = {nullptr};
+  return reduce_norm_impl(none, mc, world, shard_off, shard_n, scale, reduced, sumsq, stream);
 }
 
 extern "C" int rpeg_dp_adam_push(float* p32, float* m, float* v, const float* reduced, void* const* params,

@@ -58,7 +58,7 @@ class AdamW:
             return self.partials[: self.dp.world].sum().sqrt()
         return self.sumsq.sqrt()
 
-    def step(self, grad_scale: float = 1.0) -> None:
+    def step(self, grad_scale: float = 1.0, after_wait=None) -> None:
         self.step_count += 1
         m = self.model
         b1, b2 = self.betas
@@ -73,7 +73,7 @@ class AdamW:
             K.adamw_(self.master, self.m, self.v, m.g, m.w, lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, wd=self.wd,
                      step=self.step_count, grad_scale=grad_scale, sumsq=self.sumsq, max_norm=self.max_grad_norm)
             return
-        self.dp.fused_adam_step(self, grad_scale)
+        self.dp.fused_adam_step(self, grad_scale, after_wait)
 
     # -- checkpoint helpers
     def state_dict(self) -> dict:

@@ -36,6 +36,21 @@ def _h2d(t: Optional[torch.Tensor], device, dtype=None) -> Optional[torch.Tensor
     return out if dtype is None else out.to(dtype)
 
 
+def balanced_groups(resp_lens: List[int], prompt_len: int, group: int, ranks: int) -> List[List[int]]:
+    """Deal prompt groups (``group`` consecutive rows each) to ``ranks`` so that the token totals are as even as a
+    greedy pass makes them: groups in order of decreasing tokens, each to the rank with the fewest tokens so far (ties
+    to the lower rank, so every rank computes the same answer). Returns the sorted group indices of each rank."""
+    n_groups = len(resp_lens) // group
+    weight = [sum(prompt_len + int(l) for l in resp_lens[g * group:(g + 1) * group]) for g in range(n_groups)]
+    load = [0] * ranks
+    out: List[List[int]] = [[] for _ in range(ranks)]
+    for g in sorted(range(n_groups), key=lambda g: (-weight[g], g)):
+        r = min(range(ranks), key=lambda r: (load[r], r))
+        out[r].append(g)
+        load[r] += weight[g]
+    return [sorted(gs) for gs in out]
+
+
 class _Base:
     def __init__(self, device, dp=None):
         self.device = torch.device(device)
@@ -149,11 +164,21 @@ class GRPOTrainer(_Base):
             f_all = None
             if forced_lens is not None:
                 f_all = self._all_ranks(torch.as_tensor(forced_lens, dtype=torch.int32).to(self.device)).tolist()
-            whole = self.gen.generate(self._all_ranks(rep), self.max_new, temperature=self.algo.temperature,
+            rep_all = self._all_ranks(rep)
+            whole = self.gen.generate(rep_all, self.max_new, temperature=self.algo.temperature,
                                       seed=self.seed + 100003 * self.iteration, forced_lens=f_all, group_size=self.K)
-            lo = self.dp.rank * N
-            gen = GenerationResult(whole.tokens[lo:lo + N].contiguous(), whole.logprobs[lo:lo + N].contiguous(),
-                                   whole.lengths[lo:lo + N].contiguous(), whole.counters)
+            # Every rank holds every row now, so the rows of the data-parallel phases (reference pass, policy update)
+            # are dealt out by TOKENS rather than by position: whole prompt groups, heaviest first, each to the rank
+            # with the least work so far. The phases end when their slowest rank does.
+            mine = balanced_groups(whole.lengths.tolist(), S, self.K, self.dp.world)[self.dp.rank]
+            rows = torch.tensor([g * self.K + j for g in mine for j in range(self.K)], dtype=torch.long, device=self.device)
+            gen = GenerationResult(whole.tokens[rows].contiguous(), whole.logprobs[rows].contiguous(),
+                                   whole.lengths[rows].contiguous(), whole.counters)
+            rep = rep_all[rows].contiguous()
+            if rewards is not None:
+                self.h2d_bytes += rewards.numel() * rewards.element_size()
+                rewards = self._all_ranks(_h2d(rewards, self.device, torch.float32))[rows].contiguous()
+            N = int(rows.numel())
         else:
             gen = self.gen.generate(rep, self.max_new, temperature=self.algo.temperature,
                                     seed=self.seed + 100003 * self.iteration, forced_lens=forced_lens, group_size=self.K)
@@ -166,14 +191,16 @@ class GRPOTrainer(_Base):
         self._mark("reference")
         if rewards is None:
             raise ValueError("GRPOTrainer.step needs per-sample rewards (the reward model's output)")
-        self.h2d_bytes += rewards.numel() * rewards.element_size()
+        if not self.gen_tp:
+            self.h2d_bytes += rewards.numel() * rewards.element_size()
         ro.scores = _h2d(rewards, self.device, torch.float32)
         A.grpo_advantages(ro, self.K)
         denom = self._global_sum(ro.n_response_tokens())
         self.actor.zero_grad()
         m = A.policy_train_step(self.actor, ro, self.algo, denom_tokens=denom)
         self._mark("train")
-        self.opt.step()
+        # data parallel: the time up to the first barrier of the step is the wait for the slowest rank's backward
+        self.opt.step(after_wait=(lambda: self._mark("grad_wait")) if self.world > 1 else None)
         self._mark("optimizer")
         if self.gen_tp:
             self.gen_model.refresh()      # layout switch: the updated replicated weights -> this rank's generation shards

@@ -137,6 +137,17 @@ class TPDecodeModel:
         self.comm.allgather_cols("logits", B, self.v_loc, V)
         return logits
 
+    @staticmethod
+    def _row_parallel(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ws: torch.Tensor) -> None:
+        """This rank's partial sum of a row-parallel linear as ONE bf16 matrix (what the all-reduce reads). A short
+        contraction (many ranks) runs as a plain GEMM with 128-column tiles: 2 x 32 CTAs each walk the whole K and no
+        second kernel is needed. A long one (few ranks) is cut along K so that every SM streams a slice of the
+        weights, and the fp32 partials are summed by the split-K reduction."""
+        if a.shape[1] <= 1536:
+            K.gemm(a, w, out=out, bn=128)
+        else:
+            K.gemm(a, w, out=out, workspace=ws)
+
     def decode_step(self, token: torch.Tensor, pos: torch.Tensor, slot_ids: torch.Tensor, seq_len: torch.Tensor,
                     page_table: torch.Tensor, kcache: List[torch.Tensor], vcache: List[torch.Tensor], nsplit: int = 1,
                     groups=None) -> torch.Tensor:
@@ -159,11 +170,11 @@ class TPDecodeModel:
                                        page_table, kcache[i], vcache[i], self.n_heads_local, self.n_kv_local, cfg.head_dim)
             attn = K.paged_decode_attn(qkv, 0, kcache[i], vcache[i], page_table, seq_len, self.n_heads_local, self.n_kv_local,
                                        cfg.head_dim, scale, nsplit=nsplit, groups=groups)
-            K.gemm(attn, self.wo[i], out=part)
+            self._row_parallel(attn, self.wo[i], part, ws)
             R.allreduce_rmsnorm("part", h, p[f"l{i}.mlp_norm"], "x", "h", B, d, cfg.rms_eps)
             parts = K.gemm_partials(x, self.wgu[i], ws)
             act = K.swiglu_fwd_partials(parts)
-            K.gemm(act, self.wdown[i], out=part)
+            self._row_parallel(act, self.wdown[i], part, ws)
             last = i + 1 == cfg.n_layers
             R.allreduce_rmsnorm("part", h, p["final_norm"] if last else p[f"l{i + 1}.attn_norm"], "x", None if last else "h", B, d,
                                 cfg.rms_eps)

@@ -91,12 +91,16 @@ class DPContext:
                                       K.status_word(self.device).data_ptr(), torch.cuda.current_stream().cuda_stream),
               "rpeg_flag_barrier")
 
-    def fused_adam_step(self, opt, grad_scale: float = 1.0) -> None:
+    def fused_adam_step(self, opt, grad_scale: float = 1.0, after_wait=None) -> None:
+        """``after_wait()`` is called once the first barrier is queued: what precedes it on the stream is the wait for
+        the slowest rank's backward, what follows is the step itself (callers time the two apart)."""
         w_buf = self.buffers[f"{self.tag}.w"]
         g_buf = self.buffers[f"{self.tag}.g"]
         stream = torch.cuda.current_stream().cuda_stream
         b1, b2 = opt.betas
         self.barrier(0)                                              # every rank finished its backward
+        if after_wait is not None:
+            after_wait()
         opt.sumsq.zero_()
         check(lib().rpeg_dp_reduce_norm(g_buf.ptr_array(), self.world, opt.shard_off, opt.shard_n, grad_scale,
                                         opt.reduced.data_ptr(), opt.sumsq.data_ptr(), stream), "rpeg_dp_reduce_norm")

@@ -28,6 +28,8 @@ def test_runtime_graph_with_pipeline_parallel_training_on_two_ranks(tmp_path):
            "workload": {"batch_size": 8, "samples_per_prompt": 2, "context_length": 32, "generation_length": 48,
                         "gen_quantiles": [[0.5, 16], [1.0, 48]]},
            "training": {"max_steps": 2}, "optimizer": {"k_eval": 2, "plan_family": "pipeline_train"},
+           "data": {"synthetic_response_lengths": "quantiles"},     # rows of a group end at different lengths: the rule reward differs
+          
            "runtime_hardware": {"worker_overhead_bytes": 0},
            "runtime": {"default_backend": "engine", "gen_slots": 8, "micro_tokens": 256}, "outputs": {"seed": 3}}
     dump_mapping(cfg, tmp_path / "job.yaml")
@@ -61,6 +63,8 @@ def test_runtime_graph_with_generation_and_training_on_disjoint_gpus(tmp_path):
            "workload": {"batch_size": 8, "samples_per_prompt": 2, "context_length": 32, "generation_length": 48,
                         "gen_quantiles": [[0.5, 16], [1.0, 48]]},
            "training": {"max_steps": 3}, "optimizer": {"k_eval": 3, "plan_family": "disaggregated"},
+           "data": {"synthetic_response_lengths": "quantiles"},
+          
            "runtime_hardware": {"worker_overhead_bytes": 0}, "checkpoints": {"interval_steps": 100, "save_final": False},
            "runtime": {"default_backend": "engine", "gen_slots": 16, "micro_tokens": 1024, "node_timeout_s": 120}, "outputs": {"seed": 3}}
     dump_mapping(cfg, tmp_path / "job.yaml")
