@@ -225,11 +225,44 @@ def bench_collectives(dev, world: int) -> Dict[str, float]:
             "allreduce_sweep": dict(zip(map(str, sizes), ar_t)), "p2p_sweep": dict(zip(map(str, sizes), p2p_t))}
 
 
+def bench_fused_paths(dev, world: int) -> Dict[str, object]:
+    """This framework's own multi-GPU kernels at their working sizes (more than one rank): the fused all-reduce +
+    residual + RMSNorm of tensor-parallel decoding (microseconds per launch at 256 rows x 4096) and the gradient
+    reduction of the fused data-parallel optimizer step (GB/s of peer gradient bytes entering a rank)."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    from rpeg_b200.ops._lib import check, lib
+    from rpeg_b200.parallel.symm import SymmetricBuffer
+    from rpeg_b200.parallel.tp_decode_selftest import time_collectives
+    out: Dict[str, object] = {"tp_decode": time_collectives(dev, world)}
+    n = 256 * 1024 * 1024                                  # fp32 elements of "gradients" per rank (1 GiB)
+    grads = SymmetricBuffer(n * 4, dev, None, zero=True)
+    per = n // world // 64 * 64
+    reduced = torch.empty(per, dtype=torch.float32, device=dev)
+    sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+    rank = dist.get_rank()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def reduce_once():
+        check(lib().rpeg_dp_reduce_norm(grads.ptr_array(), world, rank * per, per, 1.0, reduced.data_ptr(), sumsq.data_ptr(), stream),
+              "rpeg_dp_reduce_norm")
+
+    dist.barrier()
+    t = torch.tensor([timed(reduce_once, warm=2, iters=5)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out["dp_reduce_s"] = float(t.item())
+    out["dp_reduce_gbs"] = (world - 1) * per * 4 / float(t.item()) / 1e9
+    dist.barrier()
+    grads.close()
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="Calibrate the planner's hardware model on this machine")
     ap.add_argument("--output", default="hw.yaml")
     ap.add_argument("--decode-layers", type=int, default=32, help="layers of the 7B-shape model used for the decode step")
-    ap.add_argument("--skip", default="", help="comma list of: memory,gemm,decode,non_gemm,engine,collectives")
+    ap.add_argument("--skip", default="", help="comma list of: memory,gemm,decode,non_gemm,engine,collectives,fused")
     args = ap.parse_args(argv)
     import torch
     import torch.distributed as dist
@@ -274,6 +307,11 @@ def main(argv=None) -> int:
                 hw[k] = c[k]
             detail.update(allreduce_busbw_gbs=c["allreduce_busbw_gbs"], p2p_gbs=c["p2p_gbs"], allreduce_sweep_s=c["allreduce_sweep"],
                           p2p_sweep_s=c["p2p_sweep"])
+        if "fused" not in skip:
+            f = bench_fused_paths(dev, world)
+            hw["tp_decode_allreduce_s"] = float(f["tp_decode"]["allreduce_rmsnorm_us"]) * 1e-6
+            hw["dp_reduce_gbs"] = float(f["dp_reduce_gbs"])
+            detail["fused_paths"] = f
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:

@@ -395,6 +395,10 @@ class NodeCostModel:
 
         def tp_allreduce(M: float) -> float:
             if hw.fabric == "nvswitch":
+                if pt > 1 and role is Role.GENERATION and hw.tp_decode_allreduce_s > 0 and M <= 8e6:
+                    # one launch of the fused decode all-reduce: its time is flag exchanges and switch round trips,
+                    # not bytes; nothing hides it, the next GEMM needs its result
+                    return hw.tp_decode_allreduce_s + M * hw.beta_coll_g
                 return 0.0 if pt <= 1 else hide * (hw.alpha_coll_g + M * hw.beta_coll_g)
             return 2 * (pt - 1) * hw.alpha_coll_g + 2 * (pt - 1) / pt * M * hw.beta_coll_g
 

@@ -63,6 +63,11 @@ class Hardware:
     gen_max_concurrency: float = 0.0           # generator slots: rows decoding at once per replica (0 = whole batch)
     gen_kv_budget_bytes: float = 0.0           # paged KV pool per GPU; caps the concurrency by the mean context (0 = no cap)
     decode_step_overhead_s: float = 0.0        # per decode step: graph launch, sampling, bookkeeping
+    tp_decode_allreduce_s: float = 0.0         # > 0: measured time of ONE fused all-reduce + residual + RMSNorm launch of the
+    #                                            tensor-parallel decode step (latency bound: two flag exchanges and a switch
+    #                                            round trip); replaces the alpha-beta estimate for decode-sized messages
+    dp_reduce_gbs: float = 0.0                 # > 0: measured rate (GB/s of gradient bytes entering a rank) of the fused
+    #                                            data-parallel gradient reduction; reported by calibrate.py
     expected_lengths: float = 0.0              # > 0: unsplit vertices are priced with the workload's length quantiles
     #                                            (rows stop at their own length) instead of every row running to the cap
     gen_shared_prompt_cost: float = 1.0        # < 1: the K samples of a prompt share its KV pages; a shared prompt token

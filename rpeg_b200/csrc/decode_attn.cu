@@ -431,6 +431,317 @@ paged_decode_attn_shared_kernel(const __nv_bfloat16* __restrict__ q, int ldq, in
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same job on the tensor cores. One persistent CTA per SM walks the (group, head) items; the shared keys of an item
+// are streamed ONCE through a ring of {K tile, V tile} stages (TMA, 128 keys = two pages per tile) and scored against
+// all queries of the group by tcgen05.mma with the KEYS on the M axis:
+//     S^T [128 keys x 16]  = K tile [128 x 128 hd] (A, K-major)  x  Q^T (B: 16 query rows x 128 hd, rows 8..15 zero)
+//     O^T [128 hd   x 16] += V^T    [128 hd x 128 keys] (A, MN-major: the V tile as stored)  x  P^T (B: 16 x 128 keys)
+// Softmax threads own one key (= TMEM lane) each: the per-query maximum over a tile is a warp shuffle plus a four-way
+// exchange through shared memory; the running maximum is refreshed lazily (only when it grows by more than 8 in log2
+// units), so O is rarely rescaled. P goes to shared memory in the B-operand layout. S, P and O are double buffered
+// (S and P by tile, O and Q by item), the next item's Q is staged while the current item runs, and the producer runs
+// ahead across item boundaries, so the HBM stream never stops between items. Output format and the rest of the row
+// (per-row kernel, combine) are those of the CUDA-core version above.
+constexpr int GT_THREADS = 192;
+constexpr int GT_STAGES = 3;
+constexpr int GT_TILE = 128;                       // keys per tile
+constexpr int GT_HALF_BYTES = 64 * 64 * 2;         // one TMA box: 64 rows x 64 columns bf16 = 8 KiB
+constexpr int GT_KV_BYTES = 128 * HD * 2;          // 32 KiB: one K (or V) tile
+constexpr int GT_STAGE_BYTES = 2 * GT_KV_BYTES;
+constexpr int GT_QP_BYTES = 16 * HD * 2;           // 4 KiB: 16 rows x 128 elements, two 64-column atoms of 2 KiB
+constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 4 * GT_QP_BYTES + 1024 /*align*/ + 1024 /*barriers, exchange*/;
+constexpr float GT_RESCALE_THRESHOLD = 8.0f;
+
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+__global__ void __launch_bounds__(GT_THREADS, 1)
+paged_decode_attn_shared_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                                   const __nv_bfloat16* __restrict__ q, int ldq, int q_col0,
+                                   const int* __restrict__ page_table, int max_pages, const int* __restrict__ group_rows,
+                                   const int* __restrict__ group_shared, float* __restrict__ partial, int n_groups, int H,
+                                   int Hkv, int nslots, float scale_log2, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint8_t* q_sm = ring + GT_STAGES * GT_STAGE_BYTES;      // [2][4 KiB]
+  uint8_t* p_sm = q_sm + 2 * GT_QP_BYTES;                 // [2][4 KiB]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_sm + 2 * GT_QP_BYTES);
+  uint64_t* kv_full = bars;                  // [3]
+  uint64_t* kv_empty = kv_full + GT_STAGES;  // [3]
+  uint64_t* s_full = kv_empty + GT_STAGES;   // [2] by tile parity
+  uint64_t* p_full = s_full + 2;             // [2] by tile parity, 4 arrivals
+  uint64_t* pv_done = p_full + 2;            // [2] by tile parity
+  uint64_t* q_full = pv_done + 2;            // [2] by item parity, 4 arrivals
+  uint64_t* o_free = q_full + 2;             // [2] by item parity, 4 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* red = reinterpret_cast<float*>(tmem_slot + 4);   // [4 warps][8 queries]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GT_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 4); mbar_init(&pv_done[b], 1);
+      mbar_init(&q_full[b], 4); mbar_init(&o_free[b], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  // Zero the operand buffers once: rows 8..15 of Q and P stay zero for good, and a tile whose second page does not
+  // exist multiplies stale but finite V rows by probabilities of exactly zero.
+  for (int i = threadIdx.x; i < (GT_STAGES * GT_STAGE_BYTES + 4 * GT_QP_BYTES) / 16; i += GT_THREADS)
+    reinterpret_cast<uint4*>(ring)[i] = make_uint4(0u, 0u, 0u, 0u);
+  fence_proxy_async_smem();
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  griddep_launch();
+  griddep_wait();   // everything above touched only this CTA's own memory
+
+  const int n_items = n_groups * H;
+  const int G = H / Hkv;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+      int t = 0;
+      for (int w = blockIdx.x; w < n_items; w += gridDim.x) {
+        const int g = w / H, h = w % H;
+        const int S = group_shared[g];
+        if (S <= 0) continue;
+        const int hk = h / G;
+        const int* pt = page_table + static_cast<size_t>(group_rows[g * GROUP_MAX]) * max_pages;
+        const int n_pages = S / PAGE;
+        for (int j = 0; j * 2 < n_pages; ++j, ++t) {
+          const int st = t % GT_STAGES;
+          const uint32_t ph = static_cast<uint32_t>(t / GT_STAGES) & 1u;
+          if (!mbar_wait(&kv_empty[st], ph ^ 1u, abort_flag, status, 800)) goto producer_done;
+          const int halves = (2 * j + 1 < n_pages) ? 2 : 1;
+          mbar_expect_tx(&kv_full[st], static_cast<uint32_t>(halves * 4 * GT_HALF_BYTES));
+          uint8_t* ks = ring + st * GT_STAGE_BYTES;
+          uint8_t* vs = ks + GT_KV_BYTES;
+          for (int hf = 0; hf < halves; ++hf) {
+            const int row0 = (pt[2 * j + hf] * Hkv + hk) * PAGE;     // first row of the (page, head) block
+            tma_load_2d(ks + hf * GT_HALF_BYTES, &tmap_k, &kv_full[st], 0, row0);
+            tma_load_2d(ks + 16384 + hf * GT_HALF_BYTES, &tmap_k, &kv_full[st], 64, row0);
+            tma_load_2d(vs + hf * GT_HALF_BYTES, &tmap_v, &kv_full[st], 0, row0);
+            tma_load_2d(vs + 16384 + hf * GT_HALF_BYTES, &tmap_v, &kv_full[st], 64, row0);
+          }
+        }
+      }
+    producer_done:;
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_qk = make_idesc_bf16(128, 16, 0, 0);
+      constexpr uint32_t id_pv = make_idesc_bf16(128, 16, 1, 0);   // A = V tile read MN-major
+      // flat list of this CTA's tiles: (item number, tile in item, tiles of the item) are advanced together
+      int w = blockIdx.x, it = -1, j = 0, nt = 0;
+      auto next_tile = [&]() -> bool {     // moves (w, it, j, nt) to the next tile; false when the items are used up
+        if (it >= 0 && j + 1 < nt) { ++j; return true; }
+        if (it >= 0) w += gridDim.x;
+        for (; w < n_items; w += gridDim.x) {
+          const int S = group_shared[w / H];
+          if (S > 0) { ++it; j = 0; nt = (S / PAGE + 1) / 2; return true; }
+        }
+        return false;
+      };
+      auto issue_qk = [&](int t, int item, int tile_j) -> bool {
+        const int st = t % GT_STAGES;
+        if (tile_j == 0 && !mbar_wait(&q_full[item & 1], static_cast<uint32_t>(item >> 1) & 1u, abort_flag, status, 810)) return false;
+        if (!mbar_wait(&kv_full[st], static_cast<uint32_t>(t / GT_STAGES) & 1u, abort_flag, status, 811)) return false;
+        tc_fence_after_sync();
+        const uint32_t ka = smem_u32(ring + st * GT_STAGE_BYTES);
+        const uint32_t qa = smem_u32(q_sm + (item & 1) * GT_QP_BYTES);
+        const uint32_t ts = tmem_base + static_cast<uint32_t>((t & 1) * 16);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_bf16_ss(ts, make_smem_desc_sw128(ka + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                       make_smem_desc_sw128(qa + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024), id_qk, k != 0 ? 1u : 0u);
+        umma_commit(&s_full[t & 1]);
+        return true;
+      };
+      if (next_tile()) {
+        int t = 0;
+        bool ok = issue_qk(0, it, j);
+        while (ok) {
+          const int cur_it = it, cur_j = j;
+          const bool more = next_tile();
+          if (more && !issue_qk(t + 1, it, j)) break;                // S of the next tile is computed under this tile's softmax
+          if (!mbar_wait(&p_full[t & 1], static_cast<uint32_t>(t >> 1) & 1u, abort_flag, status, 812)) break;
+          if (cur_j == 0 && cur_it >= 2 &&
+              !mbar_wait(&o_free[cur_it & 1], (static_cast<uint32_t>(cur_it >> 1) & 1u) ^ 1u, abort_flag, status, 813)) break;
+          tc_fence_after_sync();
+          const int st = t % GT_STAGES;
+          const uint32_t va = smem_u32(ring + st * GT_STAGE_BYTES + GT_KV_BYTES);
+          const uint32_t pa = smem_u32(p_sm + (t & 1) * GT_QP_BYTES);
+          const uint32_t to = tmem_base + 32u + static_cast<uint32_t>((cur_it & 1) * 16);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)      // 16 keys per step
+            umma_bf16_ss(to, make_smem_desc_sw128(va + k * 2048, 16384, 1024),
+                         make_smem_desc_sw128(pa + (k >> 2) * 2048 + (k & 3) * 32, 16, 1024), id_pv, (cur_j | k) != 0 ? 1u : 0u);
+          umma_commit(&kv_empty[st]);
+          umma_commit(&pv_done[t & 1]);
+          if (!more) break;
+          ++t;
+        }
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;                    // key inside a tile (softmax), head dim (O^T)
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const int tq = threadIdx.x - 64;                   // 0..127
+    auto stage_q = [&](int item_w, int item_no) {      // 8 rows x 16 chunks of 16 bytes: one chunk per thread
+      const int g = item_w / H, h = item_w % H;
+      const int row = tq >> 4, chunk = tq & 15;
+      const int br = group_rows[g * GROUP_MAX + row];
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (br >= 0) v = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(br) * ldq + q_col0 + h * HD + chunk * 8);
+      uint8_t* dst = q_sm + (item_no & 1) * GT_QP_BYTES + (chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+      *reinterpret_cast<uint4*>(dst) = v;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_full[item_no & 1]);
+    };
+    auto next_item = [&](int w0) -> int {              // first valid item at or after w0 in this CTA's sequence
+      for (int w = w0; w < n_items; w += gridDim.x)
+        if (group_shared[w / H] > 0) return w;
+      return -1;
+    };
+    int w = next_item(blockIdx.x);
+    if (w >= 0) stage_q(w, 0);
+    int t = 0;
+    bool ok = true;
+    for (int it = 0; w >= 0 && ok; ++it) {
+      const int w_next = next_item(w + gridDim.x);
+      if (w_next >= 0) stage_q(w_next, it + 1);        // Q buffer (it+1)&1 was last read by item it-1, whose MMAs are complete
+      const int g = w / H, h = w % H;
+      const int S = group_shared[g];
+      const int nt = (S / PAGE + 1) / 2;
+      float m[GROUP_MAX], l[GROUP_MAX];
+#pragma unroll
+      for (int qi = 0; qi < GROUP_MAX; ++qi) { m[qi] = -INFINITY; l[qi] = 0.f; }
+      const uint32_t t_o = tmem_base + 32u + static_cast<uint32_t>((it & 1) * 16) + lane_base;
+      for (int j = 0; j < nt; ++j, ++t) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&s_full[t & 1], static_cast<uint32_t>(t >> 1) & 1u, abort_flag, status, 820))) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t sv[8];
+        tmem_ld_32x8(tmem_base + static_cast<uint32_t>((t & 1) * 16) + lane_base, sv);
+        tmem_wait_ld();
+        const bool key_valid = j * GT_TILE + r < S;
+        float sc[GROUP_MAX];
+#pragma unroll
+        for (int qi = 0; qi < GROUP_MAX; ++qi) {
+          sc[qi] = key_valid ? __uint_as_float(sv[qi]) * scale_log2 : -INFINITY;
+          const float wm = warp_max(sc[qi]);
+          if (lane == 0) red[quad * GROUP_MAX + qi] = wm;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        float tmax[GROUP_MAX];
+        bool need = false;
+#pragma unroll
+        for (int qi = 0; qi < GROUP_MAX; ++qi) {
+          tmax[qi] = fmaxf(fmaxf(red[qi], red[GROUP_MAX + qi]), fmaxf(red[2 * GROUP_MAX + qi], red[3 * GROUP_MAX + qi]));
+          if (j == 0) m[qi] = tmax[qi];
+          else need = need || (tmax[qi] > m[qi] + GT_RESCALE_THRESHOLD);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // `red` may be rewritten by the next tile
+        if (need) {                                        // the same decision in every thread: all hold the same m and tmax
+          // PV of the previous tile must have landed before O is rescaled. Having seen s_full of this tile, the waiter
+          // is at most one completion behind on the barrier of that parity (see flash_attn_fwd_kernel).
+          if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(t - 1) & 1], static_cast<uint32_t>((t - 1) >> 1) & 1u, abort_flag, status, 821))) { ok = false; break; }
+          tc_fence_after_sync();
+          float alpha[GROUP_MAX];
+#pragma unroll
+          for (int qi = 0; qi < GROUP_MAX; ++qi) {
+            const float nm = fmaxf(m[qi], tmax[qi]);
+            alpha[qi] = exp2f(m[qi] - nm);
+            m[qi] = nm;
+            l[qi] *= alpha[qi];
+          }
+          uint32_t ov[8];
+          tmem_ld_32x8(t_o, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int qi = 0; qi < GROUP_MAX; ++qi) ov[qi] = __float_as_uint(__uint_as_float(ov[qi]) * alpha[qi]);
+          tmem_st_32x8(t_o, ov);
+          tmem_wait_st();
+          tc_fence_before_sync();
+        }
+        // P^T in the B-operand layout: row = query, 128 keys contiguous (two 64-key atoms), 128-byte swizzle
+        uint8_t* pb = p_sm + (t & 1) * GT_QP_BYTES + (r >> 6) * 2048 + (r & 7) * 2;
+        const int chunk = (r & 63) >> 3;
+#pragma unroll
+        for (int qi = 0; qi < GROUP_MAX; ++qi) {
+          const float pr = exp2f(sc[qi] - m[qi]);          // masked keys: exp2(-inf) = 0
+          l[qi] += pr;
+          *reinterpret_cast<__nv_bfloat16*>(pb + qi * 128 + ((chunk ^ qi) << 4)) = __float2bfloat16(pr);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t & 1]);
+      }
+      if (!ok) break;
+      // item epilogue: this thread is head dim r of O^T; l is summed over the 128 key owners
+      if (!__all_sync(0xffffffffu, mbar_wait(&pv_done[(t - 1) & 1], static_cast<uint32_t>((t - 1) >> 1) & 1u, abort_flag, status, 822))) { ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t ov[8];
+      tmem_ld_32x8(t_o, ov);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_free[it & 1]);
+#pragma unroll
+      for (int qi = 0; qi < GROUP_MAX; ++qi) {
+        const float ws = warp_sum(l[qi]);
+        if (lane == 0) red[quad * GROUP_MAX + qi] = ws;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+      for (int qi = 0; qi < GROUP_MAX; ++qi) {
+        const int br = group_rows[g * GROUP_MAX + qi];
+        if (br < 0) continue;
+        float* pp = partial + (static_cast<size_t>(br) * H + h) * nslots * (HD + 2);
+        pp[r] = __uint_as_float(ov[qi]);
+        if (r == 0) {
+          pp[HD] = m[qi];
+          pp[HD + 1] = red[qi] + red[GROUP_MAX + qi] + red[2 * GROUP_MAX + qi] + red[3 * GROUP_MAX + qi];
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      w = w_next;
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) __nanosleep(200000);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 64);
+  }
+}
+
 __global__ void __launch_bounds__(HD)
 decode_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int H, int nsplit) {
   griddep_launch();
@@ -536,6 +847,54 @@ extern "C" int rpeg_paged_decode_attn_grouped(const void* q, int ldq, int q_col0
   launch_pdl(paged_decode_attn_shared_kernel, dim3(H, B), dim3(128), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(q), ldq,
              q_col0, static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages,
              group_rows, group_shared, scratch, H, Hkv, nslots, scale_log2);
+  launch_pdl(paged_decode_attn_kernel, dim3(H, B, nsplit), dim3(128), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(q), ldq,
+             q_col0, static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages,
+             seq_lens, static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, row_key0, 1, nslots);
+  launch_pdl(decode_combine_kernel, dim3(H, B), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nslots);
+  return LAUNCH_OK();
+}
+
+namespace rpeg {
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                      uint32_t box_outer);
+}
+
+// rpeg_paged_decode_attn_grouped with the shared keys on the tensor cores (paged_decode_attn_shared_tc_kernel).
+// `num_pages` is the page count of the K / V pools (bounds of the TMA descriptors).
+extern "C" int rpeg_paged_decode_attn_grouped_tc(const void* q, int ldq, int q_col0, const void* kcache, const void* vcache,
+                                                 long long num_pages, const int* page_table, int max_pages, const int* seq_lens,
+                                                 void* out, float* scratch, int B, int H, int Hkv, int hd, int nsplit, float scale,
+                                                 const int* group_rows, const int* group_shared, const int* row_key0, int* status,
+                                                 void* stream) {
+  if (hd != HD || H % Hkv != 0) return -2;
+  if (nsplit < 1 || nsplit > 63) return -3;
+  if (scratch == nullptr || group_rows == nullptr || group_shared == nullptr || row_key0 == nullptr) return -4;
+  if ((ldq | q_col0) & 7) return -5;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kcache) | reinterpret_cast<uintptr_t>(vcache)) & 15) return -1;
+  if (B <= 0) return 0;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const int nslots = nsplit + 1;
+  CUtensorMap tk, tv;
+  const uint64_t rows = static_cast<uint64_t>(num_pages) * Hkv * PAGE;
+  int rc = make_tmap_bf16_2d(&tk, kcache, HD, rows, HD, 64, 64);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tv, vcache, HD, rows, HD, 64, 64);
+  if (rc) return rc - 100;
+  static bool configured = false;
+  static int num_sms = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(paged_decode_attn_shared_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM) != cudaSuccess)
+      return -20;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    configured = true;
+  }
+  const int items = B * H;
+  const int grid = items < num_sms ? items : num_sms;
+  launch_pdl(paged_decode_attn_shared_tc_kernel, dim3(grid), dim3(GT_THREADS), GT_SMEM, STREAM(stream), tk, tv,
+             static_cast<const __nv_bfloat16*>(q), ldq, q_col0, page_table, max_pages, group_rows, group_shared, scratch, B, H, Hkv,
+             nslots, scale_log2, status);
   launch_pdl(paged_decode_attn_kernel, dim3(H, B, nsplit), dim3(128), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(q), ldq,
              q_col0, static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages,
              seq_lens, static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, row_key0, 1, nslots);

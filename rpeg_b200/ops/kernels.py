@@ -487,10 +487,12 @@ def decode_scratch_numel(B: int, H: int, nsplit: int) -> int:
 
 
 def paged_decode_attn(q, q_col0, kcache, vcache, page_table, seq_lens, n_heads, n_kv_heads, head_dim, scale,
-                      nsplit: int = 1, scratch: torch.Tensor | None = None, out: torch.Tensor | None = None, groups=None):
+                      nsplit: int = 1, scratch: torch.Tensor | None = None, out: torch.Tensor | None = None, groups=None,
+                      group_tc: bool = True):
     """``groups = (group_rows [B, 8] int32, group_shared [B] int32, row_key0 [B] int32)``: rows that alias their first
     KV pages in groups (K samples of one prompt); the shared keys are then read once per group (``scratch`` must
-    hold ``nsplit + 1`` partials per row and head)."""
+    hold ``nsplit + 1`` partials per row and head). ``group_tc``: score the groups on the tensor cores (tcgen05, keys on
+    the M axis) instead of the CUDA-core kernel."""
     B = q.shape[0]
     if _chk.active():
         _chk.paged_attention("rpeg_paged_decode_attn", B, seq_lens, page_table, kcache, n_kv_heads, head_dim)
@@ -499,6 +501,15 @@ def paged_decode_attn(q, q_col0, kcache, vcache, page_table, seq_lens, n_heads, 
         group_rows, group_shared, row_key0 = groups
         if scratch is None:
             scratch = torch.empty(decode_scratch_numel(B, n_heads, nsplit + 1), dtype=torch.float32, device=q.device)
+        if group_tc:
+            check(lib().rpeg_paged_decode_attn_grouped_tc(q.data_ptr(), q.stride(0), q_col0, kcache.data_ptr(), vcache.data_ptr(),
+                                                          kcache.shape[0], page_table.data_ptr(), page_table.stride(0),
+                                                          seq_lens.data_ptr(), out.data_ptr(), scratch.data_ptr(), B, n_heads,
+                                                          n_kv_heads, head_dim, nsplit, scale, group_rows.data_ptr(),
+                                                          group_shared.data_ptr(), row_key0.data_ptr(),
+                                                          status_word(q.device).data_ptr(), _stream()),
+                  "rpeg_paged_decode_attn_grouped_tc")
+            return out
         check(lib().rpeg_paged_decode_attn_grouped(q.data_ptr(), q.stride(0), q_col0, kcache.data_ptr(), vcache.data_ptr(),
                                                    page_table.data_ptr(), page_table.stride(0), seq_lens.data_ptr(), out.data_ptr(),
                                                    scratch.data_ptr(), B, n_heads, n_kv_heads, head_dim, nsplit, scale,

@@ -24,9 +24,46 @@ import torch
 import torch.distributed as dist
 
 
+def time_collectives(dev, world: int, comm_mode=None, rows: int = 256, d: int = 4096, vocab: int = 32000, iters: int = 200) -> dict:
+    """Microseconds per launch of ``allreduce_rmsnorm`` ([rows, d] bf16 partial sums) and ``allgather_cols``
+    ([rows, vocab] logits), back to back on one stream as in a decode step; CUDA events, maximum over ranks."""
+    from rpeg_b200.parallel.tp_comm import TPCommRegion
+    R = TPCommRegion(3 * rows * d * 2 + rows * vocab * 2 + 4096, dev, None, comm_mode)
+    for name in ("part", "x", "h"):
+        R.alloc(name, rows * d * 2)
+    R.alloc("logits", rows * vocab * 2)
+    R.view("part", (rows, d)).fill_(0.01)
+    R.view("h", (rows, d)).zero_()
+    w = torch.ones(d, dtype=torch.bfloat16, device=dev)
+    h = R.view("h", (rows, d))
+    out = {"backend": R.backend, "rows": rows, "d": d, "vocab": vocab}
+    v_loc = vocab // world // 8 * 8
+    for name, fn in (("allreduce_rmsnorm_us", lambda: R.allreduce_rmsnorm("part", h, w, "x", None, rows, d, 1e-5)),
+                     ("allgather_cols_us", lambda: R.allgather_cols("logits", rows, v_loc, vocab))):
+        for _ in range(20):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name] = float(t.item())
+    R.close()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--comm", default=None, help="peer | nvls | auto (default: RPEG_TP_COMM or auto)")
+    ap.add_argument("--bench", action="store_true", help="also time the two collectives at decode size (256 rows x 4096, "
+                                                         "256 x 32000 logits): CUDA events, max over ranks, microseconds per launch")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -44,7 +81,7 @@ def main() -> int:
 
     cfg = LlamaConfig(n_layers=2, d_model=1024, d_ff=2048, n_heads=8, n_kv_heads=8, head_dim=128, vocab=2048, max_pos=256)
     full = LlamaModel(cfg, dev, seed=5)
-    tpm = TPDecodeModel(full, None, max_batch=32, comm_mode=args.comm)
+    tpm = TPDecodeModel(full, None, max_batch=256 if args.bench else 32, comm_mode=args.comm)
     R = tpm.comm
     rep = {"world": world, "backend": R.backend, "multicast_error": getattr(R, "multicast_error", None)}
 
@@ -135,6 +172,8 @@ def main() -> int:
     rep["gen_identical_on_ranks"] = same_everywhere(got_g.tokens) and same_everywhere(got_g.logprobs)
     rep["reshard_us"] = tpm.last_reshard_us
     K.check_status()
+    if args.bench:
+        rep["bench"] = time_collectives(dev, world, args.comm)
     rep["ok"] = bool(rep["ar_max_rel_err"] < 2e-2 and rep["ar_identical"] and rep["allgather_ok"] and step_err < 4e-2
                      and rep["kv_cache_matches"] and rep["gen_prefix_share"] > 0.6 and rep["gen_logprob_max_diff"] < 0.15
                      and rep["gen_identical_on_ranks"])

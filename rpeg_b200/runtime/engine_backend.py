@@ -79,6 +79,9 @@ def validate_engine_plan(compiled) -> str:
       ``"pipeline_train"``   generation / inference vertices ``(G, 1, 1)``, every training vertex ``(1, G, 1)`` (GRPO):
                              the update runs 1F1B over all ranks as stages, the publication edge is a real layout
                              switch (stage weights broadcast into the replicated generation copy)
+      ``"tp_generation"``    the generation vertex ``(1, 1, G)``: every GPU decodes the whole batch on its shard of the weights
+                             and KV heads (``models.tp_decode``), every other vertex ``(G, 1, 1)`` (GRPO); the RESHARD node of
+                             the publication edge re-slices the updated weights into the generation layout
       ``"disaggregated"``    generation data parallel on some GPUs, everything else data parallel on the others (GRPO),
                              any staleness ``tau >= 0``: the two sides run concurrently and meet through versioned
                              peer-memory channels (``engine.async_rl.AsyncGRPO``)"""
@@ -99,9 +102,11 @@ def validate_engine_plan(compiled) -> str:
         return "disaggregated"
     train = [v for v in cfg.rpeg.vertices if v.kind.role is Role.TRAINING]
     piped = g > 1 and bool(train) and all(tuple(cfg.plan.pi[v.id]) == (1, g, 1) for v in train)
+    gens = [v for v in cfg.rpeg.vertices if v.kind.role is Role.GENERATION]
+    tp_gen = g > 1 and bool(gens) and all(tuple(cfg.plan.pi[v.id]) == (1, 1, g) for v in gens)
     for v in cfg.rpeg.vertices:
         dp, pp, tp = cfg.plan.pi[v.id]
-        if piped and v in train:
+        if (piped and v in train) or (tp_gen and v in gens):
             continue
         if pp != 1 or tp != 1 or dp != g:
             raise RuntimeConfigError(f"engine backend runs data-parallel plans, or data-parallel generation with pipeline-parallel "
@@ -118,6 +123,12 @@ def validate_engine_plan(compiled) -> str:
                                  "(optimizer.plan_family: disaggregated)")
     if float(getattr(compiled.run_config.algorithm, "entropy_coef", 0.0) or 0.0) != 0.0 and compiled.run_config.algorithm.name == "dpo":
         raise RuntimeConfigError("engine backend: algorithm.entropy_coef applies to the PPO / GRPO policy objective, not to DPO; set it to 0")
+    if tp_gen:
+        if piped:
+            raise RuntimeConfigError("engine backend: tensor-parallel generation with pipeline-parallel training is not a supported combination")
+        if compiled.run_config.algorithm.name != "grpo":
+            raise RuntimeConfigError("engine backend: a tensor-parallel generation vertex is implemented for GRPO only")
+        return "tp_generation"
     return "pipeline_train" if piped else "data_parallel"
 
 
@@ -141,7 +152,7 @@ class EngineOperationHandler:
         if self.world > 1:
             if not dist.is_initialized():
                 dist.init_process_group("nccl", device_id=self.device)
-            if self.family == "data_parallel":
+            if self.family in ("data_parallel", "tp_generation"):
                 from ..parallel.dp import DPContext
                 self.dp = DPContext(self.device)
         a, w, rt, o = run.algorithm, run.workload, run.runtime, run.optimizer_runtime
@@ -176,7 +187,8 @@ class EngineOperationHandler:
         elif a.name == "grpo":
             self.trainer = GRPOTrainer(cfg, samples_per_prompt=w.samples_per_prompt, max_new=w.generation_length,
                                        prompt_len=w.context_length, lr=o.learning_rate_actor, gen_slots=rt.gen_slots,
-                                       eos_id=run.tokenizer.eos_token_id, use_graphs=rt.use_cuda_graphs, **common)
+                                       eos_id=run.tokenizer.eos_token_id, use_graphs=rt.use_cuda_graphs,
+                                       gen_tp=self.family == "tp_generation", **common)
         elif a.name == "ppo":
             r = run.models.get("reward")
             self.trainer = PPOTrainer(cfg, max_new=w.generation_length, prompt_len=w.context_length, lr_actor=o.learning_rate_actor,
@@ -219,7 +231,14 @@ class EngineOperationHandler:
     # ------------------------------------------------------------------ operators
     def _generate(self, st, step: int) -> Dict[str, Any]:
         tr, A, torch, w = self.trainer, self.A, self.torch, self.run.workload
-        prompts = self._prompts(step).to(self.device)
+        tp_gen = self.family == "tp_generation"
+        sl = self._local(w.batch_size)
+        rows_local = slice(sl.start * w.samples_per_prompt, sl.stop * w.samples_per_prompt)
+        # a tensor-parallel generation vertex works on the WHOLE batch on every rank; the data-parallel vertices after
+        # it take their slice of the result
+        prompts = (self._prompts_global(step) if (tp_gen and not self.run.data.train_prompts) else self._prompts(step)).to(self.device)
+        if tp_gen and self.run.data.train_prompts:
+            prompts = tr._all_ranks(prompts)
         rep = prompts.repeat_interleave(w.samples_per_prompt, dim=0).contiguous()
         a = self.run.algorithm
         forced = None
@@ -227,10 +246,14 @@ class EngineOperationHandler:
             from .data import quantile_lengths
             rows = w.batch_size * w.samples_per_prompt                 # drawn for the global batch, cut like the prompts
             all_lens = quantile_lengths(rows, w.quantile_tuples(), seed=self.run.data.data_seed * 1000003 + step)
-            sl = self._local(w.batch_size)
-            forced = all_lens[sl.start * w.samples_per_prompt:sl.stop * w.samples_per_prompt]
+            forced = all_lens if tp_gen else all_lens[rows_local]
         gen = tr.gen.generate(rep, w.generation_length, temperature=a.temperature, greedy=a.greedy, seed=a.seed + 100003 * step,
                               group_size=w.samples_per_prompt, top_k=a.top_k, top_p=a.top_p, forced_lens=forced)
+        if tp_gen:
+            from ..engine.generation import GenerationResult
+            gen = GenerationResult(gen.tokens[rows_local].contiguous(), gen.logprobs[rows_local].contiguous(),
+                                   gen.lengths[rows_local].contiguous(), gen.counters)
+            rep = rep[rows_local].contiguous()
         lens = gen.lengths.tolist()
         st["rollout"] = A.Rollout(rep, [w.context_length] * rep.shape[0], gen.tokens, lens, gen.logprobs, gen.response_mask(),
                                   weight_version=self.latest.get("ac_share" if self.shared else "actor", 0))
@@ -494,6 +517,16 @@ class EngineOperationHandler:
                 done = [s for s in self.steps if s < (step or 0)]
                 for s in done:           # rollouts of closed steps are dead
                     del self.steps[s]
+        elif (node.kind is ExecNodeType.RESHARD and self.family == "tp_generation" and name in ("actor", "ac_share")
+              and getattr(self.trainer, "gen_tp", False)):
+            # publication edge t_pi -> g_pi: the updated replicated weights are re-sliced into this rank's shards of the
+            # tensor-parallel generation layout (strided device copies, timed on the device)
+            gm = self.trainer.gen_model
+            before = gm.refreshes
+            gm.refresh()
+            K.check_status()
+            c.update(payload_in_bytes=node.payload_in_bytes, transferred_bytes=int(gm.shard.numel() * 2), transport="layout_switch",
+                     label=node.label, reshard_us=float(gm.last_reshard_us or 0.0), layout_switches=gm.refreshes - before)
         else:
             c.update(payload_in_bytes=node.payload_in_bytes, transferred_bytes=0, transport="in_place", label=node.label)
         ref = ContainerRef(f"{node.node_id}:output", step or 0, split_part_index(node.node_id), producer=node.node_id)

@@ -235,7 +235,7 @@ def predicted_schedule(config: Configuration, suite, workload, hw, horizon: int,
 
 
 def data_parallel_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k_eval: int, policy: MemoryPolicy, fusion: bool,
-                                transfer_policy, *, pipeline_train: bool = False) -> Optional[Configuration]:
+                                transfer_policy, *, pipeline_train: bool = False, tp_generation: bool = False) -> Optional[Configuration]:
     """The plan families the engine backend executes, all on the whole device space: every vertex data parallel over
     all GPUs (``pi = (G, 1, 1)``), or, with ``pipeline_train``, generation and inference data parallel and every
     training vertex pipeline parallel over all GPUs (``pi = (1, G, 1)``: gradients and optimizer state of a stage
@@ -252,6 +252,10 @@ def data_parallel_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k
         for v in rpeg.vertices:
             if pipeline_train and v.kind.role is Role.TRAINING:
                 plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (1, g, 1), max(mb, g)
+            elif tp_generation and v.kind.role is Role.GENERATION:
+                # every GPU decodes the whole batch on 1/G of the weights and KV heads; the publication edge from the
+                # data-parallel training vertex to this one is a layout switch (RESHARD node)
+                plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (1, 1, g), 1
             else:
                 plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (g, 1, 1), mb
         last = Configuration(rpeg, plan, space, fusion, transfer_policy)
@@ -456,7 +460,7 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
     # "disaggregated" generation on ``optimizer.gen_gpus`` GPUs and the rest elsewhere (what ``policy.tau > 0`` needs).
     engine_job = str((cfg.get("runtime") or {}).get("default_backend", "")) == "engine"
     family = str(options.get("plan_family", "data_parallel" if engine_job and space.num_devices() > 1 else "search"))
-    if family not in ("search", "data_parallel", "pipeline_train", "engine", "disaggregated"):
+    if family not in ("search", "data_parallel", "pipeline_train", "tp_generation", "engine", "disaggregated"):
         raise RuntimeConfigError(f"[optimizer] unknown plan_family {family!r}")
     if family == "disaggregated":
         best = disaggregated_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy,
@@ -464,16 +468,18 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
         if best is None:
             raise RuntimeConfigError("the disaggregated plan does not fit into memory on this machine")
         feasible, attempts = True, 0
-    if family in ("data_parallel", "pipeline_train", "engine"):
-        # "engine": whichever of the two executable families fits into memory and is predicted faster
-        if family == "pipeline_train" and algorithm != "grpo":
-            raise RuntimeConfigError("[optimizer] plan_family pipeline_train: the engine backend runs pipeline-parallel training for GRPO only")
+    if family in ("data_parallel", "pipeline_train", "tp_generation", "engine"):
+        # "engine": whichever of the executable families fits into memory and is predicted fastest. "tp_generation":
+        # generation tensor parallel over all GPUs of the node, everything else data parallel (GRPO).
+        if family in ("pipeline_train", "tp_generation") and algorithm != "grpo":
+            raise RuntimeConfigError(f"[optimizer] plan_family {family}: the engine backend runs it for GRPO only")
         cands = []
-        for piped in ((False, True) if family == "engine" else (family == "pipeline_train",)):
-            if piped and (algorithm != "grpo" or space.num_devices() < 2):
+        kinds = (("dp", "pp", "tp") if family == "engine" else ({"data_parallel": "dp", "pipeline_train": "pp", "tp_generation": "tp"}[family],))
+        for kind in kinds:
+            if kind != "dp" and (algorithm != "grpo" or space.num_devices() < 2):
                 continue
             c = data_parallel_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy,
-                                            pipeline_train=piped)
+                                            pipeline_train=kind == "pp", tp_generation=kind == "tp")
             if c is not None:
                 cands.append((predicted_schedule(c, suite, workload, hw, horizon, policy)[0].makespan(), len(cands), c))
         best = min(cands)[2] if cands else None

@@ -323,6 +323,59 @@ def test_kv_append_and_paged_decode(cuda_device, nsplit, H, Hkv):
         off += l
 
 
+@pytest.mark.parametrize("tc", [True, False])
+@pytest.mark.parametrize("H,Hkv,shared_pages", [(4, 4, 3), (8, 2, 8), (4, 4, 1)])
+def test_paged_decode_attn_with_shared_prompt_groups(cuda_device, tc, H, Hkv, shared_pages):
+    """Rows that alias their first KV pages in groups: the group kernel (tensor cores with ``tc``, CUDA cores without)
+    scores the shared keys once per group, the per-row kernel the private rest; against fp32 PyTorch over each row's
+    own page list. Groups of 8, 5 and 3 rows, one row outside any group, odd and even numbers of shared pages."""
+    hd, P = 128, K.KV_PAGE
+    g = torch.Generator(device="cpu").manual_seed(4)
+    sizes = [8, 5, 3]
+    private = [70, 1, 130, 64, 9, 33, 200, 5, 17, 64, 3, 99, 128, 45, 7, 61, 250]      # private keys per row (the last row is ungrouped)
+    B = sum(sizes) + 1
+    S = shared_pages * P
+    max_pages = shared_pages + 5
+    n_pages = 1 + len(sizes) * shared_pages + B * 5
+    kc = torch.randn(n_pages, Hkv, P, hd, generator=g).bfloat16().to(cuda_device)
+    vc = torch.randn(n_pages, Hkv, P, hd, generator=g).bfloat16().to(cuda_device)
+    table = torch.zeros(B, max_pages, dtype=torch.int32)
+    nxt, row = 1, 0
+    group_rows = torch.full((B, 8), -1, dtype=torch.int32)
+    group_shared = torch.zeros(B, dtype=torch.int32)
+    row_key0 = torch.zeros(B, dtype=torch.int32)
+    lens = []
+    for gi, n in enumerate(sizes):
+        shared = list(range(nxt, nxt + shared_pages))
+        nxt += shared_pages
+        for j in range(n):
+            table[row, :shared_pages] = torch.tensor(shared, dtype=torch.int32)
+            own = (private[row] + P - 1) // P
+            table[row, shared_pages:shared_pages + own] = torch.arange(nxt, nxt + own, dtype=torch.int32)
+            nxt += own
+            group_rows[gi, j] = row
+            row_key0[row] = S
+            lens.append(S + private[row])
+            row += 1
+        group_shared[gi] = S
+    own = (S + private[row] + P - 1) // P                        # the ungrouped row owns all its pages
+    table[row, :own] = torch.arange(nxt, nxt + own, dtype=torch.int32)
+    lens.append(S + private[row])
+    q = torch.randn(B, H * hd, generator=g).bfloat16().to(cuda_device)
+    table, seq = table.to(cuda_device), torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+    groups = (group_rows.to(cuda_device), group_shared.to(cuda_device), row_key0.to(cuda_device))
+    for nsplit in (1, 3):
+        out = K.paged_decode_attn(q, 0, kc, vc, table, seq, H, Hkv, hd, 1 / math.sqrt(hd), nsplit=nsplit, groups=groups, group_tc=tc)
+        K.check_status()
+        for b, l in enumerate(lens):
+            pages = table[b, : (l + P - 1) // P].long()
+            kk = kc[pages].float().permute(1, 0, 2, 3).reshape(Hkv, -1, hd)[:, :l].repeat_interleave(H // Hkv, 0)
+            vv = vc[pages].float().permute(1, 0, 2, 3).reshape(Hkv, -1, hd)[:, :l].repeat_interleave(H // Hkv, 0)
+            p = torch.softmax(torch.einsum("hd,hld->hl", q[b].float().view(H, hd), kk) / math.sqrt(hd), -1)
+            ref = torch.einsum("hl,hld->hd", p, vv).reshape(-1)
+            assert _rel_err(out[b], ref) < 1.5e-2, f"row {b} (nsplit {nsplit})"
+
+
 @pytest.mark.parametrize("lens", [[128], [5, 130, 257], [1000, 31, 384]])
 @pytest.mark.parametrize("H,Hkv", [(4, 4), (4, 2)])
 def test_flash_attn_fwd(cuda_device, lens, H, Hkv):

@@ -165,6 +165,34 @@ def test_engine_jobs_can_ask_for_pipeline_parallel_training(tmp_path):
     compiled.run_config.algorithm.name = "grpo"
 
 
+def test_engine_jobs_can_ask_for_tensor_parallel_generation(tmp_path):
+    """``optimizer.plan_family: tp_generation``: the generation vertex ``(1, 1, G)``, everything else ``(G, 1, 1)``. The pair
+    compiles, the publication edge from the data-parallel training vertex becomes a RESHARD node (the layout switch the
+    engine backend executes), the backend recognises the family and the graph verifies with the metadata backend."""
+    from rpeg_b200.runtime.engine_backend import validate_engine_plan
+    cfg = job_mapping("grpo", steps=2, runtime={"default_backend": "engine", "gen_slots": 16, "micro_tokens": 1024})
+    cfg["device_space"] = {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4}
+    cfg["optimizer"].update(plan_family="tp_generation")
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    res = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out", quiet=True)
+    compiled = res["compiled"]
+    assert validate_engine_plan(compiled) == "tp_generation"
+    assert tuple(compiled.config.plan.pi["g_pi"]) == (1, 1, 4) and tuple(compiled.config.plan.pi["t_pi"]) == (4, 1, 1)
+    assert any(n.kind is ExecNodeType.RESHARD for n in compiled.lowered.nodes)
+    graph, ctx, events = execute(compile_runtime_plan(res["run_file"]), tmp_path)
+    assert verify_runtime_trace(compiled, graph, events)["ok"]
+    compiled.run_config.algorithm.name = "ppo"
+    with pytest.raises(RuntimeConfigError, match="GRPO only"):
+        validate_engine_plan(compiled)
+    compiled.run_config.algorithm.name = "grpo"
+    ppo = job_mapping("ppo", steps=2, runtime={"default_backend": "engine", "gen_slots": 16, "micro_tokens": 1024})
+    ppo["device_space"] = cfg["device_space"]
+    ppo["optimizer"].update(plan_family="tp_generation")
+    dump_mapping(ppo, tmp_path / "job2.yaml")
+    with pytest.raises(RuntimeConfigError, match="GRPO only"):
+        plan_runtime_job(tmp_path / "job2.yaml", tmp_path / "out2", quiet=True)
+
+
 @pytest.mark.parametrize("tau", [0, 1])
 def test_engine_jobs_can_put_generation_and_training_on_disjoint_gpus(tmp_path, tau):
     """``optimizer.plan_family: disaggregated``: generation data parallel on ``gen_gpus`` GPUs, the rest on the others; with
