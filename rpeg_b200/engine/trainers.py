@@ -97,7 +97,8 @@ class GRPOTrainer(_Base):
     def __init__(self, cfg: LlamaConfig, *, device="cuda:0", samples_per_prompt: int = 8, max_new: int = 2048,
                  prompt_len: int = 512, algo: Optional[A.AlgoConfig] = None, lr: float = 1e-6, gen_slots: int = 64,
                  kv_budget_bytes: float = 40e9, recompute: str = "full", dp=None, seed: int = 0, eos_id: int = 2,
-                 sync_interval: int = 8, use_graphs: bool = True, gen_tp: bool = False, tp_comm: Optional[str] = None):
+                 sync_interval: int = 8, use_graphs: bool = True, gen_tp: bool = False, tp_comm: Optional[str] = None,
+                 group_attention: bool = False):
         """``gen_tp``: generate tensor parallel over all ranks of ``dp`` (every rank decodes ALL rows of the global batch
         on 1/world of the weights and KV heads, ``models.tp_decode``) while the reference pass, the policy update and the
         optimizer stay data parallel; ``gen_slots`` is then the number of rows of the whole batch decoded at once."""
@@ -136,7 +137,8 @@ class GRPOTrainer(_Base):
             self.parallelism = f"generation tp{dp.world} ({self.gen_model.comm.backend}), reference + training dp{dp.world}"
         self.gen = Generator(self.gen_model, max_slots=gen_slots, max_seq_len=prompt_len + max_new, eos_id=eos_id,
                              sync_interval=sync_interval, use_graphs=use_graphs,
-                             kv_storage=arena[: arena_bytes // 2 * 2].view(torch.bfloat16))
+                             kv_storage=arena[: arena_bytes // 2 * 2].view(torch.bfloat16),
+                             group_attention=group_attention and samples_per_prompt > 1)
         self.last_counters: Dict[str, float] = {}
         self.last_reshard_us: Optional[float] = None
 

@@ -37,6 +37,10 @@ Program = List[Instr]
 #   ("add", loc, n)                atomic add (arrival counter)
 #   ("wait", loc, minimum)         blocks while the word is below `minimum` (an acquire spin; bounded on the device)
 #   ("expect", loc, value, what)   a read that must see exactly `value`; anything else is reported as a race
+#   ("pwait", loc, parity)         mbarrier.try_wait.parity: the word counts the barrier's completed phases; the wait
+#                                  passes while the CURRENT phase's parity differs from `parity`, i.e. it cannot tell a
+#                                  phase that completed from one that completed two phases ago
+#   ("check", loc, minimum, what)  an assertion: the word must have reached `minimum` (reported as a race otherwise)
 TORN = "torn"
 
 
@@ -94,6 +98,14 @@ def explore(name: str, programs: Sequence[Program], initial: Optional[Dict[Hasha
             if op == "wait":
                 if cur == TORN or not isinstance(cur, int) or cur < ins[2]:
                     continue
+            elif op == "pwait":
+                if (int(cur) & 1) == (int(ins[2]) & 1):
+                    continue
+            elif op == "check":
+                if not isinstance(cur, int) or cur < ins[2]:
+                    what = ins[3] if len(ins) > 3 else "assertion"
+                    return Result(name, len(parent), Finding("race", f"rank {r} {what}: {loc} should have reached {ins[2]}, is {cur!r}",
+                                                            trace_of(state, (r, ins))))
             elif op == "expect":
                 if cur != ins[2]:
                     what = ins[3] if len(ins) > 3 else "read"
@@ -278,6 +290,57 @@ def staleness_programs(tau: int, steps: int, *, slots: Optional[int] = None, n_g
 
 
 # ---------------------------------------------------------------------------------------------- the suite
+def flash_fwd_programs(n_tiles: int, rescale: Sequence[int] = (), *, pv_barriers: int = 2, in_order_consume: bool = False) -> List[Program]:
+    """The mbarrier pipeline of ``flash_attn_fwd_kernel`` (csrc/flash_attn.cu) for one CTA and ``n_tiles`` KV tiles, as
+    three agents: the MMA-issuing thread, the tensor pipe (completes the issued MMAs in issue order, each at an
+    arbitrary later time, and performs their commits) and one softmax warp. ``rescale``: the tiles at which the warp
+    rescales O and therefore waits for the previous P*V product. Words count completed phases of a barrier.
+
+    ``pv_barriers = 2``: P*V of tile j commits to ``pv_done[j & 1]`` and the warp waits on the wanted tile's barrier
+    with parity ``(j >> 1) & 1`` (the kernel as it is). ``pv_barriers = 1, in_order_consume = True``: one barrier that
+    completes every tile, consumed in order with the oldest outstanding completion waited for at the top of each
+    iteration. That version deadlocks: P*V of tile j-1 may complete before the warp tests for tile j-2, the parity
+    then names the running phase, and that phase cannot end without the warp's own next P."""
+    pv = (lambda j: ("pv_done", j & 1)) if pv_barriers == 2 else (lambda j: ("pv_done", 0))
+    pv_par = (lambda j: (j >> 1) & 1) if pv_barriers == 2 else (lambda j: j & 1)
+    mma: Program = [("add", "issued", 1)]                                    # QK_0
+    pipe: Program = [("wait", "issued", 1), ("add", ("s_full", 0), 1)]
+    n_issued = 1
+    for j in range(n_tiles):
+        if j + 1 < n_tiles:
+            mma.append(("add", "issued", 1))                                 # QK_{j+1} under the softmax of tile j
+            n_issued += 1
+            pipe += [("wait", "issued", n_issued), ("add", ("s_full", (j + 1) & 1), 1)]
+        mma += [("pwait", ("p_full", j & 1), (j >> 1) & 1), ("add", "issued", 1)]   # P_j delivered -> P*V_j
+        n_issued += 1
+        pipe += [("wait", "issued", n_issued), ("add", "pv_count", 1), ("add", pv(j), 1)]
+    warp: Program = []
+    seen = 0
+    for j in range(n_tiles):
+        warp.append(("pwait", ("s_full", j & 1), (j >> 1) & 1))
+        if in_order_consume:
+            while seen <= j - 2:
+                warp.append(("pwait", pv(seen), pv_par(seen)))
+                seen += 1
+        if j in rescale and j > 0:
+            if in_order_consume:
+                while seen <= j - 1:
+                    warp.append(("pwait", pv(seen), pv_par(seen)))
+                    seen += 1
+            else:
+                warp.append(("pwait", pv(j - 1), pv_par(j - 1)))
+            warp.append(("check", "pv_count", j, f"rescales O at tile {j} before P*V of tile {j - 1} has landed"))
+        warp.append(("add", ("p_full", j & 1), 1))
+    if in_order_consume:
+        while seen <= n_tiles - 1:
+            warp.append(("pwait", pv(seen), pv_par(seen)))
+            seen += 1
+    else:
+        warp.append(("pwait", pv(n_tiles - 1), pv_par(n_tiles - 1)))
+    warp.append(("check", "pv_count", n_tiles, "reads O before the last P*V has landed"))
+    return [mma, pipe, warp]
+
+
 def check_all(verbose: bool = False) -> List[Result]:
     """Every protocol as the host code runs it; all must come out clean."""
     out: List[Result] = []
@@ -296,6 +359,11 @@ def check_all(verbose: bool = False) -> List[Result]:
     out.append(explore("staleness 1, 2 generators + 1 trainer", progs, init))
     progs, init = staleness_programs(1, 4, n_gen=1, n_train=2)
     out.append(explore("staleness 1, 1 generator + 2 trainers", progs, init))
+    import itertools
+    for n in (1, 2, 3, 5, 6):
+        for k in range(0, min(n, 3)):
+            for resc in itertools.combinations(range(1, n), k):
+                out.append(explore(f"flash forward pipeline, {n} tiles, rescale at {list(resc)}", flash_fwd_programs(n, resc)))
     if verbose:
         for r in out:
             print(f"{'ok  ' if r.ok else 'FAIL'} {r.name}: {r.states} states" + ("" if r.ok else f" -- {r.finding}"))

@@ -165,3 +165,18 @@ def test_checked_mode_validators_name_the_offending_index():
     finally:
         C.set_enabled(prev)
     assert C.active() == prev
+
+
+def test_flash_forward_pipeline_needs_one_completion_barrier_per_buffer():
+    """The mbarrier pipeline of the flash attention forward kernel. With the P*V completion on ONE barrier that
+    completes every tile and is consumed in order, a softmax warp can be two phases behind: the parity it waits for
+    then names the running phase, which needs the warp's own next arrival (deadlock; on the GPU it ran into the
+    bounded wait). Waiting directly on the wanted tile's parity of that single barrier passes too early instead. With
+    one barrier per S/P buffer, as the kernel has it, every interleaving is clean for all rescale patterns."""
+    from rpeg_b200.parallel.protocol_check import explore, flash_fwd_programs
+    old = explore("in-order consumption of one barrier", flash_fwd_programs(5, (), pv_barriers=1, in_order_consume=True))
+    assert old.finding is not None and old.finding.kind == "deadlock"
+    early = explore("direct wait on one barrier", flash_fwd_programs(5, (3,), pv_barriers=1, in_order_consume=False))
+    assert early.finding is not None and early.finding.kind == "race" and "P*V" in early.finding.message
+    for n, resc in ((1, ()), (2, (1,)), (4, ()), (5, (1, 3)), (6, (2, 3, 5)), (7, (6,))):
+        assert explore(f"{n} tiles", flash_fwd_programs(n, resc)).ok, (n, resc)
