@@ -204,9 +204,9 @@ def main() -> None:
                          "batch on its weight shard) or data parallel (every rank decodes its rows on the whole model); auto = tp")
     ap.add_argument("--tp-comm", default=None, choices=["auto", "nvls", "peer"],
                     help="tensor-parallel decode collectives: NVLS multimem or plain peer loads/stores (default: RPEG_TP_COMM or auto)")
-    ap.add_argument("--group-attention", default="off", choices=["off", "on"],
-                    help="GRPO: score the K samples of a prompt against the prompt's shared KV pages once per group on the "
-                         "tensor cores instead of once per row")
+    ap.add_argument("--group-attention", default="off", choices=["off", "cuda", "tc"],
+                    help="GRPO: score the K samples of a prompt against the prompt's shared KV pages once per group (CUDA-core or "
+                         "tcgen05 kernel) instead of once per row through L2; off by default: measured slower on the full step")
     ap.add_argument("--budget-s", type=float, default=420.0,
                     help="wall-clock budget for warm-up plus timed steps; the timed step count is cut to fit and reported")
     args = ap.parse_args()
@@ -286,7 +286,7 @@ def main() -> None:
         else:
             trainer = GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp,
                                   gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2,
-                                  gen_tp=gen_tp, tp_comm=args.tp_comm, group_attention=args.group_attention == "on")
+                                  gen_tp=gen_tp, tp_comm=args.tp_comm, group_attention={"off": False, "cuda": True, "tc": "tc"}[args.group_attention])
         batches = []
         for _ in range(n_iters):
             prompts = torch.randint(3, cfg.vocab, (B, S), generator=gen_host, dtype=torch.int32)

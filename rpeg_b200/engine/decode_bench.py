@@ -31,6 +31,7 @@ def main(argv=None) -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--group-attention", action="store_true", help="with --share: score each group's queries against the shared "
                     "keys in one pass (the group kernel) instead of relying on L2 hits")
+    ap.add_argument("--group-tc", action="store_true", help="with --group-attention: the tcgen05 group kernel instead of the CUDA-core one")
     ap.add_argument("--share", default="", help="K:S - groups of K consecutive rows alias the KV pages of their first S tokens "
                     "(K samples of one prompt), to measure what the shared pages save")
     args = ap.parse_args(argv)
@@ -57,6 +58,7 @@ def main(argv=None) -> int:
             if k_share > gen.GROUP_MAX:
                 raise SystemExit(f"--group-attention handles groups of at most {gen.GROUP_MAX} rows")
             gen.group_attention = True
+            gen.group_tc = bool(args.group_tc)
             n_groups = n // k_share
             gen.group_rows.fill_(-1)
             gen.group_rows[:n_groups, :k_share] = torch.arange(n_groups * k_share, dtype=torch.int32, device=dev).view(n_groups, k_share)

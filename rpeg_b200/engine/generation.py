@@ -92,8 +92,10 @@ class Generator:
         self.n_kv = getattr(model, "n_kv_local", cfg.n_kv_heads)
         self.n_heads = getattr(model, "n_heads_local", cfg.n_heads)
         self.eos_id, self.pad_id = eos_id, pad_id
-        # rows that alias a prompt's KV pages are attended to as a group: the shared keys are read once per group
+        # rows that alias a prompt's KV pages are attended to as a group: the shared keys are read once per group.
+        # ``True`` / ``"cuda"``: the CUDA-core group kernel; ``"tc"``: the tcgen05 one (keys on the M axis).
         self.group_attention = bool(group_attention) and not cfg.qk_norm
+        self.group_tc = str(group_attention).lower() == "tc"
         self.sync_interval = max(1, sync_interval)
         self.use_graphs = use_graphs
         self.max_seq_len = max_seq_len
@@ -150,6 +152,7 @@ class Generator:
         # and costs a little once the kernels are long (+0.8 % at 128 rows and more)
         K.set_pdl(b <= self.PDL_MAX_BATCH)
         groups = (self.group_rows[:b], self.group_shared[:b], self.row_key0[:b]) if self.group_attention else None
+        K.set_group_tc(self.group_tc)
         xf = m.decode_step(self.token[:b], self.pos[:b], self.slot_ids[:b], self.seq_len[:b], self.page_table[:b],
                            self.kcache, self.vcache, nsplit=self._nsplit(b), groups=groups)
         logits = m.lm_logits(xf, decode=True)

@@ -486,9 +486,19 @@ def decode_scratch_numel(B: int, H: int, nsplit: int) -> int:
     return int(lib().rpeg_decode_attn_scratch_bytes(B, H, nsplit)) // 4
 
 
+_GROUP_TC = False
+
+
+def set_group_tc(on: bool) -> None:
+    """Which group kernel ``paged_decode_attn(groups=...)`` uses when the caller does not say: the tcgen05 one or the
+    CUDA-core one (the default)."""
+    global _GROUP_TC
+    _GROUP_TC = bool(on)
+
+
 def paged_decode_attn(q, q_col0, kcache, vcache, page_table, seq_lens, n_heads, n_kv_heads, head_dim, scale,
                       nsplit: int = 1, scratch: torch.Tensor | None = None, out: torch.Tensor | None = None, groups=None,
-                      group_tc: bool = True):
+                      group_tc: bool | None = None):
     """``groups = (group_rows [B, 8] int32, group_shared [B] int32, row_key0 [B] int32)``: rows that alias their first
     KV pages in groups (K samples of one prompt); the shared keys are then read once per group (``scratch`` must
     hold ``nsplit + 1`` partials per row and head). ``group_tc``: score the groups on the tensor cores (tcgen05, keys on
@@ -501,7 +511,7 @@ def paged_decode_attn(q, q_col0, kcache, vcache, page_table, seq_lens, n_heads, 
         group_rows, group_shared, row_key0 = groups
         if scratch is None:
             scratch = torch.empty(decode_scratch_numel(B, n_heads, nsplit + 1), dtype=torch.float32, device=q.device)
-        if group_tc:
+        if _GROUP_TC if group_tc is None else group_tc:
             check(lib().rpeg_paged_decode_attn_grouped_tc(q.data_ptr(), q.stride(0), q_col0, kcache.data_ptr(), vcache.data_ptr(),
                                                           kcache.shape[0], page_table.data_ptr(), page_table.stride(0),
                                                           seq_lens.data_ptr(), out.data_ptr(), scratch.data_ptr(), B, n_heads,
