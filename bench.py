@@ -278,7 +278,9 @@ def main() -> None:
         # the K samples of a prompt share its KV pages, so the pool holds every row of the rank at once
         gen_tp = world > 1 and args.gen_parallel in ("auto", "tp") and not spec.get("pipeline_train")
         slots = args.gen_slots or min((B if gen_tp else b_local) * Kk, 256)
-        kv_gb = args.kv_gb or {1: 56.0, 2: 76.0}.get(world, 96.0)
+        # tensor-parallel generation: a rank holds 1/world of the heads of every row, so the token capacity that one GPU
+        # gets from 56 GB needs 56 / world GB per rank (half as much again is kept as head room)
+        kv_gb = args.kv_gb or ((84.0 / world) if gen_tp else {1: 56.0, 2: 76.0}.get(world, 96.0))
         if spec.get("pipeline_train"):
             from rpeg_b200.engine.trainers import PipelineGRPOTrainer
             trainer = PipelineGRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo,
@@ -363,6 +365,30 @@ def main() -> None:
                 p, r = p.to(device), r.to(device)
             return trainer.step(p, r)
 
+    # Recomputation policy. "auto": keep a layer's activations for the backward pass (no second forward, a quarter
+    # fewer training FLOPs) when this rank has the memory for them, else recompute every layer from its input. The
+    # activations of one microbatch are micro_tokens x layers x (7 d + 3 d_ff) bf16 values plus the attention statistics.
+    if args.recompute == "auto":
+        policy = None
+        for name in ("actor", "policy"):
+            if hasattr(trainer, name):
+                policy = getattr(trainer, name)
+        if policy is not None and getattr(policy, "g", None) is not None:
+            act_bytes = 1.15 * args.micro_tokens * cfg.n_layers * (7 * cfg.d_model + 3 * cfg.d_ff) * 2
+            torch.cuda.synchronize()
+            free_bytes = float(torch.cuda.mem_get_info(device)[0])
+            fits = torch.tensor([1 if free_bytes > act_bytes + 12e9 else 0], device=device)
+            if world > 1:
+                dist.all_reduce(fits, op=dist.ReduceOp.MIN)
+            if int(fits.item()) == 1:
+                recompute = "none"
+                for name in ("actor", "policy", "critic"):
+                    m_ = getattr(trainer, name, None)
+                    if m_ is not None and getattr(m_, "g", None) is not None:
+                        m_.recompute = "none"
+            if rank == 0:
+                print(f"[bench] recompute={recompute}: {free_bytes / 1e9:.1f} GB free, activations of a microbatch {act_bytes / 1e9:.1f} GB",
+                      file=sys.stderr, flush=True)
     parallelism_text = getattr(trainer, "parallelism", None) or f"dp{world}"
 
     def extra_metrics(line: dict) -> dict:

@@ -7,11 +7,15 @@
 //   S = Q K^T   : A = Q tile, B = K tile, both K-major in shared memory (two 64-column 128B-swizzle
 //                 atoms each), accumulator S in TMEM (double buffered so S_{j+1} is computed while
 //                 the softmax of S_j runs);
-//   O += P V    : A = P read directly from TMEM (bf16, written over S by the softmax threads),
-//                 B = V tile in shared memory, MN-major (head dim contiguous).
+//   O += P V    : A = P read directly from TMEM (bf16, written by the softmax threads into two P buffers of their
+//                 own, TMEM columns 384..511), B = V tile in shared memory, MN-major (head dim contiguous).
 // Softmax maps one thread to one query row (TMEM lane), so row max / row sum need no shuffles.
 // The running max is only refreshed when it grows by more than 8 (in log2 units); a stale max is
 // exact after the final division by l, and it makes the O rescale (TMEM load, scale, store) rare.
+// That also makes the softmax ONE pass over S per tile: after the first tile the exponentials are taken against
+// the current reference maximum while the same pass tracks the tile's true maximum; only when that maximum turns
+// out more than 8 above the reference is O rescaled and the tile's P recomputed (S is still intact, because P has
+// its own columns). TMEM loads run one chunk ahead of the arithmetic.
 //
 // Q/K/V are column blocks of one packed [T, ld] bf16 activation (the fused QKV projection output);
 // cu_seqlens[b] is the first row of sequence b. Outputs: O [T, H*128] bf16, LSE [H, T] fp32.
@@ -32,6 +36,66 @@ constexpr int FA_TILE_BYTES = 128 * 128 * 2;  // 32 KiB: one [128 x 128] bf16 ti
 constexpr int FA_KV_STAGES = 2;
 constexpr int FA_SMEM = FA_TILE_BYTES * (1 + 2 * FA_KV_STAGES) + 1024 + 256;
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;
+
+// One softmax row pass over a 128-key tile held in TMEM (thread = query row). The four 32-column chunks are loaded
+// one ahead of their use, so the TMEM load latency of chunk c+1 is covered by the arithmetic on chunk c.
+//   row_max_pass : largest unscaled score of the row (masked keys excluded).
+//   row_exp_pass : P = exp2(s * scale - m_ref) as packed bf16 into the P buffer, the row's sum of P added to `lsum`,
+//                  and the largest unscaled score seen, so that one pass serves both the exponentials and the check
+//                  whether m_ref was still a valid reference maximum.
+template <bool MASK>
+__device__ __forceinline__ float row_max_pass(uint32_t ts, int k0, int qi, int L) {
+  uint32_t a[32], b[32];
+  float tmax = -INFINITY;
+  tmem_ld_32x32(ts, a);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    tmem_wait_ld();
+    uint32_t(&cur)[32] = (c & 1) ? b : a;
+    if (c + 1 < 4) tmem_ld_32x32(ts + (c + 1) * 32, (c & 1) ? a : b);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int kj = k0 + c * 32 + i;
+      if (!MASK || (kj <= qi && kj < L)) tmax = fmaxf(tmax, __uint_as_float(cur[i]));
+    }
+  }
+  return tmax;
+}
+
+template <bool MASK>
+__device__ __forceinline__ void row_exp_pass(uint32_t ts, uint32_t tp, float scale_log2, float m_ref, int k0, int qi, int L,
+                                             bool row_valid, float& lsum, float& smax) {
+  uint32_t a[32], b[32];
+  tmem_ld_32x32(ts, a);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    tmem_wait_ld();
+    uint32_t(&cur)[32] = (c & 1) ? b : a;
+    if (c + 1 < 4) tmem_ld_32x32(ts + (c + 1) * 32, (c & 1) ? a : b);
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int kj = k0 + c * 32 + 2 * i;
+      const float s0 = __uint_as_float(cur[2 * i]), s1 = __uint_as_float(cur[2 * i + 1]);
+      float p0, p1;
+      if (MASK) {
+        const bool v0 = row_valid && kj <= qi && kj < L;
+        const bool v1 = row_valid && kj + 1 <= qi && kj + 1 < L;
+        if (v0) smax = fmaxf(smax, s0);
+        if (v1) smax = fmaxf(smax, s1);
+        p0 = v0 ? exp2f(fmaf(s0, scale_log2, -m_ref)) : 0.f;
+        p1 = v1 ? exp2f(fmaf(s1, scale_log2, -m_ref)) : 0.f;
+      } else {
+        smax = fmaxf(smax, fmaxf(s0, s1));
+        p0 = exp2f(fmaf(s0, scale_log2, -m_ref));
+        p1 = exp2f(fmaf(s1, scale_log2, -m_ref));
+      }
+      lsum += p0 + p1;
+      pk[i] = pack_bf16x2(p0, p1);
+    }
+    tmem_st_32x16(tp + c * 16, pk);
+  }
+}
 
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const int* __restrict__ cu_seqlens,
@@ -145,7 +209,7 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const int* _
           if (!mbar_wait(&v_full[st], ph, abort_flag, status, 514)) break;
           tc_fence_after_sync();
           const uint32_t v_addr = smem_u32(v_sm + st * FA_TILE_BYTES);
-          const uint32_t tp = tmem_base + static_cast<uint32_t>((j & 1) * 128);
+          const uint32_t tp = tmem_base + 384u + static_cast<uint32_t>((j & 1) * 64);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             // 16 keys per step: 8 packed TMEM columns of P, 16 rows (2 KiB) of the V tile.
@@ -179,67 +243,45 @@ flash_attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const int* _
     };
     for (int j = 0; j < n_tiles && ok; ++j) {
       const uint32_t ts = tmem_base + lane_base + static_cast<uint32_t>((j & 1) * 128);
+      const uint32_t tp = tmem_base + lane_base + 384u + static_cast<uint32_t>((j & 1) * 64);
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, status, 520))) { ok = false; break; }
       tc_fence_after_sync();
       const int k0 = j * FA_BN;
       const bool need_mask = (k0 + FA_BN - 1 > q0) || (k0 + FA_BN > L);
-      // pass 1: row max
-      float tmax = -INFINITY;
+      if (j == 0) {                       // no reference maximum yet: one extra pass finds it
+        float t0 = need_mask ? row_max_pass<true>(ts, k0, qi, L) : row_max_pass<false>(ts, k0, qi, L);
+        t0 *= scale_log2;                 // scale > 0, so max commutes with the scaling
+        m_ref = (!row_valid || t0 == -INFINITY) ? 0.f : t0;
+      }
+      float lsum = 0.f, smax = -INFINITY;
+      if (need_mask) row_exp_pass<true>(ts, tp, scale_log2, m_ref, k0, qi, L, row_valid, lsum, smax);
+      else row_exp_pass<false>(ts, tp, scale_log2, m_ref, k0, qi, L, row_valid, lsum, smax);
+      if (j > 0) {
+        float tmax = smax * scale_log2;
+        if (!row_valid || smax == -INFINITY) tmax = m_ref;
+        const bool need = tmax > m_ref + FA_RESCALE_THRESHOLD;
+        if (__any_sync(0xffffffffu, need)) {
+          if (!wait_pv(j - 1, 521)) { ok = false; break; }
+          tc_fence_after_sync();
+          const float alpha = need ? exp2f(m_ref - tmax) : 1.f;
+          if (need) { m_ref = tmax; l *= alpha; }
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(ts + c * 32, v);
-        tmem_wait_ld();
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_o + lane_base + c * 32, v);
+            tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kj = k0 + c * 32 + i;
-          const bool valid = !need_mask || (kj <= qi && kj < L);
-          if (valid) tmax = fmaxf(tmax, __uint_as_float(v[i]));
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(tmem_o + lane_base + c * 32, v);
+          }
+          // P of this tile again, against the new maximum (rows that kept theirs recompute the same values)
+          lsum = 0.f;
+          float unused = -INFINITY;
+          if (need_mask) row_exp_pass<true>(ts, tp, scale_log2, m_ref, k0, qi, L, row_valid, lsum, unused);
+          else row_exp_pass<false>(ts, tp, scale_log2, m_ref, k0, qi, L, row_valid, lsum, unused);
         }
       }
-      tmax *= scale_log2;  // scale > 0, so max commutes with the scaling
-      if (!row_valid || tmax == -INFINITY) tmax = (m_ref == -INFINITY) ? 0.f : m_ref;
-      bool need = false;
-      if (j == 0) {
-        m_ref = tmax;
-      } else {
-        need = tmax > m_ref + FA_RESCALE_THRESHOLD;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, need)) {
-        if (!wait_pv(j - 1, 521)) { ok = false; break; }
-        tc_fence_after_sync();
-        const float alpha = need ? exp2f(m_ref - tmax) : 1.f;
-        if (need) { m_ref = tmax; l *= alpha; }
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_o + lane_base + c * 32, v);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32(tmem_o + lane_base + c * 32, v);
-        }
-        tmem_wait_st();
-      }
-      // pass 2: P = exp2(s*scale - m_ref), packed bf16 written over the S buffer
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(ts + c * 32, v);
-        tmem_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int kj = k0 + c * 32 + 2 * i;
-          const bool v0 = row_valid && (!need_mask || (kj <= qi && kj < L));
-          const bool v1 = row_valid && (!need_mask || (kj + 1 <= qi && kj + 1 < L));
-          const float p0 = v0 ? exp2f(__uint_as_float(v[2 * i]) * scale_log2 - m_ref) : 0.f;
-          const float p1 = v1 ? exp2f(__uint_as_float(v[2 * i + 1]) * scale_log2 - m_ref) : 0.f;
-          l += p0 + p1;
-          pk[i] = pack_bf16x2(p0, p1);
-        }
-        tmem_st_32x16(ts + c * 16, pk);
-      }
+      l += lsum;
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
