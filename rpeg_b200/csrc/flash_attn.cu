@@ -371,11 +371,22 @@ namespace rpeg {
 //   dK  += dS^T Q         (A = dS^T TMEM, B = Q smem read MN-major)     -> TMEM cols 384..511
 //   dQ_i = dS K           (A = dS^T smem read MN-major, B = K smem read MN-major)
 //                                                                       -> TMEM cols 0..127 (S^T is dead)
-// dQ_i is drained by the same threads (now lane = query row) with fp32 vector atomics into a
-// [T, H*128] fp32 accumulator; dK (scaled) and dV are written once at the end as bf16 into the
-// K and V column blocks of a packed gradient buffer with the same layout as qkv.
+// dQ_i is drained by the same threads (now lane = query row) into a [T, H*128] fp32 accumulator: every thread
+// stages its row in shared memory, 64 columns at a time, and adds it to global memory with ONE bulk reduction
+// (cp.reduce.async.bulk ... add.f32) per row and half, instead of 32 vector atomics per row (the atomics of all
+// CTAs together saturated the L2's atomic rate and set the kernel's time). dK (scaled) and dV are written once
+// at the end as bf16 into the K and V column blocks of a packed gradient buffer with the same layout as qkv.
 // D_q = rowsum(dO * O) comes from a small pre-pass. Grouped-query attention (H a multiple of Hkv) is supported.
-constexpr int FB_SMEM = FA_TILE_BYTES * 5 + 1024 + 1024 + 256;
+constexpr int FB_STAGE_ROW = 64 + 4;                       // floats per staged dQ row: 64 values + 16 bytes of padding
+constexpr int FB_STAGE_BYTES = 128 * FB_STAGE_ROW * 4;     // (rows 272 bytes apart: conflict-free float4 stores)
+constexpr int FB_SMEM = FA_TILE_BYTES * 5 + FB_STAGE_BYTES + 1024 + 1024 + 256;
+
+// global[0 .. bytes) += shared[0 .. bytes) as fp32, one bulk operation in the current bulk group
+__device__ __forceinline__ void bulk_reduce_add_f32(float* gdst, const float* ssrc, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(ssrc)),
+               "r"(bytes)
+               : "memory");
+}
 
 __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
                                      float* __restrict__ dvec, int T, int H) {
@@ -418,7 +429,8 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid
   uint8_t* q_sm = v_sm + FA_TILE_BYTES;
   uint8_t* do_sm = q_sm + FA_TILE_BYTES;
   uint8_t* ds_sm = do_sm + FA_TILE_BYTES;
-  float* lse_sm = reinterpret_cast<float*>(ds_sm + FA_TILE_BYTES);  // [128]
+  float* dq_stage = reinterpret_cast<float*>(ds_sm + FA_TILE_BYTES);  // [128][FB_STAGE_ROW]
+  float* lse_sm = dq_stage + 128 * FB_STAGE_ROW;                      // [128]
   float* d_sm = lse_sm + 128;                                       // [128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(d_sm + 128);
   uint64_t* kv_full = bars;         // K and V landed
@@ -576,25 +588,30 @@ flash_attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid
       tc_fence_after_sync();
       const int qi = q0 + r;
       float* dq_row = dq_acc + (static_cast<size_t>(seq0 + qi) * H + h) * FA_HD;
+      float* my_stage = dq_stage + r * FB_STAGE_ROW;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + lane_base + c * 32, v);
-        tmem_wait_ld();
-        if (qi < L) {
+      for (int half = 0; half < 2; ++half) {
+        tma_store_wait_read<0>();                 // this thread's earlier bulk reads of its staging row are done
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_s + lane_base + (half * 2 + c) * 32, v);
+          tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 val = make_float4(__uint_as_float(v[4 * i]) * scale, __uint_as_float(v[4 * i + 1]) * scale,
-                                           __uint_as_float(v[4 * i + 2]) * scale, __uint_as_float(v[4 * i + 3]) * scale);
-            atomicAdd(reinterpret_cast<float4*>(dq_row + c * 32 + 4 * i), val);
-          }
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(my_stage + c * 32 + 4 * i) =
+                make_float4(__uint_as_float(v[4 * i]) * scale, __uint_as_float(v[4 * i + 1]) * scale,
+                            __uint_as_float(v[4 * i + 2]) * scale, __uint_as_float(v[4 * i + 3]) * scale);
         }
-        __syncwarp();
+        fence_proxy_async_smem();                 // the row was written with ordinary stores, the bulk engine reads it
+        if (qi < L) bulk_reduce_add_f32(dq_row + half * 64, my_stage, 64 * sizeof(float));
+        tma_store_commit();
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_drained);
     }
+    tma_store_wait<0>();          // every bulk reduction of this thread has been performed
     if (ok) {
       // dq_done of the last iteration also covers the last dV / dK accumulation
       tc_fence_after_sync();

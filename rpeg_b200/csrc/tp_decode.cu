@@ -95,6 +95,11 @@ tp_allreduce_rmsnorm_kernel(TpComm c, long long part_off, const __nv_bfloat16* _
                             const __nv_bfloat16* __restrict__ w, long long y_off, long long h_off, int B, int d, float eps,
                             long long flag_off, unsigned* __restrict__ state, unsigned long long timeout_ns, int* status) {
   __shared__ float warp_ss[8];
+  // Launched as a programmatic dependent: the next kernel of the step (a GEMM) may become resident now and fetch its
+  // first weight tiles while this kernel talks to the peers; this kernel itself waits for its producer (the GEMM that
+  // wrote the partial sums) before it reads or signals anything.
+  griddep_launch();
+  griddep_wait();
   if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;   // an earlier wait ran out: stand down
   const unsigned epoch = state[0] + 1u;
   const int rows_per = (B + c.world - 1) / c.world;
@@ -220,6 +225,8 @@ template <bool MC>
 __global__ void __launch_bounds__(256)
 tp_allgather_cols_kernel(TpComm c, long long buf_off, int B, int n_loc, int ld, long long flag_off,
                          unsigned* __restrict__ state, unsigned long long timeout_ns, int* status) {
+  griddep_launch();
+  griddep_wait();
   if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;   // an earlier wait ran out: stand down
   const unsigned epoch = state[0] + 1u;
   const int vec_per_row = n_loc >> 3;
@@ -283,11 +290,11 @@ extern "C" int rpeg_tp_allreduce_rmsnorm(void* const* peers, void* mc, int rank,
 #define RPEG_TP_AR(NV_)                                                                                                   \
   do {                                                                                                                    \
     if (mc != nullptr)                                                                                                    \
-      tp_allreduce_rmsnorm_kernel<NV_, true><<<rows_per, 256, 0, stream>>>(c, part_off, rp, wp, y_off, h_off, B, d, eps,   \
-                                                                           flag_off, state, timeout_ns, status);           \
+      launch_pdl(tp_allreduce_rmsnorm_kernel<NV_, true>, dim3(rows_per), dim3(256), 0, stream, c, part_off, rp, wp, y_off, \
+                 h_off, B, d, eps, flag_off, state, timeout_ns, status);                                                   \
     else                                                                                                                  \
-      tp_allreduce_rmsnorm_kernel<NV_, false><<<rows_per, 256, 0, stream>>>(c, part_off, rp, wp, y_off, h_off, B, d, eps,  \
-                                                                            flag_off, state, timeout_ns, status);          \
+      launch_pdl(tp_allreduce_rmsnorm_kernel<NV_, false>, dim3(rows_per), dim3(256), 0, stream, c, part_off, rp, wp, y_off, \
+                 h_off, B, d, eps, flag_off, state, timeout_ns, status);                                                   \
   } while (0)
   if (nv == 1) RPEG_TP_AR(1);
   else if (nv == 2) RPEG_TP_AR(2);
@@ -308,8 +315,10 @@ extern "C" int rpeg_tp_allgather_cols(void* const* peers, void* mc, int rank, in
   const long long total = static_cast<long long>(B) * (n_loc >> 3);
   const int grid = static_cast<int>(total / 256 < 1 ? 1 : (total / 256 > 148 ? 148 : total / 256));
   if (mc != nullptr)
-    tp_allgather_cols_kernel<true><<<grid, 256, 0, stream>>>(c, buf_off, B, n_loc, ld, flag_off, state, timeout_ns, status);
+    launch_pdl(tp_allgather_cols_kernel<true>, dim3(grid), dim3(256), 0, stream, c, buf_off, B, n_loc, ld, flag_off, state,
+               timeout_ns, status);
   else
-    tp_allgather_cols_kernel<false><<<grid, 256, 0, stream>>>(c, buf_off, B, n_loc, ld, flag_off, state, timeout_ns, status);
+    launch_pdl(tp_allgather_cols_kernel<false>, dim3(grid), dim3(256), 0, stream, c, buf_off, B, n_loc, ld, flag_off, state,
+               timeout_ns, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

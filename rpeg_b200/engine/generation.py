@@ -150,7 +150,8 @@ class Generator:
         m = self.model
         # chaining the step's kernels as programmatic dependents hides launch gaps at small batches (-3.7 % at 8 rows)
         # and costs a little once the kernels are long (+0.8 % at 128 rows and more)
-        K.set_pdl(b <= self.PDL_MAX_BATCH)
+        # (a tensor-parallel step is made of short kernels at every batch size: always chained)
+        K.set_pdl(b <= self.PDL_MAX_BATCH or getattr(m, "tp", 1) > 1)
         groups = (self.group_rows[:b], self.group_shared[:b], self.row_key0[:b]) if self.group_attention else None
         K.set_group_tc(self.group_tc)
         xf = m.decode_step(self.token[:b], self.pos[:b], self.slot_ids[:b], self.seq_len[:b], self.page_table[:b],
