@@ -23,6 +23,12 @@
 #include "common.cuh"
 #include "rpeg_kernels.h"
 
+#ifdef RPEG_DEV_PROBES
+#define RPEG_PROBE(bit) ((probe & (bit)) != 0)
+#else
+#define RPEG_PROBE(bit) false
+#endif
+
 namespace rpeg {
 
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
@@ -66,7 +72,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = M / BM;                      // host guarantees M % (BM * world) == 0
   const int n_tiles = (N + BN - 1) / BN;
-  const int num_tiles = (probe & 4) ? 0 : m_tiles * n_tiles;
+  const int num_tiles = RPEG_PROBE(4) ? 0 : m_tiles * n_tiles;
   const int num_kb = (K + BK - 1) / BK;
   const int blocks_per_rank = m_tiles / world;
 
@@ -213,7 +219,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int chunk_vecs = CHUNK_ROWS * vec_per_row;
     const int per_peer = blocks_per_rank * CHUNKS_PER_BLOCK;
     const int push_chunks = (world - 1) * per_peer;
-    for (int g = blockIdx.x; g < push_chunks && !(probe & 1); g += gridDim.x) {
+    for (int g = blockIdx.x; g < push_chunks && !RPEG_PROBE(1); g += gridDim.x) {
       const int step = g / per_peer, rest = g - step * per_peer;
       const int dst_rank = (rank - 1 - step + 2 * world) % world;
       const int blk = rank * blocks_per_rank + rest / CHUNKS_PER_BLOCK;
@@ -228,7 +234,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (i < chunk_vecs)
             v[u] = *reinterpret_cast<const uint4*>(x_local + static_cast<size_t>(row0 + i / vec_per_row) * ldx + (i % vec_per_row) * 8);
         }
-        if (probe & 2) continue;
+        if (RPEG_PROBE(2)) continue;
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const int i = i0 + u * COPY_THREADS;
@@ -262,10 +268,14 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 using namespace rpeg;
 
+// Timing probes exist only in builds with -DRPEG_DEV_PROBES (bit 0 skips the pulls, bit 1 drops the local stores, bit 2
+// skips the GEMM tiles; results are wrong with any bit set).
+#ifdef RPEG_DEV_PROBES
 static int g_ag_probe = 0;
-// Timing aid for development: bit 0 skips the pulls, bit 1 drops the local stores, bit 2 skips the GEMM tiles.
-// Results are wrong with any bit set.
 extern "C" void rpeg_ag_gemm_set_probe(int bits) { g_ag_probe = bits; }
+#else
+static constexpr int g_ag_probe = 0;
+#endif
 
 // xs[q]: rank q's X buffer ([M, ldx] bf16, symmetric); on entry rank q's own rows are valid in xs[q]. W [N, ldw]
 // bf16 local; Y [M, ldy] bf16 local. readys[q]: rank q's arrival counters uint32[M / 128] (symmetric, zeroed once);

@@ -40,7 +40,11 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
 };
 
-enum { EPI_BF16 = 0, EPI_F32 = 1 };
+// EPI_SWIGLU: B is a gated-MLP weight [2f, K] (gate rows, then up rows). Output tile tn covers the activation columns
+// [128 tn, 128 tn + 128): its B tile is 128 gate rows stacked on the 128 up rows of the same columns, the accumulator
+// holds gate in columns 0..127 and up in 128..255, and the epilogue stores silu(gate) * up as bf16, so the
+// [M, 2f] pre-activation never goes to memory (N is f here, BN must be 256).
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 
 // Optional gate in front of the first operand load: `n` version words (written by the GPUs that push new weights
 // into B's buffer, system-scope release) must all have reached `min_version` before any tile of this GEMM is
@@ -71,8 +75,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  constexpr int TN = (EPI == EPI_SWIGLU) ? BN / 2 : BN;   // output columns per tile
   const int m_tiles = (M + BM - 1) / BM;
-  const int n_tiles = (N + BN - 1) / BN;
+  const int n_tiles = (N + TN - 1) / TN;
   const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + BK - 1) / BK;
   // Split-K: work item w = tile * k_splits + split; a split covers kb_per consecutive K blocks and
@@ -156,7 +161,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const int pre = min(STAGES, kb1 - kb0);
             for (int i = 0; i < pre; ++i) {            // weights first: they do not depend on the previous kernel
               mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
-              tma_load_2d(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmap_b, &full_bar[i], (kb0 + i) * BK, tn * BN);
+              tma_load_2d(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmap_b, &full_bar[i], (kb0 + i) * BK, tn * BN);  // never EPI_SWIGLU
             }
             griddep_wait();
             for (int i = 0; i < pre; ++i)
@@ -173,7 +178,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
         int tm, tn;
         tile_coords(w / k_splits, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
+        const int m0 = tm * BM, n0 = tn * TN;
         const int kb0 = (w % k_splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         const int kb_first = kb0 + skip;
         skip = 0;
@@ -189,7 +194,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             for (int c = 0; c < BM / 64; ++c)
               tma_load_2d(sa + c * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + c * 64, kb * BK);
           }
-          if constexpr (!B_MN) {
+          if constexpr (EPI == EPI_SWIGLU) {
+            // gate rows n0.. and up rows N + n0.. (N = f): two boxes of BN / 2 rows, stacked in the B tile
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n0);
+            tma_load_2d(sb + (BN / 2) * BK * 2, &tmap_b, &full_bar[stage], kb * BK, N + n0);
+          } else if constexpr (!B_MN) {
             tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n0);
           } else {
 #pragma unroll
@@ -245,10 +254,37 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tile_coords(w / k_splits, tm, tn);
       const long long split_off = static_cast<long long>(w % k_splits) * split_stride;
       const int row = tm * BM + quad * 32 + lane;
-      const int n0 = tn * BN;
+      const int n0 = tn * TN;
       if (!__all_sync(0xffffffffu, mbar_wait(&tfull_bar[buf], acc_phase, abort_flag, status, 300))) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(buf * BN);
+      if constexpr (EPI == EPI_SWIGLU) {
+#pragma unroll 1
+        for (int c = 0; c < TN / 32; ++c) {
+          uint32_t gv[32], uv[32];
+          tmem_ld_32x32(taddr + c * 32, gv);
+          tmem_ld_32x32(taddr + TN + c * 32, uv);
+          tmem_wait_ld();
+          const int col0 = n0 + c * 32;
+          if (row < M && col0 < N) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col0 + v * 8 < N) {
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float g0 = __uint_as_float(gv[v * 8 + 2 * e]), g1 = __uint_as_float(gv[v * 8 + 2 * e + 1]);
+                  const float a0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(uv[v * 8 + 2 * e]);
+                  const float a1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(uv[v * 8 + 2 * e + 1]);
+                  o[e] = pack_bf16x2(a0, a1);
+                }
+                *reinterpret_cast<uint4*>(crow + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -509,6 +545,38 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
   return rc;
 }
 
+
+// act[M, f] = silu(A W_gate^T) * (A W_up^T) with W = [W_gate; W_up] stored [2f, K] (the gated MLP's first linear with
+// its activation in the GEMM epilogue). f must be a multiple of 128; A [M, K] and W rows K-contiguous.
+extern "C" int rpeg_gemm_swiglu(const void* A, const void* W, void* C, int M, int f, int K, int lda, int ldw, int ldc,
+                                int* status, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (M <= 0 || f <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(C)) & 15) return -1;
+  if ((lda | ldw | ldc) & 7) return -2;
+  if (f % 128) return -3;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_2d(&tb, W, K, 2ull * f, ldw, BK, 128);
+  if (rc) return rc - 100;
+  using Cfg = GemmCfg<256>;
+  auto kern = gemm_bf16_tcgen05_kernel<256, EPI_SWIGLU, false, false>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) return -20;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * (f / 128);
+  const int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, f, K, ldc, 0, 1, 0, status, WeightGate{nullptr, 0, 0u, 0ull}, 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
 
 // Skinny GEMM that leaves its split-K partials for the consumer: C_s[M,N] (fp32, s = 0..splits-1, `M*N`
 // apart in `workspace`) with sum_s C_s = A[M,K] * B[N,K]^T. The split count is chosen by the same cost

@@ -25,6 +25,12 @@
 #include "common.cuh"
 #include "rpeg_kernels.h"
 
+#ifdef RPEG_DEV_PROBES
+#define RPEG_PROBE(bit) ((probe & (bit)) != 0)
+#else
+#define RPEG_PROBE(bit) false
+#endif
+
 namespace rpeg {
 
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
@@ -201,7 +207,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       // this warp's 32 rows of the tile are stored: publish them to the owner (4 arrivals per tile, one
       // per epilogue warp, so no cross-warp barrier is needed on this path)
-      if (!(probe & 1)) __threadfence_system();
+      if (!RPEG_PROBE(1)) __threadfence_system();
       __syncwarp();
       if (lane == 0) {
         unsigned* ctr = static_cast<unsigned*>(counters.p[owner]) + (tm - owner * blocks_per_rank);
@@ -221,7 +227,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   if (*abort_flag) {
     __nanosleep(200000);
-  } else if (!(probe & 2)) {
+  } else if (!RPEG_PROBE(2)) {
     constexpr int SLOT_BYTES = 8192;
     constexpr int MAX_GROUPS = 24;
     constexpr int SUB_ROWS = 16;
@@ -340,10 +346,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 using namespace rpeg;
 
-// Timing probe for development (0 in normal use): bit 0 drops the system fence before the arrival counter, bit 1 skips the
-// owner's reduction. Results are wrong with either bit set.
+// Timing probes exist only in builds with -DRPEG_DEV_PROBES (bit 0 drops the system fence before the arrival counter,
+// bit 1 skips the owner's reduction; results are wrong with either bit set). The product build has neither the
+// switch nor the branches.
+#ifdef RPEG_DEV_PROBES
 static int g_probe = 0;
 extern "C" void rpeg_gemm_rs_set_probe(int bits) { g_probe = bits; }
+#else
+static constexpr int g_probe = 0;
+#endif
 
 // A [M, K] (lda), B [N, K] (ldb), both K-major bf16 in this rank's memory. stage[q]: rank q's staging
 // buffer of world * (M / world) * N bf16; counters[q]: rank q's M / world / 128 arrival counters

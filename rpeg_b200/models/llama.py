@@ -268,8 +268,12 @@ class LlamaModel:
                                      cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
         o = K.gemm(attn, p[f"l{i}.wo"])
         x2, rstd2, h1 = K.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], cfg.rms_eps, residual=h, want_sum=True)
-        gu = K.gemm(x2, p[f"l{i}.w_gate_up"])
-        act = K.swiglu_fwd(gu)
+        if (keep and self.recompute == "none") or cfg.d_ff % 128:
+            gu = K.gemm(x2, p[f"l{i}.w_gate_up"])          # the backward pass wants the pre-activation
+            act = K.swiglu_fwd(gu)
+        else:
+            gu = None
+            act = K.gemm_swiglu(x2, p[f"l{i}.w_gate_up"])  # activation in the GEMM epilogue: [T, 2f] never exists
         dn = K.gemm(act, p[f"l{i}.w_down"])
         if keep:
             saved = None

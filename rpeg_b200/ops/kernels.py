@@ -106,6 +106,27 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     return out
 
 
+def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(x @ W_gate.T) * (x @ W_up.T)`` with ``w_gate_up = [W_gate; W_up]`` of shape ``[2f, K]``: the gated MLP's first
+    linear with the activation applied to the fp32 accumulators in the GEMM epilogue, so the ``[M, 2f]`` pre-activation is
+    never written. ``f`` must be a multiple of 128 (callers fall back to ``gemm`` + ``swiglu_fwd`` otherwise)."""
+    _req(x, torch.bfloat16, "x")
+    _req(w_gate_up, torch.bfloat16, "w_gate_up")
+    M, Kd = x.shape
+    f = w_gate_up.shape[0] // 2
+    if w_gate_up.shape[1] != Kd or x.stride(1) != 1 or w_gate_up.stride(1) != 1:
+        raise ValueError("gemm_swiglu: x [M, K] and w_gate_up [2f, K] must share K and be contiguous in it")
+    if f % 128:
+        raise ValueError("gemm_swiglu needs d_ff to be a multiple of 128")
+    if out is None:
+        out = torch.empty((M, f), dtype=torch.bfloat16, device=x.device)
+    if M == 0:
+        return out
+    check(lib().rpeg_gemm_swiglu(x.data_ptr(), w_gate_up.data_ptr(), out.data_ptr(), M, f, Kd, x.stride(0), w_gate_up.stride(0),
+                                 out.stride(0), status_word(x.device).data_ptr(), _stream()), "rpeg_gemm_swiglu")
+    return out
+
+
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launches for the kernels launched from now on (a captured graph keeps its setting)."""
     lib().rpeg_set_pdl(int(bool(on)))

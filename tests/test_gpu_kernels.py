@@ -323,6 +323,21 @@ def test_kv_append_and_paged_decode(cuda_device, nsplit, H, Hkv):
         off += l
 
 
+@pytest.mark.parametrize("M,f,Kd", [(300, 512, 256), (128, 1408, 192), (1000, 11008, 128), (5, 128, 64)])
+def test_gemm_with_swiglu_epilogue(cuda_device, M, f, Kd):
+    """The gated MLP's first linear with silu(gate) * up applied in the GEMM epilogue, against fp32 PyTorch."""
+    g = torch.Generator(device="cpu").manual_seed(2)
+    x = torch.randn(M, Kd, generator=g).bfloat16().to(cuda_device)
+    w = (torch.randn(2 * f, Kd, generator=g) / math.sqrt(Kd)).bfloat16().to(cuda_device)
+    out = K.gemm_swiglu(x, w)
+    K.check_status()
+    gate, up = x.float() @ w[:f].float().t(), x.float() @ w[f:].float().t()
+    ref = torch.nn.functional.silu(gate) * up
+    assert _rel_err(out, ref) < 1e-2
+    two_step = K.swiglu_fwd(K.gemm(x, w))
+    assert _rel_err(out, two_step.float()) < 2e-2
+
+
 @pytest.mark.parametrize("tc", [True, False])
 @pytest.mark.parametrize("H,Hkv,shared_pages", [(4, 4, 3), (8, 2, 8), (4, 4, 1)])
 def test_paged_decode_attn_with_shared_prompt_groups(cuda_device, tc, H, Hkv, shared_pages):
