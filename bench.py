@@ -420,9 +420,9 @@ def main() -> None:
               "error": f"{where}: {type(exc).__name__}: {exc}"})
         sys.stderr.flush()
         if world > 1:
-            # The peers find out through their own bounded waits (2 s). Leave only after they had time to stop
+            # The peers find out through their own bounded waits (5 s). Leave only after they had time to stop
             # launching kernels that address this rank's memory.
-            time.sleep(6.0)
+            time.sleep(9.0)
         os._exit(1)
 
     def checked_run(i: int, tag: str):

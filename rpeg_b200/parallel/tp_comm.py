@@ -24,7 +24,7 @@ import torch.distributed as dist
 from ..ops import kernels as K
 from ..ops._lib import check, lib
 
-WAIT_NS = 2_000_000_000
+WAIT_NS = 5_000_000_000      # ranks replay the same step, but their hosts may be apart by a graph capture or a collection pause
 _FLAG_BYTES = 2 * K.MAX_PEERS * 4
 
 
