@@ -193,7 +193,7 @@ def make_critic_head(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, denom: flo
 
 
 def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_tokens: Optional[float] = None,
-                      value_model_shared: bool = False, pipeline=None) -> Dict[str, torch.Tensor]:
+                      value_model_shared: bool = False, pipeline=None, on_last_backward=None) -> Dict[str, torch.Tensor]:
     """Forward + backward of the clipped policy objective over the whole rollout (gradients are
     accumulated over microbatches; the caller runs the optimizer). ``denom_tokens`` is the GLOBAL
     response-token count when the batch is sharded over data-parallel ranks. With
@@ -207,9 +207,17 @@ def policy_train_step(model: LlamaModel, ro: Rollout, cfg: AlgoConfig, *, denom_
         pipeline.broadcast_from_last(acc)
         pipeline.broadcast_from_last(vacc)
     else:
-        for mb in _micro(ro, cfg):
+        mbs = list(_micro(ro, cfg))
+        for idx, mb in enumerate(mbs):
             xf, ctx = model.forward(mb.tokens, mb.pos, mb.cu_seqlens, mb.max_seqlen, keep=True)
-            model.backward(ctx, head(mb, xf))
+            d_xf = head(mb, xf)
+            # ``on_last_backward(layer)``: the gradients of the layers from ``layer`` up are final once the last
+            # microbatch's backward has passed it (``parallel.dp.DPContext.overlap_hook`` reduces them right away)
+            model.grad_hook = on_last_backward if idx + 1 == len(mbs) else None
+            try:
+                model.backward(ctx, d_xf)
+            finally:
+                model.grad_hook = None
     return {"loss": acc[0], "kl_sum": acc[1], "clipped": acc[2], "approx_kl_sum": acc[3], "value_loss": vacc[0],
             "entropy_sum": vacc[1]}
 

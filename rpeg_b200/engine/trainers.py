@@ -109,6 +109,7 @@ class GRPOTrainer(_Base):
         self.algo = algo or A.AlgoConfig(kl_coef=0.04)
         self.seed = seed
         self.gen_tp = bool(gen_tp) and dp is not None and dp.world > 1
+        self.overlap_grad_reduce = True
         tp = dp.world if self.gen_tp else 1
         # Gradients are dead while generating and the KV cache is dead while training, so both live
         # in one arena sized for the larger of the two.
@@ -199,7 +200,9 @@ class GRPOTrainer(_Base):
         A.grpo_advantages(ro, self.K)
         denom = self._global_sum(ro.n_response_tokens())
         self.actor.zero_grad()
-        m = A.policy_train_step(self.actor, ro, self.algo, denom_tokens=denom)
+        # data parallel: finished layers' gradients are reduced in buckets under the rest of the last backward pass
+        hook = self.dp.overlap_hook(self.opt, self.actor) if (self.world > 1 and self.overlap_grad_reduce) else None
+        m = A.policy_train_step(self.actor, ro, self.algo, denom_tokens=denom, on_last_backward=hook)
         self._mark("train")
         # data parallel: the time up to the first barrier of the step is the wait for the slowest rank's backward
         self.opt.step(after_wait=(lambda: self._mark("grad_wait")) if self.world > 1 else None)

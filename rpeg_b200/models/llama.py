@@ -200,6 +200,10 @@ class LlamaModel:
         # its first GEMM, which then loads no weight tile before the version is complete (weights that other GPUs
         # are pushing into this model's buffer).
         self.weight_gate = None
+        # ``grad_hook(i)`` is called by ``backward`` right after layer ``i``'s gradient kernels are queued (the final
+        # norm and the heads are complete by then): the data-parallel step starts reducing finished layers under the rest
+        # of the backward pass (set for the LAST microbatch of a step only: earlier ones still accumulate)
+        self.grad_hook = None
         if weights is None:
             self.init_weights(seed)
 
@@ -375,6 +379,8 @@ class LlamaModel:
         for i in reversed(range(self.layer_lo, self.layer_hi)):
             lc = ctx.layers.pop()
             d_h = self._layer_bwd(i, lc, d_h, ctx)
+            if self.grad_hook is not None:
+                self.grad_hook(i)
         if not self.is_first:
             return d_h
         K.embed_bwd(ctx.tokens, d_h, self.gp["embed"])

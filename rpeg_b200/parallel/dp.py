@@ -42,6 +42,9 @@ class DPContext:
         self.slot_base = slot_base
         self.buffers: Dict[str, SymmetricBuffer] = {}
         self._scalar = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self._side: Optional[torch.cuda.Stream] = None          # stream of the bucketed gradient reduction
+        self._covered: list = []                                # flat ranges reduced under the backward pass of this step
+        self._overlap_scale = 1.0
 
     def clone(self, tag: str) -> "DPContext":
         """Context for another model sharing this one's signal pad (own barrier slots) and buffer table: buffers are
@@ -91,6 +94,56 @@ class DPContext:
                                       K.status_word(self.device).data_ptr(), torch.cuda.current_stream().cuda_stream),
               "rpeg_flag_barrier")
 
+    # -- gradient reduction in buckets under the backward pass (ZeRO-2 style overlap)
+    def _reduce_range(self, opt, lo: int, hi: int, scale: float) -> None:
+        """This rank's part of the flat range ``[lo, hi)``: sum the peers' gradients into ``opt.reduced`` and add the
+        squared norm to ``opt.sumsq``, on the current stream."""
+        a, b = max(lo, opt.shard_off), min(hi, opt.shard_off + opt.shard_n)
+        if a >= b:
+            return
+        g_buf = self.buffers[f"{self.tag}.g"]
+        check(lib().rpeg_dp_reduce_norm(g_buf.ptr_array(), self.world, a, b - a, scale,
+                                        opt.reduced.data_ptr() + 4 * (a - opt.shard_off), opt.sumsq.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream), "rpeg_dp_reduce_norm")
+
+    def overlap_hook(self, opt, model, bucket_layers: int = 4, grad_scale: float = 1.0):
+        """Hook for ``LlamaModel.grad_hook`` during the LAST microbatch's backward pass of a step: whenever
+        ``bucket_layers`` more layers have their final gradients, a side stream waits for that point of the backward,
+        meets the peers in a flag barrier (their gradients of the bucket are final too) and reduces this rank's part of
+        the bucket, while the main stream goes on with the earlier layers. ``fused_adam_step`` then only reduces what no
+        bucket covered (the embedding), waits for the side stream and runs Adam. Reference: backward hooks filling
+        buckets for asynchronous ``reduce_scatter_tensor`` calls, at most two in flight
+        (RPEG/runtime/workers/megatron_worker.py:909-1100)."""
+        if self.world == 1:
+            return None
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        lay = model.layout
+        self._covered = []
+        self._overlap_scale = float(grad_scale)
+        opt.sumsq.zero_()
+        lo_l, hi_l = model.layer_lo, model.layer_hi
+        tail = lay.entries["final_norm"][0] if "final_norm" in lay.entries else lay.total
+
+        def start_of(layer: int) -> int:
+            return lay.entries[f"l{layer}.attn_norm"][0] if layer < hi_l else tail
+
+        def hook(i: int) -> None:
+            if (i - lo_l) % bucket_layers != 0:
+                return
+            lo = start_of(i)
+            j = min(i + bucket_layers, hi_l)
+            hi = lay.total if j == hi_l else start_of(j)         # the first bucket takes the final norm and the heads along
+            ev = torch.cuda.Event()
+            ev.record()
+            self._side.wait_event(ev)
+            with torch.cuda.stream(self._side):
+                self.barrier(3)
+                self._reduce_range(opt, lo, hi, self._overlap_scale)
+            self._covered.append((lo, hi))
+
+        return hook
+
     def fused_adam_step(self, opt, grad_scale: float = 1.0, after_wait=None) -> None:
         """``after_wait()`` is called once the first barrier is queued: what precedes it on the stream is the wait for
         the slowest rank's backward, what follows is the step itself (callers time the two apart)."""
@@ -101,9 +154,22 @@ class DPContext:
         self.barrier(0)                                              # every rank finished its backward
         if after_wait is not None:
             after_wait()
-        opt.sumsq.zero_()
-        check(lib().rpeg_dp_reduce_norm(g_buf.ptr_array(), self.world, opt.shard_off, opt.shard_n, grad_scale,
-                                        opt.reduced.data_ptr(), opt.sumsq.data_ptr(), stream), "rpeg_dp_reduce_norm")
+        if self._covered:
+            # buckets were reduced under the backward pass: what is left of the shard, then join the side stream
+            covered, self._covered = sorted(self._covered), []
+            at = 0
+            total = opt.model.layout.total
+            for lo, hi in covered + [(total, total)]:
+                if lo > at:
+                    self._reduce_range(opt, at, lo, grad_scale)
+                at = max(at, hi)
+            ev = torch.cuda.Event()
+            ev.record(self._side)
+            torch.cuda.current_stream().wait_event(ev)
+        else:
+            opt.sumsq.zero_()
+            check(lib().rpeg_dp_reduce_norm(g_buf.ptr_array(), self.world, opt.shard_off, opt.shard_n, grad_scale,
+                                            opt.reduced.data_ptr(), opt.sumsq.data_ptr(), stream), "rpeg_dp_reduce_norm")
         self.barrier(1, payload_in=opt.sumsq, payload_out=opt.partials)  # exchange partial squared norms
         check(lib().rpeg_dp_adam_push(opt.master.data_ptr(), opt.m.data_ptr(), opt.v.data_ptr(), opt.reduced.data_ptr(),
                                       w_buf.ptr_array(), self.world, opt.shard_off, opt.shard_n, opt.lr, b1, b2,
