@@ -103,9 +103,14 @@ def main() -> int:
     gens = [torch.Generator(device="cpu").manual_seed(100 + r) for r in range(world)]
     ref_p, ref_m, ref_v = w0.clone(), torch.zeros_like(w0), torch.zeros_like(w0)
     ok_steps = []
-    for step in range(1, 4):
+    for step in range(1, 6):
         grads = [torch.randn(n, generator=gens[r]) * 0.01 for r in range(world)]
         model.g[:n].copy_(grads[rank].to(dev))
+        if step >= 4:
+            # the same step with the reduction done in per-layer buckets on the side stream, as under a backward pass
+            hook = dp.overlap_hook(opt, model, bucket_layers=1)
+            for layer in reversed(range(cfg.n_layers)):
+                hook(layer)
         opt.step()
         torch.cuda.synchronize()
         K.check_status()

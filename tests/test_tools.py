@@ -412,3 +412,32 @@ def test_engine_validate_cli_without_a_gpu(capsys):
     if not torch.cuda.is_available():
         assert ev.main(["--json"]) == 2
         assert json.loads(capsys.readouterr().out)["error"] == "no CUDA device visible"
+
+
+def test_published_results_reader_and_charts(tmp_path):
+    """The published measurements' layout (``<GPUs>-<model>/metrics_report.json`` in a directory or a tar archive): rows
+    per run with both schedules, the speed-up, and one SVG chart per metric; a schedule without numbers stays empty."""
+    import importlib.util
+    import tarfile
+    spec = importlib.util.spec_from_file_location("plot_published_results", os.path.join(ROOT, "experiments", "plot_published_results.py"))
+    ppr = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ppr)
+    def report(a, b):
+        run = lambda t: None if t is None else {"runtime": {"benchmark_wall_time_s": t, "tokens_per_s": 98304 / t,
+                                                            "hardware_utilization": {"avg_utilization_pct": 90.0}}}
+        return {"schedules": {k: v for k, v in (("pardistrlm", run(a)), ("native", run(b))) if v is not None}}
+    src = tmp_path / "athena_results"
+    for name, (a, b) in {"8-7": (300.0, 390.0), "16-7": (200.0, 210.0), "16-32": (600.0, None)}.items():
+        (src / name).mkdir(parents=True)
+        (src / name / "metrics_report.json").write_text(json.dumps(report(a, b)))
+    rows = ppr.load(src)
+    assert [(r["model_b"], r["gpus"]) for r in rows] == [(7, 8), (7, 16), (32, 16)]
+    assert abs(rows[0]["speedup"] - 1.3) < 1e-9 and rows[2]["speedup"] is None and rows[2]["native.iteration_s"] is None
+    with tarfile.open(tmp_path / "r.tar.bz2", "w:bz2") as tar:
+        tar.add(src, arcname="athena_results")
+    assert ppr.load(tmp_path / "r.tar.bz2") == rows
+    assert "1.30" in ppr.table(rows)
+    written = ppr.charts(rows, tmp_path / "fig")
+    assert len(written) == 3 and all(p.read_text().startswith("<svg") for p in written)
+    (tmp_path / "nothing_here").mkdir()
+    assert ppr.main(["--results", str(tmp_path / "nothing_here")]) == 1
