@@ -468,6 +468,9 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
+  // bit 0x1000 of the tile-width hint: the caller chains this GEMM into a decode step (see `pdl` below)
+  const bool chain = (bn_hint & 0x1000) != 0;
+  bn_hint &= 0xfff;
   int bn = bn_hint;
   if (bn == 0) {
     const int m_tiles = (M + BM - 1) / BM;
@@ -516,7 +519,7 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
   }
   // Decode GEMMs (the caller passes the split-K workspace): activation x weight^T, and no kernel of a decode step
   // writes the weights, so the grid may start under the previous kernel's tail and prefetch weight tiles.
-  const int pdl = (workspace != nullptr && !transA && !transB && !accumulate && gate.flags == nullptr) ? pdl_enabled() : 0;
+  const int pdl = ((workspace != nullptr || chain) && !transA && !transB && !accumulate && gate.flags == nullptr) ? pdl_enabled() : 0;
   CUtensorMap ta, tb;
   int rc;
   if (!transA) rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);

@@ -13,6 +13,12 @@
 //                             tells the peers, and leaves only when all peers told it (flag exchange, bounded)
 //                          i.e. reduce-scatter, residual add, RMSNorm and all-gather of a row-parallel linear's
 //                          output in one launch; when it returns on a rank, that rank's buffers are complete.
+//   tp_allreduce_rmsnorm_ll : the same result for FEW rows (the long tail of a generation, where the step is bound by
+//                          latency, not by bytes). One exchange instead of three: every rank pushes its partial rows
+//                          into a slot of its own in EVERY region as 8-byte units {two bf16 values, call number}, the
+//                          receivers poll the units themselves (no flag after the data, hence no fence that waits for
+//                          the stores to be acknowledged), and every rank sums the slots of all ranks in rank order,
+//                          so the results are the same bits everywhere. Twice the bytes, about a third of the latency.
 //   tp_allgather_cols    : vocabulary-parallel LM head: every rank wrote logits[:, r*Vloc .. (r+1)*Vloc) into its
 //                          own copy of the [B, V] buffer; the kernel pushes that block into all peers' copies and
 //                          waits until the peers' blocks have landed here.
@@ -219,6 +225,146 @@ tp_allreduce_rmsnorm_kernel(TpComm c, long long part_off, const __nv_bfloat16* _
   }
 }
 
+// One-shot variant for few rows. Slot layout inside the region, from `ll_off`: [2 parities][world senders][ll_rows]
+// rows of d / 2 units, a unit being {bf16x2 data, uint32 call number}. Block b owns row b on both sides: it pushes
+// this rank's partial of the row to all ranks and reduces the row from all ranks' slots. state[2] counts these
+// calls; the parity of the call number selects the slot set, which is enough because a rank can be at most one call
+// ahead of a peer (it cannot finish call k + 1 before that peer has sent its part of k + 1, i.e. has finished call k).
+__device__ unsigned long long g_tp_trace[4];   // %globaltimer at entry / after the push / when all slots were complete
+__device__ int g_tp_trace_on;
+
+constexpr int LL_THREADS = 1024;   // one 16-byte store per thread for d = 4096: the whole row is in flight at once
+
+template <int NP, bool MC>
+__global__ void __launch_bounds__(LL_THREADS)
+tp_allreduce_rmsnorm_ll_kernel(TpComm c, long long part_off, const float* __restrict__ parts, int splits, long long split_stride,
+                               const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w, long long y_off,
+                               long long h_off, int B, int d, float eps, long long ll_off, int ll_rows,
+                               unsigned* __restrict__ state, unsigned long long timeout_ns, int* status) {
+  __shared__ float warp_ss[LL_THREADS / 32];
+  griddep_launch();
+  griddep_wait();
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;   // an earlier wait ran out: stand down
+  const bool trace = g_tp_trace_on != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+  if (trace) g_tp_trace[0] = global_timer_ns();
+  const unsigned epoch = state[2] + 1u;
+  const int row = static_cast<int>(blockIdx.x);
+  const int pairs = d >> 2;                                   // 16-byte stores: two units = four bf16 values
+  const long long row_bytes = static_cast<long long>(d) * 4;  // d / 2 units of 8 bytes
+  const long long set_off = ll_off + static_cast<long long>(epoch & 1u) * c.world * ll_rows * row_bytes;
+  char* own = static_cast<char*>(c.peer[c.rank]);
+  // ---- push this rank's partial of the row into its slot in every region
+  {
+    const uint2* src = reinterpret_cast<const uint2*>(own + part_off + static_cast<long long>(row) * d * 2);
+    const long long dst = set_off + (static_cast<long long>(c.rank) * ll_rows + row) * row_bytes;
+#pragma unroll
+    for (int k = 0; k < NP; ++k) {
+      const int i = threadIdx.x + k * LL_THREADS;
+      if (i < pairs) {
+        uint2 v;
+        if (parts != nullptr) {
+          // the producer was a split-K GEMM: its fp32 partial slabs are summed here instead of by a kernel of their own
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int sp = 0; sp < splits; ++sp) {
+            const float4 q = reinterpret_cast<const float4*>(parts + sp * split_stride + static_cast<long long>(row) * d)[i];
+            acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+          }
+          v.x = pack_bf16x2(acc.x, acc.y);
+          v.y = pack_bf16x2(acc.z, acc.w);
+        } else {
+          v = src[i];
+        }
+        const uint32_t u[4] = {v.x, epoch, v.y, epoch};
+        if constexpr (MC) {
+          mc_st_16(static_cast<char*>(c.mc) + dst + static_cast<long long>(i) * 16, u);
+        } else {
+          for (int p = 0; p < c.world; ++p) peer_st_16(static_cast<char*>(c.peer[p]) + dst + static_cast<long long>(i) * 16, u);
+        }
+      }
+    }
+  }
+  if (trace) g_tp_trace[1] = global_timer_ns();
+  // ---- collect: the units of every sender validate themselves. All senders' loads of a thread are in flight
+  // together; the sum runs in rank order once they are complete (the same bits on every rank).
+  float v[NP][4];
+  const uint64_t t0 = global_timer_ns();
+  const char* slots = own + set_off + static_cast<long long>(row) * row_bytes;
+  const long long sender_stride = static_cast<long long>(ll_rows) * row_bytes;
+#pragma unroll
+  for (int k = 0; k < NP; ++k) {
+    const int i = threadIdx.x + k * LL_THREADS;
+    v[k][0] = v[k][1] = v[k][2] = v[k][3] = 0.f;
+    if (i < pairs) {
+      uint32_t a[RPEG_MAX_PEERS][4];
+      unsigned pending = (1u << c.world) - 1u, spins = 0;
+      while (pending != 0u) {
+#pragma unroll
+        for (int p = 0; p < RPEG_MAX_PEERS; ++p)
+          if ((pending >> p) & 1u) peer_ld_16(slots + p * sender_stride + static_cast<long long>(i) * 16, a[p]);
+#pragma unroll
+        for (int p = 0; p < RPEG_MAX_PEERS; ++p)
+          if (((pending >> p) & 1u) && a[p][1] == epoch && a[p][3] == epoch) pending &= ~(1u << p);
+        if (pending != 0u && (++spins & 31u) == 0u && global_timer_ns() - t0 > timeout_ns) {
+          record_error(status, RPEG_ERR_FLAG_TIMEOUT, 720, static_cast<int>(pending));
+          break;                                               // give up: finish on what is there, the host sees the status
+        }
+      }
+#pragma unroll
+      for (int p = 0; p < RPEG_MAX_PEERS; ++p) {
+        if (p < c.world) {
+          const float2 f0 = unpack_bf16x2(a[p][0]), f1 = unpack_bf16x2(a[p][2]);
+          v[k][0] += f0.x; v[k][1] += f0.y; v[k][2] += f1.x; v[k][3] += f1.y;
+        }
+      }
+    }
+  }
+  if (trace) g_tp_trace[2] = global_timer_ns();
+  // ---- residual, bf16 residual stream, RMSNorm: everything local from here on
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NP; ++k) {
+    const int i = threadIdx.x + k * LL_THREADS;
+    if (i < pairs) {
+      if (res != nullptr) {
+        const uint2 r = reinterpret_cast<const uint2*>(res + static_cast<size_t>(row) * d)[i];
+        const float2 f0 = unpack_bf16x2(r.x), f1 = unpack_bf16x2(r.y);
+        v[k][0] += f0.x; v[k][1] += f0.y; v[k][2] += f1.x; v[k][3] += f1.y;
+      }
+      uint2 hv;
+      hv.x = pack_bf16x2(v[k][0], v[k][1]);
+      hv.y = pack_bf16x2(v[k][2], v[k][3]);
+      const float2 f0 = unpack_bf16x2(hv.x), f1 = unpack_bf16x2(hv.y);
+      v[k][0] = f0.x; v[k][1] = f0.y; v[k][2] = f1.x; v[k][3] = f1.y;
+      ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y;
+      if (h_off >= 0) reinterpret_cast<uint2*>(own + h_off + static_cast<long long>(row) * d * 2)[i] = hv;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) warp_ss[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < LL_THREADS / 32; ++k) tot += warp_ss[k];
+  const float rstd = rsqrtf(tot / static_cast<float>(d) + eps);
+#pragma unroll
+  for (int k = 0; k < NP; ++k) {
+    const int i = threadIdx.x + k * LL_THREADS;
+    if (i < pairs) {
+      const uint2 wv = reinterpret_cast<const uint2*>(w)[i];
+      const float2 b0 = unpack_bf16x2(wv.x), b1 = unpack_bf16x2(wv.y);
+      uint2 o;
+      o.x = pack_bf16x2(v[k][0] * rstd * b0.x, v[k][1] * rstd * b0.y);
+      o.y = pack_bf16x2(v[k][2] * rstd * b1.x, v[k][3] * rstd * b1.y);
+      reinterpret_cast<uint2*>(own + y_off + static_cast<long long>(row) * d * 2)[i] = o;
+    }
+  }
+  // every block read state[2] before it got here; the last one through advances the call number
+  if (threadIdx.x == 0 && atomicAdd(&state[1], 1u) == gridDim.x - 1u) {
+    state[1] = 0u;
+    state[2] = epoch;
+  }
+}
+
 // Block [B, n_loc] bf16 at column rank*n_loc of the row-major [B, ld] buffer at `buf_off`: copy it from this
 // rank's region into every peer's, then wait until all peers' blocks are here.
 template <bool MC>
@@ -321,4 +467,49 @@ extern "C" int rpeg_tp_allgather_cols(void* const* peers, void* mc, int rank, in
     launch_pdl(tp_allgather_cols_kernel<false>, dim3(grid), dim3(256), 0, stream, c, buf_off, B, n_loc, ld, flag_off, state,
                timeout_ns, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+// The one-shot variant: B <= ll_rows rows; the region holds 2 * world * ll_rows * d * 4 bytes of slots from ll_off
+// (zero before the first call); state[2] counts the calls. d must be a multiple of 4.
+extern "C" int rpeg_tp_allreduce_rmsnorm_ll(void* const* peers, void* mc, int rank, int world, long long part_off,
+                                            const float* parts, int splits, long long split_stride, const void* res, const void* w, long long y_off, long long h_off, int B, int d,
+                                            float eps, long long ll_off, int ll_rows, unsigned* state,
+                                            unsigned long long timeout_ns, int* status, void* stream_v) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  TpComm c;
+  if (fill_comm(c, peers, mc, rank, world)) return -2;
+  if ((d & 7) || ((part_off | y_off | ll_off) & 15) || (h_off >= 0 && (h_off & 15))) return -3;
+  if (B <= 0) return 0;
+  if (B > ll_rows) return -5;
+  if (parts != nullptr && (splits < 1 || (reinterpret_cast<uintptr_t>(parts) & 15) || (split_stride & 3))) return -6;
+  const int np = ((d >> 2) + LL_THREADS - 1) / LL_THREADS;
+  const __nv_bfloat16 *rp = static_cast<const __nv_bfloat16*>(res), *wp = static_cast<const __nv_bfloat16*>(w);
+#define RPEG_TP_LL(NP_)                                                                                                     \
+  do {                                                                                                                      \
+    if (mc != nullptr)                                                                                                      \
+      launch_pdl(tp_allreduce_rmsnorm_ll_kernel<NP_, true>, dim3(B), dim3(LL_THREADS), 0, stream, c, part_off, parts, splits, split_stride, rp, wp, y_off, h_off, \
+                 B, d, eps, ll_off, ll_rows, state, timeout_ns, status);                                                     \
+    else                                                                                                                    \
+      launch_pdl(tp_allreduce_rmsnorm_ll_kernel<NP_, false>, dim3(B), dim3(LL_THREADS), 0, stream, c, part_off, parts, splits, split_stride, rp, wp, y_off, h_off, \
+                 B, d, eps, ll_off, ll_rows, state, timeout_ns, status);                                                     \
+  } while (0)
+  if (np <= 1) RPEG_TP_LL(1);
+  else if (np <= 2) RPEG_TP_LL(2);
+  else if (np <= 4) RPEG_TP_LL(4);
+  else return -4;
+#undef RPEG_TP_LL
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+// Time stamps of the last traced launch of the one-shot all-reduce (block 0): ns from its start to the end of the push
+// and to the moment all senders' units of the row were complete. enable != 0 switches the stamps on.
+extern "C" int rpeg_tp_trace(int enable, unsigned long long* out2) {
+  if (out2 != nullptr) {
+    unsigned long long h[4];
+    if (cudaMemcpyFromSymbol(h, g_tp_trace, sizeof(h)) != cudaSuccess) return -22;
+    out2[0] = h[1] - h[0];
+    out2[1] = h[2] - h[0];
+  }
+  const int on = enable ? 1 : 0;
+  return cudaMemcpyToSymbol(g_tp_trace_on, &on, sizeof(on)) == cudaSuccess ? 0 : -22;
 }

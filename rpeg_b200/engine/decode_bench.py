@@ -8,12 +8,16 @@ Prints one JSON line per (batch, ctx) with the measured time and the memory-traf
 (weights once + the KV of every live row) at the given HBM bandwidth. ``--layers`` shrinks the model
 so a profiler capture of single kernels stays small; ``--no-graphs`` launches kernels one by one.
 The numbers feed ``decode_bw_eff`` of the planner's cost model.
+
+Under ``torch.distributed.run`` with N ranks the step is the tensor-parallel one (``models.tp_decode.TPDecodeModel``
+over all ranks, every rank holding 1/N of the weights and KV heads of all rows); the traffic floor is then per rank.
 """
 from __future__ import annotations
 
 import argparse
 import dataclasses
 import json
+import os
 import sys
 
 import torch
@@ -34,15 +38,29 @@ def main(argv=None) -> int:
     ap.add_argument("--group-tc", action="store_true", help="with --group-attention: the tcgen05 group kernel instead of the CUDA-core one")
     ap.add_argument("--share", default="", help="K:S - groups of K consecutive rows alias the KV pages of their first S tokens "
                     "(K samples of one prompt), to measure what the shared pages save")
+    ap.add_argument("--shard", type=int, default=1, help="on one GPU: give the model 1/N of the heads and of d_ff, i.e. the "
+                    "matrix shapes a rank of N-way tensor parallelism works on (no collectives), to see the per-kernel floor")
     args = ap.parse_args(argv)
 
     from ..models.llama import LlamaConfig, LlamaModel
     from ..ops import kernels as K
     from .generation import Generator
 
-    dev = torch.device("cuda:0")
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
     cfg = dataclasses.replace(LlamaConfig.llama7b(max_pos=4096), n_layers=args.layers)
+    if args.shard > 1:
+        cfg = dataclasses.replace(cfg, n_heads=cfg.n_heads // args.shard, n_kv_heads=cfg.n_kv_heads // args.shard,
+                                  d_ff=cfg.d_ff // args.shard // 8 * 8)
     model = LlamaModel(cfg, dev, seed=1)
+    whole = model
+    if world > 1:
+        import torch.distributed as dist
+        from ..models.tp_decode import TPDecodeModel
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        model = TPDecodeModel(whole, None, max_batch=args.slots)
     gen = Generator(model, max_slots=args.slots, max_seq_len=args.max_len, kv_budget_bytes=1e12, eos_id=2,
                     use_graphs=not args.no_graphs)
     n = gen.max_slots
@@ -64,8 +82,8 @@ def main(argv=None) -> int:
             gen.group_rows[:n_groups, :k_share] = torch.arange(n_groups * k_share, dtype=torch.int32, device=dev).view(n_groups, k_share)
             gen.group_shared[:n_groups] = shared_pages * 64
             gen.row_key0[: n_groups * k_share] = shared_pages * 64
-    weight_bytes = 2 * sum(int(t.numel()) for name, t in model.p.items() if name != "embed" and not name.startswith("scalar_head"))
-    kv_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2
+    weight_bytes = 2 * sum(int(t.numel()) for name, t in whole.p.items() if name != "embed" and not name.startswith("scalar_head")) // world
+    kv_per_token = 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2 // world
 
     def reset(b: int, ctx: int) -> None:
         gen.active.zero_()
@@ -94,10 +112,14 @@ def main(argv=None) -> int:
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / args.iters
             floor_ms = (weight_bytes + b * (ctx + args.iters / 2) * kv_per_token) / (args.hbm_gbs * 1e9) * 1e3
-            print(json.dumps({"batch": b, "ctx": ctx, "layers": cfg.n_layers, "ms_per_step": round(ms, 4),
-                              "tokens_per_s": round(b / ms * 1e3, 1), "traffic_floor_ms": round(floor_ms, 4),
-                              "fraction_of_floor": round(floor_ms / ms, 4), "graphs": not args.no_graphs}), flush=True)
+            if rank == 0:
+                print(json.dumps({"batch": b, "ctx": ctx, "layers": cfg.n_layers, "tp": world, "ms_per_step": round(ms, 4),
+                                  "tokens_per_s": round(b / ms * 1e3, 1), "traffic_floor_ms": round(floor_ms, 4),
+                                  "fraction_of_floor": round(floor_ms / ms, 4), "graphs": not args.no_graphs}), flush=True)
     K.check_status()
+    if world > 1:
+        model.comm.close()
+        dist.destroy_process_group()
     return 0
 
 

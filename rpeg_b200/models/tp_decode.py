@@ -37,7 +37,8 @@ from .llama import LlamaModel
 
 
 class TPDecodeModel:
-    def __init__(self, full: LlamaModel, group=None, max_batch: int = 256, comm_mode: Optional[str] = None):
+    def __init__(self, full: LlamaModel, group=None, max_batch: int = 256, comm_mode: Optional[str] = None,
+                 one_shot_rows: Optional[int] = None):
         cfg = full.cfg
         self.full, self.cfg, self.device = full, cfg, full.device
         multi = dist.is_initialized() and dist.get_world_size(group) > 1
@@ -73,10 +74,14 @@ class TPDecodeModel:
                 store.append(self.shard[off:off + n].view(*shape))
                 off += n
         B = self.max_batch
-        self.comm = TPCommRegion(3 * B * d * 2 + B * cfg.vocab * 2 + 4096, self.device, group, comm_mode)
+        # few rows (rows x ranks <= 256): the all-reduce is bound by latency and runs as one exchange
+        ll_rows = min(B, max(8, 256 // tp)) if one_shot_rows is None else min(B, int(one_shot_rows))
+        self.comm = TPCommRegion(3 * B * d * 2 + B * cfg.vocab * 2 + TPCommRegion.ll_bytes(tp, ll_rows, d) + 8192, self.device, group,
+                                 comm_mode)
         for name in ("part", "x", "h"):
             self.comm.alloc(name, B * d * 2)
         self.comm.alloc("logits", B * cfg.vocab * 2)
+        self.comm.enable_one_shot(ll_rows, d)
         self._ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         self._timed = False
         self.refreshes = 0
@@ -144,7 +149,7 @@ class TPDecodeModel:
         second kernel is needed. A long one (few ranks) is cut along K so that every SM streams a slice of the
         weights, and the fp32 partials are summed by the split-K reduction."""
         if a.shape[1] <= 1536:
-            K.gemm(a, w, out=out, bn=128)
+            K.gemm(a, w, out=out, bn=128, chain=True)
         else:
             K.gemm(a, w, out=out, workspace=ws)
 
@@ -164,19 +169,25 @@ class TPDecodeModel:
         x0, _, _ = K.rmsnorm_fwd(h, p["l0.attn_norm"], cfg.rms_eps)
         qkv = torch.empty((B, self.qw + 2 * self.kvw), dtype=torch.bfloat16, device=self.device)
         xin = x0
+        one_shot = R.one_shot(B, d)     # few rows: the all-reduce sums the split-K slabs itself, one kernel fewer per GEMM
+
+        def reduce_into(a, wmat, norm_w, h_out):
+            if one_shot:
+                R.allreduce_rmsnorm("part", h, norm_w, "x", h_out, B, d, cfg.rms_eps, parts=K.gemm_partials(a, wmat, ws))
+            else:
+                self._row_parallel(a, wmat, part, ws)
+                R.allreduce_rmsnorm("part", h, norm_w, "x", h_out, B, d, cfg.rms_eps)
+
         for i in range(cfg.n_layers):
             parts = K.gemm_partials(xin, self.wqkv[i], ws)
             K.rope_kv_append_partials_(parts, qkv, 0, self.qw, self.qw + self.kvw, slot_ids, pos, self.full.cos_t, self.full.sin_t,
                                        page_table, kcache[i], vcache[i], self.n_heads_local, self.n_kv_local, cfg.head_dim)
             attn = K.paged_decode_attn(qkv, 0, kcache[i], vcache[i], page_table, seq_len, self.n_heads_local, self.n_kv_local,
                                        cfg.head_dim, scale, nsplit=nsplit, groups=groups)
-            self._row_parallel(attn, self.wo[i], part, ws)
-            R.allreduce_rmsnorm("part", h, p[f"l{i}.mlp_norm"], "x", "h", B, d, cfg.rms_eps)
+            reduce_into(attn, self.wo[i], p[f"l{i}.mlp_norm"], "h")
             parts = K.gemm_partials(x, self.wgu[i], ws)
             act = K.swiglu_fwd_partials(parts)
-            self._row_parallel(act, self.wdown[i], part, ws)
             last = i + 1 == cfg.n_layers
-            R.allreduce_rmsnorm("part", h, p["final_norm"] if last else p[f"l{i + 1}.attn_norm"], "x", None if last else "h", B, d,
-                                cfg.rms_eps)
+            reduce_into(act, self.wdown[i], p["final_norm"] if last else p[f"l{i + 1}.attn_norm"], None if last else "h")
             xin = x
         return x

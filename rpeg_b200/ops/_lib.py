@@ -67,6 +67,8 @@ _SIGNATURES = {
     "rpeg_paged_decode_attn_grouped": [P, I, I, P, P, P, I, P, P, P, I, I, I, I, I, F, P, P, P, P],
     "rpeg_tp_allreduce_rmsnorm": [P, P, I, I, LL, P, P, LL, LL, I, I, F, LL, P, c_ulonglong, P, P],
     "rpeg_tp_allgather_cols": [P, P, I, I, LL, I, I, I, LL, P, c_ulonglong, P, P],
+    "rpeg_tp_allreduce_rmsnorm_ll": [P, P, I, I, LL, P, I, LL, P, P, LL, LL, I, I, F, LL, I, P, c_ulonglong, P, P],
+    "rpeg_tp_trace": [I, P],
     "rpeg_paged_decode_attn_grouped_tc": [P, I, I, P, P, LL, P, I, P, P, P, I, I, I, I, I, F, P, P, P, P, P],
     "rpeg_gemm_swiglu": [P, P, P, I, I, I, I, I, I, P, P],
     "rpeg_symm_alloc": [c_ulonglong, P],

@@ -55,9 +55,12 @@ def _req(t: torch.Tensor, dtype: torch.dtype, name: str) -> None:
 
 
 # --------------------------------------------------------------------------- GEMM
+GEMM_CHAIN = 0x1000     # flag in the tile-width argument of rpeg_gemm_bf16: launch as a programmatic dependent
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
          out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
-         bn: int = 0, workspace: torch.Tensor | None = None, gate: tuple | None = None) -> torch.Tensor:
+         bn: int = 0, workspace: torch.Tensor | None = None, gate: tuple | None = None, chain: bool = False) -> torch.Tensor:
     """``C[M,N] = op(a) @ op(b).T`` on tcgen05 tensor cores with fp32 accumulation.
 
     ``gate = (flags uint32 tensor, min_version, timeout_s)`` holds back every operand load until all words of
@@ -67,7 +70,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     of a linear weight — or ``[K,N]`` with ``trans_b``. Rows may be strided (last dim contiguous).
     ``out_dtype=float32, accumulate=True`` adds into ``out`` (used for weight-gradient accumulation).
     ``workspace`` (fp32 scratch) lets skinny problems (M <= 256, e.g. decode) run split-K so every SM
-    streams part of the weight matrix.
+    streams part of the weight matrix. ``chain``: the call is a link of a decode step whose kernels are launched as
+    programmatic dependents (``b`` is a weight matrix that no kernel of the step writes): the grid may start under the
+    previous kernel's tail and fetch weight tiles before that kernel has finished.
     """
     _req(a, torch.bfloat16, "a")
     _req(b, torch.bfloat16, "b")
@@ -100,7 +105,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         return out
     rc = lib().rpeg_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
                               out.stride(0), int(trans_a), int(trans_b), int(out_dtype == torch.float32),
-                              int(accumulate), bn, _ptr(workspace), 0 if workspace is None else workspace.numel(),
+                              int(accumulate), bn | (GEMM_CHAIN if chain else 0), _ptr(workspace), 0 if workspace is None else workspace.numel(),
                               status_word(a.device).data_ptr(), _stream())
     check(rc, "rpeg_gemm_bf16")
     return out

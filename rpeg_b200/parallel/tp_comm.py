@@ -25,7 +25,7 @@ from ..ops import kernels as K
 from ..ops._lib import check, lib
 
 WAIT_NS = 5_000_000_000      # ranks replay the same step, but their hosts may be apart by a graph capture or a collection pause
-_FLAG_BYTES = 2 * K.MAX_PEERS * 4
+_FLAG_BYTES = 256        # two flag arrays of MAX_PEERS uint32 (column all-gather), then two arrival counters (all-reduce)
 
 
 def _align(n: int, a: int = 256) -> int:
@@ -71,9 +71,10 @@ class TPCommRegion:
                 self.peer_ptrs = list(buf.peer_ptrs)
                 self.backend = "cuda-ipc peer memory"
         self._cursor = 0
+        self.ll_rows, self._ll_d = 0, 0
         self.offsets: Dict[str, Tuple[int, int]] = {}
         self.flag_off = self.nbytes - _align(_FLAG_BYTES)
-        self.state = torch.zeros(4, dtype=torch.int32, device=self.device)      # [calls finished, blocks finished]
+        self.state = torch.zeros(4, dtype=torch.int32, device=self.device)      # [calls finished, blocks finished, arrivals counted: landed, ready]
         self._peer_array = (ctypes.c_void_p * self.world)(*self.peer_ptrs)
         if self.world > 1:
             torch.cuda.synchronize(self.device)
@@ -103,6 +104,20 @@ class TPCommRegion:
         self.offsets[name] = (off, int(nbytes))
         return off
 
+    @staticmethod
+    def ll_bytes(world: int, rows: int, d: int) -> int:
+        """Slot bytes of the one-shot all-reduce: two sets (call parity) x senders x rows x d/2 units of 8 bytes."""
+        return 2 * world * rows * d * 4
+
+    def enable_one_shot(self, rows: int, d: int) -> None:
+        """Reserve the slots of the one-shot all-reduce: calls of ``allreduce_rmsnorm`` with at most ``rows`` rows of width
+        ``d`` then push their partial sums to every rank in self-validating 8-byte units and reduce locally (one
+        exchange, for the latency-bound tail of a generation) instead of reduce-scatter + all-gather (three)."""
+        if rows <= 0:
+            return
+        self.alloc("ll", self.ll_bytes(self.world, rows, d))
+        self.ll_rows, self._ll_d = int(rows), int(d)
+
     def view(self, name: str, shape, dtype=torch.bfloat16) -> torch.Tensor:
         off, nbytes = self.offsets[name]
         n = 1
@@ -114,15 +129,40 @@ class TPCommRegion:
         return self.bytes_view[off:off + n * item].view(dtype).view(*shape)
 
     # ------------------------------------------------------------------ collectives
+    def one_shot(self, B: int, d: int) -> bool:
+        """Whether ``allreduce_rmsnorm`` of ``B`` rows of width ``d`` runs as one exchange (and accepts ``parts``)."""
+        return bool(self.ll_rows) and B <= self.ll_rows and d == self._ll_d
+
     def allreduce_rmsnorm(self, part: str, res: Optional[torch.Tensor], w: torch.Tensor, y: str, h: Optional[str], B: int,
-                          d: int, eps: float) -> None:
+                          d: int, eps: float, parts=None) -> None:
         """``y = rmsnorm(sum over ranks of part + res) * w`` and ``h`` = that sum in bf16, complete in every rank's
-        region when the call's kernel has finished."""
+        region when the call's kernel has finished. ``parts`` (an ``ops.kernels.Partials`` of a split-K GEMM, only when
+        ``one_shot(B, d)``): this rank's partial sum is the sum of those fp32 slabs instead of the ``part`` buffer."""
+        if self.one_shot(B, d):
+            check(lib().rpeg_tp_allreduce_rmsnorm_ll(self._peer_array, self.mc_ptr or None, self.rank, self.world, self.offsets[part][0],
+                                                     None if parts is None else parts.buf.data_ptr(), 0 if parts is None else parts.splits,
+                                                     0 if parts is None else parts.stride,
+                                                     None if res is None else res.data_ptr(), w.data_ptr(), self.offsets[y][0],
+                                                     -1 if h is None else self.offsets[h][0], B, d, eps, self.offsets["ll"][0],
+                                                     self.ll_rows, self.state.data_ptr(), WAIT_NS, K.status_word(self.device).data_ptr(),
+                                                     torch.cuda.current_stream().cuda_stream), "rpeg_tp_allreduce_rmsnorm_ll")
+            return
+        if parts is not None:
+            raise ValueError("split-K partials are only taken by the one-shot all-reduce")
         check(lib().rpeg_tp_allreduce_rmsnorm(self._peer_array, self.mc_ptr or None, self.rank, self.world, self.offsets[part][0],
                                               None if res is None else res.data_ptr(), w.data_ptr(), self.offsets[y][0],
                                               -1 if h is None else self.offsets[h][0], B, d, eps, self.flag_off,
                                               self.state.data_ptr(), WAIT_NS, K.status_word(self.device).data_ptr(),
                                               torch.cuda.current_stream().cuda_stream), "rpeg_tp_allreduce_rmsnorm")
+
+    @staticmethod
+    def trace(enable: bool):
+        """Switch the time stamps inside the one-shot all-reduce kernel on or off; returns, for the last traced launch,
+        microseconds from its start to (push issued, all senders' units complete)."""
+        import ctypes as _ct
+        out = (_ct.c_ulonglong * 2)()
+        check(lib().rpeg_tp_trace(int(bool(enable)), out), "rpeg_tp_trace")
+        return int(out[0]) / 1e3, int(out[1]) / 1e3
 
     def allgather_cols(self, buf: str, B: int, n_loc: int, ld: int) -> None:
         """Every rank's column block ``[:, rank*n_loc : (rank+1)*n_loc]`` of the ``[B, ld]`` buffer goes to all ranks."""

@@ -6,7 +6,8 @@
 
 Checks, each against the whole model on the same GPU or against fp32 PyTorch:
   1. ``allreduce_rmsnorm``: rank-dependent partial sums -> rmsnorm(sum + residual) and the new residual stream,
-     against an NCCL all-reduce of the fp32 partials followed by fp32 PyTorch; identical bits on every rank.
+     against an NCCL all-reduce of the fp32 partials followed by fp32 PyTorch; identical bits on every rank; both
+     kernels (one exchange for few rows, reduce-scatter + all-gather otherwise) in alternation.
   2. ``allgather_cols`` against ``all_gather``.
   3. three decode steps of ``TPDecodeModel`` against ``LlamaModel.decode_step`` (separate KV caches).
   4. a greedy generation through ``Generator(TPDecodeModel)``: same tokens on every rank, log-probs close to the
@@ -25,21 +26,24 @@ import torch.distributed as dist
 
 
 def time_collectives(dev, world: int, comm_mode=None, rows: int = 256, d: int = 4096, vocab: int = 32000, iters: int = 200) -> dict:
-    """Microseconds per launch of ``allreduce_rmsnorm`` ([rows, d] bf16 partial sums) and ``allgather_cols``
-    ([rows, vocab] logits), back to back on one stream as in a decode step; CUDA events, maximum over ranks."""
+    """Microseconds per launch of ``allreduce_rmsnorm`` ([rows, d] bf16 partial sums; for few rows both as one exchange
+    and as reduce-scatter + all-gather) and of ``allgather_cols`` ([rows, vocab] logits), back to back on one stream as
+    in a decode step; CUDA events, maximum over ranks."""
     from rpeg_b200.parallel.tp_comm import TPCommRegion
-    R = TPCommRegion(3 * rows * d * 2 + rows * vocab * 2 + 4096, dev, None, comm_mode)
+    ll_rows = max(8, 256 // world)
+    R = TPCommRegion(3 * rows * d * 2 + rows * vocab * 2 + TPCommRegion.ll_bytes(world, ll_rows, d) + 8192, dev, None, comm_mode)
     for name in ("part", "x", "h"):
         R.alloc(name, rows * d * 2)
     R.alloc("logits", rows * vocab * 2)
+    R.enable_one_shot(ll_rows, d)
     R.view("part", (rows, d)).fill_(0.01)
     R.view("h", (rows, d)).zero_()
     w = torch.ones(d, dtype=torch.bfloat16, device=dev)
     h = R.view("h", (rows, d))
-    out = {"backend": R.backend, "rows": rows, "d": d, "vocab": vocab}
+    out = {"backend": R.backend, "rows": rows, "d": d, "vocab": vocab, "one_shot_rows": ll_rows}
     v_loc = vocab // world // 8 * 8
-    for name, fn in (("allreduce_rmsnorm_us", lambda: R.allreduce_rmsnorm("part", h, w, "x", None, rows, d, 1e-5)),
-                     ("allgather_cols_us", lambda: R.allgather_cols("logits", rows, v_loc, vocab))):
+
+    def timed(fn) -> float:
         for _ in range(20):
             fn()
         if world > 1:
@@ -54,7 +58,24 @@ def time_collectives(dev, world: int, comm_mode=None, rows: int = 256, d: int = 
         t = torch.tensor([e0.elapsed_time(e1) * 1e3 / iters], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        out[name] = float(t.item())
+        return float(t.item())
+
+    out["allreduce_rmsnorm_us"] = timed(lambda: R.allreduce_rmsnorm("part", h, w, "x", None, rows, d, 1e-5))
+    out["allgather_cols_us"] = timed(lambda: R.allgather_cols("logits", rows, v_loc, vocab))
+    for n in (ll_rows, 32, 8):                                       # the tail of a generation: few rows left
+        if n > ll_rows:
+            continue
+        out[f"allreduce_rmsnorm_{n}rows_one_shot_us"] = timed(lambda: R.allreduce_rmsnorm("part", h, w, "x", None, n, d, 1e-5))
+        keep, R.ll_rows = R.ll_rows, 0
+        out[f"allreduce_rmsnorm_{n}rows_two_phase_us"] = timed(lambda: R.allreduce_rmsnorm("part", h, w, "x", None, n, d, 1e-5))
+        R.ll_rows = keep
+    # where the time of a one-shot launch goes (time stamps taken inside the kernel by block 0)
+    TPCommRegion.trace(True)
+    for _ in range(5):
+        R.allreduce_rmsnorm("part", h, w, "x", None, 8, d, 1e-5)
+    torch.cuda.synchronize()
+    pushed, complete = TPCommRegion.trace(False)
+    out["one_shot_trace_us"] = {"push_issued": round(pushed, 2), "all_units_complete": round(complete, 2)}
     R.close()
     return out
 
@@ -102,10 +123,14 @@ def main() -> int:
     res = torch.randn(B, d, generator=g0).bfloat16().to(dev)
     w = (1.0 + 0.1 * torch.randn(d, generator=g0)).bfloat16().to(dev)
     errs = []
-    for call in range(3):                       # repeated calls: the device-side call counter must keep the ranks in step
+    for call in range(6):                       # repeated calls: the device-side call counters must keep the ranks in step
+        one_shot_rows, R.ll_rows = R.ll_rows, (R.ll_rows if call % 2 == 0 else 0)      # alternate the two kernels
         R.view("part", (B, d)).copy_(part * (call + 1))
         R.view("h", (B, d)).copy_(res)
+        if world > 1:
+            dist.barrier()                      # (the copies above are ordinary kernels: keep the test's own writes apart)
         R.allreduce_rmsnorm("part", R.view("h", (B, d)), w, "x", "h", B, d, cfg.rms_eps)
+        R.ll_rows = one_shot_rows
         total = (part * (call + 1)).float()
         if world > 1:
             dist.all_reduce(total)
