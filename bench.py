@@ -365,30 +365,51 @@ def main() -> None:
                 p, r = p.to(device), r.to(device)
             return trainer.step(p, r)
 
-    # Recomputation policy. "auto": keep a layer's activations for the backward pass (no second forward, a quarter
-    # fewer training FLOPs) when this rank has the memory for them, else recompute every layer from its input. The
-    # activations of one microbatch are micro_tokens x layers x (7 d + 3 d_ff) bf16 values plus the attention statistics.
+    # Recomputation policy. "auto": keep the activations of as many layers for the backward pass as this rank has the
+    # memory for (their second forward pass is skipped: up to a quarter fewer training FLOPs) and recompute the other
+    # layers from their inputs. One layer's activations of a microbatch are micro_tokens x (7 d + 3 d_ff) bf16 values plus
+    # the attention statistics. If not all layers fit with the requested microbatch and more fit with half of it, it is halved
+    # (same tokens per step, twice the launches). All ranks take the smallest answer.
+    keep_layers = None
     if args.recompute == "auto":
         policy = None
         for name in ("actor", "policy"):
             if hasattr(trainer, name):
                 policy = getattr(trainer, name)
         if policy is not None and getattr(policy, "g", None) is not None:
-            act_bytes = 1.15 * args.micro_tokens * cfg.n_layers * (7 * cfg.d_model + 3 * cfg.d_ff) * 2
             torch.cuda.synchronize()
             free_bytes = float(torch.cuda.mem_get_info(device)[0])
-            fits = torch.tensor([1 if free_bytes > act_bytes + 12e9 else 0], device=device)
+            n_l = cfg.n_layers
+
+            def layers_that_fit(micro: int) -> int:
+                per_layer = 1.15 * micro * (7 * cfg.d_model + 3 * cfg.d_ff) * 2
+                reserve = 8e9 + 3.0 * per_layer      # one layer being recomputed, backward temporaries, LM-head chunk, fragmentation
+                return max(0, min(n_l, int((free_bytes - reserve) // per_layer)))
+
+            micro = args.micro_tokens
+            fit = layers_that_fit(micro)
+            if fit < n_l and micro >= 16384 and layers_that_fit(micro // 2) > fit:
+                micro //= 2
+                fit = layers_that_fit(micro)
+            choice = torch.tensor([fit, micro], device=device, dtype=torch.int64)
             if world > 1:
-                dist.all_reduce(fits, op=dist.ReduceOp.MIN)
-            if int(fits.item()) == 1:
-                recompute = "none"
-                for name in ("actor", "policy", "critic"):
-                    m_ = getattr(trainer, name, None)
-                    if m_ is not None and getattr(m_, "g", None) is not None:
-                        m_.recompute = "none"
+                dist.all_reduce(choice, op=dist.ReduceOp.MIN)
+            keep_layers, micro = int(choice[0].item()), int(choice[1].item())
+            if micro != args.micro_tokens:
+                keep_layers = min(keep_layers, layers_that_fit(micro))
+                args.micro_tokens = micro
+                algo.micro_tokens = micro
+            recompute = "none" if keep_layers == n_l else ("full" if keep_layers == 0 else f"all but the last {keep_layers} layers")
+            for name in ("actor", "policy", "critic"):
+                m_ = getattr(trainer, name, None)
+                if m_ is not None and getattr(m_, "g", None) is not None:
+                    m_.recompute = "none" if keep_layers == n_l else "full"
+                    m_.keep_layers = 0 if keep_layers == n_l else keep_layers
             if rank == 0:
-                print(f"[bench] recompute={recompute}: {free_bytes / 1e9:.1f} GB free, activations of a microbatch {act_bytes / 1e9:.1f} GB",
+                print(f"[bench] recompute={recompute}: {free_bytes / 1e9:.1f} GB free, microbatch of {micro} tokens, "
+                      f"activations of one layer {1.15 * micro * (7 * cfg.d_model + 3 * cfg.d_ff) * 2 / 1e9:.2f} GB",
                       file=sys.stderr, flush=True)
+    recompute_state = {"value": recompute}
     parallelism_text = getattr(trainer, "parallelism", None) or f"dp{world}"
 
     def extra_metrics(line: dict) -> dict:
@@ -430,7 +451,22 @@ def main() -> None:
         word: a kernel whose bounded wait ran out must not let later steps run on its output."""
         t = time.perf_counter()
         try:
-            out = run(i % len(batches), on_device=False)
+            try:
+                out = run(i % len(batches), on_device=False)
+            except torch.cuda.OutOfMemoryError:
+                # kept activations did not fit after all (allocator fragmentation): on one GPU nothing else is in flight,
+                # so fall back to recomputing every layer and run the step again; with peers the step cannot be re-entered
+                if world > 1 or tag != "warmup" or not keep_layers:
+                    raise
+                for name in ("actor", "policy", "critic"):
+                    m_ = getattr(trainer, name, None)
+                    if m_ is not None and getattr(m_, "g", None) is not None:
+                        m_.recompute, m_.keep_layers = "full", 0
+                        m_.g.zero_()
+                recompute_state["value"] = "full (kept activations ran out of memory)"
+                torch.cuda.empty_cache()
+                print("[bench] out of memory with kept activations: recomputing every layer", file=sys.stderr, flush=True)
+                out = run(i % len(batches), on_device=False)
             K.check_status()
         except BaseException as exc:  # noqa: BLE001 - reported and re-raised as the exit code
             fail(f"{tag} step {i}", exc)
@@ -519,7 +555,7 @@ def main() -> None:
                        "global_batch": B * Kk if algo_name in ("grpo", "grpo_async") else B, "prompts": B, "samples_per_prompt": Kk,
                        "seq_len": S + T, "prompt_len": S, "max_new_tokens": T, "gen_quantiles": spec["quantiles"],
                        "parallelism": par, "optimizer": "adamw fp32 master, sharded over dp",
-                       "recompute": recompute, "micro_tokens": args.micro_tokens, "gen_slots": slots if algo_name in ("grpo", "grpo_async", "ppo") else None,
+                       "recompute": recompute_state["value"], "micro_tokens": args.micro_tokens, "gen_slots": slots if algo_name in ("grpo", "grpo_async", "ppo") else None,
                        "l2": "working set (13.5 GB of weights per model) far exceeds the 126 MB L2; no flush needed",
                        "time_budget_s": budget},
             "e2e": {"value": stats[0] / (ms_e2e / 1e3), "unit": "samples/s", "ms_per_step": ms_e2e / n_steps,

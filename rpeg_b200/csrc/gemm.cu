@@ -60,8 +60,11 @@ template <int BN, int EPI, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          void* __restrict__ Cout, int M, int N, int K, int ldc, int accumulate, int k_splits,
-                         long long split_stride, int* status, WeightGate gate, int pdl) {
+                         long long split_stride, int* status, WeightGate gate, int pdl, int a_rows) {
   using Cfg = GemmCfg<BN>;
+  // K-major A with few rows (decode): the TMA box covers only `a_rows` rows of the 128-row A tile. The MMA still reads
+  // 128 rows; what it computes from the rows nobody loaded lands in accumulator rows that the epilogue never stores.
+  const uint32_t stage_tx = static_cast<uint32_t>(Cfg::B_BYTES + (A_MN ? Cfg::A_BYTES : a_rows * BK * 2));
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -160,7 +163,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const int kb0 = (blockIdx.x % k_splits) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
             const int pre = min(STAGES, kb1 - kb0);
             for (int i = 0; i < pre; ++i) {            // weights first: they do not depend on the previous kernel
-              mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+              mbar_expect_tx(&full_bar[i], stage_tx);
               tma_load_2d(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmap_b, &full_bar[i], (kb0 + i) * BK, tn * BN);  // never EPI_SWIGLU
             }
             griddep_wait();
@@ -186,7 +189,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, status, 100)) goto producer_done;
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
-          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          mbar_expect_tx(&full_bar[stage], stage_tx);
           if constexpr (!A_MN) {
             tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
           } else {
@@ -376,7 +379,7 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
 template <int BN, int EPI, bool A_MN, bool B_MN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, int ldc,
                        int accumulate, int k_splits, long long split_stride, int* status, int num_sms,
-                       cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}, int pdl = 0) {
+                       cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}, int pdl = 0, int a_rows = BM) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, A_MN, B_MN>;
   static bool configured = false;
@@ -399,23 +402,23 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, in
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, gate, 1) == cudaSuccess
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, gate, 1, a_rows) == cudaSuccess
                ? 0 : -21;
   }
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride,
-                                                        status, gate, 0);
+                                                        status, gate, 0, a_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
 template <int BN, int EPI>
 static int dispatch_major(int transA, int transB, const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M,
                           int N, int K, int ldc, int accumulate, int k_splits, long long split_stride, int* status,
-                          int num_sms, cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}, int pdl = 0) {
-  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl);
-  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl);
+                          int num_sms, cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}, int pdl = 0, int a_rows = BM) {
+  if (!transA && !transB) return launch_gemm<BN, EPI, false, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl, a_rows);
+  if (transA && !transB) return launch_gemm<BN, EPI, true, false>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl, a_rows);
   if constexpr (BN >= 64) {  // an MN-major B tile is built from 64-column TMA boxes
-    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl);
-    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl);
+    if (!transA) return launch_gemm<BN, EPI, false, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl, a_rows);
+    return launch_gemm<BN, EPI, true, true>(ta, tb, C, M, N, K, ldc, accumulate, k_splits, split_stride, status, num_sms, stream, gate, pdl, a_rows);
   }
   return -30;
 }
@@ -426,6 +429,20 @@ static int g_num_sms = 0;
 }  // namespace rpeg
 
 using namespace rpeg;
+
+// Rows of A that the TMA box fetches per k-block: the whole 128-row tile, or only 32 / 64 rows when the problem has no
+// more (decode). Per k-block an SM then takes in 36 or 40 KB instead of 48 KB for a 256-wide weight tile, which is what
+// counts when the weights stream from memory and the activation tile is re-read from L2 by every CTA.
+// RPEG_GEMM_SKINNY_A=0 keeps the full box.
+static int a_box_rows(int M, int transA) {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("RPEG_GEMM_SKINNY_A");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (transA || !on) return BM;
+  return M <= 32 ? 32 : (M <= 64 ? 64 : BM);
+}
 
 static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int transA,
                      int transB, int out_fp32, int accumulate, int bn_hint, float* workspace, long long workspace_elems,
@@ -522,7 +539,8 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
   const int pdl = ((workspace != nullptr || chain) && !transA && !transB && !accumulate && gate.flags == nullptr) ? pdl_enabled() : 0;
   CUtensorMap ta, tb;
   int rc;
-  if (!transA) rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
+  const int a_rows = a_box_rows(M, transA);
+  if (!transA) rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, a_rows);
   else rc = make_tmap_bf16_2d(&ta, A, M, K, lda, 64, BK);
   if (rc) return rc;
   if (!transB) rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
@@ -531,9 +549,9 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
 #define RPEG_GEMM_CASE(BN_)                                                                                      \
   case BN_:                                                                                                       \
     rc = gemm_fp32 ? dispatch_major<BN_, EPI_F32>(transA, transB, ta, tb, gemm_out, M, N, K, gemm_ldc, accumulate, \
-                                                  k_splits, split_stride, status, g_num_sms, stream, gate, pdl)   \
+                                                  k_splits, split_stride, status, g_num_sms, stream, gate, pdl, a_rows)   \
                    : dispatch_major<BN_, EPI_BF16>(transA, transB, ta, tb, gemm_out, M, N, K, gemm_ldc, accumulate, \
-                                                   k_splits, split_stride, status, g_num_sms, stream, gate, pdl); \
+                                                   k_splits, split_stride, status, g_num_sms, stream, gate, pdl, a_rows); \
     break;
   switch (bn) {
     RPEG_GEMM_CASE(256)
@@ -577,7 +595,7 @@ extern "C" int rpeg_gemm_swiglu(const void* A, const void* W, void* C, int M, in
   }
   const int tiles = ((M + BM - 1) / BM) * (f / 128);
   const int grid = tiles < g_num_sms ? tiles : g_num_sms;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, f, K, ldc, 0, 1, 0, status, WeightGate{nullptr, 0, 0u, 0ull}, 0);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, C, M, f, K, ldc, 0, 1, 0, status, WeightGate{nullptr, 0, 0u, 0ull}, 0, BM);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
@@ -623,18 +641,19 @@ extern "C" int rpeg_gemm_bf16_partials(const void* A, const void* B, int M, int 
   const int k_splits = (num_kb + kb_per - 1) / kb_per;
   *k_splits_out = k_splits;
   CUtensorMap ta, tb;
-  int rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, BM);
+  const int a_rows = a_box_rows(M, 0);
+  int rc = make_tmap_bf16_2d(&ta, A, K, M, lda, BK, a_rows);
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
   if (rc) return rc - 100;
   switch (bn) {
     case 256: return launch_gemm<256, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
-                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled());
+                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
     case 128: return launch_gemm<128, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
-                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled());
+                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
     case 64: return launch_gemm<64, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
-                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled());
+                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
     default: return launch_gemm<32, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
-                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled());
+                                                             WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
   }
 }

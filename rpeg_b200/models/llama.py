@@ -175,6 +175,9 @@ class LlamaModel:
             raise ValueError("the attention kernels are specialised for head_dim = 128")
         if recompute not in ("full", "none"):
             raise ValueError("recompute must be 'full' or 'none'")
+        # with recompute == "full": the activations of the LAST `keep_layers` layers are kept all the same (as much of the
+        # second forward pass is skipped as the memory left on the GPU pays for; the backward pass frees those first)
+        self.keep_layers = 0
         self.cfg = cfg
         self.device = torch.device(device)
         self.layout = ParamLayout(cfg, stage)
@@ -259,20 +262,21 @@ class LlamaModel:
         returns ``(h1, dn)`` with the layer output being ``h1 + dn`` (the add is fused into the next
         RMSNorm)."""
         cfg, p = self.cfg, self.p
+        keep_acts = keep and (self.recompute == "none" or i >= self.layer_hi - self.keep_layers)
         if delta is None:
             h = res
             x, rstd1, _ = K.rmsnorm_fwd(h, p[f"l{i}.attn_norm"], cfg.rms_eps)
         else:
             x, rstd1, h = K.rmsnorm_fwd(delta, p[f"l{i}.attn_norm"], cfg.rms_eps, residual=res, want_sum=True)
         qkv = K.gemm(x, p[f"l{i}.wqkv"], gate=gate)
-        qkn = self._qk_norm(i, qkv, keep and self.recompute == "none") if cfg.qk_norm else None
+        qkn = self._qk_norm(i, qkv, keep_acts) if cfg.qk_norm else None
         K.rope_(qkv, ctx.pos, self.cos_t, self.sin_t, 0, cfg.n_heads, cfg.head_dim)
         K.rope_(qkv, ctx.pos, self.cos_t, self.sin_t, cfg.q_width, cfg.n_kv_heads, cfg.head_dim)
         attn, lse = K.flash_attn_fwd(qkv, 0, cfg.q_width, cfg.q_width + cfg.kv_width, ctx.cu_seqlens, ctx.max_seqlen,
                                      cfg.n_heads, cfg.n_kv_heads, cfg.head_dim)
         o = K.gemm(attn, p[f"l{i}.wo"])
         x2, rstd2, h1 = K.rmsnorm_fwd(o, p[f"l{i}.mlp_norm"], cfg.rms_eps, residual=h, want_sum=True)
-        if (keep and self.recompute == "none") or cfg.d_ff % 128:
+        if keep_acts or cfg.d_ff % 128:
             gu = K.gemm(x2, p[f"l{i}.w_gate_up"])          # the backward pass wants the pre-activation
             act = K.swiglu_fwd(gu)
         else:
@@ -281,7 +285,7 @@ class LlamaModel:
         dn = K.gemm(act, p[f"l{i}.w_down"])
         if keep:
             saved = None
-            if self.recompute == "none":
+            if keep_acts:
                 saved = dict(x=x, rstd1=rstd1, qkv=qkv, attn=attn, lse=lse, h1=h1, x2=x2, rstd2=rstd2, gu=gu, act=act, qkn=qkn)
             ctx.layers.append(_LayerCtx(h_in=h, saved=saved))
         return h1, dn, qkv

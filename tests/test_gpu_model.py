@@ -58,12 +58,15 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
-@pytest.mark.parametrize("recompute,variant", [("full", "llama"), ("none", "llama"), ("full", "qwen3"), ("none", "qwen3")])
+@pytest.mark.parametrize("recompute,variant", [("full", "llama"), ("none", "llama"), ("full", "qwen3"), ("none", "qwen3"),
+                                               ("keep the last layer", "llama"), ("keep the last layer", "qwen3")])
 def test_forward_backward_matches_pytorch(cuda_device, recompute, variant):
     torch.manual_seed(0)
     cfg = LlamaConfig.tiny() if variant == "llama" else LlamaConfig.tiny(
         d_model=512, n_heads=4, n_kv_heads=2, qk_norm=True, tie_embeddings=True, rope_scaling_factor=8.0, rms_eps=1e-6, family="qwen3")
-    model = LlamaModel(cfg, cuda_device, trainable=True, recompute=recompute, seed=1)
+    model = LlamaModel(cfg, cuda_device, trainable=True, recompute="full" if recompute.startswith("keep") else recompute, seed=1)
+    if recompute.startswith("keep"):
+        model.keep_layers = 1          # layer 1 keeps its activations, layer 0 is recomputed from its input
     lens = [37, 130, 200]
     T = sum(lens)
     tokens = torch.randint(0, cfg.vocab, (T,), device=cuda_device, dtype=torch.int32)
