@@ -197,10 +197,12 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
                          const __nv_bfloat16* __restrict__ kcache, const __nv_bfloat16* __restrict__ vcache,
                          const int* __restrict__ page_table, int max_pages, const int* __restrict__ seq_lens,
                          __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int H, int Hkv,
-                         int nsplit, float scale_log2, const int* __restrict__ row_key0, int slot_base, int nslots) {
+                         int nsplit, float scale_log2, const int* __restrict__ row_key0, int slot_base, int nslots,
+                         int* __restrict__ arrive) {
   griddep_launch();
   griddep_wait();   // may have been scheduled under the previous kernel's tail: nothing is read or written before this
   __shared__ float red_m[4], red_l[4];
+  __shared__ int is_last;
   __shared__ __align__(16) float red_o[4][HD];
   const int h = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int hk = h / (H / Hkv);
@@ -311,6 +313,47 @@ paged_decode_attn_kernel(const __nv_bfloat16* __restrict__ q, int ldq, int q_col
       }
     }
   }
+  // Combine without a second kernel: the splits of a (row, head) count their arrivals; the last one merges all
+  // partials (they are in L2 by then) and puts the counter back to zero for the next launch.
+  if (arrive != nullptr && nslots > 1) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = (atomicAdd(&arrive[b * H + h], 1) == nsplit - 1) ? 1 : 0;
+    __syncthreads();
+    if (is_last) {
+      if (threadIdx.x == 0) arrive[b * H + h] = 0;
+      __threadfence();
+      const float* pp = partial + (static_cast<size_t>(b) * H + h) * nslots * (HD + 2);
+      float gm = -INFINITY;
+      for (int s = 0; s < nslots; ++s) gm = fmaxf(gm, __ldcg(pp + s * (HD + 2) + HD));
+      float gl = 0.f, o = 0.f;
+      for (int s = 0; s < nslots; ++s) {
+        const float ms = __ldcg(pp + s * (HD + 2) + HD);
+        const float a = (ms == -INFINITY) ? 0.f : exp2f(ms - gm);
+        gl += __ldcg(pp + s * (HD + 2) + HD + 1) * a;
+        o += __ldcg(pp + s * (HD + 2) + threadIdx.x) * a;
+      }
+      out[(static_cast<size_t>(b) * H + h) * HD + threadIdx.x] = __float2bfloat16(gl > 0.f ? o / gl : 0.f);
+    }
+  }
+}
+
+// Arrival counters of the fused combine, one per (row, head); zero between launches. One split-KV decode attention
+// launch at a time per GPU may use them (the kernels of a decode step run in stream order); larger batches and
+// RPEG_DECODE_FUSED_COMBINE=0 use the separate combine kernel.
+constexpr int ARRIVE_SLOTS = 1 << 16;
+__device__ int g_decode_arrive[ARRIVE_SLOTS];
+
+static int* fused_combine_counters(int B, int H) {
+  static int on = -1;
+  static int* ptr = nullptr;
+  if (on < 0) {
+    const char* e = getenv("RPEG_DECODE_FUSED_COMBINE");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (!on || static_cast<long long>(B) * H > ARRIVE_SLOTS) return nullptr;
+  if (ptr == nullptr && cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_arrive) != cudaSuccess) return nullptr;
+  return ptr;
 }
 
 // Shared prompt pages: the K samples of one prompt alias the prompt's KV pages, so their queries can be scored
@@ -819,11 +862,12 @@ extern "C" int rpeg_paged_decode_attn(const void* q, int ldq, int q_col0, const 
   if (nsplit > 1 && scratch == nullptr) return -4;
   if (B <= 0) return 0;
   const float scale_log2 = scale * 1.4426950408889634f;
+  int* arrive = nsplit > 1 ? fused_combine_counters(B, H) : nullptr;
   launch_pdl(paged_decode_attn_kernel, dim3(dim3(H, B, nsplit)), dim3(128), 0, STREAM(stream), 
       static_cast<const __nv_bfloat16*>(q), ldq, q_col0, static_cast<const __nv_bfloat16*>(kcache),
       static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages, seq_lens,
-      static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, static_cast<const int*>(nullptr), 0, nsplit);
-  if (nsplit > 1)
+      static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, static_cast<const int*>(nullptr), 0, nsplit, arrive);
+  if (nsplit > 1 && arrive == nullptr)
     launch_pdl(decode_combine_kernel, dim3(dim3(H, B)), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
   return LAUNCH_OK();
 }
@@ -844,13 +888,15 @@ extern "C" int rpeg_paged_decode_attn_grouped(const void* q, int ldq, int q_col0
   if (B <= 0) return 0;
   const float scale_log2 = scale * 1.4426950408889634f;
   const int nslots = nsplit + 1;
+  int* arrive = fused_combine_counters(B, H);
   launch_pdl(paged_decode_attn_shared_kernel, dim3(H, B), dim3(128), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(q), ldq,
              q_col0, static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages,
              group_rows, group_shared, scratch, H, Hkv, nslots, scale_log2);
   launch_pdl(paged_decode_attn_kernel, dim3(H, B, nsplit), dim3(128), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(q), ldq,
              q_col0, static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages,
-             seq_lens, static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, row_key0, 1, nslots);
-  launch_pdl(decode_combine_kernel, dim3(H, B), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nslots);
+             seq_lens, static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, row_key0, 1, nslots, arrive);
+  if (arrive == nullptr)
+    launch_pdl(decode_combine_kernel, dim3(H, B), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nslots);
   return LAUNCH_OK();
 }
 
@@ -874,6 +920,7 @@ extern "C" int rpeg_paged_decode_attn_grouped_tc(const void* q, int ldq, int q_c
   if (B <= 0) return 0;
   const float scale_log2 = scale * 1.4426950408889634f;
   const int nslots = nsplit + 1;
+  int* arrive = fused_combine_counters(B, H);
   CUtensorMap tk, tv;
   const uint64_t rows = static_cast<uint64_t>(num_pages) * Hkv * PAGE;
   int rc = make_tmap_bf16_2d(&tk, kcache, HD, rows, HD, 64, 64);
@@ -897,8 +944,9 @@ extern "C" int rpeg_paged_decode_attn_grouped_tc(const void* q, int ldq, int q_c
              nslots, scale_log2, status);
   launch_pdl(paged_decode_attn_kernel, dim3(H, B, nsplit), dim3(128), 0, STREAM(stream), static_cast<const __nv_bfloat16*>(q), ldq,
              q_col0, static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages,
-             seq_lens, static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, row_key0, 1, nslots);
-  launch_pdl(decode_combine_kernel, dim3(H, B), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nslots);
+             seq_lens, static_cast<__nv_bfloat16*>(out), scratch, H, Hkv, nsplit, scale_log2, row_key0, 1, nslots, arrive);
+  if (arrive == nullptr)
+    launch_pdl(decode_combine_kernel, dim3(H, B), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nslots);
   return LAUNCH_OK();
 }
 
@@ -948,7 +996,7 @@ extern "C" int rpeg_paged_decode_attn_static(const void* q, int ldq, int q_col0,
   launch_pdl(paged_decode_attn_kernel, dim3(dim3(H, B, nsplit)), dim3(128), 0, STREAM(stream), 
       static_cast<const __nv_bfloat16*>(q), ldq, q_col0, static_cast<const __nv_bfloat16*>(kcache),
       static_cast<const __nv_bfloat16*>(vcache), page_table, max_pages, seq_lens, static_cast<__nv_bfloat16*>(out),
-      scratch, H, Hkv, nsplit, scale_log2, static_cast<const int*>(nullptr), 0, nsplit);
+      scratch, H, Hkv, nsplit, scale_log2, static_cast<const int*>(nullptr), 0, nsplit, static_cast<int*>(nullptr));
   if (nsplit > 1)
     launch_pdl(decode_combine_kernel, dim3(dim3(H, B)), dim3(HD), 0, STREAM(stream), scratch, static_cast<__nv_bfloat16*>(out), H, nsplit);
   return cudaGetLastError() == cudaSuccess ? 0 : RPEG_STATIC_ERR_LAUNCH;
