@@ -29,9 +29,13 @@ constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int GEMM_THREADS = 192;
 constexpr int SMEM_BUDGET = 227 * 1024 - 2048;
 
-template <int BN>
+// AR: rows of the A tile that exist in shared memory. 128, or 32 for the decode GEMMs of up to 32 rows: the stage then
+// holds 4 KB of activations instead of 16 KB and the ring gets deeper (6 stages of 256-wide weight tiles instead of 4:
+// half as many weight bytes again in flight per SM). The MMA still addresses 128 rows; rows 32..127 alias the weight
+// tile behind the activations and produce accumulator rows that the epilogue never stores.
+template <int BN, int AR = BM>
 struct GemmCfg {
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_BYTES = AR * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
@@ -56,12 +60,12 @@ struct WeightGate {
   unsigned long long timeout_ns;
 };
 
-template <int BN, int EPI, bool A_MN, bool B_MN>
+template <int BN, int EPI, bool A_MN, bool B_MN, int AR = BM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          void* __restrict__ Cout, int M, int N, int K, int ldc, int accumulate, int k_splits,
                          long long split_stride, int* status, WeightGate gate, int pdl, int a_rows) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, AR>;
   // K-major A with few rows (decode): the TMA box covers only `a_rows` rows of the 128-row A tile. The MMA still reads
   // 128 rows; what it computes from the rows nobody loaded lands in accumulator rows that the epilogue never stores.
   const uint32_t stage_tx = static_cast<uint32_t>(Cfg::B_BYTES + (A_MN ? Cfg::A_BYTES : a_rows * BK * 2));
@@ -376,12 +380,12 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
-template <int BN, int EPI, bool A_MN, bool B_MN>
+template <int BN, int EPI, bool A_MN, bool B_MN, int AR = BM>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, int M, int N, int K, int ldc,
                        int accumulate, int k_splits, long long split_stride, int* status, int num_sms,
                        cudaStream_t stream, WeightGate gate = WeightGate{nullptr, 0, 0u, 0ull}, int pdl = 0, int a_rows = BM) {
-  using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, A_MN, B_MN>;
+  using Cfg = GemmCfg<BN, AR>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, EPI, A_MN, B_MN, AR>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -646,6 +650,18 @@ extern "C" int rpeg_gemm_bf16_partials(const void* A, const void* B, int M, int 
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
   if (rc) return rc - 100;
+  // up to 32 rows: the variant whose stages hold 32 activation rows (a deeper ring of weight tiles)
+  static int deep = -1;
+  if (deep < 0) {
+    const char* e = getenv("RPEG_GEMM_DEEP_RING");
+    deep = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (deep && a_rows == 32 && bn == 256)
+    return launch_gemm<256, EPI_F32, false, false, 32>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
+                                                       WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
+  if (deep && a_rows == 32 && bn == 128)
+    return launch_gemm<128, EPI_F32, false, false, 32>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
+                                                       WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
   switch (bn) {
     case 256: return launch_gemm<256, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
                                                              WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);

@@ -341,6 +341,27 @@ def flash_fwd_programs(n_tiles: int, rescale: Sequence[int] = (), *, pv_barriers
     return [mma, pipe, warp]
 
 
+def one_shot_allreduce_programs(world: int, calls: int, *, slot_sets: int = 2) -> List[Program]:
+    """The one-exchange all-reduce of the tensor-parallel decode step (``csrc/tp_decode.cu``,
+    ``tp_allreduce_rmsnorm_ll_kernel``): in call k every rank stores its units {data, k} into its own slot of set
+    ``k % slot_sets`` in EVERY rank's region, then polls the slots of all senders in its own region until their units carry
+    k, and reduces them. No flag follows the data and nothing is acknowledged: what keeps a sender from overwriting units
+    that a slow receiver has not read yet is only that it cannot finish call k + 1 before that receiver has sent its own
+    units of call k + 1, i.e. has finished reading call k. Two slot sets are therefore enough, one is not."""
+    progs: List[Program] = []
+    for r in range(world):
+        p: Program = []
+        for k in range(1, calls + 1):
+            s = k % slot_sets
+            for t in range(world):
+                p.append(("store", ("ll", t, s, r), k))                 # a unit is one atomic 8-byte store
+            for sender in range(world):
+                p.append(("wait", ("ll", r, s, sender), k))
+                p.append(("expect", ("ll", r, s, sender), k, f"reduces rank {sender}'s units of call {k}"))
+        progs.append(p)
+    return progs
+
+
 def check_all(verbose: bool = False) -> List[Result]:
     """Every protocol as the host code runs it; all must come out clean."""
     out: List[Result] = []
@@ -352,6 +373,8 @@ def check_all(verbose: bool = False) -> List[Result]:
     out.append(explore("gemm + all-reduce, 2 ranks x 4 calls", gemm_rs_programs(2, 4, all_reduce=True)))
     out.append(explore("all-gather + gemm, 2 ranks x 4 calls", ag_gemm_programs(2, 4)))
     out.append(explore("all-gather + gemm, 3 ranks x 3 calls", ag_gemm_programs(3, 3)))
+    out.append(explore("one-exchange all-reduce, 2 ranks x 5 calls", one_shot_allreduce_programs(2, 5)))
+    out.append(explore("one-exchange all-reduce, 3 ranks x 3 calls", one_shot_allreduce_programs(3, 3)))
     for tau in (0, 1, 2):
         progs, init = staleness_programs(tau, 5 + tau)
         out.append(explore(f"staleness {tau}, 1 generator + 1 trainer", progs, init))

@@ -569,6 +569,24 @@ def test_headnorm_fwd_bwd(cuda_device):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M,N,Kd", [(8, 4096, 1376), (24, 4096, 512), (40, 1536, 4096), (130, 2752, 4096), (256, 4096, 1376)])
+def test_skinny_gemms_of_a_tensor_parallel_shard(cuda_device, M, N, Kd):
+    """The shapes one of 8 tensor-parallel ranks works on: a contraction that is not a multiple of the 64-wide k-block
+    (1376 = 11008 / 8, the last block is filled with zeros by TMA), every activation tile height (32, 64, 128 rows and two
+    tiles), as split-K partials and as a plain GEMM, against fp32 PyTorch."""
+    torch.manual_seed(M + N)
+    ws = torch.empty(8 * 1024 * 1024, dtype=torch.float32, device=cuda_device)
+    a = torch.randn(M, Kd, device=cuda_device).bfloat16()
+    w = (torch.randn(N, Kd, device=cuda_device) * 0.05).bfloat16()
+    want = a.float() @ w.float().t()
+    parts = K.gemm_partials(a, w, ws)
+    assert _rel_err(parts.reduce(), want) < 1e-2
+    assert _rel_err(K.gemm(a, w, bn=128, chain=True), want) < 1e-2
+    assert _rel_err(K.gemm(a, w, workspace=ws), want) < 1e-2
+    K.check_status()
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("M", [3, 32, 200])
 def test_split_k_partials_and_their_consumers(cuda_device, M):
     d, f, H, Hkv, hd = 1024, 1408, 8, 4, 128

@@ -180,3 +180,12 @@ def test_flash_forward_pipeline_needs_one_completion_barrier_per_buffer():
     assert early.finding is not None and early.finding.kind == "race" and "P*V" in early.finding.message
     for n, resc in ((1, ()), (2, (1,)), (4, ()), (5, (1, 3)), (6, (2, 3, 5)), (7, (6,))):
         assert explore(f"{n} tiles", flash_fwd_programs(n, resc)).ok, (n, resc)
+
+
+def test_one_exchange_allreduce_needs_two_slot_sets():
+    """The all-reduce that pushes self-validating units and never acknowledges them: clean with the two slot sets the
+    kernel alternates between, and the checker finds the overwritten units when there is only one."""
+    for world, calls in ((2, 5), (3, 3)):
+        assert pc.explore("two sets", pc.one_shot_allreduce_programs(world, calls)).ok
+        bad = pc.explore("one set", pc.one_shot_allreduce_programs(world, calls, slot_sets=1))
+        assert not bad.ok and bad.finding.kind == "race" and "units of call" in bad.finding.message
