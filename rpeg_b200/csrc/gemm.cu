@@ -29,10 +29,9 @@ constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int GEMM_THREADS = 192;
 constexpr int SMEM_BUDGET = 227 * 1024 - 2048;
 
-// AR: rows of the A tile that exist in shared memory. 128, or 32 for the decode GEMMs of up to 32 rows: the stage then
-// holds 4 KB of activations instead of 16 KB and the ring gets deeper (6 stages of 256-wide weight tiles instead of 4:
-// half as many weight bytes again in flight per SM). The MMA still addresses 128 rows; rows 32..127 alias the weight
-// tile behind the activations and produce accumulator rows that the epilogue never stores.
+// AR: rows of the A tile that exist in shared memory (128 in every instantiation in use). A variant with AR = 32 for
+// decode GEMMs of up to 32 rows (6 stages of 256-wide weight tiles instead of 4) measured 5 % SLOWER per decode step:
+// the streaming rate of the skinny GEMMs is not limited by the bytes in flight per SM.
 template <int BN, int AR = BM>
 struct GemmCfg {
   static constexpr int A_BYTES = AR * BK * 2;
@@ -650,18 +649,6 @@ extern "C" int rpeg_gemm_bf16_partials(const void* A, const void* B, int M, int 
   if (rc) return rc;
   rc = make_tmap_bf16_2d(&tb, B, K, N, ldb, BK, bn);
   if (rc) return rc - 100;
-  // up to 32 rows: the variant whose stages hold 32 activation rows (a deeper ring of weight tiles)
-  static int deep = -1;
-  if (deep < 0) {
-    const char* e = getenv("RPEG_GEMM_DEEP_RING");
-    deep = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  if (deep && a_rows == 32 && bn == 256)
-    return launch_gemm<256, EPI_F32, false, false, 32>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
-                                                       WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
-  if (deep && a_rows == 32 && bn == 128)
-    return launch_gemm<128, EPI_F32, false, false, 32>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
-                                                       WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
   switch (bn) {
     case 256: return launch_gemm<256, EPI_F32, false, false>(ta, tb, workspace, M, N, K, N, 0, k_splits, per_split, status, g_num_sms, stream,
                                                              WeightGate{nullptr, 0, 0u, 0ull}, pdl_enabled(), a_rows);
