@@ -421,7 +421,8 @@ def main() -> None:
             extra["reshard_us"] = float(reshard)
         try:
             from rpeg_b200.analytic.predict import predict_step_seconds
-            pred = predict_step_seconds(spec, world, parallelism=line["config"]["parallelism"])
+            frac = 0.0 if recompute == "none" else (1.0 if not keep_layers else max(0.0, 1.0 - keep_layers / cfg.n_layers))
+            pred = predict_step_seconds(spec, world, parallelism=line["config"]["parallelism"], recompute_fraction=frac)
             meas = line["ms_per_step"] / 1e3
             extra["cost_model"] = {"predicted_s": pred["step_s"], "measured_s": meas, "err": (pred["step_s"] - meas) / meas,
                                    "phases_s": pred.get("phases_s"), "hardware": pred.get("hardware")}

@@ -75,7 +75,7 @@ class NodeCostModel:
     suite: ModelSuite
     workload: Workload
     optimizer_stage: int = 2
-    activation_checkpointing: bool = True
+    activation_checkpointing: float = True      # True / False, or the FRACTION of the layers whose forward pass runs a second time
 
     def __post_init__(self):
         if self.optimizer_stage not in (0, 1, 2):
@@ -159,7 +159,7 @@ class NodeCostModel:
                 return n * seq * trunk + n * 2 * sh.d
             return n * seq * (trunk + 2 * _HEAD_FLOPS[model](sh.V, sh.d))
         if role is Role.TRAINING:
-            mult = 4 if self.activation_checkpointing else 3
+            mult = 3 + float(self.activation_checkpointing)
             head = {Model.ACTOR: 2 * sh.V * sh.d, Model.CRITIC: 2 * sh.d, Model.AC_SHARE: 2 * sh.V * sh.d + 2 * sh.d}
             if model in head:
                 return mult * BK * seq * (trunk + head[model])
@@ -231,6 +231,18 @@ class NodeCostModel:
         flops = tok * (2 * Lpp / pt) * sh.layer_flops_per_token(w.S) + prompt_rows * 2 * sh.V * sh.d / pt
         t_total = flops / (hw.flops_per_gpu * hw.sustained_flops_fraction * max(eta, 1e-6))
         cap = self._gen_concurrency(node, rows, w.S + self._mean_len() / 2.0)
+
+        def step_overhead(live_rows: float) -> float:
+            """What one decode step costs beyond its bytes at the memory rate: a constant (launch of the step's graph,
+            sampling, bookkeeping), the latency of every layer's chain of dependent kernels, the per-row work of the
+            element-wise kernels, and under tensor parallelism the two all-reduce launches per layer (one exchange
+            while rows x ranks <= 256, reduce-scatter + all-gather above)."""
+            t = hw.decode_step_overhead_s + Lpp * (hw.decode_layer_chain_s + hw.decode_row_layer_s * live_rows)
+            if pt > 1 and hw.tp_decode_allreduce_s > 0:
+                small = hw.tp_decode_allreduce_small_s > 0 and live_rows * pt <= 256
+                t += 2 * Lpp * (hw.tp_decode_allreduce_small_s if small else hw.tp_decode_allreduce_s)
+            return t
+
         backlog = 0.0                                                   # row-steps that waited for a free slot
         live_frac = 1.0
         sub = 32
@@ -249,12 +261,12 @@ class NodeCostModel:
                     run = live + extra
                 ctx = w.S * share + t_mid
                 step_bytes = w_bytes / e_w + run * kv_tok * ctx / e_kv + 2 * run * sh.d * Lpp * sh.sb
-                t_total += dt * (step_bytes / bw + hw.decode_step_overhead_s)
+                t_total += dt * (step_bytes / bw + step_overhead(run))
             live_frac -= frac
         if backlog > 0:                                                 # the rows that waited run on after the others
             ctx = w.S * share + self._mean_len() / 2.0
             step_bytes = w_bytes / e_w + cap * kv_tok * ctx / e_kv
-            t_total += backlog / cap * (step_bytes / bw + hw.decode_step_overhead_s)
+            t_total += backlog / cap * (step_bytes / bw + step_overhead(cap))
         return t_total
 
     def _gen_concurrency(self, node: ExecNode, b: float, past: float) -> float:
@@ -290,7 +302,7 @@ class NodeCostModel:
             return extra
         seq = self._seq_len(node)
         n = node.n_seqs if node.n_seqs is not None else w.B * w.K
-        mult = 1.0 if node.role is Role.INFERENCE else (4.0 if self.activation_checkpointing else 3.0)
+        mult = 1.0 if node.role is Role.INFERENCE else (3.0 + float(self.activation_checkpointing))
         if hw.attention_flops_eff < 1.0:
             att = mult * n * seq * 2 * sh.L * seq * sh.d
             extra += att / (P * hw.flops_per_gpu * hw.sustained_flops_fraction) * (1.0 / hw.attention_flops_eff - 1.0)
@@ -361,7 +373,7 @@ class NodeCostModel:
         ideal = Lpp * (hw.non_gemm_constant + hw.non_gemm_scaling) / pt
         extra = (at_tp - ideal) * scale
         if node.role is Role.TRAINING:
-            extra *= 4 if self.activation_checkpointing else 3
+            extra *= 3 + float(self.activation_checkpointing)
         return max(0.0, extra)
 
     # ------------------------------------------------------------------ communication
@@ -426,8 +438,12 @@ class NodeCostModel:
                 if node.is_prefill_phase:
                     cost += pp_p2p(act(n, S), m + pp - 2) + 2 * Lpp * m * tp_allreduce(act(n, S))
                 return cost + pp_p2p(act(n, 1), steps * (m + pp - 2)) + 2 * steps * Lpp * m * tp_allreduce(act(n, 1))
+            # with length quantiles and a measured launch time, the decode steps' all-reduces are counted step by step
+            # (few rows: one exchange; many: two phases) in _generation_time_by_lengths
+            by_steps = pt > 1 and hw.tp_decode_allreduce_s > 0 and hw.expected_lengths > 0 and self._length_bins() is not None
+            decode_ar = 0.0 if by_steps else 2 * (T - 1) * Lpp * m * tp_allreduce(act(BK, 1))
             return (pp_p2p(act(BK, S), m + pp - 2) + pp_p2p(act(BK, 1), (T - 1) * (m + pp - 2))
-                    + 2 * Lpp * m * tp_allreduce(act(BK, S)) + 2 * (T - 1) * Lpp * m * tp_allreduce(act(BK, 1)))
+                    + 2 * Lpp * m * tp_allreduce(act(BK, S)) + decode_ar)
         if role is Role.INFERENCE:
             n = node.n_seqs if node.n_seqs is not None else BK
             return pp_p2p(act(n, S + T), m + pp - 2) + 2 * Lpp * m * tp_allreduce(act(n, S + T))
@@ -443,7 +459,7 @@ class NodeCostModel:
                 dp = self._collective(Collective.REDUCESCATTER, msg, allocs, pd) + self._collective(Collective.ALLGATHER, msg, allocs, pd)
             if hw.fabric == "nvswitch":
                 dp *= hide
-            n_coll = 6 if self.activation_checkpointing else 4
+            n_coll = 4 + 2 * float(self.activation_checkpointing)
             return dp + pp_p2p(act(BK, S + T), m + 2 * pp - 3) + n_coll * Lpp * m * tp_allreduce(act(BK, S + T))
         raise ValueError(f"no communication model for role={role} model={model}")
 

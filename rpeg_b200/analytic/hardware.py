@@ -66,6 +66,12 @@ class Hardware:
     tp_decode_allreduce_s: float = 0.0         # > 0: measured time of ONE fused all-reduce + residual + RMSNorm launch of the
     #                                            tensor-parallel decode step (latency bound: two flag exchanges and a switch
     #                                            round trip); replaces the alpha-beta estimate for decode-sized messages
+    tp_decode_allreduce_small_s: float = 0.0   # > 0: the same for rows x ranks <= 256, where the launch is ONE exchange
+    #                                            (self-validating units pushed to every rank, reduced locally)
+    decode_layer_chain_s: float = 0.0          # per decode step and layer: latency of the chain of dependent kernels of a
+    #                                            layer (what a step costs beyond its bytes at the copy rate, at any batch)
+    decode_row_layer_s: float = 0.0            # per decode step, layer and live row: the per-row work of the element-wise
+    #                                            kernels and of the GEMMs' second activation tile
     dp_reduce_gbs: float = 0.0                 # > 0: measured rate (GB/s of gradient bytes entering a rank) of the fused
     #                                            data-parallel gradient reduction; reported by calibrate.py
     expected_lengths: float = 0.0              # > 0: unsplit vertices are priced with the workload's length quantiles

@@ -22,7 +22,7 @@ _SHAPES = {
 
 
 def bench_job_mapping(spec: Dict[str, Any], n_gpus: int, *, gen_slots: int = 256, kv_budget_bytes: float = 56e9,
-                      micro_tokens: int = 16384, hw_file: Optional[str] = None) -> Dict[str, Any]:
+                      micro_tokens: int = 16384, hw_file: Optional[str] = None, recompute_fraction: float = 1.0) -> Dict[str, Any]:
     """The benchmark configuration as a planner job mapping (the keys of ``runtime.job_plan`` job files)."""
     algo = {"grpo_async": "grpo"}.get(spec["algo"], spec["algo"])
     hw_path = Path(hw_file) if hw_file else _ROOT / "configs" / "hw_b200_measured.yaml"
@@ -41,14 +41,15 @@ def bench_job_mapping(spec: Dict[str, Any], n_gpus: int, *, gen_slots: int = 256
         workload["gen_quantiles"] = [list(q) for q in spec["quantiles"]]
     return {"run_id": "bench-prediction", "policy": {"algorithm": algo}, "hardware": hardware,
             "device_space": {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": int(n_gpus)}, "models": models, "workload": workload,
-            "optimizer": {"k_eval": 1}, "optimizer_runtime": {"distributed_optimizer": "zero1", "activation_checkpointing": True},
+            "optimizer": {"k_eval": 1}, "optimizer_runtime": {"distributed_optimizer": "zero1", "activation_checkpointing": float(recompute_fraction)},
             "runtime_hardware": {"worker_overhead_bytes": 2 ** 30, "memory_reserve_fraction": 0.02,
                                  "kv_cache_budget_bytes": float(kv_budget_bytes), "activation_token_cap": int(micro_tokens)},
             "runtime": {"default_backend": "engine", "gen_slots": int(gen_slots), "micro_tokens": int(micro_tokens)}}
 
 
 def predict_step_seconds(spec: Dict[str, Any], n_gpus: int, *, parallelism: str = "", hw_file: Optional[str] = None,
-                         gen_slots: int = 256) -> Dict[str, Any]:
+                         gen_slots: int = 256, recompute_fraction: float = 1.0) -> Dict[str, Any]:
+    """``recompute_fraction``: share of the layers whose forward pass runs again in the backward pass (1 = all)."""
     from ..core.types import Allocation, Role
     from ..ir.plan import ExecutionPlan
     from ..ir.templates import build_rpeg
@@ -56,7 +57,7 @@ def predict_step_seconds(spec: Dict[str, Any], n_gpus: int, *, parallelism: str 
     from ..runtime import job_plan as J
     from ..search.evaluate import Configuration
 
-    cfg = bench_job_mapping(spec, n_gpus, gen_slots=gen_slots, hw_file=hw_file)
+    cfg = bench_job_mapping(spec, n_gpus, gen_slots=gen_slots, hw_file=hw_file, recompute_fraction=recompute_fraction)
     base = _ROOT / "configs"
     space, hw, suite = J.job_device_space(cfg), J.job_hardware(cfg, base), J.job_suite(cfg)
     workload, policy = J.job_workload(cfg, base), J.job_memory_policy(cfg)

@@ -162,11 +162,19 @@ def job_suite(cfg: dict) -> ModelSuite:
     return ModelSuite(specs)
 
 
+def _checkpointing(value):
+    """True / False, or a number in (0, 1): the fraction of the layers that are recomputed in the backward pass."""
+    if isinstance(value, (int, float)) and not isinstance(value, bool):
+        v = min(1.0, max(0.0, float(value)))
+        return bool(v) if v in (0.0, 1.0) else v
+    return bool(value)
+
+
 def job_memory_policy(cfg: dict) -> MemoryPolicy:
     opt_rt, opt, rh = cfg.get("optimizer_runtime") or {}, cfg.get("optimizer") or {}, cfg.get("runtime_hardware") or {}
     return MemoryPolicy(
         optimizer_stage=optimizer_stage(str(opt_rt.get("distributed_optimizer", "zero1"))),
-        activation_checkpointing=bool(opt_rt.get("activation_checkpointing", True)),
+        activation_checkpointing=_checkpointing(opt_rt.get("activation_checkpointing", True)),
         runtime_overhead_fraction=float(opt.get("memory_reserve_fraction", rh.get("memory_reserve_fraction", 0.10))),
         worker_overhead_bytes=float(rh.get("worker_overhead_bytes", 10 * 1024 ** 3)),
         semantic_activation_cache_bytes=float(rh.get("semantic_activation_cache_bytes", 0)),
