@@ -151,13 +151,25 @@ def torch_arm(*, algo: str, model: Dict[str, int], prompts: int, samples_per_pro
     (workdir / "job.yaml").write_text(yaml.safe_dump(job, sort_keys=False))
     env = _env()
     out_dir = workdir / "job"
-    res = subprocess.run([sys.executable, "-m", "runtime.job_plan", "--config", str(workdir / "job.yaml"), "--out-dir", str(out_dir)],
-                         cwd=str(REF), env=env, capture_output=True, text=True, timeout=timeout_s)
+    deadline = time.perf_counter() + timeout_s
+
+    def left() -> float:
+        return max(5.0, deadline - time.perf_counter())
+
+    try:
+        res = subprocess.run([sys.executable, "-m", "runtime.job_plan", "--config", str(workdir / "job.yaml"), "--out-dir", str(out_dir)],
+                             cwd=str(REF), env=env, capture_output=True, text=True, timeout=left())
+    except subprocess.TimeoutExpired as exc:
+        raise ReferenceUnavailable(f"reference runtime.job_plan did not finish within {timeout_s:.0f} s") from exc
     if res.returncode != 0 or not (out_dir / "run.yaml").exists():
         raise ReferenceUnavailable(f"reference runtime.job_plan exited {res.returncode}: {_tail(res.stderr or res.stdout)}")
     t0 = time.perf_counter()
-    res = subprocess.run([sys.executable, "-m", "runtime.run", "--config", str(out_dir / "run.yaml")], cwd=str(REF), env=env,
-                         capture_output=True, text=True, timeout=timeout_s)
+    try:
+        res = subprocess.run([sys.executable, "-m", "runtime.run", "--config", str(out_dir / "run.yaml")], cwd=str(REF), env=env,
+                             capture_output=True, text=True, timeout=left())
+    except subprocess.TimeoutExpired as exc:
+        raise ReferenceUnavailable(f"reference runtime.run (torch_grpo backend, 1 GPU) did not finish {total} step(s) of this configuration "
+                                   f"within the {timeout_s:.0f} s given to the reference arm") from exc
     wall = time.perf_counter() - t0
     if res.returncode != 0:
         raise ReferenceUnavailable(f"reference runtime.run (torch_grpo backend, 1 GPU) exited {res.returncode}: {_tail(res.stderr or res.stdout)}")

@@ -86,9 +86,14 @@ def reference_arm(args, spec, world: int) -> dict:
                                           "(RPEG/runtime/algorithms/ppo_graph.py:950-963)"}
         import tempfile
         work = Path(tempfile.mkdtemp(prefix="rpeg_ref_arm_"))
-        r = ref_arm.torch_arm(algo=spec["algo"], model=MODEL_SHAPES[spec["model"]], prompts=spec["prompts"], samples_per_prompt=spec["k"],
-                              prompt_len=spec["prompt_len"], max_new=spec["max_new"], quantiles=spec["quantiles"], steps=max(1, min(args.steps, 3)),
-                              warmup=min(args.warmup, 1), workdir=work)
+        try:
+            r = ref_arm.torch_arm(algo=spec["algo"], model=MODEL_SHAPES[spec["model"]], prompts=spec["prompts"], samples_per_prompt=spec["k"],
+                                  prompt_len=spec["prompt_len"], max_new=spec["max_new"], quantiles=spec["quantiles"],
+                                  steps=max(1, min(args.steps, 3)), warmup=min(args.warmup, 1), workdir=work,
+                                  timeout_s=float(args.ref_budget_s))
+        finally:
+            import shutil
+            shutil.rmtree(work, ignore_errors=True)      # the model directory written for the reference is 13.5 GB
         return {**base, "metric": "rlhf_samples_per_sec", "value": r["samples_per_s"], "unit": "samples/s", "higher_is_better": True,
                 "steps": r["steps"], "ms_per_step": 1e3 * r["seconds"] / r["steps"], "gen_tokens_per_sec": r["gen_tokens_per_s"],
                 "e2e": {"value": r["samples_per_s"], "unit": "samples/s", "note": "the reference's trace is host-timed around each node, input tokenisation and copies included"},
@@ -199,6 +204,8 @@ def main() -> None:
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV cache budget per GPU in GB (0 = pick by world size)")
     ap.add_argument("--micro-tokens", type=int, default=16384)
     ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"])
+    ap.add_argument("--ref-budget-s", type=float, default=600.0, help="--impl reference: seconds the reference's own run may take "
+                    "(writing its model directory included) before the arm reports it as unavailable")
     ap.add_argument("--gen-parallel", default="auto", choices=["auto", "dp", "tp"],
                     help="generation layout on more than one GPU: tensor parallel over all ranks (every rank decodes the whole "
                          "batch on its weight shard) or data parallel (every rank decodes its rows on the whole model); auto = tp")
