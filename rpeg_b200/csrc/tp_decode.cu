@@ -244,10 +244,14 @@ tp_allreduce_rmsnorm_ll_kernel(TpComm c, long long part_off, const float* __rest
   __shared__ float warp_ss[LL_THREADS / 32];
   griddep_launch();
   griddep_wait();
-  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;   // an earlier wait ran out: stand down
-  const bool trace = g_tp_trace_on != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+  // the three words this launch depends on are fetched together (one memory round trip, not three in a row)
+  const int poisoned = status != nullptr ? *reinterpret_cast<volatile int*>(status) : 0;
+  const unsigned calls = *reinterpret_cast<volatile unsigned*>(state + 2);
+  const int trace_on = *reinterpret_cast<volatile int*>(&g_tp_trace_on);
+  if (poisoned != 0) return;   // an earlier wait ran out: stand down
+  const bool trace = trace_on != 0 && blockIdx.x == 0 && threadIdx.x == 0;
   if (trace) g_tp_trace[0] = global_timer_ns();
-  const unsigned epoch = state[2] + 1u;
+  const unsigned epoch = calls + 1u;
   const int row = static_cast<int>(blockIdx.x);
   const int pairs = d >> 2;                                   // 16-byte stores: two units = four bf16 values
   const long long row_bytes = static_cast<long long>(d) * 4;  // d / 2 units of 8 bytes
@@ -284,6 +288,18 @@ tp_allreduce_rmsnorm_ll_kernel(TpComm c, long long part_off, const float* __rest
     }
   }
   if (trace) g_tp_trace[1] = global_timer_ns();
+  // the residual and the norm weights do not depend on the peers: their loads are in flight while the units arrive
+  uint2 res_v[NP], w_v[NP];
+#pragma unroll
+  for (int k = 0; k < NP; ++k) {
+    const int i = threadIdx.x + k * LL_THREADS;
+    res_v[k] = make_uint2(0u, 0u);
+    w_v[k] = make_uint2(0u, 0u);
+    if (i < pairs) {
+      if (res != nullptr) res_v[k] = reinterpret_cast<const uint2*>(res + static_cast<size_t>(row) * d)[i];
+      w_v[k] = reinterpret_cast<const uint2*>(w)[i];
+    }
+  }
   // ---- collect: the units of every sender validate themselves. All senders' loads of a thread are in flight
   // together; the sum runs in rank order once they are complete (the same bits on every rank).
   float v[NP][4];
@@ -326,8 +342,7 @@ tp_allreduce_rmsnorm_ll_kernel(TpComm c, long long part_off, const float* __rest
     const int i = threadIdx.x + k * LL_THREADS;
     if (i < pairs) {
       if (res != nullptr) {
-        const uint2 r = reinterpret_cast<const uint2*>(res + static_cast<size_t>(row) * d)[i];
-        const float2 f0 = unpack_bf16x2(r.x), f1 = unpack_bf16x2(r.y);
+        const float2 f0 = unpack_bf16x2(res_v[k].x), f1 = unpack_bf16x2(res_v[k].y);
         v[k][0] += f0.x; v[k][1] += f0.y; v[k][2] += f1.x; v[k][3] += f1.y;
       }
       uint2 hv;
@@ -350,8 +365,7 @@ tp_allreduce_rmsnorm_ll_kernel(TpComm c, long long part_off, const float* __rest
   for (int k = 0; k < NP; ++k) {
     const int i = threadIdx.x + k * LL_THREADS;
     if (i < pairs) {
-      const uint2 wv = reinterpret_cast<const uint2*>(w)[i];
-      const float2 b0 = unpack_bf16x2(wv.x), b1 = unpack_bf16x2(wv.y);
+      const float2 b0 = unpack_bf16x2(w_v[k].x), b1 = unpack_bf16x2(w_v[k].y);
       uint2 o;
       o.x = pack_bf16x2(v[k][0] * rstd * b0.x, v[k][1] * rstd * b0.y);
       o.y = pack_bf16x2(v[k][2] * rstd * b1.x, v[k][3] * rstd * b1.y);
