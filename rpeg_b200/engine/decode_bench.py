@@ -76,6 +76,7 @@ def main(argv=None) -> int:
             if k_share > gen.GROUP_MAX:
                 raise SystemExit(f"--group-attention handles groups of at most {gen.GROUP_MAX} rows")
             gen.group_attention = True
+            gen.group_min_batch = 0
             gen.group_tc = bool(args.group_tc)
             n_groups = n // k_share
             gen.group_rows.fill_(-1)

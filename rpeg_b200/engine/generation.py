@@ -70,6 +70,7 @@ class Generator:
     BUCKETS = (256, 192, 128, 96, 64, 48, 32, 24, 16, 8)
     PDL_MAX_BATCH = 64
     GROUP_MAX = 8              # queries the group attention kernel scores per K/V tile
+    GROUP_MIN_BATCH = 128      # the group kernel is one more launch per layer: it pays only while many rows are live
     GROUP_MIN = 3              # smaller groups are cheaper row by row
 
     @staticmethod
@@ -96,6 +97,7 @@ class Generator:
         # ``True`` / ``"cuda"``: the CUDA-core group kernel; ``"tc"``: the tcgen05 one (keys on the M axis).
         self.group_attention = bool(group_attention) and not cfg.qk_norm
         self.group_tc = str(group_attention).lower() == "tc"
+        self.group_min_batch = self.GROUP_MIN_BATCH
         self.sync_interval = max(1, sync_interval)
         self.use_graphs = use_graphs
         self.max_seq_len = max_seq_len
@@ -152,7 +154,7 @@ class Generator:
         # and costs a little once the kernels are long (+0.8 % at 128 rows and more)
         # (a tensor-parallel step is made of short kernels at every batch size: always chained)
         K.set_pdl(b <= self.PDL_MAX_BATCH or getattr(m, "tp", 1) > 1)
-        groups = (self.group_rows[:b], self.group_shared[:b], self.row_key0[:b]) if self.group_attention else None
+        groups = (self.group_rows[:b], self.group_shared[:b], self.row_key0[:b]) if (self.group_attention and b >= self.group_min_batch) else None
         K.set_group_tc(self.group_tc)
         xf = m.decode_step(self.token[:b], self.pos[:b], self.slot_ids[:b], self.seq_len[:b], self.page_table[:b],
                            self.kcache, self.vcache, nsplit=self._nsplit(b), groups=groups)

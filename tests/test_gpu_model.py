@@ -219,6 +219,7 @@ def test_generation_with_shared_prompt_pages(cuda_device, S):
     shared = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=1e9, eos_id=1, sync_interval=4)
     tight = Generator(model, max_slots=8, max_seq_len=S + T, kv_budget_bytes=14.5 * page_bytes, eos_id=1, sync_interval=4,
                       group_attention=True)
+    tight.group_min_batch = 0          # the group kernel at every batch size, not only while many rows are live
     a = plain.generate(prompts, T, seed=11, forced_lens=forced)
     b = shared.generate(prompts, T, seed=11, forced_lens=forced, group_size=Kq)
     c = tight.generate(prompts, T, seed=11, forced_lens=forced, group_size=Kq)
@@ -243,6 +244,7 @@ def test_generation_with_shared_prompt_pages(cuda_device, S):
     assert same >= N - 2, f"only {same} of {N} rows identical"
     # the group attention kernel (shared keys scored once per group) must agree with the row-by-row kernel
     grouped = Generator(model, max_slots=32, max_seq_len=S + T, kv_budget_bytes=1e9, eos_id=1, sync_interval=4, group_attention=True)
+    grouped.group_min_batch = 0
     gc = grouped.generate(prompts, 24, greedy=True, group_size=Kq)
     K.check_status()
     same = sum(int(torch.equal(ga.tokens[i], gc.tokens[i])) for i in range(N))
