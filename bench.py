@@ -293,9 +293,44 @@ def main() -> None:
             trainer = PipelineGRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo,
                                           gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2)
         else:
-            trainer = GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp,
-                                  gen_slots=slots, kv_budget_bytes=kv_gb * 1e9, recompute=recompute, seed=42, eos_id=2,
-                                  gen_tp=gen_tp, tp_comm=args.tp_comm, group_attention={"off": False, "cuda": True, "tc": "tc"}[args.group_attention])
+            def build(tp: bool, slots_: int, kv_gb_: float, dp_):
+                return GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp_,
+                                   gen_slots=slots_, kv_budget_bytes=kv_gb_ * 1e9, recompute=recompute, seed=42, eos_id=2,
+                                   gen_tp=tp, tp_comm=args.tp_comm,
+                                   group_attention={"off": False, "cuda": True, "tc": "tc"}[args.group_attention])
+
+            trainer = build(gen_tp, slots, kv_gb, dp)
+            if gen_tp and args.gen_parallel == "auto":
+                # Before a long run: the tensor-parallel decode step against the whole local model on a few rows (both
+                # all-reduce kernels). If any rank disagrees, or a peer does not answer within the kernels' bounded waits,
+                # all ranks fall back to data-parallel generation instead of failing the job.
+                why = None
+                try:
+                    err = trainer.gen_model.selfcheck(rows=(8, max(64, 512 // world)))
+                    if not (err < 5e-2) or os.environ.get("RPEG_BENCH_FORCE_TP_FALLBACK") == "1":
+                        why = f"decode step differs from the whole model by {err:.3g}"
+                except Exception as exc:  # noqa: BLE001
+                    why = f"{type(exc).__name__}: {exc}"
+                    K.status_word(device).zero_()
+                bad = torch.tensor([0 if why is None else 1], device=device)
+                dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+                if int(bad.item()):
+                    if rank == 0:
+                        print(f"[bench] tensor-parallel generation failed its start-up check ({why or 'on another rank'}): "
+                              "generating data parallel", file=sys.stderr, flush=True)
+                    trainer.gen_model.comm.close()
+                    del trainer
+                    import gc
+                    gc.collect()
+                    torch.cuda.empty_cache()
+                    from rpeg_b200.parallel.dp import DPContext
+                    gen_tp = False
+                    slots = args.gen_slots or min(b_local * Kk, 256)
+                    kv_gb = args.kv_gb or {1: 56.0, 2: 76.0}.get(world, 96.0)
+                    dp = DPContext(device, tag="actor2")
+                    trainer = build(False, slots, kv_gb, dp)
+                elif rank == 0:
+                    print(f"[bench] tensor-parallel start-up check: max relative difference {err:.3g}", file=sys.stderr, flush=True)
         batches = []
         for _ in range(n_iters):
             prompts = torch.randint(3, cfg.vocab, (B, S), generator=gen_host, dtype=torch.int32)

@@ -191,3 +191,38 @@ class TPDecodeModel:
             reduce_into(act, self.wdown[i], p["final_norm"] if last else p[f"l{i + 1}.attn_norm"], None if last else "h")
             xin = x
         return x
+
+    # ------------------------------------------------------------------ start-up check
+    def selfcheck(self, rows=(8, 64), steps: int = 2) -> float:
+        """Decode ``steps`` tokens for a few rows with this tensor-parallel view and with the whole local model (scratch
+        KV caches of one page per row) and return the largest relative difference of the final hidden states over all
+        ranks. ``rows`` should cover both all-reduce kernels (rows x ranks <= 256 and above). Raises what a kernel
+        reported in the status word (a peer that did not answer). Cheap enough to run once before a long job."""
+        cfg, dev = self.cfg, self.device
+        worst = 0.0
+        for B in rows:
+            B = min(int(B), self.max_batch)
+            pages = B + 1
+            i32 = dict(dtype=torch.int32, device=dev)
+            kc_f = [torch.zeros(pages, cfg.n_kv_heads, K.KV_PAGE, cfg.head_dim, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+            vc_f = [torch.zeros_like(t) for t in kc_f]
+            kc_t = [torch.zeros(pages, self.n_kv_local, K.KV_PAGE, cfg.head_dim, dtype=torch.bfloat16, device=dev) for _ in range(cfg.n_layers)]
+            vc_t = [torch.zeros_like(t) for t in kc_t]
+            table = (torch.arange(B, **i32) + 1).view(B, 1).contiguous()
+            slot_ids = torch.arange(B, **i32)
+            g = torch.Generator(device="cpu").manual_seed(1234 + B)
+            for t in range(steps):
+                tok = torch.randint(0, cfg.vocab, (B,), generator=g, dtype=torch.int32).to(dev)
+                pos = torch.full((B,), t, **i32)
+                seq = torch.full((B,), t + 1, **i32)
+                want = self.full.decode_step(tok, pos, slot_ids, seq, table, kc_f, vc_f, nsplit=1).float()
+                got = self.decode_step(tok, pos, slot_ids, seq, table, kc_t, vc_t, nsplit=1).float()
+                worst = max(worst, float(((got - want).abs().max() / want.abs().max().clamp_min(1e-6)).item()))
+            del kc_f, vc_f, kc_t, vc_t
+        K.check_status()
+        if self.tp > 1:
+            t = torch.tensor([worst], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            worst = float(t.item())
+        return worst
+

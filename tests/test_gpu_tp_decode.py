@@ -38,3 +38,15 @@ def test_bench_tiny_two_ranks_tensor_parallel_generation():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = _last_json(r.stdout)
     assert line["n_gpus"] == 2 and line["value"] > 0 and "tp2" in line["config"]["parallelism"] and line["reshard_us"] > 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_bench_falls_back_to_data_parallel_generation_when_the_start_up_check_fails(monkeypatch):
+    """``--gen-parallel auto`` checks the tensor-parallel decode step against the whole model before the run; a failed
+    check (forced here on the host, nothing faults) must leave a working data-parallel benchmark, not a failed job."""
+    monkeypatch.setenv("RPEG_BENCH_FORCE_TP_FALLBACK", "1")
+    r = _torchrun(2, 29574, "bench.py", "--config", "grpo_tiny", "--gpus", "2", "--steps", "2", "--warmup", "3")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = _last_json(r.stdout)
+    assert line["n_gpus"] == 2 and line["value"] > 0 and line["config"]["parallelism"] == "dp2", line["config"]
+    assert "generating data parallel" in r.stderr
