@@ -329,8 +329,10 @@ def main() -> None:
                     kv_gb = args.kv_gb or {1: 56.0, 2: 76.0}.get(world, 96.0)
                     dp = DPContext(device, tag="actor2")
                     trainer = build(False, slots, kv_gb, dp)
-                elif rank == 0:
-                    print(f"[bench] tensor-parallel start-up check: max relative difference {err:.3g}", file=sys.stderr, flush=True)
+                else:
+                    torch.cuda.empty_cache()          # the check's scratch KV caches go back to the driver
+                    if rank == 0:
+                        print(f"[bench] tensor-parallel start-up check: max relative difference {err:.3g}", file=sys.stderr, flush=True)
         batches = []
         for _ in range(n_iters):
             prompts = torch.randint(3, cfg.vocab, (B, S), generator=gen_host, dtype=torch.int32)
