@@ -132,21 +132,21 @@ def planner_bench(args) -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks / throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clocks / throttle reasons of the job's GPUs with ONE nvidia-smi process while the timed region runs."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index = index
+    def __init__(self, indices):
+        self.indices = [int(i) for i in (indices if isinstance(indices, (list, tuple, range)) else [indices])]
         self.proc = None
         self.lines = []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "250", "-i", ",".join(str(i) for i in self.indices)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
@@ -159,23 +159,26 @@ class ClockSampler:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
-        sm, mx, reasons = [], [], set()
+        per_gpu, mx, reasons = {}, [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for ln in self.lines:
             parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                per_gpu.setdefault(int(parts[0]), []).append(float(parts[1]))
+                mx.append(float(parts[2]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[3:7]):
+            for name, val in zip(names, parts[4:8]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        sm = sorted(v for vals in per_gpu.values() for v in vals)
+        out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+               "reasons": sorted(reasons), "samples": len(sm)}
+        if len(per_gpu) > 1:      # the slowest GPU sets the pace of a step: show every GPU's median
+            out["sm_mhz_per_gpu"] = {str(g): sorted(v)[len(v) // 2] for g, v in sorted(per_gpu.items())}
+        return out
 
 
 def draw_lengths(n: int, quantiles, gen) -> "list[int]":
@@ -546,7 +549,7 @@ def main() -> None:
     if step_s > 0.0:
         n_steps = max(1, min(args.steps, int((budget - spent) / (1.08 * step_s))))
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(list(range(world)) if world > 1 else local_rank)
     if rank == 0:
         sampler.start()
     barrier()
