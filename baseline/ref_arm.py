@@ -129,6 +129,7 @@ def torch_arm(*, algo: str, model: Dict[str, int], prompts: int, samples_per_pro
         raise ReferenceUnavailable(f"the reference arm drives the GRPO torch backend; '{algo}' is not wired")
     workdir.mkdir(parents=True, exist_ok=True)
     total = warmup + steps
+    deadline = time.perf_counter() + timeout_s          # writing the model directory counts
     model_dir = write_assets(workdir, n_prompts=prompts * total, prompt_len=prompt_len, max_pos=prompt_len + max_new + 8, **model)
     job = {
         "run_id": "ref-grpo",
@@ -151,7 +152,6 @@ def torch_arm(*, algo: str, model: Dict[str, int], prompts: int, samples_per_pro
     (workdir / "job.yaml").write_text(yaml.safe_dump(job, sort_keys=False))
     env = _env()
     out_dir = workdir / "job"
-    deadline = time.perf_counter() + timeout_s
 
     def left() -> float:
         return max(5.0, deadline - time.perf_counter())

@@ -207,7 +207,7 @@ def main() -> None:
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV cache budget per GPU in GB (0 = pick by world size)")
     ap.add_argument("--micro-tokens", type=int, default=16384)
     ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"])
-    ap.add_argument("--ref-budget-s", type=float, default=600.0, help="--impl reference: seconds the reference's own run may take "
+    ap.add_argument("--ref-budget-s", type=float, default=480.0, help="--impl reference: seconds the reference's own run may take "
                     "(writing its model directory included) before the arm reports it as unavailable")
     ap.add_argument("--gen-parallel", default="auto", choices=["auto", "dp", "tp"],
                     help="generation layout on more than one GPU: tensor parallel over all ranks (every rank decodes the whole "
