@@ -562,7 +562,12 @@ def main() -> None:
     barrier()
     wall = time.perf_counter() - t0
     launches = _lib.launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = None
+    if rank == 0:
+        try:
+            clocks = sampler.stop()
+        except Exception as exc:  # noqa: BLE001 - a malformed sampler line must not cost the measurement
+            clocks = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [f"clock sampler failed: {type(exc).__name__}: {exc}"]}
     # e2e: CUDA events around the K public-API calls (pinned-host inputs copied in, metrics read back, every step).
     # value: the same K steps without the copies - per step, the events the trainer records after its inputs are on
     # the device and after its last optimizer kernel. Both are the maximum over ranks.
