@@ -36,9 +36,11 @@ CONFIGS = {
     # PPO with four 7B-shape models (actor, critic, reference, reward); needs >= 4 GPUs for the two Adam states
     "ppo_7b": dict(algo="ppo", model="llama7b", prompts=64, k=1, prompt_len=128, max_new=512,
                    quantiles=((0.5, 128), (0.85, 256), (1.0, 512)), min_gpus=4),
-    # PPO with a shared 13B actor/critic trunk (LM head + value head) and a 7B-shape reward model
+    # PPO with a shared 13B actor/critic trunk (LM head + value head) and a 7B-shape reward model. Per GPU: 26 GB of bf16
+    # weights + 52 GB of fp32 gradients + 156 GB / N of Adam state + the 13.5 GB reward model + the KV pool: 8 GPUs
+    # (on 4 the construction runs out of memory at 159 GB in use)
     "ppo_acshare_13b": dict(algo="ppo", model="llama13b", prompts=128, k=1, prompt_len=256, max_new=1024, shared=True,
-                            quantiles=((0.5, 256), (0.85, 512), (1.0, 1024)), min_gpus=4),
+                            quantiles=((0.5, 256), (0.85, 512), (1.0, 1024)), min_gpus=8),
     "ppo_tiny": dict(algo="ppo", model="tiny", prompts=16, k=1, prompt_len=32, max_new=64, quantiles=((0.5, 16), (0.9, 32), (1.0, 64))),
     "dpo_tiny": dict(algo="dpo", model="tiny", prompts=16, k=2, prompt_len=32, max_new=64, quantiles=None),
     # GRPO with generation and training on disjoint halves of the GPUs and one step of bounded staleness: generation of
