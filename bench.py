@@ -430,16 +430,12 @@ def main() -> None:
             free_bytes = float(torch.cuda.mem_get_info(device)[0])
             n_l = cfg.n_layers
 
-            def layers_that_fit(micro: int) -> int:
-                per_layer = 1.15 * micro * (7 * cfg.d_model + 3 * cfg.d_ff) * 2
-                reserve = 8e9 + 3.0 * per_layer      # one layer being recomputed, backward temporaries, LM-head chunk, fragmentation
-                return max(0, min(n_l, int((free_bytes - reserve) // per_layer)))
+            from rpeg_b200.engine.memory_policy import choose_kept_layers, layers_that_fit as _fit
 
-            micro = args.micro_tokens
-            fit = layers_that_fit(micro)
-            if fit < n_l and micro >= 16384 and layers_that_fit(micro // 2) > fit:
-                micro //= 2
-                fit = layers_that_fit(micro)
+            def layers_that_fit(micro: int) -> int:
+                return _fit(free_bytes, n_l, cfg.d_model, cfg.d_ff, micro)
+
+            fit, micro = choose_kept_layers(free_bytes, n_l, cfg.d_model, cfg.d_ff, args.micro_tokens)
             choice = torch.tensor([fit, micro], device=device, dtype=torch.int64)
             if world > 1:
                 dist.all_reduce(choice, op=dist.ReduceOp.MIN)
