@@ -394,12 +394,43 @@ sample_kernel(const __nv_bfloat16* __restrict__ logits, int V, int ld, float inv
   const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
   float m = -INFINITY, s = 0.f, best = -INFINITY;
   int best_i = 0;
-  for (int i = threadIdx.x; i < V; i += LP_THREADS) {
-    const float x = __bfloat162float(lr[i]) * inv_temp;
+  auto take = [&](int i, float raw) {
+    const float x = raw * inv_temp;
     online_merge(m, s, x, 1.f);
     float key = x;
     if (!greedy) key += -__logf(-__logf(hash_uniform(seed, row, i)));
-    if (key > best) { best = key; best_i = i; }
+    if (key > best || (key == best && i < best_i)) { best = key; best_i = i; }
+  };
+  if (((reinterpret_cast<uintptr_t>(lr) | static_cast<uintptr_t>(ld) * 2) & 15) == 0) {
+    // 16-byte loads, two in flight per thread: the row is read at memory speed instead of one 2-byte load per
+    // round trip (the noise of an element depends on its index only, so the result does not depend on the order)
+    const uint4* lv = reinterpret_cast<const uint4*>(lr);
+    const int nvec = V >> 3;
+    for (int j = threadIdx.x; j < nvec; j += 2 * LP_THREADS) {
+      const int j2 = j + LP_THREADS;
+      const uint4 a = lv[j];
+      uint4 b = make_uint4(0u, 0u, 0u, 0u);
+      if (j2 < nvec) b = lv[j2];
+      const uint32_t* pa = reinterpret_cast<const uint32_t*>(&a);
+      const uint32_t* pb = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(pa[e]);
+        take(j * 8 + 2 * e, f.x);
+        take(j * 8 + 2 * e + 1, f.y);
+      }
+      if (j2 < nvec) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = unpack_bf16x2(pb[e]);
+          take(j2 * 8 + 2 * e, f.x);
+          take(j2 * 8 + 2 * e + 1, f.y);
+        }
+      }
+    }
+    for (int i = (nvec << 3) + threadIdx.x; i < V; i += LP_THREADS) take(i, __bfloat162float(lr[i]));
+  } else {
+    for (int i = threadIdx.x; i < V; i += LP_THREADS) take(i, __bfloat162float(lr[i]));
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
