@@ -241,6 +241,17 @@ def test_sampler(cuda_device):
     forced[3] = 7
     tok, lp = K.sample(logits, 1.0, False, 5, forced=forced)
     assert tok[3].item() == 7 and abs(lp[3].item() - ref_lp[3, 7].item()) < 2e-3
+    # a vocabulary-sized row (16-byte loads), a row length that is no multiple of 8 and rows that start off a 16-byte
+    # boundary (scalar loads): the same argmax and log-prob on both paths
+    for rows, width in ((8, 32000), (5, 1003), (3, 1001)):
+        wide = (3 * torch.randn(rows, width, device=cuda_device)).bfloat16()
+        tok, lp = K.sample(wide, 0.7, True, 9)
+        assert torch.equal(tok.long(), wide.float().argmax(-1))
+        want = torch.log_softmax(wide.float() / 0.7, -1).gather(1, tok.long()[:, None])[:, 0]
+        assert torch.allclose(lp, want, atol=3e-3)
+        drawn, _ = K.sample(wide, 0.7, False, 77)
+        again, _ = K.sample(wide, 0.7, False, 77)
+        assert torch.equal(drawn, again) and int(drawn.max()) < width
 
 
 def test_scalar_head(cuda_device):
