@@ -208,6 +208,8 @@ def main() -> None:
     ap.add_argument("--gen-slots", type=int, default=0)
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV cache budget per GPU in GB (0 = pick by world size)")
     ap.add_argument("--micro-tokens", type=int, default=16384)
+    ap.add_argument("--gen-tp-size", type=int, default=0, help="tensor-parallel generation in groups of this many consecutive ranks "
+                    "(a divisor of --gpus; generation layout (gpus / t, 1, t)); 0 = one group of all ranks")
     ap.add_argument("--recompute", default="auto", choices=["auto", "full", "none"])
     ap.add_argument("--ref-budget-s", type=float, default=480.0, help="--impl reference: seconds the reference's own run may take "
                     "(writing its model directory included) before the arm reports it as unavailable")
@@ -289,10 +291,13 @@ def main() -> None:
         # One rank keeps the whole fp32 Adam state (81 GB for 7B) and has ~56 GB for KV; sharded ranks have more.
         # the K samples of a prompt share its KV pages, so the pool holds every row of the rank at once
         gen_tp = world > 1 and args.gen_parallel in ("auto", "tp") and not spec.get("pipeline_train")
-        slots = args.gen_slots or min((B if gen_tp else b_local) * Kk, 256)
-        # tensor-parallel generation: a rank holds 1/world of the heads of every row, so the token capacity that one GPU
-        # gets from 56 GB needs 56 / world GB per rank (half as much again is kept as head room)
-        kv_gb = args.kv_gb or ((84.0 / world) if gen_tp else {1: 56.0, 2: 76.0}.get(world, 96.0))
+        tp_size = (args.gen_tp_size or world) if gen_tp else 1
+        if gen_tp and (tp_size < 2 or world % tp_size):
+            raise SystemExit(f"--gen-tp-size {tp_size} must be a divisor (>= 2) of the {world} GPUs")
+        slots = args.gen_slots or min((B * tp_size // world if gen_tp else b_local) * Kk, 256)
+        # tensor-parallel generation: a rank holds 1/t of the heads of every row of its group, so the token capacity that
+        # one GPU gets from 56 GB needs 56 / t GB per rank (half as much again is kept as head room)
+        kv_gb = args.kv_gb or ((84.0 / tp_size) if gen_tp else {1: 56.0, 2: 76.0}.get(world, 96.0))
         if spec.get("pipeline_train"):
             from rpeg_b200.engine.trainers import PipelineGRPOTrainer
             trainer = PipelineGRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo,
@@ -301,7 +306,7 @@ def main() -> None:
             def build(tp: bool, slots_: int, kv_gb_: float, dp_):
                 return GRPOTrainer(cfg, device=device, samples_per_prompt=Kk, max_new=T, prompt_len=S, algo=algo, dp=dp_,
                                    gen_slots=slots_, kv_budget_bytes=kv_gb_ * 1e9, recompute=recompute, seed=42, eos_id=2,
-                                   gen_tp=tp, tp_comm=args.tp_comm,
+                                   gen_tp=tp, tp_comm=args.tp_comm, gen_tp_size=(tp_size if tp and tp_size != world else None),
                                    group_attention={"off": False, "cuda": True, "tc": "tc"}[args.group_attention])
 
             trainer = build(gen_tp, slots, kv_gb, dp)

@@ -63,12 +63,15 @@ def predict_step_seconds(spec: Dict[str, Any], n_gpus: int, *, parallelism: str 
     workload, policy = J.job_workload(cfg, base), J.job_memory_policy(cfg)
     rpeg = build_rpeg(cfg["policy"]["algorithm"], suite, workload)
     g = space.num_devices()
-    gen_tp = "generation tp" in parallelism
+    import re
+    m_tp = re.search(r"generation (?:dp(\d+) x )?tp(\d+)", parallelism)
+    gen_tp = m_tp is not None
+    gen_pi = (int(m_tp.group(1) or 1), 1, int(m_tp.group(2))) if gen_tp else None
     full = Allocation((0, 0, 0), (space.R, space.N, space.G))
     plan = ExecutionPlan()
     for v in rpeg.vertices:
         plan.sigma[v.id], plan.mb[v.id] = full, 1
-        plan.pi[v.id] = (1, 1, g) if (gen_tp and v.kind.role is Role.GENERATION) else (g, 1, 1)
+        plan.pi[v.id] = gen_pi if (gen_tp and v.kind.role is Role.GENERATION) else (g, 1, 1)
     trace, lowered = J.predicted_schedule(Configuration(rpeg, plan, space), suite, workload, hw, 1, policy)
     phases: Dict[str, float] = {}
     for n in lowered.nodes:

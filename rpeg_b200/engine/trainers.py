@@ -98,10 +98,13 @@ class GRPOTrainer(_Base):
                  prompt_len: int = 512, algo: Optional[A.AlgoConfig] = None, lr: float = 1e-6, gen_slots: int = 64,
                  kv_budget_bytes: float = 40e9, recompute: str = "full", dp=None, seed: int = 0, eos_id: int = 2,
                  sync_interval: int = 8, use_graphs: bool = True, gen_tp: bool = False, tp_comm: Optional[str] = None,
-                 group_attention: bool = False):
+                 group_attention: bool = False, gen_tp_size: Optional[int] = None):
         """``gen_tp``: generate tensor parallel over all ranks of ``dp`` (every rank decodes ALL rows of the global batch
         on 1/world of the weights and KV heads, ``models.tp_decode``) while the reference pass, the policy update and the
-        optimizer stay data parallel; ``gen_slots`` is then the number of rows of the whole batch decoded at once."""
+        optimizer stay data parallel; ``gen_slots`` is then the number of rows of the whole batch decoded at once.
+        ``gen_tp_size`` (a divisor of the world size, default: all ranks): generation layout ``(world / t, 1, t)``, i.e.
+        groups of ``t`` consecutive ranks decode the rows of their own prompts tensor parallel; ``gen_slots`` then counts
+        the rows of one group."""
         super().__init__(device, dp)
         self.cfg = cfg
         self.K = samples_per_prompt
@@ -111,6 +114,19 @@ class GRPOTrainer(_Base):
         self.gen_tp = bool(gen_tp) and dp is not None and dp.world > 1
         self.overlap_grad_reduce = True
         tp = dp.world if self.gen_tp else 1
+        self.tp_group, self.tp_rank, self.tp_index = (dp.group if dp is not None else None), (dp.rank if dp is not None else 0), 0
+        if self.gen_tp and gen_tp_size is not None and int(gen_tp_size) != dp.world:
+            import torch.distributed as dist
+            tp = int(gen_tp_size)
+            if tp < 2 or dp.world % tp:
+                raise ValueError(f"gen_tp_size={gen_tp_size} must be a divisor (>= 2) of the {dp.world} ranks")
+            base = dist.get_process_group_ranks(dp.group) if dp.group is not None else list(range(dp.world))
+            for gi in range(dp.world // tp):               # every rank creates every group, in the same order
+                grp = dist.new_group([base[gi * tp + j] for j in range(tp)])
+                if gi == dp.rank // tp:
+                    self.tp_group = grp
+            self.tp_rank, self.tp_index = dp.rank % tp, dp.rank // tp
+        self.tp = tp
         # Gradients are dead while generating and the KV cache is dead while training, so both live
         # in one arena sized for the larger of the two.
         from ..models.llama import ParamLayout
@@ -134,8 +150,9 @@ class GRPOTrainer(_Base):
         self.gen_model = self.actor
         if self.gen_tp:
             from ..models.tp_decode import TPDecodeModel
-            self.gen_model = TPDecodeModel(self.actor, dp.group, max_batch=gen_slots, comm_mode=tp_comm)
-            self.parallelism = f"generation tp{dp.world} ({self.gen_model.comm.backend}), reference + training dp{dp.world}"
+            self.gen_model = TPDecodeModel(self.actor, self.tp_group, max_batch=gen_slots, comm_mode=tp_comm)
+            layout = f"tp{tp}" if tp == dp.world else f"dp{dp.world // tp} x tp{tp}"
+            self.parallelism = f"generation {layout} ({self.gen_model.comm.backend}), reference + training dp{dp.world}"
         self.gen = Generator(self.gen_model, max_slots=gen_slots, max_seq_len=prompt_len + max_new, eos_id=eos_id,
                              sync_interval=sync_interval, use_graphs=use_graphs,
                              kv_storage=arena[: arena_bytes // 2 * 2].view(torch.bfloat16),
@@ -144,11 +161,12 @@ class GRPOTrainer(_Base):
         self.last_reshard_us: Optional[float] = None
 
     def _all_ranks(self, t: torch.Tensor) -> torch.Tensor:
-        """Rows of every rank, in rank order (tensor-parallel generation works on the whole batch)."""
+        """Rows of every rank of this rank's tensor-parallel generation group, in rank order (the group generates the
+        rows of all its members; with one group that is the whole batch)."""
         import torch.distributed as dist
         t = t.contiguous()
-        out = torch.empty((self.dp.world * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
-        dist.all_gather_into_tensor(out, t, group=self.dp.group)
+        out = torch.empty((self.tp * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t, group=self.tp_group)
         return out
 
     def step(self, prompts: torch.Tensor, rewards: Optional[torch.Tensor] = None,
@@ -169,11 +187,12 @@ class GRPOTrainer(_Base):
                 f_all = self._all_ranks(torch.as_tensor(forced_lens, dtype=torch.int32).to(self.device)).tolist()
             rep_all = self._all_ranks(rep)
             whole = self.gen.generate(rep_all, self.max_new, temperature=self.algo.temperature,
-                                      seed=self.seed + 100003 * self.iteration, forced_lens=f_all, group_size=self.K)
+                                      seed=self.seed + 100003 * self.iteration + 7919 * self.tp_index, forced_lens=f_all,
+                                      group_size=self.K)
             # Every rank holds every row now, so the rows of the data-parallel phases (reference pass, policy update)
             # are dealt out by TOKENS rather than by position: whole prompt groups, heaviest first, each to the rank
             # with the least work so far. The phases end when their slowest rank does.
-            mine = balanced_groups(whole.lengths.tolist(), S, self.K, self.dp.world)[self.dp.rank]
+            mine = balanced_groups(whole.lengths.tolist(), S, self.K, self.tp)[self.tp_rank]
             rows = torch.tensor([g * self.K + j for g in mine for j in range(self.K)], dtype=torch.long, device=self.device)
             gen = GenerationResult(whole.tokens[rows].contiguous(), whole.logprobs[rows].contiguous(),
                                    whole.lengths[rows].contiguous(), whole.counters)

@@ -50,3 +50,13 @@ def test_bench_falls_back_to_data_parallel_generation_when_the_start_up_check_fa
     line = _last_json(r.stdout)
     assert line["n_gpus"] == 2 and line["value"] > 0 and line["config"]["parallelism"] == "dp2", line["config"]
     assert "generating data parallel" in r.stderr
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_bench_tiny_four_ranks_generation_in_two_tensor_parallel_groups():
+    """Generation layout (2, 1, 2): two groups of two ranks, each group decodes the rows of its own prompts."""
+    r = _torchrun(4, 29575, "bench.py", "--config", "grpo_tiny", "--gpus", "4", "--steps", "2", "--warmup", "3", "--gen-tp-size", "2")
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = _last_json(r.stdout)
+    assert line["n_gpus"] == 4 and line["value"] > 0 and "dp2 x tp2" in line["config"]["parallelism"], line["config"]
+    assert line["last_step"]["grad_norm"] > 0 and line["last_step"]["samples"] > 0
