@@ -79,8 +79,9 @@ def validate_engine_plan(compiled) -> str:
       ``"pipeline_train"``   generation / inference vertices ``(G, 1, 1)``, every training vertex ``(1, G, 1)`` (GRPO):
                              the update runs 1F1B over all ranks as stages, the publication edge is a real layout
                              switch (stage weights broadcast into the replicated generation copy)
-      ``"tp_generation"``    the generation vertex ``(1, 1, G)``: every GPU decodes the whole batch on its shard of the weights
-                             and KV heads (``models.tp_decode``), every other vertex ``(G, 1, 1)`` (GRPO); the RESHARD node of
+      ``"tp_generation"``    the generation vertex ``(G / t, 1, t)``, t >= 2: groups of t consecutive GPUs decode the rows of
+                             their prompts on 1/t of the weights and KV heads each (``models.tp_decode``; t = G: every GPU
+                             decodes the whole batch), every other vertex ``(G, 1, 1)`` (GRPO); the RESHARD node of
                              the publication edge re-slices the updated weights into the generation layout
       ``"disaggregated"``    generation data parallel on some GPUs, everything else data parallel on the others (GRPO),
                              any staleness ``tau >= 0``: the two sides run concurrently and meet through versioned
@@ -103,7 +104,9 @@ def validate_engine_plan(compiled) -> str:
     train = [v for v in cfg.rpeg.vertices if v.kind.role is Role.TRAINING]
     piped = g > 1 and bool(train) and all(tuple(cfg.plan.pi[v.id]) == (1, g, 1) for v in train)
     gens = [v for v in cfg.rpeg.vertices if v.kind.role is Role.GENERATION]
-    tp_gen = g > 1 and bool(gens) and all(tuple(cfg.plan.pi[v.id]) == (1, 1, g) for v in gens)
+    gen_pis = {tuple(cfg.plan.pi[v.id]) for v in gens}
+    tp_gen = (g > 1 and len(gen_pis) == 1 and next(iter(gen_pis))[1] == 1 and next(iter(gen_pis))[2] >= 2
+              and next(iter(gen_pis))[0] * next(iter(gen_pis))[2] == g)
     for v in cfg.rpeg.vertices:
         dp, pp, tp = cfg.plan.pi[v.id]
         if (piped and v in train) or (tp_gen and v in gens):
@@ -157,6 +160,12 @@ class EngineOperationHandler:
                 self.dp = DPContext(self.device)
         a, w, rt, o = run.algorithm, run.workload, run.runtime, run.optimizer_runtime
         self.algo_name = a.name
+        # width of a tensor-parallel generation group (the world size unless the plan says (G / t, 1, t))
+        self.gen_tp_size = 1
+        if self.family == "tp_generation":
+            from ..core.types import Role
+            self.gen_tp_size = int(next(tuple(compiled.config.plan.pi[v.id]) for v in compiled.config.rpeg.vertices
+                                        if v.kind.role is Role.GENERATION)[2])
         self.shared = any(v.id == "g_ac" for v in compiled.config.rpeg.vertices)
         self.algo = A.AlgoConfig(clip_eps=a.clip, kl_coef=a.kl_coef, beta=a.beta, gamma=a.gamma, gae_lambda=a.gae_lambda,
                                  value_coef=a.value_coef, entropy_coef=a.entropy_coef, temperature=a.temperature,
@@ -188,7 +197,8 @@ class EngineOperationHandler:
             self.trainer = GRPOTrainer(cfg, samples_per_prompt=w.samples_per_prompt, max_new=w.generation_length,
                                        prompt_len=w.context_length, lr=o.learning_rate_actor, gen_slots=rt.gen_slots,
                                        eos_id=run.tokenizer.eos_token_id, use_graphs=rt.use_cuda_graphs,
-                                       gen_tp=self.family == "tp_generation", **common)
+                                       gen_tp=self.family == "tp_generation",
+                                       gen_tp_size=(self.gen_tp_size if 1 < self.gen_tp_size < self.world else None), **common)
         elif a.name == "ppo":
             r = run.models.get("reward")
             self.trainer = PPOTrainer(cfg, max_new=w.generation_length, prompt_len=w.context_length, lr_actor=o.learning_rate_actor,
@@ -233,27 +243,37 @@ class EngineOperationHandler:
         tr, A, torch, w = self.trainer, self.A, self.torch, self.run.workload
         tp_gen = self.family == "tp_generation"
         sl = self._local(w.batch_size)
-        rows_local = slice(sl.start * w.samples_per_prompt, sl.stop * w.samples_per_prompt)
-        # a tensor-parallel generation vertex works on the WHOLE batch on every rank; the data-parallel vertices after
-        # it take their slice of the result
-        prompts = (self._prompts_global(step) if (tp_gen and not self.run.data.train_prompts) else self._prompts(step)).to(self.device)
-        if tp_gen and self.run.data.train_prompts:
-            prompts = tr._all_ranks(prompts)
-        rep = prompts.repeat_interleave(w.samples_per_prompt, dim=0).contiguous()
+        K_ = w.samples_per_prompt
+        rows_local = slice(sl.start * K_, sl.stop * K_)
+        # a tensor-parallel generation group works on the prompts of ALL its members (t = world: the whole batch) on every
+        # member; the data-parallel vertices after it take their slice of the result
+        t = self.gen_tp_size if tp_gen else 1
+        gi = self.rank // t if tp_gen else 0
+        per_group = w.batch_size * t // self.world if tp_gen else w.batch_size
+        group = slice(gi * per_group, (gi + 1) * per_group)                # prompts of this rank's group
+        rows_group = slice(group.start * K_, group.stop * K_)
+        if tp_gen and not self.run.data.train_prompts:
+            prompts = self._prompts_global(step)[group].to(self.device)
+        else:
+            prompts = self._prompts(step).to(self.device)
+            if tp_gen:
+                prompts = tr._all_ranks(prompts)                            # gathered over the group
+        rep = prompts.repeat_interleave(K_, dim=0).contiguous()
         a = self.run.algorithm
         forced = None
         if self.run.data.synthetic_response_lengths == "quantiles" and w.gen_quantiles:
             from .data import quantile_lengths
-            rows = w.batch_size * w.samples_per_prompt                 # drawn for the global batch, cut like the prompts
+            rows = w.batch_size * K_                                        # drawn for the global batch, cut like the prompts
             all_lens = quantile_lengths(rows, w.quantile_tuples(), seed=self.run.data.data_seed * 1000003 + step)
-            forced = all_lens if tp_gen else all_lens[rows_local]
-        gen = tr.gen.generate(rep, w.generation_length, temperature=a.temperature, greedy=a.greedy, seed=a.seed + 100003 * step,
-                              group_size=w.samples_per_prompt, top_k=a.top_k, top_p=a.top_p, forced_lens=forced)
+            forced = all_lens[rows_group] if tp_gen else all_lens[rows_local]
+        gen = tr.gen.generate(rep, w.generation_length, temperature=a.temperature, greedy=a.greedy,
+                              seed=a.seed + 100003 * step + 7919 * gi, group_size=K_, top_k=a.top_k, top_p=a.top_p, forced_lens=forced)
         if tp_gen:
             from ..engine.generation import GenerationResult
-            gen = GenerationResult(gen.tokens[rows_local].contiguous(), gen.logprobs[rows_local].contiguous(),
-                                   gen.lengths[rows_local].contiguous(), gen.counters)
-            rep = rep[rows_local].contiguous()
+            mine = slice(rows_local.start - rows_group.start, rows_local.stop - rows_group.start)
+            gen = GenerationResult(gen.tokens[mine].contiguous(), gen.logprobs[mine].contiguous(),
+                                   gen.lengths[mine].contiguous(), gen.counters)
+            rep = rep[mine].contiguous()
         lens = gen.lengths.tolist()
         st["rollout"] = A.Rollout(rep, [w.context_length] * rep.shape[0], gen.tokens, lens, gen.logprobs, gen.response_mask(),
                                   weight_version=self.latest.get("ac_share" if self.shared else "actor", 0))

@@ -243,7 +243,7 @@ def predicted_schedule(config: Configuration, suite, workload, hw, horizon: int,
 
 
 def data_parallel_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k_eval: int, policy: MemoryPolicy, fusion: bool,
-                                transfer_policy, *, pipeline_train: bool = False, tp_generation: bool = False) -> Optional[Configuration]:
+                                transfer_policy, *, pipeline_train: bool = False, tp_generation: int = 0) -> Optional[Configuration]:
     """The plan families the engine backend executes, all on the whole device space: every vertex data parallel over
     all GPUs (``pi = (G, 1, 1)``), or, with ``pipeline_train``, generation and inference data parallel and every
     training vertex pipeline parallel over all GPUs (``pi = (1, G, 1)``: gradients and optimizer state of a stage
@@ -261,9 +261,11 @@ def data_parallel_configuration(rpeg, space: DeviceSpace, suite, workload, hw, k
             if pipeline_train and v.kind.role is Role.TRAINING:
                 plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (1, g, 1), max(mb, g)
             elif tp_generation and v.kind.role is Role.GENERATION:
-                # every GPU decodes the whole batch on 1/G of the weights and KV heads; the publication edge from the
-                # data-parallel training vertex to this one is a layout switch (RESHARD node)
-                plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (1, 1, g), 1
+                # groups of t GPUs decode the rows of their prompts on 1/t of the weights and KV heads each (t = G: every
+                # GPU decodes the whole batch); the publication edge from the data-parallel training vertex to this one
+                # is a layout switch (RESHARD node)
+                t = g if tp_generation is True else int(tp_generation)
+                plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (g // t, 1, t), 1
             else:
                 plan.sigma[v.id], plan.pi[v.id], plan.mb[v.id] = full, (g, 1, 1), mb
         last = Configuration(rpeg, plan, space, fusion, transfer_policy)
@@ -486,10 +488,25 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
         for kind in kinds:
             if kind != "dp" and (algorithm != "grpo" or space.num_devices() < 2):
                 continue
-            c = data_parallel_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy,
-                                            pipeline_train=kind == "pp", tp_generation=kind == "tp")
-            if c is not None:
-                cands.append((predicted_schedule(c, suite, workload, hw, horizon, policy)[0].makespan(), len(cands), c))
+            # generation layout (G / t, 1, t): t = G unless optimizer.generation_tp names a divisor of G, or "auto" lets
+            # the cost model choose among the divisors that also divide the attention heads
+            g_all = space.num_devices()
+            widths = [0]
+            if kind == "tp":
+                want = options.get("generation_tp", g_all)
+                actor_spec = suite.specs.get(Model.ACTOR) or suite.specs.get(Model.AC_SHARE)
+                heads = 0 if actor_spec is None else actor_spec.d // max(1, actor_spec.d_head)
+                if str(want) == "auto":
+                    widths = [t for t in range(2, g_all + 1) if g_all % t == 0 and (heads == 0 or heads % t == 0)] or [g_all]
+                else:
+                    if int(want) < 2 or g_all % int(want):
+                        raise RuntimeConfigError(f"[optimizer] generation_tp={want} must be a divisor (>= 2) of the {g_all} GPUs")
+                    widths = [int(want)]
+            for t in widths:
+                c = data_parallel_configuration(rpeg, space, suite, workload, hw, k_eval, policy, fusion, transfer_policy,
+                                                pipeline_train=kind == "pp", tp_generation=t)
+                if c is not None:
+                    cands.append((predicted_schedule(c, suite, workload, hw, horizon, policy)[0].makespan(), len(cands), c))
         best = min(cands)[2] if cands else None
         if best is None:
             raise RuntimeConfigError(f"no plan of family {family!r} fits into memory on this machine")

@@ -193,6 +193,32 @@ def test_engine_jobs_can_ask_for_tensor_parallel_generation(tmp_path):
         plan_runtime_job(tmp_path / "job2.yaml", tmp_path / "out2", quiet=True)
 
 
+def test_tensor_parallel_generation_in_groups_of_ranks(tmp_path):
+    """``optimizer.generation_tp: t``: the generation vertex ``(G / t, 1, t)`` (groups of t GPUs decode the rows of their own
+    prompts); ``auto`` lets the cost model choose among the divisors of G; anything else is refused."""
+    from rpeg_b200.runtime.engine_backend import validate_engine_plan
+    cfg = job_mapping("grpo", steps=2, runtime={"default_backend": "engine", "gen_slots": 16, "micro_tokens": 1024})
+    cfg["device_space"] = {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4}
+    cfg["optimizer"].update(plan_family="tp_generation", generation_tp=2)
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    res = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out", quiet=True)
+    compiled = res["compiled"]
+    assert tuple(compiled.config.plan.pi["g_pi"]) == (2, 1, 2) and tuple(compiled.config.plan.pi["t_pi"]) == (4, 1, 1)
+    assert validate_engine_plan(compiled) == "tp_generation"
+    assert any(n.kind is ExecNodeType.RESHARD for n in compiled.lowered.nodes)
+    graph, ctx, events = execute(compile_runtime_plan(res["run_file"]), tmp_path)
+    assert verify_runtime_trace(compiled, graph, events)["ok"]
+    cfg["optimizer"]["generation_tp"] = "auto"
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    auto = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out2", quiet=True)["compiled"]
+    dp, pp, tp = auto.config.plan.pi["g_pi"]
+    assert pp == 1 and tp in (2, 4) and dp * tp == 4 and validate_engine_plan(auto) == "tp_generation"
+    cfg["optimizer"]["generation_tp"] = 3
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    with pytest.raises(RuntimeConfigError, match="divisor"):
+        plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out3", quiet=True)
+
+
 @pytest.mark.parametrize("tau", [0, 1])
 def test_engine_jobs_can_put_generation_and_training_on_disjoint_gpus(tmp_path, tau):
     """``optimizer.plan_family: disaggregated``: generation data parallel on ``gen_gpus`` GPUs, the rest on the others; with
