@@ -150,3 +150,34 @@ def test_runtime_graph_with_tensor_parallel_generation_on_two_ranks(tmp_path):
         assert switches and all(e["counters"]["reshard_us"] > 0 and e["counters"]["transferred_bytes"] > 0 for e in switches)
     summary = json.loads((tmp_path / "out/metrics/summary.json").read_text())
     assert summary["nodes_failed"] == 0 and summary["logical_steps"] == 2 and summary["nonfinite_losses"] == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_runtime_graph_with_generation_in_two_tensor_parallel_groups_on_four_ranks(tmp_path):
+    """``optimizer.generation_tp: 2`` on four ranks: generation layout (2, 1, 2). Each group of two ranks decodes the rows of
+    its own prompts tensor parallel; every rank then trains on its slice and the gradients are reduced over all four."""
+    from rpeg_b200.runtime.io import dump_mapping
+    from rpeg_b200.runtime.job_plan import plan_runtime_job
+    from rpeg_b200.runtime.trace import read_trace
+    tiny = {"layers": 2, "hidden_dim": 256, "ffn_dim": 512, "vocab_size": 512, "head_dim": 128}
+    cfg = {"run_id": "grpo-4gpu-tpgroups", "policy": {"algorithm": "grpo"}, "hardware": {"preset": "b200_nvswitch"},
+           "device_space": {"racks": 1, "nodes_per_rack": 1, "gpus_per_node": 4},
+           "models": {"actor": tiny, "reference": {"source": "actor"}},
+           "workload": {"batch_size": 8, "samples_per_prompt": 2, "context_length": 32, "generation_length": 48,
+                        "gen_quantiles": [[0.5, 16], [1.0, 48]]},
+           "training": {"max_steps": 2}, "optimizer": {"k_eval": 2, "plan_family": "tp_generation", "generation_tp": 2},
+           "data": {"synthetic_response_lengths": "quantiles"}, "runtime_hardware": {"worker_overhead_bytes": 0},
+           "runtime": {"default_backend": "engine", "gen_slots": 16, "micro_tokens": 1024}, "outputs": {"seed": 3}}
+    dump_mapping(cfg, tmp_path / "job.yaml")
+    res = plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out", quiet=True)
+    assert tuple(res["compiled"].config.plan.pi["g_pi"]) == (2, 1, 2)
+    r = _torchrun(4, 29576, "-m", "rpeg_b200.runtime.run", "--config", str(res["run_file"]))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    for trace in ("run.jsonl", "run.rank1.jsonl", "run.rank2.jsonl", "run.rank3.jsonl"):
+        events = read_trace(tmp_path / "out/traces" / trace)
+        gen = [e for e in events if e["event"] == "finish" and e["node_id"].startswith("g_pi@") and "generated_tokens" in e["counters"]]
+        assert len(gen) == 2 and all(e["counters"]["generated_tokens"] > 0 for e in gen)
+        train = [e for e in events if e["event"] == "finish" and e["node_id"].startswith("t_pi@")]
+        assert len(train) == 2 and all(e["status"] == "ok" and e["counters"]["grad_norm"] > 0 for e in train)
+    summary = json.loads((tmp_path / "out/metrics/summary.json").read_text())
+    assert summary["nodes_failed"] == 0 and summary["logical_steps"] == 2 and summary["nonfinite_losses"] == 0
