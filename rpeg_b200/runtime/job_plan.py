@@ -488,12 +488,12 @@ def plan_runtime_job(config_path, out_dir=None, *, emit_launch: bool = False, em
         for kind in kinds:
             if kind != "dp" and (algorithm != "grpo" or space.num_devices() < 2):
                 continue
-            # generation layout (G / t, 1, t): t = G unless optimizer.generation_tp names a divisor of G, or "auto" lets
-            # the cost model choose among the divisors that also divide the attention heads
+            # generation layout (G / t, 1, t): t = G unless optimizer.generation_tp names a divisor of G, or "auto" (the
+            # default of plan_family engine) lets the cost model choose among the divisors that also divide the attention heads
             g_all = space.num_devices()
             widths = [0]
             if kind == "tp":
-                want = options.get("generation_tp", g_all)
+                want = options.get("generation_tp", "auto" if family == "engine" else g_all)
                 actor_spec = suite.specs.get(Model.ACTOR) or suite.specs.get(Model.AC_SHARE)
                 heads = 0 if actor_spec is None else actor_spec.d // max(1, actor_spec.d_head)
                 if str(want) == "auto":
