@@ -1,6 +1,6 @@
 """Puts a runnable copy of the reference under ``baseline/_ref`` for ``bench.py --impl reference``.
 
-    python baseline/install_ref.py [--source /root/reference] [--force]
+    python baseline/install_ref.py [--source <reference source tree>] [--force]
 
 The reference is pure Python and is run from its source tree (``PYTHONPATH=<tree>/RPEG:<tree>``, as its own
 runtime README does); its build backend (hatchling) is not available offline, so ``pip install`` of it
