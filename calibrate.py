@@ -8,8 +8,9 @@ What is measured, all with CUDA events after warm-up (3 warm, 10 timed, median) 
   memory_bandwidth      a 1 GiB device copy with this framework's 16-byte copy kernel
   flops_per_gpu         the tcgen05 bf16 GEMM at 8192^3
   gemm_m_half           a sweep of x[M,4096] @ W[4096,4096]^T over M, least-squares fit of eta(M) = M / (M + m_half)
-  decode_bw_eff         one CUDA-graph decode step of a 7B-shape model (batch 64, context 576) against the
-                        bytes it has to move (weights once + the KV of every live row)
+  decode_layer_chain_s  CUDA-graph decode steps of a 7B-shape model at 8 and 64 rows (context 576) against the bytes they
+  decode_row_layer_s    have to move (weights once + the KV of every live row) at the copy rate: what is left is the
+                        latency of a layer's chain of dependent kernels and the per-row work (decode_bw_eff is 1.0)
   non_gemm_constant/..  RMSNorm + RoPE + SwiGLU + flash attention of one layer at the calibration batch
   alpha/beta (g tier)   NCCL all-reduce sweep and peer-to-peer ping-pong inside the node (needs >= 2 ranks);
                         the inter-node tiers keep the preset's values (a job is one NVSwitch node)
@@ -110,20 +111,30 @@ def bench_decode(dev, hbm: float, layers: int) -> Dict[str, float]:
         gen.gen_count.fill_(1)
         gen.token.fill_(5)
 
-    reset()
-    t = timed(lambda: gen._step(b, 1.0, False, 0), warm=3, iters=20)
     weights = 2 * sum(int(p.numel()) for k, p in model.p.items() if k != "embed")
-    kv = b * (ctx + 12) * 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2
+    kv_row = (ctx + 12) * 2 * cfg.n_layers * cfg.n_kv_heads * cfg.head_dim * 2
+    times = {}
+    for rows in (8, b):                       # a small and a large batch: the step's fixed and per-row parts
+        reset()
+        times[rows] = timed(lambda: gen._step(rows, 1.0, False, 0), warm=3, iters=20)
+    t = times[b]
+    kv = b * kv_row
     del gen, model
     torch.cuda.empty_cache()
-    # The cost model prices the weight stream at decode_bw_eff and the K/V stream at min(1, 3.5 * decode_bw_eff)
-    # (RPEG/model/cost.py:330-404). The paged attention kernel reads K/V at the copy rate, so the step is
-    # t = (weights / e_w + kv) / hbm, which gives the weight-stream efficiency e_w of the skinny GEMMs.
+    # The step costs its bytes at the copy rate (the attention kernel and, within a few per cent, the skinny GEMMs
+    # stream at that rate) plus the latency of every layer's chain of dependent kernels plus per-row work:
+    #   t(rows) = (weights + rows * kv_row) / hbm + layers * (chain + per_row * rows)
+    per_row = ((times[b] - times[8]) - (b - 8) * kv_row / hbm) / (cfg.n_layers * (b - 8))
+    per_row = max(0.0, per_row)
+    chain = max(0.0, (times[8] - (weights + 8 * kv_row) / hbm) / cfg.n_layers - per_row * 8)
+    # the older single factor (weight stream efficiency with everything else folded in), kept for comparison
     t_w = t - kv / hbm
     e_w = weights / hbm / t_w if t_w > 0 else 1.0
-    if 3.5 * e_w < 1.0:                      # K/V would be priced below the copy rate too: solve with both terms
+    if 3.5 * e_w < 1.0:
         e_w = (weights + kv / 3.5) / hbm / t
-    return {"decode_step_s": t, "decode_bw_eff": min(1.0, e_w), "decode_step_traffic_fraction": min(1.0, (weights + kv) / hbm / t)}
+    return {"decode_step_s": t, "decode_step_small_s": times[8], "decode_bw_eff": 1.0, "decode_bw_eff_single_factor": min(1.0, e_w),
+            "decode_layer_chain_s": chain, "decode_row_layer_s": per_row,
+            "decode_step_traffic_fraction": min(1.0, (weights + kv) / hbm / t)}
 
 
 def bench_non_gemm(dev, batch: int = 64, seq: int = 640) -> Dict[str, float]:
@@ -297,7 +308,10 @@ def main(argv=None) -> int:
         if "decode" not in skip:
             d = bench_decode(dev, float(hw["memory_bandwidth"]), args.decode_layers)
             hw["decode_bw_eff"] = d["decode_bw_eff"]
+            hw["decode_layer_chain_s"], hw["decode_row_layer_s"] = d["decode_layer_chain_s"], d["decode_row_layer_s"]
             detail["decode_step_s"] = d["decode_step_s"]
+            detail["decode_step_small_s"] = d["decode_step_small_s"]
+            detail["decode_bw_eff_single_factor"] = d["decode_bw_eff_single_factor"]
         hw["memory_per_gpu"] = float(torch.cuda.get_device_properties(dev).total_memory)
     if world > 1:
         dist.barrier()
@@ -310,6 +324,9 @@ def main(argv=None) -> int:
         if "fused" not in skip:
             f = bench_fused_paths(dev, world)
             hw["tp_decode_allreduce_s"] = float(f["tp_decode"]["allreduce_rmsnorm_us"]) * 1e-6
+            small = [v for k, v in f["tp_decode"].items() if k.endswith("rows_one_shot_us")]
+            if small:
+                hw["tp_decode_allreduce_small_s"] = float(min(small)) * 1e-6
             hw["dp_reduce_gbs"] = float(f["dp_reduce_gbs"])
             detail["fused_paths"] = f
         dist.barrier()
