@@ -219,6 +219,27 @@ def test_tensor_parallel_generation_in_groups_of_ranks(tmp_path):
         plan_runtime_job(tmp_path / "job.yaml", tmp_path / "out3", quiet=True)
 
 
+def test_engine_family_chooses_the_generation_layout_of_the_flagship_job(tmp_path):
+    """``plan_family: engine`` on the flagship GRPO job (Llama-7B, 32 prompts x 8 samples, lengths by quantiles) with the
+    measured hardware file: generation tensor parallel from 2 GPUs on, in two groups of four at 8 GPUs (the decode step's
+    per-row work and all-reduce launches grow with the rows a group decodes), everything else data parallel."""
+    from rpeg_b200.analytic.predict import bench_job_mapping
+    spec = dict(algo="grpo", model="llama7b", prompts=32, k=8, prompt_len=512, max_new=2048,
+                quantiles=((0.5, 512), (0.9, 1024), (1.0, 2048)))
+    chosen = {}
+    for n in (2, 8):
+        cfg = bench_job_mapping(spec, n, recompute_fraction=0.0)
+        cfg["optimizer"]["plan_family"] = "engine"
+        cfg["training"] = {"max_steps": 1}
+        dump_mapping(cfg, tmp_path / f"job{n}.yaml")
+        res = plan_runtime_job(tmp_path / f"job{n}.yaml", tmp_path / f"out{n}", quiet=True)
+        pi = res["compiled"].config.plan.pi
+        chosen[n] = tuple(pi["g_pi"])
+        assert tuple(pi["t_pi"]) == (n, 1, 1) and tuple(pi["i_ref"]) == (n, 1, 1)
+    assert chosen[2] == (1, 1, 2)
+    assert chosen[8][1] == 1 and chosen[8][2] >= 2 and chosen[8][0] * chosen[8][2] == 8
+
+
 @pytest.mark.parametrize("tau", [0, 1])
 def test_engine_jobs_can_put_generation_and_training_on_disjoint_gpus(tmp_path, tau):
     """``optimizer.plan_family: disaggregated``: generation data parallel on ``gen_gpus`` GPUs, the rest on the others; with
