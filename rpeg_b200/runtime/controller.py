@@ -47,6 +47,8 @@ class WorkerGroupSpec:
     cuda: bool = False
     env: Dict[str, str] = field(default_factory=dict)
     collective_timeout_s: float = 30.0
+    hosts: Tuple[str, ...] = ()          # host of every rank (Slurm launcher); empty: all ranks on this host
+    connect_host: Optional[str] = None    # where rank 0's request port is reachable (default: loopback)
 
 
 @dataclass
@@ -61,8 +63,8 @@ class _Journalled:
 class GroupClient:
     """Socket to rank 0 of one worker group."""
 
-    def __init__(self, port: int, connect_timeout_s: float = 10.0):
-        self.sock = socket.create_connection(("127.0.0.1", port), timeout=connect_timeout_s)
+    def __init__(self, port: int, connect_timeout_s: float = 10.0, host: str = "127.0.0.1"):
+        self.sock = socket.create_connection((host, port), timeout=connect_timeout_s)
 
     def request(self, operation: str, *, node_id: str, step: int, payload: Optional[Dict[str, Any]] = None,
                 timeout_s: Optional[float] = None) -> List[Any]:
@@ -92,8 +94,10 @@ class _Managed:
 
 class WorkerGroupController:
     def __init__(self, heartbeat_dir, *, restart_retries: int = 1, log_dir: Optional[str] = None, ready_timeout_s: float = 120.0,
-                 stale_after_s: Optional[float] = None):
-        self.launcher = LocalWorkerGroupLauncher(heartbeat_dir)
+                 stale_after_s: Optional[float] = None, launcher=None):
+        """``launcher``: a ``LocalWorkerGroupLauncher`` (default) or a ``SlurmWorkerGroupLauncher`` on the same heartbeat
+        directory; with the latter every group is one ``srun`` step and a restart starts a new step."""
+        self.launcher = launcher if launcher is not None else LocalWorkerGroupLauncher(heartbeat_dir)
         self.restart_retries = int(restart_retries)
         self.log_dir = log_dir
         self.ready_timeout_s = ready_timeout_s
@@ -120,16 +124,30 @@ class WorkerGroupController:
         env["RPEG_LAUNCH_GENERATION"] = str(gen)
         self.launcher.launch(WorkerLaunch(spec.worker_id, "rpeg_b200.runtime.service",
                                           ("--table", spec.table, "--backend", spec.backend, "--collective-timeout", str(spec.collective_timeout_s)),
-                                          single_node_assignments(spec.world, (spec.worker_id,), cuda=spec.cuda),
+                                          self._assignments(spec),
                                           master_port=spec.master_port + gen, env=env, log_dir=self.log_dir))
         beats = self.launcher.wait_ready(spec.worker_id, self.ready_timeout_s)
         try:
             port = int(json.loads(beats[0].message)["port"])
-            client = GroupClient(port)
+            client = GroupClient(port, host=spec.connect_host or "127.0.0.1")
         except Exception as exc:
             self.launcher.stop(spec.worker_id, grace_s=1.0)
             raise RuntimeExecutionError(f"{spec.worker_id}: rank 0 came up without a usable request port ({exc})") from exc
         return _Managed(spec, client, gen)
+
+    @staticmethod
+    def _assignments(spec: WorkerGroupSpec):
+        if not spec.hosts:
+            return single_node_assignments(spec.world, (spec.worker_id,), cuda=spec.cuda)
+        if len(spec.hosts) != spec.world:
+            raise RuntimeExecutionError(f"{spec.worker_id}: {len(spec.hosts)} hosts for {spec.world} ranks")
+        from .launcher import RankAssignment
+        local: Dict[str, int] = {}
+        out = []
+        for r, h in enumerate(spec.hosts):
+            out.append(RankAssignment(r, local.get(h, 0), h, local.get(h, 0) if spec.cuda else None, (spec.worker_id,)))
+            local[h] = local.get(h, 0) + 1
+        return out
 
     def shutdown(self, timeout_s: float = 30.0) -> None:
         for wid, m in list(self._groups.items()):
