@@ -441,3 +441,31 @@ def test_published_results_reader_and_charts(tmp_path):
     assert len(written) == 3 and all(p.read_text().startswith("<svg") for p in written)
     (tmp_path / "nothing_here").mkdir()
     assert ppr.main(["--results", str(tmp_path / "nothing_here")]) == 1
+
+
+def test_bench_clock_sampler_reads_every_gpu_of_the_job():
+    """``bench.py``'s sampler parses ``nvidia-smi`` lines of several GPUs: overall median, per-GPU medians (the slowest GPU
+    sets the pace of a multi-GPU step), the union of the throttle reasons; malformed lines are skipped."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+
+    class Done:
+        def terminate(self):
+            pass
+
+    s = bench.ClockSampler([0, 1])
+    s.proc = Done()
+    s.lines = ["0, 1965, 1965, 800.1, Not Active, Not Active, Not Active, Active",
+               "1, 1500, 1965, 900.0, Not Active, Not Active, Not Active, Active",
+               "0, 1900, 1965, 810.3, Not Active, Not Active, Not Active, Not Active",
+               "1, 1410, 1965, 905.0, Not Active, Not Active, Active, Active",
+               "garbage line", "1, [N/A], 1965, x, -, -, -, -"]
+    out = s.stop()
+    assert out["samples"] == 4 and out["sm_max_mhz"] == 1965.0
+    assert out["sm_mhz_per_gpu"] == {"0": 1965.0, "1": 1500.0}
+    assert out["reasons"] == ["sw_power_cap", "sw_thermal_slowdown"]
+    one = bench.ClockSampler(0)
+    one.proc, one.lines = Done(), ["0, 1800, 1965, 700, Not Active, Not Active, Not Active, Not Active"]
+    assert one.stop() == {"sm_mhz": 1800.0, "sm_max_mhz": 1965.0, "reasons": [], "samples": 1}
