@@ -228,7 +228,8 @@ class NodeCostModel:
         m_half = hw.gemm_m_half
         tok = prompt_rows * w.S
         eta = tok / (tok + m_half) if m_half > 0 else 1.0
-        flops = tok * (2 * Lpp / pt) * sh.layer_flops_per_token(w.S) + prompt_rows * 2 * sh.V * sh.d / pt
+        pt_prefill = 1 if hw.tp_prefill_replicated > 0 else pt
+        flops = tok * (2 * Lpp / pt_prefill) * sh.layer_flops_per_token(w.S) + prompt_rows * 2 * sh.V * sh.d / pt_prefill
         t_total = flops / (hw.flops_per_gpu * hw.sustained_flops_fraction * max(eta, 1e-6))
         cap = self._gen_concurrency(node, rows, w.S + self._mean_len() / 2.0)
 

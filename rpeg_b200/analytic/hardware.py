@@ -68,6 +68,8 @@ class Hardware:
     #                                            round trip); replaces the alpha-beta estimate for decode-sized messages
     tp_decode_allreduce_small_s: float = 0.0   # > 0: the same for rows x ranks <= 256, where the launch is ONE exchange
     #                                            (self-validating units pushed to every rank, reduced locally)
+    tp_prefill_replicated: float = 0.0         # > 0: a tensor-parallel generation group prefills its prompts on every member
+    #                                            (the engine's generator does; the reference's model shards the prefill)
     decode_layer_chain_s: float = 0.0          # per decode step and layer: latency of the chain of dependent kernels of a
     #                                            layer (what a step costs beyond its bytes at the copy rate, at any batch)
     decode_row_layer_s: float = 0.0            # per decode step, layer and live row: the per-row work of the element-wise
