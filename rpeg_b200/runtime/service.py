@@ -9,6 +9,7 @@ operations may use collectives among the ranks), the per-rank results are gather
 ``{"ok": true, "results": [...]}`` or ``{"ok": false, "error": ...}``. A rank whose operation raised reports an
 ``error`` heartbeat, the group answers the request with the error and leaves: the controller decides whether the
 group can be started again and brought back to its state by replaying the journal of its state-building requests.
+A group whose controller closed the connection (or died) shuts itself down.
 
 Tables: ``toy`` keeps a small CPU tensor per rank as "the model" (control-plane tests, no GPU); ``engine`` holds
 ``LlamaModel`` + ``AdamW`` on the rank's GPU. Operations shared by both: ``build_model``, ``load_weight_version``,
@@ -216,13 +217,20 @@ def main(argv: Optional[List[str]] = None) -> int:
         else:
             store.write(group, rank, "ready")
         while True:
-            box: List[Any] = [recv_message(conn) if rank == 0 else None]
+            box: List[Any] = [None]
+            if rank == 0:
+                try:
+                    box[0] = recv_message(conn)
+                except (ConnectionError, OSError):
+                    # the controller is gone (it closed the connection or died): nobody will ever send a request again,
+                    # so the group leaves in an orderly way instead of lingering on its GPUs
+                    box[0] = {"operation": "shutdown", "orphaned": True}
             if world > 1:
                 dist.broadcast_object_list(box, src=0)
             req = box[0]
             op, payload = req["operation"], req.get("payload") or {}
             if op == "shutdown":
-                if rank == 0:
+                if rank == 0 and not req.get("orphaned"):
                     send_message(conn, {"ok": True, "results": []})
                 break
             mode = _injected(op, rank)

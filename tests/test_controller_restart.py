@@ -133,6 +133,19 @@ def test_paired_requests_check_both_groups_first_and_abort_both_on_failure(tmp_p
         ctl.shutdown()
 
 
+def test_a_group_whose_controller_is_gone_shuts_itself_down(tmp_path):
+    ctl = WorkerGroupController(tmp_path / "hb", log_dir=str(tmp_path / "logs"))
+    try:
+        ctl.start(_spec("actor", 2, PORT + 70))
+        ctl.request("actor", "build_model", node_id="build", step=0)
+        ctl._groups["actor"].client.close()                       # the controller's side of the connection disappears
+        beats = ctl.launcher.control.wait_for_state("actor", 2, ("finished",), 30.0)
+        assert [b.state for b in beats] == ["finished", "finished"]
+        assert ctl.launcher.wait_finished("actor", 10.0) == [0, 0]
+    finally:
+        ctl.launcher.stop_all()
+
+
 def test_which_operations_count_as_mutating():
     assert operation_mutates_model("lm_training_step") and operation_mutates_model("policy_train_step")
     assert not operation_mutates_model("checksum") and not operation_mutates_model("generate")
