@@ -477,6 +477,18 @@ def main() -> None:
             extra["cost_model"] = {"predicted_s": pred["step_s"], "measured_s": meas, "err": (pred["step_s"] - meas) / meas,
                                    "phases_s": pred.get("phases_s"), "hardware": pred.get("hardware")}
             extra["cost_model_err"] = abs(pred["step_s"] - meas) / meas
+            if world >= 4 and spec["algo"] == "grpo" and not spec.get("pipeline_train"):
+                # what the model expects from the other generation layouts on this many GPUs (--gen-tp-size)
+                try:
+                    alts = {}
+                    for t in [t for t in range(2, world + 1) if world % t == 0 and cfg.n_heads % t == 0]:
+                        name = f"tp{t}" if t == world else f"dp{world // t} x tp{t}"
+                        alts[name] = round(predict_step_seconds(spec, world, parallelism=f"generation {name}",
+                                                                recompute_fraction=frac)["step_s"], 3)
+                    alts[f"dp{world}"] = round(predict_step_seconds(spec, world, parallelism=f"dp{world}", recompute_fraction=frac)["step_s"], 3)
+                    extra["cost_model"]["predicted_s_by_generation_layout"] = alts
+                except Exception:  # noqa: BLE001 - an extra, never at the cost of the prediction above
+                    pass
         except Exception as exc:  # noqa: BLE001 - the prediction is a report, it must not fail the measurement
             extra["cost_model"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
         return extra
